@@ -1,0 +1,14 @@
+// Thread-local error message shared by the host library and the C ABI.
+#pragma once
+#include <string>
+namespace mg {
+void set_error(std::string const &msg);
+char const *last_error();
+// wraps a cudaError_t-returning call: on failure records the message and returns MG_ERR_CUDA
+int cuda_status(int cuda_error, char const *what);
+} // namespace mg
+#define MG_CUDA_TRY(expr)                                  \
+  do {                                                     \
+    int mg_st_ = mg::cuda_status((int)(expr), #expr);      \
+    if (mg_st_ != 0) return mg_st_;                        \
+  } while (0)

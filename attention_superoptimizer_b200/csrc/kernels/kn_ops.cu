@@ -1,0 +1,187 @@
+// Kernel-level (un-fused) operators in both modes.  They produce the fingerprints a fused
+// candidate is compared against (the reference's compute_*_fingerprint kernels under
+// src/kernel/cuda/) and their float counterparts.  Memory-bound element-wise code: grid-stride
+// loops sized to the SM count, one exact 64-bit sum per matmul output.
+#include "common.cuh"
+
+namespace mgk {
+
+static int blocks_for(int64_t n, int threads = 256) {
+  int64_t blocks = (n + threads - 1) / threads, cap = 148 * 8;
+  return (int)(blocks < 1 ? 1 : (blocks > cap ? cap : blocks));
+}
+
+// C[b] = A[b] x B[b] modulo PQ; dense row-major operands (matmul_kernel.cu:145-173)
+__global__ void kn_matmul_fp_kernel(uint16_t const *A, uint16_t const *B, uint16_t *C, int batches, int m, int n, int k) {
+  int64_t total = (int64_t)batches * m * n, stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    int64_t b = i / ((int64_t)m * n);
+    int r = (int)((i / n) % m), c = (int)(i % n);
+    uint16_t const *a = A + b * m * k + (int64_t)r * k, *bb = B + b * k * n + c;
+    unsigned long long acc = 0;
+    for (int kk = 0; kk < k; kk++) acc += (unsigned long long)((uint32_t)a[kk] * (uint32_t)bb[(int64_t)kk * n]);
+    C[i] = (uint16_t)(acc % PQ);
+  }
+}
+
+__global__ void kn_exp_fp_kernel(uint16_t const *x, uint16_t *y, int64_t n) {
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) y[i] = (uint16_t)field_exp(x[i]);
+}
+
+struct Dims4 { int d[4]; };
+
+__device__ __forceinline__ void broadcast_index(int64_t i, Dims4 const &xd, Dims4 const &yd, Dims4 const &zd,
+                                                int64_t &xi, int64_t &yi) {
+  int64_t xs = 1, ys = 1;
+  xi = yi = 0;
+  for (int d = 3; d >= 0; d--) {
+    xi += (i % xd.d[d]) * xs;
+    yi += (i % yd.d[d]) * ys;
+    xs *= xd.d[d];
+    ys *= yd.d[d];
+    i /= zd.d[d];
+  }
+}
+
+__global__ void kn_binary_fp_kernel(int op, uint16_t const *x, Dims4 xd, uint16_t const *y, Dims4 yd, uint16_t *z, Dims4 zd) {
+  int64_t n = (int64_t)zd.d[0] * zd.d[1] * zd.d[2] * zd.d[3], stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    int64_t xi, yi;
+    broadcast_index(i, xd, yd, zd, xi, yi);
+    uint32_t xv = x[xi], yv = y[yi], r;
+    if (op == MG_KN_DIV_OP) r = field_div(xv, yv);
+    else if (op == MG_KN_ADD_OP) r = (xv + yv) % PQ;
+    else r = (uint32_t)(((unsigned long long)xv * yv) % PQ);
+    z[i] = (uint16_t)r;
+  }
+}
+
+// out[i] = sum_k in[(i / os) * is + i % os + k * os]  (reduction_kernel.cu:80-108)
+__global__ void kn_reduction_fp_kernel(uint16_t const *x, uint16_t *y, int64_t n_out, int factor, int64_t is, int64_t os) {
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_out; i += stride) {
+    int64_t base = (i / os) * is + i % os;
+    unsigned long long acc = 0;
+    for (int k = 0; k < factor; k++) acc += x[base + (int64_t)k * os];
+    y[i] = (uint16_t)(acc % PQ);
+  }
+}
+
+// ---- float mode ------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void kn_matmul_float_kernel(T const *A, T const *B, T *C, int batches, int m, int n, int k, int a_col_major,
+                                       int b_col_major) {
+  int64_t total = (int64_t)batches * m * n, stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    int64_t b = i / ((int64_t)m * n);
+    int r = (int)((i / n) % m), c = (int)(i % n);
+    T const *a = A + b * m * k, *bb = B + b * k * n;
+    float acc = 0.f;
+    for (int kk = 0; kk < k; kk++) {
+      float av = to_float<T>(a_col_major ? a[(int64_t)kk * m + r] : a[(int64_t)r * k + kk]);
+      float bv = to_float<T>(b_col_major ? bb[(int64_t)c * k + kk] : bb[(int64_t)kk * n + c]);
+      acc = fmaf(av, bv, acc);
+    }
+    C[i] = from_float<T>(acc);
+  }
+}
+template <typename T> __global__ void kn_exp_float_kernel(T const *x, T *y, int64_t n) {
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
+    y[i] = from_float<T>(expf(to_float<T>(x[i])));
+}
+template <typename T>
+__global__ void kn_binary_float_kernel(int op, T const *x, Dims4 xd, T const *y, Dims4 yd, T *z, Dims4 zd) {
+  int64_t n = (int64_t)zd.d[0] * zd.d[1] * zd.d[2] * zd.d[3], stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    int64_t xi, yi;
+    broadcast_index(i, xd, yd, zd, xi, yi);
+    float xv = to_float<T>(x[xi]), yv = to_float<T>(y[yi]);
+    z[i] = from_float<T>(op == MG_KN_DIV_OP ? xv / yv : (op == MG_KN_ADD_OP ? xv + yv : xv * yv));
+  }
+}
+template <typename T>
+__global__ void kn_reduction_float_kernel(T const *x, T *y, int64_t n_out, int factor, int64_t is, int64_t os) {
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_out; i += stride) {
+    int64_t base = (i / os) * is + i % os;
+    float acc = 0.f;
+    for (int k = 0; k < factor; k++) acc += to_float<T>(x[base + (int64_t)k * os]);
+    y[i] = from_float<T>(acc);
+  }
+}
+
+static bool dims_ok(int32_t const *d) { return d && d[0] > 0 && d[1] > 0 && d[2] > 0 && d[3] > 0; }
+static Dims4 pack(int32_t const *d) { return Dims4{{d[0], d[1], d[2], d[3]}}; }
+} // namespace mgk
+
+using namespace mgk;
+#define ST(s) ((cudaStream_t)(s))
+
+extern "C" {
+
+int mgd_kn_matmul_fingerprint(const uint16_t *a, const uint16_t *b, uint16_t *c, int32_t batches, int32_t m, int32_t n,
+                              int32_t k, void *stream) {
+  if (!a || !b || !c || batches <= 0 || m <= 0 || n <= 0 || k <= 0) return set_error(MG_ERR_INVALID_ARGUMENT, "kn matmul: bad argument");
+  kn_matmul_fp_kernel<<<blocks_for((int64_t)batches * m * n), 256, 0, ST(stream)>>>(a, b, c, batches, m, n, k);
+  return check_launch("kn_matmul_fp_kernel");
+}
+int mgd_kn_exp_fingerprint(const uint16_t *x, uint16_t *y, int64_t n, void *stream) {
+  if (!x || !y || n <= 0) return set_error(MG_ERR_INVALID_ARGUMENT, "kn exp: bad argument");
+  kn_exp_fp_kernel<<<blocks_for(n), 256, 0, ST(stream)>>>(x, y, n);
+  return check_launch("kn_exp_fp_kernel");
+}
+int mgd_kn_binary_fingerprint(int32_t op, const uint16_t *x, const int32_t *xd, const uint16_t *y, const int32_t *yd,
+                              uint16_t *z, const int32_t *zd, void *stream) {
+  if (!x || !y || !z || !dims_ok(xd) || !dims_ok(yd) || !dims_ok(zd)) return set_error(MG_ERR_INVALID_ARGUMENT, "kn binary: bad argument");
+  if (op != MG_KN_ADD_OP && op != MG_KN_MUL_OP && op != MG_KN_DIV_OP) return set_error(MG_ERR_UNSUPPORTED, "kn binary: unknown operator");
+  int64_t n = (int64_t)zd[0] * zd[1] * zd[2] * zd[3];
+  kn_binary_fp_kernel<<<blocks_for(n), 256, 0, ST(stream)>>>(op, x, pack(xd), y, pack(yd), z, pack(zd));
+  return check_launch("kn_binary_fp_kernel");
+}
+int mgd_kn_reduction_fingerprint(const uint16_t *x, uint16_t *y, int64_t n_out, int32_t factor, int64_t is, int64_t os,
+                                 void *stream) {
+  if (!x || !y || n_out <= 0 || factor <= 0) return set_error(MG_ERR_INVALID_ARGUMENT, "kn reduction: bad argument");
+  kn_reduction_fp_kernel<<<blocks_for(n_out), 256, 0, ST(stream)>>>(x, y, n_out, factor, is, os);
+  return check_launch("kn_reduction_fp_kernel");
+}
+
+#define DISPATCH_16(dt, CALL_H, CALL_B)                                              \
+  if ((dt) == MG_DT_FLOAT16) { CALL_H; }                                              \
+  else if ((dt) == MG_DT_BFLOAT16) { CALL_B; }                                        \
+  else return set_error(MG_ERR_UNSUPPORTED, "float mode runs on fp16 or bf16 tensors");
+
+int mgd_kn_matmul_float(const void *a, const void *b, void *c, int32_t batches, int32_t m, int32_t n, int32_t k,
+                        int32_t al, int32_t bl, int32_t dt, void *stream) {
+  if (!a || !b || !c || batches <= 0 || m <= 0 || n <= 0 || k <= 0) return set_error(MG_ERR_INVALID_ARGUMENT, "kn matmul: bad argument");
+  int g = blocks_for((int64_t)batches * m * n), ac = al == MG_DMEM_COLUMN_MAJOR, bc = bl == MG_DMEM_COLUMN_MAJOR;
+  DISPATCH_16(dt, (kn_matmul_float_kernel<__half><<<g, 256, 0, ST(stream)>>>((__half const *)a, (__half const *)b, (__half *)c, batches, m, n, k, ac, bc)),
+              (kn_matmul_float_kernel<__nv_bfloat16><<<g, 256, 0, ST(stream)>>>((__nv_bfloat16 const *)a, (__nv_bfloat16 const *)b, (__nv_bfloat16 *)c, batches, m, n, k, ac, bc)))
+  return check_launch("kn_matmul_float_kernel");
+}
+int mgd_kn_exp_float(const void *x, void *y, int64_t n, int32_t dt, void *stream) {
+  if (!x || !y || n <= 0) return set_error(MG_ERR_INVALID_ARGUMENT, "kn exp: bad argument");
+  int g = blocks_for(n);
+  DISPATCH_16(dt, (kn_exp_float_kernel<__half><<<g, 256, 0, ST(stream)>>>((__half const *)x, (__half *)y, n)),
+              (kn_exp_float_kernel<__nv_bfloat16><<<g, 256, 0, ST(stream)>>>((__nv_bfloat16 const *)x, (__nv_bfloat16 *)y, n)))
+  return check_launch("kn_exp_float_kernel");
+}
+int mgd_kn_binary_float(int32_t op, const void *x, const int32_t *xd, const void *y, const int32_t *yd, void *z,
+                        const int32_t *zd, int32_t dt, void *stream) {
+  if (!x || !y || !z || !dims_ok(xd) || !dims_ok(yd) || !dims_ok(zd)) return set_error(MG_ERR_INVALID_ARGUMENT, "kn binary: bad argument");
+  if (op != MG_KN_ADD_OP && op != MG_KN_MUL_OP && op != MG_KN_DIV_OP) return set_error(MG_ERR_UNSUPPORTED, "kn binary: unknown operator");
+  int g = blocks_for((int64_t)zd[0] * zd[1] * zd[2] * zd[3]);
+  DISPATCH_16(dt, (kn_binary_float_kernel<__half><<<g, 256, 0, ST(stream)>>>(op, (__half const *)x, pack(xd), (__half const *)y, pack(yd), (__half *)z, pack(zd))),
+              (kn_binary_float_kernel<__nv_bfloat16><<<g, 256, 0, ST(stream)>>>(op, (__nv_bfloat16 const *)x, pack(xd), (__nv_bfloat16 const *)y, pack(yd), (__nv_bfloat16 *)z, pack(zd))))
+  return check_launch("kn_binary_float_kernel");
+}
+int mgd_kn_reduction_float(const void *x, void *y, int64_t n_out, int32_t factor, int64_t is, int64_t os, int32_t dt,
+                           void *stream) {
+  if (!x || !y || n_out <= 0 || factor <= 0) return set_error(MG_ERR_INVALID_ARGUMENT, "kn reduction: bad argument");
+  int g = blocks_for(n_out);
+  DISPATCH_16(dt, (kn_reduction_float_kernel<__half><<<g, 256, 0, ST(stream)>>>((__half const *)x, (__half *)y, n_out, factor, is, os)),
+              (kn_reduction_float_kernel<__nv_bfloat16><<<g, 256, 0, ST(stream)>>>((__nv_bfloat16 const *)x, (__nv_bfloat16 *)y, n_out, factor, is, os)))
+  return check_launch("kn_reduction_float_kernel");
+}
+}

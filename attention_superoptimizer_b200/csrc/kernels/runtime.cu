@@ -1,0 +1,128 @@
+// Launch bookkeeping, fills, comparison and the device status word.
+#include "common.cuh"
+#include "mugraph_rng.h"
+#include <atomic>
+#include <cstring>
+#include <string>
+
+namespace mgk {
+static std::atomic<uint64_t> g_launches{0};
+static thread_local std::string g_err;
+static int32_t *g_error_word = nullptr;
+
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+int set_error(int code, char const *msg) {
+  g_err = msg;
+  return code;
+}
+int check_launch(char const *name) {
+  cudaError_t e = cudaGetLastError();
+  if (e == cudaSuccess) {
+    count_launch();
+    return MG_OK;
+  }
+  g_err = std::string(name) + ": " + cudaGetErrorString(e);
+  return MG_ERR_CUDA;
+}
+int32_t *device_error_word() {
+  if (!g_error_word) {
+    if (cudaMalloc((void **)&g_error_word, 256) != cudaSuccess) return nullptr;
+    cudaMemset(g_error_word, 0, 256);
+  }
+  return g_error_word;
+}
+
+// ---- kernels ------------------------------------------------------------------------------------------
+__global__ void fill_fp_reference_kernel(uint16_t *p, int64_t n) {
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) p[i] = (uint16_t)(i % PQ);
+}
+
+__global__ void fill_fp_seeded_kernel(uint16_t *p, int64_t n, uint64_t seed, uint32_t modulus) {
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
+    p[i] = (uint16_t)mg_rng_uniform(seed, (uint64_t)i, modulus);
+}
+
+template <typename T> __global__ void fill_data_seeded_kernel(T *p, int64_t n, uint64_t seed, float sigma) {
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
+    p[i] = from_float<T>(mg_rng_normal(seed, (uint64_t)i) * sigma);
+}
+
+// flag starts at 1; any block that sees a difference clears it
+__global__ void compare_init_kernel(int32_t *flag) { *flag = 1; }
+__global__ void compare_u16_kernel(uint16_t const *a, uint16_t const *b, int64_t n, int32_t *flag) {
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  bool diff = false;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) diff |= a[i] != b[i];
+  if (__syncthreads_or(diff) && threadIdx.x == 0) *flag = 0;
+}
+
+static int grid_for(int64_t n, int threads) {
+  int64_t blocks = (n + threads - 1) / threads;
+  int64_t cap = 148 * 16;
+  return (int)(blocks < 1 ? 1 : (blocks > cap ? cap : blocks));
+}
+} // namespace mgk
+
+using namespace mgk;
+
+extern "C" {
+
+int mgd_fill_fingerprint_reference(uint16_t *p, int64_t n, void *stream) {
+  if (!p || n < 0) return set_error(MG_ERR_INVALID_ARGUMENT, "fill: null pointer");
+  if (n == 0) return MG_OK;
+  fill_fp_reference_kernel<<<grid_for(n, 256), 256, 0, (cudaStream_t)stream>>>(p, n);
+  return check_launch("fill_fp_reference_kernel");
+}
+
+int mgd_fill_fingerprint_seeded(uint16_t *p, int64_t n, uint64_t seed, uint32_t modulus, void *stream) {
+  if (!p || n < 0 || modulus == 0) return set_error(MG_ERR_INVALID_ARGUMENT, "fill: bad argument");
+  if (n == 0) return MG_OK;
+  fill_fp_seeded_kernel<<<grid_for(n, 256), 256, 0, (cudaStream_t)stream>>>(p, n, seed, modulus);
+  return check_launch("fill_fp_seeded_kernel");
+}
+
+int mgd_fill_data_seeded(void *p, int64_t n, uint64_t seed, float sigma, int32_t dt, void *stream) {
+  if (!p || n < 0) return set_error(MG_ERR_INVALID_ARGUMENT, "fill: bad argument");
+  if (n == 0) return MG_OK;
+  if (dt == MG_DT_FLOAT16)
+    fill_data_seeded_kernel<__half><<<grid_for(n, 256), 256, 0, (cudaStream_t)stream>>>((__half *)p, n, seed, sigma);
+  else if (dt == MG_DT_BFLOAT16)
+    fill_data_seeded_kernel<__nv_bfloat16>
+        <<<grid_for(n, 256), 256, 0, (cudaStream_t)stream>>>((__nv_bfloat16 *)p, n, seed, sigma);
+  else
+    return set_error(MG_ERR_UNSUPPORTED, "fill: 16-bit float types only");
+  return check_launch("fill_data_seeded_kernel");
+}
+
+int mgd_compare_u16(const uint16_t *a, const uint16_t *b, int64_t n, int32_t *flag, void *stream) {
+  if (!a || !b || !flag || n < 0) return set_error(MG_ERR_INVALID_ARGUMENT, "compare: null pointer");
+  compare_init_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(flag);
+  if (n > 0) compare_u16_kernel<<<grid_for(n, 256), 256, 0, (cudaStream_t)stream>>>(a, b, n, flag);
+  return check_launch("compare_u16_kernel");
+}
+
+int mgd_tables_init(const uint16_t *e, const uint16_t *p, const uint16_t *q) {
+  // The kernels carry compile-time tables; this verifies that the caller's tables agree with them.
+  FieldTables t;
+  if (!e || !p || !q) return set_error(MG_ERR_INVALID_ARGUMENT, "tables: null pointer");
+  if (std::memcmp(e, t.e, sizeof(t.e)) || std::memcmp(p, t.p, sizeof(t.p)) || std::memcmp(q, t.q, sizeof(t.q)))
+    return set_error(MG_ERR_INVALID_ARGUMENT, "tables: lookup tables differ from the built-in ones");
+  return MG_OK;
+}
+
+int mgd_read_and_clear_device_error(int32_t *code) {
+  if (!code) return set_error(MG_ERR_INVALID_ARGUMENT, "null pointer");
+  *code = 0;
+  int32_t *w = device_error_word();
+  if (!w) return set_error(MG_ERR_CUDA, "cannot allocate the device status word");
+  if (cudaMemcpy(code, w, 4, cudaMemcpyDeviceToHost) != cudaSuccess) return set_error(MG_ERR_CUDA, "status word read failed");
+  if (*code != 0) cudaMemset(w, 0, 4);
+  return MG_OK;
+}
+
+uint64_t mgd_launch_count(void) { return g_launches.load(); }
+const char *mgd_last_error(void) { return g_err.c_str(); }
+}

@@ -1,0 +1,59 @@
+// kernel::KNCustomizedOp - a kernel-graph node that owns a threadblock graph
+// (reference: include/mirage/kernel/customized.h:28-44).  Construction builds the
+// threadblock graph from an ExecutionPlan (or replays a template graph), discovers the
+// outputs and allocates them in the device arena; `fingerprint`, `run` and `profile`
+// lower the graph to an `mgd_program`, let the kernel selector match it against the
+// specialised sm_100a kernels and fall back to the generic interpreters.
+#pragma once
+#include "mirage/kernel/device_tensor.h"
+#include "mirage/kernel/operator.h"
+#include "mirage/threadblock/graph.h"
+#include <string>
+#include <vector>
+
+namespace mirage {
+namespace kernel {
+
+class KNCustomizedOp : public KNOperator {
+public:
+  KNCustomizedOp(std::vector<DTensor> const &inputs, mirage::threadblock::ExecutionPlan const &plan);
+  KNCustomizedOp(std::vector<DTensor> const &inputs, mirage::threadblock::Graph const &graph);
+  ~KNCustomizedOp() override;
+  bool profile(ProfileResult &profile) override;
+  void run(void);
+  bool fingerprint(void) override;
+  int launch_fingerprint(void *stream) override;
+  int launch_float(void *stream) override;
+  // same as the two above for `num_sets` independent tensor sets (strides in elements)
+  int launch_fingerprint_sets(int num_sets, void const *const *in, long long const *in_stride, void *const *out,
+                              long long const *out_stride, void *stream);
+
+  // Non-asserting construction: nullptr plus a message when the plan is invalid for these inputs
+  // or the outputs do not fit the arena.
+  static KNCustomizedOp *create(std::vector<DTensor> const &inputs, mirage::threadblock::ExecutionPlan const &plan,
+                                std::string *error, int *status);
+
+  // which kernel `launch_*` picks: 0 = generic interpreter, >0 = a specialised kernel (see kernel_select.h)
+  int selected_kernel(bool fingerprint_mode);
+
+  mirage::threadblock::ExecutionPlan plan;
+  mirage::threadblock::Graph bgraph;
+  // float-mode extension: per-row causal window of the speculative-decode graph (0 = off)
+  int causal_window = 0;
+  void set_causal_window(int window) {
+    causal_window = window;
+    lowered_ = false; // kernel choice depends on it
+  }
+
+private:
+  struct Deferred {};
+  KNCustomizedOp(Deferred, std::vector<DTensor> const &inputs, mirage::threadblock::ExecutionPlan const &plan);
+  bool build_from_plan(std::string *error, int *status);
+  bool lowered_ = false;
+  mgd_program program_;
+  int kernel_fp_ = -1, kernel_float_ = -1;
+  bool ensure_lowered();
+};
+
+} // namespace kernel
+} // namespace mirage

@@ -1,0 +1,158 @@
+/* mugraph_device.h - kernel-level C ABI: the only door between the host C++
+ * (graph building, validation, planning, kernel selection) and the sm_100a
+ * CUDA side.  Plain structs, pointers and sizes; every call returns an MG_*
+ * status from mugraph.h and enqueues work on the given cudaStream_t without
+ * synchronising unless stated.
+ *
+ * A threadblock graph travels as a `mgd_program`: the list of operators of one
+ * customized op with all shapes, shared-memory offsets and block / for-loop
+ * strides already resolved by the host.  It carries the information of the
+ * reference's NewKernelParams (include/mirage/threadblock/serializer/kernel_params.h:25-35)
+ * in a different container; the interpreters that consume it replace
+ * compute_customizedop_fingerprint and customized_kernel_function
+ * (src/kernel/cuda/customized_kernel.cu:39-603).
+ */
+#ifndef MUGRAPH_DEVICE_H_
+#define MUGRAPH_DEVICE_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MGD_MAX_OPS 24
+#define MGD_MAX_IO 8
+#define MGD_OP_ARGS 19
+
+/* Operator record.  `type` is a MG_TB_* code (2001 = input, 2002 = output).
+ * Shared-memory offsets are byte offsets in the reference's 2-byte-per-element plan.
+ *  input   a[0..2] row block stride (x,y,z)   a[3..5] column block stride   a[6] row for-loop stride
+ *          a[7] column for-loop stride   a[8..10] leading-dim block stride (elements)   a[11] leading-dim
+ *          for-loop stride   a[12],a[13] tensor rows, cols   a[14],a[15] tile rows, cols   a[16] MG_DMEM_* layout
+ *          a[17] tile offset   a[18] input slot
+ *  output  a[0..2] row block stride   a[3..5] column block stride   a[6..8] leading-dim block stride
+ *          a[9],a[10] tensor rows, cols   a[11],a[12] tile rows, cols   a[13] source tile offset
+ *          a[14] accumulator tile offset   a[15] output slot
+ *  matmul  a[0..2] m, n, k   a[3..5] offsets of A, B, C
+ *  exp     a[0] offset   a[1] elements                      (in place)
+ *  div/add/mul  a[0..2] shape of x (last three dims)   a[3..5] shape of y   a[6],a[7] offsets x, y   a[8] offset out
+ *  reduction    a[0] output elements   a[1] degree   a[2] inner range   a[3] offset in   a[4] offset out
+ *  concat  a[0] output elements   a[1],a[2] extents of A, B along the axis   a[3] inner size
+ *          a[4],a[5] offsets A, B   a[6] offset out */
+typedef struct mgd_op {
+  int32_t type;
+  int32_t a[MGD_OP_ARGS];
+} mgd_op;
+
+typedef struct mgd_program {
+  int32_t grid[3];
+  int32_t threads;        /* threads per block the host asks for (plan.block_dim.x) */
+  int32_t forloop_range;
+  int32_t num_ops;
+  int32_t num_inputs;
+  int32_t num_outputs;
+  int32_t smem_bytes;     /* reference plan size: 2 bytes per tile element */
+  int32_t reserved[3];
+  mgd_op ops[MGD_MAX_OPS];
+} mgd_program;
+
+/* Where the tensors of one launch live.  With num_sets > 1 the launch evaluates the
+ * program on num_sets independent tensor sets: set s reads in[i] + s*in_set_stride[i]
+ * elements and writes out[j] + s*out_set_stride[j]. */
+typedef struct mgd_bindings {
+  const void *in[MGD_MAX_IO];
+  void *out[MGD_MAX_IO];
+  int64_t in_set_stride[MGD_MAX_IO];
+  int64_t out_set_stride[MGD_MAX_IO];
+  int32_t num_sets;
+  int32_t reserved;
+} mgd_bindings;
+
+/* ---- generic interpreters (any valid threadblock graph) -------------------- */
+/* replaces compute_customizedop_fingerprint<<<grid, block, smem>>> (customized_kernel.cu:307-603) */
+int mgd_launch_fingerprint_interp(const mgd_program *prog, const mgd_bindings *bind, void *stream);
+/* replaces customized_kernel_function<<<grid, block, smem>>> (customized_kernel.cu:39-305);
+ * data_type MG_DT_FLOAT16 or MG_DT_BFLOAT16; tiles are held in fp32 shared memory */
+int mgd_launch_float_interp(const mgd_program *prog, const mgd_bindings *bind, int32_t data_type, void *stream);
+/* shared memory the float interpreter needs for `prog`; *fits = 0 when above the device limit */
+int mgd_float_interp_smem(const mgd_program *prog, size_t *bytes, int32_t *fits);
+
+/* ---- split-KV attention, the pattern of cpp_examples/group_query_attn_inc_decode.cc:46-79 ---
+ * op1: S = Q K, E = exp(S), O' = E V, R' = rowsum(E), both summed over the for-loop, one partial
+ * per grid.y split.  Shapes: Q[heads, m, d], K[heads, d, kv], V[heads, kv, d];
+ * O_part[heads, m, splits*d], R_part[heads, m, splits]. */
+typedef struct mgd_attn_split {
+  int32_t heads, m, d, kv_len;
+  int32_t splits;         /* grid.y */
+  int32_t forloop_range;  /* KV tiles per split */
+  int32_t k_layout;       /* MG_DMEM_*: row-major = memory [d][kv]; column-major = memory [kv][d] */
+  int32_t v_layout;       /* row-major = memory [kv][d]; column-major = memory [d][kv] */
+  int32_t data_type;      /* float mode only */
+  int32_t causal_window;  /* float mode only: 0 = none; w > 0 masks, for query row r (token r / (m / w)),
+                             KV positions > kv_len - w + token */
+  int32_t num_sets;
+  int32_t reserved;
+  int64_t q_set_stride, k_set_stride, v_set_stride, o_set_stride, r_set_stride; /* elements */
+} mgd_attn_split;
+int mgd_attn_split_supported(const mgd_attn_split *p, int32_t fingerprint_mode);
+int mgd_launch_attn_split_float(const mgd_attn_split *p, const void *q, const void *k, const void *v, void *o_part,
+                                void *r_part, void *stream);
+int mgd_launch_attn_split_fingerprint(const mgd_attn_split *p, const uint16_t *q, const uint16_t *k,
+                                      const uint16_t *v, uint16_t *o_part, uint16_t *r_part, void *stream);
+
+/* op2 of the same example (:80-103): O = (sum over splits of O_part) / (sum over splits of R_part) */
+typedef struct mgd_attn_merge {
+  int32_t heads, m, d, splits;
+  int32_t data_type;
+  int32_t num_sets;
+  int64_t o_part_set_stride, r_part_set_stride, out_set_stride;
+} mgd_attn_merge;
+int mgd_attn_merge_supported(const mgd_attn_merge *p, int32_t fingerprint_mode);
+int mgd_launch_attn_merge_float(const mgd_attn_merge *p, const void *o_part, const void *r_part, void *out,
+                                void *stream);
+int mgd_launch_attn_merge_fingerprint(const mgd_attn_merge *p, const uint16_t *o_part, const uint16_t *r_part,
+                                      uint16_t *out, void *stream);
+
+/* ---- un-fused kernel-level operators, fingerprint mode ----------------------
+ * replace compute_matmul_fingerprint (src/kernel/cuda/matmul_kernel.cu:145-173),
+ * compute_elementunary_fingerprint (element_unary_kernel.cu:77-94),
+ * compute_elementbinary_fingerprint (element_binary_kernel.cu:97-168),
+ * compute_reduction_fingerprint (reduction_kernel.cu:80-108) */
+int mgd_kn_matmul_fingerprint(const uint16_t *a, const uint16_t *b, uint16_t *c, int32_t batches, int32_t m,
+                              int32_t n, int32_t k, void *stream);
+int mgd_kn_exp_fingerprint(const uint16_t *x, uint16_t *y, int64_t n, void *stream);
+/* op = MG_KN_ADD_OP / MG_KN_MUL_OP / MG_KN_DIV_OP; dims are the 4 (right-aligned) extents */
+int mgd_kn_binary_fingerprint(int32_t op, const uint16_t *x, const int32_t *xdim, const uint16_t *y,
+                              const int32_t *ydim, uint16_t *z, const int32_t *zdim, void *stream);
+int mgd_kn_reduction_fingerprint(const uint16_t *x, uint16_t *y, int64_t out_elements, int32_t factor,
+                                 int64_t input_stride, int64_t output_stride, void *stream);
+/* float-mode counterparts (16-bit storage, fp32 arithmetic) */
+int mgd_kn_matmul_float(const void *a, const void *b, void *c, int32_t batches, int32_t m, int32_t n, int32_t k,
+                        int32_t a_layout, int32_t b_layout, int32_t data_type, void *stream);
+int mgd_kn_exp_float(const void *x, void *y, int64_t n, int32_t data_type, void *stream);
+int mgd_kn_binary_float(int32_t op, const void *x, const int32_t *xdim, const void *y, const int32_t *ydim, void *z,
+                        const int32_t *zdim, int32_t data_type, void *stream);
+int mgd_kn_reduction_float(const void *x, void *y, int64_t out_elements, int32_t factor, int64_t input_stride,
+                           int64_t output_stride, int32_t data_type, void *stream);
+
+/* ---- fills, compare, tables -------------------------------------------------- */
+/* init_input_fingerprint, src/kernel/cuda/input_kernel.cu:56-62 */
+int mgd_fill_fingerprint_reference(uint16_t *p, int64_t n, void *stream);
+int mgd_fill_fingerprint_seeded(uint16_t *p, int64_t n, uint64_t seed, uint32_t modulus, void *stream);
+int mgd_fill_data_seeded(void *p, int64_t n, uint64_t seed, float sigma, int32_t data_type, void *stream);
+/* *device_flag (4 bytes, device memory) <- 1 if equal else 0 */
+int mgd_compare_u16(const uint16_t *a, const uint16_t *b, int64_t n, int32_t *device_flag, void *stream);
+/* copies the lookup tables of src/kernel/device_memory_manager.cu:41-90 into constant memory
+ * of the current device; idempotent */
+int mgd_tables_init(const uint16_t *exp_tbl, const uint16_t *div_p_tbl, const uint16_t *div_q_tbl);
+/* device status word written by kernels whose bounded waits gave up; 0 = none. Synchronises. */
+int mgd_read_and_clear_device_error(int32_t *code);
+uint64_t mgd_launch_count(void);
+const char *mgd_last_error(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MUGRAPH_DEVICE_H_ */

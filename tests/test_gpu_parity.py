@@ -1,0 +1,280 @@
+"""GPU parity tests: the CUDA executor, called through the C ABI, against the CPU oracle and the
+reference-host golden vectors.  Fingerprint mode must be bit-exact; float mode within 2e-3 (fp16) /
+1e-2 (bf16) relative of the fp32 evaluation (helpers.assert_close)."""
+import json
+import os
+
+import numpy as np
+import pytest
+
+import attention_superoptimizer_b200 as mg
+from oracle import mugraph_oracle as mo
+from tests.helpers import assert_close, from_bits, spec_of, to_bits, to_oracle_plan, to_package_plan
+
+pytestmark = pytest.mark.gpu
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden", "gqa_decode_reference_host.json")
+BIG = 227 * 1024
+
+
+def golden_cases():
+    with open(GOLDEN) as f:
+        return json.load(f)["cases"]
+
+
+def build_gqa(g, B, M, D, L, S, F, kl=mg.DmemColumnMajor, vl=mg.DmemColumnMajor, dtype=mg.float16):
+    Q = g.new_input((B, M, D), dtype)
+    K = g.new_input((B, D, L), dtype, kl)
+    V = g.new_input((B, L, D), dtype, vl)
+    p1, p2 = mg.gqa_decode_plans(B, M, D, L, S, F)
+    o = g.customized([Q, K, V], p1)
+    f = g.customized(o, p2)
+    return (Q, K, V), o, f, (p1, p2)
+
+
+def oracle_fp(ins, plans, x):
+    g1 = mo.build_customized([spec_of(t) for t in ins], to_oracle_plan(plans[0]), max_smem=BIG)
+    o1 = mo.run_fingerprint(g1, x)
+    g2 = mo.build_customized(mo.output_specs(g1), to_oracle_plan(plans[1]), max_smem=BIG)
+    return o1, mo.run_fingerprint(g2, o1)
+
+
+@pytest.fixture(params=[True, False], ids=["specialised", "interpreter"])
+def rt(request, runtime):
+    runtime.set_max_smem(BIG)
+    runtime.set_specialisation(request.param)
+    yield runtime
+    runtime.set_specialisation(True)
+
+
+def test_lookup_tables_on_device(runtime):
+    e, p, q = runtime.tables()
+    assert np.array_equal(e, mo.EXP_TBL) and np.array_equal(p, mo.DIV_P_TBL) and np.array_equal(q, mo.DIV_Q_TBL)
+
+
+@pytest.mark.parametrize("case", golden_cases(), ids=lambda c: c["name"])
+def test_fingerprint_golden(rt, case):
+    """Known answers from the reference's own host code, including the reference's input fill."""
+    c = case
+    with mg.PyGraph(rt) as g:
+        ins, o, f, plans = build_gqa(g, c["B"], c["M"], c["D"], c["L"], c["S"], c["F"])
+        if c["fill"] == "reference":
+            g.fingerprint(refill_inputs=True)  # KNInputOp::fingerprint: fp[i] = i % FP_PQ
+        else:
+            for t, v in zip(ins, c["inputs_full"]):
+                t.upload_fingerprint(np.array(v, np.uint16))
+            g.fingerprint()
+        o_part, r_part, final = o[0].download_fingerprint(), o[1].download_fingerprint(), f[0].download_fingerprint()
+        assert o_part.ravel()[:4].tolist() == c["o_part_head"] and r_part.ravel()[:4].tolist() == c["r_part_head"]
+        assert str(mo.fnv1a64(np.concatenate([o_part.ravel(), r_part.ravel()]))) == c["op1_digest"]
+        assert final.ravel()[:4].tolist() == c["final_head"]
+        assert str(mo.fnv1a64(final)) == c["final_digest"]
+        if "final_full" in c:
+            assert final.ravel().tolist() == c["final_full"]
+
+
+@pytest.mark.parametrize("shape", [(2, 8, 64, 1024, 4, 4), (1, 4, 128, 512, 2, 4), (4, 16, 32, 256, 8, 1),
+                                   (3, 1, 8, 48, 3, 2), (2, 32, 128, 1024, 4, 4), (2, 5, 24, 96, 2, 3)])
+@pytest.mark.parametrize("hi", [mo.FP_P, mo.FP_PQ, 65536], ids=["lt_P", "lt_PQ", "any_u16"])
+def test_fingerprint_random_vs_oracle(rt, shape, hi):
+    B, M, D, L, S, F = shape
+    rng = np.random.default_rng(sum(shape) + hi)
+    with mg.PyGraph(rt) as g:
+        ins, o, f, plans = build_gqa(g, *shape)
+        x = [rng.integers(0, hi, size=t.shape).astype(np.uint16) for t in ins]
+        if hi == 65536:
+            x[1].ravel()[:7] = 65535  # the largest storable value
+        for t, v in zip(ins, x):
+            t.upload_fingerprint(v)
+        g.fingerprint()
+        ref1, ref2 = oracle_fp(ins, plans, x)
+        assert np.array_equal(o[0].download_fingerprint(), ref1[0])
+        assert np.array_equal(o[1].download_fingerprint(), ref1[1])
+        assert np.array_equal(f[0].download_fingerprint(), ref2[0])
+        # second evaluation is identical (no state leaks between launches)
+        g.fingerprint()
+        assert np.array_equal(f[0].download_fingerprint(), ref2[0])
+
+
+def test_fused_graph_matches_unfused_graph_on_device(rt):
+    """The reference's integration check (cpp_examples/group_query_attn_inc_decode.cc:14-108): both
+    graphs evaluated on the device from the reference fill, compared with has_same_fingerprint."""
+    B, M, D, L = 2, 8, 64, 4096
+    with mg.PyGraph(rt) as ref, mg.PyGraph(rt) as g:
+        Q = ref.new_input((B, M, D))
+        K = ref.new_input((B, D, L), layout=mg.DmemColumnMajor)
+        V = ref.new_input((B, L, D), layout=mg.DmemColumnMajor)
+        A = ref.matmul(Q, K)
+        E = ref.exp(A)
+        S = ref.reduction(E, 2)
+        Dv = ref.div(E, S)
+        O = ref.matmul(Dv, V)
+        ref.fingerprint(refill_inputs=True)
+        ins, o, f, plans = build_gqa(g, B, M, D, L, 16, 4)
+        g.fingerprint(refill_inputs=True)
+        assert O.has_same_fingerprint(f[0])
+        assert not O.has_same_fingerprint(Dv) and not f[0].has_same_fingerprint(ins[0])
+        x = [mo.reference_fill(t.shape) for t in ins]
+        assert np.array_equal(O.download_fingerprint(), mo.unfused_attention_fp(*x))
+        # un-fused intermediates against the oracle's kernel-level operators
+        assert np.array_equal(A.download_fingerprint(), mo.kn_matmul_fp(x[0], x[1]))
+        assert np.array_equal(S.download_fingerprint(), mo.kn_reduction_fp(mo.kn_exp_fp(mo.kn_matmul_fp(x[0], x[1])), 2))
+
+
+def run_generic_fp(rt, specs, plan, seed):
+    rng = np.random.default_rng(seed)
+    with mg.PyGraph(rt) as g:
+        ins = [g.new_input(s.dims, s.dtype, s.layout) for s in specs]
+        x = [rng.integers(0, mo.FP_PQ, size=s.dims).astype(np.uint16) for s in specs]
+        for t, v in zip(ins, x):
+            t.upload_fingerprint(v)
+        outs = g.customized(ins, to_package_plan(plan))
+        g.fingerprint()
+        got = [t.download_fingerprint() for t in outs]
+    want = mo.run_fingerprint(mo.build_customized(specs, plan, max_smem=BIG), x)
+    assert len(got) == len(want)
+    for a, b in zip(got, want):
+        assert np.array_equal(a, b)
+    return x, got
+
+
+def test_fingerprint_other_graphs(rt):
+    """Graphs outside the attention pattern go through the generic interpreter."""
+    # config-1 style matmul chain, grid over the intermediate columns, for-loop over K tiles of 64
+    specs = [mo.DTensorSpec((16, 1024)), mo.DTensorSpec((1024, 1024)), mo.DTensorSpec((1024, 1024))]
+    chain = mo.ExecutionPlan(
+        ops=[(mo.TB_MATMUL_OP, [(0, 0), (1, 0)]), (mo.TB_MATMUL_OP, [(3, 0), (2, 0)])],
+        input_map=[(-1, -1, -1), (1, -1, -1), (0, -1, -1)], forloop_dim=[1, 0, -1],
+        input_smem_layouts=[mo.SmemRowMajor] * 3, output_map=(1, -1, -1), forloop_range=16, grid_dim=(16, 1, 1),
+        reduction_dimx=1024)
+    x, got = run_generic_fp(rt, specs, chain, 1)
+    total = got[0].astype(np.int64).reshape(16, 16, 1024).sum(axis=1) % mo.FP_PQ
+    assert np.array_equal(total, mo.fp_matmul(mo.fp_matmul(x[0], x[1]), x[2]))
+    # concat, exp, reduction, div with broadcasting, to_dimx; 3-D tensors split over grid x and z
+    specs = [mo.DTensorSpec((4, 8, 32)), mo.DTensorSpec((4, 8, 32)), mo.DTensorSpec((4, 8, 64))]
+    mixed = mo.ExecutionPlan(
+        ops=[(mo.TB_CONCAT_2_OP, [(0, 0), (1, 0)]), (mo.TB_EXP_OP, [(3, 0)]), (mo.TB_REDUCTION_2_OP, [(4, 0)]),
+             (mo.TB_DIV_OP, [(2, 0), (5, 0)]), (mo.TB_REDUCTION_2_TO_DIMX_OP, [(6, 0)])],
+        input_map=[(0, -1, 1), (0, -1, 1), (0, -1, 1)], forloop_dim=[-1, -1, -1],
+        input_smem_layouts=[mo.SmemRowMajor] * 3, output_map=(0, -1, 1), forloop_range=1, grid_dim=(4, 1, 2),
+        reduction_dimx=16)
+    run_generic_fp(rt, specs, mixed, 2)
+    # identity: an input passed straight to an output keeps its raw values
+    specs = [mo.DTensorSpec((6, 40))]
+    ident = mo.ExecutionPlan(ops=[(mo.TB_REDUCTION_0_OP, [(0, 0)])], input_map=[(1, -1, -1)], forloop_dim=[0],
+                             input_smem_layouts=[mo.SmemRowMajor], output_map=(1, -1, -1), forloop_range=3,
+                             grid_dim=(5, 1, 1))
+    run_generic_fp(rt, specs, ident, 3)
+
+
+def float_inputs(rng, B, M, D, L, kl, vl, dtype):
+    """Logical tensors rounded to storage precision, plus their memory images."""
+    rnd = lambda a: from_bits(to_bits(a, dtype), dtype)
+    q = rnd(rng.standard_normal((B, M, D)) / np.sqrt(D))  # 1/sqrt(d) folded into Q on the host
+    k = rnd(rng.standard_normal((B, D, L)))
+    v = rnd(rng.standard_normal((B, L, D)))
+    mem = [q, k if kl == mg.DmemRowMajor else np.ascontiguousarray(k.transpose(0, 2, 1)),
+           v if vl == mg.DmemRowMajor else np.ascontiguousarray(v.transpose(0, 2, 1))]
+    return (q, k, v), mem
+
+
+@pytest.mark.parametrize("dtype", [mg.float16, mg.bfloat16], ids=["fp16", "bf16"])
+@pytest.mark.parametrize("layouts", [(mg.DmemColumnMajor, mg.DmemColumnMajor), (mg.DmemRowMajor, mg.DmemRowMajor),
+                                     (mg.DmemColumnMajor, mg.DmemRowMajor)], ids=["kc_vc", "kr_vr", "kc_vr"])
+@pytest.mark.parametrize("shape", [(2, 4, 128, 1024, 4, 4), (2, 8, 64, 512, 2, 4), (1, 32, 128, 1024, 4, 2),
+                                   (3, 1, 32, 96, 3, 2)])
+def test_float_gqa_vs_fp32_oracle(rt, shape, layouts, dtype):
+    B, M, D, L, S, F = shape
+    kl, vl = layouts
+    rng = np.random.default_rng(sum(shape))
+    with mg.PyGraph(rt) as g:
+        ins, o, f, plans = build_gqa(g, B, M, D, L, S, F, kl, vl, dtype)
+        (q, k, v), mem = float_inputs(rng, B, M, D, L, kl, vl, dtype)
+        for t, a in zip(ins, mem):
+            t.upload_data(to_bits(a, dtype))
+        g.run()
+        og1 = mo.build_customized([spec_of(t) for t in ins], to_oracle_plan(plans[0]), max_smem=BIG)
+        ref1 = mo.run_float(og1, mem)
+        assert_close(from_bits(o[0].download_data(), dtype).reshape(o[0].shape), ref1[0], dtype, "O_part")
+        assert_close(from_bits(o[1].download_data(), dtype).reshape(o[1].shape), ref1[1], dtype, "R_part")
+        final = from_bits(f[0].download_data(), dtype).reshape(f[0].shape)
+        assert_close(final, mo.attention_fp32(q, k, v), dtype, "O vs un-fused fp32 attention")
+
+
+def test_float_baseline_c2_full_size(rt):
+    """BASELINE config: 8 KV heads, group 4, head_dim 128, KV 4096, 16 splits, KV tiles of 64, fp16."""
+    B, M, D, L, S, F = 8, 4, 128, 4096, 16, 4
+    rng = np.random.default_rng(2024)
+    with mg.PyGraph(rt) as g:
+        ins, o, f, plans = build_gqa(g, B, M, D, L, S, F)
+        (q, k, v), mem = float_inputs(rng, B, M, D, L, mg.DmemColumnMajor, mg.DmemColumnMajor, mg.float16)
+        for t, a in zip(ins, mem):
+            t.upload_data(to_bits(a, mg.float16))
+        g.run()
+        final = from_bits(f[0].download_data(), mg.float16).reshape(f[0].shape)
+        assert_close(final, mo.attention_fp32(q, k, v), mg.float16, "C2 output")
+        ms = g.profile_op(3, warmup=3, iters=5)
+        assert 0 < ms < 1000
+
+
+def test_float_other_graph_generic(rt):
+    """Matmul chain in float mode through the generic interpreter."""
+    rng = np.random.default_rng(9)
+    specs = [mo.DTensorSpec((16, 256)), mo.DTensorSpec((256, 128)), mo.DTensorSpec((128, 64))]
+    plan = mo.ExecutionPlan(
+        ops=[(mo.TB_MATMUL_OP, [(0, 0), (1, 0)]), (mo.TB_MATMUL_OP, [(3, 0), (2, 0)])],
+        input_map=[(-1, -1, -1), (1, -1, -1), (0, -1, -1)], forloop_dim=[1, 0, -1],
+        input_smem_layouts=[mo.SmemRowMajor] * 3, output_map=(1, -1, -1), forloop_range=4, grid_dim=(4, 1, 1),
+        reduction_dimx=64)
+    x = [from_bits(to_bits(rng.standard_normal(s.dims) * 0.05, mg.float16), mg.float16) for s in specs]
+    with mg.PyGraph(rt) as g:
+        ins = [g.new_input(s.dims, s.dtype, s.layout) for s in specs]
+        for t, a in zip(ins, x):
+            t.upload_data(to_bits(a, mg.float16))
+        outs = g.customized(ins, to_package_plan(plan))
+        g.run()
+        got = from_bits(outs[0].download_data(), mg.float16).reshape(outs[0].shape)
+    want = mo.run_float(mo.build_customized(specs, plan), x)[0]
+    assert_close(got, want, mg.float16, "chain partials")
+
+
+def test_batched_fingerprint_sets(rt):
+    """Many independent input sets in one pass equal per-set evaluations by the oracle."""
+    import torch
+    B, M, D, L, S, F = 2, 4, 64, 512, 4, 2
+    nsets = 5
+    rng = np.random.default_rng(77)
+    with mg.PyGraph(rt) as g:
+        ins, o, f, plans = build_gqa(g, B, M, D, L, S, F)
+        xs = [[rng.integers(0, mo.FP_P, size=t.shape).astype(np.uint16) for t in ins] for _ in range(nsets)]
+        dev = [torch.from_numpy(np.stack([xs[s][i] for s in range(nsets)]).astype(np.int16)).cuda() for i in range(3)]
+        out = torch.zeros((nsets,) + f[0].shape, dtype=torch.int16, device="cuda")
+        wbytes = g.fingerprint_batched_workspace(nsets)
+        work = torch.zeros(max(wbytes, 16), dtype=torch.uint8, device="cuda")
+        torch.cuda.synchronize()
+        g.fingerprint_batched(nsets, [d.data_ptr() for d in dev], out.data_ptr(), work.data_ptr(), wbytes)
+        mg.synchronize()
+        got = out.cpu().numpy().view(np.uint16)
+        for s in range(nsets):
+            _, ref2 = oracle_fp(ins, plans, xs[s])
+            assert np.array_equal(got[s], ref2[0]), "set %d" % s
+
+
+def test_unsupported_is_an_error_not_a_fallback(rt):
+    """A graph too large for the generic float interpreter is refused with a status code."""
+    with mg.PyGraph(rt) as g:
+        specs = [(1, 128, 128), (1, 128, 128)]
+        A = g.new_input(specs[0])
+        Bt = g.new_input(specs[1])
+        plan = mg.ExecutionPlan(ops=[(mg.TB_MATMUL_OP, [(0, 0), (1, 0)]), (mg.TB_EXP_OP, [(2, 0)]),
+                                     (mg.TB_MATMUL_OP, [(3, 0), (1, 0)]), (mg.TB_MATMUL_OP, [(4, 0), (1, 0)])],
+                                input_map=[(0, -1, -1), (0, -1, -1)], forloop_dim=[-1, -1],
+                                input_smem_layouts=[mg.SmemRowMajor] * 2, output_map=(0, -1, -1), forloop_range=1,
+                                grid_dim=(1, 1, 1))
+        outs = g.customized([A, Bt], plan)  # 6 tiles of 32 KB = 192 KB planned -> 384 KB of fp32 tiles
+        with pytest.raises(mg.MuGraphError) as e:
+            g.run()
+        assert e.value.status == 5
+        A.upload_fingerprint(np.ones(A.shape, np.uint16))
+        Bt.upload_fingerprint(np.ones(Bt.shape, np.uint16))
+        g.fingerprint()  # fingerprint mode fits (2-byte tiles)
+        assert outs[0].download_fingerprint().shape == (1, 128, 128)
