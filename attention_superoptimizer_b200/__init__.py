@@ -337,6 +337,32 @@ class PyGraph:
         return sz.value
 
 
+class CapturedSequence:
+    """A launch sequence captured into a CUDA graph on `stream` (a raw cudaStream_t value)."""
+
+    def __init__(self, stream, record):
+        self.lib = _abi.load()
+        self.stream = ctypes.c_void_p(stream)
+        before = launch_count()
+        check(self.lib.mg_capture_begin(self.stream))
+        try:
+            record()
+        finally:
+            h = ctypes.c_void_p()
+            st = self.lib.mg_capture_end(self.stream, ctypes.byref(h))
+        check(st)
+        self.handle = h
+        self.kernels = launch_count() - before  # kernels one replay launches
+
+    def launch(self):
+        check(self.lib.mg_captured_launch(self.handle, self.stream))
+
+    def close(self):
+        if self.handle:
+            check(self.lib.mg_captured_destroy(self.handle))
+            self.handle = None
+
+
 def new_graph():
     return PyGraph()
 

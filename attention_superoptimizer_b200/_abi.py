@@ -82,6 +82,10 @@ SIGNATURES = {
     "mg_tensor_upload_data_async": (ctypes.c_int, [_P, _T, _P, _P]),
     "mg_tensor_download_data_async": (ctypes.c_int, [_P, _T, _P, _P]),
     "mg_graph_rebind_input": (ctypes.c_int, [_P, _I, _P, _P]),
+    "mg_capture_begin": (ctypes.c_int, [_P]),
+    "mg_capture_end": (ctypes.c_int, [_P, ctypes.POINTER(_P)]),
+    "mg_captured_launch": (ctypes.c_int, [_P, _P]),
+    "mg_captured_destroy": (ctypes.c_int, [_P]),
     "mg_device_synchronize": (ctypes.c_int, []),
     "mg_last_error": (ctypes.c_char_p, []),
     "mg_version": (ctypes.c_char_p, []),

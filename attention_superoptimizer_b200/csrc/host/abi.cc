@@ -502,6 +502,34 @@ int mg_graph_rebind_input(mg_graph *g, int32_t idx, void *data_ptr, uint16_t *fp
   return MG_OK;
 }
 
+int mg_capture_begin(void *stream) {
+  if (!stream) return fail(MG_ERR_INVALID_ARGUMENT, "capture needs a non-default stream");
+  MG_CUDA_TRY(cudaStreamBeginCapture((cudaStream_t)stream, cudaStreamCaptureModeThreadLocal));
+  return MG_OK;
+}
+int mg_capture_end(void *stream, void **captured) {
+  if (!stream || !captured) return fail(MG_ERR_INVALID_ARGUMENT, "null argument");
+  *captured = nullptr;
+  cudaGraph_t graph = nullptr;
+  MG_CUDA_TRY(cudaStreamEndCapture((cudaStream_t)stream, &graph));
+  cudaGraphExec_t exec = nullptr;
+  int st = mg::cuda_status((int)cudaGraphInstantiate(&exec, graph, 0), "cudaGraphInstantiate");
+  cudaGraphDestroy(graph);
+  if (st != MG_OK) return st;
+  *captured = exec;
+  return MG_OK;
+}
+int mg_captured_launch(void *captured, void *stream) {
+  if (!captured) return fail(MG_ERR_INVALID_ARGUMENT, "null argument");
+  MG_CUDA_TRY(cudaGraphLaunch((cudaGraphExec_t)captured, (cudaStream_t)stream));
+  return MG_OK;
+}
+int mg_captured_destroy(void *captured) {
+  if (!captured) return fail(MG_ERR_INVALID_ARGUMENT, "null argument");
+  MG_CUDA_TRY(cudaGraphExecDestroy((cudaGraphExec_t)captured));
+  return MG_OK;
+}
+
 int mg_device_synchronize(void) { return synchronize_and_check(); }
 const char *mg_last_error(void) { return mg::last_error(); }
 const char *mg_version(void) { return "mugraph-b200 0.1 (sm_100a)"; }

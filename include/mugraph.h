@@ -202,6 +202,17 @@ int mg_tensor_download_data_async(mg_runtime *rt, const mg_tensor *t, void *host
 /* rebind a graph input to caller-owned device memory (e.g. one of several rotating buffers) */
 int mg_graph_rebind_input(mg_graph *g, int32_t op_idx, void *data_ptr, uint16_t *fp_ptr);
 
+/* ---- CUDA-graph capture of launch sequences ----------------------------------
+ * At a few microseconds per customized op the CPU cost of a launch exceeds the kernel; a caller
+ * that replays the same sequence (the reference's profile loop, customized_kernel.cu:631-647, or a
+ * verification sweep) captures it once and replays it.  `stream` must be a non-default stream;
+ * only asynchronous entry points (mg_op_run, mg_graph_run, mg_graph_fingerprint_batched, the
+ * *_async copies) may be called between begin and end, after each was called once outside. */
+int mg_capture_begin(void *stream);
+int mg_capture_end(void *stream, void **captured);
+int mg_captured_launch(void *captured, void *stream);
+int mg_captured_destroy(void *captured);
+
 /* ---- misc ------------------------------------------------------------------ */
 int mg_device_synchronize(void);
 const char *mg_last_error(void);
