@@ -1,21 +1,597 @@
-// Split-KV attention kernels (placeholder translation unit while the kernels are brought up):
-// every query reports "not supported", which makes the host keep such graphs on the interpreters.
+// Split-KV attention operator and its cross-split merge, float and fingerprint mode.
+//
+// The operator is the first customized op of the grouped-query decode muGraph (the pattern of the
+// reference's cpp_examples/group_query_attn_inc_decode.cc:46-79): per (head, KV split) block and per
+// for-loop iteration   S = Q K,  E = exp(S),  O' = E V,  R' = rowsum(E),   O' and R' summed over the
+// iterations and stored as one partial per split.  The reference runs it through its interpreters
+// (src/kernel/cuda/customized_kernel.cu:39-603); here it is one kernel:
+//
+//   * K and V tiles of 64 KV positions stream through a ring of shared-memory stages filled by TMA
+//     (cp.async.bulk.tensor, 128-byte swizzle) and tracked by one mbarrier per stage; all stages are
+//     requested before the first wait, so a block keeps up to `stages` x 32 KB in flight.
+//   * Each warp owns 16 KV positions of a tile.  It computes its S slice with mma.sync (Q fragments stay
+//     in registers for the whole kernel), exponentiates in registers, reuses the accumulator fragments
+//     as the A operand of E V, and keeps its partial O' and R' in registers across all iterations; the
+//     four KV slices are summed once, through shared memory, after the loop.  S, E and the partial O'
+//     never touch shared memory.
+//   * Float mode: fp16 / bf16 operands, fp32 accumulation (m16n8k16).  The optional causal window of
+//     the speculative-decode graph is a predicate on E.
+//   * Fingerprint mode: exact arithmetic modulo PQ = 227 * 113 on the integer tensor cores.  A uint16
+//     fingerprint is two bytes x = lo + 256 hi, and a tile of uint16 in shared memory IS an interleaved
+//     u8 matrix, so ldmatrix delivers u8 fragments of m16n8k32 without any unpacking.  The 16 rows of
+//     the A operand carry three byte-masked copies of 4 query rows - [lo,0], [0,hi] and [hi,lo] - whose
+//     products with the [lo,hi] bytes of the other operand are the sums LL, HH and LH+HL; then
+//     sum x*y = LL + 256 (LH+HL) + 65536 HH exactly in int32, reduced modulo PQ once per element.
+//     The result equals the reference's per-MAC reduction (include/mirage/threadblock/cuda/matmul.h:773-804)
+//     bit for bit, for any uint16 operands.  exp is the table lookup of element_unary.h:60-66.
+//
+// Every mbarrier wait is bounded: a block that gives up records a code in the device status word and
+// returns without touching its outputs further.
 #include "common.cuh"
+#include <cuda.h>
+#include <mutex>
+#include <unordered_map>
+
+namespace mgk {
+
+constexpr int kTile = 64;        // KV positions per for-loop tile
+constexpr int kMaxStages = 6;
+constexpr int kWaitLimit = 1000000;
+constexpr int kDynSmemLimit = kSmemLimit - 1024; // the kernel also has a few bytes of static shared memory
+
+enum AttnMode { kF16 = 0, kBF16 = 1, kFingerprint = 2 };
+
+// ---- PTX wrappers ---------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(void const *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+               : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+// bounded wait: false after kWaitLimit polls
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  for (int i = 0; i < kWaitLimit; i++)
+    if (mbar_try_wait(bar, parity)) return true;
+  return false;
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, CUtensorMap const *map, uint32_t bar, int c0, int c1, int c2) {
+  asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+               ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t addr, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+template <int MODE> struct Acc { using type = float; };
+template <> struct Acc<kFingerprint> { using type = int32_t; };
+
+template <int MODE>
+__device__ __forceinline__ void mma_tile(typename Acc<MODE>::type (&c)[4], uint32_t const (&a)[4], uint32_t b0, uint32_t b1);
+template <> __device__ __forceinline__ void mma_tile<kF16>(float (&c)[4], uint32_t const (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+template <> __device__ __forceinline__ void mma_tile<kBF16>(float (&c)[4], uint32_t const (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+template <> __device__ __forceinline__ void mma_tile<kFingerprint>(int32_t (&c)[4], uint32_t const (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// A staged tile holds `rows` x `cols` 16-bit elements as cols/64 TMA boxes of [rows][64], each with the
+// 128-byte swizzle (16-byte chunk c of row r sits at chunk c ^ (r % 8)).  `chunk` counts 8-element units.
+__device__ __forceinline__ uint32_t tile_addr(uint32_t base, int rows, int row, int chunk) {
+  return base + (uint32_t)((chunk >> 3) * rows * 128 + row * 128 + (((chunk & 7) ^ (row & 7)) << 4));
+}
+
+__device__ __forceinline__ uint32_t pack_f16(float a, float b) {
+  __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t *>(&h);
+}
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t *>(&h);
+}
+
+struct AttnSplitParams {
+  void const *q;   // [sets][heads][m][d]
+  void *o_part;    // [sets][heads][m][splits*d]
+  void *r_part;    // [sets][heads][m][splits]
+  int32_t *status; // device status word
+  long long q_set_stride, o_set_stride, r_set_stride;
+  int heads, m, splits, forloop, stages, kv_len;
+  int k_rows_are_kv; // K staged as [kv][d] (memory of a column-major K) else [d][kv]
+  int v_rows_are_kv; // V staged as [kv][d] (memory of a row-major V) else [d][kv]
+  int causal_window;
+};
+
+// Shared-memory plan: [stages x (K tile, V tile)] (1024-byte aligned) | reduction scratch | barriers | exp table
+template <int MODE, int DH>
+__global__ void __launch_bounds__(256)
+attn_split_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
+                  const __grid_constant__ AttnSplitParams p) {
+  using acc_t = typename Acc<MODE>::type;
+  constexpr int kRowsPerGroup = MODE == kFingerprint ? 4 : 16; // query rows one warp's MMA rows carry
+  constexpr int kTileBytes = kTile * DH * 2;
+  constexpr int kKSteps = DH / 16;     // k-steps of Q K (contraction over head_dim)
+  constexpr int kNPairs = DH / 16;     // pairs of 8-wide output tiles of E V (output over head_dim)
+  extern __shared__ unsigned char smem_dyn[];
+  unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
+
+  int const tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  int const slice = warp & 3;          // which 16 KV positions of a tile
+  int const group = warp >> 2;         // which group of query rows
+  int const groups = blockDim.x >> 7;
+  int const g = lane >> 2, t = lane & 3;
+
+  int64_t const b = blockIdx.x;
+  int const split = (int)(b % p.splits), head = (int)((b / p.splits) % p.heads);
+  int64_t const set = b / ((int64_t)p.splits * p.heads);
+  int const batch = (int)(set * p.heads + head); // tensor maps fold (set, head) into one coordinate
+
+  uint32_t const stage_base = smem_u32(smem);
+  int const rows_scratch = MODE == kFingerprint ? 4 : (p.m < 16 ? p.m : 16);
+  acc_t *scratch = reinterpret_cast<acc_t *>(smem + (size_t)p.stages * 2 * kTileBytes);
+  size_t const scratch_bytes = (size_t)(blockDim.x >> 5) * rows_scratch * (DH + 4) * sizeof(acc_t);
+  uint64_t *bars = reinterpret_cast<uint64_t *>(smem + (size_t)p.stages * 2 * kTileBytes + ((scratch_bytes + 15) & ~(size_t)15));
+  uint16_t *exp_tab = reinterpret_cast<uint16_t *>(bars + kMaxStages);
+  __shared__ int s_failed;
+
+  if (tid == 0) {
+    s_failed = 0;
+    for (int s = 0; s < p.stages; s++) mbar_init(smem_u32(&bars[s]), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (MODE == kFingerprint) // exp table with the CRT lift folded in: E = table[S mod Q]
+    for (int i = tid; i < (int)Q; i += blockDim.x) exp_tab[i] = (uint16_t)((c_tables.e[i] * Q_MUL_P_MOD_1) % PQ);
+  __syncthreads();
+
+  int const kv_base = split * p.forloop * kTile; // first KV position of this block
+  auto issue = [&](int it) {
+    int s = it % p.stages;
+    uint32_t bar = smem_u32(&bars[s]);
+    uint32_t kdst = stage_base + (uint32_t)(s * 2 * kTileBytes), vdst = kdst + kTileBytes;
+    int kv0 = kv_base + it * kTile;
+    mbar_expect_tx(bar, 2 * kTileBytes);
+    if (p.k_rows_are_kv) {
+      for (int c = 0; c < DH / 64; c++) tma_load_3d(kdst + c * (kTile * 128), &k_map, bar, c * 64, kv0, batch);
+    } else {
+      tma_load_3d(kdst, &k_map, bar, kv0, 0, batch);
+    }
+    if (p.v_rows_are_kv) {
+      for (int c = 0; c < DH / 64; c++) tma_load_3d(vdst + c * (kTile * 128), &v_map, bar, c * 64, kv0, batch);
+    } else {
+      tma_load_3d(vdst, &v_map, bar, kv0, 0, batch);
+    }
+  };
+  if (tid == 0) {
+    int first = p.forloop < p.stages ? p.forloop : p.stages;
+    for (int it = 0; it < first; it++) issue(it);
+  }
+
+  // ---- Q fragments, resident in registers -----------------------------------------------------------
+  uint32_t qa[kKSteps][4];
+  {
+    uint16_t const *q = static_cast<uint16_t const *>(p.q) + set * p.q_set_stride + (int64_t)head * p.m * DH;
+    if (MODE == kFingerprint) {
+      int row = group * 4 + (g & 3);
+      bool valid = row < p.m;
+#pragma unroll
+      for (int ks = 0; ks < kKSteps; ks++) {
+        uint32_t w0 = valid ? __ldg(reinterpret_cast<uint32_t const *>(q + (size_t)row * DH + ks * 16 + 2 * t)) : 0u;
+        uint32_t w1 = valid ? __ldg(reinterpret_cast<uint32_t const *>(q + (size_t)row * DH + ks * 16 + 8 + 2 * t)) : 0u;
+        if (g < 4) { // MMA rows 0-3: [lo,0] bytes; MMA rows 8-11: [hi,lo] bytes
+          qa[ks][0] = w0 & 0x00FF00FFu; qa[ks][2] = w1 & 0x00FF00FFu;
+          qa[ks][1] = __byte_perm(w0, 0, 0x2301); qa[ks][3] = __byte_perm(w1, 0, 0x2301);
+        } else {     // MMA rows 4-7: [0,hi] bytes; MMA rows 12-15 unused
+          qa[ks][0] = w0 & 0xFF00FF00u; qa[ks][2] = w1 & 0xFF00FF00u;
+          qa[ks][1] = 0u; qa[ks][3] = 0u;
+        }
+      }
+    } else {
+      int r0 = group * 16 + g, r1 = r0 + 8;
+#pragma unroll
+      for (int ks = 0; ks < kKSteps; ks++) {
+        qa[ks][0] = r0 < p.m ? __ldg(reinterpret_cast<uint32_t const *>(q + (size_t)r0 * DH + ks * 16 + 2 * t)) : 0u;
+        qa[ks][1] = r1 < p.m ? __ldg(reinterpret_cast<uint32_t const *>(q + (size_t)r1 * DH + ks * 16 + 2 * t)) : 0u;
+        qa[ks][2] = r0 < p.m ? __ldg(reinterpret_cast<uint32_t const *>(q + (size_t)r0 * DH + ks * 16 + 8 + 2 * t)) : 0u;
+        qa[ks][3] = r1 < p.m ? __ldg(reinterpret_cast<uint32_t const *>(q + (size_t)r1 * DH + ks * 16 + 8 + 2 * t)) : 0u;
+      }
+    }
+  }
+
+  acc_t oacc[2 * kNPairs][4];
+#pragma unroll
+  for (int i = 0; i < 2 * kNPairs; i++)
+#pragma unroll
+    for (int j = 0; j < 4; j++) oacc[i][j] = 0;
+  acc_t racc0 = 0, racc1 = 0; // row sums of E: float: rows g and g+8; fingerprint: row g (lanes 0-15)
+
+  int const mi = lane >> 3, rr = lane & 7; // ldmatrix: this lane addresses row rr of matrix mi
+  int const kv0 = slice * 16;               // this warp's KV positions inside a tile
+  bool failed = false;
+
+  for (int it = 0; it < p.forloop; it++) {
+    int s = it % p.stages;
+    // After a wait has given up the block keeps walking the loop (so that every thread still meets the
+    // block-wide barriers below) but stops waiting; its results are discarded at the end.
+    if (!failed && !mbar_wait(smem_u32(&bars[s]), (uint32_t)((it / p.stages) & 1))) failed = true;
+    uint32_t ktile = stage_base + (uint32_t)(s * 2 * kTileBytes), vtile = ktile + kTileBytes;
+
+    // ---- S slice = Q K over this warp's 16 KV positions: two 8-wide tiles ---------------------------
+    acc_t sacc[2][4];
+#pragma unroll
+    for (int i = 0; i < 2; i++)
+#pragma unroll
+      for (int j = 0; j < 4; j++) sacc[i][j] = 0;
+#pragma unroll
+    for (int ks = 0; ks < kKSteps; ks++) {
+      uint32_t bfrag[4];
+      if (p.k_rows_are_kv) ldsm_x4(tile_addr(ktile, kTile, kv0 + (mi >> 1) * 8 + rr, ks * 2 + (mi & 1)), bfrag);
+      else ldsm_x4_trans(tile_addr(ktile, DH, ks * 16 + (mi & 1) * 8 + rr, (kv0 >> 3) + (mi >> 1)), bfrag);
+      mma_tile<MODE>(sacc[0], qa[ks], bfrag[0], bfrag[1]);
+      mma_tile<MODE>(sacc[1], qa[ks], bfrag[2], bfrag[3]);
+    }
+
+    // ---- E = exp(S) in registers, repacked as the A operand of E V ---------------------------------
+    uint32_t ea[4];
+    if (MODE == kFingerprint) {
+      uint32_t e[2][2];
+#pragma unroll
+      for (int nt = 0; nt < 2; nt++) {
+        // lanes 16-31 hold the HH sums of the query row lanes 0-15 work on
+        int32_t hh0 = __shfl_down_sync(0xffffffffu, sacc[nt][0], 16), hh1 = __shfl_down_sync(0xffffffffu, sacc[nt][1], 16);
+        uint32_t s0 = ((uint32_t)sacc[nt][0] % PQ + 256u * ((uint32_t)sacc[nt][2] % PQ) + (65536u % PQ) * ((uint32_t)hh0 % PQ)) % PQ;
+        uint32_t s1 = ((uint32_t)sacc[nt][1] % PQ + 256u * ((uint32_t)sacc[nt][3] % PQ) + (65536u % PQ) * ((uint32_t)hh1 % PQ)) % PQ;
+        e[nt][0] = exp_tab[s0 % Q];
+        e[nt][1] = exp_tab[s1 % Q];
+      }
+      uint32_t x0 = e[0][0] | (e[0][1] << 16), x1 = e[1][0] | (e[1][1] << 16);
+      uint32_t y0 = __shfl_up_sync(0xffffffffu, x0, 16), y1 = __shfl_up_sync(0xffffffffu, x1, 16);
+      if (g < 4) {
+        racc0 += (int32_t)(e[0][0] + e[0][1] + e[1][0] + e[1][1]);
+        ea[0] = x0 & 0x00FF00FFu; ea[2] = x1 & 0x00FF00FFu;
+        ea[1] = __byte_perm(x0, 0, 0x2301); ea[3] = __byte_perm(x1, 0, 0x2301);
+      } else {
+        ea[0] = y0 & 0xFF00FF00u; ea[2] = y1 & 0xFF00FF00u;
+        ea[1] = 0u; ea[3] = 0u;
+      }
+    } else {
+      float ev[2][4];
+      int pos = kv_base + it * kTile + kv0 + 2 * t; // KV position of sacc[0][0]
+#pragma unroll
+      for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+          float v = __expf(sacc[nt][j]);
+          if (p.causal_window > 0) {
+            int row = group * 16 + g + (j >> 1) * 8;
+            int token = row / (p.m / p.causal_window);
+            if (pos + nt * 8 + (j & 1) > p.kv_len - p.causal_window + token) v = 0.f;
+          }
+          ev[nt][j] = v;
+        }
+      racc0 += ev[0][0] + ev[0][1] + ev[1][0] + ev[1][1];
+      racc1 += ev[0][2] + ev[0][3] + ev[1][2] + ev[1][3];
+      if (MODE == kF16) {
+        ea[0] = pack_f16(ev[0][0], ev[0][1]); ea[1] = pack_f16(ev[0][2], ev[0][3]);
+        ea[2] = pack_f16(ev[1][0], ev[1][1]); ea[3] = pack_f16(ev[1][2], ev[1][3]);
+      } else {
+        ea[0] = pack_bf16(ev[0][0], ev[0][1]); ea[1] = pack_bf16(ev[0][2], ev[0][3]);
+        ea[2] = pack_bf16(ev[1][0], ev[1][1]); ea[3] = pack_bf16(ev[1][2], ev[1][3]);
+      }
+    }
+
+    // ---- O' += E V over this warp's 16 KV positions -------------------------------------------------
+#pragma unroll
+    for (int jp = 0; jp < kNPairs; jp++) {
+      uint32_t bfrag[4];
+      if (p.v_rows_are_kv) ldsm_x4_trans(tile_addr(vtile, kTile, kv0 + (mi & 1) * 8 + rr, jp * 2 + (mi >> 1)), bfrag);
+      else ldsm_x4(tile_addr(vtile, DH, (2 * jp + (mi >> 1)) * 8 + rr, (kv0 >> 3) + (mi & 1)), bfrag);
+      mma_tile<MODE>(oacc[2 * jp], ea, bfrag[0], bfrag[1]);
+      mma_tile<MODE>(oacc[2 * jp + 1], ea, bfrag[2], bfrag[3]);
+    }
+
+    // ---- refill the stage once every warp has read it --------------------------------------------------
+    if (p.forloop > p.stages) {
+      __syncthreads();
+      if (tid == 0 && it + p.stages < p.forloop) issue(it + p.stages);
+    }
+  }
+
+  if (failed) s_failed = 1;
+  __syncthreads();
+  if (s_failed) { // a bounded wait gave up: flag it and leave the outputs alone
+    if (tid == 0) atomicExch(p.status, 1);
+    return;
+  }
+
+  // ---- sum the four KV slices (and nothing else: rows of different groups are distinct query rows) ----
+  int const ld = DH + 4; // padded row pitch of the scratch (keeps the column walk off a single bank)
+  acc_t *mine = scratch + (size_t)warp * rows_scratch * ld;
+  acc_t *rsum = mine + DH; // the pad holds this warp's row sums: rsum[row * ld]
+  if (MODE == kFingerprint) {
+#pragma unroll
+    for (int nt = 0; nt < 2 * kNPairs; nt++) {
+      int32_t hh0 = __shfl_down_sync(0xffffffffu, oacc[nt][0], 16), hh1 = __shfl_down_sync(0xffffffffu, oacc[nt][1], 16);
+      if (g < 4) {
+        uint32_t v0 = ((uint32_t)oacc[nt][0] % PQ + 256u * ((uint32_t)oacc[nt][2] % PQ) + (65536u % PQ) * ((uint32_t)hh0 % PQ)) % PQ;
+        uint32_t v1 = ((uint32_t)oacc[nt][1] % PQ + 256u * ((uint32_t)oacc[nt][3] % PQ) + (65536u % PQ) * ((uint32_t)hh1 % PQ)) % PQ;
+        mine[g * ld + nt * 8 + 2 * t] = (int32_t)v0;
+        mine[g * ld + nt * 8 + 2 * t + 1] = (int32_t)v1;
+      }
+    }
+    int32_t r = racc0;
+    r += __shfl_xor_sync(0xffffffffu, r, 1);
+    r += __shfl_xor_sync(0xffffffffu, r, 2);
+    if (g < 4 && t == 0) rsum[g * ld] = (int32_t)((uint32_t)r % PQ);
+  } else {
+#pragma unroll
+    for (int nt = 0; nt < 2 * kNPairs; nt++) {
+      if (g < rows_scratch) {
+        mine[g * ld + nt * 8 + 2 * t] = oacc[nt][0];
+        mine[g * ld + nt * 8 + 2 * t + 1] = oacc[nt][1];
+      }
+      if (g + 8 < rows_scratch) {
+        mine[(g + 8) * ld + nt * 8 + 2 * t] = oacc[nt][2];
+        mine[(g + 8) * ld + nt * 8 + 2 * t + 1] = oacc[nt][3];
+      }
+    }
+    float r0 = racc0, r1 = racc1;
+    r0 += __shfl_xor_sync(0xffffffffu, r0, 1); r0 += __shfl_xor_sync(0xffffffffu, r0, 2);
+    r1 += __shfl_xor_sync(0xffffffffu, r1, 1); r1 += __shfl_xor_sync(0xffffffffu, r1, 2);
+    if (t == 0) {
+      if (g < rows_scratch) rsum[g * ld] = r0;
+      if (g + 8 < rows_scratch) rsum[(g + 8) * ld] = r1;
+    }
+  }
+  __syncthreads();
+
+  int const rows_per_group = kRowsPerGroup;
+  int const out_ld = p.splits * DH;
+  uint16_t *o_out = static_cast<uint16_t *>(p.o_part) + set * p.o_set_stride + (int64_t)head * p.m * out_ld + split * DH;
+  uint16_t *r_out = static_cast<uint16_t *>(p.r_part) + set * p.r_set_stride + (int64_t)head * p.m * p.splits + split;
+  // pairs of adjacent columns -> one 32-bit store
+  for (int i = tid; i < groups * rows_scratch * (DH / 2); i += blockDim.x) {
+    int c = (i % (DH / 2)) * 2, lr = (i / (DH / 2)) % rows_scratch, gr = i / ((DH / 2) * rows_scratch);
+    int row = gr * rows_per_group + lr;
+    if (row >= p.m) continue;
+    acc_t a0 = 0, a1 = 0;
+#pragma unroll
+    for (int sl = 0; sl < 4; sl++) {
+      acc_t const *src = scratch + (size_t)(gr * 4 + sl) * rows_scratch * ld + lr * ld + c;
+      a0 += src[0];
+      a1 += src[1];
+    }
+    uint32_t packed;
+    if (MODE == kFingerprint) packed = ((uint32_t)a0 % PQ) | (((uint32_t)a1 % PQ) << 16);
+    else if (MODE == kF16) packed = pack_f16((float)a0, (float)a1);
+    else packed = pack_bf16((float)a0, (float)a1);
+    *reinterpret_cast<uint32_t *>(o_out + (size_t)row * out_ld + c) = packed;
+  }
+  for (int i = tid; i < groups * rows_scratch; i += blockDim.x) {
+    int lr = i % rows_scratch, gr = i / rows_scratch, row = gr * rows_per_group + lr;
+    if (row >= p.m) continue;
+    acc_t a = 0;
+#pragma unroll
+    for (int sl = 0; sl < 4; sl++) a += scratch[(size_t)(gr * 4 + sl) * rows_scratch * ld + lr * ld + DH];
+    uint16_t v;
+    if (MODE == kFingerprint) v = (uint16_t)((uint32_t)a % PQ);
+    else if (MODE == kF16) { __half h = __float2half_rn((float)a); v = *reinterpret_cast<uint16_t *>(&h); }
+    else { __nv_bfloat16 h = __float2bfloat16_rn((float)a); v = *reinterpret_cast<uint16_t *>(&h); }
+    r_out[(size_t)row * p.splits] = v;
+  }
+}
+
+// ---- merge: O = sum_s O_part[.., s*d + c] / sum_s R_part[.., s] ---------------------------------------------
+template <int MODE>
+__global__ void __launch_bounds__(256) attn_merge_kernel(uint16_t const *o_part, uint16_t const *r_part, uint16_t *out,
+                                                         int heads, int m, int d, int splits, long long o_stride,
+                                                         long long r_stride, long long out_stride) {
+  int const head = blockIdx.x % heads;
+  int64_t const set = blockIdx.x / heads;
+  uint16_t const *op = o_part + set * o_stride + (int64_t)head * m * splits * d;
+  uint16_t const *rp = r_part + set * r_stride + (int64_t)head * m * splits;
+  uint16_t *dst = out + set * out_stride + (int64_t)head * m * d;
+  for (int i = threadIdx.x; i < m * d; i += blockDim.x) {
+    int r = i / d, c = i % d;
+    if (MODE == kFingerprint) {
+      uint32_t num = 0, den = 0;
+      for (int s = 0; s < splits; s++) {
+        num += op[(size_t)r * splits * d + s * d + c];
+        den += rp[r * splits + s];
+      }
+      dst[i] = (uint16_t)field_div(num % PQ, den % PQ);
+    } else {
+      float num = 0.f, den = 0.f;
+      for (int s = 0; s < splits; s++) {
+        uint16_t a = op[(size_t)r * splits * d + s * d + c], bb = rp[r * splits + s];
+        if (MODE == kF16) {
+          num += __half2float(*reinterpret_cast<__half const *>(&a));
+          den += __half2float(*reinterpret_cast<__half const *>(&bb));
+        } else {
+          num += __bfloat162float(*reinterpret_cast<__nv_bfloat16 const *>(&a));
+          den += __bfloat162float(*reinterpret_cast<__nv_bfloat16 const *>(&bb));
+        }
+      }
+      float v = num / den;
+      if (MODE == kF16) { __half h = __float2half_rn(v); dst[i] = *reinterpret_cast<uint16_t *>(&h); }
+      else { __nv_bfloat16 h = __float2bfloat16_rn(v); dst[i] = *reinterpret_cast<uint16_t *>(&h); }
+    }
+  }
+}
+
+// ---- host side ------------------------------------------------------------------------------------------------
+using EncodeFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, cuuint64_t const *,
+                              cuuint64_t const *, cuuint32_t const *, cuuint32_t const *, CUtensorMapInterleave,
+                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeFn encode_fn() {
+  static EncodeFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void *sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeFn>(sym);
+  });
+  return fn;
+}
+
+// 3-D map over a [batch][rows][cols] array of 16-bit elements, box [1][box_rows][64], 128-byte swizzle
+static bool make_map(CUtensorMap *map, void const *base, uint64_t batch, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+  EncodeFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[3] = {cols, rows, batch};
+  cuuint64_t strides[2] = {cols * 2, rows * cols * 2};
+  cuuint32_t box[3] = {64, box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, const_cast<void *>(base), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+static int sm_count() {
+  static int n = 0;
+  if (!n) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+  }
+  return n;
+}
+
+static int groups_for(mgd_attn_split const *p, bool fp) { return fp ? (p->m + 3) / 4 : (p->m + 15) / 16; }
+
+static bool shape_supported(mgd_attn_split const *p, bool fp) {
+  if (!p || p->heads <= 0 || p->m <= 0 || p->splits <= 0 || p->forloop_range <= 0 || p->num_sets <= 0) return false;
+  if (p->d != 64 && p->d != 128) return false;
+  if ((int64_t)p->splits * p->forloop_range * kTile != p->kv_len) return false; // tiles of 64 KV positions
+  if (groups_for(p, fp) > 2) return false;                                       // at most 8 warps per block
+  if (fp && p->forloop_range > 256) return false;                                // int32 accumulators stay exact
+  if (!fp && p->data_type != MG_DT_FLOAT16 && p->data_type != MG_DT_BFLOAT16) return false;
+  if (p->causal_window < 0 || (p->causal_window > 0 && (fp || p->m % p->causal_window != 0))) return false;
+  if (p->num_sets > 1) { // sets must be dense so that (set, head) folds into one TMA coordinate
+    int64_t kv = (int64_t)p->heads * p->d * p->kv_len;
+    if (p->k_set_stride != kv || p->v_set_stride != kv) return false;
+  }
+  return true;
+}
+
+template <int MODE, int DH>
+static int launch_split(mgd_attn_split const *p, void const *q, void const *k, void const *v, void *o, void *r, void *stream) {
+  bool const fp = MODE == kFingerprint;
+  int groups = groups_for(p, fp), threads = groups * 128;
+  int rows_scratch = fp ? 4 : (p->m < 16 ? p->m : 16);
+  size_t acc = 4, tile = (size_t)kTile * DH * 2;
+  size_t scratch = ((size_t)(threads / 32) * rows_scratch * (DH + 4) * acc + 15) & ~(size_t)15;
+  size_t fixed = 1024 + scratch + kMaxStages * 8 + 256;
+  int64_t blocks = (int64_t)p->heads * p->splits * p->num_sets;
+  // One wave: request the whole split up front.  Many waves: shallow rings so that several blocks share an SM
+  // and one block's loads overlap another's arithmetic.
+  int stages = p->forloop_range < kMaxStages ? p->forloop_range : kMaxStages;
+  if (blocks > sm_count() && stages > 2) stages = 2;
+  while (stages > 1 && fixed + stages * 2 * tile > (size_t)kDynSmemLimit) stages--;
+  size_t smem = fixed + stages * 2 * tile;
+  if (smem > (size_t)kDynSmemLimit) return set_error(MG_ERR_UNSUPPORTED, "split-KV attention: tile does not fit shared memory");
+
+  CUtensorMap kmap, vmap;
+  uint64_t batch = (uint64_t)p->heads * p->num_sets;
+  // Float tensors sit in memory as their layout tag says; fingerprint buffers are always logical row-major
+  // (the reference indexes them so whatever the tag): K as [d][kv], V as [kv][d].
+  bool k_kv = !fp && p->k_layout == MG_DMEM_COLUMN_MAJOR, v_kv = fp || p->v_layout == MG_DMEM_ROW_MAJOR;
+  bool ok = k_kv ? make_map(&kmap, k, batch, p->kv_len, DH, kTile) : make_map(&kmap, k, batch, DH, p->kv_len, DH);
+  ok = ok && (v_kv ? make_map(&vmap, v, batch, p->kv_len, DH, kTile) : make_map(&vmap, v, batch, DH, p->kv_len, DH));
+  if (!ok) return set_error(MG_ERR_CUDA, "split-KV attention: cuTensorMapEncodeTiled failed");
+
+  AttnSplitParams a;
+  a.q = q; a.o_part = o; a.r_part = r;
+  a.status = device_error_word();
+  if (!a.status) return set_error(MG_ERR_CUDA, "cannot allocate the device status word");
+  a.q_set_stride = p->q_set_stride; a.o_set_stride = p->o_set_stride; a.r_set_stride = p->r_set_stride;
+  a.heads = p->heads; a.m = p->m; a.splits = p->splits; a.forloop = p->forloop_range; a.stages = stages;
+  a.kv_len = p->kv_len; a.k_rows_are_kv = k_kv; a.v_rows_are_kv = v_kv; a.causal_window = p->causal_window;
+
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(attn_split_kernel<MODE, DH>, cudaFuncAttributeMaxDynamicSharedMemorySize, kDynSmemLimit) != cudaSuccess)
+      return check_launch("cudaFuncSetAttribute(attn_split_kernel)");
+    configured = true;
+  }
+  if (blocks > 0x7fffffffLL) return set_error(MG_ERR_UNSUPPORTED, "too many blocks for one launch");
+  attn_split_kernel<MODE, DH><<<(unsigned)blocks, threads, smem, (cudaStream_t)stream>>>(kmap, vmap, a);
+  return check_launch("attn_split_kernel");
+}
+} // namespace mgk
+
 using namespace mgk;
+
 extern "C" {
-int mgd_attn_split_supported(const mgd_attn_split *, int32_t) { return 0; }
-int mgd_attn_merge_supported(const mgd_attn_merge *, int32_t) { return 0; }
-int mgd_launch_attn_split_float(const mgd_attn_split *, const void *, const void *, const void *, void *, void *, void *) {
-  return set_error(MG_ERR_UNSUPPORTED, "split-KV attention kernel not available");
+
+int mgd_attn_split_supported(const mgd_attn_split *p, int32_t fingerprint_mode) {
+  return shape_supported(p, fingerprint_mode != 0) && encode_fn() != nullptr ? 1 : 0;
 }
-int mgd_launch_attn_split_fingerprint(const mgd_attn_split *, const uint16_t *, const uint16_t *, const uint16_t *,
-                                      uint16_t *, uint16_t *, void *) {
-  return set_error(MG_ERR_UNSUPPORTED, "split-KV attention kernel not available");
+
+int mgd_launch_attn_split_float(const mgd_attn_split *p, const void *q, const void *k, const void *v, void *o,
+                                void *r, void *stream) {
+  if (!q || !k || !v || !o || !r) return set_error(MG_ERR_INVALID_ARGUMENT, "split-KV attention: null tensor");
+  if (!shape_supported(p, false)) return set_error(MG_ERR_UNSUPPORTED, "split-KV attention: shape not supported");
+  if (p->data_type == MG_DT_FLOAT16)
+    return p->d == 128 ? launch_split<kF16, 128>(p, q, k, v, o, r, stream) : launch_split<kF16, 64>(p, q, k, v, o, r, stream);
+  return p->d == 128 ? launch_split<kBF16, 128>(p, q, k, v, o, r, stream) : launch_split<kBF16, 64>(p, q, k, v, o, r, stream);
 }
-int mgd_launch_attn_merge_float(const mgd_attn_merge *, const void *, const void *, void *, void *) {
-  return set_error(MG_ERR_UNSUPPORTED, "attention merge kernel not available");
+
+int mgd_launch_attn_split_fingerprint(const mgd_attn_split *p, const uint16_t *q, const uint16_t *k, const uint16_t *v,
+                                      uint16_t *o, uint16_t *r, void *stream) {
+  if (!q || !k || !v || !o || !r) return set_error(MG_ERR_INVALID_ARGUMENT, "split-KV attention: null tensor");
+  if (!shape_supported(p, true)) return set_error(MG_ERR_UNSUPPORTED, "split-KV attention: shape not supported");
+  return p->d == 128 ? launch_split<kFingerprint, 128>(p, q, k, v, o, r, stream)
+                     : launch_split<kFingerprint, 64>(p, q, k, v, o, r, stream);
 }
-int mgd_launch_attn_merge_fingerprint(const mgd_attn_merge *, const uint16_t *, const uint16_t *, uint16_t *, void *) {
-  return set_error(MG_ERR_UNSUPPORTED, "attention merge kernel not available");
+
+int mgd_attn_merge_supported(const mgd_attn_merge *p, int32_t) {
+  return p && p->heads > 0 && p->m > 0 && p->d > 0 && p->splits > 0 && p->splits <= 65536 ? 1 : 0;
+}
+
+int mgd_launch_attn_merge_float(const mgd_attn_merge *p, const void *o_part, const void *r_part, void *out, void *stream) {
+  if (!p || !o_part || !r_part || !out || p->num_sets <= 0) return set_error(MG_ERR_INVALID_ARGUMENT, "attention merge: bad argument");
+  unsigned blocks = (unsigned)(p->heads * p->num_sets);
+  if (p->data_type == MG_DT_FLOAT16)
+    attn_merge_kernel<kF16><<<blocks, 256, 0, (cudaStream_t)stream>>>((uint16_t const *)o_part, (uint16_t const *)r_part, (uint16_t *)out,
+        p->heads, p->m, p->d, p->splits, p->o_part_set_stride, p->r_part_set_stride, p->out_set_stride);
+  else if (p->data_type == MG_DT_BFLOAT16)
+    attn_merge_kernel<kBF16><<<blocks, 256, 0, (cudaStream_t)stream>>>((uint16_t const *)o_part, (uint16_t const *)r_part, (uint16_t *)out,
+        p->heads, p->m, p->d, p->splits, p->o_part_set_stride, p->r_part_set_stride, p->out_set_stride);
+  else
+    return set_error(MG_ERR_UNSUPPORTED, "attention merge: fp16 or bf16 only");
+  return check_launch("attn_merge_kernel");
+}
+
+int mgd_launch_attn_merge_fingerprint(const mgd_attn_merge *p, const uint16_t *o_part, const uint16_t *r_part, uint16_t *out, void *stream) {
+  if (!p || !o_part || !r_part || !out || p->num_sets <= 0) return set_error(MG_ERR_INVALID_ARGUMENT, "attention merge: bad argument");
+  unsigned blocks = (unsigned)(p->heads * p->num_sets);
+  attn_merge_kernel<kFingerprint><<<blocks, 256, 0, (cudaStream_t)stream>>>(o_part, r_part, out, p->heads, p->m, p->d, p->splits,
+                                                                            p->o_part_set_stride, p->r_part_set_stride, p->out_set_stride);
+  return check_launch("attn_merge_kernel");
 }
 }

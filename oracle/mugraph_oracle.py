@@ -641,3 +641,18 @@ def attention_fp32(q, k, v):
     q, k, v = (np.asarray(t, np.float32) for t in (q, k, v))
     e = np.exp(q @ k)
     return (e / e.sum(axis=2, keepdims=True)) @ v
+
+
+def attention_fp32_causal_window(q, k, v, window):
+    """Float-mode extension (no counterpart in the reference): the last `window` KV positions are a
+    draft window; query row r belongs to draft token r // (rows // window) and sees KV positions
+    <= kv_len - window + token.  Masked positions contribute neither to the numerator nor to the
+    row sum."""
+    q, k, v = (np.asarray(t, np.float32) for t in (q, k, v))
+    B, M, D = q.shape
+    L = k.shape[2]
+    e = np.exp(q @ k)
+    token = np.arange(M) // (M // window)
+    visible = np.arange(L)[None, :] <= (L - window + token)[:, None]
+    e = e * visible[None, :, :]
+    return (e / e.sum(axis=2, keepdims=True)) @ v

@@ -73,7 +73,8 @@ def test_fingerprint_golden(rt, case):
 
 
 @pytest.mark.parametrize("shape", [(2, 8, 64, 1024, 4, 4), (1, 4, 128, 512, 2, 4), (4, 16, 32, 256, 8, 1),
-                                   (3, 1, 8, 48, 3, 2), (2, 32, 128, 1024, 4, 4), (2, 5, 24, 96, 2, 3)])
+                                   (3, 1, 8, 48, 3, 2), (2, 32, 128, 1024, 4, 4), (2, 5, 24, 96, 2, 3),
+                                   (2, 4, 128, 2048, 2, 16), (3, 7, 64, 1024, 1, 16), (1, 1, 128, 64, 1, 1)])
 @pytest.mark.parametrize("hi", [mo.FP_P, mo.FP_PQ, 65536], ids=["lt_P", "lt_PQ", "any_u16"])
 def test_fingerprint_random_vs_oracle(rt, shape, hi):
     B, M, D, L, S, F = shape
@@ -181,7 +182,7 @@ def float_inputs(rng, B, M, D, L, kl, vl, dtype):
 @pytest.mark.parametrize("layouts", [(mg.DmemColumnMajor, mg.DmemColumnMajor), (mg.DmemRowMajor, mg.DmemRowMajor),
                                      (mg.DmemColumnMajor, mg.DmemRowMajor)], ids=["kc_vc", "kr_vr", "kc_vr"])
 @pytest.mark.parametrize("shape", [(2, 4, 128, 1024, 4, 4), (2, 8, 64, 512, 2, 4), (1, 32, 128, 1024, 4, 2),
-                                   (3, 1, 32, 96, 3, 2)])
+                                   (3, 1, 32, 96, 3, 2), (2, 20, 128, 2048, 2, 16), (1, 7, 64, 1024, 2, 8)])
 def test_float_gqa_vs_fp32_oracle(rt, shape, layouts, dtype):
     B, M, D, L, S, F = shape
     kl, vl = layouts
@@ -198,6 +199,45 @@ def test_float_gqa_vs_fp32_oracle(rt, shape, layouts, dtype):
         assert_close(from_bits(o[1].download_data(), dtype).reshape(o[1].shape), ref1[1], dtype, "R_part")
         final = from_bits(f[0].download_data(), dtype).reshape(f[0].shape)
         assert_close(final, mo.attention_fp32(q, k, v), dtype, "O vs un-fused fp32 attention")
+
+
+def test_float_causal_window_extension(runtime):
+    """Speculative-decode mask (float-mode extension of the split-KV attention kernel): 8 draft tokens x
+    group 4 = 32 query rows; fingerprint mode is unaffected by the mask."""
+    B, M, D, L, S, F, W = 2, 32, 128, 2048, 8, 4, 8
+    rng = np.random.default_rng(31)
+    runtime.set_specialisation(True)
+    with mg.PyGraph(runtime) as g:
+        ins, o, f, plans = build_gqa(g, B, M, D, L, S, F)
+        g.set_causal_window(3, W)
+        assert g.customized_info(3)["kernel_float"] == mg.KERNEL_ATTN_SPLIT
+        (q, k, v), mem = float_inputs(rng, B, M, D, L, mg.DmemColumnMajor, mg.DmemColumnMajor, mg.float16)
+        for t, a in zip(ins, mem):
+            t.upload_data(to_bits(a, mg.float16))
+        g.run()
+        final = from_bits(f[0].download_data(), mg.float16).reshape(f[0].shape)
+        assert_close(final, mo.attention_fp32_causal_window(q, k, v, W), mg.float16, "masked output")
+        unmasked = mo.attention_fp32(q, k, v)
+        assert np.abs(final - unmasked).max() > 1e-3  # the mask does change the result
+        x = [rng.integers(0, mo.FP_PQ, size=t.shape).astype(np.uint16) for t in ins]
+        for t, a in zip(ins, x):
+            t.upload_fingerprint(a)
+        g.fingerprint()
+        assert np.array_equal(f[0].download_fingerprint(), mo.unfused_attention_fp(*x))
+
+
+def test_specialised_kernels_are_selected(runtime):
+    runtime.set_specialisation(True)
+    with mg.PyGraph(runtime) as g:
+        build_gqa(g, 8, 4, 128, 4096, 16, 4)
+        i1, i2 = g.customized_info(3), g.customized_info(4)
+        assert i1["kernel_fingerprint"] == mg.KERNEL_ATTN_SPLIT and i1["kernel_float"] == mg.KERNEL_ATTN_SPLIT
+        assert i2["kernel_fingerprint"] == mg.KERNEL_ATTN_MERGE and i2["kernel_float"] == mg.KERNEL_ATTN_MERGE
+    runtime.set_specialisation(False)
+    with mg.PyGraph(runtime) as g:
+        build_gqa(g, 8, 4, 128, 4096, 16, 4)
+        assert g.customized_info(3)["kernel_float"] == mg.KERNEL_INTERPRETER
+    runtime.set_specialisation(True)
 
 
 def test_float_baseline_c2_full_size(rt):
