@@ -117,6 +117,7 @@ struct AttnSplitParams {
   int32_t *status; // device status word
   long long q_set_stride, o_set_stride, r_set_stride;
   int heads, m, splits, forloop, stages, kv_len;
+  int tile_groups;   // warp groups that work on different KV tiles of the ring at the same time
   int k_rows_are_kv; // K staged as [kv][d] (memory of a column-major K) else [d][kv]
   int v_rows_are_kv; // V staged as [kv][d] (memory of a row-major V) else [d][kv]
   int causal_window;
@@ -124,7 +125,7 @@ struct AttnSplitParams {
 
 // Shared-memory plan: [stages x (K tile, V tile)] (1024-byte aligned) | reduction scratch | barriers | exp table
 template <int MODE, int DH>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(512)
 attn_split_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
                   const __grid_constant__ AttnSplitParams p) {
   using acc_t = typename Acc<MODE>::type;
@@ -137,8 +138,9 @@ attn_split_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
 
   int const tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   int const slice = warp & 3;          // which 16 KV positions of a tile
-  int const group = warp >> 2;         // which group of query rows
-  int const groups = blockDim.x >> 7;
+  int const groups = (blockDim.x >> 7) / p.tile_groups;
+  int const group = (warp >> 2) % groups;   // which group of query rows
+  int const tgroup = (warp >> 2) / groups;  // which of the tiles processed concurrently
   int const g = lane >> 2, t = lane & 3;
 
   int64_t const b = blockIdx.x;
@@ -148,14 +150,19 @@ attn_split_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
 
   uint32_t const stage_base = smem_u32(smem);
   int const rows_scratch = MODE == kFingerprint ? 4 : (p.m < 16 ? p.m : 16);
-  acc_t *scratch = reinterpret_cast<acc_t *>(smem + (size_t)p.stages * 2 * kTileBytes);
+  // the reduction scratch reuses the stage memory once every tile has been consumed
+  acc_t *scratch = reinterpret_cast<acc_t *>(smem);
   size_t const scratch_bytes = (size_t)(blockDim.x >> 5) * rows_scratch * (DH + 4) * sizeof(acc_t);
-  uint64_t *bars = reinterpret_cast<uint64_t *>(smem + (size_t)p.stages * 2 * kTileBytes + ((scratch_bytes + 15) & ~(size_t)15));
+  size_t const stage_bytes = (size_t)p.stages * 2 * kTileBytes;
+  size_t const data_bytes = ((scratch_bytes > stage_bytes ? scratch_bytes : stage_bytes) + 15) & ~(size_t)15;
+  uint64_t *bars = reinterpret_cast<uint64_t *>(smem + data_bytes);
   uint16_t *exp_tab = reinterpret_cast<uint16_t *>(bars + kMaxStages);
   __shared__ int s_failed;
 
   if (tid == 0) {
     s_failed = 0;
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&k_map) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&v_map) : "memory");
     for (int s = 0; s < p.stages; s++) mbar_init(smem_u32(&bars[s]), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -229,11 +236,16 @@ attn_split_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
   int const kv0 = slice * 16;               // this warp's KV positions inside a tile
   bool failed = false;
 
-  for (int it = 0; it < p.forloop; it++) {
+  // Tiles are consumed in rounds of `tile_groups`: warp group tgroup takes tile round*tile_groups + tgroup.
+  int const rounds = (p.forloop + p.tile_groups - 1) / p.tile_groups;
+  for (int round = 0; round < rounds; round++) {
+    int const it = round * p.tile_groups + tgroup;
     int s = it % p.stages;
+    bool const active = it < p.forloop;
     // After a wait has given up the block keeps walking the loop (so that every thread still meets the
     // block-wide barriers below) but stops waiting; its results are discarded at the end.
-    if (!failed && !mbar_wait(smem_u32(&bars[s]), (uint32_t)((it / p.stages) & 1))) failed = true;
+    if (active && !failed && !mbar_wait(smem_u32(&bars[s]), (uint32_t)((it / p.stages) & 1))) failed = true;
+    if (active) {
     uint32_t ktile = stage_base + (uint32_t)(s * 2 * kTileBytes), vtile = ktile + kTileBytes;
 
     // ---- S slice = Q K over this warp's 16 KV positions: two 8-wide tiles ---------------------------
@@ -310,15 +322,20 @@ attn_split_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
       mma_tile<MODE>(oacc[2 * jp + 1], ea, bfrag[2], bfrag[3]);
     }
 
-    // ---- refill the stage once every warp has read it --------------------------------------------------
+    } // active
+    // ---- refill the stages of this round once every warp has read them -----------------------------------
     if (p.forloop > p.stages) {
       __syncthreads();
-      if (tid == 0 && it + p.stages < p.forloop) issue(it + p.stages);
+      if (tid == 0)
+        for (int j = 0; j < p.tile_groups; j++) {
+          int nxt = round * p.tile_groups + j + p.stages;
+          if (nxt < p.forloop) issue(nxt);
+        }
     }
   }
 
   if (failed) s_failed = 1;
-  __syncthreads();
+  __syncthreads(); // also: every tile has been read, the stage memory may be reused as scratch
   if (s_failed) { // a bounded wait gave up: flag it and leave the outputs alone
     if (tid == 0) atomicExch(p.status, 1);
     return;
@@ -369,18 +386,25 @@ attn_split_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
   int const out_ld = p.splits * DH;
   uint16_t *o_out = static_cast<uint16_t *>(p.o_part) + set * p.o_set_stride + (int64_t)head * p.m * out_ld + split * DH;
   uint16_t *r_out = static_cast<uint16_t *>(p.r_part) + set * p.r_set_stride + (int64_t)head * p.m * p.splits + split;
+  // warp index = (tile group * groups + row group) * 4 + slice: sum over tile groups and slices.
   // pairs of adjacent columns -> one 32-bit store
   for (int i = tid; i < groups * rows_scratch * (DH / 2); i += blockDim.x) {
     int c = (i % (DH / 2)) * 2, lr = (i / (DH / 2)) % rows_scratch, gr = i / ((DH / 2) * rows_scratch);
     int row = gr * rows_per_group + lr;
     if (row >= p.m) continue;
     acc_t a0 = 0, a1 = 0;
+    for (int tg = 0; tg < p.tile_groups; tg++)
 #pragma unroll
-    for (int sl = 0; sl < 4; sl++) {
-      acc_t const *src = scratch + (size_t)(gr * 4 + sl) * rows_scratch * ld + lr * ld + c;
-      a0 += src[0];
-      a1 += src[1];
-    }
+      for (int sl = 0; sl < 4; sl++) {
+        acc_t const *src = scratch + (size_t)((tg * groups + gr) * 4 + sl) * rows_scratch * ld + lr * ld + c;
+        if (MODE == kFingerprint) { // partials are already reduced modulo PQ: no overflow for any count
+          a0 = (acc_t)(((uint32_t)a0 + (uint32_t)src[0]) % PQ);
+          a1 = (acc_t)(((uint32_t)a1 + (uint32_t)src[1]) % PQ);
+        } else {
+          a0 += src[0];
+          a1 += src[1];
+        }
+      }
     uint32_t packed;
     if (MODE == kFingerprint) packed = ((uint32_t)a0 % PQ) | (((uint32_t)a1 % PQ) << 16);
     else if (MODE == kF16) packed = pack_f16((float)a0, (float)a1);
@@ -391,8 +415,13 @@ attn_split_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
     int lr = i % rows_scratch, gr = i / rows_scratch, row = gr * rows_per_group + lr;
     if (row >= p.m) continue;
     acc_t a = 0;
+    for (int tg = 0; tg < p.tile_groups; tg++)
 #pragma unroll
-    for (int sl = 0; sl < 4; sl++) a += scratch[(size_t)(gr * 4 + sl) * rows_scratch * ld + lr * ld + DH];
+      for (int sl = 0; sl < 4; sl++) {
+        acc_t v = scratch[(size_t)((tg * groups + gr) * 4 + sl) * rows_scratch * ld + lr * ld + DH];
+        if (MODE == kFingerprint) a = (acc_t)(((uint32_t)a + (uint32_t)v) % PQ);
+        else a += v;
+      }
     uint16_t v;
     if (MODE == kFingerprint) v = (uint16_t)((uint32_t)a % PQ);
     else if (MODE == kF16) { __half h = __float2half_rn((float)a); v = *reinterpret_cast<uint16_t *>(&h); }
@@ -415,6 +444,7 @@ __global__ void __launch_bounds__(256) attn_merge_kernel(uint16_t const *o_part,
     int r = i / d, c = i % d;
     if (MODE == kFingerprint) {
       uint32_t num = 0, den = 0;
+#pragma unroll 8
       for (int s = 0; s < splits; s++) {
         num += op[(size_t)r * splits * d + s * d + c];
         den += rp[r * splits + s];
@@ -422,6 +452,7 @@ __global__ void __launch_bounds__(256) attn_merge_kernel(uint16_t const *o_part,
       dst[i] = (uint16_t)field_div(num % PQ, den % PQ);
     } else {
       float num = 0.f, den = 0.f;
+#pragma unroll 8
       for (int s = 0; s < splits; s++) {
         uint16_t a = op[(size_t)r * splits * d + s * d + c], bb = rp[r * splits + s];
         if (MODE == kF16) {
@@ -501,18 +532,25 @@ static bool shape_supported(mgd_attn_split const *p, bool fp) {
 template <int MODE, int DH>
 static int launch_split(mgd_attn_split const *p, void const *q, void const *k, void const *v, void *o, void *r, void *stream) {
   bool const fp = MODE == kFingerprint;
-  int groups = groups_for(p, fp), threads = groups * 128;
+  int groups = groups_for(p, fp);
   int rows_scratch = fp ? 4 : (p->m < 16 ? p->m : 16);
   size_t acc = 4, tile = (size_t)kTile * DH * 2;
-  size_t scratch = ((size_t)(threads / 32) * rows_scratch * (DH + 4) * acc + 15) & ~(size_t)15;
-  size_t fixed = 1024 + scratch + kMaxStages * 8 + 256;
+  size_t fixed = 1024 + kMaxStages * 8 + 256 + 16;
   int64_t blocks = (int64_t)p->heads * p->splits * p->num_sets;
   // One wave: request the whole split up front.  Many waves: shallow rings so that several blocks share an SM
   // and one block's loads overlap another's arithmetic.
   int stages = p->forloop_range < kMaxStages ? p->forloop_range : kMaxStages;
   if (blocks > sm_count() && stages > 2) stages = 2;
   while (stages > 1 && fixed + stages * 2 * tile > (size_t)kDynSmemLimit) stages--;
-  size_t smem = fixed + stages * 2 * tile;
+  // Warp groups that each take a different resident tile: the per-tile chain S -> exp -> E V is latency
+  // bound, so tiles already in shared memory are worked on side by side (at most 16 warps per block).
+  // With many waves the parallelism comes from several blocks per SM instead.
+  int tile_groups = blocks > sm_count() ? 1 : (stages < 4 ? stages : 4);
+  while (tile_groups > 1 && groups * tile_groups * 128 > 512) tile_groups--;
+  int threads = groups * tile_groups * 128;
+  size_t scratch = (size_t)(threads / 32) * rows_scratch * (DH + 4) * acc;
+  size_t data = scratch > stages * 2 * tile ? scratch : stages * 2 * tile;
+  size_t smem = fixed + ((data + 15) & ~(size_t)15);
   if (smem > (size_t)kDynSmemLimit) return set_error(MG_ERR_UNSUPPORTED, "split-KV attention: tile does not fit shared memory");
 
   CUtensorMap kmap, vmap;
@@ -530,6 +568,7 @@ static int launch_split(mgd_attn_split const *p, void const *q, void const *k, v
   if (!a.status) return set_error(MG_ERR_CUDA, "cannot allocate the device status word");
   a.q_set_stride = p->q_set_stride; a.o_set_stride = p->o_set_stride; a.r_set_stride = p->r_set_stride;
   a.heads = p->heads; a.m = p->m; a.splits = p->splits; a.forloop = p->forloop_range; a.stages = stages;
+  a.tile_groups = tile_groups;
   a.kv_len = p->kv_len; a.k_rows_are_kv = k_kv; a.v_rows_are_kv = v_kv; a.causal_window = p->causal_window;
 
   static bool configured = false;
