@@ -107,8 +107,11 @@ class Runtime:
     def set_max_smem(self, nbytes):
         check(self.lib.mg_runtime_set_max_smem(self.handle, nbytes))
 
-    def set_specialisation(self, enabled):
-        check(self.lib.mg_runtime_set_specialisation(self.handle, 1 if enabled else 0))
+    def set_specialisation(self, level):
+        """0 / False = generic interpreters only, 1 = specialised kernels, 2 / True = specialised kernels plus
+        one-launch fusion of the split-KV attention operator with its merge operator."""
+        level = 2 if level is True else (0 if level is False else int(level))
+        check(self.lib.mg_runtime_set_specialisation(self.handle, level))
 
     def tables(self):
         """Host copies of the arena's exp / div_p / div_q lookup tables."""

@@ -72,6 +72,26 @@ int refuse_dry(mg_runtime *rt) {
   return MG_OK;
 }
 
+// Launch every operator of a graph in order; a split-KV attention operator directly followed by the merge
+// operator that consumes it goes out as one launch.
+int launch_all(mg_graph *g, bool fp, bool skip_inputs, void *stream) {
+  auto &ops = g->graph.operators;
+  for (size_t i = 0; i < ops.size(); i++) {
+    KNOperator *op = ops[i];
+    if (skip_inputs && op->op_type == type::KN_INPUT_OP) continue;
+    int st;
+    if (op->op_type == type::KN_CUSTOMIZED_OP && i + 1 < ops.size() &&
+        static_cast<kernel::KNCustomizedOp *>(op)->can_fuse_with(ops[i + 1], fp)) {
+      st = static_cast<kernel::KNCustomizedOp *>(op)->launch_fused(static_cast<kernel::KNCustomizedOp *>(ops[i + 1]), fp, stream);
+      i++;
+    } else {
+      st = fp ? op->launch_fingerprint(stream) : op->launch_float(stream);
+    }
+    if (st != MG_OK) return st;
+  }
+  return MG_OK;
+}
+
 int synchronize_and_check() {
   if (g_runtime.dmm && g_runtime.dmm->dry) return fail(MG_ERR_NO_DEVICE, "planning-only runtime (device < 0)");
   MG_CUDA_TRY(cudaDeviceSynchronize());
@@ -127,7 +147,7 @@ int mg_runtime_set_max_smem(mg_runtime *rt, size_t bytes) {
 
 int mg_runtime_set_specialisation(mg_runtime *rt, int enabled) {
   if (!rt || !rt->dmm) return fail(MG_ERR_INVALID_ARGUMENT, "no runtime");
-  rt->dmm->specialise = enabled != 0;
+  rt->dmm->specialise = enabled < 0 ? 0 : (enabled > 2 ? 2 : enabled);
   return MG_OK;
 }
 
@@ -278,21 +298,14 @@ int mg_op_fingerprint(mg_graph *g, int32_t idx) {
 
 int mg_graph_fingerprint(mg_graph *g) {
   if (!g) return fail(MG_ERR_INVALID_ARGUMENT, "graph is null");
-  for (KNOperator *op : g->graph.operators) {
-    int st = op->launch_fingerprint(nullptr);
-    if (st != MG_OK) return st;
-  }
-  return synchronize_and_check();
+  int st = launch_all(g, true, false, nullptr);
+  return st != MG_OK ? st : synchronize_and_check();
 }
 
 int mg_graph_fingerprint_compute(mg_graph *g) {
   if (!g) return fail(MG_ERR_INVALID_ARGUMENT, "graph is null");
-  for (KNOperator *op : g->graph.operators) {
-    if (op->op_type == type::KN_INPUT_OP) continue;
-    int st = op->launch_fingerprint(nullptr);
-    if (st != MG_OK) return st;
-  }
-  return synchronize_and_check();
+  int st = launch_all(g, true, true, nullptr);
+  return st != MG_OK ? st : synchronize_and_check();
 }
 
 int mg_op_run(mg_graph *g, int32_t idx, void *stream) {
@@ -303,11 +316,7 @@ int mg_op_run(mg_graph *g, int32_t idx, void *stream) {
 
 int mg_graph_run(mg_graph *g, void *stream) {
   if (!g) return fail(MG_ERR_INVALID_ARGUMENT, "graph is null");
-  for (KNOperator *op : g->graph.operators) {
-    int st = op->launch_float(stream);
-    if (st != MG_OK) return st;
-  }
-  return MG_OK;
+  return launch_all(g, false, false, stream);
 }
 
 int mg_op_profile(mg_graph *g, int32_t idx, int32_t warmup, int32_t iters, float *ms) {

@@ -15,6 +15,8 @@
 #include <cstdio>
 #include <cstring>
 #include <cuda_runtime.h>
+#include <mutex>
+#include <unordered_map>
 
 namespace mg {
 static thread_local std::string g_error;
@@ -71,7 +73,7 @@ static size_t round_up(size_t n) { return (n + kAlign - 1) / kAlign * kAlign; }
 
 DeviceMemoryManager::DeviceMemoryManager(int dev, size_t arena_bytes)
     : base_ptr(nullptr), offset(0), total_size(arena_bytes), exp_lookup_table(nullptr), div_p_lookup_table(nullptr),
-      div_q_lookup_table(nullptr), device(dev), max_smem(MAX_SMEM_SIZE), specialise(true), flag_word(nullptr),
+      div_q_lookup_table(nullptr), device(dev), max_smem(MAX_SMEM_SIZE), specialise(2), flag_word(nullptr),
       dry(dev < 0), ok_(false) {
   if (dry) {
     // Planning-only runtime: addresses are handed out from a range that is never dereferenced, so that
@@ -426,6 +428,33 @@ int KNReductionOp::launch_float(void *stream) {
 bool KNReductionOp::fingerprint(void) { return sync_ok(launch_fingerprint(nullptr)); }
 bool KNReductionOp::profile(ProfileResult &r) { return profile_with_events(r, 16, 16); }
 
+// ---- what the previous launch on a stream wrote -------------------------------------------------------
+// The split-KV attention kernel is launched with programmatic stream serialisation and may start loading its
+// inputs while the previous kernel of the stream is still running.  That is only allowed when that kernel
+// (if it is one of ours that releases its successor early) did not write those inputs; every launch through
+// this file records its outputs per stream.  Kernels that do not release their successor early record nothing:
+// the successor cannot start before they complete.
+namespace {
+struct Range { char const *lo, *hi; };
+std::mutex g_track_mutex;
+std::unordered_map<void *, std::vector<Range>> g_last_outputs;
+
+void record_outputs(void *stream, std::vector<Range> const &r) {
+  std::lock_guard<std::mutex> lock(g_track_mutex);
+  g_last_outputs[stream] = r;
+}
+bool inputs_untouched(void *stream, std::vector<Range> const &inputs) {
+  std::lock_guard<std::mutex> lock(g_track_mutex);
+  auto it = g_last_outputs.find(stream);
+  if (it == g_last_outputs.end()) return true;
+  for (Range const &a : it->second)
+    for (Range const &b : inputs)
+      if (a.lo < b.hi && b.lo < a.hi) return false;
+  return true;
+}
+Range range_of(void const *p, size_t bytes) { return Range{(char const *)p, (char const *)p + bytes}; }
+} // namespace
+
 // ---- customized operator -----------------------------------------------------------------------------
 KNCustomizedOp::KNCustomizedOp(Deferred, std::vector<DTensor> const &ins, ExecutionPlan const &p)
     : KNOperator(KN_CUSTOMIZED_OP, ins), plan(p), bgraph(p.grid_dim, p.block_dim, p.forloop_range, p.reduction_dimx) {
@@ -440,6 +469,22 @@ KNCustomizedOp::KNCustomizedOp(std::vector<DTensor> const &ins, ExecutionPlan co
   if (!ok) std::fprintf(stderr, "KNCustomizedOp: %s\n", err.c_str());
   assert(ok && "invalid execution plan");
   (void)ok;
+  after_build();
+}
+
+// Decide the kernels now (the choice needs no device) and reserve what the fused launch needs.
+void KNCustomizedOp::after_build() {
+  if (!ensure_lowered()) return;
+  DeviceMemoryManager *dmm = DeviceMemoryManager::get_instance();
+  if (kernel_fp_ == mg::KERNEL_ATTN_SPLIT || kernel_float_ == mg::KERNEL_ATTN_SPLIT) {
+    size_t bytes = (size_t)program_.grid[0] * sizeof(int);
+    tickets_ = static_cast<int *>(dmm->allocate_raw(bytes));
+    if (tickets_ && !dmm->dry && cudaMemset(tickets_, 0, bytes) != cudaSuccess) {
+      cudaGetLastError();
+      dmm->free_raw(tickets_);
+      tickets_ = nullptr;
+    }
+  }
 }
 
 KNCustomizedOp *KNCustomizedOp::create(std::vector<DTensor> const &ins, ExecutionPlan const &p, std::string *error,
@@ -454,6 +499,7 @@ KNCustomizedOp *KNCustomizedOp::create(std::vector<DTensor> const &ins, Executio
     delete op;
     return nullptr;
   }
+  op->after_build();
   return op;
 }
 
@@ -584,6 +630,7 @@ KNCustomizedOp::KNCustomizedOp(std::vector<DTensor> const &ins, threadblock::Gra
     else if (t >= TB_CONCAT_0_OP && t <= TB_CONCAT_2_OP) bgraph.concat(my_inputs[0], my_inputs[1], t - TB_CONCAT_0_OP);
     else assert(false && "unsupported threadblock operator");
   }
+  after_build();
 }
 
 KNCustomizedOp::~KNCustomizedOp() {
@@ -591,6 +638,7 @@ KNCustomizedOp::~KNCustomizedOp() {
     delete bgraph.operators.back();
     bgraph.operators.pop_back();
   }
+  if (tickets_) DeviceMemoryManager::get_instance()->free_raw(tickets_);
   free_outputs(output_tensors);
 }
 
@@ -603,7 +651,7 @@ bool KNCustomizedOp::ensure_lowered() {
   }
   lowered_ = true;
   kernel_fp_ = kernel_float_ = mg::KERNEL_INTERPRETER;
-  if (DeviceMemoryManager::get_instance()->specialise) {
+  if (DeviceMemoryManager::get_instance()->specialise > 0) {
     mgd_attn_split sp;
     mgd_attn_merge mp;
     if (mg::match_attn_split(program_, 1, &sp)) {
@@ -634,16 +682,9 @@ int KNCustomizedOp::launch_fingerprint_sets(int num_sets, void const *const *in,
                                             void *const *out, long long const *out_stride, void *stream) {
   if (int dry_st = refuse_if_dry()) return dry_st;
   if (!ensure_lowered()) return MG_ERR_INVALID_GRAPH;
-  if (kernel_fp_ == mg::KERNEL_ATTN_SPLIT) {
-    mgd_attn_split sp;
-    mg::match_attn_split(program_, 1, &sp);
-    sp.num_sets = num_sets;
-    sp.q_set_stride = in_stride[0]; sp.k_set_stride = in_stride[1]; sp.v_set_stride = in_stride[2];
-    sp.o_set_stride = out_stride[0]; sp.r_set_stride = out_stride[1];
-    return finish(mgd_launch_attn_split_fingerprint(&sp, (uint16_t const *)in[0], (uint16_t const *)in[1],
-                                                    (uint16_t const *)in[2], (uint16_t *)out[0], (uint16_t *)out[1],
-                                                    stream));
-  }
+  if (kernel_fp_ == mg::KERNEL_ATTN_SPLIT)
+    return launch_split(true, num_sets, in, in_stride, out, out_stride, nullptr, stream);
+  record_outputs(stream, {});
   if (kernel_fp_ == mg::KERNEL_ATTN_MERGE) {
     mgd_attn_merge mp;
     mg::match_attn_merge(program_, &mp);
@@ -675,14 +716,12 @@ int KNCustomizedOp::launch_float(void *stream) {
   if (!ensure_lowered()) return MG_ERR_INVALID_GRAPH;
   int dt = input_tensors.empty() ? (int)DT_FLOAT16 : (int)input_tensors[0].data_type;
   if (kernel_float_ == mg::KERNEL_ATTN_SPLIT) {
-    mgd_attn_split sp;
-    mg::match_attn_split(program_, 1, &sp);
-    sp.data_type = dt;
-    sp.causal_window = causal_window;
-    return finish(mgd_launch_attn_split_float(&sp, input_tensors[0].data_ptr, input_tensors[1].data_ptr,
-                                              input_tensors[2].data_ptr, output_tensors[0].data_ptr,
-                                              output_tensors[1].data_ptr, stream));
+    void const *in[3] = {input_tensors[0].data_ptr, input_tensors[1].data_ptr, input_tensors[2].data_ptr};
+    void *out[2] = {output_tensors[0].data_ptr, output_tensors[1].data_ptr};
+    long long zs[3] = {0, 0, 0};
+    return launch_split(false, 1, in, zs, out, zs, nullptr, stream);
   }
+  record_outputs(stream, {});
   if (kernel_float_ == mg::KERNEL_ATTN_MERGE) {
     mgd_attn_merge mp;
     mg::match_attn_merge(program_, &mp);
@@ -700,6 +739,65 @@ int KNCustomizedOp::launch_float(void *stream) {
   for (size_t i = 0; i < output_tensors.size(); i++) b.out[i] = output_tensors[i].data_ptr;
   b.num_sets = 1;
   return finish(mgd_launch_float_interp(&program_, &b, dt, stream));
+}
+
+// One launch of the split-KV attention kernel; with `merge` the cross-split merge operator rides along.
+int KNCustomizedOp::launch_split(bool fp, int num_sets, void const *const *in, long long const *in_stride,
+                                 void *const *out, long long const *out_stride, KNCustomizedOp *merge, void *stream) {
+  mgd_attn_split sp;
+  mg::match_attn_split(program_, 1, &sp);
+  sp.num_sets = num_sets;
+  sp.q_set_stride = in_stride[0]; sp.k_set_stride = in_stride[1]; sp.v_set_stride = in_stride[2];
+  sp.o_set_stride = out_stride[0]; sp.r_set_stride = out_stride[1];
+  sp.data_type = (int)input_tensors[0].data_type;
+  sp.causal_window = fp ? 0 : causal_window;
+  mgd_attn_launch_opts opts;
+  std::memset(&opts, 0, sizeof(opts));
+  size_t elem = 2;
+  std::vector<Range> ins, outs;
+  for (int i = 0; i < 3; i++)
+    ins.push_back(range_of(in[i], ((size_t)(num_sets - 1) * (size_t)in_stride[i] + input_tensors[i].num_elements()) * elem));
+  for (int i = 0; i < 2; i++)
+    outs.push_back(range_of(out[i], ((size_t)(num_sets - 1) * (size_t)out_stride[i] + output_tensors[i].num_elements()) * elem));
+  if (merge != nullptr) {
+    DTensor const &o = merge->output_tensors[0];
+    opts.merged_out = fp ? (void *)o.fp_ptr : o.data_ptr;
+    opts.tickets = tickets_;
+    opts.merged_set_stride = 0;
+    outs.push_back(range_of(opts.merged_out, o.num_elements() * elem));
+  }
+  opts.overlap = 1 | (inputs_untouched(stream, ins) ? 2 : 0);
+  int st = fp ? mgd_launch_attn_split_fingerprint_ex(&sp, (uint16_t const *)in[0], (uint16_t const *)in[1],
+                                                     (uint16_t const *)in[2], (uint16_t *)out[0], (uint16_t *)out[1],
+                                                     &opts, stream)
+              : mgd_launch_attn_split_float_ex(&sp, in[0], in[1], in[2], out[0], out[1], &opts, stream);
+  record_outputs(stream, st == MG_OK ? outs : std::vector<Range>{});
+  return finish(st);
+}
+
+bool KNCustomizedOp::can_fuse_with(KNOperator *next, bool fp) {
+  if (DeviceMemoryManager::get_instance()->specialise < 2 || !tickets_ || !next) return false;
+  if (next->op_type != KN_CUSTOMIZED_OP || !ensure_lowered()) return false;
+  auto *m = static_cast<KNCustomizedOp *>(next);
+  if (!m->ensure_lowered()) return false;
+  if ((fp ? kernel_fp_ : kernel_float_) != mg::KERNEL_ATTN_SPLIT) return false;
+  if ((fp ? m->kernel_fp_ : m->kernel_float_) != mg::KERNEL_ATTN_MERGE) return false;
+  if (m->input_tensors.size() != 2 || output_tensors.size() != 2) return false;
+  for (int i = 0; i < 2; i++) {
+    DTensor const &a = output_tensors[i], &b = m->input_tensors[i];
+    if (a.data_ptr != b.data_ptr || a.fp_ptr != b.fp_ptr || a.num_elements() != b.num_elements()) return false;
+  }
+  return true;
+}
+
+int KNCustomizedOp::launch_fused(KNCustomizedOp *merge, bool fp, void *stream) {
+  if (int dry_st = refuse_if_dry()) return dry_st;
+  void const *in[3];
+  void *out[2];
+  long long zs[3] = {0, 0, 0};
+  for (int i = 0; i < 3; i++) in[i] = fp ? (void const *)input_tensors[i].fp_ptr : input_tensors[i].data_ptr;
+  for (int i = 0; i < 2; i++) out[i] = fp ? (void *)output_tensors[i].fp_ptr : output_tensors[i].data_ptr;
+  return launch_split(fp, 1, in, zs, out, zs, merge, stream);
 }
 
 bool KNCustomizedOp::fingerprint(void) { return sync_ok(launch_fingerprint(nullptr)); }

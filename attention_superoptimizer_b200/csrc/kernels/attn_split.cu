@@ -121,6 +121,10 @@ struct AttnSplitParams {
   int k_rows_are_kv; // K staged as [kv][d] (memory of a column-major K) else [d][kv]
   int v_rows_are_kv; // V staged as [kv][d] (memory of a row-major V) else [d][kv]
   int causal_window;
+  void *merged_out;     // non-null: the last block of a head also merges the head's partials
+  int32_t *tickets;     // one counter per (set, head)
+  long long merged_set_stride;
+  int early_loads;      // tile loads may be issued before the wait on the previous kernel of the stream
 };
 
 // Shared-memory plan: [stages x (K tile, V tile)] (1024-byte aligned) | reduction scratch | barriers | exp table
@@ -189,14 +193,9 @@ attn_split_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
       tma_load_3d(vdst, &v_map, bar, kv0, 0, batch);
     }
   };
-  if (tid == 0) {
-    int first = p.forloop < p.stages ? p.forloop : p.stages;
-    for (int it = 0; it < first; it++) issue(it);
-  }
-
   // ---- Q fragments, resident in registers -----------------------------------------------------------
   uint32_t qa[kKSteps][4];
-  {
+  auto load_q = [&]() {
     uint16_t const *q = static_cast<uint16_t const *>(p.q) + set * p.q_set_stride + (int64_t)head * p.m * DH;
     if (MODE == kFingerprint) {
       int row = group * 4 + (g & 3);
@@ -223,7 +222,26 @@ attn_split_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
         qa[ks][3] = r1 < p.m ? __ldg(reinterpret_cast<uint32_t const *>(q + (size_t)r1 * DH + ks * 16 + 8 + 2 * t)) : 0u;
       }
     }
+  };
+  auto issue_first = [&]() {
+    if (tid == 0) {
+      int first = p.forloop < p.stages ? p.forloop : p.stages;
+      for (int it = 0; it < first; it++) issue(it);
+    }
+  };
+  // Ordering against the previous kernel of the stream (programmatic dependent launch): nothing is written
+  // to global memory, and no input that kernel may have produced is read, before griddepcontrol.wait; the next
+  // kernel is released right after, so at most two kernels of a stream are ever in flight.
+  if (p.early_loads) {
+    issue_first();
+    load_q();
   }
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (!p.early_loads) {
+    issue_first();
+    load_q();
+  }
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   acc_t oacc[2 * kNPairs][4];
 #pragma unroll
@@ -428,6 +446,53 @@ attn_split_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
     else { __nv_bfloat16 h = __float2bfloat16_rn((float)a); v = *reinterpret_cast<uint16_t *>(&h); }
     r_out[(size_t)row * p.splits] = v;
   }
+
+  // ---- optional: the last block of this head merges the head's partials ------------------------------------
+  if (p.merged_out != nullptr) {
+    __shared__ int s_last;
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+      int ticket = atomicAdd(&p.tickets[set * p.heads + head], 1);
+      s_last = ticket == p.splits - 1;
+    }
+    __syncthreads();
+    if (s_last) {
+      __threadfence();
+      uint16_t const *op = static_cast<uint16_t const *>(p.o_part) + set * p.o_set_stride + (int64_t)head * p.m * out_ld;
+      uint16_t const *rp = static_cast<uint16_t const *>(p.r_part) + set * p.r_set_stride + (int64_t)head * p.m * p.splits;
+      uint16_t *dst = static_cast<uint16_t *>(p.merged_out) + set * p.merged_set_stride + (int64_t)head * p.m * DH;
+      for (int i = tid; i < p.m * DH; i += blockDim.x) {
+        int r = i / DH, c = i % DH;
+        if (MODE == kFingerprint) {
+          uint32_t num = 0, den = 0;
+#pragma unroll 8
+          for (int sp = 0; sp < p.splits; sp++) {
+            num += __ldcg(op + (size_t)r * out_ld + sp * DH + c);
+            den += __ldcg(rp + r * p.splits + sp);
+          }
+          dst[i] = (uint16_t)field_div(num % PQ, den % PQ);
+        } else {
+          float num = 0.f, den = 0.f;
+#pragma unroll 8
+          for (int sp = 0; sp < p.splits; sp++) {
+            uint16_t a = __ldcg(op + (size_t)r * out_ld + sp * DH + c), bb = __ldcg(rp + r * p.splits + sp);
+            if (MODE == kF16) {
+              num += __half2float(*reinterpret_cast<__half const *>(&a));
+              den += __half2float(*reinterpret_cast<__half const *>(&bb));
+            } else {
+              num += __bfloat162float(*reinterpret_cast<__nv_bfloat16 const *>(&a));
+              den += __bfloat162float(*reinterpret_cast<__nv_bfloat16 const *>(&bb));
+            }
+          }
+          float v = num / den;
+          if (MODE == kF16) { __half h = __float2half_rn(v); dst[i] = *reinterpret_cast<uint16_t *>(&h); }
+          else { __nv_bfloat16 h = __float2bfloat16_rn(v); dst[i] = *reinterpret_cast<uint16_t *>(&h); }
+        }
+      }
+      if (tid == 0) p.tickets[set * p.heads + head] = 0; // ready for the next launch
+    }
+  }
 }
 
 // ---- merge: O = sum_s O_part[.., s*d + c] / sum_s R_part[.., s] ---------------------------------------------
@@ -530,7 +595,8 @@ static bool shape_supported(mgd_attn_split const *p, bool fp) {
 }
 
 template <int MODE, int DH>
-static int launch_split(mgd_attn_split const *p, void const *q, void const *k, void const *v, void *o, void *r, void *stream) {
+static int launch_split(mgd_attn_split const *p, void const *q, void const *k, void const *v, void *o, void *r,
+                        mgd_attn_launch_opts const *opts, void *stream) {
   bool const fp = MODE == kFingerprint;
   int groups = groups_for(p, fp);
   int rows_scratch = fp ? 4 : (p->m < 16 ? p->m : 16);
@@ -569,6 +635,11 @@ static int launch_split(mgd_attn_split const *p, void const *q, void const *k, v
   a.q_set_stride = p->q_set_stride; a.o_set_stride = p->o_set_stride; a.r_set_stride = p->r_set_stride;
   a.heads = p->heads; a.m = p->m; a.splits = p->splits; a.forloop = p->forloop_range; a.stages = stages;
   a.tile_groups = tile_groups;
+  a.merged_out = opts ? opts->merged_out : nullptr;
+  a.tickets = opts ? opts->tickets : nullptr;
+  a.merged_set_stride = opts ? opts->merged_set_stride : 0;
+  a.early_loads = opts && (opts->overlap & 2) ? 1 : 0;
+  if (a.merged_out && !a.tickets) return set_error(MG_ERR_INVALID_ARGUMENT, "split-KV attention: merging needs ticket counters");
   a.kv_len = p->kv_len; a.k_rows_are_kv = k_kv; a.v_rows_are_kv = v_kv; a.causal_window = p->causal_window;
 
   static bool configured = false;
@@ -578,7 +649,19 @@ static int launch_split(mgd_attn_split const *p, void const *q, void const *k, v
     configured = true;
   }
   if (blocks > 0x7fffffffLL) return set_error(MG_ERR_UNSUPPORTED, "too many blocks for one launch");
-  attn_split_kernel<MODE, DH><<<(unsigned)blocks, threads, smem, (cudaStream_t)stream>>>(kmap, vmap, a);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)blocks, 1, 1);
+  cfg.blockDim = dim3((unsigned)threads, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = (cudaStream_t)stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  if (opts && (opts->overlap & 1)) {
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+  }
+  cudaLaunchKernelEx(&cfg, attn_split_kernel<MODE, DH>, kmap, vmap, a);
   return check_launch("attn_split_kernel");
 }
 } // namespace mgk
@@ -591,21 +674,31 @@ int mgd_attn_split_supported(const mgd_attn_split *p, int32_t fingerprint_mode) 
   return shape_supported(p, fingerprint_mode != 0) && encode_fn() != nullptr ? 1 : 0;
 }
 
-int mgd_launch_attn_split_float(const mgd_attn_split *p, const void *q, const void *k, const void *v, void *o,
-                                void *r, void *stream) {
+int mgd_launch_attn_split_float_ex(const mgd_attn_split *p, const void *q, const void *k, const void *v, void *o,
+                                   void *r, const mgd_attn_launch_opts *opts, void *stream) {
   if (!q || !k || !v || !o || !r) return set_error(MG_ERR_INVALID_ARGUMENT, "split-KV attention: null tensor");
   if (!shape_supported(p, false)) return set_error(MG_ERR_UNSUPPORTED, "split-KV attention: shape not supported");
   if (p->data_type == MG_DT_FLOAT16)
-    return p->d == 128 ? launch_split<kF16, 128>(p, q, k, v, o, r, stream) : launch_split<kF16, 64>(p, q, k, v, o, r, stream);
-  return p->d == 128 ? launch_split<kBF16, 128>(p, q, k, v, o, r, stream) : launch_split<kBF16, 64>(p, q, k, v, o, r, stream);
+    return p->d == 128 ? launch_split<kF16, 128>(p, q, k, v, o, r, opts, stream) : launch_split<kF16, 64>(p, q, k, v, o, r, opts, stream);
+  return p->d == 128 ? launch_split<kBF16, 128>(p, q, k, v, o, r, opts, stream) : launch_split<kBF16, 64>(p, q, k, v, o, r, opts, stream);
+}
+
+int mgd_launch_attn_split_fingerprint_ex(const mgd_attn_split *p, const uint16_t *q, const uint16_t *k, const uint16_t *v,
+                                         uint16_t *o, uint16_t *r, const mgd_attn_launch_opts *opts, void *stream) {
+  if (!q || !k || !v || !o || !r) return set_error(MG_ERR_INVALID_ARGUMENT, "split-KV attention: null tensor");
+  if (!shape_supported(p, true)) return set_error(MG_ERR_UNSUPPORTED, "split-KV attention: shape not supported");
+  return p->d == 128 ? launch_split<kFingerprint, 128>(p, q, k, v, o, r, opts, stream)
+                     : launch_split<kFingerprint, 64>(p, q, k, v, o, r, opts, stream);
+}
+
+int mgd_launch_attn_split_float(const mgd_attn_split *p, const void *q, const void *k, const void *v, void *o,
+                                void *r, void *stream) {
+  return mgd_launch_attn_split_float_ex(p, q, k, v, o, r, nullptr, stream);
 }
 
 int mgd_launch_attn_split_fingerprint(const mgd_attn_split *p, const uint16_t *q, const uint16_t *k, const uint16_t *v,
                                       uint16_t *o, uint16_t *r, void *stream) {
-  if (!q || !k || !v || !o || !r) return set_error(MG_ERR_INVALID_ARGUMENT, "split-KV attention: null tensor");
-  if (!shape_supported(p, true)) return set_error(MG_ERR_UNSUPPORTED, "split-KV attention: shape not supported");
-  return p->d == 128 ? launch_split<kFingerprint, 128>(p, q, k, v, o, r, stream)
-                     : launch_split<kFingerprint, 64>(p, q, k, v, o, r, stream);
+  return mgd_launch_attn_split_fingerprint_ex(p, q, k, v, o, r, nullptr, stream);
 }
 
 int mgd_attn_merge_supported(const mgd_attn_merge *p, int32_t) {

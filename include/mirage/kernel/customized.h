@@ -35,6 +35,10 @@ public:
 
   // which kernel `launch_*` picks: 0 = generic interpreter, >0 = a specialised kernel (see kernel_select.h)
   int selected_kernel(bool fingerprint_mode);
+  // True when `next` is the cross-split merge operator consuming exactly this operator's two outputs and
+  // both run on the specialised kernels: the pair can then be issued as ONE launch.
+  bool can_fuse_with(KNOperator *next, bool fingerprint_mode);
+  int launch_fused(KNCustomizedOp *merge, bool fingerprint_mode, void *stream);
 
   mirage::threadblock::ExecutionPlan plan;
   mirage::threadblock::Graph bgraph;
@@ -53,6 +57,10 @@ private:
   mgd_program program_;
   int kernel_fp_ = -1, kernel_float_ = -1;
   bool ensure_lowered();
+  void after_build();
+  int launch_split(bool fingerprint_mode, int num_sets, void const *const *in, long long const *in_stride,
+                   void *const *out, long long const *out_stride, KNCustomizedOp *merge, void *stream);
+  int *tickets_ = nullptr; // per-head "last block done" counters of the fused launch (arena scratch)
 };
 
 } // namespace kernel

@@ -40,7 +40,8 @@ public:
   mirage::type::FPType *div_q_lookup_table;
   int device;
   size_t max_smem;     // budget handed to new threadblock graphs
-  bool specialise;     // allow pattern-specialised kernels
+  int specialise;      // 0 = generic interpreters only, 1 = pattern-specialised kernels, 2 = also fuse a
+                       // split-KV attention operator with the merge operator that consumes it (default)
   int *flag_word;      // 4-byte device scratch for comparisons
   bool dry;            // planning-only: no device memory behind the arena, launches refused
 

@@ -112,9 +112,10 @@ int mg_runtime_arena_usage(mg_runtime *rt, size_t *used_bytes, size_t *total_byt
 /* per-SM shared-memory budget the graph builder validates against
  * (reference: MAX_SMEM_SIZE, include/mirage/type.h:35; here the sm_100 limit by default) */
 int mg_runtime_set_max_smem(mg_runtime *rt, size_t bytes);
-/* select which kernels may be chosen: 0 = generic interpreters only, 1 = pattern-specialised kernels
- * where a graph matches (default) */
-int mg_runtime_set_specialisation(mg_runtime *rt, int enabled);
+/* select which kernels may be chosen for operators created afterwards: 0 = generic interpreters only,
+ * 1 = pattern-specialised kernels where a graph matches, 2 = also issue a split-KV attention operator and the
+ * merge operator consuming it as one launch when a whole graph is run (default) */
+int mg_runtime_set_specialisation(mg_runtime *rt, int level);
 
 /* ---- kernel graph ---------------------------------------------------------
  * kernel::Graph, include/mirage/kernel/graph.h:28-85 */

@@ -97,6 +97,26 @@ typedef struct mgd_attn_split {
   int64_t q_set_stride, k_set_stride, v_set_stride, o_set_stride, r_set_stride; /* elements */
 } mgd_attn_split;
 int mgd_attn_split_supported(const mgd_attn_split *p, int32_t fingerprint_mode);
+/* Optional extras of one split-KV launch.
+ *  merged_out / tickets: also perform the second customized op of the example (:80-103) in the same launch -
+ *    the last block of a head to finish sums the head's partials and divides ("last block done" ticket).
+ *    tickets = heads * num_sets int32 in device memory, zero before the first use; the kernel leaves them zero.
+ *  overlap: bit 0 = launch with programmatic stream serialisation, so that this kernel's blocks may be scheduled
+ *    while the previous kernel of the stream drains (every global write still waits for that kernel's completion);
+ *    bit 1 = none of the inputs was written by the previous kernel of this library on this stream, so the tile
+ *    loads may be issued before that wait. */
+typedef struct mgd_attn_launch_opts {
+  void *merged_out;          /* [num_sets][heads][m][d], NULL = partials only */
+  int32_t *tickets;
+  int64_t merged_set_stride;
+  int32_t overlap;
+  int32_t reserved;
+} mgd_attn_launch_opts;
+int mgd_launch_attn_split_float_ex(const mgd_attn_split *p, const void *q, const void *k, const void *v, void *o_part,
+                                   void *r_part, const mgd_attn_launch_opts *opts, void *stream);
+int mgd_launch_attn_split_fingerprint_ex(const mgd_attn_split *p, const uint16_t *q, const uint16_t *k,
+                                         const uint16_t *v, uint16_t *o_part, uint16_t *r_part,
+                                         const mgd_attn_launch_opts *opts, void *stream);
 int mgd_launch_attn_split_float(const mgd_attn_split *p, const void *q, const void *k, const void *v, void *o_part,
                                 void *r_part, void *stream);
 int mgd_launch_attn_split_fingerprint(const mgd_attn_split *p, const uint16_t *q, const uint16_t *k,

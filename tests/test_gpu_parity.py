@@ -38,12 +38,12 @@ def oracle_fp(ins, plans, x):
     return o1, mo.run_fingerprint(g2, o1)
 
 
-@pytest.fixture(params=[True, False], ids=["specialised", "interpreter"])
+@pytest.fixture(params=[2, 1, 0], ids=["fused", "specialised", "interpreter"])
 def rt(request, runtime):
     runtime.set_max_smem(BIG)
     runtime.set_specialisation(request.param)
     yield runtime
-    runtime.set_specialisation(True)
+    runtime.set_specialisation(2)
 
 
 def test_lookup_tables_on_device(runtime):
