@@ -596,7 +596,7 @@ static bool shape_supported(mgd_attn_split const *p, bool fp) {
 
 template <int MODE, int DH>
 static int launch_split(mgd_attn_split const *p, void const *q, void const *k, void const *v, void *o, void *r,
-                        mgd_attn_launch_opts const *opts, void *stream) {
+                        mgd_attn_launch_opts const *opts, void *stream, int32_t *status_word = nullptr) {
   bool const fp = MODE == kFingerprint;
   int groups = groups_for(p, fp);
   int rows_scratch = fp ? 4 : (p->m < 16 ? p->m : 16);
@@ -630,7 +630,7 @@ static int launch_split(mgd_attn_split const *p, void const *q, void const *k, v
 
   AttnSplitParams a;
   a.q = q; a.o_part = o; a.r_part = r;
-  a.status = device_error_word();
+  a.status = status_word ? status_word : device_error_word();
   if (!a.status) return set_error(MG_ERR_CUDA, "cannot allocate the device status word");
   a.q_set_stride = p->q_set_stride; a.o_set_stride = p->o_set_stride; a.r_set_stride = p->r_set_stride;
   a.heads = p->heads; a.m = p->m; a.splits = p->splits; a.forloop = p->forloop_range; a.stages = stages;
@@ -664,11 +664,81 @@ static int launch_split(mgd_attn_split const *p, void const *q, void const *k, v
   cudaLaunchKernelEx(&cfg, attn_split_kernel<MODE, DH>, kmap, vmap, a);
   return check_launch("attn_split_kernel");
 }
+// ---- scratch of the allocation-free entry point ---------------------------------------------------------------
+// One ticket counter per (input set, head) followed by one status word.  The array lives in the library image:
+// every GPU that loads the library holds these 16.6 KB until the process exits.  On the host the name below is
+// only a handle for cudaGetSymbolAddress - it is NOT a device address and must never be handed to a kernel.
+constexpr int kNoAllocMaxHeads = 4096;
+static __device__ __align__(256) int32_t g_noalloc_scratch[kNoAllocMaxHeads + 64];
+
+// Device address of g_noalloc_scratch on the current device; looked up once per device.
+static int noalloc_scratch(int32_t **ptr) {
+  static int32_t *per_device[64] = {nullptr};
+  static std::mutex mutex;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return set_error(MG_ERR_CUDA, "no current CUDA device");
+  std::lock_guard<std::mutex> lock(mutex);
+  if (!per_device[dev]) {
+    void *addr = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&addr, g_noalloc_scratch);
+    if (e != cudaSuccess || !addr) {
+      cudaGetLastError();
+      return set_error(MG_ERR_CUDA, "cudaGetSymbolAddress(g_noalloc_scratch) failed");
+    }
+    per_device[dev] = static_cast<int32_t *>(addr);
+  }
+  *ptr = per_device[dev];
+  return MG_OK;
+}
 } // namespace mgk
 
 using namespace mgk;
 
 extern "C" {
+
+int mgd_attn_decode_fused_noalloc(const mgd_attn_split *p, const void *q, const void *k, const void *v, void *o_part,
+                                  void *r_part, void *out, int32_t fingerprint_mode, int32_t check_status,
+                                  void *stream) {
+  if (!p || !q || !k || !v || !o_part || !r_part || !out)
+    return set_error(MG_ERR_INVALID_ARGUMENT, "allocation-free decode: null argument");
+  bool const fp = fingerprint_mode != 0;
+  if (!shape_supported(p, fp)) return set_error(MG_ERR_UNSUPPORTED, "allocation-free decode: shape not supported");
+  int64_t counters = (int64_t)p->heads * p->num_sets;
+  if (counters > kNoAllocMaxHeads)
+    return set_error(MG_ERR_INVALID_ARGUMENT,
+                     "allocation-free decode: heads * num_sets exceeds the 4096 ticket counters of the built-in scratch");
+  int32_t *scratch = nullptr;
+  int st = noalloc_scratch(&scratch);
+  if (st != MG_OK) return st;
+  // the counters must start at zero; an earlier call that was cut short may have left some behind
+  if (cudaMemsetAsync(scratch, 0, (size_t)counters * sizeof(int32_t), (cudaStream_t)stream) != cudaSuccess)
+    return check_launch("cudaMemsetAsync(ticket counters)");
+  mgd_attn_launch_opts opts;
+  opts.merged_out = out;
+  opts.tickets = scratch;
+  opts.merged_set_stride = (int64_t)p->heads * p->m * p->d;
+  opts.overlap = 0;
+  opts.reserved = 0;
+  int32_t *status = scratch + kNoAllocMaxHeads;
+  if (fp)
+    st = p->d == 128 ? launch_split<kFingerprint, 128>(p, q, k, v, o_part, r_part, &opts, stream, status)
+                     : launch_split<kFingerprint, 64>(p, q, k, v, o_part, r_part, &opts, stream, status);
+  else if (p->data_type == MG_DT_FLOAT16)
+    st = p->d == 128 ? launch_split<kF16, 128>(p, q, k, v, o_part, r_part, &opts, stream, status)
+                     : launch_split<kF16, 64>(p, q, k, v, o_part, r_part, &opts, stream, status);
+  else
+    st = p->d == 128 ? launch_split<kBF16, 128>(p, q, k, v, o_part, r_part, &opts, stream, status)
+                     : launch_split<kBF16, 64>(p, q, k, v, o_part, r_part, &opts, stream, status);
+  if (st != MG_OK || !check_status) return st;
+  if (cudaStreamSynchronize((cudaStream_t)stream) != cudaSuccess) return check_launch("cudaStreamSynchronize");
+  int32_t code = 0;
+  if (cudaMemcpy(&code, status, sizeof(code), cudaMemcpyDeviceToHost) != cudaSuccess) return check_launch("status read");
+  if (code != 0) {
+    cudaMemset(status, 0, sizeof(code));
+    return set_error(MG_ERR_DEVICE_TIMEOUT, "allocation-free decode: a bounded device wait gave up; outputs are incomplete");
+  }
+  return MG_OK;
+}
 
 int mgd_attn_split_supported(const mgd_attn_split *p, int32_t fingerprint_mode) {
   return shape_supported(p, fingerprint_mode != 0) && encode_fn() != nullptr ? 1 : 0;

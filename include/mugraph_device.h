@@ -122,6 +122,32 @@ int mgd_launch_attn_split_float(const mgd_attn_split *p, const void *q, const vo
 int mgd_launch_attn_split_fingerprint(const mgd_attn_split *p, const uint16_t *q, const uint16_t *k,
                                       const uint16_t *v, uint16_t *o_part, uint16_t *r_part, void *stream);
 
+/* Allocation-free variant of the fused decode launch (split-KV partials + cross-split merge in one kernel).
+ * It has no counterpart in the reference.
+ *
+ * Who needs it: a host that has already handed the GPU's memory to its own pool (a serving process whose
+ * allocator owns the device, or an embedding of this library next to another arena like the reference's
+ * 10 GiB slab) cannot count on a cudaMalloc inside a library succeeding, and a latency-critical loop cannot
+ * afford one, because cudaMalloc / cudaFree synchronise the device.  This entry point therefore calls no
+ * cudaMalloc, cudaFree or any allocating routine: the "last block done" ticket counters and the status word
+ * live in a file-scope device array of the library (16.6 KB per GPU that loads the library, held until exit).
+ *
+ * Limit: heads * num_sets <= 4096 counters; larger requests are rejected with MG_ERR_INVALID_ARGUMENT.
+ * The caller passes every tensor: q, k, v (inputs), o_part, r_part (partials, also outputs) and out
+ * ([num_sets][heads][m][d], dense).  p->o_set_stride / r_set_stride / q_set_stride describe the set pitch of
+ * those buffers as in mgd_attn_split.
+ *
+ * First call on a device: looks up the device address of the array (cudaGetSymbolAddress, with that device
+ * current) and configures the kernel's shared-memory limit; make that first call before any stream capture.
+ * Every call shares the one array: the counters are cleared on `stream` at the start of each call, so two calls
+ * that overlap on the GPU (different streams, or anything else that lets them run concurrently) race on them
+ * and must be serialised by the caller.
+ * check_status != 0: synchronise `stream` after the launch and return MG_ERR_DEVICE_TIMEOUT if a bounded device
+ * wait gave up (4-byte copy, still no allocation); 0: fully asynchronous, nothing is reported. */
+int mgd_attn_decode_fused_noalloc(const mgd_attn_split *p, const void *q, const void *k, const void *v, void *o_part,
+                                  void *r_part, void *out, int32_t fingerprint_mode, int32_t check_status,
+                                  void *stream);
+
 /* op2 of the same example (:80-103): O = (sum over splits of O_part) / (sum over splits of R_part) */
 typedef struct mgd_attn_merge {
   int32_t heads, m, d, splits;
