@@ -32,7 +32,7 @@ TB_REDUCTION_0_TO_DIMX_OP, TB_REDUCTION_1_TO_DIMX_OP, TB_REDUCTION_2_TO_DIMX_OP 
 TB_CONCAT_0_OP, TB_CONCAT_1_OP, TB_CONCAT_2_OP = 2200, 2201, 2202
 FP_P, FP_Q, FP_PQ = 227, 113, 25651
 
-KERNEL_INTERPRETER, KERNEL_ATTN_SPLIT, KERNEL_ATTN_MERGE = 0, 1, 2
+KERNEL_INTERPRETER, KERNEL_ATTN_SPLIT, KERNEL_ATTN_MERGE, KERNEL_ATTN_ROWS = 0, 1, 2, 3
 
 
 class InputNotFoundError(Exception):
@@ -379,6 +379,24 @@ def launch_count():
 
 
 # ---- the benchmark muGraphs as plans --------------------------------------------------------------
+def attention_prefill_plans(heads, seq_q, head_dim, kv_len, q_tile=128, kv_tile=128):
+    """The two customized operators of the dense (prefill) attention muGraph (pattern of the reference's
+    cpp_examples/multi_head_attn_prefill.cc:43-98): op1 accumulates E V and rowsum(E) over KV tiles for a tile of
+    query rows, op2 divides.  Inputs Q[heads, seq_q, d], K[heads, d, kv_len], V[heads, kv_len, d]."""
+    qt = seq_q // q_tile
+    plan1 = ExecutionPlan(
+        ops=[(TB_MATMUL_OP, [(0, 0), (1, 0)]), (TB_EXP_OP, [(3, 0)]),
+             (TB_MATMUL_OP, [(4, 0), (2, 0)]), (TB_REDUCTION_2_OP, [(4, 0)])],
+        input_map=[(0, 1, -1), (0, -1, -1), (0, -1, -1)], forloop_dim=[-1, 2, 1],
+        input_smem_layouts=[SmemRowMajor, SmemColumnMajor, SmemColumnMajor],
+        output_map=(0, 1, -1), forloop_range=kv_len // kv_tile, grid_dim=(heads, qt, 1), reduction_dimx=head_dim)
+    plan2 = ExecutionPlan(
+        ops=[(TB_DIV_OP, [(0, 0), (1, 0)])], input_map=[(0, 1, -1), (0, 1, -1)], forloop_dim=[-1, -1],
+        input_smem_layouts=[SmemRowMajor, SmemRowMajor], output_map=(0, 1, -1), forloop_range=1,
+        grid_dim=(heads, qt, 1), reduction_dimx=head_dim)
+    return plan1, plan2
+
+
 def gqa_decode_plans(num_kv_heads, group, head_dim, kv_len, splits, forloop_range):
     """The two customized operators of the grouped-query decode muGraph (pattern of the reference's
     cpp_examples/group_query_attn_inc_decode.cc:46-103).  Returns (plan1, plan2)."""

@@ -72,6 +72,46 @@ bool match_attn_split(mgd_program const &p, int, mgd_attn_split *out) {
   return true;
 }
 
+bool match_attn_rows(mgd_program const &p, mgd_attn_rows *out) {
+  if (p.num_ops != 9 || p.num_inputs != 3 || p.num_outputs != 2 || p.grid[2] != 1) return false;
+  mgd_op const *o = p.ops;
+  if (!is_input(o[0]) || !is_input(o[1]) || !is_input(o[2])) return false;
+  if (o[3].type != MG_TB_MATMUL_OP || o[4].type != MG_TB_EXP_OP || o[5].type != MG_TB_MATMUL_OP) return false;
+  if (o[6].type != MG_TB_REDUCTION_0_OP && o[6].type != MG_TB_REDUCTION_1_OP && o[6].type != MG_TB_REDUCTION_2_OP)
+    return false;
+  if (!is_output(o[7]) || !is_output(o[8])) return false;
+  int m = o[0].a[14], d = o[0].a[15], tkv = o[1].a[15], fr = p.forloop_range, gy = p.grid[1];
+  auto head_only = [](mgd_op const &in) {
+    return in.a[8] == in.a[12] * in.a[13] && in.a[9] == 0 && in.a[10] == 0 && in.a[11] == 0 && in.a[0] == 0 &&
+           in.a[2] == 0 && in.a[3] == 0 && in.a[5] == 0;
+  };
+  if (!head_only(o[0]) || !head_only(o[1]) || !head_only(o[2])) return false;
+  // Q: rows tiled by grid.y only
+  if (o[0].a[1] != m || o[0].a[4] || o[0].a[6] || o[0].a[7] || o[0].a[12] != m * gy || o[0].a[13] != d) return false;
+  // K[d, kv]: columns tiled by the for-loop only;  V[kv, d]: rows tiled by the for-loop only
+  if (o[1].a[1] || o[1].a[4] || o[1].a[6] || o[1].a[7] != tkv || o[1].a[14] != d || o[1].a[12] != d || o[1].a[13] != tkv * fr) return false;
+  if (o[2].a[1] || o[2].a[4] || o[2].a[7] || o[2].a[6] != tkv || o[2].a[14] != tkv || o[2].a[15] != d || o[2].a[13] != d ||
+      o[2].a[12] != tkv * fr)
+    return false;
+  if (o[3].a[0] != m || o[3].a[1] != tkv || o[3].a[2] != d || o[3].a[3] != o[0].a[17] || o[3].a[4] != o[1].a[17]) return false;
+  if (o[4].a[0] != o[3].a[5] || o[4].a[1] != m * tkv) return false;
+  if (o[5].a[0] != m || o[5].a[1] != d || o[5].a[2] != tkv || o[5].a[3] != o[3].a[5] || o[5].a[4] != o[2].a[17]) return false;
+  if (o[6].a[3] != o[3].a[5] || o[6].a[0] != m || o[6].a[1] != tkv || o[6].a[2] != 1) return false;
+  if (o[7].a[13] != o[5].a[5] || o[8].a[13] != o[6].a[4]) return false;
+  // outputs: rows placed by grid.y, heads by grid.x
+  if (o[7].a[11] != m || o[7].a[12] != d || o[7].a[9] != m * gy || o[7].a[10] != d || o[7].a[1] != m || o[7].a[6] != m * gy * d ||
+      o[7].a[0] || o[7].a[2] || o[7].a[3] || o[7].a[4] || o[7].a[5] || o[7].a[7] || o[7].a[8])
+    return false;
+  if (o[8].a[11] != m || o[8].a[12] != 1 || o[8].a[9] != m * gy || o[8].a[10] != 1 || o[8].a[1] != m || o[8].a[6] != m * gy ||
+      o[8].a[0] || o[8].a[2] || o[8].a[3] || o[8].a[4] || o[8].a[5] || o[8].a[7] || o[8].a[8])
+    return false;
+  std::memset(out, 0, sizeof(*out));
+  out->heads = p.grid[0]; out->seq_q = m * gy; out->d = d; out->kv_len = tkv * fr;
+  out->tile_m = m; out->tile_kv = tkv; out->forloop_range = fr;
+  out->k_layout = o[1].a[16]; out->v_layout = o[2].a[16];
+  return true;
+}
+
 bool match_attn_merge(mgd_program const &p, mgd_attn_merge *out) {
   // ops: in O_part, in R_part, reduction_to_dimx(O_part), reduction(R_part), div, out
   if (p.num_ops != 6 || p.num_inputs != 2 || p.num_outputs != 1) return false;

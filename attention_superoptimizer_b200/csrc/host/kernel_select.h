@@ -7,10 +7,13 @@ enum KernelId {
   KERNEL_INTERPRETER = 0,  // generic interpreter (any valid graph)
   KERNEL_ATTN_SPLIT = 1,   // S=QK, E=exp(S), O'=EV, R'=rowsum(E) summed over the for-loop, per KV split
   KERNEL_ATTN_MERGE = 2,   // O = sum_splits(O_part) / sum_splits(R_part)
+  KERNEL_ATTN_ROWS = 3,    // same chain with query rows split over grid.y and the whole KV axis in the for-loop
 };
 // Recognise the split-KV attention operator (pattern of the reference's
 // cpp_examples/group_query_attn_inc_decode.cc:46-79); fills `out` on success.
 bool match_attn_split(mgd_program const &p, int leading_dims_of_inputs, mgd_attn_split *out);
 // Recognise the cross-split reduction + division (same file, :80-103).
 bool match_attn_merge(mgd_program const &p, mgd_attn_merge *out);
+// Recognise the dense (prefill) form: pattern of cpp_examples/multi_head_attn_prefill.cc:43-98.
+bool match_attn_rows(mgd_program const &p, mgd_attn_rows *out);
 } // namespace mg

@@ -659,6 +659,9 @@ bool KNCustomizedOp::ensure_lowered() {
       sp.causal_window = causal_window;
       if (mgd_attn_split_supported(&sp, 1)) kernel_fp_ = mg::KERNEL_ATTN_SPLIT;
       if (mgd_attn_split_supported(&sp, 0)) kernel_float_ = mg::KERNEL_ATTN_SPLIT;
+    } else if (mgd_attn_rows rp; mg::match_attn_rows(program_, &rp)) {
+      rp.data_type = (int)input_tensors[0].data_type;
+      if (causal_window == 0 && mgd_attn_rows_supported(&rp)) kernel_float_ = mg::KERNEL_ATTN_ROWS;
     } else if (mg::match_attn_merge(program_, &mp)) {
       mp.data_type = (int)input_tensors[0].data_type;
       if (mgd_attn_merge_supported(&mp, 1)) kernel_fp_ = mg::KERNEL_ATTN_MERGE;
@@ -722,6 +725,15 @@ int KNCustomizedOp::launch_float(void *stream) {
     return launch_split(false, 1, in, zs, out, zs, nullptr, stream);
   }
   record_outputs(stream, {});
+  if (kernel_float_ == mg::KERNEL_ATTN_ROWS) {
+    mgd_attn_rows rp;
+    mg::match_attn_rows(program_, &rp);
+    rp.data_type = dt;
+    record_outputs(stream, {});
+    return finish(mgd_launch_attn_rows_float(&rp, input_tensors[0].data_ptr, input_tensors[1].data_ptr,
+                                             input_tensors[2].data_ptr, output_tensors[0].data_ptr,
+                                             output_tensors[1].data_ptr, stream));
+  }
   if (kernel_float_ == mg::KERNEL_ATTN_MERGE) {
     mgd_attn_merge mp;
     mg::match_attn_merge(program_, &mp);

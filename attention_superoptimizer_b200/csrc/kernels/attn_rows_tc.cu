@@ -1,0 +1,385 @@
+// Dense attention operator on the 5th-generation tensor cores (tcgen05 + tensor memory).
+//
+// The operator is the first customized op of the prefill muGraph (pattern of the reference's
+// cpp_examples/multi_head_attn_prefill.cc:43-98): a block owns 128 query rows of one head and walks the
+// whole KV axis in for-loop tiles of 128:   S = Q K,  E = exp(S),  O' += E V,  R' += rowsum(E).
+// Both contractions are 128x128x128 and run as tcgen05.mma (cta_group::1, kind::f16, M = N = 128, K = 16
+// per instruction) with operands in 128-byte-swizzled shared memory and fp32 accumulators in tensor memory:
+//
+//   TMEM columns [0,128) and [128,256): S, double buffered;   [256,384): O', accumulated over all KV tiles.
+//
+// Warp roles (192 threads):
+//   warp 0, one lane   TMA producer: Q once, then K and V tiles into a two-stage ring.
+//   warp 1             allocates / frees tensor memory; one lane issues every MMA and commits to mbarriers.
+//                      Issue order  S(0), S(1), O(0), S(2), O(1), ...  so the tensor pipe computes S of the
+//                      next tile while the exp of the current one runs.
+//   warps 2-5          one thread per query row: tcgen05.ld its S row (32 columns at a time), exp, row sum,
+//                      bf16/fp16 pack, store into the swizzled E tile that feeds the second MMA; at the end
+//                      read O' and R' and store them.
+// The reference executes this graph on its mma.sync interpreter (src/kernel/cuda/customized_kernel.cu:39-305).
+//
+// Every wait on an mbarrier is bounded.  A role that gives up raises a block-wide flag, the other roles stop
+// at their next wait, the block frees its tensor memory, records the failure in the device status word and
+// returns.
+#include "common.cuh"
+#include <cuda.h>
+#include <mutex>
+
+namespace mgk {
+namespace tc {
+
+constexpr int kM = 128, kN = 128, kD = 128;         // query rows per block, KV positions per tile, head dim
+constexpr int kSubTile = 128 * 64 * 2;                // one [128 rows][64 cols] 16-bit box: 16 KB
+constexpr int kOperand = 2 * kSubTile;                // a 128 x 128 operand: two boxes
+constexpr int kStages = 2;
+constexpr int kWaitLimit = 2000000;
+constexpr uint32_t kTmemCols = 512;
+
+__device__ __forceinline__ uint32_t smem_u32(void const *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+               : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded wait that also gives up as soon as another role has raised the abort flag.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+  for (int i = 0; i < kWaitLimit; i++) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 1023) == 1023 && *abort_flag) return false;
+  }
+  *abort_flag = 1;
+  return false;
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, CUtensorMap const *map, uint32_t bar, int c0, int c1, int c2) {
+  asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+               ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major operand tile staged as [rows][64] boxes with the 128-byte
+// swizzle: 8-row groups are 1024 bytes apart (stride byte offset), version 1, layout type 2 (SWIZZLE_128B).
+// `byte_offset` selects the 16-element K step inside the 64-element swizzle span (32 bytes per step).
+__device__ __forceinline__ uint64_t smem_desc(uint32_t tile_addr, uint32_t byte_offset) {
+  uint64_t d = 0;
+  d |= (uint64_t)(((tile_addr + byte_offset) & 0x3FFFF) >> 4);   // start address, 16-byte units
+  d |= (uint64_t)1 << 16;                                         // leading byte offset (unused for K-major SW128)
+  d |= (uint64_t)(1024 >> 4) << 32;                               // stride byte offset
+  d |= (uint64_t)1 << 46;                                         // descriptor version
+  d |= (uint64_t)2 << 61;                                         // SWIZZLE_128B
+  return d;
+}
+// D[tmem] (+)= A[smem] * B[smem]^T, kind::f16, issued by one thread
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+               "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+               ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+               "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+               : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+                 "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+                 "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+                 "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+               : "r"(taddr) : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+template <bool BF16> __device__ __forceinline__ uint32_t pack2(float a, float b) {
+  if (BF16) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t *>(&h);
+  }
+  __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t *>(&h);
+}
+
+struct RowsParams {
+  void *o_acc;      // [heads][seq_q][128]
+  void *r_acc;      // [heads][seq_q][1]
+  int32_t *status;
+  int heads, seq_q, kv_len, forloop;
+};
+
+struct Barriers {
+  uint64_t q_full, kv_full[kStages], kv_empty[kStages], s_full[2], s_empty[2], e_full, e_empty, o_full;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+template <bool BF16>
+__global__ void __launch_bounds__(192)
+attn_rows_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
+                    const __grid_constant__ CUtensorMap v_map, const __grid_constant__ RowsParams p) {
+  extern __shared__ unsigned char smem_dyn[];
+  unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
+  // [Q 32 KB][stage0: K 32 KB, V 32 KB][stage1: ...][E 32 KB][barriers]
+  uint32_t const q_tile = smem_u32(smem);
+  uint32_t const ring = q_tile + kOperand;
+  uint32_t const e_tile = ring + kStages * 2 * kOperand;
+  Barriers *bar = reinterpret_cast<Barriers *>(smem + kOperand + kStages * 2 * kOperand + kOperand);
+  volatile int *abort_flag = &bar->abort_flag;
+
+  int const tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  int const qtiles = p.seq_q / kM;
+  int const head = blockIdx.x / qtiles, q0 = (blockIdx.x % qtiles) * kM;
+
+  if (tid == 0) {
+    bar->abort_flag = 0;
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&q_map) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&k_map) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&v_map) : "memory");
+    mbar_init(smem_u32(&bar->q_full), 1);
+    for (int s = 0; s < kStages; s++) {
+      mbar_init(smem_u32(&bar->kv_full[s]), 1);
+      mbar_init(smem_u32(&bar->kv_empty[s]), 1);
+    }
+    for (int b = 0; b < 2; b++) {
+      mbar_init(smem_u32(&bar->s_full[b]), 1);
+      mbar_init(smem_u32(&bar->s_empty[b]), 128);
+    }
+    mbar_init(smem_u32(&bar->e_full), 128);
+    mbar_init(smem_u32(&bar->e_empty), 1);
+    mbar_init(smem_u32(&bar->o_full), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) { // tensor memory: 512 columns (S x2, O'), allocated and later freed by this warp
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bar->tmem_base)), "r"(kTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  uint32_t const tmem = bar->tmem_base;
+  uint32_t const tmem_s[2] = {tmem, tmem + 128}, tmem_o = tmem + 256;
+  int const F = p.forloop;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      mbar_expect_tx(smem_u32(&bar->q_full), kOperand);
+      tma_load_3d(q_tile, &q_map, smem_u32(&bar->q_full), 0, q0, head);
+      tma_load_3d(q_tile + kSubTile, &q_map, smem_u32(&bar->q_full), 64, q0, head);
+      for (int j = 0; j < F; j++) {
+        int s = j % kStages;
+        if (j >= kStages && !mbar_wait(smem_u32(&bar->kv_empty[s]), (uint32_t)(((j / kStages) - 1) & 1), abort_flag)) break;
+        uint32_t full = smem_u32(&bar->kv_full[s]);
+        uint32_t kdst = ring + (uint32_t)(s * 2 * kOperand), vdst = kdst + kOperand;
+        int kv0 = j * kN;
+        mbar_expect_tx(full, 2 * kOperand);
+        // K memory [heads][kv][d]: rows = KV positions, two boxes over d
+        tma_load_3d(kdst, &k_map, full, 0, kv0, head);
+        tma_load_3d(kdst + kSubTile, &k_map, full, 64, kv0, head);
+        // V memory [heads][d][kv]: rows = d, two boxes over this tile's KV positions
+        tma_load_3d(vdst, &v_map, full, kv0, 0, head);
+        tma_load_3d(vdst + kSubTile, &v_map, full, kv0 + 64, 0, head);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      // instruction descriptor: fp32 accumulate, A/B format (0 = fp16, 1 = bf16), both K-major, N = 128, M = 128
+      uint32_t const fmt = BF16 ? 1u : 0u;
+      uint32_t const idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(kN >> 3) << 17) | ((uint32_t)(kM >> 4) << 24);
+      bool ok = mbar_wait(smem_u32(&bar->q_full), 0, abort_flag);
+      for (int j = 0; j <= F && ok; j++) {
+        if (j < F) { // S(j) = Q K_j^T into S buffer j % 2
+          int s = j % kStages, b = j & 1;
+          ok = mbar_wait(smem_u32(&bar->kv_full[s]), (uint32_t)((j / kStages) & 1), abort_flag);
+          if (ok && j >= 2) ok = mbar_wait(smem_u32(&bar->s_empty[b]), (uint32_t)(((j >> 1) - 1) & 1), abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+          uint32_t ktile = ring + (uint32_t)(s * 2 * kOperand);
+#pragma unroll
+          for (int ks = 0; ks < kD / 16; ks++) {
+            uint32_t off = (uint32_t)((ks >> 2) * kSubTile + (ks & 3) * 32);
+            umma_f16(tmem_s[b], smem_desc(q_tile, off), smem_desc(ktile, off), idesc, ks > 0);
+          }
+          umma_commit(smem_u32(&bar->s_full[b]));
+        }
+        if (j >= 1) { // O' += E_{j-1} V_{j-1}
+          int t = j - 1, s = t % kStages;
+          ok = mbar_wait(smem_u32(&bar->e_full), (uint32_t)(t & 1), abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+          uint32_t vtile = ring + (uint32_t)(s * 2 * kOperand) + kOperand;
+#pragma unroll
+          for (int ks = 0; ks < kN / 16; ks++) {
+            uint32_t off = (uint32_t)((ks >> 2) * kSubTile + (ks & 3) * 32);
+            umma_f16(tmem_o, smem_desc(e_tile, off), smem_desc(vtile, off), idesc, (t > 0 || ks > 0) ? 1u : 0u);
+          }
+          umma_commit(smem_u32(&bar->e_empty));      // E may be overwritten
+          umma_commit(smem_u32(&bar->kv_empty[s]));  // K_t and V_t have been consumed
+          if (t == F - 1) umma_commit(smem_u32(&bar->o_full));
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ exp / row sums / epilogue: one thread per query row
+    int const quarter = warp & 3;                 // tensor-memory lanes this warp may touch: 32 * (warp % 4)
+    int const row = quarter * 32 + lane;
+    uint32_t const lane_base = (uint32_t)(quarter * 32) << 16;
+    float rsum = 0.f;
+    bool ok = true;
+    for (int j = 0; j < F && ok; j++) {
+      int b = j & 1;
+      ok = mbar_wait(smem_u32(&bar->s_full[b]), (uint32_t)((j >> 1) & 1), abort_flag);
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t packed[4][16]; // the row's 128 values as 16-bit pairs
+#pragma unroll
+      for (int c = 0; c < 4; c++) {
+        uint32_t v[32];
+        tmem_ld32(tmem_s[b] + lane_base + (uint32_t)(c * 32), v);
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float e0 = __expf(__uint_as_float(v[i])), e1 = __expf(__uint_as_float(v[i + 1]));
+          rsum += e0 + e1;
+          packed[c][i >> 1] = pack2<BF16>(e0, e1);
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(smem_u32(&bar->s_empty[b])); // this S buffer may be overwritten by S(j+2)
+      if (j >= 1) ok = mbar_wait(smem_u32(&bar->e_empty), (uint32_t)((j - 1) & 1), abort_flag);
+      if (!ok) break;
+      // E tile, K-major with the 128-byte swizzle: 16-byte chunk q of row r sits at chunk q ^ (r % 8)
+#pragma unroll
+      for (int c = 0; c < 4; c++)
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+          int chunk = (c & 1) * 4 + q; // chunk inside the 64-column box; box = c / 2
+          uint32_t addr = e_tile + (uint32_t)((c >> 1) * kSubTile + row * 128 + ((chunk ^ (row & 7)) << 4));
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(packed[c][4 * q]), "r"(packed[c][4 * q + 1]),
+                       "r"(packed[c][4 * q + 2]), "r"(packed[c][4 * q + 3]) : "memory");
+        }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); // make the stores visible to the tensor core's reads
+      mbar_arrive(smem_u32(&bar->e_full));
+    }
+    if (ok) ok = mbar_wait(smem_u32(&bar->o_full), 0, abort_flag);
+    if (ok) {
+      tc_fence_after();
+      uint16_t *o_row = static_cast<uint16_t *>(p.o_acc) + ((size_t)head * p.seq_q + q0 + row) * kD;
+#pragma unroll
+      for (int c = 0; c < 4; c++) {
+        uint32_t v[32];
+        tmem_ld32(tmem_o + lane_base + (uint32_t)(c * 32), v);
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+          uint4 out;
+          out.x = pack2<BF16>(__uint_as_float(v[8 * q]), __uint_as_float(v[8 * q + 1]));
+          out.y = pack2<BF16>(__uint_as_float(v[8 * q + 2]), __uint_as_float(v[8 * q + 3]));
+          out.z = pack2<BF16>(__uint_as_float(v[8 * q + 4]), __uint_as_float(v[8 * q + 5]));
+          out.w = pack2<BF16>(__uint_as_float(v[8 * q + 6]), __uint_as_float(v[8 * q + 7]));
+          *reinterpret_cast<uint4 *>(o_row + c * 32 + q * 8) = out;
+        }
+      }
+      uint32_t r2 = pack2<BF16>(rsum, 0.f);
+      static_cast<uint16_t *>(p.r_acc)[(size_t)head * p.seq_q + q0 + row] = (uint16_t)(r2 & 0xFFFF);
+    }
+  }
+
+  // ---- teardown: every role arrives here, failed or not --------------------------------------------------
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag && warp == 0 && lane == 0) {
+    // copies this block issued may still be in flight: give them a bounded time to land before the block exits
+    for (int s = 0; s < kStages; s++)
+      for (int i = 0; i < 20000 && !mbar_try_wait(smem_u32(&bar->kv_full[s]), 0) && !mbar_try_wait(smem_u32(&bar->kv_full[s]), 1); i++) {
+      }
+    atomicExch(p.status, 2);
+  }
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+  }
+}
+
+using EncodeFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, cuuint64_t const *,
+                              cuuint64_t const *, cuuint32_t const *, cuuint32_t const *, CUtensorMapInterleave,
+                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeFn encode_fn() {
+  static EncodeFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void *sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeFn>(sym);
+  });
+  return fn;
+}
+// [batch][rows][cols] 16-bit array, box [1][128][64], 128-byte swizzle
+static bool make_map(CUtensorMap *map, void const *base, uint64_t batch, uint64_t rows, uint64_t cols) {
+  EncodeFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[3] = {cols, rows, batch};
+  cuuint64_t strides[2] = {cols * 2, rows * cols * 2};
+  cuuint32_t box[3] = {64, 128, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, const_cast<void *>(base), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+static bool rows_supported(mgd_attn_rows const *p) {
+  if (!p || p->heads <= 0 || p->forloop_range <= 0) return false;
+  if (p->d != kD || p->tile_m != kM || p->tile_kv != kN) return false;
+  if (p->seq_q % kM != 0 || p->kv_len != p->forloop_range * kN) return false;
+  if (p->data_type != MG_DT_FLOAT16 && p->data_type != MG_DT_BFLOAT16) return false;
+  // both B operands must have the contraction index contiguous: K as [kv][d], V as [d][kv]
+  return p->k_layout == MG_DMEM_COLUMN_MAJOR && p->v_layout == MG_DMEM_COLUMN_MAJOR;
+}
+} // namespace tc
+} // namespace mgk
+
+using namespace mgk;
+
+extern "C" {
+
+int mgd_attn_rows_supported(const mgd_attn_rows *p) { return tc::rows_supported(p) && tc::encode_fn() != nullptr ? 1 : 0; }
+
+int mgd_launch_attn_rows_float(const mgd_attn_rows *p, const void *q, const void *k, const void *v, void *o_acc,
+                               void *r_acc, void *stream) {
+  if (!q || !k || !v || !o_acc || !r_acc) return set_error(MG_ERR_INVALID_ARGUMENT, "dense attention: null tensor");
+  if (!tc::rows_supported(p)) return set_error(MG_ERR_UNSUPPORTED, "dense attention: shape or layout not supported");
+  CUtensorMap qm, km, vm;
+  bool ok = tc::make_map(&qm, q, p->heads, p->seq_q, tc::kD) && tc::make_map(&km, k, p->heads, p->kv_len, tc::kD) &&
+            tc::make_map(&vm, v, p->heads, tc::kD, p->kv_len);
+  if (!ok) return set_error(MG_ERR_CUDA, "dense attention: cuTensorMapEncodeTiled failed");
+  tc::RowsParams a;
+  a.o_acc = o_acc; a.r_acc = r_acc;
+  a.status = device_error_word();
+  if (!a.status) return set_error(MG_ERR_CUDA, "cannot allocate the device status word");
+  a.heads = p->heads; a.seq_q = p->seq_q; a.kv_len = p->kv_len; a.forloop = p->forloop_range;
+  size_t smem = 1024 + tc::kOperand * (2 + 2 * tc::kStages) + sizeof(tc::Barriers) + 64;
+  unsigned blocks = (unsigned)(p->heads * (p->seq_q / tc::kM));
+  static bool configured[2] = {false, false};
+  bool bf16 = p->data_type == MG_DT_BFLOAT16;
+  if (!configured[bf16]) {
+    cudaError_t e = bf16 ? cudaFuncSetAttribute(tc::attn_rows_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+                         : cudaFuncSetAttribute(tc::attn_rows_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return check_launch("cudaFuncSetAttribute(attn_rows_tc_kernel)");
+    configured[bf16] = true;
+  }
+  if (bf16) tc::attn_rows_tc_kernel<true><<<blocks, 192, smem, (cudaStream_t)stream>>>(qm, km, vm, a);
+  else tc::attn_rows_tc_kernel<false><<<blocks, 192, smem, (cudaStream_t)stream>>>(qm, km, vm, a);
+  return check_launch("attn_rows_tc_kernel");
+}
+}

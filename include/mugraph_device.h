@@ -122,6 +122,20 @@ int mgd_launch_attn_split_float(const mgd_attn_split *p, const void *q, const vo
 int mgd_launch_attn_split_fingerprint(const mgd_attn_split *p, const uint16_t *q, const uint16_t *k,
                                       const uint16_t *v, uint16_t *o_part, uint16_t *r_part, void *stream);
 
+/* ---- dense attention over query-row tiles, the pattern of cpp_examples/multi_head_attn_prefill.cc:43-98 ---
+ * A block owns tile_m query rows of one head and walks the KV axis in for-loop tiles of tile_kv:
+ * S = Q K, E = exp(S), O' += E V, R' += rowsum(E).  Q[heads, seq_q, d], K[heads, d, kv_len], V[heads, kv_len, d];
+ * outputs O_acc[heads, seq_q, d] (not normalised) and R[heads, seq_q, 1].  Runs on tcgen05 tensor cores with
+ * accumulators in tensor memory; float mode only (fingerprints of such graphs use the interpreter). */
+typedef struct mgd_attn_rows {
+  int32_t heads, seq_q, d, kv_len;
+  int32_t tile_m, tile_kv, forloop_range;
+  int32_t k_layout, v_layout, data_type;
+} mgd_attn_rows;
+int mgd_attn_rows_supported(const mgd_attn_rows *p);
+int mgd_launch_attn_rows_float(const mgd_attn_rows *p, const void *q, const void *k, const void *v, void *o_acc,
+                               void *r_acc, void *stream);
+
 /* Allocation-free variant of the fused decode launch (split-KV partials + cross-split merge in one kernel).
  * It has no counterpart in the reference.
  *

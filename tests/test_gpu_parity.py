@@ -256,6 +256,58 @@ def test_float_baseline_c2_full_size(rt):
         assert 0 < ms < 1000
 
 
+def build_prefill(g, H, SQ, D, L, dtype, kl=mg.DmemColumnMajor, vl=mg.DmemColumnMajor):
+    Q = g.new_input((H, SQ, D), dtype)
+    K = g.new_input((H, D, L), dtype, kl)
+    V = g.new_input((H, L, D), dtype, vl)
+    p1, p2 = mg.attention_prefill_plans(H, SQ, D, L)
+    acc = g.customized([Q, K, V], p1)
+    out = g.customized(acc, p2)
+    return (Q, K, V), acc, out, (p1, p2)
+
+
+@pytest.mark.parametrize("dtype", [mg.bfloat16, mg.float16], ids=["bf16", "fp16"])
+@pytest.mark.parametrize("shape", [(2, 256, 512), (1, 128, 128), (3, 384, 1024)])
+def test_float_prefill_tensor_core_kernel(runtime, shape, dtype):
+    """Dense attention on tcgen05 / tensor memory (128 x 128 tiles) against the fp32 evaluation."""
+    H, SQ, L = shape
+    D = 128
+    runtime.set_max_smem(BIG)
+    runtime.set_specialisation(2)
+    rng = np.random.default_rng(H * 7 + SQ + L)
+    with mg.PyGraph(runtime) as g:
+        ins, acc, out, plans = build_prefill(g, H, SQ, D, L, dtype)
+        assert g.customized_info(3)["kernel_float"] == mg.KERNEL_ATTN_ROWS
+        (q, k, v), mem = float_inputs(rng, H, SQ, D, L, mg.DmemColumnMajor, mg.DmemColumnMajor, dtype)
+        for t, a in zip(ins, mem):
+            t.upload_data(to_bits(a, dtype))
+        g.run()
+        og1 = mo.build_customized([spec_of(t) for t in ins], to_oracle_plan(plans[0]), max_smem=BIG)
+        ref1 = mo.run_float(og1, mem)
+        assert_close(from_bits(acc[0].download_data(), dtype).reshape(acc[0].shape), ref1[0], dtype, "O_acc")
+        assert_close(from_bits(acc[1].download_data(), dtype).reshape(acc[1].shape), ref1[1], dtype, "R")
+        final = from_bits(out[0].download_data(), dtype).reshape(out[0].shape)
+        assert_close(final, mo.attention_fp32(q, k, v), dtype, "O vs un-fused fp32 attention")
+        # run again: tensor memory and barriers are set up afresh by every launch
+        g.run()
+        again = from_bits(out[0].download_data(), dtype).reshape(out[0].shape)
+        assert np.array_equal(final, again)
+
+
+def test_prefill_fingerprint_uses_interpreter(runtime):
+    """The same dense graph in fingerprint mode (128 x 128 x 128 mod-PQ contractions) stays bit-exact."""
+    H, SQ, D, L = 1, 128, 128, 256
+    runtime.set_max_smem(BIG)
+    rng = np.random.default_rng(12)
+    with mg.PyGraph(runtime) as g:
+        ins, acc, out, plans = build_prefill(g, H, SQ, D, L, mg.bfloat16)
+        x = [rng.integers(0, mo.FP_PQ, size=t.shape).astype(np.uint16) for t in ins]
+        for t, a in zip(ins, x):
+            t.upload_fingerprint(a)
+        g.fingerprint()
+        assert np.array_equal(out[0].download_fingerprint(), mo.unfused_attention_fp(*x))
+
+
 def test_float_other_graph_generic(rt):
     """Matmul chain in float mode through the generic interpreter."""
     rng = np.random.default_rng(9)
