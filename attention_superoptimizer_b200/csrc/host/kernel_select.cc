@@ -112,6 +112,29 @@ bool match_attn_rows(mgd_program const &p, mgd_attn_rows *out) {
   return true;
 }
 
+bool match_div_rows(mgd_program const &p, int *heads, int *rows, int *d) {
+  if (p.num_ops != 4 || p.num_inputs != 2 || p.num_outputs != 1 || p.grid[2] != 1 || p.forloop_range != 1) return false;
+  mgd_op const *o = p.ops;
+  if (!is_input(o[0]) || !is_input(o[1]) || o[2].type != MG_TB_DIV_OP || !is_output(o[3])) return false;
+  int m = o[0].a[14], dd = o[0].a[15], gy = p.grid[1];
+  if (o[1].a[14] != m || o[1].a[15] != 1) return false;
+  for (int i = 0; i < 2; i++) {
+    mgd_op const &in = o[i];
+    if (in.a[8] != in.a[12] * in.a[13] || in.a[9] || in.a[10] || in.a[11]) return false;
+    if (in.a[1] != m || in.a[0] || in.a[2] || in.a[3] || in.a[4] || in.a[5] || in.a[6] || in.a[7]) return false;
+    if (in.a[12] != m * gy) return false;
+  }
+  if (o[0].a[13] != dd || o[1].a[13] != 1) return false;
+  if (o[2].a[6] != o[0].a[17] || o[2].a[7] != o[1].a[17]) return false;
+  if (o[2].a[0] != 1 || o[2].a[1] != m || o[2].a[2] != dd || o[2].a[3] != 1 || o[2].a[4] != m || o[2].a[5] != 1) return false;
+  mgd_op const &so = o[3];
+  if (so.a[13] != o[2].a[8] || so.a[11] != m || so.a[12] != dd || so.a[9] != m * gy || so.a[10] != dd || so.a[1] != m ||
+      so.a[6] != m * gy * dd || so.a[0] || so.a[2] || so.a[3] || so.a[4] || so.a[5] || so.a[7] || so.a[8])
+    return false;
+  *heads = p.grid[0]; *rows = m * gy; *d = dd;
+  return true;
+}
+
 bool match_attn_merge(mgd_program const &p, mgd_attn_merge *out) {
   // ops: in O_part, in R_part, reduction_to_dimx(O_part), reduction(R_part), div, out
   if (p.num_ops != 6 || p.num_inputs != 2 || p.num_outputs != 1) return false;

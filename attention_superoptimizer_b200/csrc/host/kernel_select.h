@@ -16,4 +16,6 @@ bool match_attn_split(mgd_program const &p, int leading_dims_of_inputs, mgd_attn
 bool match_attn_merge(mgd_program const &p, mgd_attn_merge *out);
 // Recognise the dense (prefill) form: pattern of cpp_examples/multi_head_attn_prefill.cc:43-98.
 bool match_attn_rows(mgd_program const &p, mgd_attn_rows *out);
+// Recognise O = A / R with A[heads, rows, d], R[heads, rows, 1] tiled like match_attn_rows' outputs (same example, :88-98).
+bool match_div_rows(mgd_program const &p, int *heads, int *rows, int *d);
 } // namespace mg

@@ -788,12 +788,21 @@ int KNCustomizedOp::launch_split(bool fp, int num_sets, void const *const *in, l
 }
 
 bool KNCustomizedOp::can_fuse_with(KNOperator *next, bool fp) {
-  if (DeviceMemoryManager::get_instance()->specialise < 2 || !tickets_ || !next) return false;
+  if (DeviceMemoryManager::get_instance()->specialise < 2 || !next) return false;
   if (next->op_type != KN_CUSTOMIZED_OP || !ensure_lowered()) return false;
   auto *m = static_cast<KNCustomizedOp *>(next);
   if (!m->ensure_lowered()) return false;
-  if ((fp ? kernel_fp_ : kernel_float_) != mg::KERNEL_ATTN_SPLIT) return false;
-  if ((fp ? m->kernel_fp_ : m->kernel_float_) != mg::KERNEL_ATTN_MERGE) return false;
+  int mine = fp ? kernel_fp_ : kernel_float_;
+  if (mine == mg::KERNEL_ATTN_ROWS) {
+    // dense attention followed by the division of its two outputs
+    int h, r, d;
+    mgd_attn_rows rp;
+    if (fp || !mg::match_div_rows(m->program_, &h, &r, &d) || !mg::match_attn_rows(program_, &rp)) return false;
+    if (h != rp.heads || r != rp.seq_q || d != rp.d) return false;
+  } else {
+    if (mine != mg::KERNEL_ATTN_SPLIT || !tickets_) return false;
+    if ((fp ? m->kernel_fp_ : m->kernel_float_) != mg::KERNEL_ATTN_MERGE) return false;
+  }
   if (m->input_tensors.size() != 2 || output_tensors.size() != 2) return false;
   for (int i = 0; i < 2; i++) {
     DTensor const &a = output_tensors[i], &b = m->input_tensors[i];
@@ -804,6 +813,15 @@ bool KNCustomizedOp::can_fuse_with(KNOperator *next, bool fp) {
 
 int KNCustomizedOp::launch_fused(KNCustomizedOp *merge, bool fp, void *stream) {
   if (int dry_st = refuse_if_dry()) return dry_st;
+  if (!fp && kernel_float_ == mg::KERNEL_ATTN_ROWS) {
+    mgd_attn_rows rp;
+    mg::match_attn_rows(program_, &rp);
+    rp.data_type = (int)input_tensors[0].data_type;
+    record_outputs(stream, {});
+    return finish(mgd_launch_attn_rows_float_ex(&rp, input_tensors[0].data_ptr, input_tensors[1].data_ptr,
+                                                input_tensors[2].data_ptr, output_tensors[0].data_ptr,
+                                                output_tensors[1].data_ptr, merge->output_tensors[0].data_ptr, stream));
+  }
   void const *in[3];
   void *out[2];
   long long zs[3] = {0, 0, 0};

@@ -4,34 +4,54 @@
 // cpp_examples/multi_head_attn_prefill.cc:43-98): a block owns 128 query rows of one head and walks the
 // whole KV axis in for-loop tiles of 128:   S = Q K,  E = exp(S),  O' += E V,  R' += rowsum(E).
 // Both contractions are 128x128x128 and run as tcgen05.mma (cta_group::1, kind::f16, M = N = 128, K = 16
-// per instruction) with operands in 128-byte-swizzled shared memory and fp32 accumulators in tensor memory:
+// per instruction).  The A operand of both comes from tensor memory - Q is parked there once, E is handed
+// over by the exp warps in place of the S values they consumed - so each MMA reads only its 4 KB B slice (a K
+// or V tile in 128-byte-swizzled shared memory): with A in shared memory too, a 128 x 128 x 16 MMA needs
+// 128 B/clk of shared-memory bandwidth, all an SM has, and the tensor pipe starves.  Accumulators are fp32:
 //
-//   TMEM columns [0,128) and [128,256): S, double buffered;   [256,384): O', accumulated over all KV tiles.
+//   TMEM columns [0,64): Q as packed 16-bit pairs      [64,192), [192,320): S, double buffered
+//                [320,448): O', accumulated over all KV tiles
+//   E of a tile overwrites its own S buffer: the thread that read S columns [64h, 64h+64) of a row writes the
+//   32 packed columns of E to [64h, 64h+32).  MMAs issued by one thread execute in order, so the S of tile j+2
+//   cannot overwrite the buffer before the second MMA of tile j has read E from it; no extra barrier is needed.
 //
-// Warp roles (192 threads):
-//   warp 0, one lane   TMA producer: Q once, then K and V tiles into a two-stage ring.
+// Warp roles (320 threads):
+//   warp 0, one lane   TMA producer: K and V tiles into a three-stage ring.
 //   warp 1             allocates / frees tensor memory; one lane issues every MMA and commits to mbarriers.
 //                      Issue order  S(0), S(1), O(0), S(2), O(1), ...  so the tensor pipe computes S of the
 //                      next tile while the exp of the current one runs.
-//   warps 2-5          one thread per query row: tcgen05.ld its S row (32 columns at a time), exp, row sum,
-//                      bf16/fp16 pack, store into the swizzled E tile that feeds the second MMA; at the end
-//                      read O' and R' and store them.
+//   warps 2-9          two warpgroups, each thread owns one query row and one 64-column half of the tile; first
+//                      it copies its half of the Q row from global memory into tensor memory, then per tile:
+//                      tcgen05.ld its S half-row (32 columns at a time), exp, row sum, bf16/fp16 pack, tcgen05.st
+//                      the packed E half-row back to tensor memory; at the end read O' and R' and store them
+//                      (and, when the division operator is fused in, O = O' / R').  Two warps per scheduler
+//                      hide each other's MUFU and tensor-memory latency.
 // The reference executes this graph on its mma.sync interpreter (src/kernel/cuda/customized_kernel.cu:39-305).
 //
 // Every wait on an mbarrier is bounded.  A role that gives up raises a block-wide flag, the other roles stop
 // at their next wait, the block frees its tensor memory, records the failure in the device status word and
 // returns.
 #include "common.cuh"
+#include <cstdio>
 #include <cuda.h>
 #include <mutex>
 
 namespace mgk {
 namespace tc {
 
+// Optional phase timing of block 0 (compile with -DMG_ROWS_TIMING; prints cycle totals from the device).
+#ifdef MG_ROWS_TIMING
+#define TICK(var) long long var = clock64()
+#define TOCK(acc, var) acc += clock64() - var
+#else
+#define TICK(var)
+#define TOCK(acc, var)
+#endif
+
 constexpr int kM = 128, kN = 128, kD = 128;         // query rows per block, KV positions per tile, head dim
 constexpr int kSubTile = 128 * 64 * 2;                // one [128 rows][64 cols] 16-bit box: 16 KB
 constexpr int kOperand = 2 * kSubTile;                // a 128 x 128 operand: two boxes
-constexpr int kStages = 2;
+constexpr int kStages = 3;
 constexpr int kWaitLimit = 2000000;
 constexpr uint32_t kTmemCols = 512;
 
@@ -83,6 +103,22 @@ __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint6
                "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
                ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
+// same with the A operand read from tensor memory (16-bit values packed two per column)
+__device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+               "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+               ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, uint32_t const (&v)[32]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+               "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+               ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+                 "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]),
+                 "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]),
+                 "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+               : "memory");
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
@@ -109,29 +145,30 @@ template <bool BF16> __device__ __forceinline__ uint32_t pack2(float a, float b)
 }
 
 struct RowsParams {
+  void const *q;    // [heads][seq_q][128]
   void *o_acc;      // [heads][seq_q][128]
   void *r_acc;      // [heads][seq_q][1]
+  void *o_div;      // optional [heads][seq_q][128]: O' / R' (the division operator that follows, fused)
   int32_t *status;
   int heads, seq_q, kv_len, forloop;
 };
 
 struct Barriers {
-  uint64_t q_full, kv_full[kStages], kv_empty[kStages], s_full[2], s_empty[2], e_full, e_empty, o_full;
+  uint64_t q_ready, kv_full[kStages], kv_empty[kStages], s_full[2], e_full[2], o_full;
   uint32_t tmem_base;
   int abort_flag;
+  float row_sums[2][kM]; // per column half
 };
 
 template <bool BF16>
-__global__ void __launch_bounds__(192)
-attn_rows_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
-                    const __grid_constant__ CUtensorMap v_map, const __grid_constant__ RowsParams p) {
+__global__ void __launch_bounds__(320)
+attn_rows_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
+                    const __grid_constant__ RowsParams p) {
   extern __shared__ unsigned char smem_dyn[];
   unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
-  // [Q 32 KB][stage0: K 32 KB, V 32 KB][stage1: ...][E 32 KB][barriers]
-  uint32_t const q_tile = smem_u32(smem);
-  uint32_t const ring = q_tile + kOperand;
-  uint32_t const e_tile = ring + kStages * 2 * kOperand;
-  Barriers *bar = reinterpret_cast<Barriers *>(smem + kOperand + kStages * 2 * kOperand + kOperand);
+  // [stage0: K 32 KB, V 32 KB][stage1][stage2][barriers]
+  uint32_t const ring = smem_u32(smem);
+  Barriers *bar = reinterpret_cast<Barriers *>(smem + kStages * 2 * kOperand);
   volatile int *abort_flag = &bar->abort_flag;
 
   int const tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -140,20 +177,17 @@ attn_rows_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
 
   if (tid == 0) {
     bar->abort_flag = 0;
-    asm volatile("prefetch.tensormap [%0];" ::"l"(&q_map) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&k_map) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&v_map) : "memory");
-    mbar_init(smem_u32(&bar->q_full), 1);
+    mbar_init(smem_u32(&bar->q_ready), 256);
     for (int s = 0; s < kStages; s++) {
       mbar_init(smem_u32(&bar->kv_full[s]), 1);
       mbar_init(smem_u32(&bar->kv_empty[s]), 1);
     }
     for (int b = 0; b < 2; b++) {
       mbar_init(smem_u32(&bar->s_full[b]), 1);
-      mbar_init(smem_u32(&bar->s_empty[b]), 128);
+      mbar_init(smem_u32(&bar->e_full[b]), 256);
     }
-    mbar_init(smem_u32(&bar->e_full), 128);
-    mbar_init(smem_u32(&bar->e_empty), 1);
     mbar_init(smem_u32(&bar->o_full), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -166,15 +200,12 @@ attn_rows_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
   __syncthreads();
   tc_fence_after();
   uint32_t const tmem = bar->tmem_base;
-  uint32_t const tmem_s[2] = {tmem, tmem + 128}, tmem_o = tmem + 256;
+  uint32_t const tmem_q = tmem, tmem_s[2] = {tmem + 64, tmem + 192}, tmem_o = tmem + 320;
   int const F = p.forloop;
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      mbar_expect_tx(smem_u32(&bar->q_full), kOperand);
-      tma_load_3d(q_tile, &q_map, smem_u32(&bar->q_full), 0, q0, head);
-      tma_load_3d(q_tile + kSubTile, &q_map, smem_u32(&bar->q_full), 64, q0, head);
       for (int j = 0; j < F; j++) {
         int s = j % kStages;
         if (j >= kStages && !mbar_wait(smem_u32(&bar->kv_empty[s]), (uint32_t)(((j / kStages) - 1) & 1), abort_flag)) break;
@@ -196,56 +227,87 @@ attn_rows_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
       // instruction descriptor: fp32 accumulate, A/B format (0 = fp16, 1 = bf16), both K-major, N = 128, M = 128
       uint32_t const fmt = BF16 ? 1u : 0u;
       uint32_t const idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(kN >> 3) << 17) | ((uint32_t)(kM >> 4) << 24);
-      bool ok = mbar_wait(smem_u32(&bar->q_full), 0, abort_flag);
+      bool ok = mbar_wait(smem_u32(&bar->q_ready), 0, abort_flag);
+#ifdef MG_ROWS_TIMING
+      long long w_kv = 0, w_ef = 0, t_all = clock64();
+#endif
       for (int j = 0; j <= F && ok; j++) {
         if (j < F) { // S(j) = Q K_j^T into S buffer j % 2
           int s = j % kStages, b = j & 1;
+          TICK(a0);
           ok = mbar_wait(smem_u32(&bar->kv_full[s]), (uint32_t)((j / kStages) & 1), abort_flag);
-          if (ok && j >= 2) ok = mbar_wait(smem_u32(&bar->s_empty[b]), (uint32_t)(((j >> 1) - 1) & 1), abort_flag);
+          TOCK(w_kv, a0);
           if (!ok) break;
           tc_fence_after();
           uint32_t ktile = ring + (uint32_t)(s * 2 * kOperand);
 #pragma unroll
-          for (int ks = 0; ks < kD / 16; ks++) {
+          for (int ks = 0; ks < kD / 16; ks++) { // A = Q from tensor memory: 16 values = 8 packed columns per step
             uint32_t off = (uint32_t)((ks >> 2) * kSubTile + (ks & 3) * 32);
-            umma_f16(tmem_s[b], smem_desc(q_tile, off), smem_desc(ktile, off), idesc, ks > 0);
+            umma_f16_ts(tmem_s[b], tmem_q + (uint32_t)(ks * 8), smem_desc(ktile, off), idesc, ks > 0);
           }
           umma_commit(smem_u32(&bar->s_full[b]));
         }
         if (j >= 1) { // O' += E_{j-1} V_{j-1}
-          int t = j - 1, s = t % kStages;
-          ok = mbar_wait(smem_u32(&bar->e_full), (uint32_t)(t & 1), abort_flag);
+          int t = j - 1, s = t % kStages, eb = t & 1;
+          TICK(a2);
+          ok = mbar_wait(smem_u32(&bar->e_full[eb]), (uint32_t)((t >> 1) & 1), abort_flag);
+          TOCK(w_ef, a2);
           if (!ok) break;
           tc_fence_after();
           uint32_t vtile = ring + (uint32_t)(s * 2 * kOperand) + kOperand;
 #pragma unroll
-          for (int ks = 0; ks < kN / 16; ks++) {
+          for (int ks = 0; ks < kN / 16; ks++) { // A = E in the S buffer: half h at columns [64h, 64h+32), 8 per step
             uint32_t off = (uint32_t)((ks >> 2) * kSubTile + (ks & 3) * 32);
-            umma_f16(tmem_o, smem_desc(e_tile, off), smem_desc(vtile, off), idesc, (t > 0 || ks > 0) ? 1u : 0u);
+            uint32_t ecol = (uint32_t)((ks >> 2) * 64 + (ks & 3) * 8);
+            umma_f16_ts(tmem_o, tmem_s[eb] + ecol, smem_desc(vtile, off), idesc, (t > 0 || ks > 0) ? 1u : 0u);
           }
-          umma_commit(smem_u32(&bar->e_empty));      // E may be overwritten
           umma_commit(smem_u32(&bar->kv_empty[s]));  // K_t and V_t have been consumed
           if (t == F - 1) umma_commit(smem_u32(&bar->o_full));
         }
       }
+#ifdef MG_ROWS_TIMING
+      if (blockIdx.x == 0) printf("mma issuer: total %lld wait_kv %lld wait_e_full %lld (cycles, %d tiles)\n", clock64() - t_all, w_kv, w_ef, F);
+#endif
     }
   } else {
-    // ------------------------------------------------------------------ exp / row sums / epilogue: one thread per query row
+    // ------------------------------------------------------------------ exp / row sums / epilogue
+    // thread = (query row, 64-column half)
     int const quarter = warp & 3;                 // tensor-memory lanes this warp may touch: 32 * (warp % 4)
+    int const half = (warp - 2) >> 2;             // which 64 columns of a tile
     int const row = quarter * 32 + lane;
     uint32_t const lane_base = (uint32_t)(quarter * 32) << 16;
+    uint32_t const col_base = (uint32_t)(half * 64);
     float rsum = 0.f;
     bool ok = true;
+    { // park this thread's half of its Q row in tensor memory: 64 values = 32 packed columns
+      uint4 const *src = reinterpret_cast<uint4 const *>(static_cast<uint16_t const *>(p.q) +
+                                                         ((size_t)head * p.seq_q + q0 + row) * kD + col_base);
+      uint32_t qv[32];
+#pragma unroll
+      for (int i = 0; i < 8; i++) {
+        uint4 w = __ldg(src + i);
+        qv[4 * i] = w.x; qv[4 * i + 1] = w.y; qv[4 * i + 2] = w.z; qv[4 * i + 3] = w.w;
+      }
+      tmem_st32(tmem_q + lane_base + (uint32_t)(half * 32), qv);
+      tc_fence_before();
+      mbar_arrive(smem_u32(&bar->q_ready));
+    }
+#ifdef MG_ROWS_TIMING
+    long long w_sf = 0, c_exp = 0, c_st = 0, t_all = clock64();
+#endif
     for (int j = 0; j < F && ok; j++) {
       int b = j & 1;
+      TICK(b0);
       ok = mbar_wait(smem_u32(&bar->s_full[b]), (uint32_t)((j >> 1) & 1), abort_flag);
+      TOCK(w_sf, b0);
       if (!ok) break;
       tc_fence_after();
-      uint32_t packed[4][16]; // the row's 128 values as 16-bit pairs
+      TICK(b1);
+      uint32_t packed[2][16]; // this thread's 64 values as 16-bit pairs
 #pragma unroll
-      for (int c = 0; c < 4; c++) {
+      for (int c = 0; c < 2; c++) {
         uint32_t v[32];
-        tmem_ld32(tmem_s[b] + lane_base + (uint32_t)(c * 32), v);
+        tmem_ld32(tmem_s[b] + lane_base + col_base + (uint32_t)(c * 32), v);
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
           float e0 = __expf(__uint_as_float(v[i])), e1 = __expf(__uint_as_float(v[i + 1]));
@@ -253,31 +315,37 @@ attn_rows_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
           packed[c][i >> 1] = pack2<BF16>(e0, e1);
         }
       }
+      TOCK(c_exp, b1);
+      TICK(b3);
+      // E replaces the S values this thread has just consumed: 32 packed columns at the start of its own half
+      uint32_t flat[32];
+#pragma unroll
+      for (int i = 0; i < 32; i++) flat[i] = packed[i >> 4][i & 15];
+      tmem_st32(tmem_s[b] + lane_base + col_base, flat);
       tc_fence_before();
-      mbar_arrive(smem_u32(&bar->s_empty[b])); // this S buffer may be overwritten by S(j+2)
-      if (j >= 1) ok = mbar_wait(smem_u32(&bar->e_empty), (uint32_t)((j - 1) & 1), abort_flag);
-      if (!ok) break;
-      // E tile, K-major with the 128-byte swizzle: 16-byte chunk q of row r sits at chunk q ^ (r % 8)
-#pragma unroll
-      for (int c = 0; c < 4; c++)
-#pragma unroll
-        for (int q = 0; q < 4; q++) {
-          int chunk = (c & 1) * 4 + q; // chunk inside the 64-column box; box = c / 2
-          uint32_t addr = e_tile + (uint32_t)((c >> 1) * kSubTile + row * 128 + ((chunk ^ (row & 7)) << 4));
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(packed[c][4 * q]), "r"(packed[c][4 * q + 1]),
-                       "r"(packed[c][4 * q + 2]), "r"(packed[c][4 * q + 3]) : "memory");
-        }
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); // make the stores visible to the tensor core's reads
-      mbar_arrive(smem_u32(&bar->e_full));
+      mbar_arrive(smem_u32(&bar->e_full[b]));
+      TOCK(c_st, b3);
     }
+#ifdef MG_ROWS_TIMING
+    if (blockIdx.x == 0 && lane == 0 && (warp == 2 || warp == 6))
+      printf("exp warp %d: total %lld wait_s_full %lld ld+exp %lld st %lld\n", warp, clock64() - t_all, w_sf, c_exp, c_st);
+#endif
+    // the two halves of a row add up their sums (named barrier over the 256 threads of these warps; reached
+    // by all of them whether or not a wait gave up)
+    bar->row_sums[half][row] = rsum;
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    float const total = bar->row_sums[0][row] + bar->row_sums[1][row];
     if (ok) ok = mbar_wait(smem_u32(&bar->o_full), 0, abort_flag);
     if (ok) {
       tc_fence_after();
-      uint16_t *o_row = static_cast<uint16_t *>(p.o_acc) + ((size_t)head * p.seq_q + q0 + row) * kD;
+      size_t const row_off = ((size_t)head * p.seq_q + q0 + row) * kD + col_base;
+      uint16_t *o_row = static_cast<uint16_t *>(p.o_acc) + row_off;
+      uint16_t *d_row = p.o_div ? static_cast<uint16_t *>(p.o_div) + row_off : nullptr;
+      float const inv = 1.0f / total;
 #pragma unroll
-      for (int c = 0; c < 4; c++) {
+      for (int c = 0; c < 2; c++) {
         uint32_t v[32];
-        tmem_ld32(tmem_o + lane_base + (uint32_t)(c * 32), v);
+        tmem_ld32(tmem_o + lane_base + col_base + (uint32_t)(c * 32), v);
 #pragma unroll
         for (int q = 0; q < 4; q++) {
           uint4 out;
@@ -286,10 +354,19 @@ attn_rows_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
           out.z = pack2<BF16>(__uint_as_float(v[8 * q + 4]), __uint_as_float(v[8 * q + 5]));
           out.w = pack2<BF16>(__uint_as_float(v[8 * q + 6]), __uint_as_float(v[8 * q + 7]));
           *reinterpret_cast<uint4 *>(o_row + c * 32 + q * 8) = out;
+          if (d_row) {
+            out.x = pack2<BF16>(__uint_as_float(v[8 * q]) * inv, __uint_as_float(v[8 * q + 1]) * inv);
+            out.y = pack2<BF16>(__uint_as_float(v[8 * q + 2]) * inv, __uint_as_float(v[8 * q + 3]) * inv);
+            out.z = pack2<BF16>(__uint_as_float(v[8 * q + 4]) * inv, __uint_as_float(v[8 * q + 5]) * inv);
+            out.w = pack2<BF16>(__uint_as_float(v[8 * q + 6]) * inv, __uint_as_float(v[8 * q + 7]) * inv);
+            *reinterpret_cast<uint4 *>(d_row + c * 32 + q * 8) = out;
+          }
         }
       }
-      uint32_t r2 = pack2<BF16>(rsum, 0.f);
-      static_cast<uint16_t *>(p.r_acc)[(size_t)head * p.seq_q + q0 + row] = (uint16_t)(r2 & 0xFFFF);
+      if (half == 0) {
+        uint32_t r2 = pack2<BF16>(total, 0.f);
+        static_cast<uint16_t *>(p.r_acc)[(size_t)head * p.seq_q + q0 + row] = (uint16_t)(r2 & 0xFFFF);
+      }
     }
   }
 
@@ -357,18 +434,22 @@ int mgd_attn_rows_supported(const mgd_attn_rows *p) { return tc::rows_supported(
 
 int mgd_launch_attn_rows_float(const mgd_attn_rows *p, const void *q, const void *k, const void *v, void *o_acc,
                                void *r_acc, void *stream) {
+  return mgd_launch_attn_rows_float_ex(p, q, k, v, o_acc, r_acc, nullptr, stream);
+}
+
+int mgd_launch_attn_rows_float_ex(const mgd_attn_rows *p, const void *q, const void *k, const void *v, void *o_acc,
+                                  void *r_acc, void *o_div, void *stream) {
   if (!q || !k || !v || !o_acc || !r_acc) return set_error(MG_ERR_INVALID_ARGUMENT, "dense attention: null tensor");
   if (!tc::rows_supported(p)) return set_error(MG_ERR_UNSUPPORTED, "dense attention: shape or layout not supported");
-  CUtensorMap qm, km, vm;
-  bool ok = tc::make_map(&qm, q, p->heads, p->seq_q, tc::kD) && tc::make_map(&km, k, p->heads, p->kv_len, tc::kD) &&
-            tc::make_map(&vm, v, p->heads, tc::kD, p->kv_len);
+  CUtensorMap km, vm;
+  bool ok = tc::make_map(&km, k, p->heads, p->kv_len, tc::kD) && tc::make_map(&vm, v, p->heads, tc::kD, p->kv_len);
   if (!ok) return set_error(MG_ERR_CUDA, "dense attention: cuTensorMapEncodeTiled failed");
   tc::RowsParams a;
-  a.o_acc = o_acc; a.r_acc = r_acc;
+  a.q = q; a.o_acc = o_acc; a.r_acc = r_acc; a.o_div = o_div;
   a.status = device_error_word();
   if (!a.status) return set_error(MG_ERR_CUDA, "cannot allocate the device status word");
   a.heads = p->heads; a.seq_q = p->seq_q; a.kv_len = p->kv_len; a.forloop = p->forloop_range;
-  size_t smem = 1024 + tc::kOperand * (2 + 2 * tc::kStages) + sizeof(tc::Barriers) + 64;
+  size_t smem = 1024 + tc::kOperand * (2 * tc::kStages) + sizeof(tc::Barriers) + 64;
   unsigned blocks = (unsigned)(p->heads * (p->seq_q / tc::kM));
   static bool configured[2] = {false, false};
   bool bf16 = p->data_type == MG_DT_BFLOAT16;
@@ -378,8 +459,8 @@ int mgd_launch_attn_rows_float(const mgd_attn_rows *p, const void *q, const void
     if (e != cudaSuccess) return check_launch("cudaFuncSetAttribute(attn_rows_tc_kernel)");
     configured[bf16] = true;
   }
-  if (bf16) tc::attn_rows_tc_kernel<true><<<blocks, 192, smem, (cudaStream_t)stream>>>(qm, km, vm, a);
-  else tc::attn_rows_tc_kernel<false><<<blocks, 192, smem, (cudaStream_t)stream>>>(qm, km, vm, a);
+  if (bf16) tc::attn_rows_tc_kernel<true><<<blocks, 320, smem, (cudaStream_t)stream>>>(km, vm, a);
+  else tc::attn_rows_tc_kernel<false><<<blocks, 320, smem, (cudaStream_t)stream>>>(km, vm, a);
   return check_launch("attn_rows_tc_kernel");
 }
 }

@@ -135,6 +135,10 @@ typedef struct mgd_attn_rows {
 int mgd_attn_rows_supported(const mgd_attn_rows *p);
 int mgd_launch_attn_rows_float(const mgd_attn_rows *p, const void *q, const void *k, const void *v, void *o_acc,
                                void *r_acc, void *stream);
+/* same launch that also performs the division operator that follows in the example (:88-98):
+ * o_div[heads, seq_q, d] = O_acc / R, from the fp32 accumulators; NULL = none */
+int mgd_launch_attn_rows_float_ex(const mgd_attn_rows *p, const void *q, const void *k, const void *v, void *o_acc,
+                                  void *r_acc, void *o_div, void *stream);
 
 /* Allocation-free variant of the fused decode launch (split-KV partials + cross-split merge in one kernel).
  * It has no counterpart in the reference.
