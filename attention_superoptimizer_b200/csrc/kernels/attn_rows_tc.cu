@@ -205,10 +205,11 @@ attn_rows_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
-    if (lane == 0) {
-      for (int j = 0; j < F; j++) {
-        int s = j % kStages;
-        if (j >= kStages && !mbar_wait(smem_u32(&bar->kv_empty[s]), (uint32_t)(((j / kStages) - 1) & 1), abort_flag)) break;
+    // (the whole warp walks the loop and waits together; one lane issues the copies)
+    for (int j = 0; j < F; j++) {
+      int s = j % kStages;
+      if (j >= kStages && !mbar_wait(smem_u32(&bar->kv_empty[s]), (uint32_t)(((j / kStages) - 1) & 1), abort_flag)) break;
+      if (lane == 0) {
         uint32_t full = smem_u32(&bar->kv_full[s]);
         uint32_t kdst = ring + (uint32_t)(s * 2 * kOperand), vdst = kdst + kOperand;
         int kv0 = j * kN;
@@ -220,55 +221,64 @@ attn_rows_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
         tma_load_3d(vdst, &v_map, full, kv0, 0, head);
         tma_load_3d(vdst + kSubTile, &v_map, full, kv0 + 64, 0, head);
       }
+      __syncwarp();
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      // instruction descriptor: fp32 accumulate, A/B format (0 = fp16, 1 = bf16), both K-major, N = 128, M = 128
-      uint32_t const fmt = BF16 ? 1u : 0u;
-      uint32_t const idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(kN >> 3) << 17) | ((uint32_t)(kM >> 4) << 24);
-      bool ok = mbar_wait(smem_u32(&bar->q_ready), 0, abort_flag);
+    // The whole warp walks the loop and waits together (it stays converged); one lane issues.  Descriptors of a
+    // stage differ from those of stage 0 only in the start-address field, and K steps inside a tile only by a
+    // constant, so an MMA costs the issuing lane one 64-bit add.
+    // instruction descriptor: fp32 accumulate, A/B format (0 = fp16, 1 = bf16), both K-major, N = 128, M = 128
+    uint32_t const fmt = BF16 ? 1u : 0u;
+    uint32_t const idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(kN >> 3) << 17) | ((uint32_t)(kM >> 4) << 24);
+    uint64_t const desc0 = smem_desc(ring, 0);
+    bool ok = mbar_wait(smem_u32(&bar->q_ready), 0, abort_flag);
 #ifdef MG_ROWS_TIMING
-      long long w_kv = 0, w_ef = 0, t_all = clock64();
+    long long w_kv = 0, w_ef = 0, t_all = clock64();
 #endif
-      for (int j = 0; j <= F && ok; j++) {
-        if (j < F) { // S(j) = Q K_j^T into S buffer j % 2
-          int s = j % kStages, b = j & 1;
-          TICK(a0);
-          ok = mbar_wait(smem_u32(&bar->kv_full[s]), (uint32_t)((j / kStages) & 1), abort_flag);
-          TOCK(w_kv, a0);
-          if (!ok) break;
-          tc_fence_after();
-          uint32_t ktile = ring + (uint32_t)(s * 2 * kOperand);
+    for (int j = 0; j <= F && ok; j++) {
+      if (j < F) { // S(j) = Q K_j^T into S buffer j % 2
+        int s = j % kStages, b = j & 1;
+        TICK(a0);
+        ok = mbar_wait(smem_u32(&bar->kv_full[s]), (uint32_t)((j / kStages) & 1), abort_flag);
+        TOCK(w_kv, a0);
+        if (!ok) break;
+        tc_fence_after();
+        if (lane == 0) {
+          uint64_t kdesc = desc0 + (uint64_t)((s * 2 * kOperand) >> 4);
 #pragma unroll
           for (int ks = 0; ks < kD / 16; ks++) { // A = Q from tensor memory: 16 values = 8 packed columns per step
-            uint32_t off = (uint32_t)((ks >> 2) * kSubTile + (ks & 3) * 32);
-            umma_f16_ts(tmem_s[b], tmem_q + (uint32_t)(ks * 8), smem_desc(ktile, off), idesc, ks > 0);
+            uint64_t off = (uint64_t)(((ks >> 2) * kSubTile + (ks & 3) * 32) >> 4);
+            umma_f16_ts(tmem_s[b], tmem_q + (uint32_t)(ks * 8), kdesc + off, idesc, ks > 0);
           }
           umma_commit(smem_u32(&bar->s_full[b]));
         }
-        if (j >= 1) { // O' += E_{j-1} V_{j-1}
-          int t = j - 1, s = t % kStages, eb = t & 1;
-          TICK(a2);
-          ok = mbar_wait(smem_u32(&bar->e_full[eb]), (uint32_t)((t >> 1) & 1), abort_flag);
-          TOCK(w_ef, a2);
-          if (!ok) break;
-          tc_fence_after();
-          uint32_t vtile = ring + (uint32_t)(s * 2 * kOperand) + kOperand;
+        __syncwarp();
+      }
+      if (j >= 1) { // O' += E_{j-1} V_{j-1}
+        int t = j - 1, s = t % kStages, eb = t & 1;
+        TICK(a2);
+        ok = mbar_wait(smem_u32(&bar->e_full[eb]), (uint32_t)((t >> 1) & 1), abort_flag);
+        TOCK(w_ef, a2);
+        if (!ok) break;
+        tc_fence_after();
+        if (lane == 0) {
+          uint64_t vdesc = desc0 + (uint64_t)((s * 2 * kOperand + kOperand) >> 4);
 #pragma unroll
           for (int ks = 0; ks < kN / 16; ks++) { // A = E in the S buffer: half h at columns [64h, 64h+32), 8 per step
-            uint32_t off = (uint32_t)((ks >> 2) * kSubTile + (ks & 3) * 32);
+            uint64_t off = (uint64_t)(((ks >> 2) * kSubTile + (ks & 3) * 32) >> 4);
             uint32_t ecol = (uint32_t)((ks >> 2) * 64 + (ks & 3) * 8);
-            umma_f16_ts(tmem_o, tmem_s[eb] + ecol, smem_desc(vtile, off), idesc, (t > 0 || ks > 0) ? 1u : 0u);
+            umma_f16_ts(tmem_o, tmem_s[eb] + ecol, vdesc + off, idesc, (t > 0 || ks > 0) ? 1u : 0u);
           }
           umma_commit(smem_u32(&bar->kv_empty[s]));  // K_t and V_t have been consumed
           if (t == F - 1) umma_commit(smem_u32(&bar->o_full));
         }
+        __syncwarp();
       }
-#ifdef MG_ROWS_TIMING
-      if (blockIdx.x == 0) printf("mma issuer: total %lld wait_kv %lld wait_e_full %lld (cycles, %d tiles)\n", clock64() - t_all, w_kv, w_ef, F);
-#endif
     }
+#ifdef MG_ROWS_TIMING
+    if (blockIdx.x == 0 && lane == 0) printf("mma issuer: total %lld wait_kv %lld wait_e_full %lld (cycles, %d tiles)\n", clock64() - t_all, w_kv, w_ef, F);
+#endif
   } else {
     // ------------------------------------------------------------------ exp / row sums / epilogue
     // thread = (query row, 64-column half)
