@@ -154,7 +154,7 @@ struct RowsParams {
 };
 
 struct Barriers {
-  uint64_t q_ready, kv_full[kStages], kv_empty[kStages], s_full[2], e_full[2], o_full;
+  uint64_t q_ready, kv_full[kStages], kv_empty[kStages], s_full[2], e_full[2], o_full, dbg;
   uint32_t tmem_base;
   int abort_flag;
   float row_sums[2][kM]; // per column half
@@ -189,6 +189,7 @@ attn_rows_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
       mbar_init(smem_u32(&bar->e_full[b]), 256);
     }
     mbar_init(smem_u32(&bar->o_full), 1);
+    mbar_init(smem_u32(&bar->dbg), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -235,6 +236,8 @@ attn_rows_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
     bool ok = mbar_wait(smem_u32(&bar->q_ready), 0, abort_flag);
 #ifdef MG_ROWS_TIMING
     long long w_kv = 0, w_ef = 0, t_all = clock64();
+    long long ev1s[16], ev1e[16], ev2s[16], ev2e[16];
+    int dbg_n = 0; (void)dbg_n;
 #endif
     for (int j = 0; j <= F && ok; j++) {
       if (j < F) { // S(j) = Q K_j^T into S buffer j % 2
@@ -244,6 +247,9 @@ attn_rows_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
         TOCK(w_kv, a0);
         if (!ok) break;
         tc_fence_after();
+#ifdef MG_ROWS_TIMING
+        if (j < 16) ev1s[j] = clock64() - t_all;
+#endif
         if (lane == 0) {
           uint64_t kdesc = desc0 + (uint64_t)((s * 2 * kOperand) >> 4);
 #pragma unroll
@@ -252,8 +258,17 @@ attn_rows_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
             umma_f16_ts(tmem_s[b], tmem_q + (uint32_t)(ks * 8), kdesc + off, idesc, ks > 0);
           }
           umma_commit(smem_u32(&bar->s_full[b]));
+#ifdef MG_ROWS_TIMING2
+          umma_commit(smem_u32(&bar->dbg));
+#endif
         }
         __syncwarp();
+#ifdef MG_ROWS_TIMING2
+        mbar_wait(smem_u32(&bar->dbg), (uint32_t)(dbg_n++ & 1), abort_flag);
+#endif
+#ifdef MG_ROWS_TIMING
+        if (j < 16) ev1e[j] = clock64() - t_all;
+#endif
       }
       if (j >= 1) { // O' += E_{j-1} V_{j-1}
         int t = j - 1, s = t % kStages, eb = t & 1;
@@ -262,6 +277,9 @@ attn_rows_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
         TOCK(w_ef, a2);
         if (!ok) break;
         tc_fence_after();
+#ifdef MG_ROWS_TIMING
+        if (t < 16) ev2s[t] = clock64() - t_all;
+#endif
         if (lane == 0) {
           uint64_t vdesc = desc0 + (uint64_t)((s * 2 * kOperand + kOperand) >> 4);
 #pragma unroll
@@ -272,12 +290,24 @@ attn_rows_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
           }
           umma_commit(smem_u32(&bar->kv_empty[s]));  // K_t and V_t have been consumed
           if (t == F - 1) umma_commit(smem_u32(&bar->o_full));
+#ifdef MG_ROWS_TIMING2
+          umma_commit(smem_u32(&bar->dbg));
+#endif
         }
         __syncwarp();
+#ifdef MG_ROWS_TIMING2
+        mbar_wait(smem_u32(&bar->dbg), (uint32_t)(dbg_n++ & 1), abort_flag);
+#endif
+#ifdef MG_ROWS_TIMING
+        if (t < 16) ev2e[t] = clock64() - t_all;
+#endif
       }
     }
 #ifdef MG_ROWS_TIMING
-    if (blockIdx.x == 0 && lane == 0) printf("mma issuer: total %lld wait_kv %lld wait_e_full %lld (cycles, %d tiles)\n", clock64() - t_all, w_kv, w_ef, F);
+    if (blockIdx.x == 0 && lane == 0) {
+      printf("mma issuer: total %lld wait_kv %lld wait_e_full %lld (cycles, %d tiles) t0 %lld\n", clock64() - t_all, w_kv, w_ef, F, t_all);
+      for (int j = 0; j < 16 && j < F; j++) printf("  tile %2d: mma1 issue %6lld..%6lld   mma2 issue %6lld..%6lld\n", j, ev1s[j], ev1e[j], ev2s[j], ev2e[j]);
+    }
 #endif
   } else {
     // ------------------------------------------------------------------ exp / row sums / epilogue
@@ -304,6 +334,7 @@ attn_rows_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
     }
 #ifdef MG_ROWS_TIMING
     long long w_sf = 0, c_exp = 0, c_st = 0, t_all = clock64();
+    long long es[16], ee[16], et[16];
 #endif
     for (int j = 0; j < F && ok; j++) {
       int b = j & 1;
@@ -313,6 +344,9 @@ attn_rows_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
       if (!ok) break;
       tc_fence_after();
       TICK(b1);
+#ifdef MG_ROWS_TIMING
+      if (j < 16) es[j] = clock64() - t_all;
+#endif
       uint32_t packed[2][16]; // this thread's 64 values as 16-bit pairs
 #pragma unroll
       for (int c = 0; c < 2; c++) {
@@ -327,6 +361,9 @@ attn_rows_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
       }
       TOCK(c_exp, b1);
       TICK(b3);
+#ifdef MG_ROWS_TIMING
+      if (j < 16) ee[j] = clock64() - t_all;
+#endif
       // E replaces the S values this thread has just consumed: 32 packed columns at the start of its own half
       uint32_t flat[32];
 #pragma unroll
@@ -335,10 +372,16 @@ attn_rows_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
       tc_fence_before();
       mbar_arrive(smem_u32(&bar->e_full[b]));
       TOCK(c_st, b3);
+#ifdef MG_ROWS_TIMING
+      if (j < 16) et[j] = clock64() - t_all;
+#endif
     }
 #ifdef MG_ROWS_TIMING
     if (blockIdx.x == 0 && lane == 0 && (warp == 2 || warp == 6))
-      printf("exp warp %d: total %lld wait_s_full %lld ld+exp %lld st %lld\n", warp, clock64() - t_all, w_sf, c_exp, c_st);
+    {
+      printf("exp warp %d: total %lld wait_s_full %lld ld+exp %lld st %lld t0 %lld\n", warp, clock64() - t_all, w_sf, c_exp, c_st, t_all);
+      if (warp == 2) for (int j = 0; j < 16 && j < F; j++) printf("  tile %2d: s_full seen %6lld  exp done %6lld  E stored %6lld\n", j, es[j], ee[j], et[j]);
+    }
 #endif
     // the two halves of a row add up their sums (named barrier over the 256 threads of these warps; reached
     // by all of them whether or not a wait gave up)
