@@ -135,7 +135,7 @@ def run_ours(args):
     set_bytes = qb + kb + vb
     nsets = max(16, -(-(5 * L2_BYTES // 2) // set_bytes))          # > 2.5x L2 of distinct inputs
     calls = args.calls_per_step if args.calls_per_step > 0 else max(nsets, 64)
-    arena = nsets * (2 * set_bytes + (1 << 20)) + (1 << 28)
+    arena = nsets * (2 * set_bytes + (1 << 20)) + (1 << 28) + (3 << 29)   # + room for the other configs' graphs
     rt = mg.Runtime.get(device=local_rank, arena_bytes=arena)
     rt.set_specialisation(not args.interpreter_only)
     stream = torch.cuda.Stream()
@@ -250,6 +250,9 @@ def run_ours(args):
 
     # ---- fingerprint verification sweep ----------------------------------------------------------------
     fingerprint = run_fingerprint_sweep(args, mg, mo, fp_oracle, rt, torch, dist, np, rank, world, stream, timed)
+    others = None
+    if world == 1 and not args.no_other_configs:
+        others = measure_other_configs(mg, rt, stream, timed, load_peaks()[0])
 
     # ---- CPU baseline (rank 0, N = 1 only) ----------------------------------------------------------------
     cpu = None
@@ -272,7 +275,7 @@ def run_ours(args):
                        "parallelism": "kv-heads sharded x%d, no collective" % world},
             "hbm_gbs": round(sum(per_call_bytes(heads)) / (us_per_call * 1e-6) / 1e9, 1),
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(gpu_launches),
-            "clocks": clocks, "fingerprint": fingerprint,
+            "clocks": clocks, "fingerprint": fingerprint, "other_configs": others,
         }
         print(json.dumps(line))
     step_graph.close()
@@ -356,6 +359,87 @@ def run_fingerprint_sweep(args, mg, mo, fp_oracle, rt, torch, dist, np, rank, wo
             "eval_ms": round(t_eval, 3), "allgather_ms": round(t_gather, 3),
             "bytes_per_eval": 16793600, "hbm_gbs_per_gpu": round(16793600 * nchunks * chunk / (t_eval * 1e-3) / 1e9, 1),
             "kernel_op1": info["kernel_fingerprint"], "oracle_checked_sets": checked, "bit_exact": bool(ok)}
+
+
+def measure_other_configs(mg, rt, stream, timed, peaks):
+    """Device-timed numbers for the remaining BASELINE configs (N = 1 only), each replayed from a CUDA graph:
+    config 3 (speculative decode with the causal draft window, fp16), config 4 (dense prefill, bf16, tcgen05)
+    and config 1 (matmul chain; fingerprint mode on the generic interpreter - no float kernel fits it yet)."""
+    sh = stream.cuda_stream
+    out = {}
+
+    def replay_us(graphs, reps):
+        for g in graphs:
+            g.run(stream=sh, sync=False)
+        stream.synchronize()
+        seq = mg.CapturedSequence(sh, lambda: [graphs[i % len(graphs)].run(stream=sh, sync=False) for i in range(reps)])
+        ms = timed(seq.launch, 5, 3) / 5
+        seq.close()
+        return ms * 1000.0 / reps
+
+    # ---- config 3: batch 4 x 8 KV heads = 32 units, 8 draft tokens x group 4 = 32 rows, KV 8192 -------------
+    units, rows, d, kv, splits, fr, window = 32, 32, 128, 8192, 16, 8, 8
+    graphs = []
+    for s in range(2):  # two buffer sets of 135 MB each: consecutive calls never share L2 contents
+        g = mg.PyGraph(rt)
+        Q = g.new_input((units, rows, d)); K = g.new_input((units, d, kv), layout=mg.DmemColumnMajor)
+        V = g.new_input((units, kv, d), layout=mg.DmemRowMajor)
+        p1, p2 = mg.gqa_decode_plans(units, rows, d, kv, splits, fr)
+        parts = g.customized([Q, K, V], p1); g.customized(parts, p2)
+        g.set_causal_window(3, window)
+        Q.fill_data_seeded(900 + s, d ** -0.5); K.fill_data_seeded(910 + s, 1.0); V.fill_data_seeded(920 + s, 1.0)
+        graphs.append(g)
+    us = replay_us(graphs, 8)
+    nbytes = 2 * units * rows * d * 2 + 2 * units * d * kv * 2
+    out["spec_decode_c3"] = {"us_per_call": round(us, 2), "hbm_gbs": round(nbytes / us / 1e3, 1),
+                             "frac_of_hbm_peak": round(nbytes / us / 1e3 / peaks["hbm_gbs"], 4), "bytes": nbytes,
+                             "kernel": graphs[0].customized_info(3)["kernel_float"], "dtype": "fp16",
+                             "note": "32 rows x KV 8192, 16 splits x for-loop 8, causal draft window 8, fused merge"}
+    for g in reversed(graphs):
+        g.close()
+
+    # ---- config 4: 32 heads, 2048 x 2048, head_dim 128, bf16 ----------------------------------------------------
+    H, SQ, L = 32, 2048, 2048
+    g = mg.PyGraph(rt)
+    Q = g.new_input((H, SQ, d), mg.bfloat16); K = g.new_input((H, d, L), mg.bfloat16, mg.DmemColumnMajor)
+    V = g.new_input((H, L, d), mg.bfloat16, mg.DmemColumnMajor)
+    p1, p2 = mg.attention_prefill_plans(H, SQ, d, L)
+    acc = g.customized([Q, K, V], p1); g.customized(acc, p2)
+    Q.fill_data_seeded(930, d ** -0.5); K.fill_data_seeded(931, 1.0); V.fill_data_seeded(932, 1.0)
+    us = replay_us([g], 10)
+    flops = 4.0 * H * SQ * L * d
+    out["prefill_c4"] = {"us_per_call": round(us, 2), "tflops": round(flops / us / 1e6, 1),
+                         "frac_of_bf16_peak": round(flops / us / 1e6 / peaks["bf16_tflops"], 4), "flops": flops,
+                         "kernel": g.customized_info(3)["kernel_float"], "dtype": "bf16",
+                         "note": "both customized ops in one launch (division fused into the tcgen05 kernel's epilogue)"}
+    g.close()
+
+    # ---- config 1: X[16,1024] W1[1024,1024] W2[1024,1024], fingerprint mode, generic interpreter -------------------
+    g = mg.PyGraph(rt)
+    X = g.new_input((16, 1024)); W1 = g.new_input((1024, 1024)); W2 = g.new_input((1024, 1024))
+    chain = mg.ExecutionPlan(ops=[(mg.TB_MATMUL_OP, [(0, 0), (1, 0)]), (mg.TB_MATMUL_OP, [(3, 0), (2, 0)])],
+                             input_map=[(-1, -1, -1), (1, -1, -1), (0, -1, -1)], forloop_dim=[1, 0, -1],
+                             input_smem_layouts=[mg.SmemRowMajor] * 3, output_map=(1, -1, -1), forloop_range=16,
+                             grid_dim=(16, 1, 1), reduction_dimx=1024)
+    part = g.customized([X, W1, W2], chain)
+    reduce_plan = mg.ExecutionPlan(ops=[(mg.TB_REDUCTION_1_TO_DIMX_OP, [(0, 0)])], input_map=[(0, -1, -1)],
+                                   forloop_dim=[-1], input_smem_layouts=[mg.SmemRowMajor], output_map=(0, -1, -1),
+                                   forloop_range=1, grid_dim=(16, 1, 1), reduction_dimx=1024)
+    g.customized(part, reduce_plan)
+    for t, sd in ((X, 940), (W1, 941), (W2, 942)):
+        t.fill_fingerprint_seeded(sd, mg.FP_P)
+    g.fingerprint()
+    import time as _t
+    t0 = _t.perf_counter()
+    for _ in range(20):
+        g.fingerprint()
+    out["matmul_chain_c1"] = {"fingerprint_us_per_call": round((_t.perf_counter() - t0) / 20 * 1e6, 1),
+                              "kernel": g.customized_info(3)["kernel_fingerprint"],
+                              "note": "two customized ops (16 blocks over the intermediate columns, for-loop 16 over K "
+                                      "tiles of 64; then the cross-block reduction), generic fingerprint interpreter, "
+                                      "host-synchronised calls; the float form needs 400 KB of fp32 tiles and has no kernel yet"}
+    g.close()
+    return out
 
 
 def host_seeded(np, seed, n, modulus):
@@ -457,6 +541,7 @@ def main():
                     help="DmemLayout of V[heads, kv, d]: row = memory [kv][d] (KV-cache order), col = memory [d][kv]")
     ap.add_argument("--interpreter-only", action="store_true", help="disable the specialised kernels")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-other-configs", action="store_true", help="skip the extra measurements of configs 1, 3 and 4")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
