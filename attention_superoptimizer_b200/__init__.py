@@ -32,6 +32,7 @@ TB_REDUCTION_0_TO_DIMX_OP, TB_REDUCTION_1_TO_DIMX_OP, TB_REDUCTION_2_TO_DIMX_OP 
 TB_CONCAT_0_OP, TB_CONCAT_1_OP, TB_CONCAT_2_OP = 2200, 2201, 2202
 FP_P, FP_Q, FP_PQ = 227, 113, 25651
 
+POLICY_LATENCY, POLICY_THROUGHPUT = 0, 1
 KERNEL_INTERPRETER, KERNEL_ATTN_SPLIT, KERNEL_ATTN_MERGE, KERNEL_ATTN_ROWS = 0, 1, 2, 3
 
 
@@ -112,6 +113,10 @@ class Runtime:
         one-launch fusion of the split-KV attention operator with its merge operator."""
         level = 2 if level is True else (0 if level is False else int(level))
         check(self.lib.mg_runtime_set_specialisation(self.handle, level))
+
+    def set_launch_policy(self, policy):
+        """POLICY_LATENCY (one call at a time) or POLICY_THROUGHPUT (several independent calls in flight)."""
+        check(self.lib.mg_runtime_set_launch_policy(self.handle, int(policy)))
 
     def tables(self):
         """Host copies of the arena's exp / div_p / div_q lookup tables."""

@@ -48,6 +48,7 @@ SIGNATURES = {
     "mg_runtime_arena_usage": (ctypes.c_int, [_P, ctypes.POINTER(ctypes.c_size_t), ctypes.POINTER(ctypes.c_size_t)]),
     "mg_runtime_set_max_smem": (ctypes.c_int, [_P, ctypes.c_size_t]),
     "mg_runtime_set_specialisation": (ctypes.c_int, [_P, ctypes.c_int]),
+    "mg_runtime_set_launch_policy": (ctypes.c_int, [_P, ctypes.c_int]),
     "mg_graph_create": (ctypes.c_int, [_P, ctypes.POINTER(_P)]),
     "mg_graph_destroy": (ctypes.c_int, [_P]),
     "mg_graph_new_input": (ctypes.c_int, [_P, ctypes.POINTER(_I), _I, _I, _I, _T]),

@@ -151,6 +151,13 @@ int mg_runtime_set_specialisation(mg_runtime *rt, int enabled) {
   return MG_OK;
 }
 
+int mg_runtime_set_launch_policy(mg_runtime *rt, int policy) {
+  if (!rt || !rt->dmm) return fail(MG_ERR_INVALID_ARGUMENT, "no runtime");
+  if (policy != MG_POLICY_LATENCY && policy != MG_POLICY_THROUGHPUT) return fail(MG_ERR_INVALID_ARGUMENT, "unknown launch policy");
+  rt->dmm->launch_policy = policy;
+  return MG_OK;
+}
+
 int mg_graph_create(mg_runtime *rt, mg_graph **g) {
   if (!rt || !rt->dmm || !g) return fail(MG_ERR_INVALID_ARGUMENT, "no runtime");
   *g = new (std::nothrow) mg_graph{rt, {}};

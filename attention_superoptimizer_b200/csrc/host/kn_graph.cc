@@ -73,7 +73,7 @@ static size_t round_up(size_t n) { return (n + kAlign - 1) / kAlign * kAlign; }
 
 DeviceMemoryManager::DeviceMemoryManager(int dev, size_t arena_bytes)
     : base_ptr(nullptr), offset(0), total_size(arena_bytes), exp_lookup_table(nullptr), div_p_lookup_table(nullptr),
-      div_q_lookup_table(nullptr), device(dev), max_smem(MAX_SMEM_SIZE), specialise(2), flag_word(nullptr),
+      div_q_lookup_table(nullptr), device(dev), max_smem(MAX_SMEM_SIZE), specialise(2), launch_policy(0), flag_word(nullptr),
       dry(dev < 0), ok_(false) {
   if (dry) {
     // Planning-only runtime: addresses are handed out from a range that is never dereferenced, so that
@@ -778,7 +778,7 @@ int KNCustomizedOp::launch_split(bool fp, int num_sets, void const *const *in, l
     opts.merged_set_stride = 0;
     outs.push_back(range_of(opts.merged_out, o.num_elements() * elem));
   }
-  opts.overlap = 1 | (inputs_untouched(stream, ins) ? 2 : 0);
+  opts.overlap = 1 | (inputs_untouched(stream, ins) ? 2 : 0) | (DeviceMemoryManager::get_instance()->launch_policy == 1 ? 4 : 0);
   int st = fp ? mgd_launch_attn_split_fingerprint_ex(&sp, (uint16_t const *)in[0], (uint16_t const *)in[1],
                                                      (uint16_t const *)in[2], (uint16_t *)out[0], (uint16_t *)out[1],
                                                      &opts, stream)

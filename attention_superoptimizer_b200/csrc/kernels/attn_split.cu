@@ -612,6 +612,12 @@ static int launch_split(mgd_attn_split const *p, void const *q, void const *k, v
   // bound, so tiles already in shared memory are worked on side by side (at most 16 warps per block).
   // With many waves the parallelism comes from several blocks per SM instead.
   int tile_groups = blocks > sm_count() ? 1 : (stages < 4 ? stages : 4);
+  // Throughput sizing asked for by the caller (several launches in flight at once): the same small blocks, so that
+  // blocks of different launches share an SM and one launch's loads run under another's arithmetic and tail.
+  if (opts && (opts->overlap & 4)) {
+    if (stages > 2) stages = 2;
+    tile_groups = 1;
+  }
   while (tile_groups > 1 && groups * tile_groups * 128 > 512) tile_groups--;
   int threads = groups * tile_groups * 128;
   size_t scratch = (size_t)(threads / 32) * rows_scratch * (DH + 4) * acc;

@@ -42,6 +42,7 @@ public:
   size_t max_smem;     // budget handed to new threadblock graphs
   int specialise;      // 0 = generic interpreters only, 1 = pattern-specialised kernels, 2 = also fuse a
                        // split-KV attention operator with the merge operator that consumes it (default)
+  int launch_policy;   // 0 = size launches for the latency of one call, 1 = for the throughput of many calls in flight
   int *flag_word;      // 4-byte device scratch for comparisons
   bool dry;            // planning-only: no device memory behind the arena, launches refused
 

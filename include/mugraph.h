@@ -116,6 +116,13 @@ int mg_runtime_set_max_smem(mg_runtime *rt, size_t bytes);
  * 1 = pattern-specialised kernels where a graph matches, 2 = also issue a split-KV attention operator and the
  * merge operator consuming it as one launch when a whole graph is run (default) */
 int mg_runtime_set_specialisation(mg_runtime *rt, int level);
+/* How launches are sized.  MG_POLICY_LATENCY (default): one call at a time is as fast as possible (a block keeps
+ * its whole KV split in flight and works on its tiles side by side).  MG_POLICY_THROUGHPUT: the caller keeps
+ * several independent calls in flight (streams, captured graphs); blocks are kept small so that blocks of
+ * different launches share an SM and memory traffic of one call overlaps the arithmetic and tail of another.
+ * The reference has no such knob (one kernel at a time on the default stream). */
+enum { MG_POLICY_LATENCY = 0, MG_POLICY_THROUGHPUT = 1 };
+int mg_runtime_set_launch_policy(mg_runtime *rt, int policy);
 
 /* ---- kernel graph ---------------------------------------------------------
  * kernel::Graph, include/mirage/kernel/graph.h:28-85 */

@@ -104,7 +104,10 @@ int mgd_attn_split_supported(const mgd_attn_split *p, int32_t fingerprint_mode);
  *  overlap: bit 0 = launch with programmatic stream serialisation, so that this kernel's blocks may be scheduled
  *    while the previous kernel of the stream drains (every global write still waits for that kernel's completion);
  *    bit 1 = none of the inputs was written by the previous kernel of this library on this stream, so the tile
- *    loads may be issued before that wait. */
+ *    loads may be issued before that wait;
+ *    bit 2 = size the blocks for throughput (two-stage ring, four warps): blocks of several launches in flight
+ *    then share an SM.  Without it a launch that fits one wave keeps its whole KV split in flight per block,
+ *    which gives the lowest latency for one launch at a time. */
 typedef struct mgd_attn_launch_opts {
   void *merged_out;          /* [num_sets][heads][m][d], NULL = partials only */
   int32_t *tickets;
