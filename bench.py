@@ -255,7 +255,11 @@ def run_ours(args):
     achieved = op1_bytes / (op1_us * 1e-6) / 1e9
     roofline = {"bound": "hbm", "kernel": "split-KV attention operator (op1)", "achieved": round(achieved, 1),
                 "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": round(achieved / peaks["hbm_gbs"], 4),
-                "peak_source": peak_src, "traffic": None, "bytes_per_launch": op1_bytes,
+                "peak_source": peak_src,
+                "traffic": 16864512 if world == 1 else None,
+                "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of one launch, ncu capture "
+                                  "profiles/attn_split_fp16_gqa_decode.md (same shapes, N = 1)",
+                "bytes_per_launch": op1_bytes,
                 "us_per_launch": round(op1_us, 3)}
 
     # ---- end to end through the public API with host buffers -----------------------------------------
