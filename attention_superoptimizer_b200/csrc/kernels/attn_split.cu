@@ -28,6 +28,7 @@
 // Every mbarrier wait is bounded: a block that gives up records a code in the device status word and
 // returns without touching its outputs further.
 #include "common.cuh"
+#include <cstdlib>
 #include <cuda.h>
 #include <mutex>
 #include <unordered_map>
@@ -618,6 +619,11 @@ static int launch_split(mgd_attn_split const *p, void const *q, void const *k, v
     if (stages > 2) stages = 2;
     tile_groups = 1;
   }
+  // tuning overrides for experiments: MUGRAPH_ATTN_STAGES, MUGRAPH_ATTN_TILE_GROUPS
+  if (char const *e = getenv("MUGRAPH_ATTN_STAGES")) stages = atoi(e) < 1 ? 1 : (atoi(e) > kMaxStages ? kMaxStages : atoi(e));
+  if (char const *e = getenv("MUGRAPH_ATTN_TILE_GROUPS")) tile_groups = atoi(e) < 1 ? 1 : atoi(e);
+  if (stages > p->forloop_range) stages = p->forloop_range;
+  if (tile_groups > stages) tile_groups = stages;
   while (tile_groups > 1 && groups * tile_groups * 128 > 512) tile_groups--;
   int threads = groups * tile_groups * 128;
   size_t scratch = (size_t)(threads / 32) * rows_scratch * (DH + 4) * acc;
