@@ -129,7 +129,9 @@ struct AttnSplitParams {
 };
 
 // Shared-memory plan: [stages x (K tile, V tile)] (1024-byte aligned) | reduction scratch | barriers | exp table
-template <int MODE, int DH>
+// FORM: bit 0 = K staged as [kv][d] (else [d][kv]); bit 1 = V staged as [kv][d] (else [d][kv]).  A compile-time
+// property so that every ldmatrix address is one XOR and one ADD away from a per-lane constant.
+template <int MODE, int DH, int FORM>
 __global__ void __launch_bounds__(512)
 attn_split_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
                   const __grid_constant__ AttnSplitParams p) {
@@ -138,6 +140,7 @@ attn_split_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
   constexpr int kTileBytes = kTile * DH * 2;
   constexpr int kKSteps = DH / 16;     // k-steps of Q K (contraction over head_dim)
   constexpr int kNPairs = DH / 16;     // pairs of 8-wide output tiles of E V (output over head_dim)
+  constexpr bool kKRowsKv = (FORM & 1) != 0, kVRowsKv = (FORM & 2) != 0;
   extern __shared__ unsigned char smem_dyn[];
   unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
 
@@ -183,12 +186,12 @@ attn_split_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
     uint32_t kdst = stage_base + (uint32_t)(s * 2 * kTileBytes), vdst = kdst + kTileBytes;
     int kv0 = kv_base + it * kTile;
     mbar_expect_tx(bar, 2 * kTileBytes);
-    if (p.k_rows_are_kv) {
+    if (kKRowsKv) {
       for (int c = 0; c < DH / 64; c++) tma_load_3d(kdst + c * (kTile * 128), &k_map, bar, c * 64, kv0, batch);
     } else {
       tma_load_3d(kdst, &k_map, bar, kv0, 0, batch);
     }
-    if (p.v_rows_are_kv) {
+    if (kVRowsKv) {
       for (int c = 0; c < DH / 64; c++) tma_load_3d(vdst + c * (kTile * 128), &v_map, bar, c * 64, kv0, batch);
     } else {
       tma_load_3d(vdst, &v_map, bar, kv0, 0, batch);
@@ -255,6 +258,35 @@ attn_split_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
   int const kv0 = slice * 16;               // this warp's KV positions inside a tile
   bool failed = false;
 
+  // Per-lane pieces of the ldmatrix addresses (see tile_addr): what is left per step is a compile-time offset
+  // and, where the step moves along a swizzled row, one XOR.
+  uint32_t k_lane, k_x, v_lane, v_x;
+  if (kKRowsKv) {
+    int row = kv0 + (mi >> 1) * 8 + rr;
+    k_lane = (uint32_t)(row * 128);
+    k_x = (uint32_t)(((row & 7) ^ (mi & 1)) << 4);
+  } else {
+    k_lane = (uint32_t)(((mi & 1) * 8 + rr) * 128 + ((((kv0 >> 3) + (mi >> 1)) ^ rr) << 4));
+    k_x = 0;
+  }
+  if (kVRowsKv) {
+    int row = kv0 + (mi & 1) * 8 + rr;
+    v_lane = (uint32_t)(row * 128);
+    v_x = (uint32_t)(((row & 7) ^ (mi >> 1)) << 4);
+  } else {
+    v_lane = (uint32_t)(((mi >> 1) * 8 + rr) * 128 + ((((kv0 >> 3) + (mi & 1)) ^ rr) << 4));
+    v_x = 0;
+  }
+  // causal window (float mode): last KV position each of this thread's two rows may see
+  int lim0 = 0x7fffffff, lim1 = 0x7fffffff, lim_min = 0x7fffffff;
+  if (MODE != kFingerprint && p.causal_window > 0) {
+    int rows_per_token = p.m / p.causal_window;
+    int r0 = group * 16 + g, r1 = r0 + 8;
+    lim0 = p.kv_len - p.causal_window + r0 / rows_per_token;
+    lim1 = p.kv_len - p.causal_window + r1 / rows_per_token;
+    lim_min = p.kv_len - p.causal_window; // positions up to here are visible to every row
+  }
+
   // Tiles are consumed in rounds of `tile_groups`: warp group tgroup takes tile round*tile_groups + tgroup.
   int const rounds = (p.forloop + p.tile_groups - 1) / p.tile_groups;
   for (int round = 0; round < rounds; round++) {
@@ -276,8 +308,8 @@ attn_split_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
 #pragma unroll
     for (int ks = 0; ks < kKSteps; ks++) {
       uint32_t bfrag[4];
-      if (p.k_rows_are_kv) ldsm_x4(tile_addr(ktile, kTile, kv0 + (mi >> 1) * 8 + rr, ks * 2 + (mi & 1)), bfrag);
-      else ldsm_x4_trans(tile_addr(ktile, DH, ks * 16 + (mi & 1) * 8 + rr, (kv0 >> 3) + (mi >> 1)), bfrag);
+      if (kKRowsKv) ldsm_x4(ktile + k_lane + (uint32_t)((ks >> 2) * (kTile * 128)) + (k_x ^ (uint32_t)(((2 * ks) & 7) << 4)), bfrag);
+      else ldsm_x4_trans(ktile + k_lane + (uint32_t)(ks * 16 * 128), bfrag);
       mma_tile<MODE>(sacc[0], qa[ks], bfrag[0], bfrag[1]);
       mma_tile<MODE>(sacc[1], qa[ks], bfrag[2], bfrag[3]);
     }
@@ -308,16 +340,13 @@ attn_split_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
     } else {
       float ev[2][4];
       int pos = kv_base + it * kTile + kv0 + 2 * t; // KV position of sacc[0][0]
+      bool const in_window = pos + 9 > lim_min;      // some position of this thread's eight may be masked
 #pragma unroll
       for (int nt = 0; nt < 2; nt++)
 #pragma unroll
         for (int j = 0; j < 4; j++) {
           float v = __expf(sacc[nt][j]);
-          if (p.causal_window > 0) {
-            int row = group * 16 + g + (j >> 1) * 8;
-            int token = row / (p.m / p.causal_window);
-            if (pos + nt * 8 + (j & 1) > p.kv_len - p.causal_window + token) v = 0.f;
-          }
+          if (in_window && pos + nt * 8 + (j & 1) > ((j >> 1) ? lim1 : lim0)) v = 0.f;
           ev[nt][j] = v;
         }
       racc0 += ev[0][0] + ev[0][1] + ev[1][0] + ev[1][1];
@@ -335,8 +364,8 @@ attn_split_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
 #pragma unroll
     for (int jp = 0; jp < kNPairs; jp++) {
       uint32_t bfrag[4];
-      if (p.v_rows_are_kv) ldsm_x4_trans(tile_addr(vtile, kTile, kv0 + (mi & 1) * 8 + rr, jp * 2 + (mi >> 1)), bfrag);
-      else ldsm_x4(tile_addr(vtile, DH, (2 * jp + (mi >> 1)) * 8 + rr, (kv0 >> 3) + (mi & 1)), bfrag);
+      if (kVRowsKv) ldsm_x4_trans(vtile + v_lane + (uint32_t)((jp >> 2) * (kTile * 128)) + (v_x ^ (uint32_t)(((2 * jp) & 7) << 4)), bfrag);
+      else ldsm_x4(vtile + v_lane + (uint32_t)(jp * 16 * 128), bfrag);
       mma_tile<MODE>(oacc[2 * jp], ea, bfrag[0], bfrag[1]);
       mma_tile<MODE>(oacc[2 * jp + 1], ea, bfrag[2], bfrag[3]);
     }
@@ -595,6 +624,20 @@ static bool shape_supported(mgd_attn_split const *p, bool fp) {
   return true;
 }
 
+// One instantiation per (mode, head_dim, operand forms); the shared-memory opt-in is set once for each.
+template <int MODE, int DH, int FORM>
+static int launch_form(cudaLaunchConfig_t const &cfg, CUtensorMap const &kmap, CUtensorMap const &vmap,
+                       AttnSplitParams const &a) {
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(attn_split_kernel<MODE, DH, FORM>, cudaFuncAttributeMaxDynamicSharedMemorySize, kDynSmemLimit) != cudaSuccess)
+      return check_launch("cudaFuncSetAttribute(attn_split_kernel)");
+    configured = true;
+  }
+  cudaLaunchKernelEx(&cfg, attn_split_kernel<MODE, DH, FORM>, kmap, vmap, a);
+  return check_launch("attn_split_kernel");
+}
+
 template <int MODE, int DH>
 static int launch_split(mgd_attn_split const *p, void const *q, void const *k, void const *v, void *o, void *r,
                         mgd_attn_launch_opts const *opts, void *stream, int32_t *status_word = nullptr) {
@@ -654,12 +697,6 @@ static int launch_split(mgd_attn_split const *p, void const *q, void const *k, v
   if (a.merged_out && !a.tickets) return set_error(MG_ERR_INVALID_ARGUMENT, "split-KV attention: merging needs ticket counters");
   a.kv_len = p->kv_len; a.k_rows_are_kv = k_kv; a.v_rows_are_kv = v_kv; a.causal_window = p->causal_window;
 
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(attn_split_kernel<MODE, DH>, cudaFuncAttributeMaxDynamicSharedMemorySize, kDynSmemLimit) != cudaSuccess)
-      return check_launch("cudaFuncSetAttribute(attn_split_kernel)");
-    configured = true;
-  }
   if (blocks > 0x7fffffffLL) return set_error(MG_ERR_UNSUPPORTED, "too many blocks for one launch");
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)blocks, 1, 1);
@@ -673,8 +710,13 @@ static int launch_split(mgd_attn_split const *p, void const *q, void const *k, v
     cfg.attrs = attr;
     cfg.numAttrs = 1;
   }
-  cudaLaunchKernelEx(&cfg, attn_split_kernel<MODE, DH>, kmap, vmap, a);
-  return check_launch("attn_split_kernel");
+  if constexpr (MODE == kFingerprint) return launch_form<MODE, DH, 2>(cfg, kmap, vmap, a);
+  else switch ((k_kv ? 1 : 0) | (v_kv ? 2 : 0)) {
+    case 0: return launch_form<MODE, DH, 0>(cfg, kmap, vmap, a);
+    case 1: return launch_form<MODE, DH, 1>(cfg, kmap, vmap, a);
+    case 2: return launch_form<MODE, DH, 2>(cfg, kmap, vmap, a);
+    default: return launch_form<MODE, DH, 3>(cfg, kmap, vmap, a);
+  }
 }
 // ---- scratch of the allocation-free entry point ---------------------------------------------------------------
 // One ticket counter per (input set, head) followed by one status word.  The array lives in the library image:
