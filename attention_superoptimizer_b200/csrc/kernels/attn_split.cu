@@ -180,8 +180,7 @@ attn_split_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
   __syncthreads();
 
   int const kv_base = split * p.forloop * kTile; // first KV position of this block
-  auto issue = [&](int it) {
-    int s = it % p.stages;
+  auto issue = [&](int it, int s) {
     uint32_t bar = smem_u32(&bars[s]);
     uint32_t kdst = stage_base + (uint32_t)(s * 2 * kTileBytes), vdst = kdst + kTileBytes;
     int kv0 = kv_base + it * kTile;
@@ -230,7 +229,7 @@ attn_split_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
   auto issue_first = [&]() {
     if (tid == 0) {
       int first = p.forloop < p.stages ? p.forloop : p.stages;
-      for (int it = 0; it < first; it++) issue(it);
+      for (int it = 0; it < first; it++) issue(it, it);
     }
   };
   // Ordering against the previous kernel of the stream (programmatic dependent launch): nothing is written
@@ -289,13 +288,16 @@ attn_split_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
 
   // Tiles are consumed in rounds of `tile_groups`: warp group tgroup takes tile round*tile_groups + tgroup.
   int const rounds = (p.forloop + p.tile_groups - 1) / p.tile_groups;
+  // stage and barrier phase of this warp's tile, and stage of the round's first tile, kept without divisions
+  // (tile_groups <= stages, so one conditional subtraction per round is enough)
+  int s = tgroup, round_s = 0;
+  uint32_t phase = 0;
   for (int round = 0; round < rounds; round++) {
     int const it = round * p.tile_groups + tgroup;
-    int s = it % p.stages;
     bool const active = it < p.forloop;
     // After a wait has given up the block keeps walking the loop (so that every thread still meets the
     // block-wide barriers below) but stops waiting; its results are discarded at the end.
-    if (active && !failed && !mbar_wait(smem_u32(&bars[s]), (uint32_t)((it / p.stages) & 1))) failed = true;
+    if (active && !failed && !mbar_wait(smem_u32(&bars[s]), phase)) failed = true;
     if (active) {
     uint32_t ktile = stage_base + (uint32_t)(s * 2 * kTileBytes), vtile = ktile + kTileBytes;
 
@@ -377,9 +379,14 @@ attn_split_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
       if (tid == 0)
         for (int j = 0; j < p.tile_groups; j++) {
           int nxt = round * p.tile_groups + j + p.stages;
-          if (nxt < p.forloop) issue(nxt);
+          int ns = round_s + j >= p.stages ? round_s + j - p.stages : round_s + j; // the stage tile nxt - stages used
+          if (nxt < p.forloop) issue(nxt, ns);
         }
     }
+    s += p.tile_groups;
+    if (s >= p.stages) { s -= p.stages; phase ^= 1u; }
+    round_s += p.tile_groups;
+    if (round_s >= p.stages) round_s -= p.stages;
   }
 
   if (failed) s_failed = 1;
@@ -435,29 +442,35 @@ attn_split_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
   uint16_t *o_out = static_cast<uint16_t *>(p.o_part) + set * p.o_set_stride + (int64_t)head * p.m * out_ld + split * DH;
   uint16_t *r_out = static_cast<uint16_t *>(p.r_part) + set * p.r_set_stride + (int64_t)head * p.m * p.splits + split;
   // warp index = (tile group * groups + row group) * 4 + slice: sum over tile groups and slices.
-  // pairs of adjacent columns -> one 32-bit store
-  for (int i = tid; i < groups * rows_scratch * (DH / 2); i += blockDim.x) {
-    int c = (i % (DH / 2)) * 2, lr = (i / (DH / 2)) % rows_scratch, gr = i / ((DH / 2) * rows_scratch);
-    int row = gr * rows_per_group + lr;
-    if (row >= p.m) continue;
-    acc_t a0 = 0, a1 = 0;
-    for (int tg = 0; tg < p.tile_groups; tg++)
+  // A thread keeps one pair of adjacent columns (one 32-bit store) and walks down the rows.
+  {
+    int const c = (tid % (DH / 2)) * 2, row_step = blockDim.x / (DH / 2);
+    size_t const warp_pitch = (size_t)rows_scratch * ld;
+    for (int gr = 0; gr < groups; gr++)
+      for (int lr = tid / (DH / 2); lr < rows_scratch; lr += row_step) {
+        int row = gr * rows_per_group + lr;
+        if (row >= p.m) break;
+        acc_t a0 = 0, a1 = 0;
+        for (int tg = 0; tg < p.tile_groups; tg++) {
+          acc_t const *src = scratch + (size_t)((tg * groups + gr) * 4) * warp_pitch + lr * ld + c;
 #pragma unroll
-      for (int sl = 0; sl < 4; sl++) {
-        acc_t const *src = scratch + (size_t)((tg * groups + gr) * 4 + sl) * rows_scratch * ld + lr * ld + c;
-        if (MODE == kFingerprint) { // partials are already reduced modulo PQ: no overflow for any count
-          a0 = (acc_t)(((uint32_t)a0 + (uint32_t)src[0]) % PQ);
-          a1 = (acc_t)(((uint32_t)a1 + (uint32_t)src[1]) % PQ);
-        } else {
-          a0 += src[0];
-          a1 += src[1];
+          for (int sl = 0; sl < 4; sl++) {
+            if (MODE == kFingerprint) { // partials are already reduced modulo PQ: no overflow for any count
+              a0 = (acc_t)((uint32_t)a0 + (uint32_t)src[sl * warp_pitch]);
+              a1 = (acc_t)((uint32_t)a1 + (uint32_t)src[sl * warp_pitch + 1]);
+            } else {
+              a0 += src[sl * warp_pitch];
+              a1 += src[sl * warp_pitch + 1];
+            }
+          }
+          if (MODE == kFingerprint) { a0 = (acc_t)((uint32_t)a0 % PQ); a1 = (acc_t)((uint32_t)a1 % PQ); }
         }
+        uint32_t packed;
+        if (MODE == kFingerprint) packed = (uint32_t)a0 | ((uint32_t)a1 << 16);
+        else if (MODE == kF16) packed = pack_f16((float)a0, (float)a1);
+        else packed = pack_bf16((float)a0, (float)a1);
+        *reinterpret_cast<uint32_t *>(o_out + (size_t)row * out_ld + c) = packed;
       }
-    uint32_t packed;
-    if (MODE == kFingerprint) packed = ((uint32_t)a0 % PQ) | (((uint32_t)a1 % PQ) << 16);
-    else if (MODE == kF16) packed = pack_f16((float)a0, (float)a1);
-    else packed = pack_bf16((float)a0, (float)a1);
-    *reinterpret_cast<uint32_t *>(o_out + (size_t)row * out_ld + c) = packed;
   }
   for (int i = tid; i < groups * rows_scratch; i += blockDim.x) {
     int lr = i % rows_scratch, gr = i / rows_scratch, row = gr * rows_per_group + lr;
@@ -492,33 +505,41 @@ attn_split_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
       uint16_t const *op = static_cast<uint16_t const *>(p.o_part) + set * p.o_set_stride + (int64_t)head * p.m * out_ld;
       uint16_t const *rp = static_cast<uint16_t const *>(p.r_part) + set * p.r_set_stride + (int64_t)head * p.m * p.splits;
       uint16_t *dst = static_cast<uint16_t *>(p.merged_out) + set * p.merged_set_stride + (int64_t)head * p.m * DH;
-      for (int i = tid; i < p.m * DH; i += blockDim.x) {
-        int r = i / DH, c = i % DH;
+      // one pair of adjacent columns per thread and pass: 32-bit loads of the partials, one 32-bit store
+      for (int i = tid; i < p.m * (DH / 2); i += blockDim.x) {
+        int r = i / (DH / 2), c = (i % (DH / 2)) * 2;
+        uint16_t const *orow = op + (size_t)r * out_ld + c, *rrow = rp + r * p.splits;
+        uint32_t packed;
         if (MODE == kFingerprint) {
-          uint32_t num = 0, den = 0;
+          uint32_t num0 = 0, num1 = 0, den = 0;
 #pragma unroll 8
           for (int sp = 0; sp < p.splits; sp++) {
-            num += __ldcg(op + (size_t)r * out_ld + sp * DH + c);
-            den += __ldcg(rp + r * p.splits + sp);
+            uint32_t w = __ldcg(reinterpret_cast<uint32_t const *>(orow + sp * DH));
+            num0 += w & 0xFFFFu;
+            num1 += w >> 16;
+            den += __ldcg(rrow + sp);
           }
-          dst[i] = (uint16_t)field_div(num % PQ, den % PQ);
+          den %= PQ;
+          packed = (uint32_t)field_div(num0 % PQ, den) | ((uint32_t)field_div(num1 % PQ, den) << 16);
         } else {
-          float num = 0.f, den = 0.f;
+          float num0 = 0.f, num1 = 0.f, den = 0.f;
 #pragma unroll 8
           for (int sp = 0; sp < p.splits; sp++) {
-            uint16_t a = __ldcg(op + (size_t)r * out_ld + sp * DH + c), bb = __ldcg(rp + r * p.splits + sp);
+            uint32_t w = __ldcg(reinterpret_cast<uint32_t const *>(orow + sp * DH));
+            uint16_t bb = __ldcg(rrow + sp);
             if (MODE == kF16) {
-              num += __half2float(*reinterpret_cast<__half const *>(&a));
+              float2 f = __half22float2(*reinterpret_cast<__half2 const *>(&w));
+              num0 += f.x; num1 += f.y;
               den += __half2float(*reinterpret_cast<__half const *>(&bb));
             } else {
-              num += __bfloat162float(*reinterpret_cast<__nv_bfloat16 const *>(&a));
+              float2 f = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162 const *>(&w));
+              num0 += f.x; num1 += f.y;
               den += __bfloat162float(*reinterpret_cast<__nv_bfloat16 const *>(&bb));
             }
           }
-          float v = num / den;
-          if (MODE == kF16) { __half h = __float2half_rn(v); dst[i] = *reinterpret_cast<uint16_t *>(&h); }
-          else { __nv_bfloat16 h = __float2bfloat16_rn(v); dst[i] = *reinterpret_cast<uint16_t *>(&h); }
+          packed = MODE == kF16 ? pack_f16(num0 / den, num1 / den) : pack_bf16(num0 / den, num1 / den);
         }
+        *reinterpret_cast<uint32_t *>(dst + (size_t)r * DH + c) = packed;
       }
       if (tid == 0) p.tickets[set * p.heads + head] = 0; // ready for the next launch
     }
