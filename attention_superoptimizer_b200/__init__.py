@@ -213,12 +213,46 @@ class PyTensor:
 class PyGraph:
     """kernel::Graph (reference: PyGraph, core.pyx:180-236) plus the customized-operator API."""
 
-    def __init__(self, runtime: Runtime = None):
+    def __init__(self, runtime: Runtime = None, _handle=None):
         self.rt = runtime or Runtime.get()
         self.lib = self.rt.lib
+        if _handle is None:
+            _handle = ctypes.c_void_p()
+            check(self.lib.mg_graph_create(self.rt.handle, ctypes.byref(_handle)))
+        self.handle = _handle
+
+    # -- graph JSON wire format (to_json / from_json, src/kernel/graph.cc:33-159) --------------------
+    @classmethod
+    def from_json(cls, document, runtime: Runtime = None):
+        """Rebuild a graph from the reference's JSON form: a list of operators as `json(graph)` prints it, e.g.
+        one entry of a search checkpoint's "generated_graphs".  `document` is the text or the parsed list."""
+        import json as _json
+        rt = runtime or Runtime.get()
+        text = document if isinstance(document, str) else _json.dumps(document)
         h = ctypes.c_void_p()
-        check(self.lib.mg_graph_create(self.rt.handle, ctypes.byref(h)))
-        self.handle = h
+        check(rt.lib.mg_graph_from_json(rt.handle, text.encode(), ctypes.byref(h)))
+        return cls(rt, _handle=h)
+
+    def to_json(self):
+        """`json(graph).dump()` of the reference (keys in alphabetical order)."""
+        need = ctypes.c_size_t()
+        self.lib.mg_graph_to_json(self.handle, None, 0, ctypes.byref(need))
+        buf = ctypes.create_string_buffer(need.value + 1)
+        check(self.lib.mg_graph_to_json(self.handle, buf, need.value + 1, ctypes.byref(need)))
+        return buf.value.decode()
+
+    def operator(self, op_idx):
+        """(KN operator type code, [output tensors]) of operator op_idx - the way to reach the tensors of a
+        graph that was loaded from JSON."""
+        t, n = ctypes.c_int32(), ctypes.c_int32()
+        outs = (mg_tensor * 8)()
+        check(self.lib.mg_graph_operator_info(self.handle, op_idx, ctypes.byref(t), outs, 8, ctypes.byref(n)))
+        tensors = []
+        for i in range(min(8, n.value)):
+            pod = mg_tensor()
+            ctypes.memmove(ctypes.byref(pod), ctypes.byref(outs[i]), ctypes.sizeof(mg_tensor))
+            tensors.append(PyTensor(self, pod))
+        return t.value, tensors
 
     def close(self):
         if self.handle is not None:

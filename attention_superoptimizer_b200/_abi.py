@@ -63,6 +63,9 @@ SIGNATURES = {
     "mg_graph_customized_info": (ctypes.c_int, [_P, _I, ctypes.POINTER(_I), ctypes.POINTER(_I), ctypes.POINTER(_I),
                                                 ctypes.POINTER(_I)]),
     "mg_graph_customized_program": (ctypes.c_int, [_P, _I, _P, ctypes.c_size_t]),
+    "mg_graph_to_json": (ctypes.c_int, [_P, ctypes.c_char_p, ctypes.c_size_t, ctypes.POINTER(ctypes.c_size_t)]),
+    "mg_graph_from_json": (ctypes.c_int, [_P, ctypes.c_char_p, ctypes.POINTER(_P)]),
+    "mg_graph_operator_info": (ctypes.c_int, [_P, _I, ctypes.POINTER(_I), _T, _I, ctypes.POINTER(_I)]),
     "mg_graph_customized_set_causal_window": (ctypes.c_int, [_P, _I, _I]),
     "mg_op_fingerprint": (ctypes.c_int, [_P, _I]),
     "mg_graph_fingerprint": (ctypes.c_int, [_P]),

@@ -2,6 +2,7 @@
 // validates its arguments, converts between the POD structs and the C++ objects, and forwards.
 #include "mirage/kernel/device_memory_manager.h"
 #include "mirage/kernel/graph.h"
+#include "mirage/utils/json_utils.h"
 #include "mugraph.h"
 #include "status.h"
 #include <cstring>
@@ -264,6 +265,39 @@ int mg_graph_reduction(mg_graph *g, const mg_tensor *a, int32_t dim, int32_t siz
 int mg_graph_num_operators(mg_graph *g, int32_t *n) {
   if (!g || !n) return fail(MG_ERR_INVALID_ARGUMENT, "null argument");
   *n = (int)g->graph.operators.size();
+  return MG_OK;
+}
+
+int mg_graph_to_json(mg_graph *g, char *buf, size_t capacity, size_t *length) {
+  if (!g || !length) return fail(MG_ERR_INVALID_ARGUMENT, "null argument");
+  std::string text = kernel::to_json_string(g->graph);
+  *length = text.size();
+  if (!buf || capacity < text.size() + 1) return fail(MG_ERR_INVALID_ARGUMENT, "buffer too small for the JSON document");
+  std::memcpy(buf, text.c_str(), text.size() + 1);
+  return MG_OK;
+}
+
+int mg_graph_from_json(mg_runtime *rt, const char *text, mg_graph **out) {
+  if (!rt || !rt->dmm || !text || !out) return fail(MG_ERR_INVALID_ARGUMENT, "null argument");
+  *out = nullptr;
+  mg_graph *g = new (std::nothrow) mg_graph{rt, {}};
+  if (!g) return fail(MG_ERR_OUT_OF_MEMORY, "host allocation failed");
+  std::string err;
+  if (!kernel::from_json_string(text, g->graph, &err)) {
+    delete g; // releases what was built, in reverse order
+    return fail(MG_ERR_INVALID_GRAPH, err.c_str());
+  }
+  *out = g;
+  return MG_OK;
+}
+
+int mg_graph_operator_info(mg_graph *g, int32_t idx, int32_t *op_type, mg_tensor *outputs, int32_t max_outputs,
+                           int32_t *num_outputs) {
+  KNOperator *op = get_op(g, idx);
+  if (!op) return fail(MG_ERR_INVALID_ARGUMENT, "operator index out of range");
+  if (op_type) *op_type = (int32_t)op->op_type;
+  if (num_outputs) *num_outputs = (int32_t)op->output_tensors.size();
+  for (int i = 0; outputs && i < max_outputs && i < (int)op->output_tensors.size(); i++) to_pod(g, op->output_tensors[i], &outputs[i]);
   return MG_OK;
 }
 

@@ -160,6 +160,19 @@ int mg_graph_customized_program(mg_graph *g, int32_t op_idx, void *program_out, 
  * 0 switches the mask off.  Fingerprint mode ignores it. */
 int mg_graph_customized_set_causal_window(mg_graph *g, int32_t op_idx, int32_t window);
 
+/* ---- graph JSON wire format ------------------------------------------------
+ * replaces to_json(json&, Graph const&) / from_json(json const&, Graph&) (src/kernel/graph.cc:33-159) and the
+ * operators' `operator json()`; documents are exchanged as text (see include/mirage/utils/json_utils.h).
+ * mg_graph_to_json: writes at most `capacity` bytes (NUL included) and always reports the length needed
+ * (without NUL) in *length; MG_ERR_INVALID_ARGUMENT if the buffer is too small (call again with length + 1).
+ * mg_graph_from_json: builds a new graph from a document the reference or this library wrote; on failure no
+ * graph is left behind. */
+int mg_graph_to_json(mg_graph *g, char *buf, size_t capacity, size_t *length);
+int mg_graph_from_json(mg_runtime *rt, const char *text, mg_graph **g);
+/* type (MG_KN_* code) and output tensors of operator op_idx; at most max_outputs tensors are written */
+int mg_graph_operator_info(mg_graph *g, int32_t op_idx, int32_t *op_type, mg_tensor *outputs, int32_t max_outputs,
+                           int32_t *num_outputs);
+
 /* ---- the hot path ---------------------------------------------------------
  * KNOperator::fingerprint(), src/kernel/cuda/customized_kernel.cu:655-678 (and the
  * kernel-level ops' fingerprint()).  Synchronous like the reference. */

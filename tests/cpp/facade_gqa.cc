@@ -4,6 +4,7 @@
 // (no GPU): operators can be built and lowered, launching is refused.
 #include "mirage/kernel/device_memory_manager.h"
 #include "mirage/kernel/graph.h"
+#include "mirage/utils/json_utils.h"
 #include "mirage/threadblock/graph.h"
 #include <cstdio>
 #include <cstdlib>
@@ -91,6 +92,19 @@ int main() {
       CHECK(copy != nullptr && copy->output_tensors.size() == 2);
       CHECK(static_cast<kernel::KNCustomizedOp *>(copy)->plan.ops.size() == 4);
       delete copy;
+    }
+    // JSON wire format: dump, rebuild into a second graph, dump again
+    {
+      std::string doc = kernel::to_json_string(graph);
+      CHECK(doc.find("\"kn_customized_op\"") != std::string::npos && doc.find("\"tb_matmul_op\"") != std::string::npos);
+      kernel::Graph again;
+      std::string err;
+      CHECK(kernel::from_json_string(doc, again, &err));
+      CHECK(again.operators.size() == graph.operators.size());
+      auto *a = static_cast<kernel::KNCustomizedOp *>(again.operators[3]);
+      auto *b = static_cast<kernel::KNCustomizedOp *>(graph.operators[3]);
+      CHECK(a->bgraph.smem_offset == b->bgraph.smem_offset && a->output_tensors.size() == b->output_tensors.size());
+      CHECK(!kernel::from_json_string("[{\"op_type\": \"kn_matmul_op\"}]", again, &err) && !err.empty());
     }
     // no device: nothing can be computed here, and the library says so instead of falling back
     CHECK(graph.operators.back()->fingerprint() == false);
