@@ -1,0 +1,110 @@
+// Cross-split merge of one head, shared by the split-KV kernels: O = (sum over splits of O_part) / (sum over splits
+// of R_part)  - the second customized op of the reference's cpp_examples/group_query_attn_inc_decode.cc:80-103 -
+// done by the block that finished the head's last split.
+//
+// The partials were written by other SMs a moment ago, so every load is an L2 round trip: the work is arranged
+// for memory-level parallelism.  A thread owns 8 adjacent output columns of one row and issues the 16-byte loads
+// of up to 16 splits before it uses any of them; the row denominators are computed once, up front, into shared
+// memory instead of once per column group.
+#pragma once
+#include "common.cuh"
+
+namespace mgk {
+
+enum { kMergeF16 = 0, kMergeBF16 = 1, kMergeFingerprint = 2 };
+
+template <int KIND> __device__ __forceinline__ float merge_to_float(uint16_t v) {
+  if (KIND == kMergeBF16) return __bfloat162float(*reinterpret_cast<__nv_bfloat16 const *>(&v));
+  return __half2float(*reinterpret_cast<__half const *>(&v));
+}
+template <int KIND> __device__ __forceinline__ uint32_t merge_pack(float a, float b) {
+  if (KIND == kMergeBF16) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t *>(&h);
+  }
+  __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t *>(&h);
+}
+
+// op: [m][splits * D], rp: [m][splits], dst: [m][D] of one head; t / nt: index and count of the participating
+// threads; den_smem: at least m words of shared memory; sync(): barrier over the participating threads.
+template <int KIND, int D, typename Sync>
+__device__ __forceinline__ void merge_head(uint16_t const *op, uint16_t const *rp, uint16_t *dst, int m, int splits,
+                                           int t, int nt, uint32_t *den_smem, Sync sync) {
+  for (int r = t; r < m; r += nt) {
+    uint16_t const *row = rp + (size_t)r * splits;
+    if (KIND == kMergeFingerprint) {
+      uint32_t den = 0;
+#pragma unroll 8
+      for (int sp = 0; sp < splits; sp++) den += __ldcg(row + sp);
+      den_smem[r] = den % PQ;
+    } else {
+      float den = 0.f;
+#pragma unroll 8
+      for (int sp = 0; sp < splits; sp++) den += merge_to_float<KIND>(__ldcg(row + sp));
+      den_smem[r] = __float_as_uint(den);
+    }
+  }
+  sync();
+  constexpr int kGroups = D / 8;
+  size_t const out_ld = (size_t)splits * D;
+  for (int u = t; u < m * kGroups; u += nt) {
+    int const r = u / kGroups, c = (u % kGroups) * 8;
+    uint16_t const *src = op + (size_t)r * out_ld + c;
+    float facc[8];
+    uint32_t iacc[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) facc[i] = 0.f, iacc[i] = 0u;
+    auto add = [&](uint4 w) {
+      uint32_t const words[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+      for (int i = 0; i < 4; i++) {
+        if (KIND == kMergeFingerprint) {
+          iacc[2 * i] += words[i] & 0xFFFFu;
+          iacc[2 * i + 1] += words[i] >> 16;
+        } else {
+          facc[2 * i] += merge_to_float<KIND>((uint16_t)(words[i] & 0xFFFFu));
+          facc[2 * i + 1] += merge_to_float<KIND>((uint16_t)(words[i] >> 16));
+        }
+      }
+    };
+    int sp = 0;
+    for (; sp + 16 <= splits; sp += 16) { // sums of 65536 values < 25651 still fit 32 bits
+      uint4 w[16];
+#pragma unroll
+      for (int i = 0; i < 16; i++) w[i] = __ldcg(reinterpret_cast<uint4 const *>(src + (size_t)(sp + i) * D));
+#pragma unroll
+      for (int i = 0; i < 16; i++) add(w[i]);
+    }
+    for (; sp + 4 <= splits; sp += 4) {
+      uint4 w[4];
+#pragma unroll
+      for (int i = 0; i < 4; i++) w[i] = __ldcg(reinterpret_cast<uint4 const *>(src + (size_t)(sp + i) * D));
+#pragma unroll
+      for (int i = 0; i < 4; i++) add(w[i]);
+    }
+    for (; sp < splits; sp++) add(__ldcg(reinterpret_cast<uint4 const *>(src + (size_t)sp * D)));
+    uint32_t o[4];
+    if (KIND == kMergeFingerprint) {
+      uint32_t const den = den_smem[r];
+#pragma unroll
+      for (int i = 0; i < 4; i++) o[i] = field_div(iacc[2 * i] % PQ, den) | (field_div(iacc[2 * i + 1] % PQ, den) << 16);
+    } else {
+      float const den = __uint_as_float(den_smem[r]);
+#pragma unroll
+      for (int i = 0; i < 4; i++) o[i] = merge_pack<KIND>(facc[2 * i] / den, facc[2 * i + 1] / den);
+    }
+    *reinterpret_cast<uint4 *>(dst + (size_t)r * D + c) = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
+
+// Stand-alone merge launch (attn_split.cu): blocks of 128 threads take 8 query rows of one head each.  With
+// `after_previous_kernel` the launch uses programmatic stream serialisation: its blocks are scheduled while the
+// previous kernel of the stream drains and wait (griddepcontrol.wait) until that kernel's memory is visible.
+// kind: kMergeF16 / kMergeBF16 / kMergeFingerprint; d must be 64 or 128 (returns false otherwise, nothing launched).
+bool launch_merge_rows(int kind, int d, uint16_t const *o_part, uint16_t const *r_part, uint16_t *out, int heads, int m,
+                       int splits, int num_sets, long long o_set_stride, long long r_set_stride, long long out_set_stride,
+                       bool after_previous_kernel, void *stream);
+
+} // namespace mgk

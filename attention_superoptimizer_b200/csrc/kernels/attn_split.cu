@@ -28,10 +28,19 @@
 // Every mbarrier wait is bounded: a block that gives up records a code in the device status word and
 // returns without touching its outputs further.
 #include "common.cuh"
+#include "attn_merge.cuh"
 #include <cstdlib>
 #include <cuda.h>
 #include <mutex>
 #include <unordered_map>
+
+namespace mgk {
+namespace stc { // attn_split_tc.cu
+bool supported(mgd_attn_split const *p);
+int launch(mgd_attn_split const *p, void const *q, void const *k, void const *v, void *o, void *r,
+           mgd_attn_launch_opts const *opts, void *stream);
+} // namespace stc
+} // namespace mgk
 
 namespace mgk {
 
@@ -505,42 +514,10 @@ attn_split_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
       uint16_t const *op = static_cast<uint16_t const *>(p.o_part) + set * p.o_set_stride + (int64_t)head * p.m * out_ld;
       uint16_t const *rp = static_cast<uint16_t const *>(p.r_part) + set * p.r_set_stride + (int64_t)head * p.m * p.splits;
       uint16_t *dst = static_cast<uint16_t *>(p.merged_out) + set * p.merged_set_stride + (int64_t)head * p.m * DH;
-      // one pair of adjacent columns per thread and pass: 32-bit loads of the partials, one 32-bit store
-      for (int i = tid; i < p.m * (DH / 2); i += blockDim.x) {
-        int r = i / (DH / 2), c = (i % (DH / 2)) * 2;
-        uint16_t const *orow = op + (size_t)r * out_ld + c, *rrow = rp + r * p.splits;
-        uint32_t packed;
-        if (MODE == kFingerprint) {
-          uint32_t num0 = 0, num1 = 0, den = 0;
-#pragma unroll 8
-          for (int sp = 0; sp < p.splits; sp++) {
-            uint32_t w = __ldcg(reinterpret_cast<uint32_t const *>(orow + sp * DH));
-            num0 += w & 0xFFFFu;
-            num1 += w >> 16;
-            den += __ldcg(rrow + sp);
-          }
-          den %= PQ;
-          packed = (uint32_t)field_div(num0 % PQ, den) | ((uint32_t)field_div(num1 % PQ, den) << 16);
-        } else {
-          float num0 = 0.f, num1 = 0.f, den = 0.f;
-#pragma unroll 8
-          for (int sp = 0; sp < p.splits; sp++) {
-            uint32_t w = __ldcg(reinterpret_cast<uint32_t const *>(orow + sp * DH));
-            uint16_t bb = __ldcg(rrow + sp);
-            if (MODE == kF16) {
-              float2 f = __half22float2(*reinterpret_cast<__half2 const *>(&w));
-              num0 += f.x; num1 += f.y;
-              den += __half2float(*reinterpret_cast<__half const *>(&bb));
-            } else {
-              float2 f = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162 const *>(&w));
-              num0 += f.x; num1 += f.y;
-              den += __bfloat162float(*reinterpret_cast<__nv_bfloat16 const *>(&bb));
-            }
-          }
-          packed = MODE == kF16 ? pack_f16(num0 / den, num1 / den) : pack_bf16(num0 / den, num1 / den);
-        }
-        *reinterpret_cast<uint32_t *>(dst + (size_t)r * DH + c) = packed;
-      }
+      // the stage memory is free by now (every warp passed the barriers above): it holds the row denominators
+      constexpr int kKind = MODE == kFingerprint ? kMergeFingerprint : (MODE == kBF16 ? kMergeBF16 : kMergeF16);
+      merge_head<kKind, DH>(op, rp, dst, p.m, p.splits, tid, (int)blockDim.x, reinterpret_cast<uint32_t *>(smem),
+                            [] { __syncthreads(); });
       if (tid == 0) p.tickets[set * p.heads + head] = 0; // ready for the next launch
     }
   }
@@ -584,6 +561,58 @@ __global__ void __launch_bounds__(256) attn_merge_kernel(uint16_t const *o_part,
       else { __nv_bfloat16 h = __float2bfloat16_rn(v); dst[i] = *reinterpret_cast<uint16_t *>(&h); }
     }
   }
+}
+
+// ---- merge, 8 query rows of one head per block --------------------------------------------------------------------
+constexpr int kMergeRowsPerBlock = 8;
+template <int KIND, int D>
+__global__ void __launch_bounds__(128) attn_merge_rows_kernel(uint16_t const *o_part, uint16_t const *r_part, uint16_t *out,
+                                                              int heads, int m, int splits, long long o_stride,
+                                                              long long r_stride, long long out_stride) {
+  __shared__ uint32_t den[kMergeRowsPerBlock];
+  asm volatile("griddepcontrol.wait;" ::: "memory"); // no-op unless launched with programmatic serialisation
+  int const chunks = (m + kMergeRowsPerBlock - 1) / kMergeRowsPerBlock;
+  int const chunk = blockIdx.x % chunks, bh = blockIdx.x / chunks, head = bh % heads;
+  long long const set = bh / heads;
+  int const r0 = chunk * kMergeRowsPerBlock, rows = m - r0 < kMergeRowsPerBlock ? m - r0 : kMergeRowsPerBlock;
+  uint16_t const *op = o_part + set * o_stride + ((long long)head * m + r0) * splits * D;
+  uint16_t const *rp = r_part + set * r_stride + ((long long)head * m + r0) * splits;
+  uint16_t *dst = out + set * out_stride + ((long long)head * m + r0) * D;
+  merge_head<KIND, D>(op, rp, dst, rows, splits, (int)threadIdx.x, 128, den, [] { __syncthreads(); });
+}
+
+template <int KIND, int D>
+static void launch_merge_rows_t(uint16_t const *o_part, uint16_t const *r_part, uint16_t *out, int heads, int m, int splits,
+                                int num_sets, long long os, long long rs, long long outs, bool pdl, void *stream) {
+  cudaLaunchConfig_t cfg = {};
+  int const chunks = (m + kMergeRowsPerBlock - 1) / kMergeRowsPerBlock;
+  cfg.gridDim = dim3((unsigned)(heads * num_sets * chunks), 1, 1);
+  cfg.blockDim = dim3(128, 1, 1);
+  cfg.stream = (cudaStream_t)stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  if (pdl) {
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+  }
+  cudaLaunchKernelEx(&cfg, attn_merge_rows_kernel<KIND, D>, o_part, r_part, out, heads, m, splits, os, rs, outs);
+}
+
+bool launch_merge_rows(int kind, int d, uint16_t const *o_part, uint16_t const *r_part, uint16_t *out, int heads, int m,
+                       int splits, int num_sets, long long os, long long rs, long long outs, bool pdl, void *stream) {
+  if (d != 64 && d != 128) return false;
+#define MG_MERGE_CASE(K)                                                                                           \
+  if (kind == K) {                                                                                                   \
+    if (d == 128) launch_merge_rows_t<K, 128>(o_part, r_part, out, heads, m, splits, num_sets, os, rs, outs, pdl, stream); \
+    else launch_merge_rows_t<K, 64>(o_part, r_part, out, heads, m, splits, num_sets, os, rs, outs, pdl, stream);         \
+    return true;                                                                                                     \
+  }
+  MG_MERGE_CASE(kMergeF16)
+  MG_MERGE_CASE(kMergeBF16)
+  MG_MERGE_CASE(kMergeFingerprint)
+#undef MG_MERGE_CASE
+  return false;
 }
 
 // ---- host side ------------------------------------------------------------------------------------------------
@@ -819,10 +848,20 @@ int mgd_attn_split_supported(const mgd_attn_split *p, int32_t fingerprint_mode) 
   return shape_supported(p, fingerprint_mode != 0) && encode_fn() != nullptr ? 1 : 0;
 }
 
+// Which engine runs a float launch: with more than 8 query rows the mma.sync path is bound by the legacy tensor
+// pipe and the tcgen05 kernel (attn_split_tc.cu) takes over where it supports the shape.
+// MUGRAPH_ATTN_TC=0 / 1 forces the choice (tuning, tests).
+static bool use_tensor_memory_kernel(mgd_attn_split const *p) {
+  if (!stc::supported(p)) return false;
+  if (char const *e = getenv("MUGRAPH_ATTN_TC")) return atoi(e) != 0;
+  return p->m > 8;
+}
+
 int mgd_launch_attn_split_float_ex(const mgd_attn_split *p, const void *q, const void *k, const void *v, void *o,
                                    void *r, const mgd_attn_launch_opts *opts, void *stream) {
   if (!q || !k || !v || !o || !r) return set_error(MG_ERR_INVALID_ARGUMENT, "split-KV attention: null tensor");
   if (!shape_supported(p, false)) return set_error(MG_ERR_UNSUPPORTED, "split-KV attention: shape not supported");
+  if (use_tensor_memory_kernel(p)) return stc::launch(p, q, k, v, o, r, opts, stream);
   if (p->data_type == MG_DT_FLOAT16)
     return p->d == 128 ? launch_split<kF16, 128>(p, q, k, v, o, r, opts, stream) : launch_split<kF16, 64>(p, q, k, v, o, r, opts, stream);
   return p->d == 128 ? launch_split<kBF16, 128>(p, q, k, v, o, r, opts, stream) : launch_split<kBF16, 64>(p, q, k, v, o, r, opts, stream);
@@ -852,6 +891,11 @@ int mgd_attn_merge_supported(const mgd_attn_merge *p, int32_t) {
 
 int mgd_launch_attn_merge_float(const mgd_attn_merge *p, const void *o_part, const void *r_part, void *out, void *stream) {
   if (!p || !o_part || !r_part || !out || p->num_sets <= 0) return set_error(MG_ERR_INVALID_ARGUMENT, "attention merge: bad argument");
+  if (p->data_type == MG_DT_FLOAT16 || p->data_type == MG_DT_BFLOAT16)
+    if (launch_merge_rows(p->data_type == MG_DT_BFLOAT16 ? kMergeBF16 : kMergeF16, p->d, (uint16_t const *)o_part,
+                          (uint16_t const *)r_part, (uint16_t *)out, p->heads, p->m, p->splits, p->num_sets,
+                          p->o_part_set_stride, p->r_part_set_stride, p->out_set_stride, false, stream))
+      return check_launch("attn_merge_rows_kernel");
   unsigned blocks = (unsigned)(p->heads * p->num_sets);
   if (p->data_type == MG_DT_FLOAT16)
     attn_merge_kernel<kF16><<<blocks, 256, 0, (cudaStream_t)stream>>>((uint16_t const *)o_part, (uint16_t const *)r_part, (uint16_t *)out,
@@ -866,6 +910,9 @@ int mgd_launch_attn_merge_float(const mgd_attn_merge *p, const void *o_part, con
 
 int mgd_launch_attn_merge_fingerprint(const mgd_attn_merge *p, const uint16_t *o_part, const uint16_t *r_part, uint16_t *out, void *stream) {
   if (!p || !o_part || !r_part || !out || p->num_sets <= 0) return set_error(MG_ERR_INVALID_ARGUMENT, "attention merge: bad argument");
+  if (launch_merge_rows(kMergeFingerprint, p->d, o_part, r_part, out, p->heads, p->m, p->splits, p->num_sets,
+                        p->o_part_set_stride, p->r_part_set_stride, p->out_set_stride, false, stream))
+    return check_launch("attn_merge_rows_kernel");
   unsigned blocks = (unsigned)(p->heads * p->num_sets);
   attn_merge_kernel<kFingerprint><<<blocks, 256, 0, (cudaStream_t)stream>>>(o_part, r_part, out, p->heads, p->m, p->d, p->splits,
                                                                             p->o_part_set_stride, p->r_part_set_stride, p->out_set_stride);

@@ -419,10 +419,36 @@ def run_fingerprint_sweep(args, mg, mo, fp_oracle, rt, torch, dist, np, rank, wo
             "kernel_op1": info["kernel_fingerprint"], "oracle_checked_sets": checked, "bit_exact": bool(ok)}
 
 
-def measure_other_configs(mg, rt, stream, timed, peaks):
+def run_one_config(args):
+    """`--only-config`: one of the other BASELINE configs alone (profiling, tuning); prints {"other_configs": {...}}."""
+    import torch
+    import attention_superoptimizer_b200 as mg
+
+    torch.cuda.set_device(0)
+    rt = mg.Runtime.get(device=0, arena_bytes=3 << 30)
+    rt.set_specialisation(not args.interpreter_only)
+    stream = torch.cuda.Stream()
+
+    def timed(fn, steps, warmup):
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(steps):
+            fn()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1)
+
+    out = measure_other_configs(mg, rt, stream, timed, load_peaks()[0], only=args.only_config)
+    print(json.dumps({"other_configs": out}))
+
+
+def measure_other_configs(mg, rt, stream, timed, peaks, only=None):
     """Device-timed numbers for the remaining BASELINE configs (N = 1 only), each replayed from a CUDA graph:
     config 3 (speculative decode with the causal draft window, fp16), config 4 (dense prefill, bf16, tcgen05)
-    and config 1 (matmul chain; fingerprint mode on the generic interpreter - no float kernel fits it yet)."""
+    and config 1 (matmul chain, both modes on the generic interpreters).  `only` = "c1" | "c3" | "c4" runs one."""
     sh = stream.cuda_stream
     out = {}
 
@@ -431,76 +457,90 @@ def measure_other_configs(mg, rt, stream, timed, peaks):
             g.run(stream=sh, sync=False)
         stream.synchronize()
         seq = mg.CapturedSequence(sh, lambda: [graphs[i % len(graphs)].run(stream=sh, sync=False) for i in range(reps)])
-        ms = timed(seq.launch, 5, 3) / 5
+        # the clocks of an idle GPU take a while to come up: replay untimed for 0.3 s, then time 20 replays
+        t_end = time.perf_counter() + 0.3
+        while time.perf_counter() < t_end:
+            for _ in range(10):
+                seq.launch()
+            stream.synchronize()
+        ms = timed(seq.launch, 20, 3) / 20
         seq.close()
         return ms * 1000.0 / reps
 
     # ---- config 3: batch 4 x 8 KV heads = 32 units, 8 draft tokens x group 4 = 32 rows, KV 8192 -------------
-    units, rows, d, kv, splits, fr, window = 32, 32, 128, 8192, 16, 8, 8
-    graphs = []
-    for s in range(2):  # two buffer sets of 135 MB each: consecutive calls never share L2 contents
-        g = mg.PyGraph(rt)
-        Q = g.new_input((units, rows, d)); K = g.new_input((units, d, kv), layout=mg.DmemColumnMajor)
-        V = g.new_input((units, kv, d), layout=mg.DmemRowMajor)
-        p1, p2 = mg.gqa_decode_plans(units, rows, d, kv, splits, fr)
-        parts = g.customized([Q, K, V], p1); g.customized(parts, p2)
-        g.set_causal_window(3, window)
-        Q.fill_data_seeded(900 + s, d ** -0.5); K.fill_data_seeded(910 + s, 1.0); V.fill_data_seeded(920 + s, 1.0)
-        graphs.append(g)
-    us = replay_us(graphs, 8)
-    nbytes = 2 * units * rows * d * 2 + 2 * units * d * kv * 2
-    out["spec_decode_c3"] = {"us_per_call": round(us, 2), "hbm_gbs": round(nbytes / us / 1e3, 1),
-                             "frac_of_hbm_peak": round(nbytes / us / 1e3 / peaks["hbm_gbs"], 4), "bytes": nbytes,
-                             "kernel": graphs[0].customized_info(3)["kernel_float"], "dtype": "fp16",
-                             "note": "32 rows x KV 8192, 16 splits x for-loop 8, causal draft window 8, fused merge"}
-    for g in reversed(graphs):
-        g.close()
+    def config3():
+        units, rows, d, kv, splits, fr, window = 32, 32, 128, 8192, 16, 8, 8
+        graphs = []
+        for s in range(2):  # two buffer sets of 135 MB each: consecutive calls never share L2 contents
+            g = mg.PyGraph(rt)
+            Q = g.new_input((units, rows, d)); K = g.new_input((units, d, kv), layout=mg.DmemColumnMajor)
+            V = g.new_input((units, kv, d), layout=mg.DmemRowMajor)
+            p1, p2 = mg.gqa_decode_plans(units, rows, d, kv, splits, fr)
+            parts = g.customized([Q, K, V], p1); g.customized(parts, p2)
+            g.set_causal_window(3, window)
+            Q.fill_data_seeded(900 + s, d ** -0.5); K.fill_data_seeded(910 + s, 1.0); V.fill_data_seeded(920 + s, 1.0)
+            graphs.append(g)
+        us = replay_us(graphs, 8)
+        nbytes = 2 * units * rows * d * 2 + 2 * units * d * kv * 2
+        out["spec_decode_c3"] = {"us_per_call": round(us, 2), "hbm_gbs": round(nbytes / us / 1e3, 1),
+                                 "frac_of_hbm_peak": round(nbytes / us / 1e3 / peaks["hbm_gbs"], 4), "bytes": nbytes,
+                                 "kernel": graphs[0].customized_info(3)["kernel_float"], "dtype": "fp16",
+                                 "note": "32 rows x KV 8192, 16 splits x for-loop 8, causal draft window 8, fused merge"}
+        for g in reversed(graphs):
+            g.close()
 
     # ---- config 4: 32 heads, 2048 x 2048, head_dim 128, bf16 ----------------------------------------------------
-    H, SQ, L = 32, 2048, 2048
-    g = mg.PyGraph(rt)
-    Q = g.new_input((H, SQ, d), mg.bfloat16); K = g.new_input((H, d, L), mg.bfloat16, mg.DmemColumnMajor)
-    V = g.new_input((H, L, d), mg.bfloat16, mg.DmemColumnMajor)
-    p1, p2 = mg.attention_prefill_plans(H, SQ, d, L)
-    acc = g.customized([Q, K, V], p1); g.customized(acc, p2)
-    Q.fill_data_seeded(930, d ** -0.5); K.fill_data_seeded(931, 1.0); V.fill_data_seeded(932, 1.0)
-    us = replay_us([g], 10)
-    flops = 4.0 * H * SQ * L * d
-    out["prefill_c4"] = {"us_per_call": round(us, 2), "tflops": round(flops / us / 1e6, 1),
-                         "frac_of_bf16_peak": round(flops / us / 1e6 / peaks["bf16_tflops"], 4), "flops": flops,
-                         "kernel": g.customized_info(3)["kernel_float"], "dtype": "bf16",
-                         "note": "both customized ops in one launch (division fused into the tcgen05 kernel's epilogue)"}
-    g.close()
+    def config4():
+        d = 128
+        H, SQ, L = 32, 2048, 2048
+        g = mg.PyGraph(rt)
+        Q = g.new_input((H, SQ, d), mg.bfloat16); K = g.new_input((H, d, L), mg.bfloat16, mg.DmemColumnMajor)
+        V = g.new_input((H, L, d), mg.bfloat16, mg.DmemColumnMajor)
+        p1, p2 = mg.attention_prefill_plans(H, SQ, d, L)
+        acc = g.customized([Q, K, V], p1); g.customized(acc, p2)
+        Q.fill_data_seeded(930, d ** -0.5); K.fill_data_seeded(931, 1.0); V.fill_data_seeded(932, 1.0)
+        us = replay_us([g], 10)
+        flops = 4.0 * H * SQ * L * d
+        out["prefill_c4"] = {"us_per_call": round(us, 2), "tflops": round(flops / us / 1e6, 1),
+                             "frac_of_bf16_peak": round(flops / us / 1e6 / peaks["bf16_tflops"], 4), "flops": flops,
+                             "kernel": g.customized_info(3)["kernel_float"], "dtype": "bf16",
+                             "note": "both customized ops in one launch (division fused into the tcgen05 kernel's epilogue)"}
+        g.close()
 
     # ---- config 1: X[16,1024] W1[1024,1024] W2[1024,1024], fingerprint mode, generic interpreter -------------------
-    g = mg.PyGraph(rt)
-    X = g.new_input((16, 1024)); W1 = g.new_input((1024, 1024)); W2 = g.new_input((1024, 1024))
-    chain = mg.ExecutionPlan(ops=[(mg.TB_MATMUL_OP, [(0, 0), (1, 0)]), (mg.TB_MATMUL_OP, [(3, 0), (2, 0)])],
-                             input_map=[(-1, -1, -1), (1, -1, -1), (0, -1, -1)], forloop_dim=[1, 0, -1],
-                             input_smem_layouts=[mg.SmemRowMajor] * 3, output_map=(1, -1, -1), forloop_range=16,
-                             grid_dim=(16, 1, 1), reduction_dimx=1024)
-    part = g.customized([X, W1, W2], chain)
-    reduce_plan = mg.ExecutionPlan(ops=[(mg.TB_REDUCTION_1_TO_DIMX_OP, [(0, 0)])], input_map=[(0, -1, -1)],
-                                   forloop_dim=[-1], input_smem_layouts=[mg.SmemRowMajor], output_map=(0, -1, -1),
-                                   forloop_range=1, grid_dim=(16, 1, 1), reduction_dimx=1024)
-    g.customized(part, reduce_plan)
-    for t, sd in ((X, 940), (W1, 941), (W2, 942)):
-        t.fill_fingerprint_seeded(sd, mg.FP_P)
-    g.fingerprint()
-    import time as _t
-    t0 = _t.perf_counter()
-    for _ in range(20):
+    def config1():
+        g = mg.PyGraph(rt)
+        X = g.new_input((16, 1024)); W1 = g.new_input((1024, 1024)); W2 = g.new_input((1024, 1024))
+        chain = mg.ExecutionPlan(ops=[(mg.TB_MATMUL_OP, [(0, 0), (1, 0)]), (mg.TB_MATMUL_OP, [(3, 0), (2, 0)])],
+                                 input_map=[(-1, -1, -1), (1, -1, -1), (0, -1, -1)], forloop_dim=[1, 0, -1],
+                                 input_smem_layouts=[mg.SmemRowMajor] * 3, output_map=(1, -1, -1), forloop_range=16,
+                                 grid_dim=(16, 1, 1), reduction_dimx=1024)
+        part = g.customized([X, W1, W2], chain)
+        reduce_plan = mg.ExecutionPlan(ops=[(mg.TB_REDUCTION_1_TO_DIMX_OP, [(0, 0)])], input_map=[(0, -1, -1)],
+                                       forloop_dim=[-1], input_smem_layouts=[mg.SmemRowMajor], output_map=(0, -1, -1),
+                                       forloop_range=1, grid_dim=(16, 1, 1), reduction_dimx=1024)
+        g.customized(part, reduce_plan)
+        for t, sd in ((X, 940), (W1, 941), (W2, 942)):
+            t.fill_fingerprint_seeded(sd, mg.FP_P)
         g.fingerprint()
-    fp_us = (_t.perf_counter() - t0) / 20 * 1e6
-    X.fill_data_seeded(943, 1.0); W1.fill_data_seeded(944, 1.0 / 32); W2.fill_data_seeded(945, 1.0 / 32)
-    float_us = replay_us([g], 10)
-    out["matmul_chain_c1"] = {"float_us_per_call": round(float_us, 1), "fingerprint_us_per_call": round(fp_us, 1),
-                              "kernel": g.customized_info(3)["kernel_fingerprint"], "dtype": "fp16",
-                              "bytes": 4259840, "flops": 67108864,
-                              "note": "two customized ops (16 blocks over the intermediate columns, for-loop 16 over K "
-                                      "tiles of 64; then the cross-block reduction), generic interpreters; float: CUDA "
-                                      "graph replay; fingerprint: host-synchronised calls"}
-    g.close()
+        import time as _t
+        t0 = _t.perf_counter()
+        for _ in range(20):
+            g.fingerprint()
+        fp_us = (_t.perf_counter() - t0) / 20 * 1e6
+        X.fill_data_seeded(943, 1.0); W1.fill_data_seeded(944, 1.0 / 32); W2.fill_data_seeded(945, 1.0 / 32)
+        float_us = replay_us([g], 10)
+        out["matmul_chain_c1"] = {"float_us_per_call": round(float_us, 1), "fingerprint_us_per_call": round(fp_us, 1),
+                                  "kernel": g.customized_info(3)["kernel_fingerprint"], "dtype": "fp16",
+                                  "bytes": 4259840, "flops": 67108864,
+                                  "note": "two customized ops (16 blocks over the intermediate columns, for-loop 16 over K "
+                                          "tiles of 64; then the cross-block reduction), generic interpreters; float: CUDA "
+                                          "graph replay; fingerprint: host-synchronised calls"}
+        g.close()
+
+    for name, fn in (("c3", config3), ("c4", config4), ("c1", config1)):
+        if only in (None, name):
+            fn()
     return out
 
 
@@ -605,10 +645,14 @@ def main():
     ap.add_argument("--interpreter-only", action="store_true", help="disable the specialised kernels")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-other-configs", action="store_true", help="skip the extra measurements of configs 1, 3 and 4")
+    ap.add_argument("--only-config", default=None, choices=["c1", "c3", "c4"],
+                    help="measure just this other config on one GPU and print its entry (no headline line)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
         run_reference(args)
+    elif args.only_config:
+        run_one_config(args)
     else:
         run_ours(args)
 

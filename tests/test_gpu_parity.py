@@ -182,7 +182,10 @@ def float_inputs(rng, B, M, D, L, kl, vl, dtype):
 @pytest.mark.parametrize("layouts", [(mg.DmemColumnMajor, mg.DmemColumnMajor), (mg.DmemRowMajor, mg.DmemRowMajor),
                                      (mg.DmemColumnMajor, mg.DmemRowMajor)], ids=["kc_vc", "kr_vr", "kc_vr"])
 @pytest.mark.parametrize("shape", [(2, 4, 128, 1024, 4, 4), (2, 8, 64, 512, 2, 4), (1, 32, 128, 1024, 4, 2),
-                                   (3, 1, 32, 96, 3, 2), (2, 20, 128, 2048, 2, 16), (1, 7, 64, 1024, 2, 8)])
+                                   (3, 1, 32, 96, 3, 2), (2, 20, 128, 2048, 2, 16), (1, 7, 64, 1024, 2, 8),
+                                   # 176 (head, split) work items of four 128-wide tiles: more items than SMs, so
+                                   # the persistent tensor-memory kernel walks several items per block
+                                   (11, 24, 128, 8192, 16, 8)])
 def test_float_gqa_vs_fp32_oracle(rt, shape, layouts, dtype):
     B, M, D, L, S, F = shape
     kl, vl = layouts
