@@ -4,8 +4,7 @@
 //
 // The partials were written by other SMs a moment ago, so every load is an L2 round trip: the work is arranged
 // for memory-level parallelism.  A thread owns 8 adjacent output columns of one row and issues the 16-byte loads
-// of up to 16 splits before it uses any of them; the row denominators are computed once, up front, into shared
-// memory instead of once per column group.
+// of up to 16 splits - and of its row's denominators - before it uses any of them.
 #pragma once
 #include "common.cuh"
 
@@ -27,32 +26,20 @@ template <int KIND> __device__ __forceinline__ uint32_t merge_pack(float a, floa
 }
 
 // op: [m][splits * D], rp: [m][splits], dst: [m][D] of one head; t / nt: index and count of the participating
-// threads; den_smem: at least m words of shared memory; sync(): barrier over the participating threads.
-template <int KIND, int D, typename Sync>
+// threads.  Every thread also sums its row's denominators itself (a few 16-byte loads that travel with the others):
+// one L2 round trip per 16 splits, no barrier.
+template <int KIND, int D>
 __device__ __forceinline__ void merge_head(uint16_t const *op, uint16_t const *rp, uint16_t *dst, int m, int splits,
-                                           int t, int nt, uint32_t *den_smem, Sync sync) {
-  for (int r = t; r < m; r += nt) {
-    uint16_t const *row = rp + (size_t)r * splits;
-    if (KIND == kMergeFingerprint) {
-      uint32_t den = 0;
-#pragma unroll 8
-      for (int sp = 0; sp < splits; sp++) den += __ldcg(row + sp);
-      den_smem[r] = den % PQ;
-    } else {
-      float den = 0.f;
-#pragma unroll 8
-      for (int sp = 0; sp < splits; sp++) den += merge_to_float<KIND>(__ldcg(row + sp));
-      den_smem[r] = __float_as_uint(den);
-    }
-  }
-  sync();
+                                           int t, int nt) {
   constexpr int kGroups = D / 8;
   size_t const out_ld = (size_t)splits * D;
+  bool const r_vec = (splits & 7) == 0 && (reinterpret_cast<uintptr_t>(rp) & 15) == 0; // rows of R are 16-byte pieces
   for (int u = t; u < m * kGroups; u += nt) {
     int const r = u / kGroups, c = (u % kGroups) * 8;
     uint16_t const *src = op + (size_t)r * out_ld + c;
-    float facc[8];
-    uint32_t iacc[8];
+    uint16_t const *rrow = rp + (size_t)r * splits;
+    float facc[8], fden = 0.f;
+    uint32_t iacc[8], iden = 0u;
 #pragma unroll
     for (int i = 0; i < 8; i++) facc[i] = 0.f, iacc[i] = 0u;
     auto add = [&](uint4 w) {
@@ -68,36 +55,71 @@ __device__ __forceinline__ void merge_head(uint16_t const *op, uint16_t const *r
         }
       }
     };
+    auto add_den = [&](uint16_t v) {
+      if (KIND == kMergeFingerprint) iden += v;
+      else fden += merge_to_float<KIND>(v);
+    };
+    auto add_den8 = [&](uint4 w) {
+      uint32_t const words[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+      for (int i = 0; i < 4; i++) {
+        add_den((uint16_t)(words[i] & 0xFFFFu));
+        add_den((uint16_t)(words[i] >> 16));
+      }
+    };
     int sp = 0;
     for (; sp + 16 <= splits; sp += 16) { // sums of 65536 values < 25651 still fit 32 bits
-      uint4 w[16];
+      uint4 w[16], rv[2];
+      uint16_t rs[16];
 #pragma unroll
       for (int i = 0; i < 16; i++) w[i] = __ldcg(reinterpret_cast<uint4 const *>(src + (size_t)(sp + i) * D));
+      if (r_vec) {
+        rv[0] = __ldcg(reinterpret_cast<uint4 const *>(rrow + sp));
+        rv[1] = __ldcg(reinterpret_cast<uint4 const *>(rrow + sp + 8));
+      } else {
+#pragma unroll
+        for (int i = 0; i < 16; i++) rs[i] = __ldcg(rrow + sp + i);
+      }
 #pragma unroll
       for (int i = 0; i < 16; i++) add(w[i]);
+      if (r_vec) {
+        add_den8(rv[0]);
+        add_den8(rv[1]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 16; i++) add_den(rs[i]);
+      }
     }
     for (; sp + 4 <= splits; sp += 4) {
       uint4 w[4];
+      uint16_t rs[4];
 #pragma unroll
-      for (int i = 0; i < 4; i++) w[i] = __ldcg(reinterpret_cast<uint4 const *>(src + (size_t)(sp + i) * D));
+      for (int i = 0; i < 4; i++) {
+        w[i] = __ldcg(reinterpret_cast<uint4 const *>(src + (size_t)(sp + i) * D));
+        rs[i] = __ldcg(rrow + sp + i);
+      }
 #pragma unroll
-      for (int i = 0; i < 4; i++) add(w[i]);
+      for (int i = 0; i < 4; i++) {
+        add(w[i]);
+        add_den(rs[i]);
+      }
     }
-    for (; sp < splits; sp++) add(__ldcg(reinterpret_cast<uint4 const *>(src + (size_t)sp * D)));
+    for (; sp < splits; sp++) {
+      add(__ldcg(reinterpret_cast<uint4 const *>(src + (size_t)sp * D)));
+      add_den(__ldcg(rrow + sp));
+    }
     uint32_t o[4];
     if (KIND == kMergeFingerprint) {
-      uint32_t const den = den_smem[r];
+      uint32_t const den = iden % PQ;
 #pragma unroll
       for (int i = 0; i < 4; i++) o[i] = field_div(iacc[2 * i] % PQ, den) | (field_div(iacc[2 * i + 1] % PQ, den) << 16);
     } else {
-      float const den = __uint_as_float(den_smem[r]);
 #pragma unroll
-      for (int i = 0; i < 4; i++) o[i] = merge_pack<KIND>(facc[2 * i] / den, facc[2 * i + 1] / den);
+      for (int i = 0; i < 4; i++) o[i] = merge_pack<KIND>(facc[2 * i] / fden, facc[2 * i + 1] / fden);
     }
     *reinterpret_cast<uint4 *>(dst + (size_t)r * D + c) = make_uint4(o[0], o[1], o[2], o[3]);
   }
 }
-
 
 // Stand-alone merge launch (attn_split.cu): blocks of 128 threads take 8 query rows of one head each.  With
 // `after_previous_kernel` the launch uses programmatic stream serialisation: its blocks are scheduled while the

@@ -514,10 +514,8 @@ attn_split_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
       uint16_t const *op = static_cast<uint16_t const *>(p.o_part) + set * p.o_set_stride + (int64_t)head * p.m * out_ld;
       uint16_t const *rp = static_cast<uint16_t const *>(p.r_part) + set * p.r_set_stride + (int64_t)head * p.m * p.splits;
       uint16_t *dst = static_cast<uint16_t *>(p.merged_out) + set * p.merged_set_stride + (int64_t)head * p.m * DH;
-      // the stage memory is free by now (every warp passed the barriers above): it holds the row denominators
       constexpr int kKind = MODE == kFingerprint ? kMergeFingerprint : (MODE == kBF16 ? kMergeBF16 : kMergeF16);
-      merge_head<kKind, DH>(op, rp, dst, p.m, p.splits, tid, (int)blockDim.x, reinterpret_cast<uint32_t *>(smem),
-                            [] { __syncthreads(); });
+      merge_head<kKind, DH>(op, rp, dst, p.m, p.splits, tid, (int)blockDim.x);
       if (tid == 0) p.tickets[set * p.heads + head] = 0; // ready for the next launch
     }
   }
@@ -569,7 +567,6 @@ template <int KIND, int D>
 __global__ void __launch_bounds__(128) attn_merge_rows_kernel(uint16_t const *o_part, uint16_t const *r_part, uint16_t *out,
                                                               int heads, int m, int splits, long long o_stride,
                                                               long long r_stride, long long out_stride) {
-  __shared__ uint32_t den[kMergeRowsPerBlock];
   asm volatile("griddepcontrol.wait;" ::: "memory"); // no-op unless launched with programmatic serialisation
   int const chunks = (m + kMergeRowsPerBlock - 1) / kMergeRowsPerBlock;
   int const chunk = blockIdx.x % chunks, bh = blockIdx.x / chunks, head = bh % heads;
@@ -578,7 +575,7 @@ __global__ void __launch_bounds__(128) attn_merge_rows_kernel(uint16_t const *o_
   uint16_t const *op = o_part + set * o_stride + ((long long)head * m + r0) * splits * D;
   uint16_t const *rp = r_part + set * r_stride + ((long long)head * m + r0) * splits;
   uint16_t *dst = out + set * out_stride + ((long long)head * m + r0) * D;
-  merge_head<KIND, D>(op, rp, dst, rows, splits, (int)threadIdx.x, 128, den, [] { __syncthreads(); });
+  merge_head<KIND, D>(op, rp, dst, rows, splits, (int)threadIdx.x, 128);
 }
 
 template <int KIND, int D>

@@ -101,7 +101,6 @@ struct Shared {
   int abort_flag;
   int last_flag;
   float rsum[2][4][kNQ]; // [item parity][exp warp][query column]
-  uint32_t merge_den[kNQ];
 };
 
 // K_KV: K memory is [kv][d] (K-major A of S^T) else [d][kv] (MN-major); V_KV: V memory is [kv][d] (MN-major A of
@@ -441,8 +440,7 @@ attn_split_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_con
           uint16_t const *op = static_cast<uint16_t const *>(p.o_part) + set * p.o_set_stride + (long long)head * p.m * out_ld;
           uint16_t const *rp = static_cast<uint16_t const *>(p.r_part) + set * p.r_set_stride + (long long)head * p.m * p.splits;
           uint16_t *dst = static_cast<uint16_t *>(p.merged_out) + set * p.merged_set_stride + (long long)head * p.m * kD;
-          merge_head<BF16 ? kMergeBF16 : kMergeF16, kD>(op, rp, dst, p.m, p.splits, et, 128, sh->merge_den,
-                                                        [] { asm volatile("bar.sync 1, 128;" ::: "memory"); });
+          merge_head<BF16 ? kMergeBF16 : kMergeF16, kD>(op, rp, dst, p.m, p.splits, et, 128);
         }
         TOCK(c_merge, a4);
       }
