@@ -92,6 +92,7 @@ struct Params {
   int32_t *status;
   long long o_set_stride, r_set_stride, merged_set_stride;
   int heads, m, splits, tiles, kv_len, causal_window, num_items;
+  int early_loads; // the inputs were not written by the previous kernel of the stream: load before waiting for it
 };
 
 struct Shared {
@@ -172,6 +173,7 @@ attn_split_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_con
     TDECL(w_e = 0, t0 = clock64());
     TileCursor c;
     int batch = 0, kv_base = 0;
+    if (!p.early_loads) asm volatile("griddepcontrol.wait;" ::: "memory");
     for (int n = 0; n < total && ok; n++, c.advance(T)) {
       int const li = c.li, j = c.j;
       if (j == 0) { // a new item: its coordinates, and its Q
@@ -387,6 +389,10 @@ attn_split_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_con
     uint32_t const lane_base = (uint32_t)(quarter * 32) << 16;
     int const et = tid - 192;                   // 0..127 among the epilogue threads
     bool ok = true;
+    // Launched with programmatic serialisation this grid may run while the previous kernel of the stream (the
+    // merge of the call before, which reads the partials written below) is still going: no global store before it
+    // has completed.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     TDECL(w_r = 0, w_o = 0, c_out = 0, c_tick = 0, c_merge = 0, t0 = clock64());
     for (int li = 0; li < my_items; li++) {
       int const ob = li & 1, item = item_of(li), batch = batch_of(item), split = split_of(item);
@@ -571,7 +577,20 @@ int launch(mgd_attn_split const *p, void const *q, void const *k, void const *v,
       return check_launch("cudaFuncSetAttribute(attn_split_tc_kernel)");
     configured[which] = true;
   }
-  kernels[which]<<<blocks, kThreads, smem, (cudaStream_t)stream>>>(qm, km, vm, a);
+  a.early_loads = opts && (opts->overlap & 2) ? 1 : 0;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(blocks, 1, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = (cudaStream_t)stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  if (opts && (opts->overlap & 1)) {
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+  }
+  cudaLaunchKernelEx(&cfg, kernels[which], qm, km, vm, a);
   if (opts && opts->merged_out) {
     int st = check_launch("attn_split_tc_kernel");
     if (st != MG_OK) return st;
