@@ -1,0 +1,353 @@
+// Dense attention operator on tcgen05, two query tiles per block ("ping-pong").
+//
+// Same operator as attn_rows_tc.cu (first customized op of the prefill muGraph, pattern of the reference's
+// cpp_examples/multi_head_attn_prefill.cc:43-98; the division that follows it can be fused in): per 128 query rows
+//     S = Q K,  E = exp(S),  O' += E V,  R' += rowsum(E)        over KV tiles of 128
+// One query tile alone leaves the tensor pipe idle while its exp runs and the MUFU pipe idle while its MMAs run: per
+// KV tile both need about 1000 cycles (16 MMAs of 64 cycles; 16384 exps at 16 per cycle) and they depend on each
+// other.  Here a block owns TWO query tiles of a head, each with its own exp warps, and one lane issues the MMAs of
+// both in the order
+//     S0(0) S1(0) | O0(0) S0(1) | O1(0) S1(1) | O0(1) S0(2) | ...
+// so the tensor pipe works on one tile while the other tile's exp runs, and each K / V tile is fetched once for 256
+// query rows.
+//
+// Tensor memory (all 512 columns): tile i has S_i at [128 i, 128 i + 128) and O'_i at [256 + 128 i, ...).  E of a KV
+// tile overwrites its own S values (packed 16-bit pairs: the thread that read S columns [64h, 64h+64) writes E to
+// [64h, 64h+32)) and is the A operand of the O' MMAs; S of the next KV tile is issued after them by the same lane, and
+// MMAs of one lane execute in order.  Q stays in shared memory (A operand of the S MMAs).
+// Shared memory: Q0, Q1 (32 KB each), a two-stage ring of K and V tiles (64 KB per stage), barriers.
+// Operand layouts: all four combinations of K and V memory order; an operand whose N index is contiguous in memory is
+// described as MN-major.
+//
+// Warp roles (576 threads):
+//   warp 0, one lane   TMA producer: Q0, Q1 once; K and V tiles.
+//   warp 1             allocates / frees tensor memory; one lane issues every MMA and commits to mbarriers.
+//   warps 2-9          exp warps of tile 0: thread = (query row, 64-column half); tcgen05.ld its S half-row, exp, row
+//   warps 10-17        sum, pack, tcgen05.st E.  Same for tile 1.  At the end: O', R' (and O'/R' when the division
+//                      is fused) to global memory.
+// Every wait on an mbarrier is bounded; a role that gives up raises a block-wide flag, the others stop at their next
+// wait, the block frees its tensor memory, records the failure in the device status word and returns.
+#include "common.cuh"
+#include "tcgen05.cuh"
+#include <cstdlib>
+#include <mutex>
+
+namespace mgk {
+namespace pp {
+using namespace t5;
+
+constexpr int kD = 128, kTile = 128;
+constexpr int kBox = 128 * 64 * 2;   // one TMA box: 128 rows x 64 16-bit elements = 16 KB
+constexpr int kOperand = 2 * kBox;   // a 128 x 128 tile
+constexpr int kStages = 2;
+constexpr uint32_t kTmemCols = 512;
+constexpr int kThreads = 576;
+
+struct Params {
+  void *o_acc, *r_acc, *o_div;
+  int32_t *status;
+  int heads, seq_q, forloop;
+};
+
+struct Shared {
+  uint64_t q_full, kv_full[kStages], kv_empty[kStages], s_full[2], e_full[2], o_full[2];
+  uint32_t tmem_base;
+  int abort_flag;
+  float row_sums[2][2][kTile]; // [query tile][column half][row]
+};
+
+__device__ __forceinline__ uint64_t k_major_step(int ks) { return (uint64_t)(((ks >> 2) * kBox + (ks & 3) * 32) >> 4); }
+__device__ __forceinline__ uint64_t mn_major_step(int ks) { return (uint64_t)((ks * 16 * 128) >> 4); }
+
+// K_KV: K memory is [kv][d] (K-major B of S) else [d][kv] (MN-major); V_KV: V memory is [kv][d] (MN-major B of O')
+// else [d][kv] (K-major).
+template <bool BF16, bool K_KV, bool V_KV>
+__global__ void __launch_bounds__(kThreads)
+attn_rows_pp_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
+                    const __grid_constant__ CUtensorMap v_map, const __grid_constant__ Params p) {
+  extern __shared__ unsigned char smem_dyn[];
+  unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
+  // [Q0 32 KB][Q1 32 KB][stage 0: K 32 KB, V 32 KB][stage 1][barriers]
+  uint32_t const q_smem = smem_u32(smem);
+  uint32_t const ring = q_smem + 2 * kOperand;
+  Shared *sh = reinterpret_cast<Shared *>(smem + 2 * kOperand + kStages * 2 * kOperand);
+  volatile int *abort_flag = &sh->abort_flag;
+
+  int const tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  int const pairs = p.seq_q / (2 * kTile);
+  int const head = blockIdx.x / pairs, q0 = (blockIdx.x % pairs) * 2 * kTile;
+  int const F = p.forloop;
+
+  if (tid == 0) {
+    sh->abort_flag = 0;
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&q_map) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&k_map) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&v_map) : "memory");
+    mbar_init(smem_u32(&sh->q_full), 1);
+    for (int s = 0; s < kStages; s++) {
+      mbar_init(smem_u32(&sh->kv_full[s]), 1);
+      mbar_init(smem_u32(&sh->kv_empty[s]), 1);
+    }
+    for (int i = 0; i < 2; i++) {
+      mbar_init(smem_u32(&sh->s_full[i]), 1);
+      mbar_init(smem_u32(&sh->e_full[i]), 256);
+      mbar_init(smem_u32(&sh->o_full[i]), 1);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    fence_proxy_async_smem();
+  }
+  if (warp == 1) tmem_alloc(smem_u32(&sh->tmem_base), kTmemCols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  uint32_t const tmem = sh->tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t full = smem_u32(&sh->q_full);
+      mbar_expect_tx(full, 2 * kOperand);
+      for (int i = 0; i < 2; i++) { // Q memory [heads][seq_q][d]: rows = query rows, two boxes over d
+        tma_load_3d(q_smem + (uint32_t)(i * kOperand), &q_map, full, 0, q0 + i * kTile, head);
+        tma_load_3d(q_smem + (uint32_t)(i * kOperand + kBox), &q_map, full, 64, q0 + i * kTile, head);
+      }
+    }
+    __syncwarp();
+    for (int j = 0; j < F; j++) {
+      int const s = j % kStages;
+      if (j >= kStages && !mbar_wait(smem_u32(&sh->kv_empty[s]), (uint32_t)(((j / kStages) - 1) & 1), abort_flag)) break;
+      if (lane == 0) {
+        uint32_t full = smem_u32(&sh->kv_full[s]);
+        uint32_t kdst = ring + (uint32_t)(s * 2 * kOperand), vdst = kdst + kOperand;
+        int const kv0 = j * kTile;
+        mbar_expect_tx(full, 2 * kOperand);
+        if (K_KV) { // rows = KV positions, boxes over d
+          tma_load_3d(kdst, &k_map, full, 0, kv0, head);
+          tma_load_3d(kdst + kBox, &k_map, full, 64, kv0, head);
+        } else {    // rows = d, boxes over this tile's KV positions
+          tma_load_3d(kdst, &k_map, full, kv0, 0, head);
+          tma_load_3d(kdst + kBox, &k_map, full, kv0 + 64, 0, head);
+        }
+        if (V_KV) {
+          tma_load_3d(vdst, &v_map, full, 0, kv0, head);
+          tma_load_3d(vdst + kBox, &v_map, full, 64, kv0, head);
+        } else {
+          tma_load_3d(vdst, &v_map, full, kv0, 0, head);
+          tma_load_3d(vdst + kBox, &v_map, full, kv0 + 64, 0, head);
+        }
+      }
+      __syncwarp();
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    // Descriptors of stage 0 / tile 0; a stage, a tile or a K step only moves the start-address field, so the issuing
+    // lane pays one 64-bit add per operand and MMA.
+    uint32_t const fmt = BF16 ? 1u : 0u;
+    uint32_t const idesc_s = instr_desc_f16(fmt, false, !K_KV, kTile, kTile);
+    uint32_t const idesc_o = instr_desc_f16(fmt, false, V_KV, kTile, kD);
+    uint64_t const q_desc0 = smem_desc(q_smem, 16, 1024, 2);
+    uint64_t const k_desc0 = K_KV ? smem_desc(ring, 16, 1024, 2) : smem_desc(ring, kBox, 1024, 2);
+    uint64_t const v_desc0 = V_KV ? smem_desc(ring + kOperand, kBox, 1024, 2) : smem_desc(ring + kOperand, 16, 1024, 2);
+    auto issue_s = [&](int i, int j) { // S_i(j) = Q_i K_j
+      uint64_t const qd = q_desc0 + (uint64_t)((i * kOperand) >> 4);
+      uint64_t const kd = k_desc0 + (uint64_t)(((j % kStages) * 2 * kOperand) >> 4);
+      uint32_t const d_tmem = tmem + (uint32_t)(i * kTile);
+#pragma unroll
+      for (int ks = 0; ks < kD / 16; ks++)
+        umma_f16(d_tmem, qd + k_major_step(ks), kd + (K_KV ? k_major_step(ks) : mn_major_step(ks)), idesc_s, ks > 0);
+      umma_commit(smem_u32(&sh->s_full[i]));
+    };
+    auto issue_o = [&](int i, int j) { // O'_i += E_i(j) V_j; E in the S buffer: half h at columns [64h, 64h+32), 8 per step
+      uint64_t const vd = v_desc0 + (uint64_t)(((j % kStages) * 2 * kOperand) >> 4);
+      uint32_t const d_tmem = tmem + 256 + (uint32_t)(i * kTile), e_tmem = tmem + (uint32_t)(i * kTile);
+#pragma unroll
+      for (int ks = 0; ks < kTile / 16; ks++)
+        umma_f16_ts(d_tmem, e_tmem + (uint32_t)((ks >> 2) * 64 + (ks & 3) * 8), vd + (V_KV ? mn_major_step(ks) : k_major_step(ks)),
+                    idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
+    };
+    bool ok = mbar_wait(smem_u32(&sh->q_full), 0, abort_flag);
+    if (ok) ok = mbar_wait(smem_u32(&sh->kv_full[0]), 0, abort_flag);
+    if (ok) {
+      tc_fence_after();
+      if (lane == 0) {
+        issue_s(0, 0);
+        issue_s(1, 0);
+      }
+      __syncwarp();
+    }
+    for (int j = 0; j < F && ok; j++) {
+      for (int i = 0; i < 2 && ok; i++) {
+        ok = mbar_wait(smem_u32(&sh->e_full[i]), (uint32_t)(j & 1), abort_flag);
+        // K_{j+1}, V_{j+1} for the S MMA issued right behind this tile's O' MMA
+        if (ok && i == 0 && j + 1 < F) ok = mbar_wait(smem_u32(&sh->kv_full[(j + 1) % kStages]), (uint32_t)(((j + 1) / kStages) & 1), abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        if (lane == 0) {
+          issue_o(i, j);
+          if (i == 1) umma_commit(smem_u32(&sh->kv_empty[j % kStages])); // K_j, V_j consumed by both tiles
+          if (j == F - 1) umma_commit(smem_u32(&sh->o_full[i]));
+          if (j + 1 < F) issue_s(i, j + 1);
+        }
+        __syncwarp();
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ exp / row sums / epilogue of one query tile
+    int const i = (warp - 2) >> 3;                // query tile of this warp
+    int const wi = (warp - 2) & 7;                // warp inside the tile's group
+    int const quarter = warp & 3;                 // tensor-memory lanes this warp may touch: 32 * (warp % 4)
+    int const half = wi >> 2;                     // which 64 columns of a KV tile
+    int const row = quarter * 32 + lane;
+    uint32_t const lane_base = (uint32_t)(quarter * 32) << 16;
+    uint32_t const s_tmem = tmem + (uint32_t)(i * kTile) + lane_base + (uint32_t)(half * 64);
+    float rsum = 0.f;
+    bool ok = true;
+    for (int j = 0; j < F && ok; j++) {
+      ok = mbar_wait(smem_u32(&sh->s_full[i]), (uint32_t)(j & 1), abort_flag);
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t flat[32]; // this thread's 64 values as 16-bit pairs
+      {
+        uint32_t v[64];
+        tmem_ld64(s_tmem, v); // one load, one wait: the tensor-memory latency is paid once per tile
+#pragma unroll
+        for (int x = 0; x < 64; x += 2) {
+          float e0 = exp_ftz(__uint_as_float(v[x])), e1 = exp_ftz(__uint_as_float(v[x + 1]));
+          rsum += e0 + e1;
+          flat[x >> 1] = pack2<BF16>(e0, e1);
+        }
+      }
+      // E replaces the S values this thread has just consumed: 32 packed columns at the start of its own half
+      tmem_st32(s_tmem, flat);
+      tc_fence_before();
+      mbar_arrive(smem_u32(&sh->e_full[i]));
+    }
+    // the two halves of a row add up their sums (named barrier per query tile, reached whether or not a wait gave up)
+    sh->row_sums[i][half][row] = rsum;
+    if (i == 0) asm volatile("bar.sync 1, 256;" ::: "memory");
+    else asm volatile("bar.sync 2, 256;" ::: "memory");
+    float const total = sh->row_sums[i][0][row] + sh->row_sums[i][1][row];
+    if (ok) ok = mbar_wait(smem_u32(&sh->o_full[i]), 0, abort_flag);
+    if (ok) {
+      tc_fence_after();
+      size_t const row_off = ((size_t)head * p.seq_q + q0 + i * kTile + row) * kD + half * 64;
+      uint16_t *o_row = static_cast<uint16_t *>(p.o_acc) + row_off;
+      uint16_t *d_row = p.o_div ? static_cast<uint16_t *>(p.o_div) + row_off : nullptr;
+      float const inv = 1.0f / total;
+#pragma unroll
+      for (int c = 0; c < 2; c++) {
+        uint32_t v[32];
+        tmem_ld32(tmem + 256 + (uint32_t)(i * kTile) + lane_base + (uint32_t)(half * 64 + c * 32), v);
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+          uint4 out;
+          out.x = pack2<BF16>(__uint_as_float(v[8 * q]), __uint_as_float(v[8 * q + 1]));
+          out.y = pack2<BF16>(__uint_as_float(v[8 * q + 2]), __uint_as_float(v[8 * q + 3]));
+          out.z = pack2<BF16>(__uint_as_float(v[8 * q + 4]), __uint_as_float(v[8 * q + 5]));
+          out.w = pack2<BF16>(__uint_as_float(v[8 * q + 6]), __uint_as_float(v[8 * q + 7]));
+          *reinterpret_cast<uint4 *>(o_row + c * 32 + q * 8) = out;
+          if (d_row) {
+            out.x = pack2<BF16>(__uint_as_float(v[8 * q]) * inv, __uint_as_float(v[8 * q + 1]) * inv);
+            out.y = pack2<BF16>(__uint_as_float(v[8 * q + 2]) * inv, __uint_as_float(v[8 * q + 3]) * inv);
+            out.z = pack2<BF16>(__uint_as_float(v[8 * q + 4]) * inv, __uint_as_float(v[8 * q + 5]) * inv);
+            out.w = pack2<BF16>(__uint_as_float(v[8 * q + 6]) * inv, __uint_as_float(v[8 * q + 7]) * inv);
+            *reinterpret_cast<uint4 *>(d_row + c * 32 + q * 8) = out;
+          }
+        }
+      }
+      if (half == 0)
+        static_cast<uint16_t *>(p.r_acc)[(size_t)head * p.seq_q + q0 + i * kTile + row] = (uint16_t)(pack2<BF16>(total, 0.f) & 0xFFFFu);
+    }
+  }
+
+  // ---- teardown: every role arrives here, failed or not --------------------------------------------------
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag && tid == 0) {
+    // copies this block issued may still be in flight: give them a bounded time to land before the block exits
+    for (int s = 0; s < kStages; s++)
+      for (int n = 0; n < 20000 && !mbar_try_wait(smem_u32(&sh->kv_full[s]), 0) && !mbar_try_wait(smem_u32(&sh->kv_full[s]), 1); n++) {
+      }
+    atomicExch(p.status, 4);
+  }
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, kTmemCols);
+  }
+}
+
+// ---- host side ------------------------------------------------------------------------------------------------
+using EncodeFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, cuuint64_t const *,
+                              cuuint64_t const *, cuuint32_t const *, cuuint32_t const *, CUtensorMapInterleave,
+                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeFn encode_fn() {
+  static EncodeFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void *sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeFn>(sym);
+  });
+  return fn;
+}
+// [batch][rows][cols] 16-bit array, box [1][128][64], 128-byte swizzle
+static bool make_map(CUtensorMap *map, void const *base, uint64_t batch, uint64_t rows, uint64_t cols) {
+  EncodeFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[3] = {cols, rows, batch};
+  cuuint64_t strides[2] = {cols * 2, rows * cols * 2};
+  cuuint32_t box[3] = {64, 128, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, const_cast<void *>(base), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+bool supported(mgd_attn_rows const *p) {
+  if (!p || p->heads <= 0 || p->forloop_range <= 0) return false;
+  if (p->d != kD || p->tile_m != kTile || p->tile_kv != kTile) return false;
+  if (p->seq_q % (2 * kTile) != 0 || p->kv_len != p->forloop_range * kTile) return false;
+  if (p->data_type != MG_DT_FLOAT16 && p->data_type != MG_DT_BFLOAT16) return false;
+  if ((int64_t)p->heads * (p->seq_q / (2 * kTile)) > 0x7fffffffLL) return false;
+  return encode_fn() != nullptr;
+}
+
+int launch(mgd_attn_rows const *p, void const *q, void const *k, void const *v, void *o_acc, void *r_acc, void *o_div,
+           void *stream) {
+  if (!supported(p)) return set_error(MG_ERR_UNSUPPORTED, "dense attention (two query tiles per block): shape not supported");
+  bool const k_kv = p->k_layout == MG_DMEM_COLUMN_MAJOR, v_kv = p->v_layout == MG_DMEM_ROW_MAJOR;
+  CUtensorMap qm, km, vm;
+  bool ok = make_map(&qm, q, p->heads, p->seq_q, kD);
+  ok = ok && (k_kv ? make_map(&km, k, p->heads, p->kv_len, kD) : make_map(&km, k, p->heads, kD, p->kv_len));
+  ok = ok && (v_kv ? make_map(&vm, v, p->heads, p->kv_len, kD) : make_map(&vm, v, p->heads, kD, p->kv_len));
+  if (!ok) return set_error(MG_ERR_CUDA, "dense attention: cuTensorMapEncodeTiled failed");
+  Params a;
+  a.o_acc = o_acc; a.r_acc = r_acc; a.o_div = o_div;
+  a.status = device_error_word();
+  if (!a.status) return set_error(MG_ERR_CUDA, "cannot allocate the device status word");
+  a.heads = p->heads; a.seq_q = p->seq_q; a.forloop = p->forloop_range;
+  size_t const smem = 1024 + (size_t)(2 + 2 * kStages) * kOperand + sizeof(Shared) + 64;
+  unsigned const blocks = (unsigned)(p->heads * (p->seq_q / (2 * kTile)));
+  bool const bf16 = p->data_type == MG_DT_BFLOAT16;
+  using Kernel = void (*)(CUtensorMap, CUtensorMap, CUtensorMap, Params);
+  static Kernel const kernels[8] = {
+      attn_rows_pp_kernel<false, false, false>, attn_rows_pp_kernel<false, false, true>,
+      attn_rows_pp_kernel<false, true, false>,  attn_rows_pp_kernel<false, true, true>,
+      attn_rows_pp_kernel<true, false, false>,  attn_rows_pp_kernel<true, false, true>,
+      attn_rows_pp_kernel<true, true, false>,   attn_rows_pp_kernel<true, true, true>};
+  static bool configured[8] = {false, false, false, false, false, false, false, false};
+  int const which = (bf16 ? 4 : 0) | (k_kv ? 2 : 0) | (v_kv ? 1 : 0);
+  if (!configured[which]) {
+    if (cudaFuncSetAttribute(kernels[which], cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+      return check_launch("cudaFuncSetAttribute(attn_rows_pp_kernel)");
+    configured[which] = true;
+  }
+  kernels[which]<<<blocks, kThreads, smem, (cudaStream_t)stream>>>(qm, km, vm, a);
+  return check_launch("attn_rows_pp_kernel");
+}
+
+} // namespace pp
+} // namespace mgk

@@ -33,6 +33,7 @@
 // returns.
 #include "common.cuh"
 #include <cstdio>
+#include <cstdlib>
 #include <cuda.h>
 #include <mutex>
 
@@ -479,11 +480,28 @@ static bool rows_supported(mgd_attn_rows const *p) {
 } // namespace tc
 } // namespace mgk
 
+namespace mgk {
+namespace pp { // attn_rows_pp.cu: two query tiles per block, all K / V layouts
+bool supported(mgd_attn_rows const *p);
+int launch(mgd_attn_rows const *p, void const *q, void const *k, void const *v, void *o_acc, void *r_acc, void *o_div,
+           void *stream);
+} // namespace pp
+} // namespace mgk
+
 using namespace mgk;
+
+// MUGRAPH_ROWS_PP=0 keeps the one-tile-per-block kernel (tuning, tests)
+static bool use_two_tile_kernel(mgd_attn_rows const *p) {
+  if (!pp::supported(p)) return false;
+  if (char const *e = getenv("MUGRAPH_ROWS_PP")) return atoi(e) != 0 || !tc::rows_supported(p);
+  return true;
+}
 
 extern "C" {
 
-int mgd_attn_rows_supported(const mgd_attn_rows *p) { return tc::rows_supported(p) && tc::encode_fn() != nullptr ? 1 : 0; }
+int mgd_attn_rows_supported(const mgd_attn_rows *p) {
+  return ((tc::rows_supported(p) && tc::encode_fn() != nullptr) || pp::supported(p)) ? 1 : 0;
+}
 
 int mgd_launch_attn_rows_float(const mgd_attn_rows *p, const void *q, const void *k, const void *v, void *o_acc,
                                void *r_acc, void *stream) {
@@ -493,6 +511,7 @@ int mgd_launch_attn_rows_float(const mgd_attn_rows *p, const void *q, const void
 int mgd_launch_attn_rows_float_ex(const mgd_attn_rows *p, const void *q, const void *k, const void *v, void *o_acc,
                                   void *r_acc, void *o_div, void *stream) {
   if (!q || !k || !v || !o_acc || !r_acc) return set_error(MG_ERR_INVALID_ARGUMENT, "dense attention: null tensor");
+  if (use_two_tile_kernel(p)) return pp::launch(p, q, k, v, o_acc, r_acc, o_div, stream);
   if (!tc::rows_supported(p)) return set_error(MG_ERR_UNSUPPORTED, "dense attention: shape or layout not supported");
   CUtensorMap km, vm;
   bool ok = tc::make_map(&km, k, p->heads, p->kv_len, tc::kD) && tc::make_map(&vm, v, p->heads, tc::kD, p->kv_len);

@@ -330,7 +330,7 @@ attn_split_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_con
       tmem_ld32(tmem + lane_base + (uint32_t)(b * kNQ), v);
       float e[kNQ];
 #pragma unroll
-      for (int q = 0; q < kNQ; q++) e[q] = __expf(__uint_as_float(v[q]));
+      for (int q = 0; q < kNQ; q++) e[q] = exp_ftz(__uint_as_float(v[q]));
       if (p.causal_window > 0 && kv_tile + kTileKv > p.kv_len - p.causal_window) {
         // only the last tile of the sequence reaches into the draft window
         int const pos = kv_tile + row;

@@ -270,18 +270,26 @@ def build_prefill(g, H, SQ, D, L, dtype, kl=mg.DmemColumnMajor, vl=mg.DmemColumn
 
 
 @pytest.mark.parametrize("dtype", [mg.bfloat16, mg.float16], ids=["bf16", "fp16"])
-@pytest.mark.parametrize("shape", [(2, 256, 512), (1, 128, 128), (3, 384, 1024)])
-def test_float_prefill_tensor_core_kernel(runtime, shape, dtype):
-    """Dense attention on tcgen05 / tensor memory (128 x 128 tiles) against the fp32 evaluation."""
+@pytest.mark.parametrize("layouts", [(mg.DmemColumnMajor, mg.DmemColumnMajor), (mg.DmemRowMajor, mg.DmemRowMajor),
+                                     (mg.DmemColumnMajor, mg.DmemRowMajor), (mg.DmemRowMajor, mg.DmemColumnMajor)],
+                         ids=["kc_vc", "kr_vr", "kc_vr", "kr_vc"])
+@pytest.mark.parametrize("shape", [(2, 256, 512), (1, 128, 128), (3, 384, 1024), (2, 512, 1024)])
+def test_float_prefill_tensor_core_kernel(runtime, shape, layouts, dtype):
+    """Dense attention on tcgen05 / tensor memory (128 x 128 tiles) against the fp32 evaluation.  Query lengths that
+    are multiples of 256 run on the two-tiles-per-block kernel (every K / V layout), the others on the one-tile kernel
+    (K and V column-major only)."""
     H, SQ, L = shape
     D = 128
+    kl, vl = layouts
+    if SQ % 256 != 0 and layouts != (mg.DmemColumnMajor, mg.DmemColumnMajor):
+        pytest.skip("the one-tile kernel takes K and V column-major only")
     runtime.set_max_smem(BIG)
     runtime.set_specialisation(2)
     rng = np.random.default_rng(H * 7 + SQ + L)
     with mg.PyGraph(runtime) as g:
-        ins, acc, out, plans = build_prefill(g, H, SQ, D, L, dtype)
+        ins, acc, out, plans = build_prefill(g, H, SQ, D, L, dtype, kl, vl)
         assert g.customized_info(3)["kernel_float"] == mg.KERNEL_ATTN_ROWS
-        (q, k, v), mem = float_inputs(rng, H, SQ, D, L, mg.DmemColumnMajor, mg.DmemColumnMajor, dtype)
+        (q, k, v), mem = float_inputs(rng, H, SQ, D, L, kl, vl, dtype)
         for t, a in zip(ins, mem):
             t.upload_data(to_bits(a, dtype))
         g.run()
