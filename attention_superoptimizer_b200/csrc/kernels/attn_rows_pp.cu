@@ -29,12 +29,26 @@
 // wait, the block frees its tensor memory, records the failure in the device status word and returns.
 #include "common.cuh"
 #include "tcgen05.cuh"
+#include <cstdio>
 #include <cstdlib>
 #include <mutex>
 
 namespace mgk {
 namespace pp {
 using namespace t5;
+
+// Optional role timing of block 0 (compile with -DMG_PP_TIMING; prints cycle totals from the device).
+#ifdef MG_PP_TIMING
+#define TICK(var) long long var = clock64()
+#define TOCK(acc, var) acc += clock64() - var
+#define TDECL(...) long long __VA_ARGS__
+#define TPRINT(...) if (blockIdx.x == 0) printf(__VA_ARGS__)
+#else
+#define TICK(var)
+#define TOCK(acc, var)
+#define TDECL(...)
+#define TPRINT(...)
+#endif
 
 constexpr int kD = 128, kTile = 128;
 constexpr int kBox = 128 * 64 * 2;   // one TMA box: 128 rows x 64 16-bit elements = 16 KB
@@ -175,13 +189,19 @@ attn_rows_pp_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
       }
       __syncwarp();
     }
+    TDECL(w_e0 = 0, w_e1 = 0, w_kv = 0, c_issue = 0, t0 = clock64());
     for (int j = 0; j < F && ok; j++) {
       for (int i = 0; i < 2 && ok; i++) {
+        TICK(a0);
         ok = mbar_wait(smem_u32(&sh->e_full[i]), (uint32_t)(j & 1), abort_flag);
+        if (i == 0) { TOCK(w_e0, a0); } else { TOCK(w_e1, a0); }
+        TICK(a1);
         // K_{j+1}, V_{j+1} for the S MMA issued right behind this tile's O' MMA
         if (ok && i == 0 && j + 1 < F) ok = mbar_wait(smem_u32(&sh->kv_full[(j + 1) % kStages]), (uint32_t)(((j + 1) / kStages) & 1), abort_flag);
+        TOCK(w_kv, a1);
         if (!ok) break;
         tc_fence_after();
+        TICK(a2);
         if (lane == 0) {
           issue_o(i, j);
           if (i == 1) umma_commit(smem_u32(&sh->kv_empty[j % kStages])); // K_j, V_j consumed by both tiles
@@ -189,8 +209,10 @@ attn_rows_pp_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
           if (j + 1 < F) issue_s(i, j + 1);
         }
         __syncwarp();
+        TOCK(c_issue, a2);
       }
     }
+    if (lane == 0) TPRINT("mma: total %lld wait e_full0 %lld e_full1 %lld kv_full %lld issue %lld (%d kv tiles)\n", clock64() - t0, w_e0, w_e1, w_kv, c_issue, F);
   } else {
     // ------------------------------------------------------------------ exp / row sums / epilogue of one query tile
     int const i = (warp - 2) >> 3;                // query tile of this warp
@@ -202,26 +224,36 @@ attn_rows_pp_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
     uint32_t const s_tmem = tmem + (uint32_t)(i * kTile) + lane_base + (uint32_t)(half * 64);
     float rsum = 0.f;
     bool ok = true;
+    TDECL(w_s = 0, c_ld = 0, c_exp = 0, c_st = 0, t0 = clock64());
     for (int j = 0; j < F && ok; j++) {
+      TICK(a0);
       ok = mbar_wait(smem_u32(&sh->s_full[i]), (uint32_t)(j & 1), abort_flag);
+      TOCK(w_s, a0);
       if (!ok) break;
       tc_fence_after();
+      TICK(a1);
       uint32_t flat[32]; // this thread's 64 values as 16-bit pairs
       {
         uint32_t v[64];
         tmem_ld64(s_tmem, v); // one load, one wait: the tensor-memory latency is paid once per tile
+        TOCK(c_ld, a1);
+        TICK(a2);
 #pragma unroll
         for (int x = 0; x < 64; x += 2) {
           float e0 = exp_ftz(__uint_as_float(v[x])), e1 = exp_ftz(__uint_as_float(v[x + 1]));
           rsum += e0 + e1;
           flat[x >> 1] = pack2<BF16>(e0, e1);
         }
+        TOCK(c_exp, a2);
       }
+      TICK(a3);
       // E replaces the S values this thread has just consumed: 32 packed columns at the start of its own half
       tmem_st32(s_tmem, flat);
       tc_fence_before();
       mbar_arrive(smem_u32(&sh->e_full[i]));
+      TOCK(c_st, a3);
     }
+    if (lane == 0 && (warp == 2 || warp == 10)) TPRINT("exp warp %d: total %lld wait s_full %lld ld %lld exp %lld st+arrive %lld\n", warp, clock64() - t0, w_s, c_ld, c_exp, c_st);
     // the two halves of a row add up their sums (named barrier per query tile, reached whether or not a wait gave up)
     sh->row_sums[i][half][row] = rsum;
     if (i == 0) asm volatile("bar.sync 1, 256;" ::: "memory");
