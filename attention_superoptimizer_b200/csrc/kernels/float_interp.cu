@@ -115,7 +115,7 @@ __device__ void matmul_tiles(unsigned char const *Ap, unsigned char const *Bp, f
 }
 
 template <typename T>
-__global__ void __launch_bounds__(256) float_interp_kernel(const __grid_constant__ mgd_program prog,
+__global__ void __launch_bounds__(1024) float_interp_kernel(const __grid_constant__ mgd_program prog,
                                                            const __grid_constant__ mgd_bindings bind) {
   extern __shared__ __align__(16) unsigned char smem_b[];
   int const tid = threadIdx.x, nt = blockDim.x;
@@ -455,6 +455,22 @@ extern "C" int mgd_launch_float_interp(const mgd_program *prog, const mgd_bindin
                      "that way; only graphs matched by a specialised kernel can run at this size");
   int64_t blocks = (int64_t)prog->grid[0] * prog->grid[1] * prog->grid[2] * bind->num_sets;
   if (blocks > 0x7fffffffLL) return set_error(MG_ERR_UNSUPPORTED, "too many blocks for one launch");
+  // Blocks run one operator at a time with a barrier after each: big tiles get more warps to hide the latency of
+  // the dependent instruction chains (the largest operator decides; a matmul thread owns up to 16 outputs).
+  int64_t largest = 0;
+  for (int i = 0; i < prog->num_ops; i++) {
+    int32_t const *a = prog->ops[i].a;
+    int64_t work = 0;
+    switch (prog->ops[i].type) {
+      case 2001: work = (int64_t)a[14] * a[15] / 8; break;
+      case 2002: work = (int64_t)a[11] * a[12]; break;
+      case MG_TB_MATMUL_OP: work = (int64_t)a[0] * a[1] / 4; break;
+      case MG_TB_EXP_OP: work = a[1]; break;
+      default: work = a[0]; break;
+    }
+    if (work > largest) largest = work;
+  }
+  unsigned const threads = largest >= 8192 ? 1024u : (largest >= 2048 ? 512u : 256u);
   static bool configured_h = false, configured_b = false;
   if (dt == MG_DT_FLOAT16) {
     if (smem > 48 * 1024 && !configured_h) {
@@ -462,14 +478,14 @@ extern "C" int mgd_launch_float_interp(const mgd_program *prog, const mgd_bindin
         return check_launch("cudaFuncSetAttribute(float_interp_kernel)");
       configured_h = true;
     }
-    float_interp_kernel<__half><<<(unsigned)blocks, 256, smem, (cudaStream_t)stream>>>(r.prog, *bind);
+    float_interp_kernel<__half><<<(unsigned)blocks, threads, smem, (cudaStream_t)stream>>>(r.prog, *bind);
   } else if (dt == MG_DT_BFLOAT16) {
     if (smem > 48 * 1024 && !configured_b) {
       if (cudaFuncSetAttribute(float_interp_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess)
         return check_launch("cudaFuncSetAttribute(float_interp_kernel)");
       configured_b = true;
     }
-    float_interp_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, smem, (cudaStream_t)stream>>>(r.prog, *bind);
+    float_interp_kernel<__nv_bfloat16><<<(unsigned)blocks, threads, smem, (cudaStream_t)stream>>>(r.prog, *bind);
   } else {
     return set_error(MG_ERR_UNSUPPORTED, "float mode runs on fp16 or bf16 tensors");
   }

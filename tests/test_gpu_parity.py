@@ -167,6 +167,38 @@ def test_fingerprint_other_graphs(rt):
     run_generic_fp(rt, specs, ident, 3)
 
 
+@pytest.mark.parametrize("mkn", [(1, 16, 16), (4, 16, 16), (5, 32, 48), (6, 48, 32), (16, 64, 1024), (33, 128, 64),
+                                 (7, 24, 16), (8, 16, 24), (3, 5, 7)],
+                         ids=lambda s: "x".join(map(str, s)))
+def test_interpreter_matmul_shapes_and_full_range(runtime, mkn):
+    """The interpreter's matmul - integer tensor cores where k and n are multiples of 16, scalar otherwise - on row
+    counts that do not fill a 4-row group and on operands over the whole uint16 range (byte planes up to 255),
+    for-loop accumulation included."""
+    m, k, n = mkn
+    F = 2
+    runtime.set_max_smem(BIG)
+    runtime.set_specialisation(0)
+    try:
+        rng = np.random.default_rng(m * 1000 + k * 10 + n)
+        specs = [mo.DTensorSpec((m, F * k)), mo.DTensorSpec((F * k, n))]
+        plan = mo.ExecutionPlan(ops=[(mo.TB_MATMUL_OP, [(0, 0), (1, 0)])], input_map=[(-1, -1, -1), (-1, -1, -1)],
+                                forloop_dim=[1, 0], input_smem_layouts=[mo.SmemRowMajor] * 2, output_map=(-1, -1, -1),
+                                forloop_range=F, grid_dim=(1, 1, 1))
+        for hi in (mo.FP_PQ, 65536):
+            x = [rng.integers(0, hi, size=s.dims).astype(np.uint16) for s in specs]
+            with mg.PyGraph(runtime) as g:
+                ins = [g.new_input(s.dims, s.dtype, s.layout) for s in specs]
+                for t, v in zip(ins, x):
+                    t.upload_fingerprint(v)
+                outs = g.customized(ins, to_package_plan(plan))
+                g.fingerprint()
+                got = outs[0].download_fingerprint()
+            want = (x[0].astype(np.int64) @ x[1].astype(np.int64)) % mo.FP_PQ
+            assert np.array_equal(got.astype(np.int64), want), "operands below %d" % hi
+    finally:
+        runtime.set_specialisation(2)
+
+
 def float_inputs(rng, B, M, D, L, kl, vl, dtype):
     """Logical tensors rounded to storage precision, plus their memory images."""
     rnd = lambda a: from_bits(to_bits(a, dtype), dtype)
