@@ -379,6 +379,23 @@ class PyGraph:
         return sz.value
 
 
+def verify_candidates(reference: "PyTensor", candidates, stream=None):
+    """The search's verify step for a batch (src/search/search.cc:569-623): `candidates` is a list of
+    (PyGraph, output PyTensor) whose inputs are already in place; every graph is evaluated in fingerprint mode and
+    its output compared with `reference` on the device - one synchronisation for the whole batch.  Returns a list
+    of bools."""
+    n = len(candidates)
+    if n == 0:
+        return []
+    rt = reference.graph.rt
+    graphs = (ctypes.c_void_p * n)(*[g.handle for g, _ in candidates])
+    outs = (mg_tensor * n)(*[t.pod for _, t in candidates])
+    same = (ctypes.c_int32 * n)()
+    check(rt.lib.mg_verify_candidates(rt.handle, ctypes.byref(reference.pod), graphs, outs, n, same,
+                                      ctypes.c_void_p(stream or 0)))
+    return [bool(v) for v in same]
+
+
 class CapturedSequence:
     """A launch sequence captured into a CUDA graph on `stream` (a raw cudaStream_t value)."""
 

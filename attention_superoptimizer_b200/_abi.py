@@ -63,6 +63,7 @@ SIGNATURES = {
     "mg_graph_customized_info": (ctypes.c_int, [_P, _I, ctypes.POINTER(_I), ctypes.POINTER(_I), ctypes.POINTER(_I),
                                                 ctypes.POINTER(_I)]),
     "mg_graph_customized_program": (ctypes.c_int, [_P, _I, _P, ctypes.c_size_t]),
+    "mg_verify_candidates": (ctypes.c_int, [_P, _T, ctypes.POINTER(_P), _T, _I, ctypes.POINTER(_I), _P]),
     "mg_graph_to_json": (ctypes.c_int, [_P, ctypes.c_char_p, ctypes.c_size_t, ctypes.POINTER(ctypes.c_size_t)]),
     "mg_graph_from_json": (ctypes.c_int, [_P, ctypes.c_char_p, ctypes.POINTER(_P)]),
     "mg_graph_operator_info": (ctypes.c_int, [_P, _I, ctypes.POINTER(_I), _T, _I, ctypes.POINTER(_I)]),

@@ -471,6 +471,43 @@ int mg_tensor_has_same_fingerprint(mg_runtime *rt, const mg_tensor *a, const mg_
   return MG_OK;
 }
 
+int mg_verify_candidates(mg_runtime *rt, const mg_tensor *reference, mg_graph *const *candidates,
+                         const mg_tensor *outputs, int32_t n, int32_t *same, void *stream) {
+  if (int dry_st = refuse_dry(rt)) return dry_st;
+  if (!rt || !rt->dmm || !reference || !candidates || !outputs || !same || n < 0) return fail(MG_ERR_INVALID_ARGUMENT, "null argument");
+  if (n == 0) return MG_OK;
+  static int32_t *flags = nullptr; // device scratch, grows, lives as long as the process
+  static int32_t flags_capacity = 0;
+  if (n > flags_capacity) {
+    if (flags) cudaFree(flags);
+    flags = nullptr;
+    flags_capacity = 0;
+    MG_CUDA_TRY(cudaMalloc(&flags, sizeof(int32_t) * (size_t)n));
+    flags_capacity = n;
+  }
+  MG_CUDA_TRY(cudaMemsetAsync(flags, 0, sizeof(int32_t) * (size_t)n, (cudaStream_t)stream));
+  int64_t ref_elems = 1;
+  for (int d = 0; d < reference->num_dims; d++) ref_elems *= reference->dim[d];
+  for (int32_t i = 0; i < n; i++) {
+    if (!candidates[i]) return fail(MG_ERR_INVALID_ARGUMENT, "null candidate graph");
+    int st = launch_all(candidates[i], true, true, stream);
+    if (st != MG_OK) return st;
+    bool same_shape = outputs[i].num_dims == reference->num_dims && outputs[i].fp_ptr != nullptr;
+    for (int d = 0; same_shape && d < reference->num_dims; d++) same_shape = outputs[i].dim[d] == reference->dim[d];
+    if (!same_shape) continue; // flag stays 0
+    st = mgd_compare_u16(outputs[i].fp_ptr, reference->fp_ptr, ref_elems, flags + i, stream);
+    if (st != MG_OK) return fail(st, mgd_last_error());
+  }
+  MG_CUDA_TRY(cudaMemcpyAsync(same, flags, sizeof(int32_t) * (size_t)n, cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+  MG_CUDA_TRY(cudaStreamSynchronize((cudaStream_t)stream));
+  int32_t code = 0;
+  int st = mgd_read_and_clear_device_error(&code);
+  if (st != MG_OK) return fail(st, mgd_last_error());
+  if (code != 0) return fail(MG_ERR_DEVICE_TIMEOUT, "a kernel gave up a bounded wait (device status word set)");
+  for (int32_t i = 0; i < n; i++) same[i] = same[i] == 1;
+  return MG_OK;
+}
+
 static int64_t pod_elements(const mg_tensor *t) {
   int64_t n = 1;
   for (int i = 0; i < t->num_dims; i++) n *= t->dim[i];

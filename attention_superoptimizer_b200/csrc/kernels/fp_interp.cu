@@ -16,7 +16,8 @@
 
 namespace mgk {
 
-__device__ __forceinline__ void load_tile_u16(uint16_t *dst, uint16_t const *src, int rows, int cols, int ld,
+// `pitch` = elements between tile rows in shared memory (cols, or cols + 8 for a padded matmul operand)
+__device__ __forceinline__ void load_tile_u16(uint16_t *dst, uint16_t const *src, int rows, int cols, int pitch, int ld,
                                               int row0, int col0, int tid, int nthreads) {
   bool vec = (cols % 8 == 0) && (ld % 8 == 0) && (col0 % 8 == 0) && ((reinterpret_cast<uintptr_t>(src) & 15) == 0) &&
              ((reinterpret_cast<uintptr_t>(dst) & 15) == 0);
@@ -25,13 +26,13 @@ __device__ __forceinline__ void load_tile_u16(uint16_t *dst, uint16_t const *src
     for (int i = tid; i < n; i += nthreads) {
       int r = i / cv, c = (i % cv) * 8;
       uint4 v = __ldg(reinterpret_cast<uint4 const *>(src + (size_t)(row0 + r) * ld + col0 + c));
-      *reinterpret_cast<uint4 *>(dst + r * cols + c) = v;
+      *reinterpret_cast<uint4 *>(dst + r * pitch + c) = v;
     }
   } else {
     int n = rows * cols;
     for (int i = tid; i < n; i += nthreads) {
       int r = i / cols, c = i % cols;
-      dst[i] = __ldg(src + (size_t)(row0 + r) * ld + col0 + c);
+      dst[r * pitch + c] = __ldg(src + (size_t)(row0 + r) * ld + col0 + c);
     }
   }
 }
@@ -44,7 +45,7 @@ __device__ __forceinline__ void load_tile_u16(uint16_t *dst, uint16_t const *src
 // Same residue as the reference's multiply-add loop (TBMatmulFingerprinter, threadblock/cuda/matmul.h:773-804).
 // Needs k % 16 == 0 and n % 16 == 0 (ldmatrix rows of 16 bytes); a warp owns 4 rows x 16 columns of C at a time.
 __device__ __forceinline__ void matmul_fp_tensor(uint16_t const *A, uint16_t const *B, uint16_t *C, int m, int n, int k,
-                                                 int tid, int nthreads) {
+                                                 int b_pitch, int tid, int nthreads) {
   int const lane = tid & 31, warp = tid >> 5, nwarps = nthreads >> 5;
   int const g = lane >> 2, t = lane & 3, mi = lane >> 3, rr = lane & 7;
   int const row_groups = (m + 3) >> 2, col_pairs = n >> 4;
@@ -56,8 +57,8 @@ __device__ __forceinline__ void matmul_fp_tensor(uint16_t const *A, uint16_t con
     int32_t acc[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}};
     uint16_t const *arow = A + (size_t)row * k + 2 * t;
     // ldmatrix (transposed): this lane addresses k-row (mi % 2) * 8 + rr of the 8 columns starting at (mi / 2) * 8
-    uint32_t baddr = b_base + (uint32_t)((((mi & 1) * 8 + rr) * n + cp * 16 + (mi >> 1) * 8) * 2);
-    for (int k0 = 0; k0 < k; k0 += 16, baddr += (uint32_t)(16 * n * 2)) {
+    uint32_t baddr = b_base + (uint32_t)((((mi & 1) * 8 + rr) * b_pitch + cp * 16 + (mi >> 1) * 8) * 2);
+    for (int k0 = 0; k0 < k; k0 += 16, baddr += (uint32_t)(16 * b_pitch * 2)) {
       uint32_t const w0 = valid ? *reinterpret_cast<uint32_t const *>(arow + k0) : 0u;
       uint32_t const w1 = valid ? *reinterpret_cast<uint32_t const *>(arow + k0 + 8) : 0u;
       uint32_t a[4], bf[4];
@@ -124,15 +125,16 @@ __global__ void __launch_bounds__(1024) fp_interp_kernel(const __grid_constant__
           uint16_t const *src =
               static_cast<uint16_t const *>(bind.in[a[18]]) + set * bind.in_set_stride[a[18]] + lead;
           // layout tag a[16] is deliberately ignored: fingerprints are indexed row-major
-          load_tile_u16(tile(a[17]), src, a[14], a[15], a[13], row, col, tid, nt);
+          load_tile_u16(tile(a[17]), src, a[14], a[15], a[15] + ((a[16] >> 8) & 0xff), a[13], row, col, tid, nt);
           break;
         }
         case MG_TB_MATMUL_OP: {
           int m = a[0], n = a[1], k = a[2];
           uint16_t const *A = tile(a[3]), *B = tile(a[4]);
           uint16_t *C = tile(a[5]);
+          int const bp = a[6] > 0 ? a[6] : n; // row pitch of B: padded by the host when the dense pitch conflicts
           if ((k & 15) == 0 && (n & 15) == 0 && k <= 16384 && (nt & 31) == 0) {
-            matmul_fp_tensor(A, B, C, m, n, k, tid, nt);
+            matmul_fp_tensor(A, B, C, m, n, k, bp, tid, nt);
             break;
           }
           for (int i = tid; i < m * n; i += nt) {
@@ -141,12 +143,12 @@ __global__ void __launch_bounds__(1024) fp_interp_kernel(const __grid_constant__
             unsigned long long acc = 0;
             int kk = 0;
             for (; kk + 4 <= k; kk += 4) {
-              acc += (unsigned long long)((uint32_t)ar[kk] * (uint32_t)bc[(kk)*n]);
-              acc += (unsigned long long)((uint32_t)ar[kk + 1] * (uint32_t)bc[(kk + 1) * n]);
-              acc += (unsigned long long)((uint32_t)ar[kk + 2] * (uint32_t)bc[(kk + 2) * n]);
-              acc += (unsigned long long)((uint32_t)ar[kk + 3] * (uint32_t)bc[(kk + 3) * n]);
+              acc += (unsigned long long)((uint32_t)ar[kk] * (uint32_t)bc[(kk)*bp]);
+              acc += (unsigned long long)((uint32_t)ar[kk + 1] * (uint32_t)bc[(kk + 1) * bp]);
+              acc += (unsigned long long)((uint32_t)ar[kk + 2] * (uint32_t)bc[(kk + 2) * bp]);
+              acc += (unsigned long long)((uint32_t)ar[kk + 3] * (uint32_t)bc[(kk + 3) * bp]);
             }
-            for (; kk < k; kk++) acc += (unsigned long long)((uint32_t)ar[kk] * (uint32_t)bc[kk * n]);
+            for (; kk < k; kk++) acc += (unsigned long long)((uint32_t)ar[kk] * (uint32_t)bc[kk * bp]);
             C[i] = (uint16_t)(acc % PQ);
           }
           break;
@@ -251,6 +253,120 @@ int validate_program(mgd_program const *p, mgd_bindings const *b) {
     if (!b->out[i]) return set_error(MG_ERR_INVALID_ARGUMENT, "unbound output");
   return MG_OK;
 }
+
+// ---- host: padded matmul operands ---------------------------------------------------------------------------------
+// ldmatrix reads 8 rows of 16 bytes of the B operand at a time; in the reference's dense plan a row pitch that is a
+// multiple of 128 bytes puts all 8 on the same banks.  A tile that only input loaders write and only matmuls read as
+// their B operand is therefore stored with 16 bytes of padding per row; every tile behind it moves up.  Tiles keep
+// their identity (planned offset), so the aliasing of the in-place exp is unchanged.
+namespace {
+struct FpTile {
+  int planned, elems, rows, cols;
+  bool only_loaded, only_b_operand;
+  int offset, pad;
+};
+
+void pad_b_operands(mgd_program const &in, mgd_program *out, size_t *smem_bytes) {
+  FpTile tiles[3 * MGD_MAX_OPS];
+  int n = 0;
+  auto touch = [&](int planned, int elems) -> FpTile & {
+    for (int i = 0; i < n; i++)
+      if (tiles[i].planned == planned) {
+        if (elems > tiles[i].elems) tiles[i].elems = elems;
+        return tiles[i];
+      }
+    tiles[n] = FpTile{planned, elems, 0, 0, true, true, 0, 0};
+    return tiles[n++];
+  };
+  for (int i = 0; i < in.num_ops; i++) {
+    int32_t const *a = in.ops[i].a;
+    int const type = in.ops[i].type;
+    if (type == 2001) {
+      FpTile &t = touch(a[17], a[14] * a[15]);
+      t.rows = a[14]; t.cols = a[15];
+    } else if (type == MG_TB_MATMUL_OP) {
+      touch(a[3], a[0] * a[2]).only_b_operand = false;
+      touch(a[4], a[2] * a[1]);
+      FpTile &c = touch(a[5], a[0] * a[1]);
+      c.only_loaded = false;
+    } else if (type == MG_TB_EXP_OP) {
+      FpTile &t = touch(a[0], a[1]);
+      t.only_loaded = false; t.only_b_operand = false;
+    } else if (type == MG_TB_DIV_OP || type == MG_TB_ADD_OP || type == MG_TB_MUL_OP) {
+      int zx = a[0] > a[3] ? a[0] : a[3], zy = a[1] > a[4] ? a[1] : a[4], zz = a[2] > a[5] ? a[2] : a[5];
+      touch(a[6], a[0] * a[1] * a[2]).only_b_operand = false;
+      touch(a[7], a[3] * a[4] * a[5]).only_b_operand = false;
+      touch(a[8], zx * zy * zz).only_loaded = false;
+    } else if (type >= MG_TB_REDUCTION_0_OP && type <= MG_TB_REDUCTION_2_TO_DIMX_OP) {
+      touch(a[3], a[0] * a[1]).only_b_operand = false;
+      touch(a[4], a[0]).only_loaded = false;
+    } else if (type >= MG_TB_CONCAT_0_OP && type <= MG_TB_CONCAT_2_OP) {
+      int along = a[1] + a[2];
+      touch(a[4], along > 0 ? a[0] / along * a[1] : 0).only_b_operand = false;
+      touch(a[5], along > 0 ? a[0] / along * a[2] : 0).only_b_operand = false;
+      touch(a[6], a[0]).only_loaded = false;
+    } else if (type == 2002) {
+      touch(a[13], a[11] * a[12]).only_b_operand = false;
+      FpTile &acc = touch(a[14], a[11] * a[12]);
+      acc.only_loaded = false; acc.only_b_operand = false;
+    }
+  }
+  // a padded tile must really be a B operand of matching shape somewhere
+  for (int i = 0; i < n; i++) {
+    FpTile &t = tiles[i];
+    bool used_as_b = false;
+    for (int j = 0; j < in.num_ops; j++)
+      if (in.ops[j].type == MG_TB_MATMUL_OP && in.ops[j].a[4] == t.planned) {
+        used_as_b = true;
+        if (in.ops[j].a[2] != t.rows || in.ops[j].a[1] != t.cols) t.only_b_operand = false;
+      }
+    t.pad = (used_as_b && t.only_loaded && t.only_b_operand && t.rows > 0 && (t.cols * 2) % 128 == 0) ? 8 : 0;
+  }
+  // new offsets in planned order (insertion sort by planned offset: at most 72 tiles)
+  int order[3 * MGD_MAX_OPS];
+  for (int i = 0; i < n; i++) order[i] = i;
+  for (int i = 1; i < n; i++)
+    for (int j = i; j > 0 && tiles[order[j]].planned < tiles[order[j - 1]].planned; j--) {
+      int tmp = order[j]; order[j] = order[j - 1]; order[j - 1] = tmp;
+    }
+  size_t at = 0;
+  for (int i = 0; i < n; i++) {
+    FpTile &t = tiles[order[i]];
+    t.offset = (int)at;
+    size_t bytes = t.pad ? (size_t)t.rows * (t.cols + t.pad) * 2 : (size_t)t.elems * 2;
+    at += (bytes + 15) & ~(size_t)15;
+  }
+  *smem_bytes = at + 16;
+  auto find = [&](int planned) -> FpTile const & {
+    for (int i = 0; i < n; i++)
+      if (tiles[i].planned == planned) return tiles[i];
+    return tiles[0];
+  };
+  *out = in;
+  for (int i = 0; i < in.num_ops; i++) {
+    int32_t const *a = in.ops[i].a;
+    int32_t *w = out->ops[i].a;
+    int const type = in.ops[i].type;
+    if (type == 2001) {
+      w[17] = find(a[17]).offset;
+      w[16] = (a[16] & 0xff) | (find(a[17]).pad << 8);
+    } else if (type == MG_TB_MATMUL_OP) {
+      w[3] = find(a[3]).offset; w[4] = find(a[4]).offset; w[5] = find(a[5]).offset;
+      w[6] = find(a[4]).pad ? a[1] + find(a[4]).pad : 0;
+    } else if (type == MG_TB_EXP_OP) {
+      w[0] = find(a[0]).offset;
+    } else if (type == MG_TB_DIV_OP || type == MG_TB_ADD_OP || type == MG_TB_MUL_OP) {
+      w[6] = find(a[6]).offset; w[7] = find(a[7]).offset; w[8] = find(a[8]).offset;
+    } else if (type >= MG_TB_REDUCTION_0_OP && type <= MG_TB_REDUCTION_2_TO_DIMX_OP) {
+      w[3] = find(a[3]).offset; w[4] = find(a[4]).offset;
+    } else if (type >= MG_TB_CONCAT_0_OP && type <= MG_TB_CONCAT_2_OP) {
+      w[4] = find(a[4]).offset; w[5] = find(a[5]).offset; w[6] = find(a[6]).offset;
+    } else if (type == 2002) {
+      w[13] = find(a[13]).offset; w[14] = find(a[14]).offset;
+    }
+  }
+}
+} // namespace
 } // namespace mgk
 
 using namespace mgk;
@@ -258,8 +374,16 @@ using namespace mgk;
 extern "C" int mgd_launch_fingerprint_interp(const mgd_program *prog, const mgd_bindings *bind, void *stream) {
   int st = validate_program(prog, bind);
   if (st != MG_OK) return st;
-  size_t smem = (size_t)prog->smem_bytes + 16;
+  // padded operands when they fit, else the reference's dense plan as it is
+  mgd_program padded;
+  size_t smem = 0;
+  pad_b_operands(*prog, &padded, &smem);
+  if (smem > (size_t)kSmemLimit) {
+    padded = *prog;
+    smem = (size_t)prog->smem_bytes + 16;
+  }
   if (smem > (size_t)kSmemLimit) return set_error(MG_ERR_UNSUPPORTED, "threadblock graph needs more shared memory than an SM has");
+  prog = &padded;
   static size_t configured = 0;
   if (smem > 48 * 1024 && smem > configured) {
     if (cudaFuncSetAttribute(fp_interp_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess)

@@ -160,6 +160,16 @@ int mg_graph_customized_program(mg_graph *g, int32_t op_idx, void *program_out, 
  * 0 switches the mask off.  Fingerprint mode ignores it. */
 int mg_graph_customized_set_causal_window(mg_graph *g, int32_t op_idx, int32_t window);
 
+/* ---- batched verification ---------------------------------------------------
+ * The search's verify step (src/search/search.cc:569-623: run every candidate's fingerprint kernels, then
+ * DTensor::has_same_fingerprint against the computation graph, one device synchronisation and two blocking
+ * copies per candidate) as one batch: the fingerprint kernels of all n candidate graphs (inputs already in place)
+ * and the n comparisons of outputs[i] with `reference` are enqueued on `stream` back to back; one synchronisation
+ * and one copy of n flags at the end.  same[i] = 1 when candidate i's output equals the reference bit for bit
+ * (0 also when the shapes differ). */
+int mg_verify_candidates(mg_runtime *rt, const mg_tensor *reference, mg_graph *const *candidates,
+                         const mg_tensor *outputs, int32_t n, int32_t *same, void *stream);
+
 /* ---- graph JSON wire format ------------------------------------------------
  * replaces to_json(json&, Graph const&) / from_json(json const&, Graph&) (src/kernel/graph.cc:33-159) and the
  * operators' `operator json()`; documents are exchanged as text (see include/mirage/utils/json_utils.h).

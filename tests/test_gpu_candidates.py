@@ -85,3 +85,31 @@ def test_candidates_in_float_mode(runtime):
             got = from_bits(out.download_data(), mg.float16).reshape(out.shape)
         assert_close(got, want, mg.float16, "candidate structure %d" % len(seen))
     assert len(seen) >= 9
+
+
+def test_batched_verification(runtime):
+    """mg_verify_candidates: every candidate resident at once, fingerprint kernels and on-device comparisons enqueued
+    back to back, one synchronisation.  One candidate gets different inputs and must be reported as different."""
+    import contextlib
+    runtime.set_max_smem(BIG)
+    fx = load_fixture()
+    rng = np.random.default_rng(8)
+    with contextlib.ExitStack() as stack:  # graphs are released in reverse order of creation (LIFO arena)
+        ref = stack.enter_context(mg.PyGraph.from_json(fx["computation_graph"], runtime))
+        ref_in = inputs_of(ref)
+        x = [rng.integers(0, mo.FP_PQ, size=t.shape).astype(np.uint16) for t in ref_in]
+        for t, a in zip(ref_in, x):
+            t.upload_fingerprint(a)
+        ref.fingerprint()
+        ref_out = ref.operator(ref.num_operators - 1)[1][0]
+        batch = []
+        odd = 17
+        for n, doc in enumerate(fx["generated_graphs"]):
+            g = stack.enter_context(mg.PyGraph.from_json(doc, runtime))
+            for i, (t, a) in enumerate(zip(inputs_of(g), x)):
+                t.upload_fingerprint((a + 1) % mo.FP_PQ if (n == odd and i == 0) else a)
+            batch.append((g, g.operator(g.num_operators - 1)[1][0]))
+        verdict = mg.verify_candidates(ref_out, batch)
+        assert len(verdict) == 69
+        assert verdict == [n != odd for n in range(69)]
+        assert mg.verify_candidates(ref_out, []) == []
