@@ -137,7 +137,7 @@ def run_ours(args):
     calls = args.calls_per_step if args.calls_per_step > 0 else max(nsets, 64)
     arena = nsets * (2 * set_bytes + (1 << 20)) + (1 << 28) + (3 << 29)   # + room for the other configs' graphs
     rt = mg.Runtime.get(device=local_rank, arena_bytes=arena)
-    rt.set_specialisation(not args.interpreter_only)
+    rt.set_specialisation(0 if args.interpreter_only else args.specialisation)
     stream = torch.cuda.Stream()
     sh = stream.cuda_stream
 
@@ -426,7 +426,7 @@ def run_one_config(args):
 
     torch.cuda.set_device(0)
     rt = mg.Runtime.get(device=0, arena_bytes=3 << 30)
-    rt.set_specialisation(not args.interpreter_only)
+    rt.set_specialisation(0 if args.interpreter_only else args.specialisation)
     stream = torch.cuda.Stream()
 
     def timed(fn, steps, warmup):
@@ -643,6 +643,8 @@ def main():
                     help="DmemLayout of V[heads, kv, d]: row = memory [kv][d] (KV-cache order), col = memory [d][kv]")
     ap.add_argument("--streams", type=int, default=8, help="streams the independent calls of a step are spread over")
     ap.add_argument("--interpreter-only", action="store_true", help="disable the specialised kernels")
+    ap.add_argument("--specialisation", type=int, default=2, choices=[0, 1, 2],
+                    help="0 = interpreters, 1 = specialised kernels without operator fusion, 2 = with fusion (default)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-other-configs", action="store_true", help="skip the extra measurements of configs 1, 3 and 4")
     ap.add_argument("--no-latency-probes", action="store_true",
