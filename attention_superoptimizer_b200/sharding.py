@@ -46,6 +46,12 @@ def all_gather_fingerprints(local, world: int, group=None):
     return out
 
 
+def matches_reference_on_device(fingerprints, reference):
+    """The verify step on the device: `fingerprints` [n, m] and `reference` [m] are torch tensors on the same
+    device; returns a bool tensor [n] (True where the whole fingerprint equals the reference's)."""
+    return (fingerprints == reference.reshape(1, -1)).all(dim=1)
+
+
 def fingerprint_digest(row) -> bytes:
     """128-bit digest of one fingerprint (host side, for grouping)."""
     return hashlib.blake2b(row.tobytes(), digest_size=16).digest()

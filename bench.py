@@ -397,7 +397,13 @@ def run_fingerprint_sweep(args, mg, mo, fp_oracle, rt, torch, dist, np, rank, wo
             box = {}
             t_gather = timed(lambda: box.__setitem__("g", sharding.all_gather_fingerprints(local, world)), 1, 0)
             gathered = box["g"]
-        evals_per_s = (nchunks * chunk * world) / ((t_eval + t_gather) * 1e-3)
+        # compare on every rank: which of all the sets has the fingerprint of set 0 (the search's verify step)
+        from attention_superoptimizer_b200 import sharding as _sh
+        all_rows = gathered.view(-1, out[0].num_elements)
+        box = {}
+        t_compare = timed(lambda: box.__setitem__("m", _sh.matches_reference_on_device(all_rows, all_rows[0])), 1, 1)
+        equal_to_first = int(box["m"].sum().item())
+        evals_per_s = (nchunks * chunk * world) / ((t_eval + t_gather + t_compare) * 1e-3)
         # bit-exact check of a sample against the CPU oracle
         checked, ok = 0, True
         if rank == 0:
@@ -414,7 +420,8 @@ def run_fingerprint_sweep(args, mg, mo, fp_oracle, rt, torch, dist, np, rank, wo
         info = g.customized_info(3)
     return {"metric": "fingerprint_evals_per_s", "value": round(evals_per_s, 1), "unit": "evals/s",
             "sets": nchunks * chunk * world, "sets_per_gpu": nchunks * chunk, "chunk_sets": chunk,
-            "eval_ms": round(t_eval, 3), "allgather_ms": round(t_gather, 3),
+            "eval_ms": round(t_eval, 3), "allgather_ms": round(t_gather, 3), "compare_ms": round(t_compare, 3),
+            "sets_equal_to_first": equal_to_first,
             "bytes_per_eval": 16793600, "hbm_gbs_per_gpu": round(16793600 * nchunks * chunk / (t_eval * 1e-3) / 1e9, 1),
             "kernel_op1": info["kernel_fingerprint"], "oracle_checked_sets": checked, "bit_exact": bool(ok)}
 

@@ -79,6 +79,9 @@ def test_two_rank_sweep_matches_single_process(tmp_path):
     groups = sharding.dedup(want)
     assert groups[1] == [1, 4] and sorted(groups) == [0, 1, 2, 3, 5]
     assert sharding.matches_reference(want, want[4]) == [False, True, False, False, True, False]
+    import torch
+    t = torch.from_numpy(want.astype(np.int32))
+    assert sharding.matches_reference_on_device(t, t[4]).tolist() == [False, True, False, False, True, False]
 
 
 def failing_worker(rank, world, port, result_dir):
