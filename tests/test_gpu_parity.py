@@ -291,6 +291,34 @@ def test_float_baseline_c2_full_size(rt):
         assert 0 < ms < 1000
 
 
+def test_float_spec_decode_c3_full_size(runtime):
+    """BASELINE config 3 at full size: 32 (batch x KV head) units, 8 draft tokens x group 4 = 32 query rows, KV 8192,
+    16 splits x for-loop 8, causal draft window, K column-major / V row-major as the benchmark runs it: 512 work items
+    on the persistent tcgen05 kernel (3 or 4 per block) plus the merge kernel; the `mma.sync` engine on the same
+    inputs must agree with the same oracle."""
+    B, M, D, L, S, F, W = 32, 32, 128, 8192, 16, 8, 8
+    rng = np.random.default_rng(33)
+    runtime.set_max_smem(BIG)
+    runtime.set_specialisation(True)
+    kl, vl = mg.DmemColumnMajor, mg.DmemRowMajor
+    with mg.PyGraph(runtime) as g:
+        ins, o, f, plans = build_gqa(g, B, M, D, L, S, F, kl, vl)
+        g.set_causal_window(3, W)
+        (q, k, v), mem = float_inputs(rng, B, M, D, L, kl, vl, mg.float16)
+        for t, a in zip(ins, mem):
+            t.upload_data(to_bits(a, mg.float16))
+        want = mo.attention_fp32_causal_window(q, k, v, W)
+        for engine in ("1", "0"):
+            os.environ["MUGRAPH_ATTN_TC"] = engine
+            try:
+                g.run()
+                g.run()  # again: barriers, tensor memory and the launch order are set up afresh by every launch
+            finally:
+                del os.environ["MUGRAPH_ATTN_TC"]
+            final = from_bits(f[0].download_data(), mg.float16).reshape(f[0].shape)
+            assert_close(final, want, mg.float16, "masked output, engine %s" % engine)
+
+
 def build_prefill(g, H, SQ, D, L, dtype, kl=mg.DmemColumnMajor, vl=mg.DmemColumnMajor):
     Q = g.new_input((H, SQ, D), dtype)
     K = g.new_input((H, D, L), dtype, kl)
