@@ -33,14 +33,16 @@ def kv_head_shard(num_kv_heads: int, rank: int, world: int) -> Tuple[int, int]:
     return rank * per, per
 
 
-def all_gather_fingerprints(local, world: int, group=None):
+def all_gather_fingerprints(local, world: int, group=None, out=None):
     """All-gather of per-set fingerprints.  `local` is a [sets_per_rank, n] int16/uint16 tensor (CUDA with
-    NCCL, CPU with gloo); every rank must pass the same shape.  Returns [world * sets_per_rank, n]."""
+    NCCL, CPU with gloo); every rank must pass the same shape.  Returns [world * sets_per_rank, n]; `out` is an
+    optional preallocated tensor of that shape and dtype (keeps the allocator out of a timed region)."""
     import torch
     import torch.distributed as dist
     if world == 1:
         return local
-    out = torch.empty((world * local.shape[0],) + tuple(local.shape[1:]), dtype=local.dtype, device=local.device)
+    if out is None:
+        out = torch.empty((world * local.shape[0],) + tuple(local.shape[1:]), dtype=local.dtype, device=local.device)
     # moved as bytes: 16-bit integer types are not accepted by every backend
     dist.all_gather_into_tensor(out.view(torch.uint8), local.contiguous().view(torch.uint8), group=group)
     return out

@@ -406,10 +406,8 @@ def run_fingerprint_sweep(args, mg, mo, fp_oracle, rt, torch, dist, np, rank, wo
         if world > 1:
             from attention_superoptimizer_b200 import sharding
             local = result.view(my_sets, -1)
-            gathered = sharding.all_gather_fingerprints(local, world)   # warm-up (sets up the communicator)
-            box = {}
-            t_gather = timed(lambda: box.__setitem__("g", sharding.all_gather_fingerprints(local, world)), 1, 0)
-            gathered = box["g"]
+            gathered = torch.empty((world * my_sets, local.shape[1]), dtype=local.dtype, device=local.device)
+            t_gather = timed(lambda: sharding.all_gather_fingerprints(local, world, out=gathered), 1, 2)  # 2 warm-ups
         # compare on every rank: which of all the sets has the fingerprint of set 0 (the search's verify step)
         from attention_superoptimizer_b200 import sharding as _sh
         all_rows = gathered.view(-1, out[0].num_elements)
