@@ -122,6 +122,8 @@ def run_ours(args):
     from oracle import fp_oracle, mugraph_oracle as mo
 
     rank, local_rank, world = dist_env()
+    if args.streams <= 0:
+        args.streams = 8 if world == 1 else (16 if world == 2 else 32)
     if world != args.gpus:
         if world == 1 and args.gpus > 1:
             raise SystemExit("--gpus %d needs torchrun with %d ranks" % (args.gpus, args.gpus))
@@ -660,7 +662,9 @@ def main():
                     help="DmemLayout of K[heads, d, kv]: col = memory [kv][d] (KV-cache order), row = memory [d][kv]")
     ap.add_argument("--v-layout", default="row", choices=["row", "col"],
                     help="DmemLayout of V[heads, kv, d]: row = memory [kv][d] (KV-cache order), col = memory [d][kv]")
-    ap.add_argument("--streams", type=int, default=8, help="streams the independent calls of a step are spread over")
+    ap.add_argument("--streams", type=int, default=0,
+                    help="streams the independent calls of a step are spread over (0 = 8 per rank at N = 1, 16 at N = 2, "
+                         "32 from N = 4: the fewer KV heads a rank holds, the more calls fit on the GPU at once)")
     ap.add_argument("--interpreter-only", action="store_true", help="disable the specialised kernels")
     ap.add_argument("--specialisation", type=int, default=2, choices=[0, 1, 2],
                     help="0 = interpreters, 1 = specialised kernels without operator fusion, 2 = with fusion (default)")
