@@ -32,8 +32,8 @@
 //                      buffer.  After an item's last tile the row sums are reduced over each warp's 32 lanes and
 //                      handed over in shared memory.
 //   warps 6-9          epilogue, off the tile pipeline: add the four warps' row sums, read O^T (one thread per
-//                      head-dim index), store the split's partial output, and - fused merge - the block that
-//                      finishes a head last sums the head's partials and divides.
+//                      head-dim index), store the split's partial output.  (The cross-split merge is a second,
+//                      small kernel launched right behind this one.)
 // Every wait on an mbarrier is bounded; a role that gives up raises a block-wide flag, the others stop at their
 // next wait, the block frees its tensor memory, records the failure in the device status word and returns.
 #include "common.cuh"
@@ -87,10 +87,9 @@ __device__ __forceinline__ uint64_t k_major_step(int ks) { return (uint64_t)(((k
 __device__ __forceinline__ uint64_t mn_major_step(int ks) { return (uint64_t)((ks * 16 * 128) >> 4); }
 
 struct Params {
-  void *o_part, *r_part, *merged_out;
-  int32_t *tickets;
+  void *o_part, *r_part;
   int32_t *status;
-  long long o_set_stride, r_set_stride, merged_set_stride;
+  long long o_set_stride, r_set_stride;
   int heads, m, splits, tiles, kv_len, causal_window, num_items;
   int early_loads; // the inputs were not written by the previous kernel of the stream: load before waiting for it
 };
@@ -100,7 +99,6 @@ struct Shared {
   uint64_t q_full[2], q_empty[2], s_full[2], e_full[2], e_free[2], o_full[2], o_free[2], r_full[2], r_free[2];
   uint32_t tmem_base;
   int abort_flag;
-  int last_flag;
   float rsum[2][4][kNQ]; // [item parity][exp warp][query column]
 };
 
@@ -393,7 +391,7 @@ attn_split_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_con
     // merge of the call before, which reads the partials written below) is still going: no global store before it
     // has completed.
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    TDECL(w_r = 0, w_o = 0, c_out = 0, c_tick = 0, c_merge = 0, t0 = clock64());
+    TDECL(w_r = 0, w_o = 0, c_out = 0, t0 = clock64());
     for (int li = 0; li < my_items; li++) {
       int const ob = li & 1, item = item_of(li), batch = batch_of(item), split = split_of(item);
       int const set = batch / p.heads, head = batch % p.heads;
@@ -427,40 +425,17 @@ attn_split_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_con
         }
       }
       TOCK(c_out, a2);
-      TICK(a3);
-      // ---- fused merge: the block that completes a head last sums its partials and divides ----------------
-      if (p.merged_out != nullptr) { // uniform over the block
-        __threadfence();
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (et == 0) {
-          int ticket = ok ? atomicAdd(&p.tickets[batch], 1) : -1;
-          sh->last_flag = ticket == p.splits - 1;
-          if (ticket == p.splits - 1) p.tickets[batch] = 0; // ready for the next launch
-        }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        TOCK(c_tick, a3);
-        TICK(a4);
-        if (sh->last_flag) {
-          __threadfence();
-          int const out_ld = p.splits * kD;
-          uint16_t const *op = static_cast<uint16_t const *>(p.o_part) + set * p.o_set_stride + (long long)head * p.m * out_ld;
-          uint16_t const *rp = static_cast<uint16_t const *>(p.r_part) + set * p.r_set_stride + (long long)head * p.m * p.splits;
-          uint16_t *dst = static_cast<uint16_t *>(p.merged_out) + set * p.merged_set_stride + (long long)head * p.m * kD;
-          merge_head<BF16 ? kMergeBF16 : kMergeF16, kD>(op, rp, dst, p.m, p.splits, et, 128);
-        }
-        TOCK(c_merge, a4);
-      }
     }
 #ifdef MG_STC_TIMING
     if (et == 0) {
       unsigned long long gt_now;
       asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt_now));
       if (gt_now - gt_entry > 36000)
-        printf("slow [%d] epilogue done +%llu ns: wait r_full %lld o_full %lld out %lld fence+ticket %lld merge %lld items %d\n", (int)blockIdx.x,
-               gt_now - gt_entry, w_r, w_o, c_out, c_tick, c_merge, my_items);
+        printf("slow [%d] epilogue done +%llu ns: wait r_full %lld o_full %lld out %lld items %d\n", (int)blockIdx.x,
+               gt_now - gt_entry, w_r, w_o, c_out, my_items);
     }
 #endif
-    if (et == 0) TPRINT("[%d] epilogue: total %lld wait r_full %lld o_full %lld out %lld fence+ticket %lld merge %lld items %d\n", (int)blockIdx.x, clock64() - t0, w_r, w_o, c_out, c_tick, c_merge, my_items);
+    if (et == 0) TPRINT("[%d] epilogue: total %lld wait r_full %lld o_full %lld out %lld items %d\n", (int)blockIdx.x, clock64() - t0, w_r, w_o, c_out, my_items);
   }
 
   // ---- teardown: every role arrives here, failed or not --------------------------------------------------
@@ -551,9 +526,6 @@ int launch(mgd_attn_split const *p, void const *q, void const *k, void const *v,
   // The merge runs as a second, small kernel right behind this one (programmatic serialisation hides its launch):
   // inside the persistent kernel the block that finishes a head last would merge serially, and a block that is
   // last once tends to be last again.
-  a.merged_out = nullptr;
-  a.tickets = nullptr;
-  a.merged_set_stride = 0;
   a.status = device_error_word();
   if (!a.status) return set_error(MG_ERR_CUDA, "cannot allocate the device status word");
   a.o_set_stride = p->o_set_stride; a.r_set_stride = p->r_set_stride;

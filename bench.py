@@ -272,7 +272,7 @@ def run_ours(args):
     roofline = {"bound": "hbm", "kernel": "split-KV attention operator (op1)", "achieved": round(achieved, 1),
                 "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": round(achieved / peaks["hbm_gbs"], 4),
                 "peak_source": peak_src,
-                "traffic": 16864512 if world == 1 else None,
+                "traffic": 16853248 if world == 1 else None,
                 "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of one launch, ncu capture "
                                   "profiles/attn_split_fp16_gqa_decode.md (same shapes, N = 1)",
                 "bytes_per_launch": op1_bytes,
