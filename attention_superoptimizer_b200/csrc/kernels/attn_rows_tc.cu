@@ -32,6 +32,7 @@
 // at their next wait, the block frees its tensor memory, records the failure in the device status word and
 // returns.
 #include "common.cuh"
+#include "tcgen05.cuh"
 #include <cstdio>
 #include <cstdlib>
 #include <cuda.h>
@@ -349,15 +350,14 @@ attn_rows_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
       if (j < 16) es[j] = clock64() - t_all;
 #endif
       uint32_t packed[2][16]; // this thread's 64 values as 16-bit pairs
+      {
+        uint32_t v[64];
+        t5::tmem_ld64(tmem_s[b] + lane_base + col_base, v); // one load, one wait per tile
 #pragma unroll
-      for (int c = 0; c < 2; c++) {
-        uint32_t v[32];
-        tmem_ld32(tmem_s[b] + lane_base + col_base + (uint32_t)(c * 32), v);
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float e0 = __expf(__uint_as_float(v[i])), e1 = __expf(__uint_as_float(v[i + 1]));
+        for (int i = 0; i < 64; i += 2) {
+          float e0 = t5::exp_ftz(__uint_as_float(v[i])), e1 = t5::exp_ftz(__uint_as_float(v[i + 1]));
           rsum += e0 + e1;
-          packed[c][i >> 1] = pack2<BF16>(e0, e1);
+          packed[i >> 5][(i & 31) >> 1] = pack2<BF16>(e0, e1);
         }
       }
       TOCK(c_exp, b1);
