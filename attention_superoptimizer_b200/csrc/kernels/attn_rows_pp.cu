@@ -189,7 +189,7 @@ attn_rows_pp_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
       }
       __syncwarp();
     }
-    TDECL(w_e0 = 0, w_e1 = 0, w_kv = 0, c_issue = 0, t0 = clock64());
+    TDECL(w_e0 = 0, w_e1 = 0, w_kv = 0, c_issue = 0, c_o = 0, c_c = 0, c_s = 0, t0 = clock64());
     for (int j = 0; j < F && ok; j++) {
       for (int i = 0; i < 2 && ok; i++) {
         TICK(a0);
@@ -203,16 +203,22 @@ attn_rows_pp_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
         tc_fence_after();
         TICK(a2);
         if (lane == 0) {
+          TICK(b0);
           issue_o(i, j);
+          TOCK(c_o, b0);
+          TICK(b1);
           if (i == 1) umma_commit(smem_u32(&sh->kv_empty[j % kStages])); // K_j, V_j consumed by both tiles
           if (j == F - 1) umma_commit(smem_u32(&sh->o_full[i]));
+          TOCK(c_c, b1);
+          TICK(b2);
           if (j + 1 < F) issue_s(i, j + 1);
+          TOCK(c_s, b2);
         }
         __syncwarp();
         TOCK(c_issue, a2);
       }
     }
-    if (lane == 0) TPRINT("mma: total %lld wait e_full0 %lld e_full1 %lld kv_full %lld issue %lld (%d kv tiles)\n", clock64() - t0, w_e0, w_e1, w_kv, c_issue, F);
+    if (lane == 0) TPRINT("mma: total %lld wait e_full0 %lld e_full1 %lld kv_full %lld issue %lld = O %lld + commits %lld + S(incl. its commit) %lld (%d kv tiles)\n", clock64() - t0, w_e0, w_e1, w_kv, c_issue, c_o, c_c, c_s, F);
   } else {
     // ------------------------------------------------------------------ exp / row sums / epilogue of one query tile
     int const i = (warp - 2) >> 3;                // query tile of this warp
