@@ -199,6 +199,70 @@ def test_interpreter_matmul_shapes_and_full_range(runtime, mkn):
         runtime.set_specialisation(2)
 
 
+def interpreter_corner_plans():
+    """Plans that exercise the interpreters' own memory planning: operands stored with padded rows or not, tiles
+    loaded once or every iteration, in-place exp on an input tile, a matmul adding straight into the accumulator."""
+    P = mo.ExecutionPlan
+    row = [mo.SmemRowMajor]
+    return {
+        # exp in place on an input tile that does not move with the for-loop (must be reloaded every iteration),
+        # then used as the A operand; B (64 x 64: dense pitch 128 B) is padded
+        "exp_on_invariant_input": ([(8, 64), (128, 64)],
+                                   P(ops=[(mo.TB_EXP_OP, [(0, 0)]), (mo.TB_MATMUL_OP, [(2, 0), (1, 0)])],
+                                     input_map=[(-1, -1, -1), (-1, -1, -1)], forloop_dim=[-1, 0], input_smem_layouts=row * 2,
+                                     output_map=(-1, -1, -1), forloop_range=2, grid_dim=(1, 1, 1))),
+        # the same loaded tile is B of one matmul and A of another: not padded
+        "tile_as_a_and_b": ([(64, 64), (16, 64)],
+                            P(ops=[(mo.TB_MATMUL_OP, [(1, 0), (0, 0)]), (mo.TB_MATMUL_OP, [(0, 0), (0, 0)]),
+                                   (mo.TB_MATMUL_OP, [(2, 0), (3, 0)])],
+                              input_map=[(-1, -1, -1), (-1, -1, -1)], forloop_dim=[-1, -1], input_smem_layouts=row * 2,
+                              output_map=(-1, -1, -1), forloop_range=1, grid_dim=(1, 1, 1))),
+        # a computed tile (matmul result) is the B operand of the next matmul; two outputs
+        "computed_b_operand": ([(16, 32), (32, 64), (48, 16)],
+                               P(ops=[(mo.TB_MATMUL_OP, [(0, 0), (1, 0)]), (mo.TB_MATMUL_OP, [(2, 0), (3, 0)]),
+                                      (mo.TB_REDUCTION_1_OP, [(3, 0)])],
+                                 input_map=[(-1, -1, -1), (1, -1, -1), (-1, -1, -1)], forloop_dim=[-1, -1, -1],
+                                 input_smem_layouts=row * 3, output_map=(1, -1, -1), forloop_range=1, grid_dim=(2, 1, 1))),
+        # concat of two loaded tiles feeds a matmul as B; B rows of 64 elements; grid over y, for-loop over k
+        "concat_into_matmul": ([(3, 8, 64), (3, 64, 32), (3, 64, 32)],
+                               P(ops=[(mo.TB_CONCAT_2_OP, [(1, 0), (2, 0)]), (mo.TB_MATMUL_OP, [(0, 0), (3, 0)])],
+                                 input_map=[(0, -1, -1), (0, -1, -1), (0, -1, -1)], forloop_dim=[2, 1, 1],
+                                 input_smem_layouts=row * 3, output_map=(0, -1, -1), forloop_range=2, grid_dim=(3, 1, 1))),
+        # wide padded B (16 x 256), loop-invariant, A moves with the for-loop; division by a loaded tile
+        "invariant_wide_b": ([(4, 64), (16, 256), (4, 256)],
+                             P(ops=[(mo.TB_MATMUL_OP, [(0, 0), (1, 0)]), (mo.TB_DIV_OP, [(3, 0), (2, 0)])],
+                               input_map=[(-1, -1, -1), (-1, -1, -1), (-1, -1, -1)], forloop_dim=[1, -1, -1],
+                               input_smem_layouts=row * 3, output_map=(-1, -1, -1), forloop_range=4, grid_dim=(1, 1, 1))),
+    }
+
+
+@pytest.mark.parametrize("name", sorted(interpreter_corner_plans()))
+def test_interpreter_corner_plans(runtime, name):
+    dims, plan = interpreter_corner_plans()[name]
+    runtime.set_max_smem(BIG)
+    runtime.set_specialisation(0)
+    try:
+        specs = [mo.DTensorSpec(d) for d in dims]
+        run_generic_fp(runtime, specs, plan, 5)
+        rng = np.random.default_rng(6)
+        # the third tensor (a divisor in one plan) stays away from zero
+        x = [from_bits(to_bits(rng.standard_normal(s.dims) * 0.1 + (1.0 if i == 2 else 0.0), mg.float16), mg.float16)
+             for i, s in enumerate(specs)]
+        with mg.PyGraph(runtime) as g:
+            ins = [g.new_input(s.dims, s.dtype, s.layout) for s in specs]
+            for t, a in zip(ins, x):
+                t.upload_data(to_bits(a, mg.float16))
+            outs = g.customized(ins, to_package_plan(plan))
+            g.run()
+            got = [from_bits(t.download_data(), mg.float16).reshape(t.shape) for t in outs]
+        want = mo.run_float(mo.build_customized(specs, plan, max_smem=BIG), x)
+        assert len(got) == len(want)
+        for a, b in zip(got, want):
+            assert_close(a, b, mg.float16, name)
+    finally:
+        runtime.set_specialisation(2)
+
+
 def float_inputs(rng, B, M, D, L, kl, vl, dtype):
     """Logical tensors rounded to storage precision, plus their memory images."""
     rnd = lambda a: from_bits(to_bits(a, dtype), dtype)
