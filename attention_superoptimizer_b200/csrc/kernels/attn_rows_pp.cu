@@ -244,12 +244,17 @@ attn_rows_pp_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
         tmem_ld64(s_tmem, v); // one load, one wait: the tensor-memory latency is paid once per tile
         TOCK(c_ld, a1);
         TICK(a2);
+        uint64_t sum2 = 0; // packed arithmetic: the exp warps share their schedulers with the MMA-issuing lane
 #pragma unroll
         for (int x = 0; x < 64; x += 2) {
-          float e0 = exp_ftz(__uint_as_float(v[x])), e1 = exp_ftz(__uint_as_float(v[x + 1]));
-          rsum += e0 + e1;
+          float e0, e1;
+          exp_ftz2(pair(__uint_as_float(v[x]), __uint_as_float(v[x + 1])), e0, e1);
+          sum2 = add2(sum2, pair(e0, e1));
           flat[x >> 1] = pack2<BF16>(e0, e1);
         }
+        float s0, s1;
+        unpair(sum2, s0, s1);
+        rsum += s0 + s1;
         TOCK(c_exp, a2);
       }
       TICK(a3);

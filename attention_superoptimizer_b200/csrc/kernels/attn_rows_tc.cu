@@ -353,12 +353,17 @@ attn_rows_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
       {
         uint32_t v[64];
         t5::tmem_ld64(tmem_s[b] + lane_base + col_base, v); // one load, one wait per tile
+        uint64_t sum2 = 0; // packed arithmetic: fewer issue slots taken from the MMA-issuing lane
 #pragma unroll
         for (int i = 0; i < 64; i += 2) {
-          float e0 = t5::exp_ftz(__uint_as_float(v[i])), e1 = t5::exp_ftz(__uint_as_float(v[i + 1]));
-          rsum += e0 + e1;
+          float e0, e1;
+          t5::exp_ftz2(t5::pair(__uint_as_float(v[i]), __uint_as_float(v[i + 1])), e0, e1);
+          sum2 = t5::add2(sum2, t5::pair(e0, e1));
           packed[i >> 5][(i & 31) >> 1] = pack2<BF16>(e0, e1);
         }
+        float s0, s1;
+        t5::unpair(sum2, s0, s1);
+        rsum += s0 + s1;
       }
       TOCK(c_exp, b1);
       TICK(b3);

@@ -123,6 +123,43 @@ __device__ __forceinline__ float exp_ftz(float x) {
   return y;
 }
 
+// ---- two fp32 values per instruction (sm_100 packed arithmetic): half the issue slots of the scalar forms, which
+// matters beside a lane that issues MMAs (the exp warps share its scheduler) ------------------------------------------
+__device__ __forceinline__ uint64_t pair(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpair(uint64_t v, float &lo, float &hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__host__ __device__ constexpr uint64_t pair_bits(uint32_t bits) { return ((uint64_t)bits << 32) | bits; }
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ uint64_t sub2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+// exp of two values on the MUFU unit, the scaling by log2(e) done for both at once
+__device__ __forceinline__ void exp_ftz2(uint64_t x, float &e0, float &e1) {
+  float y0, y1;
+  unpair(mul2(x, pair_bits(0x3FB8AA3Bu)), y0, y1);
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e0) : "f"(y0));
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e1) : "f"(y1));
+}
+
 template <bool BF16> __device__ __forceinline__ uint32_t pack2(float a, float b) {
   if (BF16) {
     __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
