@@ -13,10 +13,17 @@
 //   * every computed tile is fp32, so chained operators do not round to 16 bits between steps;
 //   * a matmul whose result feeds nothing but an output operator adds straight into that operator's
 //     accumulator and the result tile is not allocated;
-//   * an input tile that does not move with the for-loop is loaded in the first iteration only.
+//   * an input tile that does not move with the for-loop is loaded in the first iteration only;
+//   * a matmul whose B operand is such a 16-bit tile (n % 8 == 0, k % 16 == 0) runs on the tensor cores
+//     (mma.sync m16n8k16, fp32 accumulate): its A operand, 16-bit or computed fp32, is staged as 16-bit rows in a
+//     region behind the tiles, B tiles that only such matmuls read get 16 bytes of row padding (both for
+//     conflict-free ldmatrix); other matmuls run on the CUDA cores;
+//   * the kernel's copy of the operator table and the bindings sits behind all of that.
 // Loads honour the tensor's DmemLayout: a column-major tensor keeps each [rows, cols] matrix with the
 // row index contiguous.  Outputs are rounded to nearest on store.
 #include "common.cuh"
+#include <cstdio>
+#include <cstdlib>
 
 namespace mgk {
 int validate_program(mgd_program const *p, mgd_bindings const *b);
@@ -24,6 +31,7 @@ int validate_program(mgd_program const *p, mgd_bindings const *b);
 // flag bits the host packs into operator arguments after replanning
 constexpr int kIn16 = 1 << 8;         // input a[16]: the tile keeps 16-bit elements
 constexpr int kInInvariant = 1 << 9;  // input a[16]: same tile every iteration, load once
+constexpr int kInPadShift = 16;       // input a[16] bits 16-23: elements of padding after every tile row
 
 template <typename T> __device__ __forceinline__ void cvt4(uint2 w, float *f);
 template <> __device__ __forceinline__ void cvt4<__half>(uint2 w, float *f) {
@@ -41,75 +49,155 @@ template <typename T> __device__ __forceinline__ float rd(unsigned char const *t
   return is16 ? to_float<T>(reinterpret_cast<T const *>(tile)[i]) : reinterpret_cast<float const *>(tile)[i];
 }
 
-// C (fp32, m x n) = or += A (m x k) B (k x n), all row-major in shared memory.  Threads own 4x4 or 1x4
-// patches of C (registers) when n is a multiple of four, so a B row segment is one vector load.
-template <typename T, bool A16, bool B16>
-__device__ void matmul_tiles(unsigned char const *Ap, unsigned char const *Bp, float *C, int m, int n, int k, bool add,
-                             int tid, int nt) {
-  auto a_at = [&](int idx) -> float {
-    return A16 ? to_float<T>(reinterpret_cast<T const *>(Ap)[idx]) : reinterpret_cast<float const *>(Ap)[idx];
-  };
-  auto b4_at = [&](int idx, float *f) {
-    if (B16) cvt4<T>(*reinterpret_cast<uint2 const *>(Bp + (size_t)idx * 2), f);
-    else {
-      float4 v = *reinterpret_cast<float4 const *>(Bp + (size_t)idx * 4);
-      f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
-    }
-  };
+// C (fp32, m x n) = or += A (m x k) B (k x n), all row-major in shared memory; either operand 16-bit or fp32.
+// Fallback for the shapes the tensor-core form below does not take.  One copy of the code with the operand
+// widths as run-time flags: the interpreter is bound by instruction fetch (every operator jumps to code that has
+// left the instruction cache), so a small footprint is worth more than the last FMA.
+template <typename T>
+__device__ __noinline__ void matmul_tiles(unsigned char const *Ap, unsigned char const *Bp, float *C, int m, int n, int k,
+                                          bool a16, bool b16, bool add, int tid, int nt) {
   if ((n & 3) == 0) {
     int const nq = n >> 2;
-    if ((m & 3) == 0 && (m >> 2) * nq >= nt) {
-      for (int i = tid; i < (m >> 2) * nq; i += nt) {
-        int const r = (i / nq) * 4, c = (i % nq) * 4;
-        float acc[4][4];
-#pragma unroll
-        for (int x = 0; x < 4; x++)
-#pragma unroll
-          for (int y = 0; y < 4; y++) acc[x][y] = 0.f;
-        for (int kk = 0; kk < k; kk++) {
-          float b[4];
-          b4_at(kk * n + c, b);
-#pragma unroll
-          for (int x = 0; x < 4; x++) {
-            float av = a_at((r + x) * k + kk);
-#pragma unroll
-            for (int y = 0; y < 4; y++) acc[x][y] = fmaf(av, b[y], acc[x][y]);
-          }
+    for (int i = tid; i < m * nq; i += nt) {
+      int const r = i / nq, c = (i % nq) * 4;
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+      for (int kk = 0; kk < k; kk++) {
+        float b[4];
+        if (b16) cvt4<T>(*reinterpret_cast<uint2 const *>(Bp + (size_t)(kk * n + c) * 2), b);
+        else {
+          float4 v = *reinterpret_cast<float4 const *>(Bp + (size_t)(kk * n + c) * 4);
+          b[0] = v.x; b[1] = v.y; b[2] = v.z; b[3] = v.w;
         }
+        float const av = rd<T>(Ap, a16, r * k + kk);
 #pragma unroll
-        for (int x = 0; x < 4; x++) {
-          float4 *dst = reinterpret_cast<float4 *>(C + (r + x) * n + c);
-          float4 v = make_float4(acc[x][0], acc[x][1], acc[x][2], acc[x][3]);
-          if (add) { float4 o = *dst; v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w; }
-          *dst = v;
-        }
+        for (int y = 0; y < 4; y++) acc[y] = fmaf(av, b[y], acc[y]);
       }
-    } else {
-      for (int i = tid; i < m * nq; i += nt) {
-        int const r = i / nq, c = (i % nq) * 4;
-        float acc[4] = {0.f, 0.f, 0.f, 0.f};
-        for (int kk = 0; kk < k; kk++) {
-          float b[4];
-          b4_at(kk * n + c, b);
-          float av = a_at(r * k + kk);
-#pragma unroll
-          for (int y = 0; y < 4; y++) acc[y] = fmaf(av, b[y], acc[y]);
-        }
-        float4 *dst = reinterpret_cast<float4 *>(C + r * n + c);
-        float4 v = make_float4(acc[0], acc[1], acc[2], acc[3]);
-        if (add) { float4 o = *dst; v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w; }
-        *dst = v;
-      }
+      float4 *dst = reinterpret_cast<float4 *>(C + r * n + c);
+      float4 v = make_float4(acc[0], acc[1], acc[2], acc[3]);
+      if (add) { float4 o = *dst; v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w; }
+      *dst = v;
     }
   } else {
     for (int i = tid; i < m * n; i += nt) {
       int const r = i / n, c = i % n;
       float acc = 0.f;
-      for (int kk = 0; kk < k; kk++) {
-        float bv = B16 ? to_float<T>(reinterpret_cast<T const *>(Bp)[kk * n + c]) : reinterpret_cast<float const *>(Bp)[kk * n + c];
-        acc = fmaf(a_at(r * k + kk), bv, acc);
-      }
+      for (int kk = 0; kk < k; kk++) acc = fmaf(rd<T>(Ap, a16, r * k + kk), rd<T>(Bp, b16, kk * n + c), acc);
       C[i] = add ? C[i] + acc : acc;
+    }
+  }
+}
+
+// ---- the same product on the tensor cores (mma.sync m16n8k16, fp32 accumulate) -----------------------------------
+// Taken when B keeps the tensor's 16-bit elements, n % 8 == 0 and k % 16 == 0.  A computed (fp32) A operand is
+// rounded to the tensor's 16-bit type as its fragments are built, which is what the reference's shared-memory tiles
+// hold anyway; rows of A past m enter as zeros and are not stored.  A warp owns a 16 x (8 NT) patch of C: the B
+// fragments come from ldmatrix (transposed; `b_pitch` elements between B rows, padded by the host when the dense
+// pitch would put the eight rows of a load on the same banks).
+template <typename T> __device__ __forceinline__ uint32_t pack_pair(float lo, float hi);
+template <> __device__ __forceinline__ uint32_t pack_pair<__half>(float lo, float hi) {
+  __half2 h = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t *>(&h);
+}
+template <> __device__ __forceinline__ uint32_t pack_pair<__nv_bfloat16>(float lo, float hi) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t *>(&h);
+}
+template <typename T> __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t const (&a)[4], uint32_t b0, uint32_t b1);
+template <> __device__ __forceinline__ void mma16816<__half>(float (&c)[4], uint32_t const (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+template <> __device__ __forceinline__ void mma16816<__nv_bfloat16>(float (&c)[4], uint32_t const (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// A is first written by the whole block as 16-bit rows of k + 8 elements into the staging room the host planned
+// (rows past m as zeros), so that its fragments come from one conflict-free ldmatrix per step: A's dense rows are a
+// multiple of 128 bytes apart for the usual k and four plain loads per step would share their banks.
+template <typename T>
+__device__ __noinline__ void stage_a(unsigned char const *Ap, bool a16, unsigned char *staged, int m, int k, int tid, int nt) {
+  int const half_k = k >> 1, rows = ((m + 15) >> 4) << 4, pitch2 = (k + 8) >> 1;
+  uint32_t *dst = reinterpret_cast<uint32_t *>(staged);
+  for (int i = tid; i < rows * half_k; i += nt) {
+    int const r = i / half_k, c2 = i % half_k;
+    uint32_t v = 0u;
+    if (r < m) {
+      if (a16) v = reinterpret_cast<uint32_t const *>(Ap)[(size_t)r * half_k + c2];
+      else {
+        float2 const x = reinterpret_cast<float2 const *>(Ap)[(size_t)r * half_k + c2];
+        v = pack_pair<T>(x.x, x.y);
+      }
+    }
+    dst[r * pitch2 + c2] = v;
+  }
+}
+
+template <typename T, int NT>
+__device__ __noinline__ void matmul_mma(unsigned char const *staged, unsigned char const *Bp, float *C, int m, int n, int k,
+                                        int b_pitch, bool add, int tid, int nt) {
+  int const lane = tid & 31, warp = tid >> 5, nwarps = nt >> 5;
+  int const g = lane >> 2, t = lane & 3, mi = lane >> 3, rr = lane & 7;
+  int const m_tiles = (m + 15) >> 4, n_units = n / (8 * NT);
+  int const a_pitch = k + 8;
+  uint32_t const a_base = (uint32_t)__cvta_generic_to_shared(staged), b_base = (uint32_t)__cvta_generic_to_shared(Bp);
+  for (int u = warp; u < m_tiles * n_units; u += nwarps) {
+    int const m0 = (u / n_units) * 16, n0 = (u % n_units) * 8 * NT;
+    int const r0 = m0 + g, r1 = m0 + g + 8;
+    bool const v0 = r0 < m, v1 = r1 < m;
+    float acc[NT][4];
+#pragma unroll
+    for (int x = 0; x < NT; x++)
+#pragma unroll
+      for (int y = 0; y < 4; y++) acc[x][y] = 0.f;
+    // ldmatrix addresses of this lane. A: row (mi % 2) * 8 + rr of the m-tile, k columns (mi / 2) * 8.  B
+    // (transposed load): k-row (mi % 2) * 8 + rr of the 8 columns starting at (mi / 2) * 8; with one n-tile per
+    // warp only lanes 0-15 supply addresses, the two k halves of the same 8 columns.
+    uint32_t aaddr = a_base + (uint32_t)(((m0 + (mi & 1) * 8 + rr) * a_pitch + (mi >> 1) * 8) * 2);
+    uint32_t baddr = b_base + (uint32_t)((((mi & 1) * 8 + rr) * b_pitch + n0 + (NT >= 2 ? (mi >> 1) * 8 : 0)) * 2);
+#pragma unroll 2
+    for (int k0 = 0; k0 < k; k0 += 16, baddr += (uint32_t)(16 * b_pitch * 2), aaddr += 32u) {
+      uint32_t a[4];
+      asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                   : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3]) : "r"(aaddr));
+      if (NT == 1) {
+        uint32_t b0, b1;
+        asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];" : "=r"(b0), "=r"(b1) : "r"(baddr));
+        mma16816<T>(acc[0], a, b0, b1);
+      } else {
+#pragma unroll
+        for (int h = 0; h < NT / 2; h++) {
+          uint32_t bf[4];
+          asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                       : "=r"(bf[0]), "=r"(bf[1]), "=r"(bf[2]), "=r"(bf[3]) : "r"(baddr + (uint32_t)(h * 32)));
+          mma16816<T>(acc[2 * h], a, bf[0], bf[1]);
+          mma16816<T>(acc[2 * h + 1], a, bf[2], bf[3]);
+        }
+      }
+    }
+    // C rows are a multiple of 128 bytes apart for the usual n, so eight lanes storing the same columns of eight
+    // rows would share their banks: in store j the lanes of row g take n-tile (j + g) % NT instead (the register
+    // is picked with selects: indices must be static).
+#pragma unroll
+    for (int j = 0; j < NT; j++) {
+      int const x = (j + g) & (NT - 1);
+      float lo0 = acc[0][0], lo1 = acc[0][1], hi0 = acc[0][2], hi1 = acc[0][3];
+#pragma unroll
+      for (int y = 1; y < NT; y++)
+        if (x == y) { lo0 = acc[y][0]; lo1 = acc[y][1]; hi0 = acc[y][2]; hi1 = acc[y][3]; }
+      int const c = n0 + x * 8 + 2 * t;
+      if (v0) {
+        float2 *dst = reinterpret_cast<float2 *>(C + (size_t)r0 * n + c);
+        float2 v = make_float2(lo0, lo1);
+        if (add) { float2 o = *dst; v.x += o.x; v.y += o.y; }
+        *dst = v;
+      }
+      if (v1) {
+        float2 *dst = reinterpret_cast<float2 *>(C + (size_t)r1 * n + c);
+        float2 v = make_float2(hi0, hi1);
+        if (add) { float2 o = *dst; v.x += o.x; v.y += o.y; }
+        *dst = v;
+      }
     }
   }
 }
@@ -125,28 +213,48 @@ __global__ void __launch_bounds__(1024) float_interp_kernel(const __grid_constan
   int64_t const set = b / ((int64_t)gx * gy * gz);
   auto tile = [&](int byte_offset) { return smem_b + byte_offset; };
   auto ftile = [&](int byte_offset) { return reinterpret_cast<float *>(smem_b + byte_offset); };
+  // The operator table and the bindings are read with computed indices all the time; out of the kernel parameters
+  // such a read costs tens of cycles each (about 1200 cycles of address set-up per operator were measured), out of
+  // shared memory a few.  The host puts the copy behind the tiles (prog.smem_bytes = its offset).
+  mgd_op const *ops = reinterpret_cast<mgd_op const *>(smem_b + prog.smem_bytes);
+  mgd_bindings const &bnd = *reinterpret_cast<mgd_bindings const *>(smem_b + prog.smem_bytes + prog.num_ops * (int)sizeof(mgd_op));
+  {
+    int32_t *dst = reinterpret_cast<int32_t *>(smem_b + prog.smem_bytes);
+    int const op_words = prog.num_ops * (int)(sizeof(mgd_op) / 4), bind_words = (int)(sizeof(mgd_bindings) / 4);
+    for (int i = tid; i < op_words; i += nt) dst[i] = reinterpret_cast<int32_t const *>(prog.ops)[i];
+    for (int i = tid; i < bind_words; i += nt) dst[op_words + i] = reinterpret_cast<int32_t const *>(&bind)[i];
+    __syncthreads();
+  }
 
+#ifdef MG_FI_TIMING // cycles per operator (with its barrier), printed by one thread of block 0
+  long long op_cycles[MGD_MAX_OPS] = {};
+  long long ld_setup = 0, ld_copy = 0;
+#endif
   for (int it = 0; it < prog.forloop_range; it++) {
     for (int oi = 0; oi < prog.num_ops; oi++) {
-      mgd_op const &op = prog.ops[oi];
+      mgd_op const &op = ops[oi];
       int32_t const *a = op.a;
+#ifdef MG_FI_TIMING
+      long long const op_t0 = clock64();
+#endif
       switch (op.type) {
         case 2001: {
           if ((a[16] & kInInvariant) && it > 0) break; // uniform over the block
           int row = bx * a[0] + by * a[1] + bz * a[2] + it * a[6];
           int col = bx * a[3] + by * a[4] + bz * a[5] + it * a[7];
           int64_t lead = (int64_t)bx * a[8] + (int64_t)by * a[9] + (int64_t)bz * a[10] + (int64_t)it * a[11];
-          T const *src = static_cast<T const *>(bind.in[a[18]]) + set * bind.in_set_stride[a[18]] + lead;
+          T const *src = static_cast<T const *>(bnd.in[a[18]]) + set * bnd.in_set_stride[a[18]] + lead;
           bool const keep16 = (a[16] & kIn16) != 0;
           T *dst16 = reinterpret_cast<T *>(tile(a[17]));
           float *dst32 = ftile(a[17]);
           int rows = a[14], cols = a[15], n = rows * cols;
+          int const pitch = cols + ((a[16] >> kInPadShift) & 0xff); // padded only for 16-bit tiles
           if ((a[16] & 0xff) == MG_DMEM_COLUMN_MAJOR) {
             int ld = a[12]; // rows of the whole matrix: consecutive rows are adjacent in memory
             for (int i = tid; i < n; i += nt) {
               int c = i / rows, r = i % rows;
               T v = src[(size_t)(col + c) * ld + row + r];
-              if (keep16) dst16[r * cols + c] = v;
+              if (keep16) dst16[r * pitch + c] = v;
               else dst32[r * cols + c] = to_float<T>(v);
             }
           } else {
@@ -154,15 +262,32 @@ __global__ void __launch_bounds__(1024) float_interp_kernel(const __grid_constan
             T const *first = src + (size_t)row * ld + col;
             if (keep16 && (cols & 7) == 0 && (ld & 7) == 0 && (reinterpret_cast<uintptr_t>(first) & 15) == 0) {
               int const cv = cols >> 3; // 16-byte pieces per tile row
+#ifdef MG_FI_TIMING
+              ld_setup += clock64() - op_t0;
+              long long const ld_t1 = clock64();
+#endif
               for (int i = tid; i < rows * cv; i += nt) {
                 int r = i / cv, c = i % cv;
-                reinterpret_cast<uint4 *>(dst16)[i] = __ldg(reinterpret_cast<uint4 const *>(first + (size_t)r * ld) + c);
+                *reinterpret_cast<uint4 *>(dst16 + r * pitch + c * 8) = __ldg(reinterpret_cast<uint4 const *>(first + (size_t)r * ld) + c);
+              }
+#ifdef MG_FI_TIMING
+              ld_copy += clock64() - ld_t1;
+#endif
+              // the tile of the next iteration: one prefetch per 128-byte line, so that its loads find it in L1
+              // instead of paying an L2 round trip between two barriers
+              if (it + 1 < prog.forloop_range && !(a[16] & kInInvariant)) {
+                T const *next = first + (size_t)a[6] * ld + a[7] + a[11];
+                int const lines = (cols * (int)sizeof(T) + 127) >> 7;
+                for (int i = tid; i < rows * lines; i += nt) {
+                  int r = i / lines, l = i % lines;
+                  asm volatile("prefetch.global.L1 [%0];" ::"l"(next + (size_t)r * ld + l * (128 / (int)sizeof(T))));
+                }
               }
             } else {
               for (int i = tid; i < n; i += nt) {
                 int r = i / cols, c = i % cols;
                 T v = first[(size_t)r * ld + c];
-                if (keep16) dst16[i] = v;
+                if (keep16) dst16[r * pitch + c] = v;
                 else dst32[i] = to_float<T>(v);
               }
             }
@@ -174,10 +299,17 @@ __global__ void __launch_bounds__(1024) float_interp_kernel(const __grid_constan
           unsigned char const *A = tile(a[3]), *B = tile(a[4]);
           float *C = ftile(a[5]);
           bool const add = a[8] != 0 && it > 0;
-          if (a[6] && a[7]) matmul_tiles<T, true, true>(A, B, C, m, n, k, add, tid, nt);
-          else if (a[6]) matmul_tiles<T, true, false>(A, B, C, m, n, k, add, tid, nt);
-          else if (a[7]) matmul_tiles<T, false, true>(A, B, C, m, n, k, add, tid, nt);
-          else matmul_tiles<T, false, false>(A, B, C, m, n, k, add, tid, nt);
+          if (a[10] > 0) { // host-planned staging room: B in 16 bits, n % 8 == 0, k % 16 == 0 -> tensor cores
+            unsigned char *staged = smem_b + a[10];
+            stage_a<T>(A, a[6] != 0, staged, m, k, tid, nt);
+            __syncthreads();
+            int const bp = a[9] > 0 ? a[9] : n;
+            // the wide warp patch when it still gives every warp one
+            if ((n & 31) == 0 && ((m + 15) >> 4) * (n >> 5) >= (nt >> 5)) matmul_mma<T, 4>(staged, B, C, m, n, k, bp, add, tid, nt);
+            else matmul_mma<T, 1>(staged, B, C, m, n, k, bp, add, tid, nt);
+          } else {
+            matmul_tiles<T>(A, B, C, m, n, k, a[6] != 0, a[7] != 0, add, tid, nt);
+          }
           break;
         }
         case MG_TB_EXP_OP: {
@@ -251,7 +383,7 @@ __global__ void __launch_bounds__(1024) float_interp_kernel(const __grid_constan
             int row = bx * a[0] + by * a[1] + bz * a[2];
             int col = bx * a[3] + by * a[4] + bz * a[5];
             int64_t lead = (int64_t)bx * a[6] + (int64_t)by * a[7] + (int64_t)bz * a[8];
-            T *dst = static_cast<T *>(bind.out[a[15]]) + set * bind.out_set_stride[a[15]] + lead;
+            T *dst = static_cast<T *>(bnd.out[a[15]]) + set * bnd.out_set_stride[a[15]] + lead;
             int cols = a[12], ld = a[10];
             for (int i = tid; i < n; i += nt) dst[(size_t)(row + i / cols) * ld + col + i % cols] = from_float<T>(acc[i]);
           }
@@ -259,9 +391,20 @@ __global__ void __launch_bounds__(1024) float_interp_kernel(const __grid_constan
         }
         default: break;
       }
-      __syncthreads();
+      // consecutive input loaders write different tiles and read none: their memory latencies may overlap
+      if (!(op.type == 2001 && oi + 1 < prog.num_ops && ops[oi + 1].type == 2001)) __syncthreads();
+#ifdef MG_FI_TIMING
+      op_cycles[oi] += clock64() - op_t0;
+#endif
     }
   }
+#ifdef MG_FI_TIMING
+  if (blockIdx.x == 0 && tid == 0)
+  {
+    for (int oi = 0; oi < prog.num_ops; oi++) printf("op %d type %d: %lld cycles\n", oi, ops[oi].type, op_cycles[oi]);
+    printf("loaders (vector path): setup %lld copy %lld\n", ld_setup, ld_copy);
+  }
+#endif
 }
 
 // ---- host: shared-memory replanning ------------------------------------------------------------------------------
@@ -273,7 +416,10 @@ struct TileUse {
   bool computed;  // written by any other operator
   bool dropped;   // folded into an output accumulator
   int offset;     // byte offset in this kernel's plan
+  int rows, cols; // shape the loader writes (loaded tiles)
+  int pad;        // extra elements per row: a 16-bit matmul B operand whose dense pitch conflicts in ldmatrix
   bool is16() const { return loaded && !computed; }
+  size_t bytes() const { return pad ? (size_t)rows * (cols + pad) * 2 : (size_t)elems * (is16() ? 2 : 4); }
 };
 
 struct Replanned {
@@ -293,7 +439,7 @@ struct TileTable {
     int i = find(planned);
     if (i < 0) {
       i = n++;
-      t[i] = TileUse{planned, elems, false, false, false, 0};
+      t[i] = TileUse{planned, elems, false, false, false, 0, 0, 0, 0};
     } else if (elems > t[i].elems) {
       t[i].elems = elems;
     }
@@ -340,7 +486,10 @@ void replan(mgd_program const &in, Replanned *out) {
     mgd_op const &op = in.ops[i];
     int32_t const *a = op.a;
     if (op.type == 2001) {
-      tt.t[tt.touch(a[17], a[14] * a[15])].loaded = true;
+      TileUse &t = tt.t[tt.touch(a[17], a[14] * a[15])];
+      t.loaded = true;
+      t.rows = a[14];
+      t.cols = a[15];
     } else if (op.type == MG_TB_MATMUL_OP) {
       tt.touch(a[3], a[0] * a[2]);
       tt.touch(a[4], a[2] * a[1]);
@@ -380,13 +529,56 @@ void replan(mgd_program const &in, Replanned *out) {
       tt.t[tt.find(src)].dropped = true;
     }
   }
-  // pass 3: offsets, 16-byte aligned
-  size_t at = 0;
+  // pass 3: offsets, 16-byte aligned.  A 16-bit tile that is read only as the B operand of tensor-core matmuls of
+  // its own shape gets 8 elements of row padding when its dense pitch is a multiple of 128 bytes (the eight rows
+  // of an ldmatrix would share their banks); without it if the padded plan does not fit.
   for (int i = 0; i < tt.n; i++) {
-    if (tt.t[i].dropped) continue;
-    tt.t[i].offset = (int)at;
-    at += ((size_t)tt.t[i].elems * (tt.t[i].is16() ? 2 : 4) + 15) & ~(size_t)15;
+    TileUse &t = tt.t[i];
+    if (!t.is16() || t.rows <= 0 || (t.cols * 2) % 128 != 0) continue;
+    bool only_b = true, used = false;
+    for (int o = 0; o < in.num_ops; o++) {
+      mgd_op const &op = in.ops[o];
+      int const reads = reads_of(op, t.planned);
+      if (reads == 0) continue;
+      if (op.type == MG_TB_MATMUL_OP && op.a[4] == t.planned && op.a[3] != t.planned && op.a[2] == t.rows &&
+          op.a[1] == t.cols && (op.a[2] & 15) == 0)
+        used = true;
+      else
+        only_b = false;
+    }
+    t.pad = (used && only_b) ? 8 : 0;
   }
+  // staging room for the A operand of the tensor-core matmuls (16-bit rows of k + 8 elements, m rounded up to 16),
+  // one region shared by all of them
+  size_t staging = 0;
+  for (int i = 0; i < in.num_ops; i++) {
+    int32_t const *a = in.ops[i].a;
+    if (in.ops[i].type != MG_TB_MATMUL_OP || !tt.t[tt.find(a[4])].is16() || (a[1] & 7) != 0 || (a[2] & 15) != 0) continue;
+    size_t const need = (size_t)((a[0] + 15) / 16 * 16) * (a[2] + 8) * 2;
+    if (need > staging) staging = need;
+  }
+  size_t const table = (size_t)in.num_ops * sizeof(mgd_op) + sizeof(mgd_bindings) + 32;
+  size_t at = 0;
+  int staging_offset = 0;
+  for (int pass = 0; pass < 2; pass++) {
+    at = 0;
+    for (int i = 0; i < tt.n; i++) {
+      if (tt.t[i].dropped) continue;
+      tt.t[i].offset = (int)at;
+      at += (tt.t[i].bytes() + 15) & ~(size_t)15;
+    }
+    if (staging > 0 && at + staging + table <= (size_t)kSmemLimit) {
+      staging_offset = (int)at;
+      at += staging;
+      break;
+    }
+    // no room for the staging area: those matmuls run on the CUDA cores, which read B densely
+    for (int i = 0; i < tt.n; i++) tt.t[i].pad = 0;
+  }
+  // behind the tiles: the kernel's copy of the operator table and the bindings
+  at = (at + 15) & ~(size_t)15;
+  p.smem_bytes = (int32_t)at;
+  at += (size_t)in.num_ops * sizeof(mgd_op) + sizeof(mgd_bindings);
   out->smem_bytes = at + 16;
   // pass 4: rewrite operands
   auto off = [&](int planned) { return tt.t[tt.find(planned)].offset; };
@@ -397,13 +589,15 @@ void replan(mgd_program const &in, Replanned *out) {
     int type = in.ops[i].type;
     if (type == 2001) {
       w[17] = off(a[17]);
-      w[16] = (a[16] & 0xff) | (is16(a[17]) ? kIn16 : 0);
+      w[16] = (a[16] & 0xff) | (is16(a[17]) ? kIn16 : 0) | (tt.t[tt.find(a[17])].pad << kInPadShift);
       // no for-loop stride and nothing overwrites the tile: the first iteration's copy stays valid
       if (is16(a[17]) && a[6] == 0 && a[7] == 0 && a[11] == 0) w[16] |= kInInvariant;
     } else if (type == MG_TB_MATMUL_OP) {
       w[3] = off(a[3]); w[4] = off(a[4]);
       w[6] = is16(a[3]); w[7] = is16(a[4]);
       w[8] = 0;
+      w[9] = tt.t[tt.find(a[4])].pad ? a[1] + tt.t[tt.find(a[4])].pad : 0; // row pitch of B when it is padded
+      w[10] = (is16(a[4]) && (a[1] & 7) == 0 && (a[2] & 15) == 0) ? staging_offset : 0;
       w[5] = tt.t[tt.find(a[5])].dropped ? -1 : off(a[5]);
     } else if (type == MG_TB_EXP_OP) {
       w[0] = off(a[0]);
@@ -456,21 +650,29 @@ extern "C" int mgd_launch_float_interp(const mgd_program *prog, const mgd_bindin
   int64_t blocks = (int64_t)prog->grid[0] * prog->grid[1] * prog->grid[2] * bind->num_sets;
   if (blocks > 0x7fffffffLL) return set_error(MG_ERR_UNSUPPORTED, "too many blocks for one launch");
   // Blocks run one operator at a time with a barrier after each: big tiles get more warps to hide the latency of
-  // the dependent instruction chains (the largest operator decides; a matmul thread owns up to 16 outputs).
+  // the dependent instruction chains (the largest operator decides).  More warps also repeat every operator's
+  // set-up code more often (32 warps share four schedulers), so loaders and tensor-core matmuls, which need few
+  // warps, ask for less: the matmul chain of 16 x 64 x 1024 tiles ran 129 us on 512 threads, 144 on 1024, 148 on 256.
   int64_t largest = 0;
   for (int i = 0; i < prog->num_ops; i++) {
     int32_t const *a = prog->ops[i].a;
     int64_t work = 0;
     switch (prog->ops[i].type) {
-      case 2001: work = (int64_t)a[14] * a[15] / 8; break;
-      case 2002: work = (int64_t)a[11] * a[12]; break;
-      case MG_TB_MATMUL_OP: work = (int64_t)a[0] * a[1] / 4; break;
+      case 2001: work = (int64_t)a[14] * a[15] / 16; break;
+      case 2002: work = (int64_t)a[11] * a[12] / (r.prog.ops[i].a[17] ? 4 : 1); break; // fused: stores once, at the end
+      case MG_TB_MATMUL_OP:
+        work = r.prog.ops[i].a[10] > 0 ? (int64_t)((a[0] + 15) / 16) * a[1] * 4 : (int64_t)a[0] * a[1] / 4;
+        break;
       case MG_TB_EXP_OP: work = a[1]; break;
       default: work = a[0]; break;
     }
     if (work > largest) largest = work;
   }
-  unsigned const threads = largest >= 8192 ? 1024u : (largest >= 2048 ? 512u : 256u);
+  unsigned threads = largest >= 8192 ? 1024u : (largest >= 2048 ? 512u : 256u);
+  if (char const *forced = std::getenv("MUGRAPH_INTERP_THREADS")) { // 256, 512 or 1024: for measurements
+    int const v = std::atoi(forced);
+    if (v == 256 || v == 512 || v == 1024) threads = (unsigned)v;
+  }
   static bool configured_h = false, configured_b = false;
   if (dt == MG_DT_FLOAT16) {
     if (smem > 48 * 1024 && !configured_h) {
