@@ -199,6 +199,58 @@ def test_interpreter_matmul_shapes_and_full_range(runtime, mkn):
         runtime.set_specialisation(2)
 
 
+@pytest.mark.parametrize("dtype", [mg.float16, mg.bfloat16], ids=["fp16", "bf16"])
+@pytest.mark.parametrize("mkn", [(1, 16, 16), (4, 16, 8), (5, 32, 48), (16, 64, 1024), (33, 128, 64), (20, 48, 96),
+                                 (7, 24, 16), (8, 16, 20), (3, 5, 7), (4, 64, 1600)],
+                         ids=lambda s: "x".join(map(str, s)))
+def test_float_interpreter_matmul_shapes(runtime, mkn, dtype):
+    """The float interpreter's matmul: tensor cores (mma.sync, A staged as 16-bit rows, B rows padded when their
+    dense pitch is a multiple of 128 bytes) when n % 8 == 0 and k % 16 == 0, for row counts that do not fill a
+    16-row tile and for one or four n-tiles per warp; the CUDA cores otherwise, and when the staging room does not
+    fit beside the tiles (the 64 x 1600 B tile); for-loop accumulation included.  A second plan feeds a computed
+    (fp32) tile into the A side."""
+    m, k, n = mkn
+    F = 2
+    runtime.set_max_smem(BIG)
+    runtime.set_specialisation(0)
+    try:
+        rng = np.random.default_rng(m * 1000 + k * 10 + n)
+        rnd = lambda a: from_bits(to_bits(a, dtype), dtype)
+        specs = [mo.DTensorSpec((m, F * k), dtype), mo.DTensorSpec((F * k, n), dtype)]
+        plan = mo.ExecutionPlan(ops=[(mo.TB_MATMUL_OP, [(0, 0), (1, 0)])], input_map=[(-1, -1, -1), (-1, -1, -1)],
+                                forloop_dim=[1, 0], input_smem_layouts=[mo.SmemRowMajor] * 2, output_map=(-1, -1, -1),
+                                forloop_range=F, grid_dim=(1, 1, 1))
+        x = [rnd(rng.standard_normal(s.dims) * (1.0 if i == 0 else k ** -0.5)) for i, s in enumerate(specs)]
+        with mg.PyGraph(runtime) as g:
+            ins = [g.new_input(s.dims, s.dtype, s.layout) for s in specs]
+            for t, a in zip(ins, x):
+                t.upload_data(to_bits(a, dtype))
+            outs = g.customized(ins, to_package_plan(plan))
+            g.run()
+            got = from_bits(outs[0].download_data(), dtype).reshape(outs[0].shape)
+        assert_close(got, x[0].astype(np.float64) @ x[1].astype(np.float64), dtype, "A B")
+        if m * n > 4096:  # the chained plan of the big shapes does not fit as fp32 tiles
+            return
+        # (A B) C with the computed product as the A operand of the second matmul; C is [n, 16]
+        specs2 = specs + [mo.DTensorSpec((n, 16), dtype)]
+        plan2 = mo.ExecutionPlan(ops=[(mo.TB_MATMUL_OP, [(0, 0), (1, 0)]), (mo.TB_MATMUL_OP, [(3, 0), (2, 0)])],
+                                 input_map=[(-1, -1, -1)] * 3, forloop_dim=[1, 0, -1],
+                                 input_smem_layouts=[mo.SmemRowMajor] * 3, output_map=(-1, -1, -1), forloop_range=F,
+                                 grid_dim=(1, 1, 1))
+        x2 = x + [rnd(rng.standard_normal((n, 16)) * n ** -0.5)]
+        with mg.PyGraph(runtime) as g:
+            ins = [g.new_input(s.dims, s.dtype, s.layout) for s in specs2]
+            for t, a in zip(ins, x2):
+                t.upload_data(to_bits(a, dtype))
+            outs = g.customized(ins, to_package_plan(plan2))
+            g.run()
+            got = from_bits(outs[0].download_data(), dtype).reshape(outs[0].shape)
+        want = mo.run_float(mo.build_customized(specs2, plan2, max_smem=BIG), x2)[0]
+        assert_close(got, want, dtype, "(A B) C")
+    finally:
+        runtime.set_specialisation(2)
+
+
 def interpreter_corner_plans():
     """Plans that exercise the interpreters' own memory planning: operands stored with padded rows or not, tiles
     loaded once or every iteration, in-place exp on an input tile, a matmul adding straight into the accumulator."""
