@@ -33,6 +33,9 @@ TB_CONCAT_0_OP, TB_CONCAT_1_OP, TB_CONCAT_2_OP = 2200, 2201, 2202
 FP_P, FP_Q, FP_PQ = 227, 113, 25651
 
 POLICY_LATENCY, POLICY_THROUGHPUT = 0, 1
+OPT_ATTN_STAGES, OPT_ATTN_TILE_GROUPS, OPT_ATTN_ENGINE, OPT_ROWS_ENGINE, OPT_INTERP_THREADS, OPT_WAIT_LIMIT = range(6)
+ENGINE_AUTO, ENGINE_MMA_SYNC, ENGINE_TCGEN05 = 0, 1, 2
+ROWS_AUTO, ROWS_ONE_TILE, ROWS_TWO_TILES = 0, 1, 2
 KERNEL_INTERPRETER, KERNEL_ATTN_SPLIT, KERNEL_ATTN_MERGE, KERNEL_ATTN_ROWS = 0, 1, 2, 3
 
 
@@ -117,6 +120,20 @@ class Runtime:
     def set_launch_policy(self, policy):
         """POLICY_LATENCY (one call at a time) or POLICY_THROUGHPUT (several independent calls in flight)."""
         check(self.lib.mg_runtime_set_launch_policy(self.handle, int(policy)))
+
+    def set_option(self, key, value):
+        """Tuning switch OPT_* (0 = automatic); read when a launch is configured."""
+        check(self.lib.mg_runtime_set_option(self.handle, int(key), int(value)))
+
+    def get_option(self, key):
+        v = ctypes.c_int32()
+        check(self.lib.mg_runtime_get_option(self.handle, int(key), ctypes.byref(v)))
+        return v.value
+
+    def selftest_bounded_wait(self, poll_limit=4096, stream=None):
+        """Enqueue the failure-path self-test: a wait nobody satisfies gives up after `poll_limit` polls and sets
+        the device status word; the next synchronising call raises MG_ERR_DEVICE_TIMEOUT once."""
+        check(self.lib.mg_selftest_bounded_wait(self.handle, int(poll_limit), ctypes.c_void_p(stream or 0)))
 
     def tables(self):
         """Host copies of the arena's exp / div_p / div_q lookup tables."""
@@ -420,6 +437,20 @@ class CapturedSequence:
         if self.handle:
             check(self.lib.mg_captured_destroy(self.handle))
             self.handle = None
+
+
+def fill_fingerprint_seeded_raw(runtime, device_ptr, num_elements, seed, modulus=FP_P):
+    """Seeded uniform fill of caller-owned device memory (uint16 fingerprints), same generator as
+    PyTensor.fill_fingerprint_seeded."""
+    pod = mg_tensor()
+    pod.data_type, pod.num_dims, pod.dim[0] = float16, 1, int(num_elements)
+    pod.fp_ptr = int(device_ptr)
+    check(runtime.lib.mg_tensor_fill_fingerprint_seeded(runtime.handle, ctypes.byref(pod), int(seed), int(modulus)))
+
+
+def stream_inputs_written(stream=None):
+    """Tell the library that work of the caller's own on `stream` wrote input tensors of its graphs."""
+    check(_abi.load().mg_stream_inputs_written(ctypes.c_void_p(stream or 0)))
 
 
 def new_graph():

@@ -49,6 +49,10 @@ SIGNATURES = {
     "mg_runtime_set_max_smem": (ctypes.c_int, [_P, ctypes.c_size_t]),
     "mg_runtime_set_specialisation": (ctypes.c_int, [_P, ctypes.c_int]),
     "mg_runtime_set_launch_policy": (ctypes.c_int, [_P, ctypes.c_int]),
+    "mg_runtime_set_option": (ctypes.c_int, [_P, _I, _I]),
+    "mg_runtime_get_option": (ctypes.c_int, [_P, _I, ctypes.POINTER(_I)]),
+    "mg_stream_inputs_written": (ctypes.c_int, [_P]),
+    "mg_selftest_bounded_wait": (ctypes.c_int, [_P, _I, _P]),
     "mg_graph_create": (ctypes.c_int, [_P, ctypes.POINTER(_P)]),
     "mg_graph_destroy": (ctypes.c_int, [_P]),
     "mg_graph_new_input": (ctypes.c_int, [_P, ctypes.POINTER(_I), _I, _I, _I, _T]),

@@ -120,6 +120,7 @@ int mg_runtime_create(int device, size_t arena_bytes, mg_runtime **rt) {
 int mg_runtime_destroy(mg_runtime *rt) {
   if (!rt || !rt->dmm) return fail(MG_ERR_INVALID_ARGUMENT, "no runtime");
   DeviceMemoryManager::destroy();
+  mg::forget_streams();
   rt->dmm = nullptr;
   return MG_OK;
 }
@@ -157,6 +158,35 @@ int mg_runtime_set_launch_policy(mg_runtime *rt, int policy) {
   if (policy != MG_POLICY_LATENCY && policy != MG_POLICY_THROUGHPUT) return fail(MG_ERR_INVALID_ARGUMENT, "unknown launch policy");
   rt->dmm->launch_policy = policy;
   return MG_OK;
+}
+
+static_assert(MG_OPT_ATTN_STAGES == MGD_OPT_ATTN_STAGES && MG_OPT_ATTN_TILE_GROUPS == MGD_OPT_ATTN_TILE_GROUPS &&
+                  MG_OPT_ATTN_ENGINE == MGD_OPT_ATTN_ENGINE && MG_OPT_ROWS_ENGINE == MGD_OPT_ROWS_ENGINE &&
+                  MG_OPT_INTERP_THREADS == MGD_OPT_INTERP_THREADS && MG_OPT_WAIT_LIMIT == MGD_OPT_WAIT_LIMIT,
+              "the option keys of the two headers are the same numbers");
+
+int mg_runtime_set_option(mg_runtime *rt, int32_t key, int32_t value) {
+  if (!rt || !rt->dmm) return fail(MG_ERR_INVALID_ARGUMENT, "no runtime");
+  int st = mgd_set_option(key, value);
+  return st == MG_OK ? MG_OK : fail(st, mgd_last_error());
+}
+
+int mg_runtime_get_option(mg_runtime *rt, int32_t key, int32_t *value) {
+  if (!rt || !rt->dmm) return fail(MG_ERR_INVALID_ARGUMENT, "no runtime");
+  int st = mgd_get_option(key, value);
+  return st == MG_OK ? MG_OK : fail(st, mgd_last_error());
+}
+
+int mg_stream_inputs_written(void *stream) {
+  mg::stream_wrote_anything(stream);
+  return MG_OK;
+}
+
+int mg_selftest_bounded_wait(mg_runtime *rt, int32_t poll_limit, void *stream) {
+  if (int dry_st = refuse_dry(rt)) return dry_st;
+  if (!rt || !rt->dmm) return fail(MG_ERR_INVALID_ARGUMENT, "no runtime");
+  int st = mgd_selftest_bounded_wait(poll_limit, stream);
+  return st == MG_OK ? MG_OK : fail(st, mgd_last_error());
 }
 
 int mg_graph_create(mg_runtime *rt, mg_graph **g) {
@@ -476,15 +506,14 @@ int mg_verify_candidates(mg_runtime *rt, const mg_tensor *reference, mg_graph *c
   if (int dry_st = refuse_dry(rt)) return dry_st;
   if (!rt || !rt->dmm || !reference || !candidates || !outputs || !same || n < 0) return fail(MG_ERR_INVALID_ARGUMENT, "null argument");
   if (n == 0) return MG_OK;
-  static int32_t *flags = nullptr; // device scratch, grows, lives as long as the process
-  static int32_t flags_capacity = 0;
-  if (n > flags_capacity) {
-    if (flags) cudaFree(flags);
-    flags = nullptr;
-    flags_capacity = 0;
-    MG_CUDA_TRY(cudaMalloc(&flags, sizeof(int32_t) * (size_t)n));
-    flags_capacity = n;
-  }
+  // n result flags from the arena: taken here, given back (LIFO) before returning; nothing else allocates in between
+  struct ArenaScratch {
+    DeviceMemoryManager *dmm;
+    void *p;
+    ~ArenaScratch() { if (p) dmm->free_raw(p); }
+  } scratch{rt->dmm, rt->dmm->allocate_raw(sizeof(int32_t) * (size_t)n)};
+  if (!scratch.p) return fail(MG_ERR_OUT_OF_MEMORY, "device arena exhausted (verification flags)");
+  int32_t *flags = static_cast<int32_t *>(scratch.p);
   MG_CUDA_TRY(cudaMemsetAsync(flags, 0, sizeof(int32_t) * (size_t)n, (cudaStream_t)stream));
   int64_t ref_elems = 1;
   for (int d = 0; d < reference->num_dims; d++) ref_elems *= reference->dim[d];
@@ -519,24 +548,28 @@ static size_t pod_data_bytes(const mg_tensor *t) {
 
 int mg_tensor_fill_fingerprint_reference(mg_runtime *rt, const mg_tensor *t) {
   if (int dry_st = refuse_dry(rt)) return dry_st;
+  mg::stream_wrote_anything(nullptr);
   if (!rt || !rt->dmm || !t || !t->fp_ptr) return fail(MG_ERR_INVALID_ARGUMENT, "null argument");
   int st = mgd_fill_fingerprint_reference(t->fp_ptr, pod_elements(t), nullptr);
   return st == MG_OK ? synchronize_and_check() : fail(st, mgd_last_error());
 }
 int mg_tensor_fill_fingerprint_seeded(mg_runtime *rt, const mg_tensor *t, uint64_t seed, uint32_t modulus) {
   if (int dry_st = refuse_dry(rt)) return dry_st;
+  mg::stream_wrote_anything(nullptr);
   if (!rt || !rt->dmm || !t || !t->fp_ptr || modulus == 0 || modulus > 65536) return fail(MG_ERR_INVALID_ARGUMENT, "bad fill request");
   int st = mgd_fill_fingerprint_seeded(t->fp_ptr, pod_elements(t), seed, modulus, nullptr);
   return st == MG_OK ? synchronize_and_check() : fail(st, mgd_last_error());
 }
 int mg_tensor_fill_data_seeded(mg_runtime *rt, const mg_tensor *t, uint64_t seed, float sigma) {
   if (int dry_st = refuse_dry(rt)) return dry_st;
+  mg::stream_wrote_anything(nullptr);
   if (!rt || !rt->dmm || !t || !t->data_ptr) return fail(MG_ERR_INVALID_ARGUMENT, "null argument");
   int st = mgd_fill_data_seeded(t->data_ptr, pod_elements(t), seed, sigma, t->data_type, nullptr);
   return st == MG_OK ? synchronize_and_check() : fail(st, mgd_last_error());
 }
 int mg_tensor_upload_fingerprint(mg_runtime *rt, const mg_tensor *t, const uint16_t *host) {
   if (int dry_st = refuse_dry(rt)) return dry_st;
+  mg::stream_wrote_anything(nullptr);
   if (!rt || !t || !host || !t->fp_ptr) return fail(MG_ERR_INVALID_ARGUMENT, "null argument");
   MG_CUDA_TRY(cudaMemcpy(t->fp_ptr, host, (size_t)pod_elements(t) * 2, cudaMemcpyHostToDevice));
   return MG_OK;
@@ -549,6 +582,7 @@ int mg_tensor_download_fingerprint(mg_runtime *rt, const mg_tensor *t, uint16_t 
 }
 int mg_tensor_upload_data(mg_runtime *rt, const mg_tensor *t, const void *host) {
   if (int dry_st = refuse_dry(rt)) return dry_st;
+  mg::stream_wrote_anything(nullptr);
   if (!rt || !t || !host || !t->data_ptr) return fail(MG_ERR_INVALID_ARGUMENT, "null argument");
   MG_CUDA_TRY(cudaMemcpy(t->data_ptr, host, pod_data_bytes(t), cudaMemcpyHostToDevice));
   return MG_OK;
@@ -561,6 +595,7 @@ int mg_tensor_download_data(mg_runtime *rt, const mg_tensor *t, void *host) {
 }
 int mg_tensor_upload_data_async(mg_runtime *rt, const mg_tensor *t, const void *host, void *stream) {
   if (int dry_st = refuse_dry(rt)) return dry_st;
+  mg::stream_wrote_anything(stream);
   if (!rt || !t || !host || !t->data_ptr) return fail(MG_ERR_INVALID_ARGUMENT, "null argument");
   MG_CUDA_TRY(cudaMemcpyAsync(t->data_ptr, host, pod_data_bytes(t), cudaMemcpyHostToDevice, (cudaStream_t)stream));
   return MG_OK;
@@ -585,6 +620,7 @@ int mg_graph_rebind_input(mg_graph *g, int32_t idx, void *data_ptr, uint16_t *fp
         if (fp_ptr) in.fp_ptr = fp_ptr;
       }
   (void)t;
+  mg::forget_streams(); // the new buffers may have been written by anything, on any stream
   static_cast<kernel::KNInputOp *>(op)->skip_fill = true;
   return MG_OK;
 }

@@ -10,12 +10,14 @@ enum KernelId {
   KERNEL_ATTN_ROWS = 3,    // same chain with query rows split over grid.y and the whole KV axis in the for-loop
 };
 // Recognise the split-KV attention operator (pattern of the reference's
-// cpp_examples/group_query_attn_inc_decode.cc:46-79); fills `out` on success.
-bool match_attn_split(mgd_program const &p, int leading_dims_of_inputs, mgd_attn_split *out);
-// Recognise the cross-split reduction + division (same file, :80-103).
-bool match_attn_merge(mgd_program const &p, mgd_attn_merge *out);
+// cpp_examples/group_query_attn_inc_decode.cc:46-79); fills `out` on success.  The second matmul and the row
+// reduction may come in either order; *o_output = which of the operator's two outputs (0 or 1) is O'.
+bool match_attn_split(mgd_program const &p, mgd_attn_split *out, int *o_output);
+// Recognise the cross-split reduction + division (same file, :80-103); *o_part_input = which input is O_part.
+bool match_attn_merge(mgd_program const &p, mgd_attn_merge *out, int *o_part_input);
 // Recognise the dense (prefill) form: pattern of cpp_examples/multi_head_attn_prefill.cc:43-98.
-bool match_attn_rows(mgd_program const &p, mgd_attn_rows *out);
-// Recognise O = A / R with A[heads, rows, d], R[heads, rows, 1] tiled like match_attn_rows' outputs (same example, :88-98).
-bool match_div_rows(mgd_program const &p, int *heads, int *rows, int *d);
+bool match_attn_rows(mgd_program const &p, mgd_attn_rows *out, int *o_output);
+// Recognise O = A / R with A[heads, rows, d], R[heads, rows, 1] tiled like match_attn_rows' outputs (same example,
+// :88-98); *numerator_input = which input is A.
+bool match_div_rows(mgd_program const &p, int *heads, int *rows, int *d, int *numerator_input);
 } // namespace mg

@@ -38,6 +38,10 @@ using namespace mirage::type;
 using mirage::threadblock::ExecutionPlan;
 using mirage::threadblock::STensor;
 
+namespace {
+void record_anything(void *stream); // defined with the stream bookkeeping below
+}
+
 // ---- DTensor ---------------------------------------------------------------------------------
 int DTensor::next_guid = 10000000;
 
@@ -300,6 +304,7 @@ bool KNInputOp::profile(ProfileResult &r) {
 int KNInputOp::launch_fingerprint(void *stream) {
   if (int dry_st = refuse_if_dry()) return dry_st;
   if (skip_fill) return MG_OK;
+  record_anything(stream);
   return mgd_fill_fingerprint_reference(output_tensors[0].fp_ptr, (int64_t)output_tensors[0].num_elements(), stream);
 }
 int KNInputOp::launch_float(void *) { return MG_OK; }
@@ -326,6 +331,7 @@ KNMatmulOp::KNMatmulOp(DTensor const &A, DTensor const &B) : KNOperator(KN_MATMU
 KNMatmulOp::~KNMatmulOp() { free_outputs(output_tensors); }
 int KNMatmulOp::launch_fingerprint(void *stream) {
   if (int dry_st = refuse_if_dry()) return dry_st;
+  record_anything(stream);
   DTensor const &A = input_tensors[0], &B = input_tensors[1], &C = output_tensors[0];
   int nd = A.num_dims, batches = 1;
   for (int i = 0; i < nd - 2; i++) batches *= A.dim[i];
@@ -334,6 +340,7 @@ int KNMatmulOp::launch_fingerprint(void *stream) {
 }
 int KNMatmulOp::launch_float(void *stream) {
   if (int dry_st = refuse_if_dry()) return dry_st;
+  record_anything(stream);
   DTensor const &A = input_tensors[0], &B = input_tensors[1], &C = output_tensors[0];
   int nd = A.num_dims, batches = 1;
   for (int i = 0; i < nd - 2; i++) batches *= A.dim[i];
@@ -349,11 +356,13 @@ KNElementUnaryOp::KNElementUnaryOp(DTensor const &A, KNOperatorType t) : KNOpera
 KNElementUnaryOp::~KNElementUnaryOp() { free_outputs(output_tensors); }
 int KNElementUnaryOp::launch_fingerprint(void *stream) {
   if (int dry_st = refuse_if_dry()) return dry_st;
+  record_anything(stream);
   return mgd_kn_exp_fingerprint(input_tensors[0].fp_ptr, output_tensors[0].fp_ptr,
                                 (int64_t)output_tensors[0].num_elements(), stream);
 }
 int KNElementUnaryOp::launch_float(void *stream) {
   if (int dry_st = refuse_if_dry()) return dry_st;
+  record_anything(stream);
   return mgd_kn_exp_float(input_tensors[0].data_ptr, output_tensors[0].data_ptr,
                           (int64_t)output_tensors[0].num_elements(), (int)input_tensors[0].data_type, stream);
 }
@@ -373,6 +382,7 @@ static void right_aligned_dims(DTensor const &t, int32_t out[4]) {
 }
 int KNElementBinaryOp::launch_fingerprint(void *stream) {
   if (int dry_st = refuse_if_dry()) return dry_st;
+  record_anything(stream);
   int32_t xd[4], yd[4], zd[4];
   right_aligned_dims(input_tensors[0], xd);
   right_aligned_dims(input_tensors[1], yd);
@@ -382,6 +392,7 @@ int KNElementBinaryOp::launch_fingerprint(void *stream) {
 }
 int KNElementBinaryOp::launch_float(void *stream) {
   if (int dry_st = refuse_if_dry()) return dry_st;
+  record_anything(stream);
   int32_t xd[4], yd[4], zd[4];
   right_aligned_dims(input_tensors[0], xd);
   right_aligned_dims(input_tensors[1], yd);
@@ -410,6 +421,7 @@ static void reduction_geometry(DTensor const &in, DTensor const &out, int dim, i
 }
 int KNReductionOp::launch_fingerprint(void *stream) {
   if (int dry_st = refuse_if_dry()) return dry_st;
+  record_anything(stream);
   int64_t is, os;
   int factor;
   reduction_geometry(input_tensors[0], output_tensors[0], reduction_dim_idx, is, os, factor);
@@ -418,6 +430,7 @@ int KNReductionOp::launch_fingerprint(void *stream) {
 }
 int KNReductionOp::launch_float(void *stream) {
   if (int dry_st = refuse_if_dry()) return dry_st;
+  record_anything(stream);
   int64_t is, os;
   int factor;
   reduction_geometry(input_tensors[0], output_tensors[0], reduction_dim_idx, is, os, factor);
@@ -430,23 +443,30 @@ bool KNReductionOp::profile(ProfileResult &r) { return profile_with_events(r, 16
 
 // ---- what the previous launch on a stream wrote -------------------------------------------------------
 // The split-KV attention kernel is launched with programmatic stream serialisation and may start loading its
-// inputs while the previous kernel of the stream is still running.  That is only allowed when that kernel
-// (if it is one of ours that releases its successor early) did not write those inputs; every launch through
-// this file records its outputs per stream.  Kernels that do not release their successor early record nothing:
-// the successor cannot start before they complete.
+// inputs while the previous kernel of the stream is still running.  That is only allowed when the library KNOWS
+// that kernel and knows that it did not write those inputs.  Every launch through this file therefore records,
+// per stream, what it wrote: a list of address ranges for the split-KV kernel, "anything" for every other kernel
+// of the library and for copies and fills that go through the C ABI.  A stream the library has not launched on
+// yet, and a stream on which the caller reported work of its own (mg_stream_inputs_written), count as
+// "anything": the early loads are then left out for the next launch.
 namespace {
 struct Range { char const *lo, *hi; };
 std::mutex g_track_mutex;
 std::unordered_map<void *, std::vector<Range>> g_last_outputs;
+constexpr size_t kMaxTrackedStreams = 4096; // the table is cleared beyond this: forgetting is the safe direction
 
 void record_outputs(void *stream, std::vector<Range> const &r) {
   std::lock_guard<std::mutex> lock(g_track_mutex);
+  if (g_last_outputs.size() > kMaxTrackedStreams) g_last_outputs.clear();
   g_last_outputs[stream] = r;
+}
+void record_anything(void *stream) {
+  record_outputs(stream, {Range{(char const *)nullptr, (char const *)UINTPTR_MAX}});
 }
 bool inputs_untouched(void *stream, std::vector<Range> const &inputs) {
   std::lock_guard<std::mutex> lock(g_track_mutex);
   auto it = g_last_outputs.find(stream);
-  if (it == g_last_outputs.end()) return true;
+  if (it == g_last_outputs.end()) return false; // unknown predecessor
   for (Range const &a : it->second)
     for (Range const &b : inputs)
       if (a.lo < b.hi && b.lo < a.hi) return false;
@@ -454,6 +474,18 @@ bool inputs_untouched(void *stream, std::vector<Range> const &inputs) {
 }
 Range range_of(void const *p, size_t bytes) { return Range{(char const *)p, (char const *)p + bytes}; }
 } // namespace
+
+} // namespace kernel
+} // namespace mirage
+namespace mg {
+void stream_wrote_anything(void *stream) { mirage::kernel::record_anything(stream); }
+void forget_streams() {
+  std::lock_guard<std::mutex> lock(mirage::kernel::g_track_mutex);
+  mirage::kernel::g_last_outputs.clear();
+}
+} // namespace mg
+namespace mirage {
+namespace kernel {
 
 // ---- customized operator -----------------------------------------------------------------------------
 KNCustomizedOp::KNCustomizedOp(Deferred, std::vector<DTensor> const &ins, ExecutionPlan const &p)
@@ -651,21 +683,25 @@ bool KNCustomizedOp::ensure_lowered() {
   }
   lowered_ = true;
   kernel_fp_ = kernel_float_ = mg::KERNEL_INTERPRETER;
+  o_output_ = o_input_ = 0;
   if (DeviceMemoryManager::get_instance()->specialise > 0) {
     mgd_attn_split sp;
     mgd_attn_merge mp;
-    if (mg::match_attn_split(program_, 1, &sp)) {
+    int h, r, d;
+    if (mg::match_attn_split(program_, &sp, &o_output_)) {
       sp.data_type = (int)input_tensors[0].data_type;
       sp.causal_window = causal_window;
       if (mgd_attn_split_supported(&sp, 1)) kernel_fp_ = mg::KERNEL_ATTN_SPLIT;
       if (mgd_attn_split_supported(&sp, 0)) kernel_float_ = mg::KERNEL_ATTN_SPLIT;
-    } else if (mgd_attn_rows rp; mg::match_attn_rows(program_, &rp)) {
+    } else if (mgd_attn_rows rp; mg::match_attn_rows(program_, &rp, &o_output_)) {
       rp.data_type = (int)input_tensors[0].data_type;
       if (causal_window == 0 && mgd_attn_rows_supported(&rp)) kernel_float_ = mg::KERNEL_ATTN_ROWS;
-    } else if (mg::match_attn_merge(program_, &mp)) {
+    } else if (mg::match_attn_merge(program_, &mp, &o_input_)) {
       mp.data_type = (int)input_tensors[0].data_type;
       if (mgd_attn_merge_supported(&mp, 1)) kernel_fp_ = mg::KERNEL_ATTN_MERGE;
       if (mgd_attn_merge_supported(&mp, 0)) kernel_float_ = mg::KERNEL_ATTN_MERGE;
+    } else {
+      mg::match_div_rows(program_, &h, &r, &d, &o_input_); // only consulted by can_fuse_with of the producer
     }
   }
   return true;
@@ -685,12 +721,21 @@ int KNCustomizedOp::launch_fingerprint_sets(int num_sets, void const *const *in,
                                             void *const *out, long long const *out_stride, void *stream) {
   if (int dry_st = refuse_if_dry()) return dry_st;
   if (!ensure_lowered()) return MG_ERR_INVALID_GRAPH;
-  if (kernel_fp_ == mg::KERNEL_ATTN_SPLIT)
-    return launch_split(true, num_sets, in, in_stride, out, out_stride, nullptr, stream);
-  record_outputs(stream, {});
+  if (kernel_fp_ == mg::KERNEL_ATTN_SPLIT) {
+    void *o[2] = {out[o_output_], out[1 - o_output_]};
+    long long os[2] = {out_stride[o_output_], out_stride[1 - o_output_]};
+    return launch_split(true, num_sets, in, in_stride, o, os, nullptr, stream);
+  }
+  record_anything(stream);
   if (kernel_fp_ == mg::KERNEL_ATTN_MERGE) {
     mgd_attn_merge mp;
-    mg::match_attn_merge(program_, &mp);
+    mg::match_attn_merge(program_, &mp, nullptr);
+    void const *ordered[2] = {in[o_input_], in[1 - o_input_]};
+    long long const ordered_stride[2] = {in_stride[o_input_], in_stride[1 - o_input_]};
+    in = ordered;
+    in_stride = ordered_stride;
+    // the merge kernel writes its one output and nothing else
+    record_outputs(stream, {range_of(out[0], ((size_t)(num_sets - 1) * (size_t)out_stride[0] + output_tensors[0].num_elements()) * 2)});
     mp.num_sets = num_sets;
     mp.o_part_set_stride = in_stride[0]; mp.r_part_set_stride = in_stride[1]; mp.out_set_stride = out_stride[0];
     return finish(mgd_launch_attn_merge_fingerprint(&mp, (uint16_t const *)in[0], (uint16_t const *)in[1],
@@ -720,25 +765,25 @@ int KNCustomizedOp::launch_float(void *stream) {
   int dt = input_tensors.empty() ? (int)DT_FLOAT16 : (int)input_tensors[0].data_type;
   if (kernel_float_ == mg::KERNEL_ATTN_SPLIT) {
     void const *in[3] = {input_tensors[0].data_ptr, input_tensors[1].data_ptr, input_tensors[2].data_ptr};
-    void *out[2] = {output_tensors[0].data_ptr, output_tensors[1].data_ptr};
+    void *out[2] = {output_tensors[o_output_].data_ptr, output_tensors[1 - o_output_].data_ptr};
     long long zs[3] = {0, 0, 0};
     return launch_split(false, 1, in, zs, out, zs, nullptr, stream);
   }
-  record_outputs(stream, {});
+  record_anything(stream);
   if (kernel_float_ == mg::KERNEL_ATTN_ROWS) {
     mgd_attn_rows rp;
-    mg::match_attn_rows(program_, &rp);
+    mg::match_attn_rows(program_, &rp, nullptr);
     rp.data_type = dt;
-    record_outputs(stream, {});
     return finish(mgd_launch_attn_rows_float(&rp, input_tensors[0].data_ptr, input_tensors[1].data_ptr,
-                                             input_tensors[2].data_ptr, output_tensors[0].data_ptr,
-                                             output_tensors[1].data_ptr, stream));
+                                             input_tensors[2].data_ptr, output_tensors[o_output_].data_ptr,
+                                             output_tensors[1 - o_output_].data_ptr, stream));
   }
   if (kernel_float_ == mg::KERNEL_ATTN_MERGE) {
     mgd_attn_merge mp;
-    mg::match_attn_merge(program_, &mp);
+    mg::match_attn_merge(program_, &mp, nullptr);
     mp.data_type = dt;
-    return finish(mgd_launch_attn_merge_float(&mp, input_tensors[0].data_ptr, input_tensors[1].data_ptr,
+    record_outputs(stream, {range_of(output_tensors[0].data_ptr, output_tensors[0].num_elements() * 2)});
+    return finish(mgd_launch_attn_merge_float(&mp, input_tensors[o_input_].data_ptr, input_tensors[1 - o_input_].data_ptr,
                                               output_tensors[0].data_ptr, stream));
   }
   if (causal_window != 0) {
@@ -757,7 +802,7 @@ int KNCustomizedOp::launch_float(void *stream) {
 int KNCustomizedOp::launch_split(bool fp, int num_sets, void const *const *in, long long const *in_stride,
                                  void *const *out, long long const *out_stride, KNCustomizedOp *merge, void *stream) {
   mgd_attn_split sp;
-  mg::match_attn_split(program_, 1, &sp);
+  mg::match_attn_split(program_, &sp, nullptr);
   sp.num_sets = num_sets;
   sp.q_set_stride = in_stride[0]; sp.k_set_stride = in_stride[1]; sp.v_set_stride = in_stride[2];
   sp.o_set_stride = out_stride[0]; sp.r_set_stride = out_stride[1];
@@ -769,8 +814,10 @@ int KNCustomizedOp::launch_split(bool fp, int num_sets, void const *const *in, l
   std::vector<Range> ins, outs;
   for (int i = 0; i < 3; i++)
     ins.push_back(range_of(in[i], ((size_t)(num_sets - 1) * (size_t)in_stride[i] + input_tensors[i].num_elements()) * elem));
-  for (int i = 0; i < 2; i++)
-    outs.push_back(range_of(out[i], ((size_t)(num_sets - 1) * (size_t)out_stride[i] + output_tensors[i].num_elements()) * elem));
+  for (int i = 0; i < 2; i++) { // out[0] = O', out[1] = R': output_tensors[o_output_] and the other one
+    DTensor const &t = output_tensors[i == 0 ? o_output_ : 1 - o_output_];
+    outs.push_back(range_of(out[i], ((size_t)(num_sets - 1) * (size_t)out_stride[i] + t.num_elements()) * elem));
+  }
   if (merge != nullptr) {
     DTensor const &o = merge->output_tensors[0];
     opts.merged_out = fp ? (void *)o.fp_ptr : o.data_ptr;
@@ -783,7 +830,8 @@ int KNCustomizedOp::launch_split(bool fp, int num_sets, void const *const *in, l
                                                      (uint16_t const *)in[2], (uint16_t *)out[0], (uint16_t *)out[1],
                                                      &opts, stream)
               : mgd_launch_attn_split_float_ex(&sp, in[0], in[1], in[2], out[0], out[1], &opts, stream);
-  record_outputs(stream, st == MG_OK ? outs : std::vector<Range>{});
+  if (st == MG_OK) record_outputs(stream, outs);
+  else record_anything(stream);
   return finish(st);
 }
 
@@ -797,15 +845,16 @@ bool KNCustomizedOp::can_fuse_with(KNOperator *next, bool fp) {
     // dense attention followed by the division of its two outputs
     int h, r, d;
     mgd_attn_rows rp;
-    if (fp || !mg::match_div_rows(m->program_, &h, &r, &d) || !mg::match_attn_rows(program_, &rp)) return false;
+    if (fp || !mg::match_div_rows(m->program_, &h, &r, &d, nullptr) || !mg::match_attn_rows(program_, &rp, nullptr)) return false;
     if (h != rp.heads || r != rp.seq_q || d != rp.d) return false;
   } else {
     if (mine != mg::KERNEL_ATTN_SPLIT || !tickets_) return false;
     if ((fp ? m->kernel_fp_ : m->kernel_float_) != mg::KERNEL_ATTN_MERGE) return false;
   }
   if (m->input_tensors.size() != 2 || output_tensors.size() != 2) return false;
-  for (int i = 0; i < 2; i++) {
-    DTensor const &a = output_tensors[i], &b = m->input_tensors[i];
+  for (int i = 0; i < 2; i++) { // i = 0: the attention result, i = 1: the row sums
+    DTensor const &a = output_tensors[i == 0 ? o_output_ : 1 - o_output_];
+    DTensor const &b = m->input_tensors[i == 0 ? m->o_input_ : 1 - m->o_input_];
     if (a.data_ptr != b.data_ptr || a.fp_ptr != b.fp_ptr || a.num_elements() != b.num_elements()) return false;
   }
   return true;
@@ -815,18 +864,22 @@ int KNCustomizedOp::launch_fused(KNCustomizedOp *merge, bool fp, void *stream) {
   if (int dry_st = refuse_if_dry()) return dry_st;
   if (!fp && kernel_float_ == mg::KERNEL_ATTN_ROWS) {
     mgd_attn_rows rp;
-    mg::match_attn_rows(program_, &rp);
+    mg::match_attn_rows(program_, &rp, nullptr);
     rp.data_type = (int)input_tensors[0].data_type;
-    record_outputs(stream, {});
+    record_anything(stream);
     return finish(mgd_launch_attn_rows_float_ex(&rp, input_tensors[0].data_ptr, input_tensors[1].data_ptr,
-                                                input_tensors[2].data_ptr, output_tensors[0].data_ptr,
-                                                output_tensors[1].data_ptr, merge->output_tensors[0].data_ptr, stream));
+                                                input_tensors[2].data_ptr, output_tensors[o_output_].data_ptr,
+                                                output_tensors[1 - o_output_].data_ptr,
+                                                merge->output_tensors[0].data_ptr, stream));
   }
   void const *in[3];
   void *out[2];
   long long zs[3] = {0, 0, 0};
   for (int i = 0; i < 3; i++) in[i] = fp ? (void const *)input_tensors[i].fp_ptr : input_tensors[i].data_ptr;
-  for (int i = 0; i < 2; i++) out[i] = fp ? (void *)output_tensors[i].fp_ptr : output_tensors[i].data_ptr;
+  for (int i = 0; i < 2; i++) {
+    DTensor const &t = output_tensors[i == 0 ? o_output_ : 1 - o_output_];
+    out[i] = fp ? (void *)t.fp_ptr : t.data_ptr;
+  }
   return launch_split(fp, 1, in, zs, out, zs, merge, stream);
 }
 

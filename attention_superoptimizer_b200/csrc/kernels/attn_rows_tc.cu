@@ -54,37 +54,17 @@ constexpr int kM = 128, kN = 128, kD = 128;         // query rows per block, KV 
 constexpr int kSubTile = 128 * 64 * 2;                // one [128 rows][64 cols] 16-bit box: 16 KB
 constexpr int kOperand = 2 * kSubTile;                // a 128 x 128 operand: two boxes
 constexpr int kStages = 3;
-constexpr int kWaitLimit = 2000000;
 constexpr uint32_t kTmemCols = 512;
 
-__device__ __forceinline__ uint32_t smem_u32(void const *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-               : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-  return ok != 0;
-}
+using ptx::smem_u32;
+using ptx::mbar_init;
+using ptx::mbar_expect_tx;
+using ptx::mbar_arrive;
+using ptx::mbar_try_wait;
+using ptx::tma_load_3d;
 // Bounded wait that also gives up as soon as another role has raised the abort flag.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
-  for (int i = 0; i < kWaitLimit; i++) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 1023) == 1023 && *abort_flag) return false;
-  }
-  *abort_flag = 1;
-  return false;
-}
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, CUtensorMap const *map, uint32_t bar, int c0, int c1, int c2) {
-  asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-               ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
+  return ptx::mbar_wait_or_abort(bar, parity, abort_flag);
 }
 
 // Shared-memory matrix descriptor of a K-major operand tile staged as [rows][64] boxes with the 128-byte
@@ -495,10 +475,10 @@ int launch(mgd_attn_rows const *p, void const *q, void const *k, void const *v, 
 
 using namespace mgk;
 
-// MUGRAPH_ROWS_PP=0 keeps the one-tile-per-block kernel (tuning, tests)
+// MGD_OPT_ROWS_ENGINE = 1 keeps the one-tile-per-block kernel where it supports the shape (tuning, tests)
 static bool use_two_tile_kernel(mgd_attn_rows const *p) {
   if (!pp::supported(p)) return false;
-  if (char const *e = getenv("MUGRAPH_ROWS_PP")) return atoi(e) != 0 || !tc::rows_supported(p);
+  if (option(MGD_OPT_ROWS_ENGINE) == 1) return !tc::rows_supported(p);
   return true;
 }
 

@@ -28,8 +28,9 @@
 // Every mbarrier wait is bounded: a block that gives up records a code in the device status word and
 // returns without touching its outputs further.
 #include "common.cuh"
+#include "ptx.cuh"
 #include "attn_merge.cuh"
-#include <cstdlib>
+#include <atomic>
 #include <cuda.h>
 #include <mutex>
 #include <unordered_map>
@@ -46,36 +47,16 @@ namespace mgk {
 
 constexpr int kTile = 64;        // KV positions per for-loop tile
 constexpr int kMaxStages = 6;
-constexpr int kWaitLimit = 1000000;
 constexpr int kDynSmemLimit = kSmemLimit - 1024; // the kernel also has a few bytes of static shared memory
 
 enum AttnMode { kF16 = 0, kBF16 = 1, kFingerprint = 2 };
 
-// ---- PTX wrappers ---------------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(void const *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-               : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-  return ok != 0;
-}
-// bounded wait: false after kWaitLimit polls
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-  for (int i = 0; i < kWaitLimit; i++)
-    if (mbar_try_wait(bar, parity)) return true;
-  return false;
-}
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, CUtensorMap const *map, uint32_t bar, int c0, int c1, int c2) {
-  asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-               ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
-}
+// ---- PTX wrappers (mbarrier, TMA: ptx.cuh) -----------------------------------------------------------------
+using ptx::smem_u32;
+using ptx::mbar_init;
+using ptx::mbar_expect_tx;
+using ptx::mbar_wait;
+using ptx::tma_load_3d;
 __device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t (&r)[4]) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
@@ -135,6 +116,7 @@ struct AttnSplitParams {
   int32_t *tickets;     // one counter per (set, head)
   long long merged_set_stride;
   int early_loads;      // tile loads may be issued before the wait on the previous kernel of the stream
+  int wait_limit;       // polls before a tile wait gives up
 };
 
 // Shared-memory plan: [stages x (K tile, V tile)] (1024-byte aligned) | reduction scratch | barriers | exp table
@@ -178,11 +160,10 @@ attn_split_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
 
   if (tid == 0) {
     s_failed = 0;
-    asm volatile("prefetch.tensormap [%0];" ::"l"(&k_map) : "memory");
-    asm volatile("prefetch.tensormap [%0];" ::"l"(&v_map) : "memory");
+    ptx::prefetch_tensormap(&k_map);
+    ptx::prefetch_tensormap(&v_map);
     for (int s = 0; s < p.stages; s++) mbar_init(smem_u32(&bars[s]), 1);
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    ptx::mbar_init_fence();
   }
   if (MODE == kFingerprint) // exp table with the CRT lift folded in: E = table[S mod Q]
     for (int i = tid; i < (int)Q; i += blockDim.x) exp_tab[i] = (uint16_t)((c_tables.e[i] * Q_MUL_P_MOD_1) % PQ);
@@ -235,10 +216,12 @@ attn_split_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
       }
     }
   };
+  int issued = 0; // tiles requested so far (thread 0 only): tile i lands in stage i % stages
   auto issue_first = [&]() {
     if (tid == 0) {
       int first = p.forloop < p.stages ? p.forloop : p.stages;
       for (int it = 0; it < first; it++) issue(it, it);
+      issued = first;
     }
   };
   // Ordering against the previous kernel of the stream (programmatic dependent launch): nothing is written
@@ -248,12 +231,12 @@ attn_split_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
     issue_first();
     load_q();
   }
-  asm volatile("griddepcontrol.wait;" ::: "memory");
+  ptx::grid_dependency_wait();
   if (!p.early_loads) {
     issue_first();
     load_q();
   }
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  ptx::grid_launch_dependents();
 
   acc_t oacc[2 * kNPairs][4];
 #pragma unroll
@@ -306,7 +289,7 @@ attn_split_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
     bool const active = it < p.forloop;
     // After a wait has given up the block keeps walking the loop (so that every thread still meets the
     // block-wide barriers below) but stops waiting; its results are discarded at the end.
-    if (active && !failed && !mbar_wait(smem_u32(&bars[s]), phase)) failed = true;
+    if (active && !failed && !mbar_wait(smem_u32(&bars[s]), phase, p.wait_limit)) failed = true;
     if (active) {
     uint32_t ktile = stage_base + (uint32_t)(s * 2 * kTileBytes), vtile = ktile + kTileBytes;
 
@@ -385,11 +368,14 @@ attn_split_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
     // ---- refill the stages of this round once every warp has read them -----------------------------------
     if (p.forloop > p.stages) {
       __syncthreads();
-      if (tid == 0)
+      if (tid == 0 && !failed) // a block that has given up requests nothing more
         for (int j = 0; j < p.tile_groups; j++) {
           int nxt = round * p.tile_groups + j + p.stages;
           int ns = round_s + j >= p.stages ? round_s + j - p.stages : round_s + j; // the stage tile nxt - stages used
-          if (nxt < p.forloop) issue(nxt, ns);
+          if (nxt < p.forloop) {
+            issue(nxt, ns);
+            issued = nxt + 1;
+          }
         }
     }
     s += p.tile_groups;
@@ -401,7 +387,22 @@ attn_split_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
   if (failed) s_failed = 1;
   __syncthreads(); // also: every tile has been read, the stage memory may be reused as scratch
   if (s_failed) { // a bounded wait gave up: flag it and leave the outputs alone
-    if (tid == 0) atomicExch(p.status, 1);
+    if (tid == 0) {
+      atomicExch(p.status, 1);
+      // Tile loads still in flight must land before this block's shared memory is handed to another block:
+      // stage s received tiles s, s + stages, ...; wait (bounded again) for the last of them.
+      for (int st = 0; st < p.stages && st < issued; st++) {
+        int loads = (issued - st + p.stages - 1) / p.stages;
+        mbar_wait(smem_u32(&bars[st]), (uint32_t)((loads - 1) & 1));
+      }
+      // The head's ticket counter must still come back to zero for the next launch: take the ticket, and reset
+      // the counter if this block is the last of its head.  (A healthy last block merges whatever partials there
+      // are; the status word tells the host that the outputs of this launch are incomplete.)
+      if (p.merged_out != nullptr) {
+        int ticket = atomicAdd(&p.tickets[set * p.heads + head], 1);
+        if (ticket == p.splits - 1) p.tickets[set * p.heads + head] = 0;
+      }
+    }
     return;
   }
 
@@ -643,13 +644,21 @@ static bool make_map(CUtensorMap *map, void const *base, uint64_t batch, uint64_
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+constexpr int kMaxDevices = 64;
+static int current_device() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) dev = 0;
+  return dev;
+}
+
 static int sm_count() {
-  static int n = 0;
+  static std::atomic<int> per_device[kMaxDevices];
+  int dev = current_device();
+  int n = per_device[dev].load(std::memory_order_relaxed);
   if (!n) {
-    int dev = 0;
-    cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
     if (n <= 0) n = 148;
+    per_device[dev].store(n, std::memory_order_relaxed);
   }
   return n;
 }
@@ -675,11 +684,12 @@ static bool shape_supported(mgd_attn_split const *p, bool fp) {
 template <int MODE, int DH, int FORM>
 static int launch_form(cudaLaunchConfig_t const &cfg, CUtensorMap const &kmap, CUtensorMap const &vmap,
                        AttnSplitParams const &a) {
-  static bool configured = false;
-  if (!configured) {
+  static std::atomic<bool> configured[kMaxDevices]; // the attribute is a property of the function on one device
+  int const dev = current_device();
+  if (!configured[dev].load(std::memory_order_acquire)) {
     if (cudaFuncSetAttribute(attn_split_kernel<MODE, DH, FORM>, cudaFuncAttributeMaxDynamicSharedMemorySize, kDynSmemLimit) != cudaSuccess)
       return check_launch("cudaFuncSetAttribute(attn_split_kernel)");
-    configured = true;
+    configured[dev].store(true, std::memory_order_release);
   }
   cudaLaunchKernelEx(&cfg, attn_split_kernel<MODE, DH, FORM>, kmap, vmap, a);
   return check_launch("attn_split_kernel");
@@ -709,9 +719,9 @@ static int launch_split(mgd_attn_split const *p, void const *q, void const *k, v
     if (stages > 2) stages = 2;
     tile_groups = 1;
   }
-  // tuning overrides for experiments: MUGRAPH_ATTN_STAGES, MUGRAPH_ATTN_TILE_GROUPS
-  if (char const *e = getenv("MUGRAPH_ATTN_STAGES")) stages = atoi(e) < 1 ? 1 : (atoi(e) > kMaxStages ? kMaxStages : atoi(e));
-  if (char const *e = getenv("MUGRAPH_ATTN_TILE_GROUPS")) tile_groups = atoi(e) < 1 ? 1 : atoi(e);
+  // tuning overrides (MGD_OPT_ATTN_STAGES, MGD_OPT_ATTN_TILE_GROUPS; 0 = the sizing above)
+  if (int forced = option(MGD_OPT_ATTN_STAGES)) stages = forced > kMaxStages ? kMaxStages : forced;
+  if (int forced = option(MGD_OPT_ATTN_TILE_GROUPS)) tile_groups = forced;
   if (stages > p->forloop_range) stages = p->forloop_range;
   if (tile_groups > stages) tile_groups = stages;
   while (tile_groups > 1 && groups * tile_groups * 128 > 512) tile_groups--;
@@ -741,6 +751,9 @@ static int launch_split(mgd_attn_split const *p, void const *q, void const *k, v
   a.tickets = opts ? opts->tickets : nullptr;
   a.merged_set_stride = opts ? opts->merged_set_stride : 0;
   a.early_loads = opts && (opts->overlap & 2) ? 1 : 0;
+  // MGD_OPT_WAIT_LIMIT: 0 = default, 1 = give up without polling, n = n polls
+  int const forced_limit = option(MGD_OPT_WAIT_LIMIT);
+  a.wait_limit = forced_limit == 0 ? ptx::kWaitLimit : (forced_limit == 1 ? 0 : forced_limit);
   if (a.merged_out && !a.tickets) return set_error(MG_ERR_INVALID_ARGUMENT, "split-KV attention: merging needs ticket counters");
   a.kv_len = p->kv_len; a.k_rows_are_kv = k_kv; a.v_rows_are_kv = v_kv; a.causal_window = p->causal_window;
 
@@ -811,8 +824,12 @@ int mgd_attn_decode_fused_noalloc(const mgd_attn_split *p, const void *q, const 
   int32_t *scratch = nullptr;
   int st = noalloc_scratch(&scratch);
   if (st != MG_OK) return st;
-  // the counters must start at zero; an earlier call that was cut short may have left some behind
-  if (cudaMemsetAsync(scratch, 0, (size_t)counters * sizeof(int32_t), (cudaStream_t)stream) != cudaSuccess)
+  // the counters must start at zero; an earlier call that was cut short may have left some behind.  The status
+  // word is cleared as well, so that what a call reports is its own: a timeout of an earlier call that nobody
+  // checked (check_status = 0) is forgotten here.
+  int32_t *status = scratch + kNoAllocMaxHeads;
+  if (cudaMemsetAsync(scratch, 0, (size_t)counters * sizeof(int32_t), (cudaStream_t)stream) != cudaSuccess ||
+      cudaMemsetAsync(status, 0, sizeof(int32_t), (cudaStream_t)stream) != cudaSuccess)
     return check_launch("cudaMemsetAsync(ticket counters)");
   mgd_attn_launch_opts opts;
   opts.merged_out = out;
@@ -820,7 +837,6 @@ int mgd_attn_decode_fused_noalloc(const mgd_attn_split *p, const void *q, const 
   opts.merged_set_stride = (int64_t)p->heads * p->m * p->d;
   opts.overlap = 0;
   opts.reserved = 0;
-  int32_t *status = scratch + kNoAllocMaxHeads;
   if (fp)
     st = p->d == 128 ? launch_split<kFingerprint, 128>(p, q, k, v, o_part, r_part, &opts, stream, status)
                      : launch_split<kFingerprint, 64>(p, q, k, v, o_part, r_part, &opts, stream, status);
@@ -847,10 +863,10 @@ int mgd_attn_split_supported(const mgd_attn_split *p, int32_t fingerprint_mode) 
 
 // Which engine runs a float launch: with more than 8 query rows the mma.sync path is bound by the legacy tensor
 // pipe and the tcgen05 kernel (attn_split_tc.cu) takes over where it supports the shape.
-// MUGRAPH_ATTN_TC=0 / 1 forces the choice (tuning, tests).
+// MGD_OPT_ATTN_ENGINE forces the choice (tuning, tests).
 static bool use_tensor_memory_kernel(mgd_attn_split const *p) {
   if (!stc::supported(p)) return false;
-  if (char const *e = getenv("MUGRAPH_ATTN_TC")) return atoi(e) != 0;
+  if (int forced = option(MGD_OPT_ATTN_ENGINE)) return forced == 2;
   return p->m > 8;
 }
 

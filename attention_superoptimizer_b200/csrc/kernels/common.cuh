@@ -61,6 +61,7 @@ void count_launch();
 int set_error(int code, char const *msg);
 int check_launch(char const *kernel_name); // cudaGetLastError -> MG_* status
 int32_t *device_error_word();              // 4-byte device status word, lazily allocated
+int option(int key);                       // current value of a MGD_OPT_* switch (0 = automatic)
 
 constexpr int kSmemLimit = 227 * 1024;
 

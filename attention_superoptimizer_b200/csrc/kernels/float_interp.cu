@@ -669,10 +669,8 @@ extern "C" int mgd_launch_float_interp(const mgd_program *prog, const mgd_bindin
     if (work > largest) largest = work;
   }
   unsigned threads = largest >= 8192 ? 1024u : (largest >= 2048 ? 512u : 256u);
-  if (char const *forced = std::getenv("MUGRAPH_INTERP_THREADS")) { // 256, 512 or 1024: for measurements
-    int const v = std::atoi(forced);
+  if (int const v = option(MGD_OPT_INTERP_THREADS)) // 256, 512 or 1024: for measurements
     if (v == 256 || v == 512 || v == 1024) threads = (unsigned)v;
-  }
   static bool configured_h = false, configured_b = false;
   if (dt == MG_DT_FLOAT16) {
     if (smem > 48 * 1024 && !configured_h) {

@@ -409,10 +409,8 @@ extern "C" int mgd_launch_fingerprint_interp(const mgd_program *prog, const mgd_
     if (work > largest) largest = work;
   }
   unsigned threads = largest >= 8192 ? 1024u : (largest >= 2048 ? 512u : 256u);
-  if (char const *forced = std::getenv("MUGRAPH_INTERP_THREADS")) { // 256, 512 or 1024: for measurements
-    int const v = std::atoi(forced);
+  if (int const v = option(MGD_OPT_INTERP_THREADS)) // 256, 512 or 1024: for measurements
     if (v == 256 || v == 512 || v == 1024) threads = (unsigned)v;
-  }
   fp_interp_kernel<<<(unsigned)blocks, threads, smem, (cudaStream_t)stream>>>(*prog, *bind);
   return check_launch("fp_interp_kernel");
 }

@@ -1,0 +1,78 @@
+// Inline-PTX primitives every sm_100a kernel of this library shares: shared-memory addresses, mbarriers with
+// bounded waits, TMA tile loads, proxy fences and the programmatic-dependent-launch controls.  One definition, one
+// poll limit: a wait that runs out never hangs the GPU - it reports failure to its caller, which records a code in
+// the device status word and winds the block down.
+#pragma once
+#include <cstdint>
+#include <cuda.h>
+
+namespace mgk {
+namespace ptx {
+
+// Polls of one mbarrier before a wait gives up.  At roughly 20-40 ns per poll this is tens of milliseconds: far
+// above any legitimate wait of these kernels, far below a watchdog.
+constexpr int kWaitLimit = 2000000;
+
+__device__ __forceinline__ uint32_t smem_u32(void const *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+// makes freshly initialised barriers visible to the async proxy (TMA, tcgen05.commit)
+__device__ __forceinline__ void mbar_init_fence() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+               : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded wait: false after `limit` polls.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int limit = kWaitLimit) {
+  for (int i = 0; i < limit; i++)
+    if (mbar_try_wait(bar, parity)) return true;
+  return false;
+}
+// Bounded wait of a kernel whose roles wait on one another: gives up at once when another role has raised the
+// abort flag, raises it when the limit is hit.
+__device__ __forceinline__ bool mbar_wait_or_abort(uint32_t bar, uint32_t parity, volatile int *abort_flag,
+                                                   int limit = kWaitLimit) {
+  for (int i = 0; i < limit; i++) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 1023) == 1023 && *abort_flag) return false;
+  }
+  *abort_flag = 1;
+  return false;
+}
+
+// TMA tile loads (no multicast anywhere in this library).  The innermost coordinate times the element size must be
+// a multiple of 16 bytes.
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, CUtensorMap const *map, uint32_t bar, int c0, int c1) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+               ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, CUtensorMap const *map, uint32_t bar, int c0, int c1, int c2) {
+  asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+               ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+__device__ __forceinline__ void prefetch_tensormap(CUtensorMap const *map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
+// writes of the generic proxy (st.shared) become visible to the async proxy (TMA, tcgen05 operand reads)
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// Programmatic dependent launch: wait for the previous kernel of the stream (a no-op for a plain launch), and let
+// the next kernel's blocks be scheduled.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+} // namespace ptx
+} // namespace mgk

@@ -1,5 +1,6 @@
 // Launch bookkeeping, fills, comparison and the device status word.
 #include "common.cuh"
+#include "ptx.cuh"
 #include "mugraph_rng.h"
 #include <atomic>
 #include <cstring>
@@ -24,6 +25,9 @@ int check_launch(char const *name) {
   g_err = std::string(name) + ": " + cudaGetErrorString(e);
   return MG_ERR_CUDA;
 }
+static std::atomic<int32_t> g_options[MGD_OPT_COUNT];
+int option(int key) { return key >= 0 && key < MGD_OPT_COUNT ? g_options[key].load(std::memory_order_relaxed) : 0; }
+
 int32_t *device_error_word() {
   if (!g_error_word) {
     if (cudaMalloc((void **)&g_error_word, 256) != cudaSuccess) return nullptr;
@@ -57,6 +61,17 @@ __global__ void compare_u16_kernel(uint16_t const *a, uint16_t const *b, int64_t
   bool diff = false;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) diff |= a[i] != b[i];
   if (__syncthreads_or(diff) && threadIdx.x == 0) *flag = 0;
+}
+
+// One block, one barrier with a single expected arrival that never comes: exercises the bounded wait and the
+// status word without any other work.
+__global__ void bounded_wait_selftest_kernel(int limit, int32_t *status) {
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) {
+    ptx::mbar_init(ptx::smem_u32(&bar), 1);
+    ptx::mbar_init_fence();
+    if (!ptx::mbar_wait(ptx::smem_u32(&bar), 0, limit)) atomicExch(status, 2);
+  }
 }
 
 static int grid_for(int64_t n, int threads) {
@@ -121,6 +136,25 @@ int mgd_read_and_clear_device_error(int32_t *code) {
   if (cudaMemcpy(code, w, 4, cudaMemcpyDeviceToHost) != cudaSuccess) return set_error(MG_ERR_CUDA, "status word read failed");
   if (*code != 0) cudaMemset(w, 0, 4);
   return MG_OK;
+}
+
+int mgd_set_option(int32_t key, int32_t value) {
+  if (key < 0 || key >= MGD_OPT_COUNT || value < 0) return set_error(MG_ERR_INVALID_ARGUMENT, "unknown option or negative value");
+  g_options[key].store(value, std::memory_order_relaxed);
+  return MG_OK;
+}
+int mgd_get_option(int32_t key, int32_t *value) {
+  if (key < 0 || key >= MGD_OPT_COUNT || !value) return set_error(MG_ERR_INVALID_ARGUMENT, "unknown option");
+  *value = option(key);
+  return MG_OK;
+}
+
+int mgd_selftest_bounded_wait(int32_t poll_limit, void *stream) {
+  if (poll_limit < 1 || poll_limit > ptx::kWaitLimit) return set_error(MG_ERR_INVALID_ARGUMENT, "poll limit out of range");
+  int32_t *w = device_error_word();
+  if (!w) return set_error(MG_ERR_CUDA, "cannot allocate the device status word");
+  bounded_wait_selftest_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(poll_limit, w);
+  return check_launch("bounded_wait_selftest_kernel");
 }
 
 uint64_t mgd_launch_count(void) { return g_launches.load(); }

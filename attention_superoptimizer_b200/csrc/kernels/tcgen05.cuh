@@ -3,43 +3,23 @@
 #pragma once
 #include <cstdint>
 #include <cuda.h>
+#include "ptx.cuh"
 
 namespace mgk {
 namespace t5 {
 
-constexpr int kWaitLimit = 2000000; // polls of one mbarrier before a role gives up
-
-__device__ __forceinline__ uint32_t smem_u32(void const *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-               : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-  return ok != 0;
-}
+using ptx::smem_u32;
+using ptx::mbar_init;
+using ptx::mbar_expect_tx;
+using ptx::mbar_arrive;
+using ptx::mbar_try_wait;
+using ptx::tma_load_3d;
+using ptx::fence_proxy_async_smem;
+constexpr int kWaitLimit = ptx::kWaitLimit;
 // Bounded wait; gives up at once when another role has raised the abort flag, raises it when the limit is hit.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
-  for (int i = 0; i < kWaitLimit; i++) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 1023) == 1023 && *abort_flag) return false;
-  }
-  *abort_flag = 1;
-  return false;
+  return ptx::mbar_wait_or_abort(bar, parity, abort_flag);
 }
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, CUtensorMap const *map, uint32_t bar, int c0, int c1, int c2) {
-  asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-               ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
-}
-// writes of the generic proxy (st.shared) become visible to the async proxy (tcgen05.mma operand reads)
-__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 // ---- shared-memory matrix descriptors ---------------------------------------------------------------------------
 // layout_type: 2 = 128-byte swizzle, 4 = 64-byte swizzle.  Offsets are bytes and are stored in 16-byte units.

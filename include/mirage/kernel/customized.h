@@ -56,6 +56,10 @@ private:
   bool lowered_ = false;
   mgd_program program_;
   int kernel_fp_ = -1, kernel_float_ = -1;
+  // Operand order of a matched pattern: which of the two outputs is the (un-normalised) attention result, and,
+  // for an operator that consumes such a pair, which of its two inputs is.  Hand-written plans give 0; plans
+  // found by a search may list the row-sum first.
+  int o_output_ = 0, o_input_ = 0;
   bool ensure_lowered();
   void after_build();
   int launch_split(bool fingerprint_mode, int num_sets, void const *const *in, long long const *in_stride,

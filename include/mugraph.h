@@ -124,6 +124,33 @@ int mg_runtime_set_specialisation(mg_runtime *rt, int level);
 enum { MG_POLICY_LATENCY = 0, MG_POLICY_THROUGHPUT = 1 };
 int mg_runtime_set_launch_policy(mg_runtime *rt, int policy);
 
+/* Tuning switches of the kernels (process-wide; 0 = let the library decide).  They are read when a launch is
+ * configured: a captured sequence keeps the values it was recorded with.  The reference has no such knobs. */
+enum {
+  MG_OPT_ATTN_STAGES = 0,       /* split-KV attention: shared-memory ring depth, 1..6 */
+  MG_OPT_ATTN_TILE_GROUPS = 1,  /* split-KV attention: KV tiles of the ring worked on side by side, 1..4 */
+  MG_OPT_ATTN_ENGINE = 2,       /* split-KV attention, float mode: 1 = mma.sync kernel, 2 = tcgen05 kernel */
+  MG_OPT_ROWS_ENGINE = 3,       /* dense attention: 1 = one query tile per block, 2 = two query tiles per block */
+  MG_OPT_INTERP_THREADS = 4,    /* generic interpreters: threads per block, 256 / 512 / 1024 */
+  MG_OPT_WAIT_LIMIT = 5         /* split-KV attention: polls before a tile wait gives up; 1 = give up without polling
+                                   (failure-path tests), n > 1 = n polls */
+};
+int mg_runtime_set_option(mg_runtime *rt, int32_t key, int32_t value);
+int mg_runtime_get_option(mg_runtime *rt, int32_t key, int32_t *value);
+/* The split-KV attention kernel starts fetching K and V while the previous kernel of its stream is still draining,
+ * when the library knows that kernel and knows it did not write them.  Launches, copies and fills that go through
+ * this ABI are tracked.  A caller that writes a graph's input tensors with work of its own (a kernel given
+ * data_ptr / fp_ptr) enqueued on `stream` says so with this call, after enqueueing that work and before the next
+ * launch of this library on that stream; that launch then reads its inputs only after the stream's previous kernel
+ * has completed.  No counterpart in the reference (one kernel at a time on the default stream). */
+int mg_stream_inputs_written(void *stream);
+/* Failure-path self-test (no counterpart in the reference, which exits on any CUDA error,
+ * include/mirage/utils/cuda_helper.h:30-38): enqueues a one-block kernel that waits on an mbarrier nobody arrives
+ * at, gives up after `poll_limit` polls and records a code in the device status word.  Nothing hangs or faults;
+ * the next synchronising call (mg_device_synchronize, mg_graph_fingerprint ...) returns MG_ERR_DEVICE_TIMEOUT once,
+ * and later launches run normally. */
+int mg_selftest_bounded_wait(mg_runtime *rt, int32_t poll_limit, void *stream);
+
 /* ---- kernel graph ---------------------------------------------------------
  * kernel::Graph, include/mirage/kernel/graph.h:28-85 */
 int mg_graph_create(mg_runtime *rt, mg_graph **g);

@@ -46,6 +46,24 @@ typedef struct mgd_op {
   int32_t a[MGD_OP_ARGS];
 } mgd_op;
 
+/* Names of the slots of mgd_op.a[] listed above ("+ axis" = three consecutive slots for grid x, y, z). */
+enum {
+  MGD_IN_ROW_BLOCK_STRIDE = 0 /* + axis */, MGD_IN_COL_BLOCK_STRIDE = 3 /* + axis */, MGD_IN_ROW_LOOP_STRIDE = 6,
+  MGD_IN_COL_LOOP_STRIDE = 7, MGD_IN_LEAD_BLOCK_STRIDE = 8 /* + axis */, MGD_IN_LEAD_LOOP_STRIDE = 11,
+  MGD_IN_ROWS = 12, MGD_IN_COLS = 13, MGD_IN_TILE_ROWS = 14, MGD_IN_TILE_COLS = 15, MGD_IN_LAYOUT = 16,
+  MGD_IN_TILE_OFFSET = 17, MGD_IN_SLOT = 18
+};
+enum {
+  MGD_OUT_ROW_BLOCK_STRIDE = 0 /* + axis */, MGD_OUT_COL_BLOCK_STRIDE = 3 /* + axis */,
+  MGD_OUT_LEAD_BLOCK_STRIDE = 6 /* + axis */, MGD_OUT_ROWS = 9, MGD_OUT_COLS = 10, MGD_OUT_TILE_ROWS = 11,
+  MGD_OUT_TILE_COLS = 12, MGD_OUT_SOURCE_OFFSET = 13, MGD_OUT_ACCUM_OFFSET = 14, MGD_OUT_SLOT = 15
+};
+enum { MGD_MM_M = 0, MGD_MM_N = 1, MGD_MM_K = 2, MGD_MM_A_OFFSET = 3, MGD_MM_B_OFFSET = 4, MGD_MM_C_OFFSET = 5 };
+enum { MGD_EXP_OFFSET = 0, MGD_EXP_ELEMENTS = 1 };
+enum { MGD_BIN_X_SHAPE = 0 /* + 0..2 */, MGD_BIN_Y_SHAPE = 3 /* + 0..2 */, MGD_BIN_X_OFFSET = 6, MGD_BIN_Y_OFFSET = 7,
+       MGD_BIN_OUT_OFFSET = 8 };
+enum { MGD_RED_OUT_ELEMENTS = 0, MGD_RED_DEGREE = 1, MGD_RED_INNER = 2, MGD_RED_IN_OFFSET = 3, MGD_RED_OUT_OFFSET = 4 };
+
 typedef struct mgd_program {
   int32_t grid[3];
   int32_t threads;        /* threads per block the host asks for (plan.block_dim.x) */
@@ -100,7 +118,8 @@ int mgd_attn_split_supported(const mgd_attn_split *p, int32_t fingerprint_mode);
 /* Optional extras of one split-KV launch.
  *  merged_out / tickets: also perform the second customized op of the example (:80-103) in the same launch -
  *    the last block of a head to finish sums the head's partials and divides ("last block done" ticket).
- *    tickets = heads * num_sets int32 in device memory, zero before the first use; the kernel leaves them zero.
+ *    tickets = heads * num_sets int32 in device memory, zero before the first use; the kernel leaves them zero
+ *    (also when a block's bounded wait gave up: such a block still takes its ticket).
  *  overlap: bit 0 = launch with programmatic stream serialisation, so that this kernel's blocks may be scheduled
  *    while the previous kernel of the stream drains (every global write still waits for that kernel's completion);
  *    bit 1 = none of the inputs was written by the previous kernel of this library on this stream, so the tile
@@ -164,7 +183,10 @@ int mgd_launch_attn_rows_float_ex(const mgd_attn_rows *p, const void *q, const v
  * that overlap on the GPU (different streams, or anything else that lets them run concurrently) race on them
  * and must be serialised by the caller.
  * check_status != 0: synchronise `stream` after the launch and return MG_ERR_DEVICE_TIMEOUT if a bounded device
- * wait gave up (4-byte copy, still no allocation); 0: fully asynchronous, nothing is reported. */
+ * wait gave up (4-byte copy, still no allocation); 0: fully asynchronous, nothing is reported.  The status word is
+ * cleared on `stream` at the start of every call, so a call reports only its own launch: a timeout of an earlier
+ * call made with check_status = 0 is lost once the next call starts.
+ * The shared-memory limit of the kernel is configured per device, on the first call on that device. */
 int mgd_attn_decode_fused_noalloc(const mgd_attn_split *p, const void *q, const void *k, const void *v, void *o_part,
                                   void *r_part, void *out, int32_t fingerprint_mode, int32_t check_status,
                                   void *stream);
@@ -216,6 +238,27 @@ int mgd_compare_u16(const uint16_t *a, const uint16_t *b, int64_t n, int32_t *de
 int mgd_tables_init(const uint16_t *exp_tbl, const uint16_t *div_p_tbl, const uint16_t *div_q_tbl);
 /* device status word written by kernels whose bounded waits gave up; 0 = none. Synchronises. */
 int mgd_read_and_clear_device_error(int32_t *code);
+
+/* ---- tuning switches ----------------------------------------------------------
+ * Process-wide launch options of the kernels (the reference has none: its launch shapes are the plan's).
+ * Read when a launch is configured, so a captured sequence keeps the values it was recorded with.
+ * 0 always means "let the library decide". */
+enum {
+  MGD_OPT_ATTN_STAGES = 0,        /* split-KV attention: shared-memory ring depth, 1..6 */
+  MGD_OPT_ATTN_TILE_GROUPS = 1,   /* split-KV attention: KV tiles of the ring worked on side by side, 1..4 */
+  MGD_OPT_ATTN_ENGINE = 2,        /* split-KV attention, float mode: 1 = mma.sync kernel, 2 = tcgen05 kernel */
+  MGD_OPT_ROWS_ENGINE = 3,        /* dense attention: 1 = one query tile per block, 2 = two query tiles per block */
+  MGD_OPT_INTERP_THREADS = 4,     /* generic interpreters: threads per block, 256 / 512 / 1024 */
+  MGD_OPT_WAIT_LIMIT = 5,         /* split-KV attention: polls before a tile wait gives up; 1 = give up without
+                                     polling (failure-path tests), n > 1 = n polls */
+  MGD_OPT_COUNT = 6
+};
+int mgd_set_option(int32_t key, int32_t value);
+int mgd_get_option(int32_t key, int32_t *value);
+/* Failure-path self-test: one block waits on an mbarrier nobody arrives at, for `poll_limit` polls, then records
+ * code 2 in the device status word and returns - the GPU neither hangs nor faults.  The next call that reads the
+ * status word (mgd_read_and_clear_device_error, mg_device_synchronize) reports it. */
+int mgd_selftest_bounded_wait(int32_t poll_limit, void *stream);
 uint64_t mgd_launch_count(void);
 const char *mgd_last_error(void);
 

@@ -115,6 +115,28 @@ def reference_fill(shape):
     return (np.arange(n, dtype=np.int64) % FP_PQ).astype(np.uint16).reshape(shape)
 
 
+def seeded_uniform(seed, n, modulus):
+    """Host twin of mg_rng_uniform (include/mugraph_rng.h): splitmix64 finaliser over (seed, index), upper 32 bits
+    modulo `modulus`; the device fill of the same seed produces the same uint16 values."""
+    with np.errstate(over="ignore"):
+        idx = np.arange(n, dtype=np.uint64)
+        z = np.uint64(seed) * np.uint64(0x9E3779B97F4A7C15) + idx * np.uint64(0xD1B54A32D192ED03) + np.uint64(0x632BE59BD9B4E019)
+        z = (z ^ (z >> np.uint64(30))) * np.uint64(0xBF58476D1CE4E5B9)
+        z = (z ^ (z >> np.uint64(27))) * np.uint64(0x94D049BB133111EB)
+        z = z ^ (z >> np.uint64(31))
+    return ((z >> np.uint64(32)) % np.uint64(modulus)).astype(np.uint16)
+
+
+SWEEP_BASE_SEED = 2024
+
+
+def sweep_inputs(set_index, specs, modulus=FP_P):
+    """Input tensors of set `set_index` of the verification sweep: tensor i of set s is the seeded uniform fill
+    with seed 3 * (2024 + s) + i, values in [0, modulus)."""
+    return [seeded_uniform(3 * (SWEEP_BASE_SEED + set_index) + i, int(np.prod(sp.dims)), modulus).reshape(sp.dims)
+            for i, sp in enumerate(specs)]
+
+
 def fnv1a64(values) -> int:
     """Digest used by the known-answer tables: FNV-1a over the integer values."""
     h = 1469598103934665603

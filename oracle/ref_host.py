@@ -30,6 +30,11 @@ def _ints(seq):
     return arr
 
 
+def set_threads(n):
+    """OpenMP threads for the block loop (n <= 0 leaves the setting); returns the count in effect."""
+    return int(_load().ref_set_threads(int(n)))
+
+
 def tables():
     lib = _load()
     e = np.zeros(113, np.uint16)

@@ -27,6 +27,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <omp.h>
 #include <vector>
 #include <vector_types.h>
 using std::max;
@@ -336,6 +337,12 @@ void ref_customized_set_input(void *h, int idx, uint16_t const *fp) {
 }
 
 void ref_customized_fingerprint(void *h) { ((RefOp *)h)->op->fingerprint(); }
+
+// Threads the block loop of fingerprint() uses from now on (<= 0: leave as is); returns the count in effect.
+int ref_set_threads(int n) {
+  if (n > 0) omp_set_num_threads(n);
+  return omp_get_max_threads();
+}
 
 void ref_customized_get_output(void *h, int idx, uint16_t *fp) {
   RefOp *r = (RefOp *)h;

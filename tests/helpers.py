@@ -59,14 +59,19 @@ def from_bits(b, dtype):
 RTOL = {mg.float16: 2e-3, mg.bfloat16: 1e-2}
 
 
-def assert_close(got, ref, dtype, what=""):
+def assert_close(got, ref, dtype, what="", outlier_fraction=0.0, outlier_cap=1.0):
+    """Every element within rtol * (|ref| + rms(ref)).  `outlier_fraction` > 0 lets that share of the elements
+    exceed the bound, but none by more than the factor `outlier_cap`: used only where the operand rounding of the
+    16-bit tensor cores has a heavy tail of its own (un-normalised exp weights at full size, see the test that
+    passes it).  Returns the worst relative error."""
     got = np.asarray(got, np.float64)
     ref = np.asarray(ref, np.float64)
     assert got.shape == ref.shape, (got.shape, ref.shape)
     rtol = RTOL[dtype]
     scale = np.sqrt(np.mean(ref ** 2)) + 1e-30
-    err = np.abs(got - ref)
-    bound = rtol * (np.abs(ref) + scale)
-    worst = float(np.max(err / (np.abs(ref) + scale)))
-    assert np.all(err <= bound), "%s: worst relative error %.3e > %.1e" % (what, worst, rtol)
+    rel = np.abs(got - ref) / (np.abs(ref) + scale)
+    worst = float(np.max(rel))
+    over = int(np.count_nonzero(rel > rtol))
+    assert over <= outlier_fraction * rel.size, "%s: worst relative error %.3e > %.1e (%d elements over)" % (what, worst, rtol, over)
+    assert worst <= rtol * max(1.0, outlier_cap), "%s: worst relative error %.3e > %.1e x %.2f" % (what, worst, rtol, outlier_cap)
     return worst

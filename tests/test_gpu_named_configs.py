@@ -1,0 +1,415 @@
+"""GPU parity at the sizes and input distributions the benchmark configurations name, plus the kernel-level
+operators and the failure path.  Everything goes through the C ABI; fingerprints must be bit-exact, float mode
+within 2e-3 (fp16) / 1e-2 (bf16) of an fp32 / fp64 host evaluation (helpers.assert_close)."""
+import json
+import os
+
+import numpy as np
+import pytest
+
+import attention_superoptimizer_b200 as mg
+from oracle import mugraph_oracle as mo
+from tests.helpers import assert_close, from_bits, to_bits, to_package_plan
+
+pytestmark = pytest.mark.gpu
+BIG = 227 * 1024
+GOLDEN_SWEEP = os.path.join(os.path.dirname(__file__), "golden", "sweep_digests_gqa_decode.json")
+
+
+# ---- dense prefill at full size ---------------------------------------------------------------------------------
+@pytest.mark.parametrize("engine", [mg.ROWS_TWO_TILES, mg.ROWS_ONE_TILE], ids=["two_tiles", "one_tile"])
+def test_float_prefill_full_size(runtime, engine):
+    """Multi-head attention prefill as the benchmark runs it: 32 heads, 2048 x 2048, head_dim 128, bf16, K and V
+    column-major.  256 blocks of the two-tile kernel on 148 SMs (a second wave on SMs whose tensor memory has just
+    been released, 16 KV tiles per block) and 512 blocks of the one-tile kernel.  The un-normalised accumulator,
+    the row sums and the divided output are compared with an fp32 evaluation; a second run must be identical.
+
+    Tolerance: this muGraph has no running maximum, so E = exp(S) is log-normal and a few large weights dominate
+    an output element; rounding E to bf16 for the second contraction (8 significant bits, as any bf16 tensor-core
+    attention does) then has a heavy-tailed error.  An exact model of that pipeline (fp32 S, E rounded to bf16,
+    fp32 accumulation, bf16 store) evaluated on the host shows a worst element of 7e-3 to 8.3e-3 per head against
+    the 1e-2 bound; over 32 heads (8.4 M elements per tensor) an element now and then lands a few percent above it.
+    So here, and only here, one element per million may exceed the bound, none by more than a factor 1.5; the
+    root-mean-square error must stay below a quarter of the bound."""
+    H, SQ, D, L = 32, 2048, 128, 2048
+    dtype = mg.bfloat16
+    runtime.set_max_smem(BIG)
+    runtime.set_specialisation(2)
+    runtime.set_option(mg.OPT_ROWS_ENGINE, engine)
+    rng = np.random.default_rng(404)
+    rnd = lambda a: from_bits(to_bits(a, dtype), dtype)
+    try:
+        with mg.PyGraph(runtime) as g:
+            Q = g.new_input((H, SQ, D), dtype)
+            K = g.new_input((H, D, L), dtype, mg.DmemColumnMajor)
+            V = g.new_input((H, L, D), dtype, mg.DmemColumnMajor)
+            p1, p2 = mg.attention_prefill_plans(H, SQ, D, L)
+            acc = g.customized([Q, K, V], p1)
+            out = g.customized(acc, p2)
+            assert g.customized_info(3)["kernel_float"] == mg.KERNEL_ATTN_ROWS
+            q = rnd(rng.standard_normal((H, SQ, D), dtype=np.float32) / np.sqrt(D))
+            k = rnd(rng.standard_normal((H, D, L), dtype=np.float32))
+            v = rnd(rng.standard_normal((H, L, D), dtype=np.float32))
+            Q.upload_data(to_bits(q, dtype))
+            K.upload_data(to_bits(np.ascontiguousarray(k.transpose(0, 2, 1)), dtype))
+            V.upload_data(to_bits(np.ascontiguousarray(v.transpose(0, 2, 1)), dtype))
+            g.run()
+            got_acc = from_bits(acc[0].download_data(), dtype).reshape(acc[0].shape)
+            got_r = from_bits(acc[1].download_data(), dtype).reshape(acc[1].shape)
+            got = from_bits(out[0].download_data(), dtype).reshape(out[0].shape)
+            # fp32 evaluation head by head (keeps the host working set small)
+            want_acc, want_r = np.empty_like(got_acc), np.empty_like(got_r)
+            for h in range(H):
+                e = np.exp(q[h] @ k[h])
+                want_r[h] = e.sum(axis=1, keepdims=True)
+                want_acc[h] = e @ v[h]
+            for name, a, b in (("O_acc", got_acc, want_acc), ("R", got_r, want_r), ("O", got, want_acc / want_r)):
+                assert_close(a, b, dtype, name, outlier_fraction=1e-6, outlier_cap=1.5)
+                rms_err = np.sqrt(np.mean((a.astype(np.float64) - b) ** 2)) / np.sqrt(np.mean(b.astype(np.float64) ** 2))
+                assert rms_err < 2.5e-3, "%s: rms relative error %.2e" % (name, rms_err)
+            g.run()
+            again = from_bits(out[0].download_data(), dtype).reshape(out[0].shape)
+            assert np.array_equal(got, again)
+    finally:
+        runtime.set_option(mg.OPT_ROWS_ENGINE, mg.ROWS_AUTO)
+
+
+# ---- matmul chain on the named input distribution ------------------------------------------------------------------
+def chain_plans():
+    chain = mo.ExecutionPlan(
+        ops=[(mo.TB_MATMUL_OP, [(0, 0), (1, 0)]), (mo.TB_MATMUL_OP, [(3, 0), (2, 0)])],
+        input_map=[(-1, -1, -1), (1, -1, -1), (0, -1, -1)], forloop_dim=[1, 0, -1],
+        input_smem_layouts=[mo.SmemRowMajor] * 3, output_map=(1, -1, -1), forloop_range=16, grid_dim=(16, 1, 1),
+        reduction_dimx=1024)
+    reduce_plan = mo.ExecutionPlan(ops=[(mo.TB_REDUCTION_1_TO_DIMX_OP, [(0, 0)])], input_map=[(0, -1, -1)],
+                                   forloop_dim=[-1], input_smem_layouts=[mo.SmemRowMajor], output_map=(0, -1, -1),
+                                   forloop_range=1, grid_dim=(16, 1, 1), reduction_dimx=1024)
+    return chain, reduce_plan
+
+
+@pytest.mark.parametrize("specialisation", [2, 0], ids=["default", "interpreter"])
+@pytest.mark.parametrize("dtype", [mg.float16, mg.bfloat16], ids=["fp16", "bf16"])
+def test_float_matmul_chain_named_distribution(runtime, dtype, specialisation):
+    """X[16,1024] W1[1024,1024] W2[1024,1024] with every tensor ~ N(0, 0.02), as the configuration names it.  The
+    block partials are about 2e-3 in magnitude (normal fp16 numbers), the result about 8e-3.  The partial tensor is
+    compared with the fp32 evaluation of the first operator, the result with the fp32 evaluation of the second
+    operator on the stored partials and with the fp64 product of the three matrices."""
+    runtime.set_max_smem(BIG)
+    runtime.set_specialisation(specialisation)
+    rng = np.random.default_rng(20)
+    specs = [mo.DTensorSpec((16, 1024), dtype), mo.DTensorSpec((1024, 1024), dtype), mo.DTensorSpec((1024, 1024), dtype)]
+    chain, reduce_plan = chain_plans()
+    x = [from_bits(to_bits(rng.standard_normal(s.dims) * 0.02, dtype), dtype) for s in specs]
+    try:
+        with mg.PyGraph(runtime) as g:
+            ins = [g.new_input(s.dims, dtype, s.layout) for s in specs]
+            for t, a in zip(ins, x):
+                t.upload_data(to_bits(a, dtype))
+            part = g.customized(ins, to_package_plan(chain))
+            outs = g.customized(part, to_package_plan(reduce_plan))
+            g.run()
+            got_part = from_bits(part[0].download_data(), dtype).reshape(part[0].shape)
+            got = from_bits(outs[0].download_data(), dtype).reshape(outs[0].shape)
+    finally:
+        runtime.set_specialisation(2)
+    g1 = mo.build_customized(specs, chain, max_smem=BIG)
+    assert_close(got_part, mo.run_float(g1, x)[0], dtype, "chain partials")
+    g2 = mo.build_customized(mo.output_specs(g1), reduce_plan, max_smem=BIG)
+    assert_close(got, mo.run_float(g2, [got_part])[0], dtype, "chain result from the stored partials")
+    exact = (x[0].astype(np.float64) @ x[1].astype(np.float64)) @ x[2].astype(np.float64)
+    assert 1e-3 < np.sqrt(np.mean(exact ** 2)) < 1e-1
+    assert_close(got, exact, dtype, "chain result vs fp64 product")
+
+
+@pytest.mark.parametrize("specialisation", [2, 0], ids=["default", "interpreter"])
+def test_fingerprint_matmul_chain_full_size(runtime, specialisation):
+    """The same chain in fingerprint mode at full size, inputs uniform in [0, 227): both operators bit-exact."""
+    runtime.set_max_smem(BIG)
+    runtime.set_specialisation(specialisation)
+    rng = np.random.default_rng(21)
+    specs = [mo.DTensorSpec((16, 1024)), mo.DTensorSpec((1024, 1024)), mo.DTensorSpec((1024, 1024))]
+    chain, reduce_plan = chain_plans()
+    x = [rng.integers(0, mo.FP_P, size=s.dims).astype(np.uint16) for s in specs]
+    try:
+        with mg.PyGraph(runtime) as g:
+            ins = [g.new_input(s.dims) for s in specs]
+            for t, a in zip(ins, x):
+                t.upload_fingerprint(a)
+            part = g.customized(ins, to_package_plan(chain))
+            outs = g.customized(part, to_package_plan(reduce_plan))
+            g.fingerprint()
+            got_part, got = part[0].download_fingerprint(), outs[0].download_fingerprint()
+            g.fingerprint()
+            assert np.array_equal(got, outs[0].download_fingerprint())
+    finally:
+        runtime.set_specialisation(2)
+    g1 = mo.build_customized(specs, chain, max_smem=BIG)
+    want_part = mo.run_fingerprint(g1, x)[0]
+    assert np.array_equal(got_part, want_part)
+    assert np.array_equal(got, mo.fp_matmul(mo.fp_matmul(x[0], x[1]), x[2]))
+
+
+# ---- verification sweep against digests of the reference's own code ------------------------------------------------------
+def test_sweep_sets_match_reference_digests(runtime):
+    """256 input sets of the sweep (device-side seeded fills, 64 sets per batched launch) against the digests the
+    reference's host code produced for the same seeds."""
+    import torch
+    with open(GOLDEN_SWEEP) as f:
+        golden = json.load(f)
+    sh = golden["shape"]
+    B, M, D, L, S, F = sh["B"], sh["M"], sh["D"], sh["L"], sh["S"], sh["F"]
+    nsets, chunk = 256, 64
+    runtime.set_specialisation(2)
+    with mg.PyGraph(runtime) as g:
+        Q = g.new_input((B, M, D))
+        K = g.new_input((B, D, L), layout=mg.DmemColumnMajor)
+        V = g.new_input((B, L, D), layout=mg.DmemColumnMajor)
+        p1, p2 = mg.gqa_decode_plans(B, M, D, L, S, F)
+        out = g.customized(g.customized([Q, K, V], p1), p2)
+        elems = [t.num_elements for t in (Q, K, V)]
+        bufs = [torch.empty(chunk * n, dtype=torch.int16, device="cuda") for n in elems]
+        result = torch.zeros(nsets * out[0].num_elements, dtype=torch.int16, device="cuda")
+        wbytes = g.fingerprint_batched_workspace(chunk)
+        work = torch.empty(max(wbytes, 256), dtype=torch.uint8, device="cuda")
+        for c in range(nsets // chunk):
+            for i, (buf, n) in enumerate(zip(bufs, elems)):
+                for s in range(chunk):
+                    mg.fill_fingerprint_seeded_raw(runtime, buf.data_ptr() + 2 * s * n, n, 3 * (2024 + c * chunk + s) + i, mg.FP_P)
+            g.fingerprint_batched(chunk, [b.data_ptr() for b in bufs], result.data_ptr() + 2 * c * chunk * out[0].num_elements,
+                                  work.data_ptr(), wbytes)
+            mg.synchronize()
+        host = result.cpu().numpy().view(np.uint16).reshape(nsets, -1)
+    for s in range(nsets):
+        assert str(mo.fnv1a64(host[s])) == golden["digests"][s], "set %d" % s
+    for s, head in golden["head_of_set"].items():
+        if int(s) < nsets:
+            assert host[int(s)][:4].tolist() == head
+    # the host twin of the device fill, and the numpy oracle, agree with the same digests
+    specs, o1, o2 = mo.gqa_decode_plans(B, M, D, L, S, F)
+    x = mo.sweep_inputs(3, specs)
+    assert np.array_equal(mo.unfused_attention_fp(*x).ravel(), host[3])
+
+
+# ---- un-fused kernel-level operators --------------------------------------------------------------------------------------
+@pytest.mark.parametrize("shapes", [((4, 8, 64), (4, 8, 64)), ((4, 8, 64), (4, 8, 1)), ((2, 3, 16, 40), (2, 3, 1, 40)),
+                                    ((33, 17), (1, 17))], ids=["same", "bcast_last", "bcast_rows_4d", "bcast_first"])
+def test_kn_binary_operators_both_modes(runtime, shapes):
+    """Graph::add / mul / div (src/kernel/element_binary.cc; fingerprints: element_binary_kernel.cu:97-168) with and
+    without broadcasting: fingerprints bit-exact against the oracle, float values against numpy."""
+    xs, ys = shapes
+    rng = np.random.default_rng(sum(xs) + sum(ys))
+    with mg.PyGraph(runtime) as g:
+        X, Y = g.new_input(xs), g.new_input(ys)
+        outs = {"add": g.add(X, Y), "mul": g.mul(X, Y), "div": g.div(X, Y)}
+        for hi in (mo.FP_P, mo.FP_PQ):
+            x = rng.integers(0, hi, size=xs).astype(np.uint16)
+            y = rng.integers(0, hi, size=ys).astype(np.uint16)
+            y.ravel()[:2] = 0  # the zero divisor maps to "inverse" 1 in both residue fields
+            X.upload_fingerprint(x)
+            Y.upload_fingerprint(y)
+            g.fingerprint()
+            assert np.array_equal(outs["add"].download_fingerprint(), mo.kn_add_fp(x, y))
+            assert np.array_equal(outs["mul"].download_fingerprint(), mo.kn_mul_fp(x, y))
+            assert np.array_equal(outs["div"].download_fingerprint(), mo.kn_div_fp(x, y))
+        for dtype in (mg.float16,):
+            rnd = lambda a: from_bits(to_bits(a, dtype), dtype)
+            x = rnd(rng.standard_normal(xs))
+            y = rnd(rng.standard_normal(ys) * 0.25 + 2.0)
+            X.upload_data(to_bits(x, dtype))
+            Y.upload_data(to_bits(y, dtype))
+            g.run()
+            for name, want in (("add", x + y), ("mul", x * y), ("div", x / y)):
+                got = from_bits(outs[name].download_data(), dtype).reshape(outs[name].shape)
+                assert_close(got, want, dtype, name)
+
+
+@pytest.mark.parametrize("dtype", [mg.float16, mg.bfloat16], ids=["fp16", "bf16"])
+def test_kn_float_matmul_exp_reduction(runtime, dtype):
+    """The float kernels of the un-fused graph (what a search times candidates against): batched matmul with a
+    column-major B, exp, reduction along the last dim and along a middle dim."""
+    B, M, D, L = 3, 8, 64, 256
+    rng = np.random.default_rng(91)
+    rnd = lambda a: from_bits(to_bits(a, dtype), dtype)
+    with mg.PyGraph(runtime) as g:
+        Q = g.new_input((B, M, D), dtype)
+        K = g.new_input((B, D, L), dtype, mg.DmemColumnMajor)
+        V = g.new_input((B, L, D), dtype)
+        S = g.matmul(Q, K)
+        E = g.exp(S)
+        R = g.reduction(E, 2)
+        P = g.div(E, R)
+        O = g.matmul(P, V)
+        H = g.reduction(V, 1, 64)  # [B, 256, D] -> [B, 64, D]: sums of 4 rows strided by 64
+        q = rnd(rng.standard_normal((B, M, D)) / np.sqrt(D))
+        k = rnd(rng.standard_normal((B, D, L)))
+        v = rnd(rng.standard_normal((B, L, D)))
+        Q.upload_data(to_bits(q, dtype))
+        K.upload_data(to_bits(np.ascontiguousarray(k.transpose(0, 2, 1)), dtype))
+        V.upload_data(to_bits(v, dtype))
+        g.run()
+        rd = lambda t: from_bits(t.download_data(), dtype).reshape(t.shape)
+        s = rd(S)
+        assert_close(s, q.astype(np.float64) @ k.astype(np.float64), dtype, "S")
+        e = rd(E)
+        assert_close(e, np.exp(s.astype(np.float64)), dtype, "exp on the stored S")
+        r = rd(R)
+        assert_close(r, e.astype(np.float64).sum(axis=2, keepdims=True), dtype, "row sums of the stored E")
+        pr = rd(P)
+        assert_close(pr, e.astype(np.float64) / r, dtype, "division")
+        assert_close(rd(O), pr.astype(np.float64) @ v, dtype, "P V")
+        if dtype == mg.float16:  # bf16 storage of S alone (8 bits under an exp) already costs more than this bound
+            assert_close(rd(O), mo.attention_fp32(q, k, v), mg.bfloat16, "whole un-fused attention")
+        want_h = v.astype(np.float64).reshape(B, L // 64, 64, D).sum(axis=1)
+        assert_close(rd(H), want_h, dtype, "strided reduction")
+        x = [rng.integers(0, mo.FP_PQ, size=t.shape).astype(np.uint16) for t in (Q, K, V)]
+        for t, a in zip((Q, K, V), x):
+            t.upload_fingerprint(a)
+        g.fingerprint()
+        assert np.array_equal(O.download_fingerprint(), mo.unfused_attention_fp(*x))
+        assert np.array_equal(H.download_fingerprint(), mo.kn_reduction_fp(x[2], 1, 64))
+
+
+# ---- launch policies ------------------------------------------------------------------------------------------------------
+def test_throughput_policy_parity_and_captured_overlap(runtime):
+    """The launch sizing the benchmark's headline uses (small blocks, several calls in flight): every graph on its
+    own stream lane inside one captured step, replayed three times; each output against the fp32 evaluation, the
+    device status word clean."""
+    import torch
+    B, M, D, L, S, F = 8, 4, 128, 4096, 16, 4
+    ngraphs = 6
+    rng = np.random.default_rng(55)
+    rnd = lambda a: from_bits(to_bits(a, mg.float16), mg.float16)
+    runtime.set_specialisation(2)
+    graphs, wants = [], []
+    try:
+        runtime.set_launch_policy(mg.POLICY_THROUGHPUT)
+        for i in range(ngraphs):
+            g = mg.PyGraph(runtime)
+            Q = g.new_input((B, M, D)); K = g.new_input((B, D, L), layout=mg.DmemColumnMajor); V = g.new_input((B, L, D))
+            p1, p2 = mg.gqa_decode_plans(B, M, D, L, S, F)
+            out = g.customized(g.customized([Q, K, V], p1), p2)
+            q = rnd(rng.standard_normal((B, M, D)) / np.sqrt(D)); k = rnd(rng.standard_normal((B, D, L))); v = rnd(rng.standard_normal((B, L, D)))
+            Q.upload_data(to_bits(q, mg.float16))
+            K.upload_data(to_bits(np.ascontiguousarray(k.transpose(0, 2, 1)), mg.float16))
+            V.upload_data(to_bits(v, mg.float16))
+            graphs.append((g, out[0]))
+            wants.append(mo.attention_fp32(q, k, v))
+        main = torch.cuda.Stream()
+        lanes = [main] + [torch.cuda.Stream() for _ in range(2)]
+        for g, _ in graphs:
+            g.run(stream=main.cuda_stream, sync=False)
+        torch.cuda.synchronize()
+
+        def record():
+            ev = torch.cuda.Event(); ev.record(main)
+            for s in lanes[1:]:
+                s.wait_event(ev)
+            for rep in range(2):  # a graph is launched twice per step, always on the same lane
+                for i, (g, _) in enumerate(graphs):
+                    g.run(stream=lanes[i % len(lanes)].cuda_stream, sync=False)
+            for s in lanes[1:]:
+                e = torch.cuda.Event(); e.record(s); main.wait_event(e)
+
+        seq = mg.CapturedSequence(main.cuda_stream, record)
+        for _ in range(3):
+            seq.launch()
+        mg.synchronize()  # raises if a bounded wait gave up
+        seq.close()
+        for (g, out), want in zip(graphs, wants):
+            got = from_bits(out.download_data(), mg.float16).reshape(out.shape)
+            assert_close(got, want, mg.float16, "throughput policy")
+    finally:
+        runtime.set_launch_policy(mg.POLICY_LATENCY)
+        for g, _ in reversed(graphs):
+            g.close()
+
+
+# ---- failure path -----------------------------------------------------------------------------------------------------------
+def test_bounded_wait_reports_timeout_and_context_survives(runtime):
+    """A device wait that nobody satisfies gives up after its poll limit, the status word travels back as
+    MG_ERR_DEVICE_TIMEOUT exactly once, and the next launches work.  Nothing here faults or hangs the GPU: the wait
+    is a bounded loop."""
+    runtime.set_specialisation(2)
+    mg.synchronize()
+    runtime.selftest_bounded_wait(poll_limit=2000)
+    with pytest.raises(mg.MuGraphError) as e:
+        mg.synchronize()
+    assert e.value.status == 6
+    mg.synchronize()  # reported once, then clean
+    B, M, D, L, S, F = 2, 4, 128, 1024, 4, 4
+    rng = np.random.default_rng(8)
+    with mg.PyGraph(runtime) as g:
+        Q = g.new_input((B, M, D)); K = g.new_input((B, D, L), layout=mg.DmemColumnMajor); V = g.new_input((B, L, D), layout=mg.DmemColumnMajor)
+        p1, p2 = mg.gqa_decode_plans(B, M, D, L, S, F)
+        out = g.customized(g.customized([Q, K, V], p1), p2)
+        x = [rng.integers(0, mo.FP_PQ, size=t.shape).astype(np.uint16) for t in (Q, K, V)]
+        for t, a in zip((Q, K, V), x):
+            t.upload_fingerprint(a)
+        want = mo.unfused_attention_fp(*x)
+        g.fingerprint()
+        assert np.array_equal(out[0].download_fingerprint(), want)
+        # The fused split-KV kernel with a tile wait that gives up without polling: every block reports, takes its
+        # ticket and drains its loads; the call returns the timeout status; the head counters are back at zero, so
+        # the next evaluation is right again.
+        runtime.set_option(mg.OPT_WAIT_LIMIT, 1)
+        try:
+            with pytest.raises(mg.MuGraphError) as e:
+                g.fingerprint()
+            assert e.value.status == 6
+        finally:
+            runtime.set_option(mg.OPT_WAIT_LIMIT, 0)
+        for _ in range(2):
+            g.fingerprint()
+            assert np.array_equal(out[0].download_fingerprint(), want)
+
+
+# ---- operand order of searched candidates ----------------------------------------------------------------------------------
+@pytest.mark.parametrize("specialisation", [2, 1, 0], ids=["fused", "specialised", "interpreter"])
+def test_attention_plans_with_the_row_sum_first(runtime, specialisation):
+    """Plans as a search emits them: the row reduction before the second matmul, so the operator's outputs are
+    [row sums, attention partials], and the merge operator takes them in that order.  The specialised kernels must
+    be selected for this order too, and all engines agree with the oracle in both modes."""
+    B, M, D, L, S, F = 4, 4, 128, 2048, 8, 4
+    runtime.set_max_smem(BIG)
+    runtime.set_specialisation(specialisation)
+    rng = np.random.default_rng(17)
+    plan1 = mg.ExecutionPlan(
+        ops=[(mg.TB_MATMUL_OP, [(0, 0), (1, 0)]), (mg.TB_EXP_OP, [(3, 0)]), (mg.TB_REDUCTION_2_OP, [(4, 0)]),
+             (mg.TB_MATMUL_OP, [(4, 0), (2, 0)])],
+        input_map=[(0, -1, -1), (0, 2, -1), (0, 1, -1)], forloop_dim=[-1, 2, 1],
+        input_smem_layouts=[mg.SmemRowMajor, mg.SmemColumnMajor, mg.SmemColumnMajor], output_map=(0, 2, -1),
+        forloop_range=F, grid_dim=(B, S, 1), reduction_dimx=D)
+    plan2 = mg.ExecutionPlan(
+        ops=[(mg.TB_REDUCTION_2_OP, [(0, 0)]), (mg.TB_REDUCTION_2_TO_DIMX_OP, [(1, 0)]), (mg.TB_DIV_OP, [(3, 0), (2, 0)])],
+        input_map=[(0, -1, -1), (0, -1, -1)], forloop_dim=[-1, -1], input_smem_layouts=[mg.SmemRowMajor] * 2,
+        output_map=(0, -1, -1), forloop_range=1, grid_dim=(B, 1, 1), reduction_dimx=D)
+    try:
+        with mg.PyGraph(runtime) as g:
+            Q = g.new_input((B, M, D)); K = g.new_input((B, D, L), layout=mg.DmemColumnMajor); V = g.new_input((B, L, D))
+            parts = g.customized([Q, K, V], plan1)
+            assert parts[0].shape == (B, M, S) and parts[1].shape == (B, M, S * D)
+            out = g.customized(parts, plan2)
+            if specialisation > 0:
+                assert g.customized_info(3)["kernel_float"] == mg.KERNEL_ATTN_SPLIT
+                assert g.customized_info(3)["kernel_fingerprint"] == mg.KERNEL_ATTN_SPLIT
+                assert g.customized_info(4)["kernel_fingerprint"] == mg.KERNEL_ATTN_MERGE
+            x = [rng.integers(0, mo.FP_PQ, size=t.shape).astype(np.uint16) for t in (Q, K, V)]
+            for t, a in zip((Q, K, V), x):
+                t.upload_fingerprint(a)
+            g.fingerprint()
+            assert np.array_equal(out[0].download_fingerprint(), mo.unfused_attention_fp(*x))
+            from tests.helpers import spec_of, to_oracle_plan
+            g1 = mo.build_customized([spec_of(t) for t in (Q, K, V)], to_oracle_plan(plan1), max_smem=BIG)
+            want1 = mo.run_fingerprint(g1, x)
+            assert np.array_equal(parts[0].download_fingerprint(), want1[0])
+            assert np.array_equal(parts[1].download_fingerprint(), want1[1])
+            rnd = lambda a: from_bits(to_bits(a, mg.float16), mg.float16)
+            q = rnd(rng.standard_normal((B, M, D)) / np.sqrt(D)); k = rnd(rng.standard_normal((B, D, L))); v = rnd(rng.standard_normal((B, L, D)))
+            Q.upload_data(to_bits(q, mg.float16))
+            K.upload_data(to_bits(np.ascontiguousarray(k.transpose(0, 2, 1)), mg.float16))
+            V.upload_data(to_bits(v, mg.float16))
+            g.run()
+            got = from_bits(out[0].download_data(), mg.float16).reshape(out[0].shape)
+            assert_close(got, mo.attention_fp32(q, k, v), mg.float16, "row sum first")
+    finally:
+        runtime.set_specialisation(2)

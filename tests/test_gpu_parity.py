@@ -424,15 +424,15 @@ def test_float_spec_decode_c3_full_size(runtime):
         for t, a in zip(ins, mem):
             t.upload_data(to_bits(a, mg.float16))
         want = mo.attention_fp32_causal_window(q, k, v, W)
-        for engine in ("1", "0"):
-            os.environ["MUGRAPH_ATTN_TC"] = engine
+        for engine in (mg.ENGINE_TCGEN05, mg.ENGINE_MMA_SYNC):
+            runtime.set_option(mg.OPT_ATTN_ENGINE, engine)
             try:
                 g.run()
                 g.run()  # again: barriers, tensor memory and the launch order are set up afresh by every launch
             finally:
-                del os.environ["MUGRAPH_ATTN_TC"]
+                runtime.set_option(mg.OPT_ATTN_ENGINE, mg.ENGINE_AUTO)
             final = from_bits(f[0].download_data(), mg.float16).reshape(f[0].shape)
-            assert_close(final, want, mg.float16, "masked output, engine %s" % engine)
+            assert_close(final, want, mg.float16, "masked output, engine %d" % engine)
 
 
 def build_prefill(g, H, SQ, D, L, dtype, kl=mg.DmemColumnMajor, vl=mg.DmemColumnMajor):

@@ -166,3 +166,21 @@ def test_invalid_plans_are_rejected():
         mo.build_customized(specs, bad)
     with pytest.raises(mo.InvalidGraph):
         mo.build_customized(specs, p1, max_smem=512)
+
+
+def test_oracle_matches_reference_sweep_digests():
+    """The committed per-set digests of the verification sweep (produced by the reference's own host code) against
+    the numpy restatement, on a few of the 4096 sets."""
+    import json
+    import os
+    path = os.path.join(os.path.dirname(__file__), "golden", "sweep_digests_gqa_decode.json")
+    with open(path) as f:
+        golden = json.load(f)
+    sh = golden["shape"]
+    assert len(golden["digests"]) == 4096
+    specs, _, _ = mo.gqa_decode_plans(sh["B"], sh["M"], sh["D"], sh["L"], sh["S"], sh["F"])
+    for s in (0, 1, 2047, 4095):
+        out = mo.unfused_attention_fp(*mo.sweep_inputs(s, specs))
+        assert str(mo.fnv1a64(out)) == golden["digests"][s]
+        if str(s) in golden["head_of_set"]:
+            assert out.ravel()[:4].tolist() == golden["head_of_set"][str(s)]
