@@ -390,6 +390,19 @@ class PyGraph:
                                                     ctypes.c_void_p(workspace_ptr), ctypes.byref(sz),
                                                     ctypes.c_void_p(stream or 0)))
 
+    def run_batched(self, num_sets, in_ptrs, out_ptr, workspace_ptr, workspace_bytes, stream=None):
+        """`num_sets` independent float-mode calls of this graph as one pass (device pointers to dense
+        [set][tensor] arrays of 16-bit values); asynchronous on `stream`."""
+        arr = (ctypes.c_void_p * len(in_ptrs))(*in_ptrs)
+        sz = ctypes.c_size_t(workspace_bytes)
+        check(self.lib.mg_graph_run_batched(self.handle, num_sets, arr, ctypes.c_void_p(out_ptr),
+                                            ctypes.c_void_p(workspace_ptr), ctypes.byref(sz), ctypes.c_void_p(stream or 0)))
+
+    def run_batched_workspace(self, num_sets):
+        sz = ctypes.c_size_t(0)
+        check(self.lib.mg_graph_run_batched(self.handle, num_sets, None, None, None, ctypes.byref(sz), None))
+        return sz.value
+
     def fingerprint_batched_workspace(self, num_sets):
         sz = ctypes.c_size_t(0)
         check(self.lib.mg_graph_fingerprint_batched(self.handle, num_sets, None, None, None, ctypes.byref(sz), None))
@@ -437,6 +450,22 @@ class CapturedSequence:
         if self.handle:
             check(self.lib.mg_captured_destroy(self.handle))
             self.handle = None
+
+
+def compare_fingerprint_rows(runtime, a_ptr, b_ptr, rows, row_elements, flags_ptr, mismatch_count_ptr=None, stream=None):
+    """Row-wise equality of two device arrays of fingerprints; flags_ptr -> int32[rows] (1 = equal),
+    mismatch_count_ptr -> optional int32 (rows that differ).  Asynchronous on `stream`."""
+    check(runtime.lib.mg_compare_fingerprint_rows(runtime.handle, ctypes.c_void_p(a_ptr), ctypes.c_void_p(b_ptr), int(rows),
+                                                  int(row_elements), ctypes.c_void_p(flags_ptr),
+                                                  ctypes.c_void_p(mismatch_count_ptr or 0), ctypes.c_void_p(stream or 0)))
+
+
+def fill_data_seeded_raw(runtime, device_ptr, num_elements, seed, sigma, dtype=None):
+    """Seeded N(0, sigma) fill of caller-owned device memory holding 16-bit floats."""
+    pod = mg_tensor()
+    pod.data_type, pod.num_dims, pod.dim[0] = dtype or float16, 1, int(num_elements)
+    pod.data_ptr = int(device_ptr)
+    check(runtime.lib.mg_tensor_fill_data_seeded(runtime.handle, ctypes.byref(pod), int(seed), float(sigma)))
 
 
 def fill_fingerprint_seeded_raw(runtime, device_ptr, num_elements, seed, modulus=FP_P):

@@ -75,11 +75,14 @@ SIGNATURES = {
     "mg_op_fingerprint": (ctypes.c_int, [_P, _I]),
     "mg_graph_fingerprint": (ctypes.c_int, [_P]),
     "mg_graph_fingerprint_compute": (ctypes.c_int, [_P]),
+    "mg_graph_fingerprint_enqueue": (ctypes.c_int, [_P, _P]),
     "mg_op_run": (ctypes.c_int, [_P, _I, _P]),
     "mg_op_profile": (ctypes.c_int, [_P, _I, _I, _I, ctypes.POINTER(ctypes.c_float)]),
     "mg_graph_run": (ctypes.c_int, [_P, _P]),
     "mg_graph_fingerprint_batched": (ctypes.c_int, [_P, _I, ctypes.POINTER(_P), _P, _P,
                                                     ctypes.POINTER(ctypes.c_size_t), _P]),
+    "mg_graph_run_batched": (ctypes.c_int, [_P, _I, ctypes.POINTER(_P), _P, _P, ctypes.POINTER(ctypes.c_size_t), _P]),
+    "mg_compare_fingerprint_rows": (ctypes.c_int, [_P, _P, _P, ctypes.c_int64, ctypes.c_int64, _P, _P, _P]),
     "mg_tensor_has_same_fingerprint": (ctypes.c_int, [_P, _T, _T, ctypes.POINTER(_I)]),
     "mg_tensor_fill_fingerprint_reference": (ctypes.c_int, [_P, _T]),
     "mg_tensor_fill_fingerprint_seeded": (ctypes.c_int, [_P, _T, ctypes.c_uint64, ctypes.c_uint32]),

@@ -2,6 +2,7 @@
 // validates its arguments, converts between the POD structs and the C++ objects, and forwards.
 #include "mirage/kernel/device_memory_manager.h"
 #include "mirage/kernel/graph.h"
+#include "kernel_select.h"
 #include "mirage/utils/json_utils.h"
 #include "mugraph.h"
 #include "status.h"
@@ -379,6 +380,11 @@ int mg_graph_fingerprint_compute(mg_graph *g) {
   return st != MG_OK ? st : synchronize_and_check();
 }
 
+int mg_graph_fingerprint_enqueue(mg_graph *g, void *stream) {
+  if (!g) return fail(MG_ERR_INVALID_ARGUMENT, "graph is null");
+  return launch_all(g, true, true, stream);
+}
+
 int mg_op_run(mg_graph *g, int32_t idx, void *stream) {
   KNOperator *op = get_op(g, idx);
   if (!op) return fail(MG_ERR_INVALID_ARGUMENT, "operator index out of range");
@@ -419,12 +425,13 @@ int mg_op_profile(mg_graph *g, int32_t idx, int32_t warmup, int32_t iters, float
   return synchronize_and_check();
 }
 
-int mg_graph_fingerprint_batched(mg_graph *g, int32_t num_sets, const uint16_t *const *in_fp, uint16_t *out_fp,
-                                 void *workspace, size_t *workspace_bytes, void *stream) {
+// Shared body of the two batched entry points.  Workspace layout: every customized-op output except the final one
+// gets num_sets * elements 16-bit values (256-byte aligned); then, in float mode, heads * num_sets ticket counters
+// for each split-KV operator that is issued together with its merge operator.
+static int run_batched(mg_graph *g, bool fp, int32_t num_sets, const void *const *in_ptrs, void *out_ptr, void *workspace,
+                       size_t *workspace_bytes, void *stream) {
   if (!g || num_sets <= 0 || !workspace_bytes) return fail(MG_ERR_INVALID_ARGUMENT, "bad batched request");
   auto &ops = g->graph.operators;
-  // layout of the intermediates: every customized-op output except the final one gets
-  // num_sets * elements uint16 in the workspace, 256-byte aligned
   std::vector<KNOperator *> inputs, work;
   for (KNOperator *op : ops) {
     if (op->op_type == type::KN_INPUT_OP) inputs.push_back(op);
@@ -443,29 +450,47 @@ int mg_graph_fingerprint_batched(mg_graph *g, int32_t num_sets, const uint16_t *
       slots.push_back({work[w], (int)t, need, e});
       need += ((size_t)e * 2 * (size_t)num_sets + 255) / 256 * 256;
     }
+  // Float mode issues a split-KV operator and the merge that consumes it as one launch (fingerprint sweeps are
+  // faster with the merge as a launch of its own over all sets).
+  std::vector<size_t> ticket_offset(work.size(), (size_t)-1);
+  size_t const tickets_begin = need;
+  if (!fp)
+    for (size_t w = 0; w + 1 < work.size(); w++) {
+      auto *c = static_cast<kernel::KNCustomizedOp *>(work[w]);
+      if (c->selected_kernel(false) == mg::KERNEL_ATTN_SPLIT && c->can_fuse_with(work[w + 1], false)) {
+        ticket_offset[w] = need;
+        need += ((size_t)c->plan.grid_dim.x * (size_t)num_sets * sizeof(int) + 255) / 256 * 256;
+        w++;
+      }
+    }
   if (!workspace) {
     *workspace_bytes = need;
     return MG_OK;
   }
+  if (int dry_st = refuse_dry(g->rt)) return dry_st;
   if (*workspace_bytes < need) return fail(MG_ERR_INVALID_ARGUMENT, "workspace too small");
-  if (!in_fp || !out_fp) return fail(MG_ERR_INVALID_ARGUMENT, "null tensor pointers");
+  if (!in_ptrs || !out_ptr) return fail(MG_ERR_INVALID_ARGUMENT, "null tensor pointers");
+  if (need > tickets_begin) {
+    MG_CUDA_TRY(cudaMemsetAsync((char *)workspace + tickets_begin, 0, need - tickets_begin, (cudaStream_t)stream));
+    mg::stream_wrote_anything(stream);
+  }
   auto locate = [&](DTensor const &t, void const **ptr, long long *stride) -> bool {
     for (size_t i = 0; i < inputs.size(); i++)
       if (inputs[i] == t.owner_op) {
-        *ptr = in_fp[i];
+        *ptr = in_ptrs[i];
         *stride = (long long)t.num_elements();
         return true;
       }
     for (Slot const &s : slots)
       if (s.op == t.owner_op && s.ts == t.owner_ts_idx) {
-        *ptr = s.offset == (size_t)-1 ? (void const *)out_fp : (void const *)((char *)workspace + s.offset);
+        *ptr = s.offset == (size_t)-1 ? (void const *)out_ptr : (void const *)((char *)workspace + s.offset);
         *stride = s.elems;
         return true;
       }
     return false;
   };
-  for (KNOperator *op : work) {
-    auto *c = static_cast<kernel::KNCustomizedOp *>(op);
+  for (size_t w = 0; w < work.size(); w++) {
+    auto *c = static_cast<kernel::KNCustomizedOp *>(work[w]);
     void const *in[MGD_MAX_IO];
     void *out[MGD_MAX_IO];
     long long is[MGD_MAX_IO], os[MGD_MAX_IO];
@@ -477,10 +502,39 @@ int mg_graph_fingerprint_batched(mg_graph *g, int32_t num_sets, const uint16_t *
       if (!locate(c->output_tensors[i], &p, &os[i])) return fail(MG_ERR_INVALID_GRAPH, "internal: output slot missing");
       out[i] = const_cast<void *>(p);
     }
-    int st = c->launch_fingerprint_sets(num_sets, in, is, out, os, stream);
+    int st;
+    if (ticket_offset[w] != (size_t)-1) {
+      auto *m = static_cast<kernel::KNCustomizedOp *>(work[w + 1]);
+      void const *mp;
+      long long ms;
+      if (!locate(m->output_tensors[0], &mp, &ms)) return fail(MG_ERR_INVALID_GRAPH, "internal: output slot missing");
+      st = c->launch_fused_sets(m, false, num_sets, in, is, out, os, const_cast<void *>(mp), ms,
+                                reinterpret_cast<int *>((char *)workspace + ticket_offset[w]), stream);
+      w++;
+    } else {
+      st = fp ? c->launch_fingerprint_sets(num_sets, in, is, out, os, stream) : c->launch_float_sets(num_sets, in, is, out, os, stream);
+    }
     if (st != MG_OK) return st;
   }
   return MG_OK;
+}
+
+int mg_graph_fingerprint_batched(mg_graph *g, int32_t num_sets, const uint16_t *const *in_fp, uint16_t *out_fp,
+                                 void *workspace, size_t *workspace_bytes, void *stream) {
+  return run_batched(g, true, num_sets, reinterpret_cast<const void *const *>(in_fp), out_fp, workspace, workspace_bytes, stream);
+}
+
+int mg_graph_run_batched(mg_graph *g, int32_t num_sets, const void *const *in_data, void *out_data, void *workspace,
+                         size_t *workspace_bytes, void *stream) {
+  return run_batched(g, false, num_sets, in_data, out_data, workspace, workspace_bytes, stream);
+}
+
+int mg_compare_fingerprint_rows(mg_runtime *rt, const uint16_t *a, const uint16_t *b, int64_t rows, int64_t row_elements,
+                                int32_t *equal_flags, int32_t *mismatch_count, void *stream) {
+  if (int dry_st = refuse_dry(rt)) return dry_st;
+  if (!rt || !rt->dmm) return fail(MG_ERR_INVALID_ARGUMENT, "no runtime");
+  int st = mgd_compare_rows_u16(a, b, rows, row_elements, equal_flags, mismatch_count, stream);
+  return st == MG_OK ? MG_OK : fail(st, mgd_last_error());
 }
 
 int mg_tensor_has_same_fingerprint(mg_runtime *rt, const mg_tensor *a, const mg_tensor *b, int32_t *same) {

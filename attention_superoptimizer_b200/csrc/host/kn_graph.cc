@@ -719,34 +719,61 @@ static int finish(int st) {
 
 int KNCustomizedOp::launch_fingerprint_sets(int num_sets, void const *const *in, long long const *in_stride,
                                             void *const *out, long long const *out_stride, void *stream) {
+  return launch_sets(true, num_sets, in, in_stride, out, out_stride, stream);
+}
+int KNCustomizedOp::launch_float_sets(int num_sets, void const *const *in, long long const *in_stride,
+                                      void *const *out, long long const *out_stride, void *stream) {
+  return launch_sets(false, num_sets, in, in_stride, out, out_stride, stream);
+}
+
+// One launch of this operator over `num_sets` independent tensor sets, on whichever kernel was selected.
+int KNCustomizedOp::launch_sets(bool fp, int num_sets, void const *const *in, long long const *in_stride,
+                                void *const *out, long long const *out_stride, void *stream) {
   if (int dry_st = refuse_if_dry()) return dry_st;
   if (!ensure_lowered()) return MG_ERR_INVALID_GRAPH;
-  if (kernel_fp_ == mg::KERNEL_ATTN_SPLIT) {
+  if (num_sets <= 0) return MG_ERR_INVALID_ARGUMENT;
+  int const kernel = fp ? kernel_fp_ : kernel_float_;
+  int const dt = input_tensors.empty() ? (int)DT_FLOAT16 : (int)input_tensors[0].data_type;
+  if (kernel == mg::KERNEL_ATTN_SPLIT) {
     void *o[2] = {out[o_output_], out[1 - o_output_]};
     long long os[2] = {out_stride[o_output_], out_stride[1 - o_output_]};
-    return launch_split(true, num_sets, in, in_stride, o, os, nullptr, stream);
+    return launch_split(fp, num_sets, in, in_stride, o, os, nullptr, stream);
   }
-  record_anything(stream);
-  if (kernel_fp_ == mg::KERNEL_ATTN_MERGE) {
+  if (kernel == mg::KERNEL_ATTN_ROWS) {
+    if (num_sets != 1) {
+      mg::set_error("the dense attention kernel takes one tensor set per launch");
+      return MG_ERR_UNSUPPORTED;
+    }
+    mgd_attn_rows rp;
+    mg::match_attn_rows(program_, &rp, nullptr);
+    rp.data_type = dt;
+    record_anything(stream);
+    return finish(mgd_launch_attn_rows_float(&rp, in[0], in[1], in[2], out[o_output_], out[1 - o_output_], stream));
+  }
+  if (kernel == mg::KERNEL_ATTN_MERGE) {
     mgd_attn_merge mp;
     mg::match_attn_merge(program_, &mp, nullptr);
-    void const *ordered[2] = {in[o_input_], in[1 - o_input_]};
-    long long const ordered_stride[2] = {in_stride[o_input_], in_stride[1 - o_input_]};
-    in = ordered;
-    in_stride = ordered_stride;
     // the merge kernel writes its one output and nothing else
     record_outputs(stream, {range_of(out[0], ((size_t)(num_sets - 1) * (size_t)out_stride[0] + output_tensors[0].num_elements()) * 2)});
     mp.num_sets = num_sets;
-    mp.o_part_set_stride = in_stride[0]; mp.r_part_set_stride = in_stride[1]; mp.out_set_stride = out_stride[0];
-    return finish(mgd_launch_attn_merge_fingerprint(&mp, (uint16_t const *)in[0], (uint16_t const *)in[1],
-                                                    (uint16_t *)out[0], stream));
+    mp.data_type = dt;
+    mp.o_part_set_stride = in_stride[o_input_]; mp.r_part_set_stride = in_stride[1 - o_input_]; mp.out_set_stride = out_stride[0];
+    if (fp)
+      return finish(mgd_launch_attn_merge_fingerprint(&mp, (uint16_t const *)in[o_input_], (uint16_t const *)in[1 - o_input_],
+                                                      (uint16_t *)out[0], stream));
+    return finish(mgd_launch_attn_merge_float(&mp, in[o_input_], in[1 - o_input_], out[0], stream));
   }
+  if (!fp && causal_window != 0) {
+    mg::set_error("the causal window is implemented by the split-KV attention kernel only");
+    return MG_ERR_UNSUPPORTED;
+  }
+  record_anything(stream);
   mgd_bindings b;
   std::memset(&b, 0, sizeof(b));
   for (int i = 0; i < program_.num_inputs; i++) { b.in[i] = in[i]; b.in_set_stride[i] = in_stride[i]; }
   for (int i = 0; i < program_.num_outputs; i++) { b.out[i] = out[i]; b.out_set_stride[i] = out_stride[i]; }
   b.num_sets = num_sets;
-  return finish(mgd_launch_fingerprint_interp(&program_, &b, stream));
+  return finish(fp ? mgd_launch_fingerprint_interp(&program_, &b, stream) : mgd_launch_float_interp(&program_, &b, dt, stream));
 }
 
 int KNCustomizedOp::launch_fingerprint(void *stream) {
@@ -756,51 +783,23 @@ int KNCustomizedOp::launch_fingerprint(void *stream) {
   if (input_tensors.size() > MGD_MAX_IO || output_tensors.size() > MGD_MAX_IO) return MG_ERR_UNSUPPORTED;
   for (size_t i = 0; i < input_tensors.size(); i++) in[i] = input_tensors[i].fp_ptr;
   for (size_t i = 0; i < output_tensors.size(); i++) out[i] = output_tensors[i].fp_ptr;
-  return launch_fingerprint_sets(1, in, zs, out, zs, stream);
+  return launch_sets(true, 1, in, zs, out, zs, stream);
 }
 
 int KNCustomizedOp::launch_float(void *stream) {
-  if (int dry_st = refuse_if_dry()) return dry_st;
-  if (!ensure_lowered()) return MG_ERR_INVALID_GRAPH;
-  int dt = input_tensors.empty() ? (int)DT_FLOAT16 : (int)input_tensors[0].data_type;
-  if (kernel_float_ == mg::KERNEL_ATTN_SPLIT) {
-    void const *in[3] = {input_tensors[0].data_ptr, input_tensors[1].data_ptr, input_tensors[2].data_ptr};
-    void *out[2] = {output_tensors[o_output_].data_ptr, output_tensors[1 - o_output_].data_ptr};
-    long long zs[3] = {0, 0, 0};
-    return launch_split(false, 1, in, zs, out, zs, nullptr, stream);
-  }
-  record_anything(stream);
-  if (kernel_float_ == mg::KERNEL_ATTN_ROWS) {
-    mgd_attn_rows rp;
-    mg::match_attn_rows(program_, &rp, nullptr);
-    rp.data_type = dt;
-    return finish(mgd_launch_attn_rows_float(&rp, input_tensors[0].data_ptr, input_tensors[1].data_ptr,
-                                             input_tensors[2].data_ptr, output_tensors[o_output_].data_ptr,
-                                             output_tensors[1 - o_output_].data_ptr, stream));
-  }
-  if (kernel_float_ == mg::KERNEL_ATTN_MERGE) {
-    mgd_attn_merge mp;
-    mg::match_attn_merge(program_, &mp, nullptr);
-    mp.data_type = dt;
-    record_outputs(stream, {range_of(output_tensors[0].data_ptr, output_tensors[0].num_elements() * 2)});
-    return finish(mgd_launch_attn_merge_float(&mp, input_tensors[o_input_].data_ptr, input_tensors[1 - o_input_].data_ptr,
-                                              output_tensors[0].data_ptr, stream));
-  }
-  if (causal_window != 0) {
-    mg::set_error("the causal window is implemented by the split-KV attention kernel only");
-    return MG_ERR_UNSUPPORTED;
-  }
-  mgd_bindings b;
-  std::memset(&b, 0, sizeof(b));
-  for (size_t i = 0; i < input_tensors.size(); i++) b.in[i] = input_tensors[i].data_ptr;
-  for (size_t i = 0; i < output_tensors.size(); i++) b.out[i] = output_tensors[i].data_ptr;
-  b.num_sets = 1;
-  return finish(mgd_launch_float_interp(&program_, &b, dt, stream));
+  void const *in[MGD_MAX_IO];
+  void *out[MGD_MAX_IO];
+  long long zs[MGD_MAX_IO] = {0};
+  if (input_tensors.size() > MGD_MAX_IO || output_tensors.size() > MGD_MAX_IO) return MG_ERR_UNSUPPORTED;
+  for (size_t i = 0; i < input_tensors.size(); i++) in[i] = input_tensors[i].data_ptr;
+  for (size_t i = 0; i < output_tensors.size(); i++) out[i] = output_tensors[i].data_ptr;
+  return launch_sets(false, 1, in, zs, out, zs, stream);
 }
 
-// One launch of the split-KV attention kernel; with `merge` the cross-split merge operator rides along.
+// One launch of the split-KV attention kernel (out[0] = O', out[1] = R'); with `merge` the cross-split merge
+// operator rides along.
 int KNCustomizedOp::launch_split(bool fp, int num_sets, void const *const *in, long long const *in_stride,
-                                 void *const *out, long long const *out_stride, KNCustomizedOp *merge, void *stream) {
+                                 void *const *out, long long const *out_stride, FusedMerge const *merge, void *stream) {
   mgd_attn_split sp;
   mg::match_attn_split(program_, &sp, nullptr);
   sp.num_sets = num_sets;
@@ -819,11 +818,10 @@ int KNCustomizedOp::launch_split(bool fp, int num_sets, void const *const *in, l
     outs.push_back(range_of(out[i], ((size_t)(num_sets - 1) * (size_t)out_stride[i] + t.num_elements()) * elem));
   }
   if (merge != nullptr) {
-    DTensor const &o = merge->output_tensors[0];
-    opts.merged_out = fp ? (void *)o.fp_ptr : o.data_ptr;
-    opts.tickets = tickets_;
-    opts.merged_set_stride = 0;
-    outs.push_back(range_of(opts.merged_out, o.num_elements() * elem));
+    opts.merged_out = merge->out;
+    opts.tickets = merge->tickets;
+    opts.merged_set_stride = merge->set_stride;
+    outs.push_back(range_of(merge->out, merge->bytes));
   }
   opts.overlap = 1 | (inputs_untouched(stream, ins) ? 2 : 0) | (DeviceMemoryManager::get_instance()->launch_policy == 1 ? 4 : 0);
   int st = fp ? mgd_launch_attn_split_fingerprint_ex(&sp, (uint16_t const *)in[0], (uint16_t const *)in[1],
@@ -861,26 +859,35 @@ bool KNCustomizedOp::can_fuse_with(KNOperator *next, bool fp) {
 }
 
 int KNCustomizedOp::launch_fused(KNCustomizedOp *merge, bool fp, void *stream) {
-  if (int dry_st = refuse_if_dry()) return dry_st;
-  if (!fp && kernel_float_ == mg::KERNEL_ATTN_ROWS) {
-    mgd_attn_rows rp;
-    mg::match_attn_rows(program_, &rp, nullptr);
-    rp.data_type = (int)input_tensors[0].data_type;
-    record_anything(stream);
-    return finish(mgd_launch_attn_rows_float_ex(&rp, input_tensors[0].data_ptr, input_tensors[1].data_ptr,
-                                                input_tensors[2].data_ptr, output_tensors[o_output_].data_ptr,
-                                                output_tensors[1 - o_output_].data_ptr,
-                                                merge->output_tensors[0].data_ptr, stream));
-  }
   void const *in[3];
   void *out[2];
   long long zs[3] = {0, 0, 0};
   for (int i = 0; i < 3; i++) in[i] = fp ? (void const *)input_tensors[i].fp_ptr : input_tensors[i].data_ptr;
-  for (int i = 0; i < 2; i++) {
-    DTensor const &t = output_tensors[i == 0 ? o_output_ : 1 - o_output_];
-    out[i] = fp ? (void *)t.fp_ptr : t.data_ptr;
+  for (int i = 0; i < 2; i++) out[i] = fp ? (void *)output_tensors[i].fp_ptr : output_tensors[i].data_ptr;
+  DTensor const &o = merge->output_tensors[0];
+  return launch_fused_sets(merge, fp, 1, in, zs, out, zs, fp ? (void *)o.fp_ptr : o.data_ptr, 0, tickets_, stream);
+}
+
+int KNCustomizedOp::launch_fused_sets(KNCustomizedOp *merge, bool fp, int num_sets, void const *const *in,
+                                      long long const *in_stride, void *const *out, long long const *out_stride,
+                                      void *merged_out, long long merged_stride, int *tickets, void *stream) {
+  if (int dry_st = refuse_if_dry()) return dry_st;
+  if (!fp && kernel_float_ == mg::KERNEL_ATTN_ROWS) {
+    if (num_sets != 1) {
+      mg::set_error("the dense attention kernel takes one tensor set per launch");
+      return MG_ERR_UNSUPPORTED;
+    }
+    mgd_attn_rows rp;
+    mg::match_attn_rows(program_, &rp, nullptr);
+    rp.data_type = (int)input_tensors[0].data_type;
+    record_anything(stream);
+    return finish(mgd_launch_attn_rows_float_ex(&rp, in[0], in[1], in[2], out[o_output_], out[1 - o_output_], merged_out, stream));
   }
-  return launch_split(fp, 1, in, zs, out, zs, merge, stream);
+  void *o[2] = {out[o_output_], out[1 - o_output_]};
+  long long os[2] = {out_stride[o_output_], out_stride[1 - o_output_]};
+  FusedMerge fm{merged_out, merged_stride,
+                ((size_t)(num_sets - 1) * (size_t)merged_stride + merge->output_tensors[0].num_elements()) * 2, tickets};
+  return launch_split(fp, num_sets, in, in_stride, o, os, &fm, stream);
 }
 
 bool KNCustomizedOp::fingerprint(void) { return sync_ok(launch_fingerprint(nullptr)); }

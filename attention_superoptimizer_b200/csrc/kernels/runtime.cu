@@ -74,6 +74,29 @@ __global__ void bounded_wait_selftest_kernel(int limit, int32_t *status) {
   }
 }
 
+// One block per row (grid-stride over rows): 128-bit loads when the rows allow it, one flag per row.
+__global__ void compare_rows_u16_kernel(uint16_t const *a, uint16_t const *b, int64_t rows, int64_t row_elems, int vec_ok,
+                                        int32_t *flags, int32_t *mismatches) {
+  for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
+    uint16_t const *pa = a + r * row_elems, *pb = b + r * row_elems;
+    bool diff = false;
+    if (vec_ok) {
+      uint4 const *va = reinterpret_cast<uint4 const *>(pa), *vb = reinterpret_cast<uint4 const *>(pb);
+      for (int64_t i = threadIdx.x; i < row_elems / 8; i += blockDim.x) {
+        uint4 x = __ldg(va + i), y = __ldg(vb + i);
+        diff |= (x.x != y.x) | (x.y != y.y) | (x.z != y.z) | (x.w != y.w);
+      }
+    } else {
+      for (int64_t i = threadIdx.x; i < row_elems; i += blockDim.x) diff |= pa[i] != pb[i];
+    }
+    int any = __syncthreads_or(diff);
+    if (threadIdx.x == 0) {
+      flags[r] = any ? 0 : 1;
+      if (any && mismatches) atomicAdd(mismatches, 1);
+    }
+  }
+}
+
 static int grid_for(int64_t n, int threads) {
   int64_t blocks = (n + threads - 1) / threads;
   int64_t cap = 148 * 16;
@@ -117,6 +140,18 @@ int mgd_compare_u16(const uint16_t *a, const uint16_t *b, int64_t n, int32_t *fl
   compare_init_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(flag);
   if (n > 0) compare_u16_kernel<<<grid_for(n, 256), 256, 0, (cudaStream_t)stream>>>(a, b, n, flag);
   return check_launch("compare_u16_kernel");
+}
+
+int mgd_compare_rows_u16(const uint16_t *a, const uint16_t *b, int64_t rows, int64_t row_elems, int32_t *flags,
+                         int32_t *mismatches, void *stream) {
+  if (!a || !b || !flags || rows < 0 || row_elems <= 0) return set_error(MG_ERR_INVALID_ARGUMENT, "compare rows: bad argument");
+  if (mismatches && cudaMemsetAsync(mismatches, 0, sizeof(int32_t), (cudaStream_t)stream) != cudaSuccess)
+    return check_launch("cudaMemsetAsync(mismatch count)");
+  if (rows == 0) return MG_OK;
+  int const vec_ok = row_elems % 8 == 0 && (reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b)) % 16 == 0;
+  int64_t const blocks = rows < 148 * 16 ? rows : 148 * 16;
+  compare_rows_u16_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(a, b, rows, row_elems, vec_ok, flags, mismatches);
+  return check_launch("compare_rows_u16_kernel");
 }
 
 int mgd_tables_init(const uint16_t *e, const uint16_t *p, const uint16_t *q) {

@@ -3,23 +3,28 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
 
-Headline workload (BASELINE config "GQA incremental decode", fp16): batch 1, 32 query heads, 8 KV
-heads (group 4), head_dim 128, KV length 4096; the muGraph is two customized operators (split-KV
-partials over 16 blocks with a for-loop over KV tiles of 64, then the cross-block reduction and
-division).  One STEP = `calls_per_step` evaluations of that muGraph, each on a different resident
-K/V/Q buffer set so that no call finds its inputs in L2 (the sets together exceed 2x the L2 size);
-the step is replayed from a CUDA graph.  `value` = microseconds per call (whole muGraph, both
-operators).  With N GPUs the 8 KV heads are sharded N ways (strong scaling, no collective on the
-data path).
+Headline workload (GQA incremental decode, fp16): batch 1, 32 query heads, 8 KV heads (group 4), head_dim 128,
+KV length 4096; the muGraph is two customized operators (split-KV partials over 16 blocks with a for-loop over KV
+tiles of 64, then the cross-block reduction and division).  A CALL is one evaluation of that muGraph on one
+Q/K/V set.  One STEP = `calls_per_step` independent calls, each on its own resident Q/K/V set, issued as batched
+launches (`--batch` calls per kernel: split-KV and merge of all the batch's calls in ONE launch) that run back to
+back on one stream; the sets a step reads exceed 2.5x the L2 size, so no call finds its inputs there.  `value` =
+microseconds per call.  With N GPUs the 8 KV heads are sharded N ways (strong scaling, no collective on the data
+path).
 
-Also measured in the same run and reported as extra keys:
-  roofline            the split-KV kernel alone: algorithmic bytes (Q+K+V read once) / event time
-  fingerprint         the verification sweep: the same muGraph evaluated in fingerprint mode on
-                      independent seeded input sets, sharded over ranks, result fingerprints
-                      all-gathered over NCCL; evals/s over all ranks
-  e2e                 the same call through the public API with host buffers: pinned H2D of Q,K,V,
-                      both operators, D2H of the output, per call
-  cpu_baseline        the fp32 host evaluator of the same muGraph (oracle/f32_oracle.c) on this box
+Reported beside it:
+  roofline            the batched kernel: algorithmic bytes per launch (Q + K + V read once, O written) / mean launch
+                      duration inside the timed region / measured HBM peak
+  per_call_launch     one kernel launch per call: `calls` launches spread over several streams (throughput sizing),
+                      strictly one after the other on one stream (latency sizing), one un-captured call, and the
+                      reference's own profile protocol (same buffers, K/V stay in L2)
+  fingerprint         the verification sweep: the same muGraph in fingerprint mode on 4096 seeded input sets,
+                      sharded over ranks, fingerprints all-gathered (NCCL) and compared row by row on the device
+                      with reference fingerprints; every row is also checked against digests of the reference's
+                      own host code
+  e2e                 one call through the public API with host buffers: pinned H2D of Q,K,V, the muGraph, D2H of O
+  cpu_baseline        CPU evaluation of the same work on this box (float: fp32 port; fingerprints: the reference's
+                      own fingerprinter classes), one core and all cores
 All inputs are synthetic (seeded), shaped and distributed as the configuration names them.
 """
 import argparse
@@ -29,17 +34,18 @@ import statistics
 import subprocess
 import sys
 import tempfile
-import threading
 import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
-# ---- workload constants (BASELINE configs 2 and 5) ----------------------------------------------
+# ---- workload constants (decode muGraph and verification sweep) ------------------------------------------
 KV_HEADS, GROUP, HEAD_DIM, KV_LEN, SPLITS, FORLOOP = 8, 4, 128, 4096, 16, 4
 L2_BYTES = 126 * 1024 * 1024
 SWEEP_SETS = 4096
+SWEEP_DIGESTS = os.path.join(ROOT, "tests", "golden", "sweep_digests_gqa_decode.json")
+TRAFFIC_FILE = os.path.join(ROOT, "profiles", "attn_split_fp16_gqa_decode_batched.json")
 
 
 def per_call_bytes(heads):
@@ -53,7 +59,14 @@ def load_peaks():
     if os.path.exists(path):
         with open(path) as f:
             return json.load(f), "measured (MEASURED_PEAKS.json)"
-    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}, "fallback (6.65 TB/s)"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}, "fallback (6.65 TB/s, 1.59 PFLOP/s)"
+
+
+def host_cores():
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
 
 
 class ClockSampler:
@@ -70,8 +83,9 @@ class ClockSampler:
         try:
             self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.FIELDS,
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "50"],
                                          stdout=self.file, stderr=subprocess.DEVNULL)
+            time.sleep(0.15)  # let the first sample land before the region starts
         except Exception:
             self.proc = None
 
@@ -135,79 +149,13 @@ def run_ours(args):
 
     qb, kb, vb, ob = per_call_bytes(heads)
     set_bytes = qb + kb + vb
-    nsets = max(16, -(-(5 * L2_BYTES // 2) // set_bytes))          # > 2.5x L2 of distinct inputs
-    calls = args.calls_per_step if args.calls_per_step > 0 else max(nsets, 64)
+    nsets = max(16, -(-(5 * L2_BYTES // 2) // set_bytes))          # per-call-launch protocols: > 2.5x L2 of inputs
     arena = nsets * (2 * set_bytes + (1 << 20)) + (1 << 28) + (3 << 29)   # + room for the other configs' graphs
     rt = mg.Runtime.get(device=local_rank, arena_bytes=arena)
     rt.set_specialisation(0 if args.interpreter_only else args.specialisation)
     stream = torch.cuda.Stream()
     sh = stream.cuda_stream
-
-    # ---- decode graphs: one per resident buffer set ---------------------------------------------
-    plan1, plan2 = mg.gqa_decode_plans(heads, GROUP, HEAD_DIM, KV_LEN, SPLITS, FORLOOP)
-    k_layout = mg.DmemColumnMajor if args.k_layout == "col" else mg.DmemRowMajor
-    v_layout = mg.DmemColumnMajor if args.v_layout == "col" else mg.DmemRowMajor
-    graphs = []
-    for s in range(nsets):
-        g = mg.PyGraph(rt)
-        Q = g.new_input((heads, GROUP, HEAD_DIM), mg.float16)
-        K = g.new_input((heads, HEAD_DIM, KV_LEN), mg.float16, k_layout)
-        V = g.new_input((heads, KV_LEN, HEAD_DIM), mg.float16, v_layout)
-        parts = g.customized([Q, K, V], plan1)
-        out = g.customized(parts, plan2)
-        seed = 2024 + 1000 * rank + s
-        Q.fill_data_seeded(3 * seed, HEAD_DIM ** -0.5)   # 1/sqrt(d) folded into Q
-        K.fill_data_seeded(3 * seed + 1, 1.0)
-        V.fill_data_seeded(3 * seed + 2, 1.0)
-        graphs.append((g, (Q, K, V), out[0]))
-    info = graphs[0][0].customized_info(3)
-    info2 = graphs[0][0].customized_info(4)
-
-    # one un-captured pass (sets function attributes), then capture
-    for g, _, _ in graphs:
-        g.run(stream=sh, sync=False)
-    torch.cuda.synchronize()
-
-    # Independent calls (different buffer sets) may be put on several streams inside the captured step so that
-    # more than one call is in flight; --streams 1 keeps strict stream order (each call after the previous one).
-    lanes = [stream] + [torch.cuda.Stream() for _ in range(max(0, args.streams - 1))]
-
-    def fan_out():
-        if len(lanes) > 1:
-            ev = torch.cuda.Event()
-            ev.record(stream)
-            for s in lanes[1:]:
-                s.wait_event(ev)
-
-    def fan_in():
-        for s in lanes[1:]:
-            ev = torch.cuda.Event()
-            ev.record(s)
-            stream.wait_event(ev)
-
-    def record_calls():
-        fan_out()
-        for c in range(calls):
-            graphs[c % nsets][0].run(stream=lanes[c % len(lanes)].cuda_stream, sync=False)
-        fan_in()
-
-    def record_op1():
-        fan_out()
-        for c in range(calls):
-            graphs[c % nsets][0].run_op(3, stream=lanes[c % len(lanes)].cuda_stream)
-        fan_in()
-
-    # The headline protocol keeps `--streams` independent calls in flight and sizes launches for throughput;
-    # the stream-ordered protocol (one stream, each call after the previous one, launches sized for latency) is
-    # captured first and reported beside it.
-    all_lanes, lanes = lanes, [stream]
-    rt.set_launch_policy(mg.POLICY_LATENCY)
-    ordered_graph = mg.CapturedSequence(sh, record_calls)
-    lanes = all_lanes
-    rt.set_launch_policy(mg.POLICY_THROUGHPUT if args.streams > 1 else mg.POLICY_LATENCY)
-    step_graph = mg.CapturedSequence(sh, record_calls)
-    op1_graph = mg.CapturedSequence(sh, record_op1)
-    rt.set_launch_policy(mg.POLICY_LATENCY)
+    peaks, peak_src = load_peaks()
 
     def barrier():
         if world > 1:
@@ -231,29 +179,134 @@ def run_ours(args):
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return float(ms.item())
 
+    plan1, plan2 = mg.gqa_decode_plans(heads, GROUP, HEAD_DIM, KV_LEN, SPLITS, FORLOOP)
+    k_layout = mg.DmemColumnMajor if args.k_layout == "col" else mg.DmemRowMajor
+    v_layout = mg.DmemColumnMajor if args.v_layout == "col" else mg.DmemRowMajor
+
+    # ---- headline: batched launches over dense resident sets -------------------------------------------------
+    batch = args.batch
+    nbatches = max(2, -(-(5 * L2_BYTES // 2) // (batch * set_bytes)))     # distinct batches a replay walks through
+    elems = [qb // 2, kb // 2, vb // 2]
+    dense = [torch.empty(nbatches * batch * n, dtype=torch.int16, device="cuda") for n in elems]
+    dense_out = torch.zeros(nbatches * batch * (ob // 2), dtype=torch.int16, device="cuda")
+    for i, (buf, n) in enumerate(zip(dense, elems)):
+        for s in range(nbatches * batch):
+            mg.fill_data_seeded_raw(rt, buf.data_ptr() + 2 * s * n, n, 3 * (2024 + 1000 * rank + s) + i,
+                                    HEAD_DIM ** -0.5 if i == 0 else 1.0)   # 1/sqrt(d) folded into Q
+    bg = mg.PyGraph(rt)
+    bQ = bg.new_input((heads, GROUP, HEAD_DIM), mg.float16)
+    bK = bg.new_input((heads, HEAD_DIM, KV_LEN), mg.float16, k_layout)
+    bV = bg.new_input((heads, KV_LEN, HEAD_DIM), mg.float16, v_layout)
+    b_out = bg.customized(bg.customized([bQ, bK, bV], plan1), plan2)
+    wbytes = bg.run_batched_workspace(batch)
+    bwork = torch.empty(max(wbytes, 256), dtype=torch.uint8, device="cuda")
+
+    def launch_batch(b, on=sh):
+        bg.run_batched(batch, [d.data_ptr() + 2 * b * batch * n for d, n in zip(dense, elems)],
+                       dense_out.data_ptr() + b * batch * ob, bwork.data_ptr(), wbytes, stream=on)
+
+    for b in range(nbatches):
+        launch_batch(b)
+    mg.synchronize()
+    before = mg.launch_count()
+    batched_graph = mg.CapturedSequence(sh, lambda: [launch_batch(b) for b in range(nbatches)])
+    kernels_per_replay = batched_graph.kernels
+    calls_per_replay = nbatches * batch
+    # a step long enough for the clock sampler to see it: about 30 ms of back-to-back launches
+    replays = args.replays_per_step if args.replays_per_step > 0 else max(1, round(30e3 / (calls_per_replay * 2.9 * heads / KV_HEADS + 20)))
+    calls = replays * calls_per_replay
+
+    def step():
+        for _ in range(replays):
+            batched_graph.launch()
+
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    launches_before = mg.launch_count()
-    total_ms = timed(step_graph.launch, args.steps, args.warmup)
-    # nvidia-smi samples every 100 ms and the timed region can be shorter: keep replaying the same step
-    # (untimed) for about a second so that the sampler sees the clocks under this load
-    t_end = time.perf_counter() + 1.0
-    while time.perf_counter() < t_end:
-        for _ in range(20):
-            step_graph.launch()
-        stream.synchronize()
+    total_ms = timed(step, args.steps, args.warmup)
     clocks = sampler.stop() if rank == 0 else {}
+    mg.synchronize()   # reads the device status word: a bounded wait that gave up would raise here
     ms_per_step = total_ms / args.steps
     us_per_call = ms_per_step * 1000.0 / calls
-    gpu_launches = args.steps * step_graph.kernels
+    gpu_launches = args.steps * replays * kernels_per_replay
+    us_per_launch = ms_per_step * 1000.0 / (replays * kernels_per_replay)
+    launch_bytes = batch * (qb + kb + vb + ob)
+    achieved = launch_bytes / (us_per_launch * 1e-6) / 1e9
+    traffic, traffic_src = None, None
+    if os.path.exists(TRAFFIC_FILE):
+        with open(TRAFFIC_FILE) as f:
+            t = json.load(f)
+        # the capture's DRAM bytes per call, scaled to this launch (traffic grows in proportion to the calls)
+        traffic = int(t["dram_bytes_per_call_per_kv_head"] * heads * batch)
+        traffic_src = t["source"]
+    roofline = {"bound": "hbm", "kernel": "attn_split_kernel<fp16,128> over %d calls (split-KV partials + fused merge)" % batch,
+                "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                "frac": round(achieved / peaks["hbm_gbs"], 4), "peak_source": peak_src,
+                "traffic": traffic, "traffic_source": traffic_src,
+                "bytes_per_launch": launch_bytes, "us_per_launch": round(us_per_launch, 3),
+                "launches_timed": int(gpu_launches)}
 
-    # ---- dominant kernel alone: roofline ----------------------------------------------------------
-    ordered_us = timed(ordered_graph.launch, max(3, args.steps // 2), 3) / max(3, args.steps // 2) * 1000.0 / calls
-    op1_ms = timed(op1_graph.launch, max(3, args.steps // 2), 3) / max(3, args.steps // 2)
-    # Single call, not captured: events around one evaluation of the muGraph (a different buffer set each time),
-    # median of 200; and the reference's own protocol (KNCustomizedOp::profile: 1024 untimed + 1024 timed launches
-    # of op1 on the same buffers, so K and V stay in L2).
+    # output check of the timed protocol: a few calls of the last replay against the fp32 evaluation
+    checked_calls, worst = 0, 0.0
+    if rank == 0:
+        from tests.helpers import assert_close, from_bits
+        host_out = dense_out.cpu().numpy().view(np.uint16).reshape(nbatches * batch, heads, GROUP, HEAD_DIM)
+        for s in sorted({0, batch - 1, nbatches * batch - 1}):
+            q, k, v = (from_bits(d[s * n:(s + 1) * n].cpu().numpy().view(np.uint16), mg.float16) for d, n in zip(dense, elems))
+            q = q.reshape(heads, GROUP, HEAD_DIM)
+            k = k.reshape(heads, KV_LEN, HEAD_DIM).transpose(0, 2, 1) if args.k_layout == "col" else k.reshape(heads, HEAD_DIM, KV_LEN)
+            v = v.reshape(heads, KV_LEN, HEAD_DIM) if args.v_layout == "row" else v.reshape(heads, HEAD_DIM, KV_LEN).transpose(0, 2, 1)
+            worst = max(worst, assert_close(from_bits(host_out[s], mg.float16), mo.attention_fp32(q, k, v), mg.float16,
+                                            "timed call %d" % s))
+            checked_calls += 1
+
+    # ---- one kernel launch per call: resident graphs, several protocols ------------------------------------------
+    graphs = []
+    for s in range(nsets):
+        g = mg.PyGraph(rt)
+        Q = g.new_input((heads, GROUP, HEAD_DIM), mg.float16)
+        K = g.new_input((heads, HEAD_DIM, KV_LEN), mg.float16, k_layout)
+        V = g.new_input((heads, KV_LEN, HEAD_DIM), mg.float16, v_layout)
+        parts = g.customized([Q, K, V], plan1)
+        out = g.customized(parts, plan2)
+        seed = 5000 + 1000 * rank + s
+        Q.fill_data_seeded(3 * seed, HEAD_DIM ** -0.5)
+        K.fill_data_seeded(3 * seed + 1, 1.0)
+        V.fill_data_seeded(3 * seed + 2, 1.0)
+        graphs.append((g, (Q, K, V), out[0]))
+    info = graphs[0][0].customized_info(3)
+    info2 = graphs[0][0].customized_info(4)
+    for g, _, _ in graphs:
+        g.run(stream=sh, sync=False)
+    torch.cuda.synchronize()
+    pc_calls = max(nsets, 64)
+    lanes = [stream] + [torch.cuda.Stream() for _ in range(max(0, args.streams - 1))]
+
+    def record_calls(use):
+        """pc_calls launches; a graph always goes to the same lane, so two launches of one graph (they share the
+        graph's ticket counters and output buffers) are ordered by their stream."""
+        if len(use) > 1:
+            ev = torch.cuda.Event()
+            ev.record(stream)
+            for s in use[1:]:
+                s.wait_event(ev)
+        for c in range(pc_calls):
+            gi = c % nsets
+            graphs[gi][0].run(stream=use[gi % len(use)].cuda_stream, sync=False)
+        for s in use[1:]:
+            ev = torch.cuda.Event()
+            ev.record(s)
+            stream.wait_event(ev)
+
+    rt.set_launch_policy(mg.POLICY_LATENCY)
+    ordered_graph = mg.CapturedSequence(sh, lambda: record_calls([stream]))
+    rt.set_launch_policy(mg.POLICY_THROUGHPUT if args.streams > 1 else mg.POLICY_LATENCY)
+    streams_graph = mg.CapturedSequence(sh, lambda: record_calls(lanes))
+    rt.set_launch_policy(mg.POLICY_LATENCY)
+    reps = 40
+    ordered_us = timed(lambda: [ordered_graph.launch() for _ in range(reps)], 3, 2) / 3 / reps * 1000.0 / pc_calls
+    streams_us = timed(lambda: [streams_graph.launch() for _ in range(reps)], 3, 2) / 3 / reps * 1000.0 / pc_calls
+    mg.synchronize()
     singles = []
     for c in range(0 if args.no_latency_probes else 210):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -263,52 +316,66 @@ def run_ours(args):
         stream.synchronize()
         if c >= 10:
             singles.append(e0.elapsed_time(e1) * 1000.0)
-    single_us = statistics.median(singles) if singles else float("nan")
-    l2_resident_us = float("nan") if args.no_latency_probes else graphs[0][0].profile_op(3) * 1000.0
-    op1_us = op1_ms * 1000.0 / calls
-    peaks, peak_src = load_peaks()
-    op1_bytes = qb + kb + vb
-    achieved = op1_bytes / (op1_us * 1e-6) / 1e9
-    roofline = {"bound": "hbm", "kernel": "split-KV attention operator (op1)", "achieved": round(achieved, 1),
-                "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": round(achieved / peaks["hbm_gbs"], 4),
-                "peak_source": peak_src,
-                "traffic": 16853248 if world == 1 else None,
-                "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of one launch, ncu capture "
-                                  "profiles/attn_split_fp16_gqa_decode.md (same shapes, N = 1)",
-                "bytes_per_launch": op1_bytes,
-                "us_per_launch": round(op1_us, 3)}
+    single_us = statistics.median(singles) if singles else None
+    l2_resident_us = None if args.no_latency_probes else graphs[0][0].profile_op(3) * 1000.0
+    call_bytes = qb + kb + vb + ob
+
+    def frac_of(us):
+        return None if not us else round(call_bytes / (us * 1e-6) / 1e9 / peaks["hbm_gbs"], 4)
+
+    per_call_launch = {
+        "streams_us_per_call": round(streams_us, 3), "streams": args.streams, "streams_frac_of_hbm_peak": frac_of(streams_us),
+        "stream_ordered_us_per_call": round(ordered_us, 3), "stream_ordered_frac_of_hbm_peak": frac_of(ordered_us),
+        "single_call_us_median": None if single_us is None else round(single_us, 3),
+        "single_call_frac_of_hbm_peak": frac_of(single_us),
+        "l2_resident_profile_us": None if l2_resident_us is None else round(l2_resident_us, 3),
+        "calls": pc_calls, "resident_buffer_sets": nsets, "kernel_op1": info["kernel_float"], "kernel_op2": info2["kernel_float"],
+        "note": "one fused kernel per call; streams: calls spread over lanes inside a captured step, blocks sized for "
+                "throughput; stream_ordered: one stream, each call after the previous one (programmatic dependent "
+                "launch), blocks sized for latency; single: events around one un-captured call, median of 200; "
+                "l2_resident: the reference's profile protocol (1024 + 1024 launches of op1 on the same buffers)"}
 
     # ---- end to end through the public API with host buffers -----------------------------------------
-    g0, (Q0, K0, V0), O0 = graphs[0]
-    host_in = [torch.empty(t.num_elements, dtype=torch.float16).pin_memory() for t in (Q0, K0, V0)]
-    host_out = torch.empty(O0.num_elements, dtype=torch.float16).pin_memory()
-    for h, t in zip(host_in, (Q0, K0, V0)):
-        h.copy_(torch.from_numpy(t.download_data().view(np.float16)))
-    lib, rth = rt.lib, rt.handle
-    import ctypes
+    host_in = torch.empty(sum(elems), dtype=torch.int16).pin_memory()
+    host_in.copy_(torch.cat([d[:n] for d, n in zip(dense, elems)]).cpu())
+    host_out_pinned = torch.empty(ob // 2, dtype=torch.int16).pin_memory()
+    dev_in = torch.empty(sum(elems), dtype=torch.int16, device="cuda")
+    dev_out = torch.empty(ob // 2, dtype=torch.int16, device="cuda")
+    w1 = bg.run_batched_workspace(1)
+    work1 = torch.empty(max(w1, 256), dtype=torch.uint8, device="cuda")
+    offs = [0, elems[0], elems[0] + elems[1]]
 
     def e2e_call():
-        for h, t in zip(host_in, (Q0, K0, V0)):
-            mg.check(lib.mg_tensor_upload_data_async(rth, ctypes.byref(t.pod), h.data_ptr(), sh))
-        g0.run(stream=sh, sync=False)
-        mg.check(lib.mg_tensor_download_data_async(rth, ctypes.byref(O0.pod), host_out.data_ptr(), sh))
-        stream.synchronize()   # the caller reads the result
+        with torch.cuda.stream(stream):
+            dev_in.copy_(host_in, non_blocking=True)                      # one pinned H2D copy of Q | K | V
+            mg.stream_inputs_written(sh)                                  # torch's copy is work the library cannot see
+            bg.run_batched(1, [dev_in.data_ptr() + 2 * o for o in offs], dev_out.data_ptr(), work1.data_ptr(), w1, stream=sh)
+            host_out_pinned.copy_(dev_out, non_blocking=True)             # D2H of O
+        stream.synchronize()                                              # the caller reads the result
 
     e2e_calls = max(5, min(50, args.steps))
     e2e_ms = timed(e2e_call, e2e_calls, 3) / e2e_calls
+    # the same set through the batched launch of the timed protocol (another block shape, so equal up to rounding)
+    from tests.helpers import from_bits as _fb
+    e2e_diff = float(np.abs(_fb(host_out_pinned.numpy().view(np.uint16).ravel(), mg.float16) -
+                            _fb(dense_out[:ob // 2].cpu().numpy().view(np.uint16).ravel(), mg.float16)).max())
     e2e = {"value": round(e2e_ms * 1000.0, 2), "unit": "us/call", "h2d_bytes_per_step": qb + kb + vb,
-           "d2h_bytes_per_step": ob, "note": "one call per e2e step: pinned H2D of Q,K,V + both operators + D2H of O"}
+           "d2h_bytes_per_step": ob, "pcie_gbs": round((qb + kb + vb) / (e2e_ms * 1e-3) / 1e9, 1),
+           "max_abs_diff_vs_device_resident_result": round(e2e_diff, 6),
+           "note": "one call per e2e step through mg_graph_run_batched with caller-owned buffers: one pinned H2D copy of "
+                   "Q|K|V, the fused kernel, D2H of O, stream synchronisation"}
 
     # ---- fingerprint verification sweep ----------------------------------------------------------------
-    fingerprint = run_fingerprint_sweep(args, mg, mo, fp_oracle, rt, torch, dist, np, rank, world, stream, timed)
+    fingerprint = run_fingerprint_sweep(args, mg, mo, rt, torch, dist, np, rank, world, stream, timed, barrier)
     others = None
     if world == 1 and not args.no_other_configs:
-        others = measure_other_configs(mg, rt, stream, timed, load_peaks()[0])
+        others = measure_other_configs(mg, rt, stream, timed, peaks)
 
-    # ---- CPU baseline (rank 0, N = 1 only) ----------------------------------------------------------------
+    # ---- CPU baselines (rank 0, N = 1 only) ----------------------------------------------------------------
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        cpu = cpu_float_baseline(mo, fp_oracle, np, budget_s=12.0)
+        cpu = cpu_float_baseline(mo, fp_oracle, np, budget_s=8.0)
+        fingerprint["cpu_baseline"] = cpu_fingerprint_baseline(mo, np, budget_s=8.0)
 
     if rank == 0:
         line = {
@@ -316,38 +383,54 @@ def run_ours(args):
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4),
             "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "fp16",
             "data": "synthetic (seeded N(0,1) K/V, Q pre-scaled by 1/sqrt(d); fingerprints uniform in [0,227))",
-            "config": {"workload": "GQA incremental decode muGraph (BASELINE config 2): batch 1, 32 q heads, 8 kv heads, "
-                                   "head_dim 128, kv_len 4096, 16 KV splits x for-loop 4 (tiles of 64), 2 customized ops",
-                       "kv_heads_per_gpu": heads, "calls_per_step": calls, "resident_buffer_sets": nsets,
-                       "l2_defeat": "each call reads a different buffer set; sets total %.0f MB > 2x L2" % (nsets * set_bytes / 1e6),
-                       "replay": "CUDA graph of calls_per_step muGraph evaluations; the calls of a step are independent "
-                                 "(distinct buffer sets) and spread over %d streams, launches sized for throughput" % args.streams,
-                       "streams": args.streams,
-                       "kernel_op1": info["kernel_float"], "kernel_op2": info2["kernel_float"],
+            "config": {"workload": "GQA incremental decode muGraph: batch 1, 32 q heads, 8 kv heads, head_dim 128, kv_len 4096, "
+                                   "16 KV splits x for-loop 4 (tiles of 64), 2 customized ops",
+                       "kv_heads_per_gpu": heads, "calls_per_step": calls, "calls_per_launch": batch,
+                       "launches_per_step": replays * kernels_per_replay, "resident_sets": nbatches * batch,
+                       "l2_defeat": "every call reads its own resident set; a replay walks %.0f MB of inputs (> 2.5x L2) before "
+                                    "any set is read again" % (nbatches * batch * set_bytes / 1e6),
+                       "replay": "CUDA graph of %d batched launches (split-KV + merge of %d independent calls in one kernel), "
+                                 "replayed %d times per step on one stream" % (nbatches, batch, replays),
                        "k_layout": args.k_layout, "v_layout": args.v_layout,
                        "parallelism": "kv-heads sharded x%d, no collective" % world},
-            "hbm_gbs": round(sum(per_call_bytes(heads)) / (us_per_call * 1e-6) / 1e9, 1),
+            "hbm_gbs": round(call_bytes / (us_per_call * 1e-6) / 1e9, 1),
+            "output_check": {"calls_checked": checked_calls, "worst_rel_err_vs_fp32": round(worst, 6), "tolerance": 2e-3},
+            "per_call_launch": per_call_launch,
             "stream_ordered_us_per_call": round(ordered_us, 3),
-            "single_call_us_median": None if args.no_latency_probes else round(single_us, 3),
-            "l2_resident_profile_us": None if args.no_latency_probes else round(l2_resident_us, 3),
+            "single_call_us_median": None if single_us is None else round(single_us, 3),
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(gpu_launches),
             "clocks": clocks, "fingerprint": fingerprint, "other_configs": others,
         }
         print(json.dumps(line))
-    step_graph.close()
-    op1_graph.close()
+    batched_graph.close()
+    streams_graph.close()
     ordered_graph.close()
     for g, _, _ in reversed(graphs):
         g.close()
+    bg.close()
     if world > 1:
         dist.destroy_process_group()
 
 
-def run_fingerprint_sweep(args, mg, mo, fp_oracle, rt, torch, dist, np, rank, world, stream, timed):
-    """BASELINE config 5: the decode muGraph in fingerprint mode over independent seeded input sets
-    (uniform in [0, 227)), sets sharded over ranks, processed in resident chunks; result fingerprints
-    all-gathered.  A few sets are checked bit-exactly against the CPU oracle."""
-    import ctypes
+def fnv1a64_rows(np, rows):
+    """FNV-1a-64 of every row of a [n, m] uint16 array (the digest of tests/golden/sweep_digests_gqa_decode.json),
+    vectorised over the rows."""
+    h = np.full(rows.shape[0], 1469598103934665603, dtype=np.uint64)
+    prime = np.uint64(1099511628211)
+    cols = np.ascontiguousarray(rows.T).astype(np.uint64)
+    with np.errstate(over="ignore"):
+        for c in range(cols.shape[0]):
+            h = (h ^ cols[c]) * prime
+    return h
+
+
+def run_fingerprint_sweep(args, mg, mo, rt, torch, dist, np, rank, world, stream, timed, barrier):
+    """The verification sweep: the decode muGraph in fingerprint mode over independent seeded input sets (uniform in
+    [0, 227)), sets sharded over ranks.  Timed region: evaluation of this rank's sets in chunks, all-gather of each
+    chunk's fingerprints on a second stream while the next chunk evaluates, row-wise comparison of all gathered
+    fingerprints with reference fingerprints on the device.  The reference fingerprints are those of an untimed
+    first pass, every row of which is checked on the host against the digests produced by the reference's own host
+    code (tests/golden/sweep_digests_gqa_decode.json)."""
     sh = stream.cuda_stream
     total_sets = args.sweep_sets
     my_sets = total_sets // world
@@ -359,89 +442,122 @@ def run_fingerprint_sweep(args, mg, mo, fp_oracle, rt, torch, dist, np, rank, wo
         K = g.new_input((B, D, L), layout=mg.DmemColumnMajor)
         V = g.new_input((B, L, D), layout=mg.DmemColumnMajor)
         p1, p2 = mg.gqa_decode_plans(B, M, D, L, SPLITS, FORLOOP)
-        parts = g.customized([Q, K, V], p1)
-        out = g.customized(parts, p2)
+        out = g.customized(g.customized([Q, K, V], p1), p2)
         elems = [t.num_elements for t in (Q, K, V)]
-        # All input sets of this rank stay resident when they fit (4096 sets = 69 GB on one GPU): the evaluation
-        # launches then go out back to back and the device time has no host gaps in it.  Otherwise one chunk is
-        # resident at a time and refilled (outside the timed regions) between evaluations.
+        row = out[0].num_elements
+        # All input sets of this rank stay resident when they fit (4096 sets = 69 GB on one GPU); otherwise one
+        # chunk is resident at a time and refilled (outside the timed regions) between evaluations.
         free_bytes, _ = torch.cuda.mem_get_info()
         resident = my_sets * 2 * sum(elems) < 0.7 * free_bytes
         held = my_sets if resident else chunk
         bufs = [torch.empty(held * n, dtype=torch.int16, device="cuda") for n in elems]
-        result = torch.zeros(my_sets * out[0].num_elements, dtype=torch.int16, device="cuda")
+        # fingerprints are kept chunk-major: [chunk index][rank][set in chunk][row], so that the all-gather of one
+        # chunk is one contiguous block; set (r, c, s) is global set r * my_sets + c * chunk + s
+        local = torch.zeros((nchunks, chunk, row), dtype=torch.int16, device="cuda")
+        gathered = torch.zeros((nchunks, world, chunk, row), dtype=torch.int16, device="cuda") if world > 1 else local.view(nchunks, 1, chunk, row)
         wbytes = g.fingerprint_batched_workspace(chunk)
         work = torch.empty(max(wbytes, 256), dtype=torch.uint8, device="cuda")
+        flags = torch.zeros(nchunks * world * chunk, dtype=torch.int32, device="cuda")
+        mismatches = torch.zeros(1, dtype=torch.int32, device="cuda")
+        side = torch.cuda.Stream()
 
         def fill_chunk(c):
-            # set s (global index) uses seed 2024 + s; tensor id 0,1,2 = Q,K,V
             slot0 = c * chunk if resident else 0
             for i, (buf, n) in enumerate(zip(bufs, elems)):
                 for s in range(chunk):
                     gs = rank * my_sets + c * chunk + s
-                    pod = mg.mg_tensor()
-                    pod.data_type, pod.num_dims, pod.dim[0] = mg.float16, 1, n
-                    pod.fp_ptr = buf.data_ptr() + 2 * (slot0 + s) * n
-                    mg.check(rt.lib.mg_tensor_fill_fingerprint_seeded(rt.handle, ctypes.byref(pod), 3 * (2024 + gs) + i, mg.FP_P))
+                    mg.fill_fingerprint_seeded_raw(rt, buf.data_ptr() + 2 * (slot0 + s) * n, n, 3 * (2024 + gs) + i, mg.FP_P)
 
         def eval_chunk(c):
             slot0 = c * chunk if resident else 0
             g.fingerprint_batched(chunk, [b.data_ptr() + 2 * slot0 * n for b, n in zip(bufs, elems)],
-                                  result.data_ptr() + 2 * c * chunk * out[0].num_elements, work.data_ptr(), wbytes, stream=sh)
+                                  local[c].data_ptr(), work.data_ptr(), wbytes, stream=sh)
 
-        fill_chunk(0)
-        eval_chunk(0)
-        torch.cuda.synchronize()
+        def gather_chunk(c):
+            """all-gather of chunk c on the side stream, after the evaluation that produced it"""
+            if world == 1:
+                return
+            ev = torch.cuda.Event()
+            ev.record(stream)
+            side.wait_event(ev)
+            with torch.cuda.stream(side):
+                dist.all_gather_into_tensor(gathered[c].view(torch.uint8).view(-1), local[c].view(torch.uint8).view(-1))
+
+        def join_side():
+            if world > 1:
+                ev = torch.cuda.Event()
+                ev.record(side)
+                stream.wait_event(ev)
+
+        # ---- untimed first pass: produces the reference fingerprints, checked on the host against the digests
+        for c in range(nchunks):
+            fill_chunk(c)
+            eval_chunk(c)
+            gather_chunk(c)
+            if not resident:
+                torch.cuda.synchronize()   # the next fill reuses the chunk's input buffers
+        join_side()
+        barrier()
+        reference = gathered.clone()
+        checked, ok = 0, True
+        if rank == 0 and os.path.exists(SWEEP_DIGESTS) and total_sets <= SWEEP_SETS:
+            with open(SWEEP_DIGESTS) as f:
+                want = np.array([int(x) for x in json.load(f)["digests"]], dtype=np.uint64)
+            host = reference.cpu().numpy().view(np.uint16)                       # [nchunks, world, chunk, row]
+            got = fnv1a64_rows(np, host.reshape(-1, row)).reshape(nchunks, world, chunk)
+            for c in range(nchunks):
+                for r in range(world):
+                    first = r * my_sets + c * chunk
+                    ok = ok and bool(np.array_equal(got[c, r], want[first:first + chunk]))
+                    checked += chunk
+        # ---- timed pass
+        gathered.zero_() if world > 1 else local.zero_()
+        barrier()
+
+        def sweep():
+            for c in range(nchunks):
+                eval_chunk(c)
+                gather_chunk(c)
+            join_side()
+            mg.compare_fingerprint_rows(rt, gathered.data_ptr(), reference.data_ptr(), nchunks * world * chunk, row,
+                                        flags.data_ptr(), mismatches.data_ptr(), stream=sh)
+
         if resident:
-            for c in range(1, nchunks):
-                fill_chunk(c)
+            t_total = timed(sweep, 1, 0)
+            # the evaluation alone, for the per-GPU bandwidth figure
             t_eval = timed(lambda: [eval_chunk(c) for c in range(nchunks)], 1, 0)
         else:
-            t_eval = 0.0
+            t_total, t_eval = 0.0, 0.0
             for c in range(nchunks):
-                if c > 0:
-                    fill_chunk(c)
-                t_eval += timed(lambda: eval_chunk(c), 1, 0)
-        # all-gather of the result fingerprints (8 KB per set) for dedup / comparison on every rank
-        gathered = result
-        t_gather = 0.0
-        if world > 1:
-            from attention_superoptimizer_b200 import sharding
-            local = result.view(my_sets, -1)
-            gathered = torch.empty((world * my_sets, local.shape[1]), dtype=local.dtype, device=local.device)
-            t_gather = timed(lambda: sharding.all_gather_fingerprints(local, world, out=gathered), 1, 2)  # 2 warm-ups
-        # compare on every rank: which of all the sets has the fingerprint of set 0 (the search's verify step)
-        from attention_superoptimizer_b200 import sharding as _sh
-        all_rows = gathered.view(-1, out[0].num_elements)
-        box = {}
-        t_compare = timed(lambda: box.__setitem__("m", _sh.matches_reference_on_device(all_rows, all_rows[0])), 1, 1)
-        equal_to_first = int(box["m"].sum().item())
-        evals_per_s = (nchunks * chunk * world) / ((t_eval + t_gather + t_compare) * 1e-3)
-        # bit-exact check of a sample against the CPU oracle
-        checked, ok = 0, True
-        if rank == 0:
-            specs, op1, op2 = mo.gqa_decode_plans(B, M, D, L, SPLITS, FORLOOP)
-            g1 = mo.build_customized(specs, op1)
-            g2 = mo.build_customized(mo.output_specs(g1), op2)
-            host = gathered.cpu().numpy().view(np.uint16).reshape(-1, out[0].num_elements)
-            for gs in sorted({0, my_sets - 1, (total_sets // world) * (world - 1)}):
-                x = [host_seeded(np, 3 * (2024 + gs) + i, n, mg.FP_P).reshape(s.dims) for i, (n, s) in enumerate(zip(elems, specs))]
-                o1, _ = fp_oracle.run(g1, x)
-                o2, _ = fp_oracle.run(g2, o1)
-                ok = ok and gs < host.shape[0] and np.array_equal(host[gs], o2[0].ravel())
-                checked += 1
+                fill_chunk(c)
+                t = timed(lambda: eval_chunk(c), 1, 0)
+                t_eval += t
+                t_total += t
+                gather_chunk(c)
+            join_side()
+            t_total += timed(lambda: mg.compare_fingerprint_rows(rt, gathered.data_ptr(), reference.data_ptr(), nchunks * world * chunk,
+                                                                 row, flags.data_ptr(), mismatches.data_ptr(), stream=sh), 1, 0)
+        mg.synchronize()
+        rows_equal = int(flags.sum().item())
+        evals_per_s = (nchunks * chunk * world) / (t_total * 1e-3)
         info = g.customized_info(3)
     return {"metric": "fingerprint_evals_per_s", "value": round(evals_per_s, 1), "unit": "evals/s",
             "sets": nchunks * chunk * world, "sets_per_gpu": nchunks * chunk, "chunk_sets": chunk,
             "inputs_resident": bool(resident),
-            "eval_ms": round(t_eval, 3), "allgather_ms": round(t_gather, 3), "compare_ms": round(t_compare, 3),
-            "sets_equal_to_first": equal_to_first,
+            "sweep_ms": round(t_total, 3), "eval_only_ms": round(t_eval, 3),
+            "timed_region": "evaluation of all chunks + all-gather of each chunk on a second stream + row-wise device "
+                            "comparison of all gathered fingerprints with the reference fingerprints",
+            "rows_equal_to_reference": rows_equal, "rows_compared": nchunks * chunk * world,
+            "mismatches": int(mismatches.item()),
             "bytes_per_eval": 16793600, "hbm_gbs_per_gpu": round(16793600 * nchunks * chunk / (t_eval * 1e-3) / 1e9, 1),
-            "kernel_op1": info["kernel_fingerprint"], "oracle_checked_sets": checked, "bit_exact": bool(ok)}
+            "frac_of_hbm_peak_per_gpu": round(16793600 * nchunks * chunk / (t_eval * 1e-3) / 1e9 / load_peaks()[0]["hbm_gbs"], 4),
+            "kernel_op1": info["kernel_fingerprint"], "oracle_checked_sets": checked,
+            "oracle": "FNV-1a-64 digests of the reference's own host code (oracle/_ref), tests/golden/sweep_digests_gqa_decode.json",
+            "bit_exact": bool(ok and checked > 0 and rows_equal == nchunks * chunk * world)}
 
 
 def run_one_config(args):
-    """`--only-config`: one of the other BASELINE configs alone (profiling, tuning); prints {"other_configs": {...}}."""
+    """`--only-config`: one of the other configurations alone (profiling, tuning); prints {"other_configs": {...}}."""
     import torch
     import attention_superoptimizer_b200 as mg
 
@@ -462,33 +578,44 @@ def run_one_config(args):
         torch.cuda.synchronize()
         return e0.elapsed_time(e1)
 
-    out = measure_other_configs(mg, rt, stream, timed, load_peaks()[0], only=args.only_config)
+    out = measure_other_configs(mg, rt, stream, timed, load_peaks()[0], only=args.only_config, quick=args.quick)
     print(json.dumps({"other_configs": out}))
 
 
-def measure_other_configs(mg, rt, stream, timed, peaks, only=None):
-    """Device-timed numbers for the remaining BASELINE configs (N = 1 only), each replayed from a CUDA graph:
-    config 3 (speculative decode with the causal draft window, fp16), config 4 (dense prefill, bf16, tcgen05)
-    and config 1 (matmul chain, both modes on the generic interpreters).  `only` = "c1" | "c3" | "c4" runs one."""
+def measure_other_configs(mg, rt, stream, timed, peaks, only=None, quick=False):
+    """Device-timed numbers for the remaining configurations (N = 1 only), each replayed from a CUDA graph:
+    speculative decode with the causal draft window (fp16), dense prefill (bf16, tcgen05) and the matmul chain (both
+    modes on the generic interpreters).  `only` = "c1" | "c3" | "c4" runs one; `quick` = few replays (profiling)."""
     sh = stream.cuda_stream
     out = {}
 
-    def replay_us(graphs, reps):
-        for g in graphs:
-            g.run(stream=sh, sync=False)
+    def replay_us(launch_all, reps):
+        launch_all(1)
         stream.synchronize()
-        seq = mg.CapturedSequence(sh, lambda: [graphs[i % len(graphs)].run(stream=sh, sync=False) for i in range(reps)])
-        # the clocks of an idle GPU take a while to come up: replay untimed for 0.3 s, then time 20 replays
-        t_end = time.perf_counter() + 0.3
-        while time.perf_counter() < t_end:
-            for _ in range(10):
-                seq.launch()
-            stream.synchronize()
-        ms = timed(seq.launch, 20, 3) / 20
+        seq = mg.CapturedSequence(sh, lambda: launch_all(reps))
+        if quick:
+            ms = timed(seq.launch, 2, 1) / 2
+        else:
+            # the clocks of an idle GPU take a while to come up: replay untimed for 0.3 s, then time 20 replays
+            t_end = time.perf_counter() + 0.3
+            while time.perf_counter() < t_end:
+                for _ in range(10):
+                    seq.launch()
+                stream.synchronize()
+            ms = timed(seq.launch, 20, 3) / 20
         seq.close()
+        mg.synchronize()
         return ms * 1000.0 / reps
 
-    # ---- config 3: batch 4 x 8 KV heads = 32 units, 8 draft tokens x group 4 = 32 rows, KV 8192 -------------
+    def graphs_runner(graphs):
+        return lambda reps: [graphs[i % len(graphs)].run(stream=sh, sync=False) for i in range(max(reps, len(graphs)) if reps == 1 else reps)]
+
+    def hbm_roofline(nbytes, us, kernel):
+        gbs = nbytes / us / 1e3
+        return {"bound": "hbm", "kernel": kernel, "achieved": round(gbs, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                "frac": round(gbs / peaks["hbm_gbs"], 4), "bytes_per_call": nbytes}
+
+    # ---- speculative decode: batch 4 x 8 KV heads = 32 units, 8 draft tokens x group 4 = 32 rows, KV 8192 -------------
     def config3():
         units, rows, d, kv, splits, fr, window = 32, 32, 128, 8192, 16, 8, 8
         graphs = []
@@ -501,16 +628,18 @@ def measure_other_configs(mg, rt, stream, timed, peaks, only=None):
             g.set_causal_window(3, window)
             Q.fill_data_seeded(900 + s, d ** -0.5); K.fill_data_seeded(910 + s, 1.0); V.fill_data_seeded(920 + s, 1.0)
             graphs.append(g)
-        us = replay_us(graphs, 8)
+        us = replay_us(graphs_runner(graphs), 8)
         nbytes = 2 * units * rows * d * 2 + 2 * units * d * kv * 2
         out["spec_decode_c3"] = {"us_per_call": round(us, 2), "hbm_gbs": round(nbytes / us / 1e3, 1),
                                  "frac_of_hbm_peak": round(nbytes / us / 1e3 / peaks["hbm_gbs"], 4), "bytes": nbytes,
+                                 "roofline": hbm_roofline(nbytes, us, "attn_split_tc_kernel + attn_merge_rows_kernel"),
                                  "kernel": graphs[0].customized_info(3)["kernel_float"], "dtype": "fp16",
-                                 "note": "32 rows x KV 8192, 16 splits x for-loop 8, causal draft window 8, fused merge"}
+                                 "note": "32 rows x KV 8192, 16 splits x for-loop 8, causal draft window 8, merge kernel behind "
+                                         "the tcgen05 split-KV kernel (programmatic dependent launch)"}
         for g in reversed(graphs):
             g.close()
 
-    # ---- config 4: 32 heads, 2048 x 2048, head_dim 128, bf16 ----------------------------------------------------
+    # ---- prefill: 32 heads, 2048 x 2048, head_dim 128, bf16 ----------------------------------------------------
     def config4():
         d = 128
         H, SQ, L = 32, 2048, 2048
@@ -520,15 +649,20 @@ def measure_other_configs(mg, rt, stream, timed, peaks, only=None):
         p1, p2 = mg.attention_prefill_plans(H, SQ, d, L)
         acc = g.customized([Q, K, V], p1); g.customized(acc, p2)
         Q.fill_data_seeded(930, d ** -0.5); K.fill_data_seeded(931, 1.0); V.fill_data_seeded(932, 1.0)
-        us = replay_us([g], 10)
+        us = replay_us(graphs_runner([g]), 10)
         flops = 4.0 * H * SQ * L * d
-        out["prefill_c4"] = {"us_per_call": round(us, 2), "tflops": round(flops / us / 1e6, 1),
-                             "frac_of_bf16_peak": round(flops / us / 1e6 / peaks["bf16_tflops"], 4), "flops": flops,
+        tf = flops / us / 1e6
+        out["prefill_c4"] = {"us_per_call": round(us, 2), "tflops": round(tf, 1),
+                             "frac_of_bf16_peak": round(tf / peaks["bf16_tflops"], 4), "flops": flops,
+                             "roofline": {"bound": "tensor", "kernel": "attn_rows_pp_kernel<bf16>", "achieved": round(tf, 1),
+                                          "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": round(tf / peaks["bf16_tflops"], 4),
+                                          "frac_of_sustained_peak": round(tf / peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"]), 4),
+                                          "flops_per_call": flops},
                              "kernel": g.customized_info(3)["kernel_float"], "dtype": "bf16",
                              "note": "both customized ops in one launch (division fused into the tcgen05 kernel's epilogue)"}
         g.close()
 
-    # ---- config 1: X[16,1024] W1[1024,1024] W2[1024,1024], fingerprint mode, generic interpreter -------------------
+    # ---- matmul chain: X[16,1024] W1[1024,1024] W2[1024,1024], generic interpreters, both modes -------------------
     def config1():
         g = mg.PyGraph(rt)
         X = g.new_input((16, 1024)); W1 = g.new_input((1024, 1024)); W2 = g.new_input((1024, 1024))
@@ -544,19 +678,21 @@ def measure_other_configs(mg, rt, stream, timed, peaks, only=None):
         for t, sd in ((X, 940), (W1, 941), (W2, 942)):
             t.fill_fingerprint_seeded(sd, mg.FP_P)
         g.fingerprint()
-        import time as _t
-        t0 = _t.perf_counter()
-        for _ in range(20):
-            g.fingerprint()
-        fp_us = (_t.perf_counter() - t0) / 20 * 1e6
-        X.fill_data_seeded(943, 1.0); W1.fill_data_seeded(944, 1.0 / 32); W2.fill_data_seeded(945, 1.0 / 32)
-        float_us = replay_us([g], 10)
+        lib, h = g.lib, g.handle
+        fp_us = replay_us(lambda reps: [mg.check(lib.mg_graph_fingerprint_enqueue(h, sh)) for _ in range(reps)], 10)
+        X.fill_data_seeded(943, 0.02); W1.fill_data_seeded(944, 0.02); W2.fill_data_seeded(945, 0.02)
+        float_us = replay_us(graphs_runner([g]), 10)
+        nbytes = 4259840
         out["matmul_chain_c1"] = {"float_us_per_call": round(float_us, 1), "fingerprint_us_per_call": round(fp_us, 1),
                                   "kernel": g.customized_info(3)["kernel_fingerprint"], "dtype": "fp16",
-                                  "bytes": 4259840, "flops": 67108864,
+                                  "bytes": nbytes, "flops": 67108864,
+                                  "roofline_float": hbm_roofline(nbytes, float_us, "float_interp_kernel<fp16>"),
+                                  "roofline_fingerprint": hbm_roofline(nbytes, fp_us, "fp_interp_kernel"),
                                   "note": "two customized ops (16 blocks over the intermediate columns, for-loop 16 over K "
-                                          "tiles of 64; then the cross-block reduction), generic interpreters; float: CUDA "
-                                          "graph replay; fingerprint: host-synchronised calls"}
+                                          "tiles of 64; then the cross-block reduction), generic interpreters; inputs N(0, 0.02) / "
+                                          "uniform [0,227); both modes replayed from a CUDA graph; the HBM floor of 0.65 us is "
+                                          "not the binding limit of 16 blocks (launch latency and the plan's redundant "
+                                          "arithmetic are)"}
         g.close()
 
     for name, fn in (("c3", config3), ("c4", config4), ("c1", config1)):
@@ -565,20 +701,7 @@ def measure_other_configs(mg, rt, stream, timed, peaks, only=None):
     return out
 
 
-def host_seeded(np, seed, n, modulus):
-    """Host twin of mg_rng_uniform (include/mugraph_rng.h): splitmix64 finaliser over (seed, index)."""
-    with np.errstate(over="ignore"):
-        idx = np.arange(n, dtype=np.uint64)
-        z = np.uint64(seed) * np.uint64(0x9E3779B97F4A7C15) + idx * np.uint64(0xD1B54A32D192ED03) + np.uint64(0x632BE59BD9B4E019)
-        z = (z ^ (z >> np.uint64(30))) * np.uint64(0xBF58476D1CE4E5B9)
-        z = (z ^ (z >> np.uint64(27))) * np.uint64(0x94D049BB133111EB)
-        z = z ^ (z >> np.uint64(31))
-    return ((z >> np.uint64(32)) % np.uint64(modulus)).astype(np.uint16)
-
-
-def cpu_float_baseline(mo, fp_oracle, np, budget_s, threads=0):
-    """Times the fp32 host evaluator (oracle/f32_oracle.c, OpenMP) on whole C2 calls for about
-    `budget_s` seconds.  Returns the cpu_baseline object."""
+def decode_float_inputs(mo, np):
     B, M, D, L = KV_HEADS, GROUP, HEAD_DIM, KV_LEN
     rng = np.random.default_rng(2024)
     specs, p1, p2 = mo.gqa_decode_plans(B, M, D, L, SPLITS, FORLOOP)
@@ -587,18 +710,69 @@ def cpu_float_baseline(mo, fp_oracle, np, budget_s, threads=0):
     q = (rng.standard_normal((B, M, D)) / np.sqrt(D)).astype(np.float16).astype(np.float32)
     k = rng.standard_normal((B, L, D)).astype(np.float16).astype(np.float32)   # memory image, column-major
     v = rng.standard_normal((B, D, L)).astype(np.float16).astype(np.float32)
-    used = 1
-    fp_oracle.run_float(g1, [q, k, v], threads)  # warm-up
+    return g1, g2, [q, k, v]
+
+
+def time_loop(fn, budget_s, max_n=50000):
+    fn()  # warm-up
     n, t0 = 0, time.perf_counter()
     while True:
-        o1, used = fp_oracle.run_float(g1, [q, k, v], threads)
-        fp_oracle.run_float(g2, o1, threads)
+        fn()
         n += 1
-        if time.perf_counter() - t0 > budget_s or n >= 50000:
+        if time.perf_counter() - t0 > budget_s or n >= max_n:
             break
-    dt = time.perf_counter() - t0
-    return {"value": round(dt / n * 1e6, 1), "unit": "us/call", "cores": int(used), "kind": "port",
-            "sample": "%d whole C2 muGraph calls (both operators) by the fp32 host evaluator oracle/f32_oracle.c in %.1f s" % (n, dt)}
+    return (time.perf_counter() - t0) / n, n
+
+
+def cpu_float_baseline(mo, fp_oracle, np, budget_s):
+    """Times the fp32 host evaluator (oracle/f32_oracle.c, OpenMP) on whole decode calls: all cores the process may
+    use, and one core.  Returns the cpu_baseline object (value = all cores)."""
+    g1, g2, x = decode_float_inputs(mo, np)
+    cores = host_cores()
+
+    def call(threads):
+        o1, _ = fp_oracle.run_float(g1, x, threads)
+        fp_oracle.run_float(g2, o1, threads)
+
+    t_all, n_all = time_loop(lambda: call(cores), budget_s * 0.6)
+    t_one, n_one = time_loop(lambda: call(1), budget_s * 0.4)
+    return {"value": round(t_all * 1e6, 1), "unit": "us/call", "cores": cores, "kind": "port",
+            "value_1core": round(t_one * 1e6, 1),
+            "sample": "%d (all cores) + %d (one core) whole decode muGraph calls, both operators, by the fp32 host evaluator "
+                      "oracle/f32_oracle.c (the reference has no CPU float path)" % (n_all, n_one)}
+
+
+def cpu_fingerprint_baseline(mo, np, budget_s):
+    """Times one fingerprint evaluation of the decode muGraph (both operators, one input set of the sweep) by the
+    reference's own fingerprinter classes compiled for the host (oracle/_ref), falling back to the plain-C port when
+    that library is absent: all cores and one core.  Reported as evaluations per second."""
+    from oracle import fp_oracle, ref_host
+    B, M, D, L = KV_HEADS, GROUP, HEAD_DIM, KV_LEN
+    specs, p1, p2 = mo.gqa_decode_plans(B, M, D, L, SPLITS, FORLOOP)
+    x = mo.sweep_inputs(0, specs)
+    cores = host_cores()
+    if ref_host.available():
+        kind, what = "reference", "the reference's host serialiser + fingerprinter classes (oracle/_ref/libref_host.so)"
+
+        def call(threads):
+            ref_host.set_threads(threads)
+            o1, _ = ref_host.customized_fingerprint(specs, p1, x)
+            ref_host.customized_fingerprint([mo.DTensorSpec(o.shape) for o in o1], p2, o1)
+    else:
+        kind, what = "port", "oracle/fp_oracle.c"
+        g1 = mo.build_customized(specs, p1)
+        g2 = mo.build_customized(mo.output_specs(g1), p2)
+
+        def call(threads):
+            o1, _ = fp_oracle.run(g1, x, 1, threads)
+            fp_oracle.run(g2, o1, 1, threads)
+
+    t_all, n_all = time_loop(lambda: call(cores), budget_s * 0.5, 2000)
+    t_one, n_one = time_loop(lambda: call(1), budget_s * 0.5, 2000)
+    return {"value": round(1.0 / t_all, 2), "unit": "evals/s", "cores": cores, "kind": kind,
+            "value_1core": round(1.0 / t_one, 2),
+            "sample": "%d (all cores) + %d (one core) evaluations of input set 0 of the sweep (33.5 M modular multiply-adds "
+                      "each) by %s; the full sweep is 4096 such evaluations" % (n_all, n_one, what)}
 
 
 # =================================================================================================
@@ -610,23 +784,18 @@ def run_reference(args):
         return
     import numpy as np
     from oracle import fp_oracle, mugraph_oracle as mo
-    # each step = one bounded sample: `calls` whole C2 muGraph evaluations by the fp32 host evaluator
-    B, M, D, L = KV_HEADS, GROUP, HEAD_DIM, KV_LEN
-    rng = np.random.default_rng(2024)
-    specs, p1, p2 = mo.gqa_decode_plans(B, M, D, L, SPLITS, FORLOOP)
-    g1 = mo.build_customized(specs, p1)
-    g2 = mo.build_customized(mo.output_specs(g1), p2)
-    q = (rng.standard_normal((B, M, D)) / np.sqrt(D)).astype(np.float16).astype(np.float32)
-    k = rng.standard_normal((B, L, D)).astype(np.float16).astype(np.float32)
-    v = rng.standard_normal((B, D, L)).astype(np.float16).astype(np.float32)
+    # each step = one bounded sample: `calls` whole decode muGraph evaluations by the fp32 host evaluator.
+    # The thread count is set explicitly: a launcher may export OMP_NUM_THREADS=1.
+    g1, g2, x = decode_float_inputs(mo, np)
+    cores = host_cores()
     calls = 4
-    used = 1
+    used = cores
 
     def step():
         nonlocal used
         for _ in range(calls):
-            o1, used = fp_oracle.run_float(g1, [q, k, v], 0)
-            fp_oracle.run_float(g2, o1, 0)
+            o1, used = fp_oracle.run_float(g1, x, cores)
+            fp_oracle.run_float(g2, o1, cores)
 
     for _ in range(args.warmup):
         step()
@@ -635,12 +804,13 @@ def run_reference(args):
         step()
     dt = time.perf_counter() - t0
     us = dt / (args.steps * calls) * 1e6
-    sample = "%d steps x %d whole C2 muGraph calls, fp32 host evaluator (oracle/f32_oracle.c, OpenMP)" % (args.steps, calls)
+    sample = "%d steps x %d whole decode muGraph calls, fp32 host evaluator (oracle/f32_oracle.c, OpenMP, %d threads)" % (args.steps, calls, used)
     line = {"impl": "reference", "metric": "gqa_decode_customized_op_us_per_call", "value": round(us, 1), "unit": "us/call",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dt / args.steps * 1e3, 3),
             "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "fp32",
             "data": "synthetic (seeded)",
-            "config": {"workload": "GQA incremental decode muGraph (BASELINE config 2), CPU evaluation",
+            "config": {"workload": "GQA incremental decode muGraph: batch 1, 32 q heads, 8 kv heads, head_dim 128, kv_len 4096, "
+                                   "16 KV splits x for-loop 4 (tiles of 64), 2 customized ops; CPU evaluation",
                        "calls_per_step": calls,
                        "note": "the reference has no CPU evaluation path and its GPU float interpreter does not compute "
                                "correct values; this arm times the fp32 host evaluator of the same graph semantics"},
@@ -655,25 +825,28 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--calls-per-step", type=int, default=0, help="muGraph evaluations per step (0 = auto)")
+    ap.add_argument("--batch", type=int, default=64, help="independent calls per batched launch of the headline protocol")
+    ap.add_argument("--replays-per-step", type=int, default=0,
+                    help="replays of the captured launch sequence per step (0 = about 30 ms per step)")
     ap.add_argument("--sweep-sets", type=int, default=SWEEP_SETS, help="input sets of the fingerprint sweep (all ranks)")
-    ap.add_argument("--sweep-chunk", type=int, default=128, help="sets resident per chunk and rank")
+    ap.add_argument("--sweep-chunk", type=int, default=128, help="sets per evaluation launch and rank")
     ap.add_argument("--k-layout", default="col", choices=["row", "col"],
                     help="DmemLayout of K[heads, d, kv]: col = memory [kv][d] (KV-cache order), row = memory [d][kv]")
     ap.add_argument("--v-layout", default="row", choices=["row", "col"],
                     help="DmemLayout of V[heads, kv, d]: row = memory [kv][d] (KV-cache order), col = memory [d][kv]")
     ap.add_argument("--streams", type=int, default=0,
-                    help="streams the independent calls of a step are spread over (0 = 8 per rank at N = 1, 16 at N = 2, "
-                         "32 from N = 4: the fewer KV heads a rank holds, the more calls fit on the GPU at once)")
+                    help="per-call-launch protocol: streams the calls are spread over (0 = 8 per rank at N = 1, 16 at N = 2, "
+                         "32 from N = 4)")
     ap.add_argument("--interpreter-only", action="store_true", help="disable the specialised kernels")
     ap.add_argument("--specialisation", type=int, default=2, choices=[0, 1, 2],
                     help="0 = interpreters, 1 = specialised kernels without operator fusion, 2 = with fusion (default)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--no-other-configs", action="store_true", help="skip the extra measurements of configs 1, 3 and 4")
+    ap.add_argument("--no-other-configs", action="store_true", help="skip the extra measurements of the other configurations")
     ap.add_argument("--no-latency-probes", action="store_true",
                     help="skip the single-call latency and the 1024 + 1024 launch L2-resident measurement (short launch lists)")
     ap.add_argument("--only-config", default=None, choices=["c1", "c3", "c4"],
-                    help="measure just this other config on one GPU and print its entry (no headline line)")
+                    help="measure just this other configuration on one GPU and print its entry (no headline line)")
+    ap.add_argument("--quick", action="store_true", help="with --only-config: a handful of replays only (profiler runs)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":

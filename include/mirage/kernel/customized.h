@@ -27,6 +27,14 @@ public:
   // same as the two above for `num_sets` independent tensor sets (strides in elements)
   int launch_fingerprint_sets(int num_sets, void const *const *in, long long const *in_stride, void *const *out,
                               long long const *out_stride, void *stream);
+  int launch_float_sets(int num_sets, void const *const *in, long long const *in_stride, void *const *out,
+                        long long const *out_stride, void *stream);
+  // The fused pair (this operator + `merge`, see can_fuse_with) for `num_sets` independent tensor sets in one
+  // launch: in / out as above (out = this operator's two outputs in operator order), merged_out = the merge
+  // operator's output, tickets = heads * num_sets zeroed int32 of device memory.
+  int launch_fused_sets(KNCustomizedOp *merge, bool fingerprint_mode, int num_sets, void const *const *in,
+                        long long const *in_stride, void *const *out, long long const *out_stride, void *merged_out,
+                        long long merged_stride, int *tickets, void *stream);
 
   // Non-asserting construction: nullptr plus a message when the plan is invalid for these inputs
   // or the outputs do not fit the arena.
@@ -62,8 +70,16 @@ private:
   int o_output_ = 0, o_input_ = 0;
   bool ensure_lowered();
   void after_build();
+  struct FusedMerge { // the merge operator's output riding along with a split-KV launch
+    void *out;
+    long long set_stride;
+    size_t bytes;
+    int *tickets;
+  };
   int launch_split(bool fingerprint_mode, int num_sets, void const *const *in, long long const *in_stride,
-                   void *const *out, long long const *out_stride, KNCustomizedOp *merge, void *stream);
+                   void *const *out, long long const *out_stride, FusedMerge const *merge, void *stream);
+  int launch_sets(bool fingerprint_mode, int num_sets, void const *const *in, long long const *in_stride,
+                  void *const *out, long long const *out_stride, void *stream);
   int *tickets_ = nullptr; // per-head "last block done" counters of the fused launch (arena scratch)
 };
 

@@ -220,6 +220,10 @@ int mg_graph_fingerprint(mg_graph *g);
 /* same, but input operators keep whatever their buffers hold (uploaded or seeded contents)
  * instead of being refilled with i % FP_PQ */
 int mg_graph_fingerprint_compute(mg_graph *g);
+/* mg_graph_fingerprint_compute without the synchronisation: the fingerprint kernels of every non-input operator
+ * are enqueued on `stream` (a sequence a verifier captures and replays, or overlaps with other work); the caller
+ * synchronises, e.g. with mg_device_synchronize, which also reports a bounded wait that gave up */
+int mg_graph_fingerprint_enqueue(mg_graph *g, void *stream);
 /* KNCustomizedOp::run(), customized_kernel.cu:605-613: asynchronous launch on `stream`
  * (a cudaStream_t; NULL = default stream) */
 int mg_op_run(mg_graph *g, int32_t op_idx, void *stream);
@@ -229,6 +233,9 @@ int mg_op_run(mg_graph *g, int32_t op_idx, void *stream);
 int mg_op_profile(mg_graph *g, int32_t op_idx, int32_t warmup, int32_t iters, float *ms);
 /* run every operator of the graph in order on `stream` (asynchronous) */
 int mg_graph_run(mg_graph *g, void *stream);
+/* A graph owns the scratch of its fused launches (one ticket counter per head): two launches of the SAME graph
+ * must not be in flight at the same time (different streams without an ordering between them).  Different graphs
+ * are independent. */
 
 /* Batched fingerprint evaluation: the same graph evaluated on `num_sets` independent
  * input sets in one pass.  Input i of set s is read at in_fp[i] + s * elements(input i);
@@ -238,6 +245,22 @@ int mg_graph_run(mg_graph *g, void *stream);
  * Stands in for `num_sets` repetitions of the verify loop, src/search/search.cc:601-603. */
 int mg_graph_fingerprint_batched(mg_graph *g, int32_t num_sets, const uint16_t *const *in_fp, uint16_t *out_fp,
                                  void *workspace, size_t *workspace_bytes, void *stream);
+
+/* The float-mode counterpart: `num_sets` independent calls of the same graph (KNCustomizedOp::run,
+ * customized_kernel.cu:605-613, repeated) as one pass - one kernel per customized operator over all sets, and a
+ * split-KV attention operator together with the merge operator consuming it as ONE kernel.  Input i of set s is
+ * read at in_data[i] + s * elements(input i) 16-bit values, the last operator's output 0 of set s is written to
+ * out_data + s * elements(output); same workspace protocol as above.  Asynchronous on `stream`. */
+int mg_graph_run_batched(mg_graph *g, int32_t num_sets, const void *const *in_data, void *out_data, void *workspace,
+                         size_t *workspace_bytes, void *stream);
+
+/* Row-wise comparison of two fingerprint arrays [rows][row_elements] on the device, one pass over both:
+ * equal_flags[r] = 1 when row r of `a` equals row r of `b` bit for bit, else 0; *mismatch_count (optional, device
+ * memory, zeroed by this call) = rows that differ.  All pointers are device memory; asynchronous on `stream`.
+ * The search's verify loop (src/search/search.cc:601-609: one DTensor::has_same_fingerprint with two blocking
+ * copies per candidate) for a whole batch of gathered fingerprints. */
+int mg_compare_fingerprint_rows(mg_runtime *rt, const uint16_t *a, const uint16_t *b, int64_t rows, int64_t row_elements,
+                                int32_t *equal_flags, int32_t *mismatch_count, void *stream);
 
 /* DTensor::has_same_fingerprint, src/kernel/cuda/device_tensor_kernel.cu:22-53;
  * compared on the device, one 4-byte result copied back */

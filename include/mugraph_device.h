@@ -233,6 +233,9 @@ int mgd_fill_fingerprint_seeded(uint16_t *p, int64_t n, uint64_t seed, uint32_t 
 int mgd_fill_data_seeded(void *p, int64_t n, uint64_t seed, float sigma, int32_t data_type, void *stream);
 /* *device_flag (4 bytes, device memory) <- 1 if equal else 0 */
 int mgd_compare_u16(const uint16_t *a, const uint16_t *b, int64_t n, int32_t *device_flag, void *stream);
+/* row-wise: equal_flags[r] <- 1 if a[r][:] == b[r][:] else 0; *mismatch_count (optional) <- rows that differ */
+int mgd_compare_rows_u16(const uint16_t *a, const uint16_t *b, int64_t rows, int64_t row_elements, int32_t *equal_flags,
+                         int32_t *mismatch_count, void *stream);
 /* copies the lookup tables of src/kernel/device_memory_manager.cu:41-90 into constant memory
  * of the current device; idempotent */
 int mgd_tables_init(const uint16_t *exp_tbl, const uint16_t *div_p_tbl, const uint16_t *div_q_tbl);

@@ -413,3 +413,69 @@ def test_attention_plans_with_the_row_sum_first(runtime, specialisation):
             assert_close(got, mo.attention_fp32(q, k, v), mg.float16, "row sum first")
     finally:
         runtime.set_specialisation(2)
+
+
+# ---- batched float launch and row-wise comparison ---------------------------------------------------------------------------
+@pytest.mark.parametrize("shape", [(8, 4, 128, 4096, 16, 4), (2, 16, 128, 1024, 4, 4)], ids=["decode", "16_rows_tcgen05"])
+def test_batched_float_run_equals_single_calls(runtime, shape):
+    """Several independent float-mode calls of one graph in one pass (split-KV + merge as one kernel over all the
+    sets) give what the graph gives for each set alone, and what the fp32 evaluation gives."""
+    import torch
+    B, M, D, L, S, F = shape
+    nsets = 5
+    runtime.set_specialisation(2)
+    rng = np.random.default_rng(61)
+    rnd = lambda a: from_bits(to_bits(a, mg.float16), mg.float16)
+    with mg.PyGraph(runtime) as g:
+        Q = g.new_input((B, M, D)); K = g.new_input((B, D, L), layout=mg.DmemColumnMajor); V = g.new_input((B, L, D))
+        p1, p2 = mg.gqa_decode_plans(B, M, D, L, S, F)
+        out = g.customized(g.customized([Q, K, V], p1), p2)
+        qs = [rnd(rng.standard_normal((B, M, D)) / np.sqrt(D)) for _ in range(nsets)]
+        ks = [rnd(rng.standard_normal((B, D, L))) for _ in range(nsets)]
+        vs = [rnd(rng.standard_normal((B, L, D))) for _ in range(nsets)]
+        bits = lambda xs, tr: torch.from_numpy(np.stack([to_bits(np.ascontiguousarray(x.transpose(0, 2, 1)) if tr else x, mg.float16)
+                                                           for x in xs]).astype(np.int16)).cuda()
+        dev = [bits(qs, False), bits(ks, True), bits(vs, False)]
+        res = torch.zeros((nsets, B, M, D), dtype=torch.int16, device="cuda")
+        wbytes = g.run_batched_workspace(nsets)
+        work = torch.empty(max(wbytes, 256), dtype=torch.uint8, device="cuda")
+        torch.cuda.synchronize()
+        for _ in range(2):  # twice: the ticket counters in the workspace are cleared by every call
+            res.zero_()
+            torch.cuda.synchronize()
+            g.run_batched(nsets, [d.data_ptr() for d in dev], res.data_ptr(), work.data_ptr(), wbytes)
+            mg.synchronize()
+            got = from_bits(res.cpu().numpy().view(np.uint16), mg.float16)
+            for s in range(nsets):
+                assert_close(got[s], mo.attention_fp32(qs[s], ks[s], vs[s]), mg.float16, "set %d" % s)
+        Q.upload_data(to_bits(qs[2], mg.float16))
+        K.upload_data(to_bits(np.ascontiguousarray(ks[2].transpose(0, 2, 1)), mg.float16))
+        V.upload_data(to_bits(vs[2], mg.float16))
+        g.run()
+        single = from_bits(out[0].download_data(), mg.float16).reshape(out[0].shape)
+        # a single call is launched with other block shapes (more KV tiles side by side), so the partial sums are
+        # added in another order: equal up to fp16 rounding, not bit for bit
+        assert_close(single, got[2], mg.float16, "single call vs the same set in a batch")
+
+
+def test_compare_fingerprint_rows(runtime):
+    import torch
+    rows, n = 37, 4096
+    rng = np.random.default_rng(3)
+    a = rng.integers(0, mo.FP_PQ, size=(rows, n)).astype(np.uint16)
+    b = a.copy()
+    differ = [0, 5, 36]
+    b[0, 0] ^= 1; b[5, n - 1] ^= 1; b[36, 1234] ^= 7
+    da, db = torch.from_numpy(a.astype(np.int16)).cuda(), torch.from_numpy(b.astype(np.int16)).cuda()
+    flags = torch.full((rows,), -1, dtype=torch.int32, device="cuda")
+    count = torch.full((1,), -1, dtype=torch.int32, device="cuda")
+    torch.cuda.synchronize()
+    mg.compare_fingerprint_rows(runtime, da.data_ptr(), db.data_ptr(), rows, n, flags.data_ptr(), count.data_ptr())
+    mg.synchronize()
+    assert flags.cpu().tolist() == [0 if r in differ else 1 for r in range(rows)]
+    assert int(count.item()) == len(differ)
+    # rows whose length or alignment rules out 128-bit loads
+    mg.compare_fingerprint_rows(runtime, da.data_ptr() + 2, db.data_ptr() + 2, 5, 4095, flags.data_ptr(), None)
+    mg.synchronize()
+    want = [int(np.array_equal(a.ravel()[1 + r * 4095:1 + (r + 1) * 4095], b.ravel()[1 + r * 4095:1 + (r + 1) * 4095])) for r in range(5)]
+    assert flags.cpu().tolist()[:5] == want
