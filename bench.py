@@ -371,6 +371,10 @@ def run_ours(args):
     if world == 1 and not args.no_other_configs:
         others = measure_other_configs(mg, rt, stream, timed, peaks)
 
+    # ---- the reference's own GPU fingerprint kernel on the same box (rank 0, N = 1 only) -------------------------
+    if rank == 0 and world == 1 and not args.no_reference_gpu:
+        fingerprint["reference_gpu"] = reference_gpu_fingerprint(mo, np, torch, mg, rt, fingerprint["value"])
+
     # ---- CPU baselines (rank 0, N = 1 only) ----------------------------------------------------------------
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
@@ -701,6 +705,46 @@ def measure_other_configs(mg, rt, stream, timed, peaks, only=None, quick=False):
     return out
 
 
+def reference_gpu_fingerprint(mo, np, torch, mg, rt, our_evals_per_s):
+    """The reference's compute_customizedop_fingerprint built for sm_100a (oracle/_ref/libref_gpu.so) on evaluations
+    of the sweep, launched the way the reference launches it (`for op: op->fingerprint()`: one kernel and one
+    device synchronisation per operator, one input set at a time).  Its result for a seeded set is compared with
+    the committed digest of that set."""
+    from oracle import ref_gpu
+    if not ref_gpu.available():
+        return {"unavailable": "oracle/_ref/libref_gpu.so has not been built (needs the reference checkout)"}
+    B, M, D, L = KV_HEADS, GROUP, HEAD_DIM, KV_LEN
+    specs, p1, p2 = mo.gqa_decode_plans(B, M, D, L, SPLITS, FORLOOP)
+    op1 = ref_gpu.CustomizedOp(specs, p1)
+    op2 = ref_gpu.CustomizedOp(None, p2, producer=op1)
+    try:
+        s = 7
+        bufs = []
+        for i, sp in enumerate(specs):
+            n = int(np.prod(sp.dims))
+            b = torch.empty(n, dtype=torch.int16, device="cuda")
+            mg.fill_fingerprint_seeded_raw(rt, b.data_ptr(), n, 3 * (2024 + s) + i, mg.FP_P)
+            op1.set_input_from_device(i, b.data_ptr())
+            bufs.append(b)
+        op1.fingerprint()
+        op2.fingerprint()
+        ok = None
+        if os.path.exists(SWEEP_DIGESTS):
+            with open(SWEEP_DIGESTS) as f:
+                ok = str(mo.fnv1a64(op2.output(0))) == json.load(f)["digests"][s]
+        ref_gpu.time_pair(op1, op2, 20)
+        iters = 300
+        ms = ref_gpu.time_pair(op1, op2, iters)
+    finally:
+        op2.destroy()
+        op1.destroy()
+    return {"value": round(1000.0 / ms, 1), "unit": "evals/s", "ms_per_eval": round(ms, 4), "evaluations_timed": iters,
+            "matches_committed_digest": ok, "ratio_ours_over_reference_gpu": round(our_evals_per_s * ms / 1000.0, 1),
+            "kernel": "compute_customizedop_fingerprint (src/kernel/cuda/customized_kernel.cu:307-603), sm_100a build",
+            "protocol": "the reference's: per input set, one launch and one cudaDeviceSynchronize per customized operator "
+                        "(customized_kernel.cu:655-678); wall clock"}
+
+
 def decode_float_inputs(mo, np):
     B, M, D, L = KV_HEADS, GROUP, HEAD_DIM, KV_LEN
     rng = np.random.default_rng(2024)
@@ -841,6 +885,7 @@ def main():
     ap.add_argument("--specialisation", type=int, default=2, choices=[0, 1, 2],
                     help="0 = interpreters, 1 = specialised kernels without operator fusion, 2 = with fusion (default)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-reference-gpu", action="store_true", help="skip the reference's own GPU fingerprint kernel")
     ap.add_argument("--no-other-configs", action="store_true", help="skip the extra measurements of the other configurations")
     ap.add_argument("--no-latency-probes", action="store_true",
                     help="skip the single-call latency and the 1024 + 1024 launch L2-resident measurement (short launch lists)")
