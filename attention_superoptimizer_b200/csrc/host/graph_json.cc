@@ -465,6 +465,12 @@ struct Reader {
 namespace mirage {
 namespace kernel {
 
+std::string to_json_string(KNOperator const &op) {
+  std::string out;
+  dump(to_value(&op), out);
+  return out;
+}
+
 std::string to_json_string(Graph const &g) {
   JValue root = jarr();
   for (KNOperator const *op : g.operators) root.arr.push_back(to_value(op));

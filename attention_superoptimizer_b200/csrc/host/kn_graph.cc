@@ -900,12 +900,28 @@ bool KNCustomizedOp::profile(ProfileResult &result) {
 }
 
 // ---- Graph ---------------------------------------------------------------------------------------
-Graph::Graph(void) {}
-Graph::~Graph() {
-  while (!operators.empty()) {
-    delete operators.back();
-    operators.pop_back();
+Graph::Graph(void) : owners_(std::make_shared<int>(0)) {}
+Graph::Graph(Graph const &other) : operators(other.operators), owners_(other.owners_) {}
+Graph &Graph::operator=(Graph const &other) {
+  if (this != &other) {
+    drop();
+    operators = other.operators;
+    owners_ = other.owners_;
   }
+  return *this;
+}
+Graph::~Graph() { drop(); }
+void Graph::release() { owners_.reset(); }
+// Gives up this copy's share; the last copy deletes the operators in its list, newest first.
+void Graph::drop() {
+  bool const last = owners_ && owners_.use_count() == 1;
+  owners_.reset();
+  if (last)
+    while (!operators.empty()) {
+      delete operators.back();
+      operators.pop_back();
+    }
+  operators.clear();
 }
 
 static bool fits_arena(DTensor const &t) {

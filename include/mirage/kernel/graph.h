@@ -6,6 +6,7 @@
 #include "mirage/kernel/device_tensor.h"
 #include "mirage/kernel/operator.h"
 #include "mirage/threadblock/graph.h"
+#include <memory>
 #include <vector>
 
 namespace mirage {
@@ -14,9 +15,16 @@ namespace kernel {
 class Graph {
 public:
   Graph(void);
-  ~Graph(); // deletes the operators in reverse order: arena frees are LIFO
-  Graph(Graph const &) = delete;
-  Graph &operator=(Graph const &) = delete;
+  // Copies are shallow, as in the reference (its Graph is a plain struct around `operators`, and callers such as
+  // the search keep graphs by value, src/search/search.cc:13-21): the operator list is copied, the operators
+  // themselves are shared.  The reference never deletes operators; here the LAST live copy of a graph deletes
+  // the operators still in its list, in reverse order (arena frees are LIFO).  A caller that deletes operators
+  // itself (the search pops and deletes while backtracking) removes them from the list first, as it does today,
+  // or calls release() to take over ownership of everything.
+  Graph(Graph const &other);
+  Graph &operator=(Graph const &other);
+  ~Graph();
+  void release(); // this copy, and every copy made from it afterwards, no longer deletes anything
 
   DTensor new_input(std::vector<int> const &dims, mirage::type::DataType data_type,
                     mirage::layout::DmemLayout layout);
@@ -48,6 +56,10 @@ public:
   KNOperator *create_customized_op(std::vector<DTensor> const &inputs, mirage::threadblock::Graph const &graph);
 
   std::vector<KNOperator *> operators;
+
+private:
+  void drop();
+  std::shared_ptr<int> owners_; // one count shared by all copies; null after release()
 };
 
 } // namespace kernel

@@ -4,9 +4,9 @@
 // objects, src/utils/json_utils.cc).
 //
 // The reference speaks nlohmann::json values; this library has no third-party JSON dependency, so the same
-// documents travel as text.  With nlohmann available a caller writes
-//     json j = json::parse(mirage::kernel::to_json_string(g));        // json(g)
-//     mirage::kernel::from_json_string(j.dump(), g);                  // from_json(j, g)
+// documents travel as text.  A caller that has nlohmann/json.hpp on its include path includes
+// mirage/utils/json_nlohmann.h and gets the reference's own spellings back: `json j = g;` (to_json by argument
+// lookup), `j.get_to(g)` / `from_json(j, g)`, and `mirage::kernel::operator_json(*op)` for `json(*op)`.
 // Documents written by the reference (for instance the search checkpoints' "generated_graphs" entries) load
 // unchanged, and documents written here load in the reference.
 #pragma once
@@ -18,6 +18,8 @@ namespace kernel {
 
 // The graph as a JSON array of operators, keys in alphabetical order as nlohmann's dump() prints them.
 std::string to_json_string(Graph const &g);
+// One operator: the document the reference's `operator json()` of that operator class builds.
+std::string to_json_string(KNOperator const &op);
 
 // Rebuilds the operators described by `text` into `g` (normally an empty graph), following the reference's
 // from_json: inputs by shape / data type / layout, matmul / exp / div / add / mul / reduction by the guids of

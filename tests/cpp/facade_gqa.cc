@@ -5,6 +5,9 @@
 #include "mirage/kernel/device_memory_manager.h"
 #include "mirage/kernel/graph.h"
 #include "mirage/utils/json_utils.h"
+#ifdef MG_TEST_NLOHMANN
+#include "mirage/utils/json_nlohmann.h"
+#endif
 #include "mirage/threadblock/graph.h"
 #include <cstdio>
 #include <cstdlib>
@@ -106,6 +109,33 @@ int main() {
       CHECK(a->bgraph.smem_offset == b->bgraph.smem_offset && a->output_tensors.size() == b->output_tensors.size());
       CHECK(!kernel::from_json_string("[{\"op_type\": \"kn_matmul_op\"}]", again, &err) && !err.empty());
     }
+    // copies are shallow and share ownership, as the reference's callers expect: a copy taken by value (the
+    // search keeps the computation graph that way) sees the same operators, grows on its own, and going out of
+    // scope deletes nothing while the original lives
+    {
+      size_t before = (size_t)kernel::DeviceMemoryManager::get_instance()->offset;
+      {
+        kernel::Graph by_value = graph;
+        CHECK(by_value.operators.size() == graph.operators.size() && by_value.operators[3] == graph.operators[3]);
+        kernel::Graph assigned;
+        assigned = by_value;
+        CHECK(assigned.operators.back() == graph.operators.back());
+      }
+      CHECK((size_t)kernel::DeviceMemoryManager::get_instance()->offset == before);
+      CHECK(graph.operators.back()->output_tensors.size() == 1);
+    }
+#ifdef MG_TEST_NLOHMANN
+    // the nlohmann::json spellings of the wire format (header-only adapter over the text functions)
+    {
+      json j = graph;
+      CHECK(j.is_array() && j.size() == graph.operators.size() && j[3]["op_type"] == "kn_customized_op");
+      CHECK(kernel::operator_json(*graph.operators[0])["op_type"] == "kn_input_op");
+      kernel::Graph rebuilt;
+      j.get_to(rebuilt);
+      CHECK(rebuilt.operators.size() == graph.operators.size());
+      CHECK(json(rebuilt).dump().size() == j.dump().size());
+    }
+#endif
     // no device: nothing can be computed here, and the library says so instead of falling back
     CHECK(graph.operators.back()->fingerprint() == false);
     ProfileResult result;

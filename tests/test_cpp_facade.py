@@ -1,7 +1,9 @@
 """The C++ facade (include/mirage/**) compiles and links like the reference's headers do: a translation of the
 reference's grouped-query decode example is built with g++ against libmugraph.so and run without a GPU."""
+import glob
 import os
 import subprocess
+import sysconfig
 
 from attention_superoptimizer_b200 import _abi
 
@@ -13,6 +15,28 @@ def test_cpp_example_builds_and_runs(tmp_path):
     libdir = os.path.dirname(_abi.LIB_PATH)
     cmd = ["g++", "-std=c++17", "-O1", os.path.join(ROOT, "tests", "cpp", "facade_gqa.cc"), "-I" + os.path.join(ROOT, "include"),
            "-I/usr/local/cuda/include", "-L" + libdir, "-lmugraph", "-Wl,-rpath," + libdir, "-o", exe]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    r = subprocess.run([exe], capture_output=True, text=True, timeout=60)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "facade ok" in r.stdout
+
+
+def test_cpp_example_with_the_nlohmann_adapter(tmp_path):
+    """Same program with mirage/utils/json_nlohmann.h: `json j = graph`, `j.get_to(graph)`, operator_json.  Needs
+    nlohmann/json.hpp, which is not part of this repository: taken from wherever a Python package happens to
+    carry it, skipped when none does."""
+    import pytest
+    site = sysconfig.get_paths()["purelib"]
+    hits = glob.glob(os.path.join(site, "**", "nlohmann", "json.hpp"), recursive=True)
+    if not hits:
+        pytest.skip("no nlohmann/json.hpp on this machine")
+    inc = os.path.dirname(os.path.dirname(hits[0]))
+    exe = str(tmp_path / "facade_gqa_json")
+    libdir = os.path.dirname(_abi.LIB_PATH)
+    cmd = ["g++", "-std=c++17", "-O1", "-DMG_TEST_NLOHMANN", os.path.join(ROOT, "tests", "cpp", "facade_gqa.cc"),
+           "-I" + os.path.join(ROOT, "include"), "-I" + inc, "-I/usr/local/cuda/include", "-L" + libdir, "-lmugraph",
+           "-Wl,-rpath," + libdir, "-o", exe]
     r = subprocess.run(cmd, capture_output=True, text=True)
     assert r.returncode == 0, r.stderr
     r = subprocess.run([exe], capture_output=True, text=True, timeout=60)
