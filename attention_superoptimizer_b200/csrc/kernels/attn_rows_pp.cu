@@ -321,21 +321,8 @@ attn_rows_pp_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
 }
 
 // ---- host side ------------------------------------------------------------------------------------------------
-using EncodeFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, cuuint64_t const *,
-                              cuuint64_t const *, cuuint32_t const *, cuuint32_t const *, CUtensorMapInterleave,
-                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-static EncodeFn encode_fn() {
-  static EncodeFn fn = nullptr;
-  static std::once_flag once;
-  std::call_once(once, [] {
-    void *sym = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeFn>(sym);
-  });
-  return fn;
-}
+using EncodeFn = TensorMapEncodeFn; // cuTensorMapEncodeTiled through the shared lookup (ptx.cuh)
+static EncodeFn encode_fn() { return tensor_map_encoder(); }
 // [batch][rows][cols] 16-bit array, box [1][128][64], 128-byte swizzle
 static bool make_map(CUtensorMap *map, void const *base, uint64_t batch, uint64_t rows, uint64_t cols) {
   EncodeFn fn = encode_fn();

@@ -14,6 +14,10 @@
 //   * a matmul whose result feeds nothing but an output operator adds straight into that operator's
 //     accumulator and the result tile is not allocated;
 //   * an input tile that does not move with the for-loop is loaded in the first iteration only;
+//   * 16-bit input tiles of row-major tensors are fetched by the TMA engine, the moving ones into a multi-stage ring
+//     along the for-loop (interp_common.cuh); other input tiles use plain loads;
+//   * a matmul by a loop-invariant tile whose result is only summed over the for-loop is taken once, after the loop,
+//     on the sum of its left operands (interp_common.cuh);
 //   * a matmul whose B operand is such a 16-bit tile (n % 8 == 0, k % 16 == 0) runs on the tensor cores
 //     (mma.sync m16n8k16, fp32 accumulate): its A operand, 16-bit or computed fp32, is staged as 16-bit rows in a
 //     region behind the tiles, B tiles that only such matmuls read get 16 bytes of row padding (both for
@@ -22,7 +26,9 @@
 // Loads honour the tensor's DmemLayout: a column-major tensor keeps each [rows, cols] matrix with the
 // row index contiguous.  Outputs are rounded to nearest on store.
 #include "common.cuh"
+#include "interp_common.cuh"
 #include <cstdio>
+#include <cstring>
 #include <cstdlib>
 
 namespace mgk {
@@ -30,7 +36,6 @@ int validate_program(mgd_program const *p, mgd_bindings const *b);
 
 // flag bits the host packs into operator arguments after replanning
 constexpr int kIn16 = 1 << 8;         // input a[16]: the tile keeps 16-bit elements
-constexpr int kInInvariant = 1 << 9;  // input a[16]: same tile every iteration, load once
 constexpr int kInPadShift = 16;       // input a[16] bits 16-23: elements of padding after every tile row
 
 template <typename T> __device__ __forceinline__ void cvt4(uint2 w, float *f);
@@ -115,8 +120,11 @@ template <> __device__ __forceinline__ void mma16816<__nv_bfloat16>(float (&c)[4
 // A is first written by the whole block as 16-bit rows of k + 8 elements into the staging room the host planned
 // (rows past m as zeros), so that its fragments come from one conflict-free ldmatrix per step: A's dense rows are a
 // multiple of 128 bytes apart for the usual k and four plain loads per step would share their banks.
+// `residual`: stage what the 16-bit rounding of an fp32 operand left over, A - round(A), instead of round(A); a
+// product taken once after the for-loop adds that second term so that the sum it multiplies keeps fp32 precision.
 template <typename T>
-__device__ __noinline__ void stage_a(unsigned char const *Ap, bool a16, unsigned char *staged, int m, int k, int tid, int nt) {
+__device__ __noinline__ void stage_a(unsigned char const *Ap, bool a16, unsigned char *staged, int m, int k, int tid, int nt,
+                                     bool residual = false) {
   int const half_k = k >> 1, rows = ((m + 15) >> 4) << 4, pitch2 = (k + 8) >> 1;
   uint32_t *dst = reinterpret_cast<uint32_t *>(staged);
   for (int i = tid; i < rows * half_k; i += nt) {
@@ -127,15 +135,21 @@ __device__ __noinline__ void stage_a(unsigned char const *Ap, bool a16, unsigned
       else {
         float2 const x = reinterpret_cast<float2 const *>(Ap)[(size_t)r * half_k + c2];
         v = pack_pair<T>(x.x, x.y);
+        if (residual) {
+          T const *h = reinterpret_cast<T const *>(&v);
+          v = pack_pair<T>(x.x - to_float<T>(h[0]), x.y - to_float<T>(h[1]));
+        }
       }
     }
     dst[r * pitch2 + c2] = v;
   }
 }
 
+// `b_swizzled`: B sits as 64-column boxes of k rows x 128 bytes with the 128-byte swizzle, as the TMA engine wrote it
+// (16-byte unit u of row r at unit u ^ (r % 8)); dense or padded rows of `b_pitch` elements otherwise.
 template <typename T, int NT>
 __device__ __noinline__ void matmul_mma(unsigned char const *staged, unsigned char const *Bp, float *C, int m, int n, int k,
-                                        int b_pitch, bool add, int tid, int nt) {
+                                        int b_pitch, bool b_swizzled, bool add, int tid, int nt) {
   int const lane = tid & 31, warp = tid >> 5, nwarps = nt >> 5;
   int const g = lane >> 2, t = lane & 3, mi = lane >> 3, rr = lane & 7;
   int const m_tiles = (m + 15) >> 4, n_units = n / (8 * NT);
@@ -155,8 +169,16 @@ __device__ __noinline__ void matmul_mma(unsigned char const *staged, unsigned ch
     // warp only lanes 0-15 supply addresses, the two k halves of the same 8 columns.
     uint32_t aaddr = a_base + (uint32_t)(((m0 + (mi & 1) * 8 + rr) * a_pitch + (mi >> 1) * 8) * 2);
     uint32_t baddr = b_base + (uint32_t)((((mi & 1) * 8 + rr) * b_pitch + n0 + (NT >= 2 ? (mi >> 1) * 8 : 0)) * 2);
+    uint32_t bstep = (uint32_t)(16 * b_pitch * 2), bnext = 32u; // next 16 k-rows; next 16 columns (second x4 load)
+    if (b_swizzled) {
+      int const unit = (n0 >> 3) + (NT >= 2 ? (mi >> 1) : 0); // 16-byte unit of the row; 8 per box; NT = 4: + 2 for the second load
+      uint32_t const rowpart = (uint32_t)((unit >> 3) * k * 128 + ((mi & 1) * 8 + rr) * 128);
+      baddr = b_base + rowpart + (uint32_t)(((unit & 7) ^ rr) << 4);
+      bnext = (uint32_t)((((unit + 2) & 7) ^ rr) << 4) - (uint32_t)(((unit & 7) ^ rr) << 4); // same box: n0 % 32 == 0
+      bstep = 16u * 128u;
+    }
 #pragma unroll 2
-    for (int k0 = 0; k0 < k; k0 += 16, baddr += (uint32_t)(16 * b_pitch * 2), aaddr += 32u) {
+    for (int k0 = 0; k0 < k; k0 += 16, baddr += bstep, aaddr += 32u) {
       uint32_t a[4];
       asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                    : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3]) : "r"(aaddr));
@@ -169,7 +191,7 @@ __device__ __noinline__ void matmul_mma(unsigned char const *staged, unsigned ch
         for (int h = 0; h < NT / 2; h++) {
           uint32_t bf[4];
           asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
-                       : "=r"(bf[0]), "=r"(bf[1]), "=r"(bf[2]), "=r"(bf[3]) : "r"(baddr + (uint32_t)(h * 32)));
+                       : "=r"(bf[0]), "=r"(bf[1]), "=r"(bf[2]), "=r"(bf[3]) : "r"(baddr + (uint32_t)h * bnext));
           mma16816<T>(acc[2 * h], a, bf[0], bf[1]);
           mma16816<T>(acc[2 * h + 1], a, bf[2], bf[3]);
         }
@@ -204,15 +226,30 @@ __device__ __noinline__ void matmul_mma(unsigned char const *staged, unsigned ch
 
 template <typename T>
 __global__ void __launch_bounds__(1024) float_interp_kernel(const __grid_constant__ mgd_program prog,
-                                                           const __grid_constant__ mgd_bindings bind) {
-  extern __shared__ __align__(16) unsigned char smem_b[];
-  int const tid = threadIdx.x, nt = blockDim.x;
+                                                           const __grid_constant__ mgd_bindings bind,
+                                                           const __grid_constant__ interp::TmaPlan tma,
+                                                           const __grid_constant__ interp::TmaMaps maps, int32_t *status) {
+  extern __shared__ __align__(16) unsigned char smem_dyn[];
+  // swizzled boxes want their 1024-byte pattern aligned: the plan's offsets are relative to an aligned base
+  // (the host leaves room for that only when a tensor-map form is in use)
+  unsigned char *smem_b = (tma.tiled_mask | tma.swizzled_mask)
+                              ? reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023)
+                              : smem_dyn;
+  __shared__ uint64_t bars[interp::kMaxStages + 1]; // [0 .. stages) ring stages, [kMaxStages] tiles fetched once
+  int const tid = threadIdx.x, nt = blockDim.x, lane = tid & 31, warp = tid >> 5;
   int const gx = prog.grid[0], gy = prog.grid[1], gz = prog.grid[2];
   int64_t b = blockIdx.x;
   int const bx = (int)(b % gx), by = (int)((b / gx) % gy), bz = (int)((b / ((int64_t)gx * gy)) % gz);
   int64_t const set = b / ((int64_t)gx * gy * gz);
-  auto tile = [&](int byte_offset) { return smem_b + byte_offset; };
-  auto ftile = [&](int byte_offset) { return reinterpret_cast<float *>(smem_b + byte_offset); };
+  int const last = prog.forloop_range - 1;
+  // a tile of the ring lives in stage (iteration % stages); every other tile at its planned place
+  int stage_offset = 0;
+  auto tile = [&](int byte_offset) {
+    int const extra = (unsigned)(byte_offset - tma.ring_lo) < (unsigned)tma.ring_bytes ? stage_offset : 0;
+    return smem_b + byte_offset + extra;
+  };
+  auto ftile = [&](int byte_offset) { return reinterpret_cast<float *>(smem_b + byte_offset); }; // fp32 tiles are never in the ring
+  uint32_t const tma_mask = tma.moving_mask | tma.once_mask;
   // The operator table and the bindings are read with computed indices all the time; out of the kernel parameters
   // such a read costs tens of cycles each (about 1200 cycles of address set-up per operator were measured), out of
   // shared memory a few.  The host puts the copy behind the tiles (prog.smem_bytes = its offset).
@@ -223,23 +260,86 @@ __global__ void __launch_bounds__(1024) float_interp_kernel(const __grid_constan
     int const op_words = prog.num_ops * (int)(sizeof(mgd_op) / 4), bind_words = (int)(sizeof(mgd_bindings) / 4);
     for (int i = tid; i < op_words; i += nt) dst[i] = reinterpret_cast<int32_t const *>(prog.ops)[i];
     for (int i = tid; i < bind_words; i += nt) dst[op_words + i] = reinterpret_cast<int32_t const *>(&bind)[i];
+    if (tid == 0) {
+      for (int s = 0; s <= interp::kMaxStages; s++) ptx::mbar_init(ptx::smem_u32(&bars[s]), 1);
+      ptx::mbar_init_fence();
+    }
     __syncthreads();
+  }
+  // Row copies of every input in `mask` for iteration `it`, into ring stage `stage` (ignored for the once-tiles),
+  // completing on `bar`; called by warp 0.  Only 16-bit tiles of row-major tensors are in these masks.
+  auto issue = [&](uint32_t mask, int it, int stage, uint32_t bar, int tx) {
+    if (lane == 0) ptx::mbar_expect_tx(bar, (uint32_t)tx);
+    __syncwarp();
+    for (int oi = 0; oi < prog.num_ops; oi++) {
+      if (!((mask >> oi) & 1u)) continue;
+      int32_t const *a = ops[oi].a;
+      int row = bx * a[0] + by * a[1] + bz * a[2] + it * a[6];
+      int col = bx * a[3] + by * a[4] + bz * a[5] + it * a[7];
+      int64_t lead = (int64_t)bx * a[8] + (int64_t)by * a[9] + (int64_t)bz * a[10] + (int64_t)it * a[11];
+      int const in_ring = (unsigned)(a[17] - tma.ring_lo) < (unsigned)tma.ring_bytes;
+      uint32_t dst = ptx::smem_u32(smem_b + a[17] + (in_ring ? stage * tma.ring_bytes : 0));
+      int const form = ((tma.swizzled_mask >> oi) & 1u) ? 2 : (int)((tma.tiled_mask >> oi) & 1u);
+      if (form) {
+        int const z = (int)((set * bnd.in_set_stride[a[18]] + lead) / ((int64_t)a[12] * a[13]));
+        interp::issue_tile_boxes(dst, &maps.m[a[18]], form, a[14], a[15], col, row, z, bar, lane);
+      } else {
+        uint16_t const *first = static_cast<uint16_t const *>(bnd.in[a[18]]) + set * bnd.in_set_stride[a[18]] + lead +
+                                (size_t)row * a[13] + col;
+        interp::issue_tile_rows(dst, first, a[14], a[15], a[15] + ((a[16] >> kInPadShift) & 0xff), a[13], bar, lane);
+      }
+    }
+  };
+  int issued = 0; // iterations whose ring tiles have been requested
+  if (warp == 0) {
+    if (tma.once_mask) issue(tma.once_mask, 0, 0, ptx::smem_u32(&bars[interp::kMaxStages]), tma.once_tx);
+    if (tma.stages > 0)
+      for (; issued < tma.stages && issued <= last; issued++)
+        issue(tma.moving_mask, issued, issued, ptx::smem_u32(&bars[issued]), tma.moving_tx);
+  }
+  // Bounded waits: when one runs out the block records it, waits (bounded again) for the copies still in flight so
+  // that none lands in shared memory of a later block, and returns.
+  auto give_up = [&]() {
+    if (tid == 0) {
+      atomicExch(status, 3);
+      if (tma.once_mask) ptx::mbar_wait(ptx::smem_u32(&bars[interp::kMaxStages]), 0);
+      for (int s = 0; s < tma.stages && s < issued; s++) {
+        int const loads = (issued - s + tma.stages - 1) / tma.stages;
+        ptx::mbar_wait(ptx::smem_u32(&bars[s]), (uint32_t)((loads - 1) & 1));
+      }
+    }
+  };
+  if (tma.once_mask) {
+    bool ok = ptx::mbar_wait(ptx::smem_u32(&bars[interp::kMaxStages]), 0);
+    if (!__syncthreads_and(ok)) { give_up(); return; }
   }
 
 #ifdef MG_FI_TIMING // cycles per operator (with its barrier), printed by one thread of block 0
   long long op_cycles[MGD_MAX_OPS] = {};
   long long ld_setup = 0, ld_copy = 0;
 #endif
-  for (int it = 0; it < prog.forloop_range; it++) {
+  for (int it = 0; it <= last; it++) {
+    if (tma.stages > 0) {
+      int const s = it % tma.stages;
+      stage_offset = s * tma.ring_bytes;
+      bool ok = ptx::mbar_wait(ptx::smem_u32(&bars[s]), (uint32_t)((it / tma.stages) & 1));
+      if (!__syncthreads_and(ok)) { give_up(); return; }
+    }
     for (int oi = 0; oi < prog.num_ops; oi++) {
       mgd_op const &op = ops[oi];
       int32_t const *a = op.a;
+      if (op.type == interp::kOpInput) {
+        if ((tma_mask >> oi) & 1u) continue;                              // fetched by the TMA engine
+        if (it > 0 && ((tma.plain_once_mask >> oi) & 1u)) continue;       // same tile as in the first iteration
+      } else if (a[interp::kPhaseSlot] != 0 && it != last) {
+        continue;                                                         // runs once, after the loop
+      }
+      bool const first = it == 0 || (op.type != interp::kOpInput && a[interp::kPhaseSlot] != 0);
 #ifdef MG_FI_TIMING
       long long const op_t0 = clock64();
 #endif
       switch (op.type) {
         case 2001: {
-          if ((a[16] & kInInvariant) && it > 0) break; // uniform over the block
           int row = bx * a[0] + by * a[1] + bz * a[2] + it * a[6];
           int col = bx * a[3] + by * a[4] + bz * a[5] + it * a[7];
           int64_t lead = (int64_t)bx * a[8] + (int64_t)by * a[9] + (int64_t)bz * a[10] + (int64_t)it * a[11];
@@ -275,7 +375,7 @@ __global__ void __launch_bounds__(1024) float_interp_kernel(const __grid_constan
 #endif
               // the tile of the next iteration: one prefetch per 128-byte line, so that its loads find it in L1
               // instead of paying an L2 round trip between two barriers
-              if (it + 1 < prog.forloop_range && !(a[16] & kInInvariant)) {
+              if (it + 1 < prog.forloop_range && !((tma.plain_once_mask >> oi) & 1u)) {
                 T const *next = first + (size_t)a[6] * ld + a[7] + a[11];
                 int const lines = (cols * (int)sizeof(T) + 127) >> 7;
                 for (int i = tid; i < rows * lines; i += nt) {
@@ -298,15 +398,24 @@ __global__ void __launch_bounds__(1024) float_interp_kernel(const __grid_constan
           int m = a[0], n = a[1], k = a[2];
           unsigned char const *A = tile(a[3]), *B = tile(a[4]);
           float *C = ftile(a[5]);
-          bool const add = a[8] != 0 && it > 0;
+          bool const add = a[8] != 0 && !first;
           if (a[10] > 0) { // host-planned staging room: B in 16 bits, n % 8 == 0, k % 16 == 0 -> tensor cores
             unsigned char *staged = smem_b + a[10];
             stage_a<T>(A, a[6] != 0, staged, m, k, tid, nt);
             __syncthreads();
             int const bp = a[9] > 0 ? a[9] : n;
             // the wide warp patch when it still gives every warp one
-            if ((n & 31) == 0 && ((m + 15) >> 4) * (n >> 5) >= (nt >> 5)) matmul_mma<T, 4>(staged, B, C, m, n, k, bp, add, tid, nt);
-            else matmul_mma<T, 1>(staged, B, C, m, n, k, bp, add, tid, nt);
+            bool const wide = (n & 31) == 0 && ((m + 15) >> 4) * (n >> 5) >= (nt >> 5);
+            bool const swz = a[11] != 0;
+            if (wide) matmul_mma<T, 4>(staged, B, C, m, n, k, bp, swz, add, tid, nt);
+            else matmul_mma<T, 1>(staged, B, C, m, n, k, bp, swz, add, tid, nt);
+            if (a[interp::kPhaseSlot] != 0 && a[6] == 0) { // taken once on an fp32 sum: add the rounding residual's product
+              __syncthreads();
+              stage_a<T>(A, false, staged, m, k, tid, nt, true);
+              __syncthreads();
+              if (wide) matmul_mma<T, 4>(staged, B, C, m, n, k, bp, swz, true, tid, nt);
+              else matmul_mma<T, 1>(staged, B, C, m, n, k, bp, swz, true, tid, nt);
+            }
           } else {
             matmul_tiles<T>(A, B, C, m, n, k, a[6] != 0, a[7] != 0, add, tid, nt);
           }
@@ -366,13 +475,24 @@ __global__ void __launch_bounds__(1024) float_interp_kernel(const __grid_constan
           }
           break;
         }
+        case interp::kOpAccumulate: { // running sum of a tile over the for-loop (the hoisted matmul's left operand)
+          unsigned char const *x = tile(a[1]);
+          bool const x16 = a[3] != 0;
+          float *acc = ftile(a[2]);
+          if (first) {
+            for (int i = tid; i < a[0]; i += nt) acc[i] = rd<T>(x, x16, i);
+          } else {
+            for (int i = tid; i < a[0]; i += nt) acc[i] += rd<T>(x, x16, i);
+          }
+          break;
+        }
         case 2002: {
           int n = a[11] * a[12];
           float *acc = ftile(a[14]);
           if (!a[17]) { // a[17]: the producing matmul already added into the accumulator
             unsigned char const *x = tile(a[13]);
             bool const x16 = a[16] != 0;
-            if (it == 0) {
+            if (first) {
               for (int i = tid; i < n; i += nt) acc[i] = rd<T>(x, x16, i);
             } else {
               for (int i = tid; i < n; i += nt) acc[i] += rd<T>(x, x16, i);
@@ -391,11 +511,17 @@ __global__ void __launch_bounds__(1024) float_interp_kernel(const __grid_constan
         }
         default: break;
       }
-      // consecutive input loaders write different tiles and read none: their memory latencies may overlap
-      if (!(op.type == 2001 && oi + 1 < prog.num_ops && ops[oi + 1].type == 2001)) __syncthreads();
+      __syncthreads();
 #ifdef MG_FI_TIMING
       op_cycles[oi] += clock64() - op_t0;
 #endif
+    }
+    // every thread is past its last read of this iteration's stage: request the tiles of iteration it + stages into it
+    if (warp == 0 && tma.stages > 0 && issued <= last) {
+      ptx::fence_proxy_async_smem();
+      int const s = it % tma.stages;
+      issue(tma.moving_mask, issued, s, ptx::smem_u32(&bars[s]), tma.moving_tx);
+      issued++;
     }
   }
 #ifdef MG_FI_TIMING
@@ -418,12 +544,21 @@ struct TileUse {
   int offset;     // byte offset in this kernel's plan
   int rows, cols; // shape the loader writes (loaded tiles)
   int pad;        // extra elements per row: a 16-bit matmul B operand whose dense pitch conflicts in ldmatrix
+  bool ring;      // refilled by the TMA engine every iteration: lives in the multi-stage ring
+  bool swizzled;  // stored as 64-column boxes with the 128-byte swizzle (instead of padded rows)
+  bool boxed;     // fetched as one dense tensor-map box
   bool is16() const { return loaded && !computed; }
   size_t bytes() const { return pad ? (size_t)rows * (cols + pad) * 2 : (size_t)elems * (is16() ? 2 : 4); }
+  // a tensor-map box must land on a 128-byte boundary; the swizzle pattern repeats every 1024 bytes
+  size_t alignment() const { return swizzled ? 1024 : (boxed ? 128 : 16); }
+  size_t room() const { return (bytes() + alignment() - 1) & ~(alignment() - 1); }
+  size_t place(size_t at) const { return (at + alignment() - 1) & ~(alignment() - 1); }
 };
 
 struct Replanned {
   mgd_program prog;
+  interp::TmaPlan tma;
+  interp::TmaMaps maps;
   size_t smem_bytes;
 };
 
@@ -439,7 +574,7 @@ struct TileTable {
     int i = find(planned);
     if (i < 0) {
       i = n++;
-      t[i] = TileUse{planned, elems, false, false, false, 0, 0, 0, 0};
+      t[i] = TileUse{planned, elems, false, false, false, 0, 0, 0, 0, false, false, false};
     } else if (elems > t[i].elems) {
       t[i].elems = elems;
     }
@@ -447,39 +582,16 @@ struct TileTable {
   }
 };
 
-bool is_reduction(int type) { return type >= MG_TB_REDUCTION_0_OP && type <= MG_TB_REDUCTION_2_TO_DIMX_OP; }
-bool is_concat(int type) { return type == MG_TB_CONCAT_0_OP || type == MG_TB_CONCAT_1_OP || type == MG_TB_CONCAT_2_OP; }
-bool is_binary(int type) { return type == MG_TB_DIV_OP || type == MG_TB_ADD_OP || type == MG_TB_MUL_OP; }
+using interp::is_binary;
+using interp::is_concat;
+using interp::is_reduction;
+using interp::reads_of;
+using interp::written_by;
 
-// number of operand reads of tile `planned` by operator `op` (an in-place exp counts as a read)
-int reads_of(mgd_op const &op, int planned) {
-  int32_t const *a = op.a;
-  int n = 0;
-  if (op.type == MG_TB_MATMUL_OP) n = (a[3] == planned) + (a[4] == planned);
-  else if (op.type == MG_TB_EXP_OP) n = a[0] == planned;
-  else if (is_binary(op.type)) n = (a[6] == planned) + (a[7] == planned);
-  else if (is_reduction(op.type)) n = a[3] == planned;
-  else if (is_concat(op.type)) n = (a[4] == planned) + (a[5] == planned);
-  else if (op.type == 2002) n = a[13] == planned;
-  return n;
-}
-
-// tile written by `op`, or -1
-int written_by(mgd_op const &op) {
-  int32_t const *a = op.a;
-  if (op.type == 2001) return a[17];
-  if (op.type == MG_TB_MATMUL_OP) return a[5];
-  if (op.type == MG_TB_EXP_OP) return a[0];
-  if (is_binary(op.type)) return a[8];
-  if (is_reduction(op.type)) return a[4];
-  if (is_concat(op.type)) return a[6];
-  if (op.type == 2002) return a[14];
-  return -1;
-}
-
-void replan(mgd_program const &in, Replanned *out) {
+void replan(mgd_program const &in, mgd_bindings const *bind, Replanned *out) {
   TileTable tt;
   out->prog = in;
+  std::memset(&out->tma, 0, sizeof(out->tma));
   mgd_program &p = out->prog;
   // pass 1: every tile with its size and who writes it
   for (int i = 0; i < in.num_ops; i++) {
@@ -509,6 +621,9 @@ void replan(mgd_program const &in, Replanned *out) {
       tt.touch(a[4], along > 0 ? a[0] / along * a[1] : 0);
       tt.touch(a[5], along > 0 ? a[0] / along * a[2] : 0);
       tt.t[tt.touch(a[6], a[0])].computed = true;
+    } else if (op.type == interp::kOpAccumulate) {
+      tt.touch(a[1], a[0]);
+      tt.t[tt.touch(a[2], a[0])].computed = true;
     } else if (op.type == 2002) {
       tt.touch(a[13], a[11] * a[12]);
       tt.t[tt.touch(a[14], a[11] * a[12])].computed = true;
@@ -560,18 +675,87 @@ void replan(mgd_program const &in, Replanned *out) {
   size_t const table = (size_t)in.num_ops * sizeof(mgd_op) + sizeof(mgd_bindings) + 32;
   size_t at = 0;
   int staging_offset = 0;
+  interp::TmaPlan &tma = out->tma;
   for (int pass = 0; pass < 2; pass++) {
-    at = 0;
+    // Which inputs the TMA engine fetches (needs the row pitches of this pass): 16-bit tiles of row-major tensors
+    // whose rows are 16-byte aligned; the ones that move with the for-loop go through the ring.
+    std::memset(&tma, 0, sizeof(tma));
+    std::memset(&out->maps, 0, sizeof(out->maps));
+    for (int i = 0; i < tt.n; i++) {
+      tt.t[i].ring = false;
+      tt.t[i].swizzled = tt.t[i].boxed = false; // a second pass starts over
+    }
+    for (int i = 0; i < in.num_ops; i++) {
+      mgd_op const &op = in.ops[i];
+      if (op.type != 2001) continue;
+      TileUse &t = tt.t[tt.find(op.a[17])];
+      int writers = 0;
+      for (int j = 0; j < in.num_ops; j++) writers += written_by(in.ops[j]) == t.planned;
+      bool const invariant = t.is16() && !interp::input_moves(op) && writers == 1;
+      int const slot = op.a[18];
+      bool const eligible = bind != nullptr && t.is16() && writers == 1 && t.elems == t.rows * t.cols &&
+                            interp::tma_eligible(op, bind->in[slot], bind->in_set_stride[slot], bind->num_sets, t.cols + t.pad, true);
+      if (eligible) {
+        int form = interp::tiled_form(op, bind->in_set_stride[slot], bind->num_sets, t.pad > 0);
+        if (form && !interp::make_tile_map(&out->maps.m[slot], bind->in[slot], (uint64_t)op.a[13], (uint64_t)op.a[12],
+                                           interp::matrices_addressed(in, op, bind->in_set_stride[slot], bind->num_sets),
+                                           form == 2 ? 64u : (uint32_t)t.cols, (uint32_t)t.rows, form == 2))
+          form = 0;
+        if (form == 2) {
+          tma.swizzled_mask |= 1u << i;
+          t.swizzled = true;
+          t.pad = 0;
+        } else if (form == 1) {
+          tma.tiled_mask |= 1u << i;
+          t.boxed = true;
+        }
+      }
+      if (eligible && (invariant || in.forloop_range == 1)) {
+        tma.once_mask |= 1u << i;
+        tma.once_tx += t.rows * t.cols * 2;
+      } else if (eligible) {
+        tma.moving_mask |= 1u << i;
+        tma.moving_tx += t.rows * t.cols * 2;
+        t.ring = true;
+      } else if (invariant) {
+        tma.plain_once_mask |= 1u << i;
+      }
+    }
+    size_t ring_bytes = 0, rest_bytes = 0;
     for (int i = 0; i < tt.n; i++) {
       if (tt.t[i].dropped) continue;
-      tt.t[i].offset = (int)at;
-      at += (tt.t[i].bytes() + 15) & ~(size_t)15;
+      if (tt.t[i].ring) ring_bytes = tt.t[i].place(ring_bytes) + tt.t[i].room();
+      else rest_bytes += tt.t[i].room() + (tt.t[i].alignment() > 16 ? tt.t[i].alignment() : 0);
     }
-    if (staging > 0 && at + staging + table <= (size_t)kSmemLimit) {
+    ring_bytes = (ring_bytes + 1023) & ~(size_t)1023;
+    int stages = 0;
+    if (ring_bytes > 0) {
+      stages = in.forloop_range < 3 ? in.forloop_range : 3;
+      while (stages > 1 && ring_bytes * stages + rest_bytes + staging + table + 1024 > (size_t)interp::kDynSmemLimit) stages--;
+    }
+    tma.stages = stages;
+    tma.ring_lo = 0;
+    tma.ring_bytes = (int32_t)ring_bytes;
+    at = 0;
+    for (int i = 0; i < tt.n; i++) { // the ring first
+      if (tt.t[i].dropped || !tt.t[i].ring) continue;
+      at = tt.t[i].place(at);
+      tt.t[i].offset = (int)at;
+      at += tt.t[i].room();
+    }
+    at = ring_bytes * (size_t)stages;
+    for (int i = 0; i < tt.n; i++) {
+      if (tt.t[i].dropped || tt.t[i].ring) continue;
+      at = tt.t[i].place(at);
+      tt.t[i].offset = (int)at;
+      at += tt.t[i].room();
+    }
+    if (staging > 0 && at + staging + table + 1024 <= (size_t)interp::kDynSmemLimit) {
       staging_offset = (int)at;
       at += staging;
       break;
     }
+    if (staging == 0) break;
     // no room for the staging area: those matmuls run on the CUDA cores, which read B densely
     for (int i = 0; i < tt.n; i++) tt.t[i].pad = 0;
   }
@@ -579,7 +763,7 @@ void replan(mgd_program const &in, Replanned *out) {
   at = (at + 15) & ~(size_t)15;
   p.smem_bytes = (int32_t)at;
   at += (size_t)in.num_ops * sizeof(mgd_op) + sizeof(mgd_bindings);
-  out->smem_bytes = at + 16;
+  out->smem_bytes = at + 16 + ((out->tma.tiled_mask | out->tma.swizzled_mask) ? 1024 : 0); // + room to align the base
   // pass 4: rewrite operands
   auto off = [&](int planned) { return tt.t[tt.find(planned)].offset; };
   auto is16 = [&](int planned) { return tt.t[tt.find(planned)].is16() ? 1 : 0; };
@@ -590,14 +774,13 @@ void replan(mgd_program const &in, Replanned *out) {
     if (type == 2001) {
       w[17] = off(a[17]);
       w[16] = (a[16] & 0xff) | (is16(a[17]) ? kIn16 : 0) | (tt.t[tt.find(a[17])].pad << kInPadShift);
-      // no for-loop stride and nothing overwrites the tile: the first iteration's copy stays valid
-      if (is16(a[17]) && a[6] == 0 && a[7] == 0 && a[11] == 0) w[16] |= kInInvariant;
     } else if (type == MG_TB_MATMUL_OP) {
       w[3] = off(a[3]); w[4] = off(a[4]);
       w[6] = is16(a[3]); w[7] = is16(a[4]);
       w[8] = 0;
       w[9] = tt.t[tt.find(a[4])].pad ? a[1] + tt.t[tt.find(a[4])].pad : 0; // row pitch of B when it is padded
       w[10] = (is16(a[4]) && (a[1] & 7) == 0 && (a[2] & 15) == 0) ? staging_offset : 0;
+      w[11] = tt.t[tt.find(a[4])].swizzled ? 1 : 0;
       w[5] = tt.t[tt.find(a[5])].dropped ? -1 : off(a[5]);
     } else if (type == MG_TB_EXP_OP) {
       w[0] = off(a[0]);
@@ -610,6 +793,9 @@ void replan(mgd_program const &in, Replanned *out) {
     } else if (is_concat(type)) {
       w[4] = off(a[4]); w[5] = off(a[5]); w[6] = off(a[6]);
       w[7] = is16(a[4]); w[8] = is16(a[5]);
+    } else if (type == interp::kOpAccumulate) {
+      w[1] = off(a[1]); w[2] = off(a[2]);
+      w[3] = is16(a[1]);
     } else if (type == 2002) {
       w[14] = off(a[14]);
       w[17] = fused_matmul[i] >= 0 ? 1 : 0;
@@ -631,19 +817,30 @@ extern "C" int mgd_float_interp_smem(const mgd_program *prog, size_t *bytes, int
   if (!prog || !bytes || !fits) return set_error(MG_ERR_INVALID_ARGUMENT, "null pointer");
   if (prog->num_ops <= 0 || prog->num_ops > MGD_MAX_OPS) return set_error(MG_ERR_INVALID_ARGUMENT, "operator count out of range");
   Replanned r;
-  replan(*prog, &r);
+  mgd_program rewritten = *prog;
+  interp::hoist_invariant_products(rewritten);
+  replan(rewritten, nullptr, &r);
+  if (r.smem_bytes > (size_t)interp::kDynSmemLimit) replan(*prog, nullptr, &r);
   *bytes = r.smem_bytes;
-  *fits = *bytes <= (size_t)kSmemLimit;
+  *fits = *bytes <= (size_t)interp::kDynSmemLimit;
   return MG_OK;
 }
 
 extern "C" int mgd_launch_float_interp(const mgd_program *prog, const mgd_bindings *bind, int32_t dt, void *stream) {
   int st = validate_program(prog, bind);
   if (st != MG_OK) return st;
+  // Rewrite (hoisted products), then plan with the TMA ring; step back to the plain program and plain loads when
+  // that does not fit.
   Replanned r;
-  replan(*prog, &r);
+  mgd_program rewritten = *prog;
+  interp::hoist_invariant_products(rewritten);
+  replan(rewritten, bind, &r);
+  if (r.smem_bytes > (size_t)interp::kDynSmemLimit) replan(rewritten, nullptr, &r);
+  if (r.smem_bytes > (size_t)interp::kDynSmemLimit) replan(*prog, nullptr, &r);
   size_t smem = r.smem_bytes;
-  if (smem > (size_t)kSmemLimit)
+  int32_t *status = device_error_word();
+  if (!status) return set_error(MG_ERR_CUDA, "cannot allocate the device status word");
+  if (smem > (size_t)interp::kDynSmemLimit)
     return set_error(MG_ERR_UNSUPPORTED,
                      "the generic float interpreter keeps computed tiles in fp32 and this graph needs more than 227 KB "
                      "that way; only graphs matched by a specialised kernel can run at this size");
@@ -654,12 +851,15 @@ extern "C" int mgd_launch_float_interp(const mgd_program *prog, const mgd_bindin
   // set-up code more often (32 warps share four schedulers), so loaders and tensor-core matmuls, which need few
   // warps, ask for less: the matmul chain of 16 x 64 x 1024 tiles ran 129 us on 512 threads, 144 on 1024, 148 on 256.
   int64_t largest = 0;
-  for (int i = 0; i < prog->num_ops; i++) {
-    int32_t const *a = prog->ops[i].a;
+  for (int i = 0; i < r.prog.num_ops; i++) {
+    int32_t const *a = r.prog.ops[i].a;
     int64_t work = 0;
-    switch (prog->ops[i].type) {
-      case 2001: work = (int64_t)a[14] * a[15] / 16; break;
-      case 2002: work = (int64_t)a[11] * a[12] / (r.prog.ops[i].a[17] ? 4 : 1); break; // fused: stores once, at the end
+    switch (r.prog.ops[i].type) {
+      case 2001: // plain loads; nothing for the threads to do when the TMA engine fetches the tile
+        work = ((r.tma.moving_mask | r.tma.once_mask) >> i) & 1u ? 0 : (int64_t)a[14] * a[15] / 16;
+        break;
+      case interp::kOpAccumulate: work = a[0]; break;
+      case 2002: work = (int64_t)a[11] * a[12] / ((a[17] || a[interp::kPhaseSlot]) ? 4 : 1); break; // stores once, at the end
       case MG_TB_MATMUL_OP:
         work = r.prog.ops[i].a[10] > 0 ? (int64_t)((a[0] + 15) / 16) * a[1] * 4 : (int64_t)a[0] * a[1] / 4;
         break;
@@ -674,18 +874,18 @@ extern "C" int mgd_launch_float_interp(const mgd_program *prog, const mgd_bindin
   static bool configured_h = false, configured_b = false;
   if (dt == MG_DT_FLOAT16) {
     if (smem > 48 * 1024 && !configured_h) {
-      if (cudaFuncSetAttribute(float_interp_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess)
+      if (cudaFuncSetAttribute(float_interp_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, interp::kDynSmemLimit) != cudaSuccess)
         return check_launch("cudaFuncSetAttribute(float_interp_kernel)");
       configured_h = true;
     }
-    float_interp_kernel<__half><<<(unsigned)blocks, threads, smem, (cudaStream_t)stream>>>(r.prog, *bind);
+    float_interp_kernel<__half><<<(unsigned)blocks, threads, smem, (cudaStream_t)stream>>>(r.prog, *bind, r.tma, r.maps, status);
   } else if (dt == MG_DT_BFLOAT16) {
     if (smem > 48 * 1024 && !configured_b) {
-      if (cudaFuncSetAttribute(float_interp_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess)
+      if (cudaFuncSetAttribute(float_interp_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, interp::kDynSmemLimit) != cudaSuccess)
         return check_launch("cudaFuncSetAttribute(float_interp_kernel)");
       configured_b = true;
     }
-    float_interp_kernel<__nv_bfloat16><<<(unsigned)blocks, threads, smem, (cudaStream_t)stream>>>(r.prog, *bind);
+    float_interp_kernel<__nv_bfloat16><<<(unsigned)blocks, threads, smem, (cudaStream_t)stream>>>(r.prog, *bind, r.tma, r.maps, status);
   } else {
     return set_error(MG_ERR_UNSUPPORTED, "float mode runs on fp16 or bf16 tensors");
   }

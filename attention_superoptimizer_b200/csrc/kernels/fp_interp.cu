@@ -9,11 +9,16 @@
 //   * matmul runs on the integer tensor cores where the shape allows (matmul_fp_tensor), else keeps an exact
 //     64-bit sum of products; either way one reduction modulo PQ per output instead of one after every
 //     multiply-add (same residue, valid for any uint16 operands);
-//   * tiles whose rows are 16-byte aligned are loaded with 128-bit accesses;
+//   * input tiles are fetched by the TMA engine into a multi-stage ring along the for-loop (interp_common.cuh);
+//     tiles whose rows are not 16-byte aligned fall back to plain (128-bit where possible) loads;
+//   * a matmul by a loop-invariant tile whose result is only summed over the for-loop is taken once, after the loop,
+//     on the sum of its left operands (interp_common.cuh: same residues);
 //   * lookup tables live in constant memory;
 //   * shared-memory tiles keep the planned offsets, so the aliasing of the in-place exp is the same.
 #include "common.cuh"
+#include "interp_common.cuh"
 #include <cstdlib>
+#include <cstring>
 
 namespace mgk {
 
@@ -45,8 +50,9 @@ __device__ __forceinline__ void load_tile_u16(uint16_t *dst, uint16_t const *src
 //     A B = LL + 256 (LH + HL) + 65536 HH        reduced modulo PQ once per output.
 // Same residue as the reference's multiply-add loop (TBMatmulFingerprinter, threadblock/cuda/matmul.h:773-804).
 // Needs k % 16 == 0 and n % 16 == 0 (ldmatrix rows of 16 bytes); a warp owns 4 rows x 16 columns of C at a time.
+// `b_swizzled`: B sits as 64-column boxes of k rows x 128 bytes with the 128-byte swizzle, as the TMA engine wrote it.
 __device__ __forceinline__ void matmul_fp_tensor(uint16_t const *A, uint16_t const *B, uint16_t *C, int m, int n, int k,
-                                                 int b_pitch, int tid, int nthreads) {
+                                                 int b_pitch, bool b_swizzled, int tid, int nthreads) {
   int const lane = tid & 31, warp = tid >> 5, nwarps = nthreads >> 5;
   int const g = lane >> 2, t = lane & 3, mi = lane >> 3, rr = lane & 7;
   int const row_groups = (m + 3) >> 2, col_pairs = n >> 4;
@@ -59,7 +65,13 @@ __device__ __forceinline__ void matmul_fp_tensor(uint16_t const *A, uint16_t con
     uint16_t const *arow = A + (size_t)row * k + 2 * t;
     // ldmatrix (transposed): this lane addresses k-row (mi % 2) * 8 + rr of the 8 columns starting at (mi / 2) * 8
     uint32_t baddr = b_base + (uint32_t)((((mi & 1) * 8 + rr) * b_pitch + cp * 16 + (mi >> 1) * 8) * 2);
-    for (int k0 = 0; k0 < k; k0 += 16, baddr += (uint32_t)(16 * b_pitch * 2)) {
+    uint32_t bstep = (uint32_t)(16 * b_pitch * 2);
+    if (b_swizzled) {
+      int const unit = cp * 2 + (mi >> 1); // 16-byte unit of the row: 8 per box
+      baddr = b_base + (uint32_t)((unit >> 3) * k * 128 + ((mi & 1) * 8 + rr) * 128 + (((unit & 7) ^ rr) << 4));
+      bstep = 16u * 128u;
+    }
+    for (int k0 = 0; k0 < k; k0 += 16, baddr += bstep) {
       uint32_t const w0 = valid ? *reinterpret_cast<uint32_t const *>(arow + k0) : 0u;
       uint32_t const w1 = valid ? *reinterpret_cast<uint32_t const *>(arow + k0 + 8) : 0u;
       uint32_t a[4], bf[4];
@@ -92,34 +104,102 @@ __device__ __forceinline__ void matmul_fp_tensor(uint16_t const *A, uint16_t con
 }
 
 __global__ void __launch_bounds__(1024) fp_interp_kernel(const __grid_constant__ mgd_program prog,
-                                                        const __grid_constant__ mgd_bindings bind) {
-  extern __shared__ __align__(16) unsigned char smem_raw[];
-  int const tid = threadIdx.x, nt = blockDim.x;
+                                                        const __grid_constant__ mgd_bindings bind,
+                                                        const __grid_constant__ interp::TmaPlan tma,
+                                                        const __grid_constant__ interp::TmaMaps maps, int32_t *status) {
+  extern __shared__ __align__(16) unsigned char smem_dyn[];
+  // swizzled boxes want their 1024-byte pattern aligned: the plan's offsets are relative to an aligned base
+  // (the host leaves room for that only when a tensor-map form is in use)
+  unsigned char *smem_raw = (tma.tiled_mask | tma.swizzled_mask)
+                                ? reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023)
+                                : smem_dyn;
+  __shared__ uint64_t bars[interp::kMaxStages + 1]; // [0 .. stages) ring stages, [kMaxStages] tiles fetched once
+  int const tid = threadIdx.x, nt = blockDim.x, lane = tid & 31, warp = tid >> 5;
   int const gx = prog.grid[0], gy = prog.grid[1], gz = prog.grid[2];
   int64_t b = blockIdx.x;
   int const bx = (int)(b % gx), by = (int)((b / gx) % gy), bz = (int)((b / ((int64_t)gx * gy)) % gz);
   int64_t const set = b / ((int64_t)gx * gy * gz);
-  auto tile = [&](int byte_offset) { return reinterpret_cast<uint16_t *>(smem_raw + byte_offset); };
+  int const last = prog.forloop_range - 1;
+  // a tile of the ring lives in stage (iteration % stages); every other tile at its planned place
+  int stage_offset = 0;
+  auto tile = [&](int byte_offset) {
+    int const extra = (unsigned)(byte_offset - tma.ring_lo) < (unsigned)tma.ring_bytes ? stage_offset : 0;
+    return reinterpret_cast<uint16_t *>(smem_raw + byte_offset + extra);
+  };
+  uint32_t const tma_mask = tma.moving_mask | tma.once_mask;
 
-  // An input tile that does not move with the for-loop and that no in-place operator overwrites is the same in every
-  // iteration: it is loaded once (the reference reloads it; the values are identical).
-  uint32_t load_once = 0;
-  for (int oi = 0; oi < prog.num_ops; oi++) {
-    mgd_op const &op = prog.ops[oi];
-    if (op.type != 2001 || op.a[6] != 0 || op.a[7] != 0 || op.a[11] != 0) continue;
-    bool overwritten = false;
-    for (int oj = 0; oj < prog.num_ops; oj++)
-      if (prog.ops[oj].type == MG_TB_EXP_OP && prog.ops[oj].a[0] == op.a[17]) overwritten = true;
-    if (!overwritten) load_once |= 1u << oi;
+  if (tid == 0) {
+    for (int s = 0; s <= interp::kMaxStages; s++) ptx::mbar_init(ptx::smem_u32(&bars[s]), 1);
+    ptx::mbar_init_fence();
+  }
+  __syncthreads();
+  // Row copies of every input in `mask` for iteration `it`, into ring stage `stage` (ignored for the once-tiles),
+  // completing on `bar`; called by warp 0.
+  auto issue = [&](uint32_t mask, int it, int stage, uint32_t bar, int tx) {
+    if (lane == 0) ptx::mbar_expect_tx(bar, (uint32_t)tx);
+    __syncwarp();
+    for (int oi = 0; oi < prog.num_ops; oi++) {
+      if (!((mask >> oi) & 1u)) continue;
+      int32_t const *a = prog.ops[oi].a;
+      int row = bx * a[0] + by * a[1] + bz * a[2] + it * a[6];
+      int col = bx * a[3] + by * a[4] + bz * a[5] + it * a[7];
+      int64_t lead = (int64_t)bx * a[8] + (int64_t)by * a[9] + (int64_t)bz * a[10] + (int64_t)it * a[11];
+      int const in_ring = (unsigned)(a[17] - tma.ring_lo) < (unsigned)tma.ring_bytes;
+      uint32_t dst = ptx::smem_u32(smem_raw + a[17] + (in_ring ? stage * tma.ring_bytes : 0));
+      int const form = ((tma.swizzled_mask >> oi) & 1u) ? 2 : (int)((tma.tiled_mask >> oi) & 1u);
+      if (form) {
+        int const z = (int)((set * bind.in_set_stride[a[18]] + lead) / ((int64_t)a[12] * a[13]));
+        interp::issue_tile_boxes(dst, &maps.m[a[18]], form, a[14], a[15], col, row, z, bar, lane);
+      } else {
+        uint16_t const *first = static_cast<uint16_t const *>(bind.in[a[18]]) + set * bind.in_set_stride[a[18]] + lead +
+                                (size_t)row * a[13] + col;
+        interp::issue_tile_rows(dst, first, a[14], a[15], a[15] + ((a[16] >> 8) & 0xff), a[13], bar, lane);
+      }
+    }
+  };
+  int issued = 0; // iterations whose ring tiles have been requested
+  if (warp == 0) {
+    if (tma.once_mask) issue(tma.once_mask, 0, 0, ptx::smem_u32(&bars[interp::kMaxStages]), tma.once_tx);
+    if (tma.stages > 0)
+      for (; issued < tma.stages && issued <= last; issued++)
+        issue(tma.moving_mask, issued, issued, ptx::smem_u32(&bars[issued]), tma.moving_tx);
+  }
+  // Bounded waits: when one runs out the block records it, waits (bounded again) for the copies still in flight so
+  // that none lands in shared memory of a later block, and returns.
+  auto give_up = [&]() {
+    if (tid == 0) {
+      atomicExch(status, 3);
+      if (tma.once_mask) ptx::mbar_wait(ptx::smem_u32(&bars[interp::kMaxStages]), 0);
+      for (int s = 0; s < tma.stages && s < issued; s++) {
+        int const loads = (issued - s + tma.stages - 1) / tma.stages;
+        ptx::mbar_wait(ptx::smem_u32(&bars[s]), (uint32_t)((loads - 1) & 1));
+      }
+    }
+  };
+  if (tma.once_mask) {
+    bool ok = ptx::mbar_wait(ptx::smem_u32(&bars[interp::kMaxStages]), 0);
+    if (!__syncthreads_and(ok)) { give_up(); return; }
   }
 
-  for (int it = 0; it < prog.forloop_range; it++) {
+  for (int it = 0; it <= last; it++) {
+    if (tma.stages > 0) {
+      int const s = it % tma.stages;
+      stage_offset = s * tma.ring_bytes;
+      bool ok = ptx::mbar_wait(ptx::smem_u32(&bars[s]), (uint32_t)((it / tma.stages) & 1));
+      if (!__syncthreads_and(ok)) { give_up(); return; }
+    }
     for (int oi = 0; oi < prog.num_ops; oi++) {
       mgd_op const &op = prog.ops[oi];
       int32_t const *a = op.a;
+      if (op.type == interp::kOpInput) {
+        if ((tma_mask >> oi) & 1u) continue;                              // fetched by the TMA engine
+        if (it > 0 && ((tma.plain_once_mask >> oi) & 1u)) continue;       // same tile as in the first iteration
+      } else if (a[interp::kPhaseSlot] != 0 && it != last) {
+        continue;                                                         // runs once, after the loop
+      }
+      bool const first = it == 0 || (op.type != interp::kOpInput && a[interp::kPhaseSlot] != 0);
       switch (op.type) {
-        case 2001: { // input tile
-          if (it > 0 && ((load_once >> oi) & 1u)) break;
+        case interp::kOpInput: { // input tile on plain loads
           int row = bx * a[0] + by * a[1] + bz * a[2] + it * a[6];
           int col = bx * a[3] + by * a[4] + bz * a[5] + it * a[7];
           int64_t lead = (int64_t)bx * a[8] + (int64_t)by * a[9] + (int64_t)bz * a[10] + (int64_t)it * a[11];
@@ -135,7 +215,7 @@ __global__ void __launch_bounds__(1024) fp_interp_kernel(const __grid_constant__
           uint16_t *C = tile(a[5]);
           int const bp = a[6] > 0 ? a[6] : n; // row pitch of B: padded by the host when the dense pitch conflicts
           if ((k & 15) == 0 && (n & 15) == 0 && k <= 16384 && (nt & 31) == 0) {
-            matmul_fp_tensor(A, B, C, m, n, k, bp, tid, nt);
+            matmul_fp_tensor(A, B, C, m, n, k, bp, a[7] != 0, tid, nt);
             break;
           }
           for (int i = tid; i < m * n; i += nt) {
@@ -208,29 +288,54 @@ __global__ void __launch_bounds__(1024) fp_interp_kernel(const __grid_constant__
           }
           break;
         }
-        case 2002: { // output: accumulate over the for-loop, store after the last iteration
+        case interp::kOpAccumulate: { // running sum of a tile over the for-loop (the hoisted matmul's left operand)
+          uint16_t const *x = tile(a[1]);
+          uint16_t *acc = tile(a[2]);
+          if (first) {
+            for (int i = tid; i < a[0]; i += nt) acc[i] = (uint16_t)((uint32_t)x[i] % PQ);
+          } else {
+            for (int i = tid; i < a[0]; i += nt) acc[i] = (uint16_t)(((uint32_t)x[i] + (uint32_t)acc[i]) % PQ);
+          }
+          break;
+        }
+        case interp::kOpOutput: { // output: accumulate over the for-loop, store after the last iteration
           int n = a[11] * a[12];
           uint16_t const *x = tile(a[13]);
           uint16_t *acc = tile(a[14]);
-          if (it == 0) {
+          if (first) {
             for (int i = tid; i < n; i += nt) acc[i] = x[i];
           } else {
             for (int i = tid; i < n; i += nt) acc[i] = (uint16_t)(((uint32_t)x[i] + (uint32_t)acc[i]) % PQ);
           }
-          if (it == prog.forloop_range - 1) {
+          if (it == last) {
             __syncthreads();
             int row = bx * a[0] + by * a[1] + bz * a[2];
             int col = bx * a[3] + by * a[4] + bz * a[5];
             int64_t lead = (int64_t)bx * a[6] + (int64_t)by * a[7] + (int64_t)bz * a[8];
             uint16_t *dst = static_cast<uint16_t *>(bind.out[a[15]]) + set * bind.out_set_stride[a[15]] + lead;
             int cols = a[12], ld = a[10];
-            for (int i = tid; i < n; i += nt) dst[(size_t)(row + i / cols) * ld + col + i % cols] = acc[i];
+            if ((cols & 1) == 0 && (ld & 1) == 0 && (col & 1) == 0 && (reinterpret_cast<uintptr_t>(dst) & 3) == 0) {
+              for (int i = tid; i < n / 2; i += nt) { // two columns per store
+                int const e = 2 * i;
+                *reinterpret_cast<uint32_t *>(dst + (size_t)(row + e / cols) * ld + col + e % cols) =
+                    *reinterpret_cast<uint32_t const *>(acc + e);
+              }
+            } else {
+              for (int i = tid; i < n; i += nt) dst[(size_t)(row + i / cols) * ld + col + i % cols] = acc[i];
+            }
           }
           break;
         }
         default: break; // rejected on the host before launch
       }
       __syncthreads();
+    }
+    // every thread is past its last read of this iteration's stage: request the tiles of iteration it + stages into it
+    if (warp == 0 && tma.stages > 0 && issued <= last) {
+      ptx::fence_proxy_async_smem();
+      int const s = it % tma.stages;
+      issue(tma.moving_mask, issued, s, ptx::smem_u32(&bars[s]), tma.moving_tx);
+      issued++;
     }
   }
 }
@@ -255,20 +360,35 @@ int validate_program(mgd_program const *p, mgd_bindings const *b) {
   return MG_OK;
 }
 
-// ---- host: padded matmul operands ---------------------------------------------------------------------------------
-// ldmatrix reads 8 rows of 16 bytes of the B operand at a time; in the reference's dense plan a row pitch that is a
-// multiple of 128 bytes puts all 8 on the same banks.  A tile that only input loaders write and only matmuls read as
-// their B operand is therefore stored with 16 bytes of padding per row; every tile behind it moves up.  Tiles keep
-// their identity (planned offset), so the aliasing of the in-place exp is unchanged.
+// ---- host: shared-memory plan of this kernel ----------------------------------------------------------------------
+// The reference's dense plan with three changes.  (1) ldmatrix reads 8 rows of 16 bytes of a matmul's B operand at a
+// time; a row pitch that is a multiple of 128 bytes puts all 8 on the same banks, so a tile that only input loaders
+// write and only matmuls read as their B operand is stored with 16 bytes of padding per row.  (2) The tiles the TMA
+// engine refills every iteration come first, back to back, and that region exists `stages` times (the ring).
+// (3) Every other tile follows in planned order.  Tiles keep their identity (planned offset), so the aliasing of the
+// in-place exp is unchanged.
 namespace {
 struct FpTile {
   int planned, elems, rows, cols;
   bool only_loaded, only_b_operand;
   int offset, pad;
+  bool ring;
+  bool swizzled; // stored as 64-column boxes with the 128-byte swizzle (instead of padded rows)
+  bool boxed;    // fetched as one dense tensor-map box
+  // a tensor-map box must land on a 128-byte boundary; the swizzle pattern repeats every 1024 bytes
+  size_t alignment() const { return swizzled ? 1024 : (boxed ? 128 : 16); }
 };
 
-void pad_b_operands(mgd_program const &in, mgd_program *out, size_t *smem_bytes) {
-  FpTile tiles[3 * MGD_MAX_OPS];
+struct FpPlan {
+  mgd_program prog;
+  interp::TmaPlan tma;
+  interp::TmaMaps maps;
+  size_t smem_bytes;
+  bool ok;
+};
+
+void plan_fingerprint_program(mgd_program const &in, mgd_bindings const &bind, bool pad, bool use_tma, FpPlan *out) {
+  FpTile tiles[3 * MGD_MAX_OPS + 4];
   int n = 0;
   auto touch = [&](int planned, int elems) -> FpTile & {
     for (int i = 0; i < n; i++)
@@ -276,13 +396,13 @@ void pad_b_operands(mgd_program const &in, mgd_program *out, size_t *smem_bytes)
         if (elems > tiles[i].elems) tiles[i].elems = elems;
         return tiles[i];
       }
-    tiles[n] = FpTile{planned, elems, 0, 0, true, true, 0, 0};
+    tiles[n] = FpTile{planned, elems, 0, 0, true, true, 0, 0, false, false, false};
     return tiles[n++];
   };
   for (int i = 0; i < in.num_ops; i++) {
     int32_t const *a = in.ops[i].a;
     int const type = in.ops[i].type;
-    if (type == 2001) {
+    if (type == interp::kOpInput) {
       FpTile &t = touch(a[17], a[14] * a[15]);
       t.rows = a[14]; t.cols = a[15];
     } else if (type == MG_TB_MATMUL_OP) {
@@ -293,25 +413,34 @@ void pad_b_operands(mgd_program const &in, mgd_program *out, size_t *smem_bytes)
     } else if (type == MG_TB_EXP_OP) {
       FpTile &t = touch(a[0], a[1]);
       t.only_loaded = false; t.only_b_operand = false;
-    } else if (type == MG_TB_DIV_OP || type == MG_TB_ADD_OP || type == MG_TB_MUL_OP) {
+    } else if (interp::is_binary(type)) {
       int zx = a[0] > a[3] ? a[0] : a[3], zy = a[1] > a[4] ? a[1] : a[4], zz = a[2] > a[5] ? a[2] : a[5];
       touch(a[6], a[0] * a[1] * a[2]).only_b_operand = false;
       touch(a[7], a[3] * a[4] * a[5]).only_b_operand = false;
       touch(a[8], zx * zy * zz).only_loaded = false;
-    } else if (type >= MG_TB_REDUCTION_0_OP && type <= MG_TB_REDUCTION_2_TO_DIMX_OP) {
+    } else if (interp::is_reduction(type)) {
       touch(a[3], a[0] * a[1]).only_b_operand = false;
       touch(a[4], a[0]).only_loaded = false;
-    } else if (type >= MG_TB_CONCAT_0_OP && type <= MG_TB_CONCAT_2_OP) {
+    } else if (interp::is_concat(type)) {
       int along = a[1] + a[2];
       touch(a[4], along > 0 ? a[0] / along * a[1] : 0).only_b_operand = false;
       touch(a[5], along > 0 ? a[0] / along * a[2] : 0).only_b_operand = false;
       touch(a[6], a[0]).only_loaded = false;
-    } else if (type == 2002) {
+    } else if (type == interp::kOpAccumulate) {
+      touch(a[1], a[0]).only_b_operand = false;
+      FpTile &acc = touch(a[2], a[0]);
+      acc.only_loaded = false; acc.only_b_operand = false;
+    } else if (type == interp::kOpOutput) {
       touch(a[13], a[11] * a[12]).only_b_operand = false;
       FpTile &acc = touch(a[14], a[11] * a[12]);
       acc.only_loaded = false; acc.only_b_operand = false;
     }
   }
+  auto find = [&](int planned) -> FpTile & {
+    for (int i = 0; i < n; i++)
+      if (tiles[i].planned == planned) return tiles[i];
+    return tiles[0];
+  };
   // a padded tile must really be a B operand of matching shape somewhere
   for (int i = 0; i < n; i++) {
     FpTile &t = tiles[i];
@@ -321,48 +450,127 @@ void pad_b_operands(mgd_program const &in, mgd_program *out, size_t *smem_bytes)
         used_as_b = true;
         if (in.ops[j].a[2] != t.rows || in.ops[j].a[1] != t.cols) t.only_b_operand = false;
       }
-    t.pad = (used_as_b && t.only_loaded && t.only_b_operand && t.rows > 0 && (t.cols * 2) % 128 == 0) ? 8 : 0;
+    t.pad = (pad && used_as_b && t.only_loaded && t.only_b_operand && t.rows > 0 && (t.cols * 2) % 128 == 0) ? 8 : 0;
   }
-  // new offsets in planned order (insertion sort by planned offset: at most 72 tiles)
-  int order[3 * MGD_MAX_OPS];
+  // which inputs the TMA engine fetches, and how: an input whose tile is the same in every iteration and that no
+  // in-place operator overwrites is fetched once; every other eligible input goes through the ring
+  interp::TmaPlan &tma = out->tma;
+  std::memset(&tma, 0, sizeof(tma));
+  std::memset(&out->maps, 0, sizeof(out->maps));
+  for (int i = 0; i < in.num_ops; i++) {
+    mgd_op const &op = in.ops[i];
+    if (op.type != interp::kOpInput) continue;
+    FpTile &t = find(op.a[17]);
+    int writers = 0;
+    bool overwritten = false;
+    for (int j = 0; j < in.num_ops; j++) {
+      if (interp::written_by(in.ops[j]) == t.planned) writers++;
+      if (in.ops[j].type == MG_TB_EXP_OP && in.ops[j].a[0] == t.planned) overwritten = true;
+    }
+    bool const invariant = !interp::input_moves(op) && !overwritten && writers == 1;
+    int const slot = op.a[18];
+    bool const eligible = use_tma && writers <= 2 && t.elems == t.rows * t.cols &&
+                          interp::tma_eligible(op, bind.in[slot], bind.in_set_stride[slot], bind.num_sets, t.cols + t.pad, false);
+    if (eligible) {
+      // the tiled forms need a tensor map; one input per tile only (a tile has one layout)
+      int inputs_of_tile = 0;
+      for (int j = 0; j < in.num_ops; j++) inputs_of_tile += in.ops[j].type == interp::kOpInput && in.ops[j].a[17] == t.planned;
+      int form = inputs_of_tile == 1 ? interp::tiled_form(op, bind.in_set_stride[slot], bind.num_sets, t.pad > 0) : 0;
+      if (form && !interp::make_tile_map(&out->maps.m[slot], bind.in[slot], (uint64_t)op.a[13], (uint64_t)op.a[12],
+                                         interp::matrices_addressed(in, op, bind.in_set_stride[slot], bind.num_sets),
+                                         form == 2 ? 64u : (uint32_t)t.cols, (uint32_t)t.rows, form == 2))
+        form = 0;
+      if (form == 2) {
+        tma.swizzled_mask |= 1u << i;
+        t.swizzled = true;
+        t.pad = 0;
+      } else if (form == 1) {
+        tma.tiled_mask |= 1u << i;
+        t.boxed = true;
+      }
+    }
+    if (eligible && invariant) {
+      tma.once_mask |= 1u << i;
+      tma.once_tx += t.rows * t.cols * 2;
+    } else if (eligible && in.forloop_range > 1 && !t.ring) {
+      // (a tile two inputs write cannot be in the ring twice: the second one stays on plain loads)
+      bool shared_tile = false;
+      for (int j = 0; j < i; j++)
+        if (in.ops[j].type == interp::kOpInput && in.ops[j].a[17] == t.planned) shared_tile = true;
+      if (!shared_tile) {
+        tma.moving_mask |= 1u << i;
+        tma.moving_tx += t.rows * t.cols * 2;
+        t.ring = true;
+      }
+    } else if (eligible && in.forloop_range == 1 && writers == 1) {
+      tma.once_mask |= 1u << i; // a single iteration: everything is fetched once
+      tma.once_tx += t.rows * t.cols * 2;
+    } else if (invariant) {
+      tma.plain_once_mask |= 1u << i;
+    }
+  }
+  // offsets: ring tiles first (planned order), then the rest (planned order); insertion sort, at most 76 tiles
+  int order[3 * MGD_MAX_OPS + 4];
   for (int i = 0; i < n; i++) order[i] = i;
+  auto before = [&](FpTile const &x, FpTile const &y) { return x.ring != y.ring ? x.ring : x.planned < y.planned; };
   for (int i = 1; i < n; i++)
-    for (int j = i; j > 0 && tiles[order[j]].planned < tiles[order[j - 1]].planned; j--) {
+    for (int j = i; j > 0 && before(tiles[order[j]], tiles[order[j - 1]]); j--) {
       int tmp = order[j]; order[j] = order[j - 1]; order[j - 1] = tmp;
     }
+  auto bytes_of = [](FpTile const &t) {
+    size_t b = t.pad ? (size_t)t.rows * (t.cols + t.pad) * 2 : (size_t)t.elems * 2;
+    return (b + t.alignment() - 1) & ~(t.alignment() - 1);
+  };
+  // tiles start on their alignment; the ring then repeats at a multiple of 1024 bytes
+  auto place = [](size_t at, FpTile const &t) { return (at + t.alignment() - 1) & ~(t.alignment() - 1); };
+  size_t ring_bytes = 0, rest_bytes = 0;
+  for (int i = 0; i < n; i++) {
+    FpTile const &t = tiles[order[i]];
+    if (t.ring) ring_bytes = place(ring_bytes, t) + bytes_of(t);
+    else rest_bytes += bytes_of(t) + (t.alignment() > 16 ? t.alignment() : 0);
+  }
+  ring_bytes = (ring_bytes + 1023) & ~(size_t)1023;
+  int stages = 0;
+  if (ring_bytes > 0) {
+    stages = in.forloop_range < 3 ? in.forloop_range : 3;
+    while (stages > 1 && ring_bytes * stages + rest_bytes + 16 + 1024 > (size_t)interp::kDynSmemLimit) stages--;
+  }
+  tma.stages = stages;
+  tma.ring_lo = 0;
+  tma.ring_bytes = (int32_t)ring_bytes;
   size_t at = 0;
   for (int i = 0; i < n; i++) {
     FpTile &t = tiles[order[i]];
+    if (!t.ring && at < ring_bytes * (size_t)(stages > 0 ? stages : 0)) at = ring_bytes * (size_t)stages;
+    at = place(at, t);
     t.offset = (int)at;
-    size_t bytes = t.pad ? (size_t)t.rows * (t.cols + t.pad) * 2 : (size_t)t.elems * 2;
-    at += (bytes + 15) & ~(size_t)15;
+    at += bytes_of(t);
   }
-  *smem_bytes = at + 16;
-  auto find = [&](int planned) -> FpTile const & {
-    for (int i = 0; i < n; i++)
-      if (tiles[i].planned == planned) return tiles[i];
-    return tiles[0];
-  };
-  *out = in;
+  if (at < ring_bytes * (size_t)stages) at = ring_bytes * (size_t)stages;
+  out->smem_bytes = at + 16 + ((tma.tiled_mask | tma.swizzled_mask) ? 1024 : 0); // + room to align the base to 1024 bytes
+  out->prog = in;
   for (int i = 0; i < in.num_ops; i++) {
     int32_t const *a = in.ops[i].a;
-    int32_t *w = out->ops[i].a;
+    int32_t *w = out->prog.ops[i].a;
     int const type = in.ops[i].type;
-    if (type == 2001) {
+    if (type == interp::kOpInput) {
       w[17] = find(a[17]).offset;
       w[16] = (a[16] & 0xff) | (find(a[17]).pad << 8);
     } else if (type == MG_TB_MATMUL_OP) {
       w[3] = find(a[3]).offset; w[4] = find(a[4]).offset; w[5] = find(a[5]).offset;
       w[6] = find(a[4]).pad ? a[1] + find(a[4]).pad : 0;
+      w[7] = find(a[4]).swizzled ? 1 : 0;
     } else if (type == MG_TB_EXP_OP) {
       w[0] = find(a[0]).offset;
-    } else if (type == MG_TB_DIV_OP || type == MG_TB_ADD_OP || type == MG_TB_MUL_OP) {
+    } else if (interp::is_binary(type)) {
       w[6] = find(a[6]).offset; w[7] = find(a[7]).offset; w[8] = find(a[8]).offset;
-    } else if (type >= MG_TB_REDUCTION_0_OP && type <= MG_TB_REDUCTION_2_TO_DIMX_OP) {
+    } else if (interp::is_reduction(type)) {
       w[3] = find(a[3]).offset; w[4] = find(a[4]).offset;
-    } else if (type >= MG_TB_CONCAT_0_OP && type <= MG_TB_CONCAT_2_OP) {
+    } else if (interp::is_concat(type)) {
       w[4] = find(a[4]).offset; w[5] = find(a[5]).offset; w[6] = find(a[6]).offset;
-    } else if (type == 2002) {
+    } else if (type == interp::kOpAccumulate) {
+      w[1] = find(a[1]).offset; w[2] = find(a[2]).offset;
+    } else if (type == interp::kOpOutput) {
       w[13] = find(a[13]).offset; w[14] = find(a[14]).offset;
     }
   }
@@ -375,21 +583,24 @@ using namespace mgk;
 extern "C" int mgd_launch_fingerprint_interp(const mgd_program *prog, const mgd_bindings *bind, void *stream) {
   int st = validate_program(prog, bind);
   if (st != MG_OK) return st;
-  // padded operands when they fit, else the reference's dense plan as it is
-  mgd_program padded;
-  size_t smem = 0;
-  pad_b_operands(*prog, &padded, &smem);
-  if (smem > (size_t)kSmemLimit) {
-    padded = *prog;
-    smem = (size_t)prog->smem_bytes + 16;
-  }
-  if (smem > (size_t)kSmemLimit) return set_error(MG_ERR_UNSUPPORTED, "threadblock graph needs more shared memory than an SM has");
-  prog = &padded;
+  // Rewrite (hoisted products), then plan: padded operands and the TMA ring when they fit, else step back towards
+  // the reference's dense plan with plain loads.
+  mgd_program rewritten = *prog;
+  interp::hoist_invariant_products(rewritten);
+  FpPlan plan;
+  plan_fingerprint_program(rewritten, *bind, true, true, &plan);
+  if (plan.smem_bytes > (size_t)interp::kDynSmemLimit) plan_fingerprint_program(rewritten, *bind, false, true, &plan);
+  if (plan.smem_bytes > (size_t)interp::kDynSmemLimit) plan_fingerprint_program(*prog, *bind, false, false, &plan);
+  size_t const smem = plan.smem_bytes;
+  if (smem > (size_t)interp::kDynSmemLimit) return set_error(MG_ERR_UNSUPPORTED, "threadblock graph needs more shared memory than an SM has");
+  int32_t *status = device_error_word();
+  if (!status) return set_error(MG_ERR_CUDA, "cannot allocate the device status word");
+  prog = &plan.prog;
   static size_t configured = 0;
   if (smem > 48 * 1024 && smem > configured) {
-    if (cudaFuncSetAttribute(fp_interp_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess)
+    if (cudaFuncSetAttribute(fp_interp_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, interp::kDynSmemLimit) != cudaSuccess)
       return check_launch("cudaFuncSetAttribute(fp_interp_kernel)");
-    configured = kSmemLimit;
+    configured = interp::kDynSmemLimit;
   }
   int64_t blocks = (int64_t)prog->grid[0] * prog->grid[1] * prog->grid[2] * bind->num_sets;
   if (blocks > 0x7fffffffLL) return set_error(MG_ERR_UNSUPPORTED, "too many blocks for one launch");
@@ -400,8 +611,11 @@ extern "C" int mgd_launch_fingerprint_interp(const mgd_program *prog, const mgd_
     int32_t const *a = prog->ops[i].a;
     int64_t work = 0;
     switch (prog->ops[i].type) {
-      case 2001: work = (int64_t)a[14] * a[15] / 8; break;            // 16-byte loads
-      case 2002: work = (int64_t)a[11] * a[12]; break;
+      case interp::kOpInput: // 16-byte plain loads; nothing for the threads to do when the TMA engine fetches it
+        work = ((plan.tma.moving_mask | plan.tma.once_mask) >> i) & 1u ? 0 : (int64_t)a[14] * a[15] / 8;
+        break;
+      case interp::kOpOutput: work = (int64_t)a[11] * a[12] / (a[interp::kPhaseSlot] ? 4 : 1); break;
+      case interp::kOpAccumulate: work = a[0]; break;
       case MG_TB_MATMUL_OP: work = (int64_t)a[0] * a[1]; break;
       case MG_TB_EXP_OP: work = a[1]; break;
       default: work = a[0]; break;
@@ -411,6 +625,6 @@ extern "C" int mgd_launch_fingerprint_interp(const mgd_program *prog, const mgd_
   unsigned threads = largest >= 8192 ? 1024u : (largest >= 2048 ? 512u : 256u);
   if (int const v = option(MGD_OPT_INTERP_THREADS)) // 256, 512 or 1024: for measurements
     if (v == 256 || v == 512 || v == 1024) threads = (unsigned)v;
-  fp_interp_kernel<<<(unsigned)blocks, threads, smem, (cudaStream_t)stream>>>(*prog, *bind);
+  fp_interp_kernel<<<(unsigned)blocks, threads, smem, (cudaStream_t)stream>>>(*prog, *bind, plan.tma, plan.maps, status);
   return check_launch("fp_interp_kernel");
 }

@@ -4,6 +4,7 @@
 #include "mugraph_rng.h"
 #include <atomic>
 #include <cstring>
+#include <mutex>
 #include <string>
 
 namespace mgk {
@@ -27,6 +28,19 @@ int check_launch(char const *name) {
 }
 static std::atomic<int32_t> g_options[MGD_OPT_COUNT];
 int option(int key) { return key >= 0 && key < MGD_OPT_COUNT ? g_options[key].load(std::memory_order_relaxed) : 0; }
+
+TensorMapEncodeFn tensor_map_encoder() {
+  static TensorMapEncodeFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void *sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<TensorMapEncodeFn>(sym);
+  });
+  return fn;
+}
 
 int32_t *device_error_word() {
   if (!g_error_word) {
