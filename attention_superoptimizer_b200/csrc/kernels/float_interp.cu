@@ -266,36 +266,34 @@ __global__ void __launch_bounds__(1024) float_interp_kernel(const __grid_constan
     }
     __syncthreads();
   }
-  // Row copies of every input in `mask` for iteration `it`, into ring stage `stage` (ignored for the once-tiles),
-  // completing on `bar`; called by warp 0.  Only 16-bit tiles of row-major tensors are in these masks.
+  // the inputs the TMA engine fetches (16-bit tiles of row-major tensors), resolved once for this block
+  __shared__ interp::TileFetch fetch[MGD_MAX_IO];
+  int const n_fetch = __popc(tma_mask);
+  if (tid < prog.num_ops && ((tma_mask >> tid) & 1u)) {
+    int32_t const *a = ops[tid].a;
+    interp::resolve_fetch(fetch[__popc(tma_mask & ((1u << tid) - 1u))], a, tma, maps, tid, bnd.in[a[18]],
+                          set * bnd.in_set_stride[a[18]], bx, by, bz, a[15] + ((a[16] >> kInPadShift) & 0xff), smem_b);
+  }
+  __syncthreads();
   auto issue = [&](uint32_t mask, int it, int stage, uint32_t bar, int tx) {
-    if (lane == 0) ptx::mbar_expect_tx(bar, (uint32_t)tx);
-    __syncwarp();
-    for (int oi = 0; oi < prog.num_ops; oi++) {
-      if (!((mask >> oi) & 1u)) continue;
-      int32_t const *a = ops[oi].a;
-      int row = bx * a[0] + by * a[1] + bz * a[2] + it * a[6];
-      int col = bx * a[3] + by * a[4] + bz * a[5] + it * a[7];
-      int64_t lead = (int64_t)bx * a[8] + (int64_t)by * a[9] + (int64_t)bz * a[10] + (int64_t)it * a[11];
-      int const in_ring = (unsigned)(a[17] - tma.ring_lo) < (unsigned)tma.ring_bytes;
-      uint32_t dst = ptx::smem_u32(smem_b + a[17] + (in_ring ? stage * tma.ring_bytes : 0));
-      int const form = ((tma.swizzled_mask >> oi) & 1u) ? 2 : (int)((tma.tiled_mask >> oi) & 1u);
-      if (form) {
-        int const z = (int)((set * bnd.in_set_stride[a[18]] + lead) / ((int64_t)a[12] * a[13]));
-        interp::issue_tile_boxes(dst, &maps.m[a[18]], form, a[14], a[15], col, row, z, bar, lane);
-      } else {
-        uint16_t const *first = static_cast<uint16_t const *>(bnd.in[a[18]]) + set * bnd.in_set_stride[a[18]] + lead +
-                                (size_t)row * a[13] + col;
-        interp::issue_tile_rows(dst, first, a[14], a[15], a[15] + ((a[16] >> kInPadShift) & 0xff), a[13], bar, lane);
-      }
-    }
+    interp::issue_fetches(fetch, n_fetch, mask == tma.moving_mask ? 1 : 0, it, stage, bar, tx, lane);
   };
   int issued = 0; // iterations whose ring tiles have been requested
+#ifdef MG_FI_TIMING
+  long long const pro_t0 = clock64();
+  long long pro_t1 = 0, pro_t2 = 0;
+#endif
   if (warp == 0) {
     if (tma.once_mask) issue(tma.once_mask, 0, 0, ptx::smem_u32(&bars[interp::kMaxStages]), tma.once_tx);
+#ifdef MG_FI_TIMING
+    pro_t1 = clock64();
+#endif
     if (tma.stages > 0)
       for (; issued < tma.stages && issued <= last; issued++)
         issue(tma.moving_mask, issued, issued, ptx::smem_u32(&bars[issued]), tma.moving_tx);
+#ifdef MG_FI_TIMING
+    pro_t2 = clock64();
+#endif
   }
   // Bounded waits: when one runs out the block records it, waits (bounded again) for the copies still in flight so
   // that none lands in shared memory of a later block, and returns.
@@ -313,18 +311,29 @@ __global__ void __launch_bounds__(1024) float_interp_kernel(const __grid_constan
     bool ok = ptx::mbar_wait(ptx::smem_u32(&bars[interp::kMaxStages]), 0);
     if (!__syncthreads_and(ok)) { give_up(); return; }
   }
+#ifdef MG_FI_TIMING
+  if (blockIdx.x == 0 && tid == 0)
+    printf("prologue: issue once %lld, issue ring %lld, once wait %lld cycles\n", pro_t1 - pro_t0, pro_t2 - pro_t1, clock64() - pro_t2);
+#endif
 
 #ifdef MG_FI_TIMING // cycles per operator (with its barrier), printed by one thread of block 0
   long long op_cycles[MGD_MAX_OPS] = {};
-  long long ld_setup = 0, ld_copy = 0;
+  long long ld_setup = 0, ld_copy = 0, wait_cycles = 0, issue_cycles = 0;
+  long long const kernel_t0 = clock64();
 #endif
   for (int it = 0; it <= last; it++) {
+#ifdef MG_FI_TIMING
+    long long const wait_t0 = clock64();
+#endif
     if (tma.stages > 0) {
       int const s = it % tma.stages;
       stage_offset = s * tma.ring_bytes;
       bool ok = ptx::mbar_wait(ptx::smem_u32(&bars[s]), (uint32_t)((it / tma.stages) & 1));
       if (!__syncthreads_and(ok)) { give_up(); return; }
     }
+#ifdef MG_FI_TIMING
+    wait_cycles += clock64() - wait_t0;
+#endif
     for (int oi = 0; oi < prog.num_ops; oi++) {
       mgd_op const &op = ops[oi];
       int32_t const *a = op.a;
@@ -517,16 +526,23 @@ __global__ void __launch_bounds__(1024) float_interp_kernel(const __grid_constan
 #endif
     }
     // every thread is past its last read of this iteration's stage: request the tiles of iteration it + stages into it
+#ifdef MG_FI_TIMING
+    long long const issue_t0 = clock64();
+#endif
     if (warp == 0 && tma.stages > 0 && issued <= last) {
       ptx::fence_proxy_async_smem();
       int const s = it % tma.stages;
       issue(tma.moving_mask, issued, s, ptx::smem_u32(&bars[s]), tma.moving_tx);
       issued++;
     }
+#ifdef MG_FI_TIMING
+    issue_cycles += clock64() - issue_t0;
+#endif
   }
 #ifdef MG_FI_TIMING
   if (blockIdx.x == 0 && tid == 0)
   {
+    printf("kernel %lld cycles; ring waits %lld; issue %lld; threads %d stages %d\n", clock64() - kernel_t0, wait_cycles, issue_cycles, nt, tma.stages);
     for (int oi = 0; oi < prog.num_ops; oi++) printf("op %d type %d: %lld cycles\n", oi, ops[oi].type, op_cycles[oi]);
     printf("loaders (vector path): setup %lld copy %lld\n", ld_setup, ld_copy);
   }
@@ -853,6 +869,9 @@ extern "C" int mgd_launch_float_interp(const mgd_program *prog, const mgd_bindin
   int64_t largest = 0;
   for (int i = 0; i < r.prog.num_ops; i++) {
     int32_t const *a = r.prog.ops[i].a;
+    // what runs once after the loop does not size the block when the loop is long: its few big operators finish
+    // on fewer warps, every iteration's barriers are cheaper for it
+    if (r.prog.ops[i].type != 2001 && a[interp::kPhaseSlot] != 0 && r.prog.forloop_range >= 4) continue;
     int64_t work = 0;
     switch (r.prog.ops[i].type) {
       case 2001: // plain loads; nothing for the threads to do when the TMA engine fetches the tile
@@ -868,9 +887,9 @@ extern "C" int mgd_launch_float_interp(const mgd_program *prog, const mgd_bindin
     }
     if (work > largest) largest = work;
   }
-  unsigned threads = largest >= 8192 ? 1024u : (largest >= 2048 ? 512u : 256u);
-  if (int const v = option(MGD_OPT_INTERP_THREADS)) // 256, 512 or 1024: for measurements
-    if (v == 256 || v == 512 || v == 1024) threads = (unsigned)v;
+  unsigned threads = largest >= 8192 ? 1024u : (largest >= 2048 ? 512u : (largest >= 512 ? 256u : 128u));
+  if (int const v = option(MGD_OPT_INTERP_THREADS)) // 128 ... 1024: for measurements
+    if (v == 128 || v == 256 || v == 512 || v == 1024) threads = (unsigned)v;
   static bool configured_h = false, configured_b = false;
   if (dt == MG_DT_FLOAT16) {
     if (smem > 48 * 1024 && !configured_h) {

@@ -133,29 +133,17 @@ __global__ void __launch_bounds__(1024) fp_interp_kernel(const __grid_constant__
     ptx::mbar_init_fence();
   }
   __syncthreads();
-  // Row copies of every input in `mask` for iteration `it`, into ring stage `stage` (ignored for the once-tiles),
-  // completing on `bar`; called by warp 0.
+  // the inputs the TMA engine fetches, resolved once for this block
+  __shared__ interp::TileFetch fetch[MGD_MAX_IO];
+  int const n_fetch = __popc(tma_mask);
+  if (tid < prog.num_ops && ((tma_mask >> tid) & 1u)) {
+    int32_t const *a = prog.ops[tid].a;
+    interp::resolve_fetch(fetch[__popc(tma_mask & ((1u << tid) - 1u))], a, tma, maps, tid, bind.in[a[18]],
+                          set * bind.in_set_stride[a[18]], bx, by, bz, a[15] + ((a[16] >> 8) & 0xff), smem_raw);
+  }
+  __syncthreads();
   auto issue = [&](uint32_t mask, int it, int stage, uint32_t bar, int tx) {
-    if (lane == 0) ptx::mbar_expect_tx(bar, (uint32_t)tx);
-    __syncwarp();
-    for (int oi = 0; oi < prog.num_ops; oi++) {
-      if (!((mask >> oi) & 1u)) continue;
-      int32_t const *a = prog.ops[oi].a;
-      int row = bx * a[0] + by * a[1] + bz * a[2] + it * a[6];
-      int col = bx * a[3] + by * a[4] + bz * a[5] + it * a[7];
-      int64_t lead = (int64_t)bx * a[8] + (int64_t)by * a[9] + (int64_t)bz * a[10] + (int64_t)it * a[11];
-      int const in_ring = (unsigned)(a[17] - tma.ring_lo) < (unsigned)tma.ring_bytes;
-      uint32_t dst = ptx::smem_u32(smem_raw + a[17] + (in_ring ? stage * tma.ring_bytes : 0));
-      int const form = ((tma.swizzled_mask >> oi) & 1u) ? 2 : (int)((tma.tiled_mask >> oi) & 1u);
-      if (form) {
-        int const z = (int)((set * bind.in_set_stride[a[18]] + lead) / ((int64_t)a[12] * a[13]));
-        interp::issue_tile_boxes(dst, &maps.m[a[18]], form, a[14], a[15], col, row, z, bar, lane);
-      } else {
-        uint16_t const *first = static_cast<uint16_t const *>(bind.in[a[18]]) + set * bind.in_set_stride[a[18]] + lead +
-                                (size_t)row * a[13] + col;
-        interp::issue_tile_rows(dst, first, a[14], a[15], a[15] + ((a[16] >> 8) & 0xff), a[13], bar, lane);
-      }
-    }
+    interp::issue_fetches(fetch, n_fetch, mask == tma.moving_mask ? 1 : 0, it, stage, bar, tx, lane);
   };
   int issued = 0; // iterations whose ring tiles have been requested
   if (warp == 0) {
@@ -609,6 +597,8 @@ extern "C" int mgd_launch_fingerprint_interp(const mgd_program *prog, const mgd_
   int64_t largest = 0;
   for (int i = 0; i < prog->num_ops; i++) {
     int32_t const *a = prog->ops[i].a;
+    // what runs once after the loop does not size the block when the loop is long
+    if (prog->ops[i].type != interp::kOpInput && a[interp::kPhaseSlot] != 0 && prog->forloop_range >= 4) continue;
     int64_t work = 0;
     switch (prog->ops[i].type) {
       case interp::kOpInput: // 16-byte plain loads; nothing for the threads to do when the TMA engine fetches it
@@ -622,9 +612,9 @@ extern "C" int mgd_launch_fingerprint_interp(const mgd_program *prog, const mgd_
     }
     if (work > largest) largest = work;
   }
-  unsigned threads = largest >= 8192 ? 1024u : (largest >= 2048 ? 512u : 256u);
-  if (int const v = option(MGD_OPT_INTERP_THREADS)) // 256, 512 or 1024: for measurements
-    if (v == 256 || v == 512 || v == 1024) threads = (unsigned)v;
+  unsigned threads = largest >= 8192 ? 1024u : (largest >= 2048 ? 512u : (largest >= 512 ? 256u : 128u));
+  if (int const v = option(MGD_OPT_INTERP_THREADS)) // 128 ... 1024: for measurements
+    if (v == 128 || v == 256 || v == 512 || v == 1024) threads = (unsigned)v;
   fp_interp_kernel<<<(unsigned)blocks, threads, smem, (cudaStream_t)stream>>>(*prog, *bind, plan.tma, plan.maps, status);
   return check_launch("fp_interp_kernel");
 }

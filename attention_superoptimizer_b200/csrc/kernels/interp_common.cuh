@@ -28,7 +28,7 @@ constexpr int kOpInput = 2001, kOpOutput = 2002;
 constexpr int kOpAccumulate = 2990; // internal: acc = first ? x : acc + x   a[0] elements, a[1] source, a[2] accumulator
 constexpr int kPhaseSlot = 18;      // non-input operators: a[18] = 1 -> runs once, after the last for-loop iteration
 constexpr int kMaxStages = 4;
-constexpr int kDynSmemLimit = kSmemLimit - 128;  // dynamic shared memory: the kernels also hold a few barriers statically
+constexpr int kDynSmemLimit = kSmemLimit - 768; // dynamic shared memory: the kernels also hold a few barriers statically
 
 inline bool is_reduction(int type) { return type >= MG_TB_REDUCTION_0_OP && type <= MG_TB_REDUCTION_2_TO_DIMX_OP; }
 inline bool is_concat(int type) { return type == MG_TB_CONCAT_0_OP || type == MG_TB_CONCAT_1_OP || type == MG_TB_CONCAT_2_OP; }
@@ -193,6 +193,10 @@ inline bool tma_eligible(mgd_op const &in, void const *base, int64_t set_stride,
 }
 
 #ifdef __CUDACC__
+__device__ __forceinline__ void issue_tile_boxes(uint32_t dst, CUtensorMap const *map, int form, int rows, int cols, int col,
+                                                 int row, int z, uint32_t bar, int lane);
+__device__ __forceinline__ void issue_tile_rows(uint32_t dst, uint16_t const *first, int rows, int cols, int pitch, int ld,
+                                                uint32_t bar, int lane);
 __device__ __forceinline__ void bulk_load_row(uint32_t dst, void const *src, uint32_t bytes, uint32_t bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
@@ -207,6 +211,54 @@ __device__ __forceinline__ void issue_tile_boxes(uint32_t dst, CUtensorMap const
       ptx::tma_load_3d(dst + (uint32_t)(c * rows * 128), map, bar, col + 64 * c, row, z);
   } else if (lane == 0) {
     ptx::tma_load_3d(dst, map, bar, col, row, z);
+  }
+}
+
+// One TMA-fetched input, resolved once per block: where its tile goes, where it comes from in the first iteration
+// and how far every iteration moves it.  Issuing a stage then is a walk over a few of these records.
+struct TileFetch {
+  CUtensorMap const *map;  // tiled forms
+  uint16_t const *first;   // row copies: first element of the tile in iteration 0
+  int64_t dfirst;          //   elements every iteration adds
+  uint32_t dst;            // shared address of the tile (stage 0)
+  int32_t stage_stride;    // bytes to the same tile in the next ring stage (0: fetched once)
+  int32_t form, rows, cols, pitch, ld;
+  int32_t col, row, z, dcol, drow, dz;
+  int32_t moving;
+};
+
+// Called by thread `oi` < num_ops for operator record `a` of an input in the TMA masks: fills fetch[slot in mask order].
+__device__ __forceinline__ void resolve_fetch(TileFetch &f, int32_t const *a, TmaPlan const &tma, TmaMaps const &maps, int oi,
+                                              void const *base, int64_t set_offset, int bx, int by, int bz, int pitch,
+                                              unsigned char *smem_base) {
+  int const row = bx * a[0] + by * a[1] + bz * a[2], col = bx * a[3] + by * a[4] + bz * a[5];
+  int64_t const lead = (int64_t)bx * a[8] + (int64_t)by * a[9] + (int64_t)bz * a[10];
+  int64_t const mat = (int64_t)a[12] * a[13];
+  f.map = &maps.m[a[18]];
+  f.first = static_cast<uint16_t const *>(base) + set_offset + lead + (size_t)row * a[13] + col;
+  f.dfirst = (int64_t)a[6] * a[13] + a[7] + a[11];
+  f.moving = (int)((tma.moving_mask >> oi) & 1u);
+  f.dst = ptx::smem_u32(smem_base + a[17]);
+  f.stage_stride = f.moving ? tma.ring_bytes : 0;
+  f.form = ((tma.swizzled_mask >> oi) & 1u) ? 2 : (int)((tma.tiled_mask >> oi) & 1u);
+  f.rows = a[14]; f.cols = a[15]; f.pitch = pitch; f.ld = a[13];
+  f.col = col; f.row = row; f.dcol = a[7]; f.drow = a[6];
+  f.z = f.form ? (int)((set_offset + lead) / mat) : 0;
+  f.dz = f.form ? (int)(a[11] / mat) : 0;
+}
+
+// Requests iteration `it` of every resolved input with `moving` == want_moving into ring stage `stage`, completing on
+// `bar` after `tx` bytes; called by all lanes of one warp.
+__device__ __forceinline__ void issue_fetches(TileFetch const *fetch, int n, int want_moving, int it, int stage, uint32_t bar,
+                                              int tx, int lane) {
+  if (lane == 0) ptx::mbar_expect_tx(bar, (uint32_t)tx);
+  __syncwarp();
+  for (int i = 0; i < n; i++) {
+    TileFetch const &f = fetch[i];
+    if (f.moving != want_moving) continue;
+    uint32_t const dst = f.dst + (uint32_t)(stage * f.stage_stride);
+    if (f.form) issue_tile_boxes(dst, f.map, f.form, f.rows, f.cols, f.col + it * f.dcol, f.row + it * f.drow, f.z + it * f.dz, bar, lane);
+    else issue_tile_rows(dst, f.first + it * f.dfirst, f.rows, f.cols, f.pitch, f.ld, bar, lane);
   }
 }
 

@@ -2,9 +2,14 @@
 
 * decode: the KV heads of a grouped-query attention call are independent (they are already `grid.x` of the
   muGraph), so rank r evaluates heads [r*H/N, (r+1)*H/N) - no collective on the data path;
-* verification sweep: independent input sets (or candidate graphs) are split evenly over the ranks; every
-  rank evaluates its share and the resulting fingerprints are all-gathered so that each rank can compare
-  and de-duplicate all of them.
+* speculative decode: the batch x KV-head units of a call are independent too; rank r evaluates a contiguous
+  range of them, again without a collective;
+* verification sweep: independent input sets are split evenly over the ranks; every rank evaluates its share
+  and the resulting fingerprints are all-gathered so that each rank can compare and de-duplicate all of them;
+* candidate graphs: the candidates a search wants verified are dealt round-robin to the ranks; every rank
+  verifies its share against the computation graph's fingerprint and the pass / fail flags (and, on request,
+  a digest of every candidate's fingerprint) are all-gathered, so every rank ends up with the verdict on every
+  candidate (the reference verifies them one after the other on one GPU, src/search/search.cc:569-623).
 
 The reference is single-GPU (it has no collective anywhere); `torch.distributed` is used as plumbing only:
 NCCL over NVLink on GPUs, gloo in the CPU tests.
@@ -85,3 +90,66 @@ def matches_reference(fingerprints, reference) -> List[bool]:
     reference src/search/search.cc:601-609)"""
     import numpy as np
     return [bool(np.array_equal(fingerprints[i], reference)) for i in range(fingerprints.shape[0])]
+
+
+def unit_shard(num_units: int, rank: int, world: int) -> Tuple[int, int]:
+    """Contiguous range of the independent (batch, KV head) units of a decode call that `rank` evaluates; the
+    count must divide evenly so that every rank runs the same plan."""
+    if num_units % world != 0:
+        raise ValueError("%d units do not split evenly over %d ranks" % (num_units, world))
+    per = num_units // world
+    return rank * per, per
+
+
+def candidate_shard(num_candidates: int, rank: int, world: int) -> List[int]:
+    """Indices of the candidates `rank` verifies: round-robin, so that candidates of similar cost (a search emits
+    them in families) spread over the ranks."""
+    if not (0 <= rank < world):
+        raise ValueError("bad shard request")
+    return list(range(rank, num_candidates, world))
+
+
+def verify_candidates_sharded(num_candidates: int, verify_local, world: int, rank: int, device=None, group=None):
+    """Distributed form of the search's verify step.  `verify_local(indices)` verifies the candidates with those
+    indices on this rank's GPU and returns, per candidate, either a bool or a (bool, 64-bit digest of its
+    fingerprint) pair - on the GPU path it wraps `verify_candidates` of this package.  The flags (and digests) of
+    all ranks are all-gathered; returns (flags, digests) as lists of length num_candidates on every rank, digests
+    None when the callable gives none.  One small collective per call: 16 bytes per candidate."""
+    import torch
+    import torch.distributed as dist
+    mine = candidate_shard(num_candidates, rank, world)
+    results = list(verify_local(mine)) if mine else []
+    if len(results) != len(mine):
+        raise ValueError("verify_local returned %d results for %d candidates" % (len(results), len(mine)))
+    per_rank = -(-num_candidates // world) if num_candidates else 0
+    # [per_rank, 2] int64 rows (flag, digest); ranks with fewer candidates pad with -1
+    local = torch.full((max(per_rank, 1), 2), -1, dtype=torch.int64)
+    with_digests = False
+    for j, r in enumerate(results):
+        if isinstance(r, tuple):
+            flag, digest = r
+            with_digests = True
+            # digests are unsigned 64-bit values: carried as their two's-complement image
+            local[j, 1] = int(digest) - (1 << 64) if int(digest) >= (1 << 63) else int(digest)
+        else:
+            flag = r
+        local[j, 0] = 1 if flag else 0
+    if world == 1:
+        gathered = local.unsqueeze(0)
+    else:
+        if device is not None:
+            local = local.to(device)
+        flat = torch.empty((world * local.shape[0], 2), dtype=local.dtype, device=local.device)
+        dist.all_gather_into_tensor(flat, local, group=group)
+        gathered = flat.cpu().view(world, local.shape[0], 2)
+    flags: List[bool] = [False] * num_candidates
+    digests: List[int] = [0] * num_candidates
+    any_digest = with_digests
+    for r in range(world):
+        for j, idx in enumerate(candidate_shard(num_candidates, r, world)):
+            flags[idx] = bool(gathered[r, j, 0].item() == 1)
+            d = int(gathered[r, j, 1].item())
+            if d != -1 or with_digests:
+                any_digest = any_digest or d != -1
+            digests[idx] = d + (1 << 64) if d < 0 else d
+    return flags, (digests if any_digest else None)

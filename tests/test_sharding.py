@@ -111,3 +111,54 @@ def test_rank_that_leaves_is_detected_not_waited_for_forever(tmp_path):
         p.join(60)
         assert not p.is_alive()
     assert open(os.path.join(str(tmp_path), "outcome.txt")).read().startswith("error")
+
+
+# ---- candidate graphs dealt round-robin, verdicts all-gathered ----------------------------------------------------
+CANDIDATES = 7
+
+
+def candidate_fingerprint(i):
+    """Stand-in for candidate graph i: candidates 2 and 5 compute something else than the reference."""
+    rng = np.random.default_rng(3 if i not in (2, 5) else 100 + i)
+    return rng.integers(0, mo.FP_PQ, size=64).astype(np.uint16)
+
+
+def verify_worker(rank, world, port, result_dir):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        reference = candidate_fingerprint(0)
+
+        def verify_local(indices):
+            seen.extend(indices)
+            return [(bool(np.array_equal(candidate_fingerprint(i), reference)), mo.fnv1a64(candidate_fingerprint(i)))
+                    for i in indices]
+
+        seen = []
+        flags, digests = sharding.verify_candidates_sharded(CANDIDATES, verify_local, world, rank)
+        np.save(os.path.join(result_dir, "flags%d.npy" % rank), np.array(flags))
+        np.save(os.path.join(result_dir, "digests%d.npy" % rank), np.array(digests, dtype=np.uint64))
+        np.save(os.path.join(result_dir, "seen%d.npy" % rank), np.array(seen))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_candidate_shards_and_two_rank_verification(tmp_path):
+    for n in (0, 1, 7, 69):
+        for world in (1, 2, 3, 8):
+            dealt = sorted(i for r in range(world) for i in sharding.candidate_shard(n, r, world))
+            assert dealt == list(range(n))
+    assert sharding.unit_shard(32, 3, 8) == (12, 4)
+    with pytest.raises(ValueError):
+        sharding.unit_shard(32, 0, 5)
+    world, port = 2, free_port()
+    mp.spawn(verify_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
+    want_flags = [i not in (2, 5) for i in range(CANDIDATES)]
+    want_digests = [mo.fnv1a64(candidate_fingerprint(i)) for i in range(CANDIDATES)]
+    for r in range(world):
+        assert np.load(os.path.join(str(tmp_path), "flags%d.npy" % r)).tolist() == want_flags
+        assert np.load(os.path.join(str(tmp_path), "digests%d.npy" % r)).tolist() == want_digests
+        assert np.load(os.path.join(str(tmp_path), "seen%d.npy" % r)).tolist() == list(range(r, CANDIDATES, world))
+    # single process: same interface, no collective
+    flags, digests = sharding.verify_candidates_sharded(3, lambda idx: [i != 1 for i in idx], 1, 0)
+    assert flags == [True, False, True] and digests is None
