@@ -224,7 +224,11 @@ __device__ __noinline__ void matmul_mma(unsigned char const *staged, unsigned ch
   }
 }
 
-template <typename T>
+// LEAN: an instance without the code of the element-wise operators, the reductions, concat, the plain loaders and
+// the CUDA-core matmul, for programs of TMA-fetched inputs, tensor-core matmuls, accumulation and outputs only.  The
+// interpreter's time goes into fetching the code of one operator after another; the small instance stays in the
+// instruction cache.
+template <typename T, bool LEAN>
 __global__ void __launch_bounds__(1024) float_interp_kernel(const __grid_constant__ mgd_program prog,
                                                            const __grid_constant__ mgd_bindings bind,
                                                            const __grid_constant__ interp::TmaPlan tma,
@@ -342,13 +346,15 @@ __global__ void __launch_bounds__(1024) float_interp_kernel(const __grid_constan
         if (it > 0 && ((tma.plain_once_mask >> oi) & 1u)) continue;       // same tile as in the first iteration
       } else if (a[interp::kPhaseSlot] != 0 && it != last) {
         continue;                                                         // runs once, after the loop
+      } else if (op.type == interp::kOpAccumulate && a[4] != 0) {
+        continue;                                                         // the matmul before it did the adding
       }
       bool const first = it == 0 || (op.type != interp::kOpInput && a[interp::kPhaseSlot] != 0);
 #ifdef MG_FI_TIMING
       long long const op_t0 = clock64();
 #endif
       switch (op.type) {
-        case 2001: {
+        case 2001: if constexpr (!LEAN) {
           int row = bx * a[0] + by * a[1] + bz * a[2] + it * a[6];
           int col = bx * a[3] + by * a[4] + bz * a[5] + it * a[7];
           int64_t lead = (int64_t)bx * a[8] + (int64_t)by * a[9] + (int64_t)bz * a[10] + (int64_t)it * a[11];
@@ -402,7 +408,7 @@ __global__ void __launch_bounds__(1024) float_interp_kernel(const __grid_constan
             }
           }
           break;
-        }
+        } else break;
         case MG_TB_MATMUL_OP: {
           int m = a[0], n = a[1], k = a[2];
           unsigned char const *A = tile(a[3]), *B = tile(a[4]);
@@ -425,19 +431,19 @@ __global__ void __launch_bounds__(1024) float_interp_kernel(const __grid_constan
               if (wide) matmul_mma<T, 4>(staged, B, C, m, n, k, bp, swz, true, tid, nt);
               else matmul_mma<T, 1>(staged, B, C, m, n, k, bp, swz, true, tid, nt);
             }
-          } else {
+          } else if constexpr (!LEAN) {
             matmul_tiles<T>(A, B, C, m, n, k, a[6] != 0, a[7] != 0, add, tid, nt);
           }
           break;
         }
-        case MG_TB_EXP_OP: {
+        case MG_TB_EXP_OP: if constexpr (!LEAN) {
           float *x = ftile(a[0]);
           for (int i = tid; i < a[1]; i += nt) x[i] = expf(x[i]);
           break;
-        }
+        } else break;
         case MG_TB_DIV_OP:
         case MG_TB_ADD_OP:
-        case MG_TB_MUL_OP: {
+        case MG_TB_MUL_OP: if constexpr (!LEAN) {
           int const xd[3] = {a[0], a[1], a[2]}, yd[3] = {a[3], a[4], a[5]};
           int const zd[3] = {max(xd[0], yd[0]), max(xd[1], yd[1]), max(xd[2], yd[2])};
           unsigned char const *x = tile(a[6]), *y = tile(a[7]);
@@ -457,9 +463,9 @@ __global__ void __launch_bounds__(1024) float_interp_kernel(const __grid_constan
             z[i] = op.type == MG_TB_DIV_OP ? xv / yv : (op.type == MG_TB_ADD_OP ? xv + yv : xv * yv);
           }
           break;
-        }
+        } else break;
         case MG_TB_REDUCTION_0_OP: case MG_TB_REDUCTION_1_OP: case MG_TB_REDUCTION_2_OP:
-        case MG_TB_REDUCTION_0_TO_DIMX_OP: case MG_TB_REDUCTION_1_TO_DIMX_OP: case MG_TB_REDUCTION_2_TO_DIMX_OP: {
+        case MG_TB_REDUCTION_0_TO_DIMX_OP: case MG_TB_REDUCTION_1_TO_DIMX_OP: case MG_TB_REDUCTION_2_TO_DIMX_OP: if constexpr (!LEAN) {
           int n_out = a[0], degree = a[1], inner = a[2];
           unsigned char const *x = tile(a[3]);
           bool const x16 = a[5] != 0;
@@ -471,8 +477,8 @@ __global__ void __launch_bounds__(1024) float_interp_kernel(const __grid_constan
             y[i] = acc;
           }
           break;
-        }
-        case MG_TB_CONCAT_0_OP: case MG_TB_CONCAT_1_OP: case MG_TB_CONCAT_2_OP: {
+        } else break;
+        case MG_TB_CONCAT_0_OP: case MG_TB_CONCAT_1_OP: case MG_TB_CONCAT_2_OP: if constexpr (!LEAN) {
           int n_out = a[0], ad = a[1], bd = a[2], inner = a[3];
           unsigned char const *A = tile(a[4]), *B = tile(a[5]);
           bool const a16 = a[7] != 0, b16 = a[8] != 0;
@@ -483,7 +489,7 @@ __global__ void __launch_bounds__(1024) float_interp_kernel(const __grid_constan
                               : rd<T>(B, b16, in_idx + (along - ad) * inner + outer * inner * bd);
           }
           break;
-        }
+        } else break;
         case interp::kOpAccumulate: { // running sum of a tile over the for-loop (the hoisted matmul's left operand)
           unsigned char const *x = tile(a[1]);
           bool const x16 = a[3] != 0;
@@ -649,8 +655,9 @@ void replan(mgd_program const &in, mgd_bindings const *bind, Replanned *out) {
   int fused_matmul[MGD_MAX_OPS];
   for (int i = 0; i < in.num_ops; i++) fused_matmul[i] = -1;
   for (int o = 0; o < in.num_ops; o++) {
-    if (in.ops[o].type != 2002) continue;
-    int src = in.ops[o].a[13], writer = -1, writers = 0, reads = 0;
+    bool const is_acc = in.ops[o].type == interp::kOpAccumulate; // the running sum of a hoisted product's operand
+    if (in.ops[o].type != 2002 && !is_acc) continue;
+    int src = is_acc ? in.ops[o].a[1] : in.ops[o].a[13], writer = -1, writers = 0, reads = 0;
     for (int i = 0; i < in.num_ops; i++) {
       if (written_by(in.ops[i]) == src) { writers++; writer = i; }
       reads += reads_of(in.ops[i], src);
@@ -810,8 +817,14 @@ void replan(mgd_program const &in, mgd_bindings const *bind, Replanned *out) {
       w[4] = off(a[4]); w[5] = off(a[5]); w[6] = off(a[6]);
       w[7] = is16(a[4]); w[8] = is16(a[5]);
     } else if (type == interp::kOpAccumulate) {
-      w[1] = off(a[1]); w[2] = off(a[2]);
-      w[3] = is16(a[1]);
+      w[2] = off(a[2]);
+      w[4] = fused_matmul[i] >= 0 ? 1 : 0; // the producing matmul adds into the running sum itself
+      w[1] = w[4] ? 0 : off(a[1]);
+      w[3] = w[4] ? 0 : is16(a[1]);
+      if (w[4]) {
+        p.ops[fused_matmul[i]].a[5] = w[2];
+        p.ops[fused_matmul[i]].a[8] = 1;
+      }
     } else if (type == 2002) {
       w[14] = off(a[14]);
       w[17] = fused_matmul[i] >= 0 ? 1 : 0;
@@ -890,21 +903,51 @@ extern "C" int mgd_launch_float_interp(const mgd_program *prog, const mgd_bindin
   unsigned threads = largest >= 8192 ? 1024u : (largest >= 2048 ? 512u : (largest >= 512 ? 256u : 128u));
   if (int const v = option(MGD_OPT_INTERP_THREADS)) // 128 ... 1024: for measurements
     if (v == 128 || v == 256 || v == 512 || v == 1024) threads = (unsigned)v;
+  // the lean instance: every input fetched by the TMA engine, every matmul on the tensor cores, nothing else but
+  // accumulation and outputs
+  bool lean = true;
+  for (int i = 0; i < r.prog.num_ops && lean; i++) {
+    mgd_op const &op = r.prog.ops[i];
+    if (op.type == 2001) lean = ((r.tma.moving_mask | r.tma.once_mask) >> i) & 1u;
+    else if (op.type == MG_TB_MATMUL_OP) lean = op.a[10] > 0;
+    else lean = op.type == interp::kOpAccumulate || op.type == 2002;
+  }
+  if (lean) {
+    static bool lean_h = false, lean_b = false;
+    if (dt == MG_DT_FLOAT16) {
+      if (smem > 48 * 1024 && !lean_h) {
+        if (cudaFuncSetAttribute(float_interp_kernel<__half, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, interp::kDynSmemLimit) != cudaSuccess)
+          return check_launch("cudaFuncSetAttribute(float_interp_kernel)");
+        lean_h = true;
+      }
+      float_interp_kernel<__half, true><<<(unsigned)blocks, threads, smem, (cudaStream_t)stream>>>(r.prog, *bind, r.tma, r.maps, status);
+      return check_launch("float_interp_kernel");
+    }
+    if (dt == MG_DT_BFLOAT16) {
+      if (smem > 48 * 1024 && !lean_b) {
+        if (cudaFuncSetAttribute(float_interp_kernel<__nv_bfloat16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, interp::kDynSmemLimit) != cudaSuccess)
+          return check_launch("cudaFuncSetAttribute(float_interp_kernel)");
+        lean_b = true;
+      }
+      float_interp_kernel<__nv_bfloat16, true><<<(unsigned)blocks, threads, smem, (cudaStream_t)stream>>>(r.prog, *bind, r.tma, r.maps, status);
+      return check_launch("float_interp_kernel");
+    }
+  }
   static bool configured_h = false, configured_b = false;
   if (dt == MG_DT_FLOAT16) {
     if (smem > 48 * 1024 && !configured_h) {
-      if (cudaFuncSetAttribute(float_interp_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, interp::kDynSmemLimit) != cudaSuccess)
+      if (cudaFuncSetAttribute(float_interp_kernel<__half, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, interp::kDynSmemLimit) != cudaSuccess)
         return check_launch("cudaFuncSetAttribute(float_interp_kernel)");
       configured_h = true;
     }
-    float_interp_kernel<__half><<<(unsigned)blocks, threads, smem, (cudaStream_t)stream>>>(r.prog, *bind, r.tma, r.maps, status);
+    float_interp_kernel<__half, false><<<(unsigned)blocks, threads, smem, (cudaStream_t)stream>>>(r.prog, *bind, r.tma, r.maps, status);
   } else if (dt == MG_DT_BFLOAT16) {
     if (smem > 48 * 1024 && !configured_b) {
-      if (cudaFuncSetAttribute(float_interp_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, interp::kDynSmemLimit) != cudaSuccess)
+      if (cudaFuncSetAttribute(float_interp_kernel<__nv_bfloat16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, interp::kDynSmemLimit) != cudaSuccess)
         return check_launch("cudaFuncSetAttribute(float_interp_kernel)");
       configured_b = true;
     }
-    float_interp_kernel<__nv_bfloat16><<<(unsigned)blocks, threads, smem, (cudaStream_t)stream>>>(r.prog, *bind, r.tma, r.maps, status);
+    float_interp_kernel<__nv_bfloat16, false><<<(unsigned)blocks, threads, smem, (cudaStream_t)stream>>>(r.prog, *bind, r.tma, r.maps, status);
   } else {
     return set_error(MG_ERR_UNSUPPORTED, "float mode runs on fp16 or bf16 tensors");
   }

@@ -367,9 +367,11 @@ def run_ours(args):
 
     # ---- fingerprint verification sweep ----------------------------------------------------------------
     fingerprint = run_fingerprint_sweep(args, mg, mo, rt, torch, dist, np, rank, world, stream, timed, barrier)
+    candidates = None if args.no_other_configs else run_candidate_verification(mg, rt, torch, dist, np, rank, world, stream)
     others = None
-    if world == 1 and not args.no_other_configs:
-        others = measure_other_configs(mg, rt, stream, timed, peaks)
+    if not args.no_other_configs:
+        # N = 1: all three other configurations; N > 1: the speculative decode, its batch x KV-head units sharded
+        others = measure_other_configs(mg, rt, stream, timed, peaks, only=None if world == 1 else "c3", world=world, rank=rank)
 
     # ---- the reference's own GPU fingerprint kernel on the same box (rank 0, N = 1 only) -------------------------
     if rank == 0 and world == 1 and not args.no_reference_gpu:
@@ -403,7 +405,7 @@ def run_ours(args):
             "stream_ordered_us_per_call": round(ordered_us, 3),
             "single_call_us_median": None if single_us is None else round(single_us, 3),
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(gpu_launches),
-            "clocks": clocks, "fingerprint": fingerprint, "other_configs": others,
+            "clocks": clocks, "fingerprint": fingerprint, "candidates": candidates, "other_configs": others,
         }
         print(json.dumps(line))
     batched_graph.close()
@@ -560,6 +562,62 @@ def run_fingerprint_sweep(args, mg, mo, rt, torch, dist, np, rank, world, stream
             "bit_exact": bool(ok and checked > 0 and rows_equal == nchunks * chunk * world)}
 
 
+def run_candidate_verification(mg, rt, torch, dist, np, rank, world, stream):
+    """The search's verify step on independent candidate graphs: the 69 muGraphs of the reference's own search
+    checkpoint for the speculative-decode attention graph (tests/golden/spec_decode_candidates.json.gz), dealt
+    round-robin over the ranks; every rank evaluates its candidates' fingerprint kernels and compares each result
+    with the computation graph's fingerprint on the device (one synchronisation per rank), then the verdicts are
+    all-gathered.  Wall clock around the whole step, max over ranks."""
+    import contextlib
+    import gzip
+    from attention_superoptimizer_b200 import sharding
+    path = os.path.join(ROOT, "tests", "golden", "spec_decode_candidates.json.gz")
+    if not os.path.exists(path):
+        return None
+    with gzip.open(path) as f:
+        fx = json.loads(f.read().decode())
+    docs = fx["generated_graphs"]
+    sh = stream.cuda_stream
+
+    def inputs_of(g):
+        return [g.operator(i)[1][0] for i in range(g.num_operators) if g.operator(i)[0] == 1001]
+
+    with contextlib.ExitStack() as stack:
+        ref = stack.enter_context(mg.PyGraph.from_json(fx["computation_graph"], rt))
+        for i, t in enumerate(inputs_of(ref)):
+            t.fill_fingerprint_seeded(700 + i, mg.FP_PQ)
+        ref.fingerprint()
+        ref_out = ref.operator(ref.num_operators - 1)[1][0]
+        mine = sharding.candidate_shard(len(docs), rank, world)
+        batch = []
+        for n in mine:
+            g = stack.enter_context(mg.PyGraph.from_json(docs[n], rt))
+            for i, t in enumerate(inputs_of(g)):
+                t.fill_fingerprint_seeded(700 + i, mg.FP_PQ)
+            batch.append((g, g.operator(g.num_operators - 1)[1][0]))
+
+        def step():
+            return sharding.verify_candidates_sharded(len(docs), lambda idx: mg.verify_candidates(ref_out, batch, stream=sh),
+                                                      world, rank, device=torch.device("cuda") if world > 1 else None)
+
+        step()
+        times = []
+        for _ in range(5):
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            flags, _ = step()
+            times.append(time.perf_counter() - t0)
+        ms = torch.tensor([statistics.median(times) * 1e3], device="cuda")
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    return {"candidates": len(docs), "candidates_per_gpu": len(mine), "all_equal_to_computation_graph": bool(all(flags)),
+            "ms_per_batch": round(float(ms.item()), 3), "candidates_per_s": round(len(docs) / (float(ms.item()) * 1e-3), 1),
+            "note": "69 candidate muGraphs of the reference's search checkpoint, round-robin over ranks, fingerprint kernels + "
+                    "on-device comparison per candidate, all-gather of the verdicts; wall clock, median of 5"}
+
+
 def run_one_config(args):
     """`--only-config`: one of the other configurations alone (profiling, tuning); prints {"other_configs": {...}}."""
     import torch
@@ -586,7 +644,7 @@ def run_one_config(args):
     print(json.dumps({"other_configs": out}))
 
 
-def measure_other_configs(mg, rt, stream, timed, peaks, only=None, quick=False):
+def measure_other_configs(mg, rt, stream, timed, peaks, only=None, quick=False, world=1, rank=0):
     """Device-timed numbers for the remaining configurations (N = 1 only), each replayed from a CUDA graph:
     speculative decode with the causal draft window (fp16), dense prefill (bf16, tcgen05) and the matmul chain (both
     modes on the generic interpreters).  `only` = "c1" | "c3" | "c4" runs one; `quick` = few replays (profiling)."""
@@ -621,7 +679,7 @@ def measure_other_configs(mg, rt, stream, timed, peaks, only=None, quick=False):
 
     # ---- speculative decode: batch 4 x 8 KV heads = 32 units, 8 draft tokens x group 4 = 32 rows, KV 8192 -------------
     def config3():
-        units, rows, d, kv, splits, fr, window = 32, 32, 128, 8192, 16, 8, 8
+        units, rows, d, kv, splits, fr, window = 32 // world, 32, 128, 8192, 16, 8, 8   # units sharded over the ranks
         graphs = []
         for s in range(2):  # two buffer sets of 135 MB each: consecutive calls never share L2 contents
             g = mg.PyGraph(rt)
@@ -630,11 +688,12 @@ def measure_other_configs(mg, rt, stream, timed, peaks, only=None, quick=False):
             p1, p2 = mg.gqa_decode_plans(units, rows, d, kv, splits, fr)
             parts = g.customized([Q, K, V], p1); g.customized(parts, p2)
             g.set_causal_window(3, window)
-            Q.fill_data_seeded(900 + s, d ** -0.5); K.fill_data_seeded(910 + s, 1.0); V.fill_data_seeded(920 + s, 1.0)
+            Q.fill_data_seeded(900 + s + 50 * rank, d ** -0.5); K.fill_data_seeded(910 + s + 50 * rank, 1.0); V.fill_data_seeded(920 + s + 50 * rank, 1.0)
             graphs.append(g)
         us = replay_us(graphs_runner(graphs), 8)
         nbytes = 2 * units * rows * d * 2 + 2 * units * d * kv * 2
-        out["spec_decode_c3"] = {"us_per_call": round(us, 2), "hbm_gbs": round(nbytes / us / 1e3, 1),
+        out["spec_decode_c3"] = {"us_per_call": round(us, 2), "units_per_gpu": units, "n_gpus": world,
+                                 "hbm_gbs": round(nbytes / us / 1e3, 1),
                                  "frac_of_hbm_peak": round(nbytes / us / 1e3 / peaks["hbm_gbs"], 4), "bytes": nbytes,
                                  "roofline": hbm_roofline(nbytes, us, "attn_split_tc_kernel + attn_merge_rows_kernel"),
                                  "kernel": graphs[0].customized_info(3)["kernel_float"], "dtype": "fp16",
