@@ -260,80 +260,84 @@ def run_ours(args):
                                             "timed call %d" % s))
             checked_calls += 1
 
-    # ---- one kernel launch per call: resident graphs, several protocols ------------------------------------------
-    graphs = []
-    for s in range(nsets):
-        g = mg.PyGraph(rt)
-        Q = g.new_input((heads, GROUP, HEAD_DIM), mg.float16)
-        K = g.new_input((heads, HEAD_DIM, KV_LEN), mg.float16, k_layout)
-        V = g.new_input((heads, KV_LEN, HEAD_DIM), mg.float16, v_layout)
-        parts = g.customized([Q, K, V], plan1)
-        out = g.customized(parts, plan2)
-        seed = 5000 + 1000 * rank + s
-        Q.fill_data_seeded(3 * seed, HEAD_DIM ** -0.5)
-        K.fill_data_seeded(3 * seed + 1, 1.0)
-        V.fill_data_seeded(3 * seed + 2, 1.0)
-        graphs.append((g, (Q, K, V), out[0]))
-    info = graphs[0][0].customized_info(3)
-    info2 = graphs[0][0].customized_info(4)
-    for g, _, _ in graphs:
-        g.run(stream=sh, sync=False)
-    torch.cuda.synchronize()
-    pc_calls = max(nsets, 64)
-    lanes = [stream] + [torch.cuda.Stream() for _ in range(max(0, args.streams - 1))]
-
-    def record_calls(use):
-        """pc_calls launches; a graph always goes to the same lane, so two launches of one graph (they share the
-        graph's ticket counters and output buffers) are ordered by their stream."""
-        if len(use) > 1:
-            ev = torch.cuda.Event()
-            ev.record(stream)
-            for s in use[1:]:
-                s.wait_event(ev)
-        for c in range(pc_calls):
-            gi = c % nsets
-            graphs[gi][0].run(stream=use[gi % len(use)].cuda_stream, sync=False)
-        for s in use[1:]:
-            ev = torch.cuda.Event()
-            ev.record(s)
-            stream.wait_event(ev)
-
-    rt.set_launch_policy(mg.POLICY_LATENCY)
-    ordered_graph = mg.CapturedSequence(sh, lambda: record_calls([stream]))
-    rt.set_launch_policy(mg.POLICY_THROUGHPUT if args.streams > 1 else mg.POLICY_LATENCY)
-    streams_graph = mg.CapturedSequence(sh, lambda: record_calls(lanes))
-    rt.set_launch_policy(mg.POLICY_LATENCY)
-    reps = 40
-    ordered_us = timed(lambda: [ordered_graph.launch() for _ in range(reps)], 3, 2) / 3 / reps * 1000.0 / pc_calls
-    streams_us = timed(lambda: [streams_graph.launch() for _ in range(reps)], 3, 2) / 3 / reps * 1000.0 / pc_calls
-    mg.synchronize()
-    singles = []
-    for c in range(0 if args.no_latency_probes else 210):
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(stream)
-        graphs[c % nsets][0].run(stream=sh, sync=False)
-        e1.record(stream)
-        stream.synchronize()
-        if c >= 10:
-            singles.append(e0.elapsed_time(e1) * 1000.0)
-    single_us = statistics.median(singles) if singles else None
-    l2_resident_us = None if args.no_latency_probes else graphs[0][0].profile_op(3) * 1000.0
+    per_call_launch, ordered_us, single_us, graphs = None, None, None, []
     call_bytes = qb + kb + vb + ob
+    streams_graph = ordered_graph = None
+    if not args.no_per_call_launch:
+        # ---- one kernel launch per call: resident graphs, several protocols ------------------------------------------
+        graphs = []
+        for s in range(nsets):
+            g = mg.PyGraph(rt)
+            Q = g.new_input((heads, GROUP, HEAD_DIM), mg.float16)
+            K = g.new_input((heads, HEAD_DIM, KV_LEN), mg.float16, k_layout)
+            V = g.new_input((heads, KV_LEN, HEAD_DIM), mg.float16, v_layout)
+            parts = g.customized([Q, K, V], plan1)
+            out = g.customized(parts, plan2)
+            seed = 5000 + 1000 * rank + s
+            Q.fill_data_seeded(3 * seed, HEAD_DIM ** -0.5)
+            K.fill_data_seeded(3 * seed + 1, 1.0)
+            V.fill_data_seeded(3 * seed + 2, 1.0)
+            graphs.append((g, (Q, K, V), out[0]))
+        info = graphs[0][0].customized_info(3)
+        info2 = graphs[0][0].customized_info(4)
+        for g, _, _ in graphs:
+            g.run(stream=sh, sync=False)
+        torch.cuda.synchronize()
+        pc_calls = max(nsets, 64)
+        lanes = [stream] + [torch.cuda.Stream() for _ in range(max(0, args.streams - 1))]
 
-    def frac_of(us):
-        return None if not us else round(call_bytes / (us * 1e-6) / 1e9 / peaks["hbm_gbs"], 4)
+        def record_calls(use):
+            """pc_calls launches; a graph always goes to the same lane, so two launches of one graph (they share the
+            graph's ticket counters and output buffers) are ordered by their stream."""
+            if len(use) > 1:
+                ev = torch.cuda.Event()
+                ev.record(stream)
+                for s in use[1:]:
+                    s.wait_event(ev)
+            for c in range(pc_calls):
+                gi = c % nsets
+                graphs[gi][0].run(stream=use[gi % len(use)].cuda_stream, sync=False)
+            for s in use[1:]:
+                ev = torch.cuda.Event()
+                ev.record(s)
+                stream.wait_event(ev)
 
-    per_call_launch = {
-        "streams_us_per_call": round(streams_us, 3), "streams": args.streams, "streams_frac_of_hbm_peak": frac_of(streams_us),
-        "stream_ordered_us_per_call": round(ordered_us, 3), "stream_ordered_frac_of_hbm_peak": frac_of(ordered_us),
-        "single_call_us_median": None if single_us is None else round(single_us, 3),
-        "single_call_frac_of_hbm_peak": frac_of(single_us),
-        "l2_resident_profile_us": None if l2_resident_us is None else round(l2_resident_us, 3),
-        "calls": pc_calls, "resident_buffer_sets": nsets, "kernel_op1": info["kernel_float"], "kernel_op2": info2["kernel_float"],
-        "note": "one fused kernel per call; streams: calls spread over lanes inside a captured step, blocks sized for "
-                "throughput; stream_ordered: one stream, each call after the previous one (programmatic dependent "
-                "launch), blocks sized for latency; single: events around one un-captured call, median of 200; "
-                "l2_resident: the reference's profile protocol (1024 + 1024 launches of op1 on the same buffers)"}
+        rt.set_launch_policy(mg.POLICY_LATENCY)
+        ordered_graph = mg.CapturedSequence(sh, lambda: record_calls([stream]))
+        rt.set_launch_policy(mg.POLICY_THROUGHPUT if args.streams > 1 else mg.POLICY_LATENCY)
+        streams_graph = mg.CapturedSequence(sh, lambda: record_calls(lanes))
+        rt.set_launch_policy(mg.POLICY_LATENCY)
+        reps = 40
+        ordered_us = timed(lambda: [ordered_graph.launch() for _ in range(reps)], 3, 2) / 3 / reps * 1000.0 / pc_calls
+        streams_us = timed(lambda: [streams_graph.launch() for _ in range(reps)], 3, 2) / 3 / reps * 1000.0 / pc_calls
+        mg.synchronize()
+        singles = []
+        for c in range(0 if args.no_latency_probes else 210):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            graphs[c % nsets][0].run(stream=sh, sync=False)
+            e1.record(stream)
+            stream.synchronize()
+            if c >= 10:
+                singles.append(e0.elapsed_time(e1) * 1000.0)
+        single_us = statistics.median(singles) if singles else None
+        l2_resident_us = None if args.no_latency_probes else graphs[0][0].profile_op(3) * 1000.0
+        call_bytes = qb + kb + vb + ob
+
+        def frac_of(us):
+            return None if not us else round(call_bytes / (us * 1e-6) / 1e9 / peaks["hbm_gbs"], 4)
+
+        per_call_launch = {
+            "streams_us_per_call": round(streams_us, 3), "streams": args.streams, "streams_frac_of_hbm_peak": frac_of(streams_us),
+            "stream_ordered_us_per_call": round(ordered_us, 3), "stream_ordered_frac_of_hbm_peak": frac_of(ordered_us),
+            "single_call_us_median": None if single_us is None else round(single_us, 3),
+            "single_call_frac_of_hbm_peak": frac_of(single_us),
+            "l2_resident_profile_us": None if l2_resident_us is None else round(l2_resident_us, 3),
+            "calls": pc_calls, "resident_buffer_sets": nsets, "kernel_op1": info["kernel_float"], "kernel_op2": info2["kernel_float"],
+            "note": "one fused kernel per call; streams: calls spread over lanes inside a captured step, blocks sized for "
+                    "throughput; stream_ordered: one stream, each call after the previous one (programmatic dependent "
+                    "launch), blocks sized for latency; single: events around one un-captured call, median of 200; "
+                    "l2_resident: the reference's profile protocol (1024 + 1024 launches of op1 on the same buffers)"}
 
     # ---- end to end through the public API with host buffers -----------------------------------------
     host_in = torch.empty(sum(elems), dtype=torch.int16).pin_memory()
@@ -402,15 +406,16 @@ def run_ours(args):
             "hbm_gbs": round(call_bytes / (us_per_call * 1e-6) / 1e9, 1),
             "output_check": {"calls_checked": checked_calls, "worst_rel_err_vs_fp32": round(worst, 6), "tolerance": 2e-3},
             "per_call_launch": per_call_launch,
-            "stream_ordered_us_per_call": round(ordered_us, 3),
+            "stream_ordered_us_per_call": None if ordered_us is None else round(ordered_us, 3),
             "single_call_us_median": None if single_us is None else round(single_us, 3),
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(gpu_launches),
             "clocks": clocks, "fingerprint": fingerprint, "candidates": candidates, "other_configs": others,
         }
         print(json.dumps(line))
     batched_graph.close()
-    streams_graph.close()
-    ordered_graph.close()
+    if streams_graph is not None:
+        streams_graph.close()
+        ordered_graph.close()
     for g, _, _ in reversed(graphs):
         g.close()
     bg.close()
@@ -946,6 +951,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-reference-gpu", action="store_true", help="skip the reference's own GPU fingerprint kernel")
     ap.add_argument("--no-other-configs", action="store_true", help="skip the extra measurements of the other configurations")
+    ap.add_argument("--no-per-call-launch", action="store_true",
+                    help="skip the protocols that launch one kernel per call (short launch lists for the profiler)")
     ap.add_argument("--no-latency-probes", action="store_true",
                     help="skip the single-call latency and the 1024 + 1024 launch L2-resident measurement (short launch lists)")
     ap.add_argument("--only-config", default=None, choices=["c1", "c3", "c4"],
