@@ -163,7 +163,8 @@ int mg_runtime_set_launch_policy(mg_runtime *rt, int policy) {
 
 static_assert(MG_OPT_ATTN_STAGES == MGD_OPT_ATTN_STAGES && MG_OPT_ATTN_TILE_GROUPS == MGD_OPT_ATTN_TILE_GROUPS &&
                   MG_OPT_ATTN_ENGINE == MGD_OPT_ATTN_ENGINE && MG_OPT_ROWS_ENGINE == MGD_OPT_ROWS_ENGINE &&
-                  MG_OPT_INTERP_THREADS == MGD_OPT_INTERP_THREADS && MG_OPT_WAIT_LIMIT == MGD_OPT_WAIT_LIMIT,
+                  MG_OPT_INTERP_THREADS == MGD_OPT_INTERP_THREADS && MG_OPT_WAIT_LIMIT == MGD_OPT_WAIT_LIMIT &&
+                  MG_OPT_ATTN_PERSISTENT == MGD_OPT_ATTN_PERSISTENT,
               "the option keys of the two headers are the same numbers");
 
 int mg_runtime_set_option(mg_runtime *rt, int32_t key, int32_t value) {
@@ -426,7 +427,7 @@ int mg_op_profile(mg_graph *g, int32_t idx, int32_t warmup, int32_t iters, float
 }
 
 // Shared body of the two batched entry points.  Workspace layout: every customized-op output except the final one
-// gets num_sets * elements 16-bit values (256-byte aligned); then, in float mode, heads * num_sets ticket counters
+// gets num_sets * elements 16-bit values (256-byte aligned); then heads * num_sets ticket counters
 // for each split-KV operator that is issued together with its merge operator.
 static int run_batched(mg_graph *g, bool fp, int32_t num_sets, const void *const *in_ptrs, void *out_ptr, void *workspace,
                        size_t *workspace_bytes, void *stream) {
@@ -450,19 +451,18 @@ static int run_batched(mg_graph *g, bool fp, int32_t num_sets, const void *const
       slots.push_back({work[w], (int)t, need, e});
       need += ((size_t)e * 2 * (size_t)num_sets + 255) / 256 * 256;
     }
-  // Float mode issues a split-KV operator and the merge that consumes it as one launch (fingerprint sweeps are
-  // faster with the merge as a launch of its own over all sets).
+  // A split-KV operator and the merge that consumes it are issued as one launch.  The partials between them live in
+  // the workspace and nobody else reads them, which lets the kernel sum consecutive splits of a head on the chip.
   std::vector<size_t> ticket_offset(work.size(), (size_t)-1);
   size_t const tickets_begin = need;
-  if (!fp)
-    for (size_t w = 0; w + 1 < work.size(); w++) {
-      auto *c = static_cast<kernel::KNCustomizedOp *>(work[w]);
-      if (c->selected_kernel(false) == mg::KERNEL_ATTN_SPLIT && c->can_fuse_with(work[w + 1], false)) {
-        ticket_offset[w] = need;
-        need += ((size_t)c->plan.grid_dim.x * (size_t)num_sets * sizeof(int) + 255) / 256 * 256;
-        w++;
-      }
+  for (size_t w = 0; w + 1 < work.size(); w++) {
+    auto *c = static_cast<kernel::KNCustomizedOp *>(work[w]);
+    if (c->selected_kernel(fp) == mg::KERNEL_ATTN_SPLIT && c->can_fuse_with(work[w + 1], fp)) {
+      ticket_offset[w] = need;
+      need += ((size_t)c->plan.grid_dim.x * (size_t)num_sets * sizeof(int) + 255) / 256 * 256;
+      w++;
     }
+  }
   if (!workspace) {
     *workspace_bytes = need;
     return MG_OK;
@@ -508,8 +508,9 @@ static int run_batched(mg_graph *g, bool fp, int32_t num_sets, const void *const
       void const *mp;
       long long ms;
       if (!locate(m->output_tensors[0], &mp, &ms)) return fail(MG_ERR_INVALID_GRAPH, "internal: output slot missing");
-      st = c->launch_fused_sets(m, false, num_sets, in, is, out, os, const_cast<void *>(mp), ms,
-                                reinterpret_cast<int *>((char *)workspace + ticket_offset[w]), stream);
+      st = c->launch_fused_sets(m, fp, num_sets, in, is, out, os, const_cast<void *>(mp), ms,
+                                reinterpret_cast<int *>((char *)workspace + ticket_offset[w]), stream,
+                                /*partials_are_scratch=*/true); // the intermediates live in the caller's workspace
       w++;
     } else {
       st = fp ? c->launch_fingerprint_sets(num_sets, in, is, out, os, stream) : c->launch_float_sets(num_sets, in, is, out, os, stream);

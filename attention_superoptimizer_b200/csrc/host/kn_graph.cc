@@ -823,7 +823,8 @@ int KNCustomizedOp::launch_split(bool fp, int num_sets, void const *const *in, l
     opts.merged_set_stride = merge->set_stride;
     outs.push_back(range_of(merge->out, merge->bytes));
   }
-  opts.overlap = 1 | (inputs_untouched(stream, ins) ? 2 : 0) | (DeviceMemoryManager::get_instance()->launch_policy == 1 ? 4 : 0);
+  opts.overlap = 1 | (inputs_untouched(stream, ins) ? 2 : 0) | (DeviceMemoryManager::get_instance()->launch_policy == 1 ? 4 : 0) |
+                 (merge != nullptr && merge->partials_are_scratch ? 8 : 0);
   int st = fp ? mgd_launch_attn_split_fingerprint_ex(&sp, (uint16_t const *)in[0], (uint16_t const *)in[1],
                                                      (uint16_t const *)in[2], (uint16_t *)out[0], (uint16_t *)out[1],
                                                      &opts, stream)
@@ -870,7 +871,8 @@ int KNCustomizedOp::launch_fused(KNCustomizedOp *merge, bool fp, void *stream) {
 
 int KNCustomizedOp::launch_fused_sets(KNCustomizedOp *merge, bool fp, int num_sets, void const *const *in,
                                       long long const *in_stride, void *const *out, long long const *out_stride,
-                                      void *merged_out, long long merged_stride, int *tickets, void *stream) {
+                                      void *merged_out, long long merged_stride, int *tickets, void *stream,
+                                      bool partials_are_scratch) {
   if (int dry_st = refuse_if_dry()) return dry_st;
   if (!fp && kernel_float_ == mg::KERNEL_ATTN_ROWS) {
     if (num_sets != 1) {
@@ -886,7 +888,8 @@ int KNCustomizedOp::launch_fused_sets(KNCustomizedOp *merge, bool fp, int num_se
   void *o[2] = {out[o_output_], out[1 - o_output_]};
   long long os[2] = {out_stride[o_output_], out_stride[1 - o_output_]};
   FusedMerge fm{merged_out, merged_stride,
-                ((size_t)(num_sets - 1) * (size_t)merged_stride + merge->output_tensors[0].num_elements()) * 2, tickets};
+                ((size_t)(num_sets - 1) * (size_t)merged_stride + merge->output_tensors[0].num_elements()) * 2, tickets,
+                partials_are_scratch};
   return launch_split(fp, num_sets, in, in_stride, o, os, &fm, stream);
 }
 

@@ -28,9 +28,13 @@ template <int KIND> __device__ __forceinline__ uint32_t merge_pack(float a, floa
 // op: [m][splits * D], rp: [m][splits], dst: [m][D] of one head; t / nt: index and count of the participating
 // threads.  Every thread also sums its row's denominators itself (a few 16-byte loads that travel with the others):
 // one L2 round trip per 16 splits, no barrier.
+// held: bit s set = slot s holds a sum (bits beyond 63 count as set).  The split-KV kernel clears bits when it has
+// summed several consecutive splits on the chip and written only the first slot of the run; the other slots were
+// never written: they are loaded with the others (the memory is there) and left out of the sums.
 template <int KIND, int D>
 __device__ __forceinline__ void merge_head(uint16_t const *op, uint16_t const *rp, uint16_t *dst, int m, int splits,
-                                           int t, int nt) {
+                                           int t, int nt, uint64_t held = ~0ull) {
+  auto holds = [&](int sp) { return sp >= 64 || ((held >> sp) & 1ull) != 0; };
   constexpr int kGroups = D / 8;
   size_t const out_ld = (size_t)splits * D;
   bool const r_vec = (splits & 7) == 0 && (reinterpret_cast<uintptr_t>(rp) & 15) == 0; // rows of R are 16-byte pieces
@@ -59,12 +63,12 @@ __device__ __forceinline__ void merge_head(uint16_t const *op, uint16_t const *r
       if (KIND == kMergeFingerprint) iden += v;
       else fden += merge_to_float<KIND>(v);
     };
-    auto add_den8 = [&](uint4 w) {
+    auto add_den8 = [&](uint4 w, int first) { // denominators of slots first .. first + 7
       uint32_t const words[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
       for (int i = 0; i < 4; i++) {
-        add_den((uint16_t)(words[i] & 0xFFFFu));
-        add_den((uint16_t)(words[i] >> 16));
+        if (holds(first + 2 * i)) add_den((uint16_t)(words[i] & 0xFFFFu));
+        if (holds(first + 2 * i + 1)) add_den((uint16_t)(words[i] >> 16));
       }
     };
     int sp = 0;
@@ -81,13 +85,15 @@ __device__ __forceinline__ void merge_head(uint16_t const *op, uint16_t const *r
         for (int i = 0; i < 16; i++) rs[i] = __ldcg(rrow + sp + i);
       }
 #pragma unroll
-      for (int i = 0; i < 16; i++) add(w[i]);
+      for (int i = 0; i < 16; i++)
+        if (holds(sp + i)) add(w[i]);
       if (r_vec) {
-        add_den8(rv[0]);
-        add_den8(rv[1]);
+        add_den8(rv[0], sp);
+        add_den8(rv[1], sp + 8);
       } else {
 #pragma unroll
-        for (int i = 0; i < 16; i++) add_den(rs[i]);
+        for (int i = 0; i < 16; i++)
+          if (holds(sp + i)) add_den(rs[i]);
       }
     }
     for (; sp + 4 <= splits; sp += 4) {
@@ -99,15 +105,17 @@ __device__ __forceinline__ void merge_head(uint16_t const *op, uint16_t const *r
         rs[i] = __ldcg(rrow + sp + i);
       }
 #pragma unroll
-      for (int i = 0; i < 4; i++) {
-        add(w[i]);
-        add_den(rs[i]);
+      for (int i = 0; i < 4; i++)
+        if (holds(sp + i)) {
+          add(w[i]);
+          add_den(rs[i]);
+        }
+    }
+    for (; sp < splits; sp++)
+      if (holds(sp)) {
+        add(__ldcg(reinterpret_cast<uint4 const *>(src + (size_t)sp * D)));
+        add_den(__ldcg(rrow + sp));
       }
-    }
-    for (; sp < splits; sp++) {
-      add(__ldcg(reinterpret_cast<uint4 const *>(src + (size_t)sp * D)));
-      add_den(__ldcg(rrow + sp));
-    }
     uint32_t o[4];
     if (KIND == kMergeFingerprint) {
       uint32_t const den = iden % PQ;

@@ -117,13 +117,20 @@ struct AttnSplitParams {
   long long merged_set_stride;
   int early_loads;      // tile loads may be issued before the wait on the previous kernel of the stream
   int wait_limit;       // polls before a tile wait gives up
+  int num_sets;
+  int sum_runs;         // persistent with a fused merge whose partials are scratch: consecutive splits of a head
+                        // are summed in the accumulators, only sums that straddle blocks go through memory
+  int persistent;       // fewer blocks than work items: a block walks items blockIdx.x, + gridDim.x, ... and the tile
+                        // ring runs on across item boundaries (the reduction scratch then has room of its own)
 };
 
 // Shared-memory plan: [stages x (K tile, V tile)] (1024-byte aligned) | reduction scratch | barriers | exp table
 // FORM: bit 0 = K staged as [kv][d] (else [d][kv]); bit 1 = V staged as [kv][d] (else [d][kv]).  A compile-time
 // property so that every ldmatrix address is one XOR and one ADD away from a per-lane constant.
-template <int MODE, int DH, int FORM>
-__global__ void __launch_bounds__(512)
+// PERSIST: the block walks several work items (a compile-time property: the one-item kernel keeps no item state in
+// registers across its loop; the walking one is launched with 128 threads, three blocks to an SM).
+template <int MODE, int DH, int FORM, bool PERSIST>
+__global__ void __launch_bounds__(PERSIST ? 128 : 512, PERSIST ? 3 : 1)
 attn_split_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
                   const __grid_constant__ AttnSplitParams p) {
   using acc_t = typename Acc<MODE>::type;
@@ -142,18 +149,35 @@ attn_split_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
   int const tgroup = (warp >> 2) / groups;  // which of the tiles processed concurrently
   int const g = lane >> 2, t = lane & 3;
 
-  int64_t const b = blockIdx.x;
-  int const split = (int)(b % p.splits), head = (int)((b / p.splits) % p.heads);
-  int64_t const set = b / ((int64_t)p.splits * p.heads);
-  int const batch = (int)(set * p.heads + head); // tensor maps fold (set, head) into one coordinate
+  // Work items: one (set, head, split) each, split fastest.  A plain launch has one block per item.  A persistent
+  // launch has fewer blocks than items and block b takes a contiguous run of them, [lo, lo + n_local): its tile ring
+  // keeps running across item boundaries, and when the merge is fused, consecutive splits of one head simply keep
+  // accumulating in registers - partials go to memory only where a head's splits straddle two blocks.
+  // (item numbers fit 31 bits: the launch refuses more)
+  uint32_t const n_items = (uint32_t)p.splits * (uint32_t)p.heads * (uint32_t)p.num_sets;
+  uint32_t const per_block = PERSIST ? n_items / gridDim.x : 1u, extra = PERSIST ? n_items % gridDim.x : 0u; // the first `extra` blocks take one more
+  uint32_t const lo = PERSIST ? blockIdx.x * per_block + (blockIdx.x < extra ? blockIdx.x : extra) : blockIdx.x;
+  int const n_local = PERSIST ? (int)per_block + (blockIdx.x < extra ? 1 : 0) : 1;
+  int const total_tiles = n_local * p.forloop;
+  bool const fused_runs = PERSIST && p.sum_runs;
+  int split = 0, head = 0, kv_base = 0; // of the item being computed
+  int set = 0;
+  auto select_item = [&](int li) {
+    uint32_t const x = lo + (uint32_t)li, unit = x / (uint32_t)p.splits; // unit = set * heads + head
+    split = (int)(x - unit * (uint32_t)p.splits);
+    set = (int)(unit / (uint32_t)p.heads);
+    head = (int)(unit - (uint32_t)set * (uint32_t)p.heads);
+    kv_base = split * p.forloop * kTile; // first KV position of the item
+  };
 
   uint32_t const stage_base = smem_u32(smem);
   int const rows_scratch = MODE == kFingerprint ? 4 : (p.m < 16 ? p.m : 16);
-  // the reduction scratch reuses the stage memory once every tile has been consumed
-  acc_t *scratch = reinterpret_cast<acc_t *>(smem);
+  // the reduction scratch reuses the stage memory once every tile has been consumed; a persistent block has tiles of
+  // its next item arriving by then, so its scratch sits behind the stages
   size_t const scratch_bytes = (size_t)(blockDim.x >> 5) * rows_scratch * (DH + 4) * sizeof(acc_t);
   size_t const stage_bytes = (size_t)p.stages * 2 * kTileBytes;
-  size_t const data_bytes = ((scratch_bytes > stage_bytes ? scratch_bytes : stage_bytes) + 15) & ~(size_t)15;
+  acc_t *scratch = reinterpret_cast<acc_t *>(smem + (PERSIST ? stage_bytes : 0));
+  size_t const data_bytes = ((PERSIST ? stage_bytes + scratch_bytes : (scratch_bytes > stage_bytes ? scratch_bytes : stage_bytes)) + 15) & ~(size_t)15;
   uint64_t *bars = reinterpret_cast<uint64_t *>(smem + data_bytes);
   uint16_t *exp_tab = reinterpret_cast<uint16_t *>(bars + kMaxStages);
   __shared__ int s_failed;
@@ -169,11 +193,22 @@ attn_split_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
     for (int i = tid; i < (int)Q; i += blockDim.x) exp_tab[i] = (uint16_t)((c_tables.e[i] * Q_MUL_P_MOD_1) % PQ);
   __syncthreads();
 
-  int const kv_base = split * p.forloop * kTile; // first KV position of this block
-  auto issue = [&](int it, int s) {
+  // Requests the next tile of this block's tile sequence (items in order, `forloop` tiles each) into stage s.
+  // Thread 0 keeps the coordinates of that tile: KV position and (set, head), which the tensor maps fold into one
+  // coordinate.
+  // (kept in shared memory: registers of every thread are scarcer than one thread's few shared-memory accesses)
+  __shared__ int s_next_kv, s_next_batch, s_issued; // s_issued: tiles requested so far; tile i lands in stage i % stages
+  auto issue = [&](int s) {
     uint32_t bar = smem_u32(&bars[s]);
     uint32_t kdst = stage_base + (uint32_t)(s * 2 * kTileBytes), vdst = kdst + kTileBytes;
-    int kv0 = kv_base + it * kTile;
+    int const kv0 = s_next_kv, batch = s_next_batch;
+    if (PERSIST && kv0 + kTile == p.kv_len) { // the head's last tile: on to the next head
+      s_next_kv = 0;
+      s_next_batch = batch + 1;
+    } else {
+      s_next_kv = kv0 + kTile;
+    }
+    s_issued++;
     mbar_expect_tx(bar, 2 * kTileBytes);
     if (kKRowsKv) {
       for (int c = 0; c < DH / 64; c++) tma_load_3d(kdst + c * (kTile * 128), &k_map, bar, c * 64, kv0, batch);
@@ -189,7 +224,7 @@ attn_split_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
   // ---- Q fragments, resident in registers -----------------------------------------------------------
   uint32_t qa[kKSteps][4];
   auto load_q = [&]() {
-    uint16_t const *q = static_cast<uint16_t const *>(p.q) + set * p.q_set_stride + (int64_t)head * p.m * DH;
+    uint16_t const *q = static_cast<uint16_t const *>(p.q) + (int64_t)set * p.q_set_stride + (int64_t)head * p.m * DH;
     if (MODE == kFingerprint) {
       int row = group * 4 + (g & 3);
       bool valid = row < p.m;
@@ -216,17 +251,17 @@ attn_split_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
       }
     }
   };
-  int issued = 0; // tiles requested so far (thread 0 only): tile i lands in stage i % stages
   auto issue_first = [&]() {
     if (tid == 0) {
-      int first = p.forloop < p.stages ? p.forloop : p.stages;
-      for (int it = 0; it < first; it++) issue(it, it);
-      issued = first;
+      int first = total_tiles < p.stages ? total_tiles : p.stages;
+      s_next_kv = kv_base, s_next_batch = set * p.heads + head, s_issued = 0; // select_item(0) came first
+      for (int gt = 0; gt < first; gt++) issue(gt);
     }
   };
   // Ordering against the previous kernel of the stream (programmatic dependent launch): nothing is written
   // to global memory, and no input that kernel may have produced is read, before griddepcontrol.wait; the next
   // kernel is released right after, so at most two kernels of a stream are ever in flight.
+  select_item(0);
   if (p.early_loads) {
     issue_first();
     load_q();
@@ -238,16 +273,23 @@ attn_split_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
   }
   ptx::grid_launch_dependents();
 
+  // stage and barrier phase of this warp's tile, and stage of the round's first tile, kept without divisions
+  // (tile_groups <= stages, so one conditional subtraction per round is enough); they run on across items
+  int s = tgroup, round_s = 0;
+  uint32_t phase = 0;
+  bool failed = false;
+  // Accumulators of the run of splits being summed: one item, or with a fused merge every split of the head that this
+  // block holds.  run_first = the split the run began with (the slot its partial goes to).
   acc_t oacc[2 * kNPairs][4];
 #pragma unroll
   for (int i = 0; i < 2 * kNPairs; i++)
 #pragma unroll
     for (int j = 0; j < 4; j++) oacc[i][j] = 0;
   acc_t racc0 = 0, racc1 = 0; // row sums of E: float: rows g and g+8; fingerprint: row g (lanes 0-15)
+  int run_first = split;
 
   int const mi = lane >> 3, rr = lane & 7; // ldmatrix: this lane addresses row rr of matrix mi
   int const kv0 = slice * 16;               // this warp's KV positions inside a tile
-  bool failed = false;
 
   // Per-lane pieces of the ldmatrix addresses (see tile_addr): what is left per step is a compile-time offset
   // and, where the step moves along a swizzled row, one XOR.
@@ -280,10 +322,7 @@ attn_split_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
 
   // Tiles are consumed in rounds of `tile_groups`: warp group tgroup takes tile round*tile_groups + tgroup.
   int const rounds = (p.forloop + p.tile_groups - 1) / p.tile_groups;
-  // stage and barrier phase of this warp's tile, and stage of the round's first tile, kept without divisions
-  // (tile_groups <= stages, so one conditional subtraction per round is enough)
-  int s = tgroup, round_s = 0;
-  uint32_t phase = 0;
+  for (int li = 0; li < n_local; li++) {
   for (int round = 0; round < rounds; round++) {
     int const it = round * p.tile_groups + tgroup;
     bool const active = it < p.forloop;
@@ -366,15 +405,14 @@ attn_split_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
 
     } // active
     // ---- refill the stages of this round once every warp has read them -----------------------------------
-    if (p.forloop > p.stages) {
+    if (total_tiles > p.stages) {
       __syncthreads();
       if (tid == 0 && !failed) // a block that has given up requests nothing more
         for (int j = 0; j < p.tile_groups; j++) {
-          int nxt = round * p.tile_groups + j + p.stages;
+          int nxt = li * p.forloop + round * p.tile_groups + j + p.stages; // (a persistent block has tile_groups = 1)
           int ns = round_s + j >= p.stages ? round_s + j - p.stages : round_s + j; // the stage tile nxt - stages used
-          if (nxt < p.forloop) {
-            issue(nxt, ns);
-            issued = nxt + 1;
+          if (nxt < total_tiles) {
+            issue(ns);
           }
         }
     }
@@ -384,6 +422,23 @@ attn_split_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
     if (round_s >= p.stages) round_s -= p.stages;
   }
 
+  // A run ends with the head's last split or the block's last item; without a fused merge every item is a run.
+  int const covered = split - run_first + 1; // splits summed in the accumulators
+  bool const run_ends = !fused_runs || split == p.splits - 1 || li == n_local - 1;
+  bool const whole_head = fused_runs && covered == p.splits; // nothing of this head is anywhere else: finish it here
+  int const run_head = head, run_set = set, run_slot = run_first; // where the run's sums go
+  bool new_rows = false; // the next item has other query rows
+  if (PERSIST && li + 1 < n_local) {
+    select_item(li + 1);
+    new_rows = head != run_head || set != run_set;
+    if (run_ends) run_first = split;
+    if (new_rows) { // on their way into L2 while this run is written out (m * DH 16-bit values, 128-byte lines)
+      char const *rows = static_cast<char const *>(p.q) + ((int64_t)set * p.q_set_stride + (int64_t)head * p.m * DH) * 2;
+      if (tid * 128 < p.m * DH * 2) asm volatile("prefetch.global.L2 [%0];" ::"l"(rows + tid * 128));
+    }
+  }
+  if (!run_ends) continue; // (a run that goes on stays with its head: no new rows)
+
   if (failed) s_failed = 1;
   __syncthreads(); // also: every tile has been read, the stage memory may be reused as scratch
   if (s_failed) { // a bounded wait gave up: flag it and leave the outputs alone
@@ -391,6 +446,7 @@ attn_split_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
       atomicExch(p.status, 1);
       // Tile loads still in flight must land before this block's shared memory is handed to another block:
       // stage s received tiles s, s + stages, ...; wait (bounded again) for the last of them.
+      int const issued = s_issued;
       for (int st = 0; st < p.stages && st < issued; st++) {
         int loads = (issued - st + p.stages - 1) / p.stages;
         mbar_wait(smem_u32(&bars[st]), (uint32_t)((loads - 1) & 1));
@@ -398,10 +454,12 @@ attn_split_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
       // The head's ticket counter must still come back to zero for the next launch: take the ticket, and reset
       // the counter if this block is the last of its head.  (A healthy last block merges whatever partials there
       // are; the status word tells the host that the outputs of this launch are incomplete.)
-      if (p.merged_out != nullptr) {
-        int ticket = atomicAdd(&p.tickets[set * p.heads + head], 1);
-        if (ticket == p.splits - 1) p.tickets[set * p.heads + head] = 0;
-      }
+      if (p.merged_out != nullptr)
+        for (int rest = li - (covered - 1); rest < n_local; rest++) { // the open run and the items not reached
+          int const unit = (int)((lo + (uint32_t)rest) / (uint32_t)p.splits);
+          int ticket = atomicAdd(&p.tickets[unit], 1);
+          if (ticket == p.splits - 1) p.tickets[unit] = 0;
+        }
     }
     return;
   }
@@ -449,9 +507,34 @@ attn_split_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
 
   int const rows_per_group = kRowsPerGroup;
   int const out_ld = p.splits * DH;
-  uint16_t *o_out = static_cast<uint16_t *>(p.o_part) + set * p.o_set_stride + (int64_t)head * p.m * out_ld + split * DH;
-  uint16_t *r_out = static_cast<uint16_t *>(p.r_part) + set * p.r_set_stride + (int64_t)head * p.m * p.splits + split;
+  // a run's sums go to the slot of its first split
+  uint16_t *o_out = static_cast<uint16_t *>(p.o_part) + (int64_t)run_set * p.o_set_stride + (int64_t)run_head * p.m * out_ld + run_slot * DH;
+  uint16_t *r_out = static_cast<uint16_t *>(p.r_part) + (int64_t)run_set * p.r_set_stride + (int64_t)run_head * p.m * p.splits + run_slot;
+  uint16_t *final_out = p.merged_out == nullptr ? nullptr : static_cast<uint16_t *>(p.merged_out) + (int64_t)run_set * p.merged_set_stride + (int64_t)run_head * p.m * DH;
+  __shared__ acc_t s_den[32]; // row sums of a head that is finished in place
   // warp index = (tile group * groups + row group) * 4 + slice: sum over tile groups and slices.
+  for (int i = tid; i < groups * rows_scratch; i += blockDim.x) {
+    int lr = i % rows_scratch, gr = i / rows_scratch, row = gr * rows_per_group + lr;
+    if (row >= p.m) continue;
+    acc_t a = 0;
+    for (int tg = 0; tg < p.tile_groups; tg++)
+#pragma unroll
+      for (int sl = 0; sl < 4; sl++) {
+        acc_t v = scratch[(size_t)((tg * groups + gr) * 4 + sl) * rows_scratch * ld + lr * ld + DH];
+        if (MODE == kFingerprint) a = (acc_t)(((uint32_t)a + (uint32_t)v) % PQ);
+        else a += v;
+      }
+    if (whole_head) {
+      s_den[i] = a;
+      continue;
+    }
+    uint16_t v;
+    if (MODE == kFingerprint) v = (uint16_t)((uint32_t)a % PQ);
+    else if (MODE == kF16) { __half h = __float2half_rn((float)a); v = *reinterpret_cast<uint16_t *>(&h); }
+    else { __nv_bfloat16 h = __float2bfloat16_rn((float)a); v = *reinterpret_cast<uint16_t *>(&h); }
+    r_out[(size_t)row * p.splits] = v;
+  }
+  if (whole_head) __syncthreads();
   // A thread keeps one pair of adjacent columns (one 32-bit store) and walks down the rows.
   {
     int const c = (tid % (DH / 2)) * 2, row_step = blockDim.x / (DH / 2);
@@ -476,50 +559,64 @@ attn_split_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
           if (MODE == kFingerprint) { a0 = (acc_t)((uint32_t)a0 % PQ); a1 = (acc_t)((uint32_t)a1 % PQ); }
         }
         uint32_t packed;
+        if (whole_head) { // the division of the merge, on sums that never left the chip
+          acc_t const den = s_den[gr * rows_scratch + lr];
+          if (MODE == kFingerprint) packed = field_div((uint32_t)a0, (uint32_t)den % PQ) | (field_div((uint32_t)a1, (uint32_t)den % PQ) << 16);
+          else if (MODE == kF16) packed = pack_f16((float)a0 / (float)den, (float)a1 / (float)den);
+          else packed = pack_bf16((float)a0 / (float)den, (float)a1 / (float)den);
+          *reinterpret_cast<uint32_t *>(final_out + (size_t)row * DH + c) = packed;
+          continue;
+        }
         if (MODE == kFingerprint) packed = (uint32_t)a0 | ((uint32_t)a1 << 16);
         else if (MODE == kF16) packed = pack_f16((float)a0, (float)a1);
         else packed = pack_bf16((float)a0, (float)a1);
         *reinterpret_cast<uint32_t *>(o_out + (size_t)row * out_ld + c) = packed;
       }
   }
-  for (int i = tid; i < groups * rows_scratch; i += blockDim.x) {
-    int lr = i % rows_scratch, gr = i / rows_scratch, row = gr * rows_per_group + lr;
-    if (row >= p.m) continue;
-    acc_t a = 0;
-    for (int tg = 0; tg < p.tile_groups; tg++)
-#pragma unroll
-      for (int sl = 0; sl < 4; sl++) {
-        acc_t v = scratch[(size_t)((tg * groups + gr) * 4 + sl) * rows_scratch * ld + lr * ld + DH];
-        if (MODE == kFingerprint) a = (acc_t)(((uint32_t)a + (uint32_t)v) % PQ);
-        else a += v;
-      }
-    uint16_t v;
-    if (MODE == kFingerprint) v = (uint16_t)((uint32_t)a % PQ);
-    else if (MODE == kF16) { __half h = __float2half_rn((float)a); v = *reinterpret_cast<uint16_t *>(&h); }
-    else { __nv_bfloat16 h = __float2bfloat16_rn((float)a); v = *reinterpret_cast<uint16_t *>(&h); }
-    r_out[(size_t)row * p.splits] = v;
-  }
 
-  // ---- optional: the last block of this head merges the head's partials ------------------------------------
-  if (p.merged_out != nullptr) {
+  // ---- optional: the block that completes a head's splits merges the head's partials -----------------------
+  if (p.merged_out != nullptr && !whole_head) {
     __shared__ int s_last;
     __threadfence();
     __syncthreads();
+    int const unit = run_set * p.heads + run_head;
     if (tid == 0) {
-      int ticket = atomicAdd(&p.tickets[set * p.heads + head], 1);
-      s_last = ticket == p.splits - 1;
+      int ticket = atomicAdd(&p.tickets[unit], covered);
+      s_last = ticket + covered == p.splits;
     }
     __syncthreads();
     if (s_last) {
       __threadfence();
-      uint16_t const *op = static_cast<uint16_t const *>(p.o_part) + set * p.o_set_stride + (int64_t)head * p.m * out_ld;
-      uint16_t const *rp = static_cast<uint16_t const *>(p.r_part) + set * p.r_set_stride + (int64_t)head * p.m * p.splits;
-      uint16_t *dst = static_cast<uint16_t *>(p.merged_out) + set * p.merged_set_stride + (int64_t)head * p.m * DH;
+      uint16_t const *op = static_cast<uint16_t const *>(p.o_part) + (int64_t)run_set * p.o_set_stride + (int64_t)run_head * p.m * out_ld;
+      uint16_t const *rp = static_cast<uint16_t const *>(p.r_part) + (int64_t)run_set * p.r_set_stride + (int64_t)run_head * p.m * p.splits;
       constexpr int kKind = MODE == kFingerprint ? kMergeFingerprint : (MODE == kBF16 ? kMergeBF16 : kMergeF16);
-      merge_head<kKind, DH>(op, rp, dst, p.m, p.splits, tid, (int)blockDim.x);
-      if (tid == 0) p.tickets[set * p.heads + head] = 0; // ready for the next launch
+      uint64_t held = ~0ull;
+      if (fused_runs) {
+        // Only the slots that begin a run hold sums: split 0, and every split that is the first item of a block.
+        // Thread s looks at slot s (at most 64 splits here); the votes of the first two warps make the mask.
+        __shared__ uint32_t s_held[2];
+        if (tid < 64) {
+          uint32_t const x = (uint32_t)unit * (uint32_t)p.splits + (uint32_t)tid, wide = extra * (per_block + 1);
+          bool const starts_block = x < wide ? x % (per_block + 1) == 0 : (x - wide) % per_block == 0;
+          uint32_t const votes = __ballot_sync(0xffffffffu, tid < p.splits && (tid == 0 || starts_block));
+          if (lane == 0) s_held[warp] = votes;
+        }
+        __syncthreads();
+        held = (uint64_t)s_held[0] | ((uint64_t)s_held[1] << 32);
+      }
+      merge_head<kKind, DH>(op, rp, final_out, p.m, p.splits, tid, (int)blockDim.x, held);
+      if (tid == 0) p.tickets[unit] = 0; // ready for the next launch
     }
   }
+  if (PERSIST) { // the next run starts from nothing
+#pragma unroll
+    for (int i = 0; i < 2 * kNPairs; i++)
+#pragma unroll
+      for (int j = 0; j < 4; j++) oacc[i][j] = 0;
+    racc0 = 0, racc1 = 0;
+    if (new_rows) load_q();
+  }
+  } // work items of this block
 }
 
 // ---- merge: O = sum_s O_part[.., s*d + c] / sum_s R_part[.., s] ---------------------------------------------
@@ -667,18 +764,30 @@ static bool shape_supported(mgd_attn_split const *p, bool fp) {
 }
 
 // One instantiation per (mode, head_dim, operand forms); the shared-memory opt-in is set once for each.
-template <int MODE, int DH, int FORM>
-static int launch_form(cudaLaunchConfig_t const &cfg, CUtensorMap const &kmap, CUtensorMap const &vmap,
-                       AttnSplitParams const &a) {
+template <int MODE, int DH, int FORM, bool PERSIST>
+static int launch_form_as(cudaLaunchConfig_t cfg, CUtensorMap const &kmap, CUtensorMap const &vmap, AttnSplitParams const &a) {
   static std::atomic<bool> configured[kMaxDevices]; // the attribute is a property of the function on one device
   int const dev = current_device();
   if (!configured[dev].load(std::memory_order_acquire)) {
-    if (cudaFuncSetAttribute(attn_split_kernel<MODE, DH, FORM>, cudaFuncAttributeMaxDynamicSharedMemorySize, kDynSmemLimit) != cudaSuccess)
+    if (cudaFuncSetAttribute(attn_split_kernel<MODE, DH, FORM, PERSIST>, cudaFuncAttributeMaxDynamicSharedMemorySize, kDynSmemLimit) != cudaSuccess)
       return check_launch("cudaFuncSetAttribute(attn_split_kernel)");
     configured[dev].store(true, std::memory_order_release);
   }
-  cudaLaunchKernelEx(&cfg, attn_split_kernel<MODE, DH, FORM>, kmap, vmap, a);
+  if (PERSIST) { // as many blocks as are resident at once; each walks its share of the work items
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attn_split_kernel<MODE, DH, FORM, PERSIST>, (int)cfg.blockDim.x,
+                                                      cfg.dynamicSmemBytes) != cudaSuccess || per_sm <= 0)
+      return check_launch("cudaOccupancyMaxActiveBlocksPerMultiprocessor(attn_split_kernel)");
+    unsigned resident = (unsigned)per_sm * (unsigned)sm_count();
+    if (resident < cfg.gridDim.x) cfg.gridDim.x = resident;
+  }
+  cudaLaunchKernelEx(&cfg, attn_split_kernel<MODE, DH, FORM, PERSIST>, kmap, vmap, a);
   return check_launch("attn_split_kernel");
+}
+
+template <int MODE, int DH, int FORM>
+static int launch_form(cudaLaunchConfig_t const &cfg, CUtensorMap const &kmap, CUtensorMap const &vmap, AttnSplitParams const &a) {
+  return a.persistent ? launch_form_as<MODE, DH, FORM, true>(cfg, kmap, vmap, a) : launch_form_as<MODE, DH, FORM, false>(cfg, kmap, vmap, a);
 }
 
 template <int MODE, int DH>
@@ -713,8 +822,22 @@ static int launch_split(mgd_attn_split const *p, void const *q, void const *k, v
   while (tile_groups > 1 && groups * tile_groups * 128 > 512) tile_groups--;
   int threads = groups * tile_groups * 128;
   size_t scratch = (size_t)(threads / 32) * rows_scratch * (DH + 4) * acc;
-  size_t data = scratch > stages * 2 * tile ? scratch : stages * 2 * tile;
+  // More blocks than fit at once: resident blocks that walk the work items, their tile rings running on from one
+  // item to the next (MGD_OPT_ATTN_PERSISTENT: 0 = this policy, 1 = never, 2 = whenever the shape allows it).
+  int const persist_opt = option(MGD_OPT_ATTN_PERSISTENT);
+  bool persistent = threads == 128 && persist_opt != 1 && blocks > sm_count() &&
+                    fixed + stages * 2 * tile + scratch + 16 <= (size_t)kDynSmemLimit;
+  // with a fused merge over scratch partials a persistent block sums up to a whole head in its accumulators: the
+  // 32-bit integer ones of fingerprint mode are exact for 256 tiles
+  bool sum_runs = persistent && opts && opts->merged_out && (opts->overlap & 8);
+  if (fp && (int64_t)p->splits * p->forloop_range > 256) sum_runs = false;
+  if (p->splits > 64) sum_runs = false; // the merge keeps one bit per split slot
+  // A fused merge that must leave every partial in memory takes a ticket per item; a walking block would stall its
+  // tile ring on each of them (measured: a third slower than one block per item), so it is not used there.
+  if (opts && opts->merged_out && !sum_runs && persist_opt != 2) persistent = false;
+  size_t data = persistent ? stages * 2 * tile + scratch : (scratch > stages * 2 * tile ? scratch : stages * 2 * tile);
   size_t smem = fixed + ((data + 15) & ~(size_t)15);
+
   if (smem > (size_t)kDynSmemLimit) return set_error(MG_ERR_UNSUPPORTED, "split-KV attention: tile does not fit shared memory");
 
   CUtensorMap kmap, vmap;
@@ -733,6 +856,9 @@ static int launch_split(mgd_attn_split const *p, void const *q, void const *k, v
   a.q_set_stride = p->q_set_stride; a.o_set_stride = p->o_set_stride; a.r_set_stride = p->r_set_stride;
   a.heads = p->heads; a.m = p->m; a.splits = p->splits; a.forloop = p->forloop_range; a.stages = stages;
   a.tile_groups = tile_groups;
+  a.num_sets = p->num_sets;
+  a.persistent = persistent ? 1 : 0;
+  a.sum_runs = sum_runs ? 1 : 0;
   a.merged_out = opts ? opts->merged_out : nullptr;
   a.tickets = opts ? opts->tickets : nullptr;
   a.merged_set_stride = opts ? opts->merged_set_stride : 0;

@@ -34,7 +34,7 @@ public:
   // operator's output, tickets = heads * num_sets zeroed int32 of device memory.
   int launch_fused_sets(KNCustomizedOp *merge, bool fingerprint_mode, int num_sets, void const *const *in,
                         long long const *in_stride, void *const *out, long long const *out_stride, void *merged_out,
-                        long long merged_stride, int *tickets, void *stream);
+                        long long merged_stride, int *tickets, void *stream, bool partials_are_scratch = false);
 
   // Non-asserting construction: nullptr plus a message when the plan is invalid for these inputs
   // or the outputs do not fit the arena.
@@ -75,6 +75,7 @@ private:
     long long set_stride;
     size_t bytes;
     int *tickets;
+    bool partials_are_scratch; // nobody reads the split-KV partials after the launch
   };
   int launch_split(bool fingerprint_mode, int num_sets, void const *const *in, long long const *in_stride,
                    void *const *out, long long const *out_stride, FusedMerge const *merge, void *stream);

@@ -132,8 +132,10 @@ enum {
   MG_OPT_ATTN_ENGINE = 2,       /* split-KV attention, float mode: 1 = mma.sync kernel, 2 = tcgen05 kernel */
   MG_OPT_ROWS_ENGINE = 3,       /* dense attention: 1 = one query tile per block, 2 = two query tiles per block */
   MG_OPT_INTERP_THREADS = 4,    /* generic interpreters: threads per block, 256 / 512 / 1024 */
-  MG_OPT_WAIT_LIMIT = 5         /* split-KV attention: polls before a tile wait gives up; 1 = give up without polling
+  MG_OPT_WAIT_LIMIT = 5,        /* split-KV attention: polls before a tile wait gives up; 1 = give up without polling
                                    (failure-path tests), n > 1 = n polls */
+  MG_OPT_ATTN_PERSISTENT = 6    /* split-KV attention with more blocks than fit at once: 1 = one block per work item,
+                                   2 = resident blocks that walk the work items (the default where it fits) */
 };
 int mg_runtime_set_option(mg_runtime *rt, int32_t key, int32_t value);
 int mg_runtime_get_option(mg_runtime *rt, int32_t key, int32_t *value);

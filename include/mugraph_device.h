@@ -126,7 +126,10 @@ int mgd_attn_split_supported(const mgd_attn_split *p, int32_t fingerprint_mode);
  *    loads may be issued before that wait;
  *    bit 2 = size the blocks for throughput (two-stage ring, four warps): blocks of several launches in flight
  *    then share an SM.  Without it a launch that fits one wave keeps its whole KV split in flight per block,
- *    which gives the lowest latency for one launch at a time. */
+ *    which gives the lowest latency for one launch at a time;
+ *    bit 3 (with merged_out) = o_part / r_part are scratch that nobody reads after the launch: a launch with more
+ *    blocks than fit at once then sums consecutive splits of a head on the chip and writes only the partial sums the
+ *    merge needs (some slots of o_part / r_part stay untouched). */
 typedef struct mgd_attn_launch_opts {
   void *merged_out;          /* [num_sets][heads][m][d], NULL = partials only */
   int32_t *tickets;
@@ -254,7 +257,9 @@ enum {
   MGD_OPT_INTERP_THREADS = 4,     /* generic interpreters: threads per block, 256 / 512 / 1024 */
   MGD_OPT_WAIT_LIMIT = 5,         /* split-KV attention: polls before a tile wait gives up; 1 = give up without
                                      polling (failure-path tests), n > 1 = n polls */
-  MGD_OPT_COUNT = 6
+  MGD_OPT_ATTN_PERSISTENT = 6,    /* split-KV attention with more blocks than fit at once: 1 = one block per work item,
+                                     2 = resident blocks that walk the work items (the default where it fits) */
+  MGD_OPT_COUNT = 7
 };
 int mgd_set_option(int32_t key, int32_t value);
 int mgd_get_option(int32_t key, int32_t *value);

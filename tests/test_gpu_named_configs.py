@@ -416,13 +416,16 @@ def test_attention_plans_with_the_row_sum_first(runtime, specialisation):
 
 
 # ---- batched float launch and row-wise comparison ---------------------------------------------------------------------------
-@pytest.mark.parametrize("shape", [(8, 4, 128, 4096, 16, 4), (2, 16, 128, 1024, 4, 4)], ids=["decode", "16_rows_tcgen05"])
+@pytest.mark.parametrize("shape", [(8, 4, 128, 4096, 16, 4, 5), (2, 16, 128, 1024, 4, 4, 5), (8, 4, 128, 1024, 4, 4, 83),
+                                   (3, 4, 64, 768, 3, 4, 70)],
+                         ids=["decode", "16_rows_tcgen05", "whole_heads_per_block", "three_splits_d64"])
 def test_batched_float_run_equals_single_calls(runtime, shape):
     """Several independent float-mode calls of one graph in one pass (split-KV + merge as one kernel over all the
-    sets) give what the graph gives for each set alone, and what the fp32 evaluation gives."""
+    sets) give what the graph gives for each set alone, and what the fp32 evaluation gives.  With many sets the
+    launch has fewer blocks than (set, head, split) items: a block then sums runs of consecutive splits on the chip,
+    finishing whole heads in place and merging the heads it shares with a neighbour through memory."""
     import torch
-    B, M, D, L, S, F = shape
-    nsets = 5
+    B, M, D, L, S, F, nsets = shape
     runtime.set_specialisation(2)
     rng = np.random.default_rng(61)
     rnd = lambda a: from_bits(to_bits(a, mg.float16), mg.float16)
@@ -448,6 +451,16 @@ def test_batched_float_run_equals_single_calls(runtime, shape):
             got = from_bits(res.cpu().numpy().view(np.uint16), mg.float16)
             for s in range(nsets):
                 assert_close(got[s], mo.attention_fp32(qs[s], ks[s], vs[s]), mg.float16, "set %d" % s)
+        # the same with one block per item
+        runtime.set_option(mg.OPT_ATTN_PERSISTENT, 1)
+        try:
+            res.zero_()
+            torch.cuda.synchronize()
+            g.run_batched(nsets, [d.data_ptr() for d in dev], res.data_ptr(), work.data_ptr(), wbytes)
+            mg.synchronize()
+        finally:
+            runtime.set_option(mg.OPT_ATTN_PERSISTENT, 0)
+        assert_close(from_bits(res.cpu().numpy().view(np.uint16), mg.float16), got, mg.float16, "block per item vs walking blocks")
         Q.upload_data(to_bits(qs[2], mg.float16))
         K.upload_data(to_bits(np.ascontiguousarray(ks[2].transpose(0, 2, 1)), mg.float16))
         V.upload_data(to_bits(vs[2], mg.float16))

@@ -96,6 +96,29 @@ def test_fingerprint_random_vs_oracle(rt, shape, hi):
         assert np.array_equal(f[0].download_fingerprint(), ref2[0])
 
 
+@pytest.mark.parametrize("shape", [(64, 4, 64, 512, 4, 2), (150, 4, 128, 256, 2, 2)], ids=["256_items", "300_items"])
+def test_fingerprint_walking_blocks_keep_every_partial(rt, shape):
+    """More (head, split) items than blocks that fit at once, evaluated by blocks that walk the items (forced: the
+    default keeps one block per item when the partials are tensors of the graph): both outputs of the first
+    operator and the result of the second equal the oracle's."""
+    rng = np.random.default_rng(5 + sum(shape))
+    rt.set_option(mg.OPT_ATTN_PERSISTENT, 2)
+    try:
+        with mg.PyGraph(rt) as g:
+            ins, o, f, plans = build_gqa(g, *shape)
+            x = [rng.integers(0, mo.FP_PQ, size=t.shape).astype(np.uint16) for t in ins]
+            for t, v in zip(ins, x):
+                t.upload_fingerprint(v)
+            for _ in range(2):
+                g.fingerprint()
+                ref1, ref2 = oracle_fp(ins, plans, x)
+                assert np.array_equal(o[0].download_fingerprint(), ref1[0])
+                assert np.array_equal(o[1].download_fingerprint(), ref1[1])
+                assert np.array_equal(f[0].download_fingerprint(), ref2[0])
+    finally:
+        rt.set_option(mg.OPT_ATTN_PERSISTENT, 0)
+
+
 def test_fused_graph_matches_unfused_graph_on_device(rt):
     """The reference's integration check (cpp_examples/group_query_attn_inc_decode.cc:14-108): both
     graphs evaluated on the device from the reference fill, compared with has_same_fingerprint."""
@@ -554,11 +577,13 @@ def test_float_matmul_chain_c1_full_size(rt, dtype):
     assert_close(got, exact, dtype, "chain result vs fp64 product")
 
 
-def test_batched_fingerprint_sets(rt):
-    """Many independent input sets in one pass equal per-set evaluations by the oracle."""
+@pytest.mark.parametrize("shape", [(2, 4, 64, 512, 4, 2, 5), (4, 4, 128, 512, 4, 2, 150), (3, 3, 64, 384, 3, 2, 97)],
+                         ids=["few_sets", "whole_heads_per_block", "three_splits"])
+def test_batched_fingerprint_sets(rt, shape):
+    """Many independent input sets in one pass equal per-set evaluations by the oracle (with many sets a block of the
+    fused kernel sums runs of consecutive splits of a head; modulo arithmetic makes that exact)."""
     import torch
-    B, M, D, L, S, F = 2, 4, 64, 512, 4, 2
-    nsets = 5
+    B, M, D, L, S, F, nsets = shape
     rng = np.random.default_rng(77)
     with mg.PyGraph(rt) as g:
         ins, o, f, plans = build_gqa(g, B, M, D, L, S, F)
@@ -571,9 +596,20 @@ def test_batched_fingerprint_sets(rt):
         g.fingerprint_batched(nsets, [d.data_ptr() for d in dev], out.data_ptr(), work.data_ptr(), wbytes)
         mg.synchronize()
         got = out.cpu().numpy().view(np.uint16)
-        for s in range(nsets):
+        for s in sorted(set(range(0, nsets, max(1, nsets // 12))) | {nsets - 1}):
             _, ref2 = oracle_fp(ins, plans, xs[s])
             assert np.array_equal(got[s], ref2[0]), "set %d" % s
+        # every set: the same launch with one block per (set, head, split) item
+        first = got.copy()
+        rt.set_option(mg.OPT_ATTN_PERSISTENT, 1)
+        try:
+            out.zero_()
+            torch.cuda.synchronize()
+            g.fingerprint_batched(nsets, [d.data_ptr() for d in dev], out.data_ptr(), work.data_ptr(), wbytes)
+            mg.synchronize()
+        finally:
+            rt.set_option(mg.OPT_ATTN_PERSISTENT, 0)
+        assert np.array_equal(out.cpu().numpy().view(np.uint16), first)
 
 
 def test_unsupported_is_an_error_not_a_fallback(rt):
