@@ -261,17 +261,22 @@ attn_split_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
   // Ordering against the previous kernel of the stream (programmatic dependent launch): nothing is written
   // to global memory, and no input that kernel may have produced is read, before griddepcontrol.wait; the next
   // kernel is released right after, so at most two kernels of a stream are ever in flight.
+  // With inputs that the previous kernel did not write, a one-item block goes further: it also does its arithmetic
+  // before the wait and only holds back its stores, so the previous kernel's write-out, ticket and merge run under it.
+  bool const late_wait = !PERSIST && p.early_loads;
   select_item(0);
   if (p.early_loads) {
     issue_first();
     load_q();
   }
-  ptx::grid_dependency_wait();
-  if (!p.early_loads) {
-    issue_first();
-    load_q();
+  if (!late_wait) {
+    ptx::grid_dependency_wait();
+    if (!p.early_loads) {
+      issue_first();
+      load_q();
+    }
+    ptx::grid_launch_dependents();
   }
-  ptx::grid_launch_dependents();
 
   // stage and barrier phase of this warp's tile, and stage of the round's first tile, kept without divisions
   // (tile_groups <= stages, so one conditional subtraction per round is enough); they run on across items
@@ -439,6 +444,10 @@ attn_split_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
   }
   if (!run_ends) continue; // (a run that goes on stays with its head: no new rows)
 
+  if (late_wait) { // from here on global memory is written
+    ptx::grid_dependency_wait();
+    ptx::grid_launch_dependents();
+  }
   if (failed) s_failed = 1;
   __syncthreads(); // also: every tile has been read, the stage memory may be reused as scratch
   if (s_failed) { // a bounded wait gave up: flag it and leave the outputs alone
