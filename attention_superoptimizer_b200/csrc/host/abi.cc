@@ -15,8 +15,15 @@ using kernel::DeviceMemoryManager;
 using kernel::DTensor;
 using kernel::KNOperator;
 
+// Side streams of the verification step: candidate graphs are independent of each other and a candidate's kernels
+// fill a fraction of the GPU, so they are dealt over a few lanes that fork from and join the caller's stream.
+constexpr int kVerifyLanes = 8;
 struct mg_runtime {
   DeviceMemoryManager *dmm;
+  cudaStream_t lanes[kVerifyLanes];
+  cudaEvent_t lane_done[kVerifyLanes];
+  cudaEvent_t fork;
+  bool lanes_ready;
 };
 struct mg_graph {
   mg_runtime *rt;
@@ -24,7 +31,7 @@ struct mg_graph {
 };
 
 namespace {
-mg_runtime g_runtime{nullptr};
+mg_runtime g_runtime{};
 
 int fail(int code, char const *msg) {
   mg::set_error(msg);
@@ -118,8 +125,27 @@ int mg_runtime_create(int device, size_t arena_bytes, mg_runtime **rt) {
   return MG_OK;
 }
 
+static bool ensure_lanes(mg_runtime *rt) {
+  if (rt->lanes_ready) return true;
+  for (int i = 0; i < kVerifyLanes; i++) {
+    if (cudaStreamCreateWithFlags(&rt->lanes[i], cudaStreamNonBlocking) != cudaSuccess) return false;
+    if (cudaEventCreateWithFlags(&rt->lane_done[i], cudaEventDisableTiming) != cudaSuccess) return false;
+  }
+  if (cudaEventCreateWithFlags(&rt->fork, cudaEventDisableTiming) != cudaSuccess) return false;
+  rt->lanes_ready = true;
+  return true;
+}
+
 int mg_runtime_destroy(mg_runtime *rt) {
   if (!rt || !rt->dmm) return fail(MG_ERR_INVALID_ARGUMENT, "no runtime");
+  if (rt->lanes_ready) {
+    for (int i = 0; i < kVerifyLanes; i++) {
+      cudaStreamDestroy(rt->lanes[i]);
+      cudaEventDestroy(rt->lane_done[i]);
+    }
+    cudaEventDestroy(rt->fork);
+    rt->lanes_ready = false;
+  }
   DeviceMemoryManager::destroy();
   mg::forget_streams();
   rt->dmm = nullptr;
@@ -572,15 +598,32 @@ int mg_verify_candidates(mg_runtime *rt, const mg_tensor *reference, mg_graph *c
   MG_CUDA_TRY(cudaMemsetAsync(flags, 0, sizeof(int32_t) * (size_t)n, (cudaStream_t)stream));
   int64_t ref_elems = 1;
   for (int d = 0; d < reference->num_dims; d++) ref_elems *= reference->dim[d];
-  for (int32_t i = 0; i < n; i++) {
+  for (int32_t i = 0; i < n; i++)
     if (!candidates[i]) return fail(MG_ERR_INVALID_ARGUMENT, "null candidate graph");
-    int st = launch_all(candidates[i], true, true, stream);
-    if (st != MG_OK) return st;
+  // Candidate i runs on lane i % lanes: the lanes start after what the caller's stream holds so far (the inputs, the
+  // reference's fingerprint, the cleared flags) and the caller's stream continues after all of them.
+  int const lanes = n < kVerifyLanes ? n : kVerifyLanes;
+  if (!ensure_lanes(rt)) return fail(MG_ERR_CUDA, "cannot create the verification streams");
+  MG_CUDA_TRY(cudaEventRecord(rt->fork, (cudaStream_t)stream));
+  for (int l = 0; l < lanes; l++) MG_CUDA_TRY(cudaStreamWaitEvent(rt->lanes[l], rt->fork, 0));
+  int failed_st = MG_OK;
+  for (int32_t i = 0; i < n && failed_st == MG_OK; i++) {
+    void *lane = rt->lanes[i % lanes];
+    int st = launch_all(candidates[i], true, true, lane);
+    if (st != MG_OK) { failed_st = st; break; }
     bool same_shape = outputs[i].num_dims == reference->num_dims && outputs[i].fp_ptr != nullptr;
     for (int d = 0; same_shape && d < reference->num_dims; d++) same_shape = outputs[i].dim[d] == reference->dim[d];
     if (!same_shape) continue; // flag stays 0
-    st = mgd_compare_u16(outputs[i].fp_ptr, reference->fp_ptr, ref_elems, flags + i, stream);
-    if (st != MG_OK) return fail(st, mgd_last_error());
+    st = mgd_compare_u16(outputs[i].fp_ptr, reference->fp_ptr, ref_elems, flags + i, lane);
+    if (st != MG_OK) failed_st = fail(st, mgd_last_error());
+  }
+  for (int l = 0; l < lanes; l++) { // joined also when a launch was refused: the flags go back to the arena below
+    cudaEventRecord(rt->lane_done[l], rt->lanes[l]);
+    cudaStreamWaitEvent((cudaStream_t)stream, rt->lane_done[l], 0);
+  }
+  if (failed_st != MG_OK) {
+    cudaStreamSynchronize((cudaStream_t)stream);
+    return failed_st;
   }
   MG_CUDA_TRY(cudaMemcpyAsync(same, flags, sizeof(int32_t) * (size_t)n, cudaMemcpyDeviceToHost, (cudaStream_t)stream));
   MG_CUDA_TRY(cudaStreamSynchronize((cudaStream_t)stream));
