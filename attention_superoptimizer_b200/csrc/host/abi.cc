@@ -28,6 +28,14 @@ struct mg_runtime {
 struct mg_graph {
   mg_runtime *rt;
   kernel::Graph graph;
+  // Ticket counters of the batched entry points (one per (set, head) of every fused split-KV + merge pair): device
+  // memory of the graph's own, zeroed when allocated; every launch leaves them zero.  Not in the caller's workspace,
+  // so that no clearing copy sits between two launches of a stream and one launch can start under the other's tail.
+  int *batch_tickets = nullptr;
+  size_t batch_ticket_ints = 0;
+  ~mg_graph() {
+    if (batch_tickets) cudaFree(batch_tickets);
+  }
 };
 
 namespace {
@@ -453,8 +461,7 @@ int mg_op_profile(mg_graph *g, int32_t idx, int32_t warmup, int32_t iters, float
 }
 
 // Shared body of the two batched entry points.  Workspace layout: every customized-op output except the final one
-// gets num_sets * elements 16-bit values (256-byte aligned); then heads * num_sets ticket counters
-// for each split-KV operator that is issued together with its merge operator.
+// gets num_sets * elements 16-bit values (256-byte aligned).
 static int run_batched(mg_graph *g, bool fp, int32_t num_sets, const void *const *in_ptrs, void *out_ptr, void *workspace,
                        size_t *workspace_bytes, void *stream) {
   if (!g || num_sets <= 0 || !workspace_bytes) return fail(MG_ERR_INVALID_ARGUMENT, "bad batched request");
@@ -479,13 +486,13 @@ static int run_batched(mg_graph *g, bool fp, int32_t num_sets, const void *const
     }
   // A split-KV operator and the merge that consumes it are issued as one launch.  The partials between them live in
   // the workspace and nobody else reads them, which lets the kernel sum consecutive splits of a head on the chip.
-  std::vector<size_t> ticket_offset(work.size(), (size_t)-1);
-  size_t const tickets_begin = need;
+  std::vector<size_t> ticket_offset(work.size(), (size_t)-1); // in counters, into the graph's ticket array
+  size_t ticket_ints = 0;
   for (size_t w = 0; w + 1 < work.size(); w++) {
     auto *c = static_cast<kernel::KNCustomizedOp *>(work[w]);
     if (c->selected_kernel(fp) == mg::KERNEL_ATTN_SPLIT && c->can_fuse_with(work[w + 1], fp)) {
-      ticket_offset[w] = need;
-      need += ((size_t)c->plan.grid_dim.x * (size_t)num_sets * sizeof(int) + 255) / 256 * 256;
+      ticket_offset[w] = ticket_ints;
+      ticket_ints += ((size_t)c->plan.grid_dim.x * (size_t)num_sets + 63) / 64 * 64;
       w++;
     }
   }
@@ -496,9 +503,15 @@ static int run_batched(mg_graph *g, bool fp, int32_t num_sets, const void *const
   if (int dry_st = refuse_dry(g->rt)) return dry_st;
   if (*workspace_bytes < need) return fail(MG_ERR_INVALID_ARGUMENT, "workspace too small");
   if (!in_ptrs || !out_ptr) return fail(MG_ERR_INVALID_ARGUMENT, "null tensor pointers");
-  if (need > tickets_begin) {
-    MG_CUDA_TRY(cudaMemsetAsync((char *)workspace + tickets_begin, 0, need - tickets_begin, (cudaStream_t)stream));
-    mg::stream_wrote_anything(stream);
+  if (ticket_ints > g->batch_ticket_ints) {
+    // grown on the first call and when a call brings more sets (allocation synchronises the device: not for a stream
+    // that is being captured - make the first call of a size outside the capture)
+    if (g->batch_tickets) MG_CUDA_TRY(cudaFree(g->batch_tickets));
+    g->batch_tickets = nullptr;
+    g->batch_ticket_ints = 0;
+    MG_CUDA_TRY(cudaMalloc(&g->batch_tickets, ticket_ints * sizeof(int)));
+    MG_CUDA_TRY(cudaMemset(g->batch_tickets, 0, ticket_ints * sizeof(int)));
+    g->batch_ticket_ints = ticket_ints;
   }
   auto locate = [&](DTensor const &t, void const **ptr, long long *stride) -> bool {
     for (size_t i = 0; i < inputs.size(); i++)
@@ -535,7 +548,7 @@ static int run_batched(mg_graph *g, bool fp, int32_t num_sets, const void *const
       long long ms;
       if (!locate(m->output_tensors[0], &mp, &ms)) return fail(MG_ERR_INVALID_GRAPH, "internal: output slot missing");
       st = c->launch_fused_sets(m, fp, num_sets, in, is, out, os, const_cast<void *>(mp), ms,
-                                reinterpret_cast<int *>((char *)workspace + ticket_offset[w]), stream,
+                                g->batch_tickets + ticket_offset[w], stream,
                                 /*partials_are_scratch=*/true); // the intermediates live in the caller's workspace
       w++;
     } else {

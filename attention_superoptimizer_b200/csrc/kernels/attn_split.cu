@@ -261,9 +261,10 @@ attn_split_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
   // Ordering against the previous kernel of the stream (programmatic dependent launch): nothing is written
   // to global memory, and no input that kernel may have produced is read, before griddepcontrol.wait; the next
   // kernel is released right after, so at most two kernels of a stream are ever in flight.
-  // With inputs that the previous kernel did not write, a one-item block goes further: it also does its arithmetic
-  // before the wait and only holds back its stores, so the previous kernel's write-out, ticket and merge run under it.
-  bool const late_wait = !PERSIST && p.early_loads;
+  // With inputs that the previous kernel did not write, a block goes further: it also does its arithmetic before the
+  // wait and only holds back its stores, so the previous kernel's write-out, tickets and merges run under it.
+  // A walking block does the same up to the end of its first run.
+  bool late_wait = p.early_loads != 0;
   select_item(0);
   if (p.early_loads) {
     issue_first();
@@ -447,6 +448,7 @@ attn_split_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
   if (late_wait) { // from here on global memory is written
     ptx::grid_dependency_wait();
     ptx::grid_launch_dependents();
+    late_wait = false;
   }
   if (failed) s_failed = 1;
   __syncthreads(); // also: every tile has been read, the stage memory may be reused as scratch

@@ -243,7 +243,11 @@ int mg_graph_run(mg_graph *g, void *stream);
  * input sets in one pass.  Input i of set s is read at in_fp[i] + s * elements(input i);
  * the last operator's output 0 for set s is written to out_fp + s * elements(output).
  * Intermediate tensors of all sets live in `workspace` (device memory,
- * `*workspace_bytes` from the query call with workspace = NULL).
+ * `*workspace_bytes` from the query call with workspace = NULL); what is in it when the call starts does not
+ * matter, and nothing in it is meant for the caller.  The ticket counters of fused launches are device memory of the
+ * graph's own: the first call, and a call with more sets than any before, allocates them (which synchronises the
+ * device, so make that call outside a stream capture); after that consecutive calls on a stream run without any
+ * copy or clearing between their kernels.
  * Stands in for `num_sets` repetitions of the verify loop, src/search/search.cc:601-603. */
 int mg_graph_fingerprint_batched(mg_graph *g, int32_t num_sets, const uint16_t *const *in_fp, uint16_t *out_fp,
                                  void *workspace, size_t *workspace_bytes, void *stream);
