@@ -470,6 +470,17 @@ __global__ void __launch_bounds__(1024) float_interp_kernel(const __grid_constan
           unsigned char const *x = tile(a[3]);
           bool const x16 = a[5] != 0;
           float *y = ftile(a[4]);
+          if (n_out < nt && degree >= 8) { // fewer sums than threads: a warp per sum, lanes stride over the terms
+            for (int i = tid >> 5; i < n_out; i += nt >> 5) {
+              int const base = (i / inner) * (inner * degree) + i % inner;
+              float acc = 0.f;
+              for (int k = tid & 31; k < degree; k += 32) acc += rd<T>(x, x16, base + k * inner);
+#pragma unroll
+              for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+              if ((tid & 31) == 0) y[i] = acc;
+            }
+            break;
+          }
           for (int i = tid; i < n_out; i += nt) {
             int pos = (i / inner) * (inner * degree) + i % inner;
             float acc = 0.f;

@@ -16,6 +16,7 @@
 //   * lookup tables live in constant memory;
 //   * shared-memory tiles keep the planned offsets, so the aliasing of the in-place exp is the same.
 #include "common.cuh"
+#include <cstdio>
 #include "interp_common.cuh"
 #include <cstdlib>
 #include <cstring>
@@ -51,30 +52,48 @@ __device__ __forceinline__ void load_tile_u16(uint16_t *dst, uint16_t const *src
 // Same residue as the reference's multiply-add loop (TBMatmulFingerprinter, threadblock/cuda/matmul.h:773-804).
 // Needs k % 16 == 0 and n % 16 == 0 (ldmatrix rows of 16 bytes); a warp owns 4 rows x 16 columns of C at a time.
 // `b_swizzled`: B sits as 64-column boxes of k rows x 128 bytes with the 128-byte swizzle, as the TMA engine wrote it.
-__device__ __forceinline__ void matmul_fp_tensor(uint16_t const *A, uint16_t const *B, uint16_t *C, int m, int n, int k,
-                                                 int b_pitch, bool b_swizzled, int tid, int nthreads) {
+// CP = column pairs (16 columns each) a warp works on side by side: the A fragments of a k-step are loaded once for all
+// of them.  KC = accumulate chains along k (k-step i goes to chain i % KC; the chains are added at the end - int32
+// sums, the same total as one chain).  CP * KC * 2 MMAs are independent of each other, which is what hides the
+// latency of the integer MMA (a dependent chain ran at about 300 cycles per k-step).
+template <int CP, int KC>
+__device__ __forceinline__ void matmul_fp_tensor_cp(uint16_t const *A, uint16_t const *B, uint16_t *C, int m, int n, int k,
+                                                    int b_pitch, bool b_swizzled, int tid, int nthreads) {
   int const lane = tid & 31, warp = tid >> 5, nwarps = nthreads >> 5;
   int const g = lane >> 2, t = lane & 3, mi = lane >> 3, rr = lane & 7;
-  int const row_groups = (m + 3) >> 2, col_pairs = n >> 4;
+  int const row_groups = (m + 3) >> 2, col_blocks = (n >> 4) / CP;
   uint32_t const b_base = (uint32_t)__cvta_generic_to_shared(B);
-  for (int w = warp; w < row_groups * col_pairs; w += nwarps) {
-    int const rg = w / col_pairs, cp = w % col_pairs;
+  for (int w = warp; w < row_groups * col_blocks; w += nwarps) {
+    int const rg = w / col_blocks, cb = w % col_blocks;
     int const row = rg * 4 + (g & 3);
     bool const valid = row < m;
-    int32_t acc[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}};
+    int32_t acc[KC][CP][2][4];
+#pragma unroll
+    for (int kc = 0; kc < KC; kc++)
+#pragma unroll
+      for (int c = 0; c < CP; c++)
+#pragma unroll
+        for (int h = 0; h < 2; h++)
+#pragma unroll
+          for (int j = 0; j < 4; j++) acc[kc][c][h][j] = 0;
     uint16_t const *arow = A + (size_t)row * k + 2 * t;
     // ldmatrix (transposed): this lane addresses k-row (mi % 2) * 8 + rr of the 8 columns starting at (mi / 2) * 8
-    uint32_t baddr = b_base + (uint32_t)((((mi & 1) * 8 + rr) * b_pitch + cp * 16 + (mi >> 1) * 8) * 2);
-    uint32_t bstep = (uint32_t)(16 * b_pitch * 2);
-    if (b_swizzled) {
-      int const unit = cp * 2 + (mi >> 1); // 16-byte unit of the row: 8 per box
-      baddr = b_base + (uint32_t)((unit >> 3) * k * 128 + ((mi & 1) * 8 + rr) * 128 + (((unit & 7) ^ rr) << 4));
-      bstep = 16u * 128u;
+    uint32_t baddr[CP], bstep = (uint32_t)(16 * b_pitch * 2);
+#pragma unroll
+    for (int c = 0; c < CP; c++) {
+      int const cp = cb * CP + c;
+      baddr[c] = b_base + (uint32_t)((((mi & 1) * 8 + rr) * b_pitch + cp * 16 + (mi >> 1) * 8) * 2);
+      if (b_swizzled) {
+        int const unit = cp * 2 + (mi >> 1); // 16-byte unit of the row: 8 per box
+        baddr[c] = b_base + (uint32_t)((unit >> 3) * k * 128 + ((mi & 1) * 8 + rr) * 128 + (((unit & 7) ^ rr) << 4));
+      }
     }
-    for (int k0 = 0; k0 < k; k0 += 16, baddr += bstep) {
+    if (b_swizzled) bstep = 16u * 128u;
+    // one k-step (16 uint16 of A's rows against 16 rows of B) into chain `kc`
+    auto step = [&](int k0, int32_t (&into)[CP][2][4]) {
       uint32_t const w0 = valid ? *reinterpret_cast<uint32_t const *>(arow + k0) : 0u;
       uint32_t const w1 = valid ? *reinterpret_cast<uint32_t const *>(arow + k0 + 8) : 0u;
-      uint32_t a[4], bf[4];
+      uint32_t a[4];
       if (g < 4) { // MMA rows 0-3: [lo,0] bytes; MMA rows 8-11: [hi,lo] bytes
         a[0] = w0 & 0x00FF00FFu; a[2] = w1 & 0x00FF00FFu;
         a[1] = __byte_perm(w0, 0, 0x2301); a[3] = __byte_perm(w1, 0, 0x2301);
@@ -82,28 +101,69 @@ __device__ __forceinline__ void matmul_fp_tensor(uint16_t const *A, uint16_t con
         a[0] = w0 & 0xFF00FF00u; a[2] = w1 & 0xFF00FF00u;
         a[1] = 0u; a[3] = 0u;
       }
-      asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
-                   : "=r"(bf[0]), "=r"(bf[1]), "=r"(bf[2]), "=r"(bf[3]) : "r"(baddr));
+      uint32_t bf[CP][4];
 #pragma unroll
-      for (int h = 0; h < 2; h++)
-        asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                     : "+r"(acc[h][0]), "+r"(acc[h][1]), "+r"(acc[h][2]), "+r"(acc[h][3])
-                     : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(bf[2 * h]), "r"(bf[2 * h + 1]));
-    }
-#pragma unroll
-    for (int h = 0; h < 2; h++) {
-      // lanes 16-31 hold the HH sums of the rows lanes 0-15 work on
-      int32_t const hh0 = __shfl_down_sync(0xffffffffu, acc[h][0], 16), hh1 = __shfl_down_sync(0xffffffffu, acc[h][1], 16);
-      if (g < 4 && valid) {
-        uint32_t v0 = ((uint32_t)acc[h][0] % PQ + 256u * ((uint32_t)acc[h][2] % PQ) + (65536u % PQ) * ((uint32_t)hh0 % PQ)) % PQ;
-        uint32_t v1 = ((uint32_t)acc[h][1] % PQ + 256u * ((uint32_t)acc[h][3] % PQ) + (65536u % PQ) * ((uint32_t)hh1 % PQ)) % PQ;
-        *reinterpret_cast<uint32_t *>(C + (size_t)row * n + cp * 16 + h * 8 + 2 * t) = v0 | (v1 << 16);
+      for (int c = 0; c < CP; c++) {
+        asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(bf[c][0]), "=r"(bf[c][1]), "=r"(bf[c][2]), "=r"(bf[c][3]) : "r"(baddr[c]));
+        baddr[c] += bstep;
       }
+#pragma unroll
+      for (int c = 0; c < CP; c++)
+#pragma unroll
+        for (int h = 0; h < 2; h++)
+          asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                       : "+r"(into[c][h][0]), "+r"(into[c][h][1]), "+r"(into[c][h][2]), "+r"(into[c][h][3])
+                       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(bf[c][2 * h]), "r"(bf[c][2 * h + 1]));
+    };
+    int k0 = 0;
+    for (; k0 + 16 * KC <= k; k0 += 16 * KC) {
+#pragma unroll
+      for (int kc = 0; kc < KC; kc++) step(k0 + 16 * kc, acc[kc]);
     }
+    for (; k0 < k; k0 += 16) step(k0, acc[0]);
+#pragma unroll
+    for (int kc = 1; kc < KC; kc++)
+#pragma unroll
+      for (int c = 0; c < CP; c++)
+#pragma unroll
+        for (int h = 0; h < 2; h++)
+#pragma unroll
+          for (int j = 0; j < 4; j++) acc[0][c][h][j] += acc[kc][c][h][j];
+#pragma unroll
+    for (int c = 0; c < CP; c++)
+#pragma unroll
+      for (int h = 0; h < 2; h++) {
+        // lanes 16-31 hold the HH sums of the rows lanes 0-15 work on
+        int32_t const hh0 = __shfl_down_sync(0xffffffffu, acc[0][c][h][0], 16), hh1 = __shfl_down_sync(0xffffffffu, acc[0][c][h][1], 16);
+        if (g < 4 && valid) {
+          uint32_t v0 = ((uint32_t)acc[0][c][h][0] % PQ + 256u * ((uint32_t)acc[0][c][h][2] % PQ) + (65536u % PQ) * ((uint32_t)hh0 % PQ)) % PQ;
+          uint32_t v1 = ((uint32_t)acc[0][c][h][1] % PQ + 256u * ((uint32_t)acc[0][c][h][3] % PQ) + (65536u % PQ) * ((uint32_t)hh1 % PQ)) % PQ;
+          *reinterpret_cast<uint32_t *>(C + (size_t)row * n + (cb * CP + c) * 16 + h * 8 + 2 * t) = v0 | (v1 << 16);
+        }
+      }
   }
 }
 
-__global__ void __launch_bounds__(1024) fp_interp_kernel(const __grid_constant__ mgd_program prog,
+// WIDE: the kernel instance has registers for eight independent MMA pairs (blocks of up to 512 threads), else four
+template <bool WIDE>
+__device__ __forceinline__ void matmul_fp_tensor(uint16_t const *A, uint16_t const *B, uint16_t *C, int m, int n, int k,
+                                                 int b_pitch, bool b_swizzled, int tid, int nthreads) {
+  // as many column pairs side by side as still leave every warp a piece of the tile; the rest as chains along k
+  int const row_groups = (m + 3) >> 2, col_pairs = n >> 4, nwarps = nthreads >> 5;
+  if (WIDE) {
+    if ((col_pairs & 3) == 0 && row_groups * (col_pairs >> 2) >= nwarps) matmul_fp_tensor_cp<4, 1>(A, B, C, m, n, k, b_pitch, b_swizzled, tid, nthreads);
+    else if ((col_pairs & 1) == 0 && row_groups * (col_pairs >> 1) >= nwarps) matmul_fp_tensor_cp<2, 2>(A, B, C, m, n, k, b_pitch, b_swizzled, tid, nthreads);
+    else matmul_fp_tensor_cp<1, 4>(A, B, C, m, n, k, b_pitch, b_swizzled, tid, nthreads);
+  } else {
+    if ((col_pairs & 1) == 0 && row_groups * (col_pairs >> 1) >= nwarps) matmul_fp_tensor_cp<2, 1>(A, B, C, m, n, k, b_pitch, b_swizzled, tid, nthreads);
+    else matmul_fp_tensor_cp<1, 2>(A, B, C, m, n, k, b_pitch, b_swizzled, tid, nthreads);
+  }
+}
+
+// MAXT: the largest block this instance is launched with (1024: 64 registers a thread; 512: 128)
+template <int MAXT>
+__global__ void __launch_bounds__(MAXT) fp_interp_kernel(const __grid_constant__ mgd_program prog,
                                                         const __grid_constant__ mgd_bindings bind,
                                                         const __grid_constant__ interp::TmaPlan tma,
                                                         const __grid_constant__ interp::TmaMaps maps, int32_t *status) {
@@ -131,6 +191,17 @@ __global__ void __launch_bounds__(1024) fp_interp_kernel(const __grid_constant__
   if (tid == 0) {
     for (int s = 0; s <= interp::kMaxStages; s++) ptx::mbar_init(ptx::smem_u32(&bars[s]), 1);
     ptx::mbar_init_fence();
+  }
+  // The finite-field tables in shared memory: threads of a warp look up different entries, which the constant cache
+  // serves one address at a time (an exp over a 4096-element tile took 8 k cycles that way, 0.3 k from here).
+  uint16_t *const tab_exp = tma.field_tables ? reinterpret_cast<uint16_t *>(smem_dyn + tma.field_tables - 1) : nullptr;
+  uint16_t *const tab_p = tab_exp + Q, *const tab_q = tab_exp + Q + P;
+  if (tab_exp != nullptr) {
+    for (int i = tid; i < (int)Q; i += nt) {
+      tab_exp[i] = (uint16_t)((c_tables.e[i] * Q_MUL_P_MOD_1) % PQ); // the lift to Z_PQ folded in
+      tab_q[i] = c_tables.q[i];
+    }
+    for (int i = tid; i < (int)P; i += nt) tab_p[i] = c_tables.p[i];
   }
   __syncthreads();
   // the inputs the TMA engine fetches, resolved once for this block
@@ -169,14 +240,27 @@ __global__ void __launch_bounds__(1024) fp_interp_kernel(const __grid_constant__
     if (!__syncthreads_and(ok)) { give_up(); return; }
   }
 
+#ifdef MG_FP_TIMING // cycles of thread 0 per operator, summed over the for-loop; block 0 prints them
+  long long t_op[MGD_MAX_OPS] = {}, t_wait = 0, t_issue = 0, t_begin = clock64();
+#endif
   for (int it = 0; it <= last; it++) {
+#ifdef MG_FP_TIMING
+    long long t_w0 = clock64();
+#endif
     if (tma.stages > 0) {
       int const s = it % tma.stages;
       stage_offset = s * tma.ring_bytes;
       bool ok = ptx::mbar_wait(ptx::smem_u32(&bars[s]), (uint32_t)((it / tma.stages) & 1));
       if (!__syncthreads_and(ok)) { give_up(); return; }
     }
+#ifdef MG_FP_TIMING
+    t_wait += clock64() - t_w0;
+#endif
     for (int oi = 0; oi < prog.num_ops; oi++) {
+#ifdef MG_FP_TIMING
+      long long const t_o0 = clock64();
+      struct Tock { long long &acc; long long t0; __device__ ~Tock() { acc += clock64() - t0; } } tock{t_op[oi], t_o0};
+#endif
       mgd_op const &op = prog.ops[oi];
       int32_t const *a = op.a;
       if (op.type == interp::kOpInput) {
@@ -203,7 +287,7 @@ __global__ void __launch_bounds__(1024) fp_interp_kernel(const __grid_constant__
           uint16_t *C = tile(a[5]);
           int const bp = a[6] > 0 ? a[6] : n; // row pitch of B: padded by the host when the dense pitch conflicts
           if ((k & 15) == 0 && (n & 15) == 0 && k <= 16384 && (nt & 31) == 0) {
-            matmul_fp_tensor(A, B, C, m, n, k, bp, a[7] != 0, tid, nt);
+            matmul_fp_tensor<(MAXT <= 512)>(A, B, C, m, n, k, bp, a[7] != 0, tid, nt);
             break;
           }
           for (int i = tid; i < m * n; i += nt) {
@@ -224,7 +308,11 @@ __global__ void __launch_bounds__(1024) fp_interp_kernel(const __grid_constant__
         }
         case MG_TB_EXP_OP: {
           uint16_t *x = tile(a[0]);
-          for (int i = tid; i < a[1]; i += nt) x[i] = (uint16_t)field_exp(x[i]);
+          if (tab_exp != nullptr) {
+            for (int i = tid; i < a[1]; i += nt) x[i] = tab_exp[x[i] % Q];
+          } else {
+            for (int i = tid; i < a[1]; i += nt) x[i] = (uint16_t)field_exp(x[i]);
+          }
           break;
         }
         case MG_TB_DIV_OP:
@@ -245,7 +333,9 @@ __global__ void __launch_bounds__(1024) fp_interp_kernel(const __grid_constant__
               rest /= zd[d];
             }
             uint32_t xv = x[xi], yv = y[yi], r;
-            if (op.type == MG_TB_DIV_OP) r = field_div(xv, yv);
+            if (op.type == MG_TB_DIV_OP)
+              r = tab_exp != nullptr ? ((xv % P) * tab_p[yv % P] * Q_MUL_P_MOD_1 + (xv % Q) * tab_q[yv % Q] * P_MUL_Q_MOD_1) % PQ
+                                     : field_div(xv, yv);
             else if (op.type == MG_TB_ADD_OP) r = (xv + yv) % PQ;
             else r = (uint32_t)(((unsigned long long)xv * yv) % PQ);
             z[i] = (uint16_t)r;
@@ -257,6 +347,18 @@ __global__ void __launch_bounds__(1024) fp_interp_kernel(const __grid_constant__
           int n_out = a[0], degree = a[1], inner = a[2];
           uint16_t const *x = tile(a[3]);
           uint16_t *y = tile(a[4]);
+          if (n_out < nt && degree >= 8 && degree < 65536) {
+            // fewer sums than threads: a warp per sum, lanes stride over the terms (a sum of 65535 terms fits 32 bits)
+            for (int i = warp; i < n_out; i += nt >> 5) {
+              int const base = (i / inner) * (inner * degree) + i % inner;
+              uint32_t acc = 0;
+              for (int k = lane; k < degree; k += 32) acc += x[base + k * inner];
+#pragma unroll
+              for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+              if (lane == 0) y[i] = (uint16_t)(acc % PQ);
+            }
+            break;
+          }
           for (int i = tid; i < n_out; i += nt) {
             int pos = (i / inner) * (inner * degree) + i % inner;
             unsigned long long acc = 0;
@@ -319,13 +421,28 @@ __global__ void __launch_bounds__(1024) fp_interp_kernel(const __grid_constant__
       __syncthreads();
     }
     // every thread is past its last read of this iteration's stage: request the tiles of iteration it + stages into it
+#ifdef MG_FP_TIMING
+    long long t_i0 = clock64();
+#endif
     if (warp == 0 && tma.stages > 0 && issued <= last) {
       ptx::fence_proxy_async_smem();
       int const s = it % tma.stages;
       issue(tma.moving_mask, issued, s, ptx::smem_u32(&bars[s]), tma.moving_tx);
       issued++;
     }
+#ifdef MG_FP_TIMING
+    t_issue += clock64() - t_i0;
+#endif
   }
+#ifdef MG_FP_TIMING
+  if (blockIdx.x == 0 && tid == 0) {
+    printf("fp_interp: %d threads, %d iterations, ring stages %d, total %lld cycles, tile waits %lld, issue %lld\n", nt, last + 1,
+           tma.stages, clock64() - t_begin, t_wait, t_issue);
+    for (int oi = 0; oi < prog.num_ops; oi++)
+      printf("  op %d type %d: %lld cycles  (a0..a2 %d %d %d, a6 %d, a7 %d)\n", oi, prog.ops[oi].type, t_op[oi], prog.ops[oi].a[0],
+             prog.ops[oi].a[1], prog.ops[oi].a[2], prog.ops[oi].a[6], prog.ops[oi].a[7]);
+  }
+#endif
 }
 
 static bool op_type_known(int t) {
@@ -579,16 +696,29 @@ extern "C" int mgd_launch_fingerprint_interp(const mgd_program *prog, const mgd_
   plan_fingerprint_program(rewritten, *bind, true, true, &plan);
   if (plan.smem_bytes > (size_t)interp::kDynSmemLimit) plan_fingerprint_program(rewritten, *bind, false, true, &plan);
   if (plan.smem_bytes > (size_t)interp::kDynSmemLimit) plan_fingerprint_program(*prog, *bind, false, false, &plan);
-  size_t const smem = plan.smem_bytes;
+  size_t smem = plan.smem_bytes;
   if (smem > (size_t)interp::kDynSmemLimit) return set_error(MG_ERR_UNSUPPORTED, "threadblock graph needs more shared memory than an SM has");
+  // room for the finite-field tables behind the plan, when the program looks anything up and an SM has the room
+  plan.tma.field_tables = 0;
+  for (int i = 0; i < plan.prog.num_ops; i++) {
+    int const t = plan.prog.ops[i].type;
+    if ((t == MG_TB_EXP_OP || t == MG_TB_DIV_OP) && ((smem + 15) & ~(size_t)15) + interp::kFieldTableBytes <= (size_t)interp::kDynSmemLimit) {
+      plan.tma.field_tables = (int32_t)((smem + 15) & ~(size_t)15) + 1;
+      smem = ((smem + 15) & ~(size_t)15) + interp::kFieldTableBytes;
+      break;
+    }
+  }
   int32_t *status = device_error_word();
   if (!status) return set_error(MG_ERR_CUDA, "cannot allocate the device status word");
   prog = &plan.prog;
-  static size_t configured = 0;
-  if (smem > 48 * 1024 && smem > configured) {
-    if (cudaFuncSetAttribute(fp_interp_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, interp::kDynSmemLimit) != cudaSuccess)
+  static bool configured[64] = {}; // per device: both instances
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+  if (smem > 48 * 1024 && !configured[dev]) {
+    if (cudaFuncSetAttribute(fp_interp_kernel<1024>, cudaFuncAttributeMaxDynamicSharedMemorySize, interp::kDynSmemLimit) != cudaSuccess ||
+        cudaFuncSetAttribute(fp_interp_kernel<512>, cudaFuncAttributeMaxDynamicSharedMemorySize, interp::kDynSmemLimit) != cudaSuccess)
       return check_launch("cudaFuncSetAttribute(fp_interp_kernel)");
-    configured = interp::kDynSmemLimit;
+    configured[dev] = true;
   }
   int64_t blocks = (int64_t)prog->grid[0] * prog->grid[1] * prog->grid[2] * bind->num_sets;
   if (blocks > 0x7fffffffLL) return set_error(MG_ERR_UNSUPPORTED, "too many blocks for one launch");
@@ -615,6 +745,7 @@ extern "C" int mgd_launch_fingerprint_interp(const mgd_program *prog, const mgd_
   unsigned threads = largest >= 8192 ? 1024u : (largest >= 2048 ? 512u : (largest >= 512 ? 256u : 128u));
   if (int const v = option(MGD_OPT_INTERP_THREADS)) // 128 ... 1024: for measurements
     if (v == 128 || v == 256 || v == 512 || v == 1024) threads = (unsigned)v;
-  fp_interp_kernel<<<(unsigned)blocks, threads, smem, (cudaStream_t)stream>>>(*prog, *bind, plan.tma, plan.maps, status);
+  if (threads > 512) fp_interp_kernel<1024><<<(unsigned)blocks, threads, smem, (cudaStream_t)stream>>>(*prog, *bind, plan.tma, plan.maps, status);
+  else fp_interp_kernel<512><<<(unsigned)blocks, threads, smem, (cudaStream_t)stream>>>(*prog, *bind, plan.tma, plan.maps, status);
   return check_launch("fp_interp_kernel");
 }

@@ -130,7 +130,10 @@ struct TmaPlan {
   uint32_t plain_once_mask; // inputs on plain loads whose tile is the same in every iteration: loaded in the first only
   uint32_t tiled_mask;      // of the TMA inputs: fetched as one dense tensor-map box
   uint32_t swizzled_mask;   // of the TMA inputs: fetched as 64-column tensor-map boxes with the 128-byte swizzle
+  int32_t field_tables;     // fingerprint interpreter: byte offset + 1 (from the start of the dynamic shared memory) of
+                            // a copy of the finite-field tables, 0 = none (the program has no exp or div, or no room)
 };
+constexpr int kFieldTableBytes = 1024; // exp lifted to Z_PQ [Q], inverses mod P [P], inverses mod Q [Q], 16 bits each
 
 // tensor maps of the inputs fetched in a tiled form, by input slot: [matrices][rows][cols] of 16-bit elements
 struct TmaMaps {

@@ -1,10 +1,16 @@
 // Kernel-level (un-fused) operators in both modes.  They produce the fingerprints a fused
 // candidate is compared against (the reference's compute_*_fingerprint kernels under
 // src/kernel/cuda/) and their float counterparts.  Memory-bound element-wise code: grid-stride
-// loops sized to the SM count, one exact 64-bit sum per matmul output.
+// loops sized to the SM count, one exact 64-bit sum per matmul output.  The float matmul runs on the tensor cores
+// (kn_matmul_tc.cu) where its operands can be described to the TMA unit; the loop here takes the rest.
 #include "common.cuh"
 
 namespace mgk {
+namespace kmm { // kn_matmul_tc.cu: the float matmul on tcgen05
+bool supported(void const *a, void const *b, int batches, int m, int n, int k, int a_col_major, int b_col_major);
+int launch(void const *a, void const *b, void *c, int batches, int m, int n, int k, int dtype, int a_col_major, int b_col_major,
+           void *stream);
+} // namespace kmm
 
 static int blocks_for(int64_t n, int threads = 256) {
   int64_t blocks = (n + threads - 1) / threads, cap = 148 * 8;
@@ -156,6 +162,10 @@ int mgd_kn_matmul_float(const void *a, const void *b, void *c, int32_t batches, 
                         int32_t al, int32_t bl, int32_t dt, void *stream) {
   if (!a || !b || !c || batches <= 0 || m <= 0 || n <= 0 || k <= 0) return set_error(MG_ERR_INVALID_ARGUMENT, "kn matmul: bad argument");
   int g = blocks_for((int64_t)batches * m * n), ac = al == MG_DMEM_COLUMN_MAJOR, bc = bl == MG_DMEM_COLUMN_MAJOR;
+  // tensor cores (tcgen05) wherever a tensor map can describe the operands; MGD_OPT_KN_MATMUL_ENGINE: 1 = CUDA cores
+  if ((dt == MG_DT_FLOAT16 || dt == MG_DT_BFLOAT16) && option(MGD_OPT_KN_MATMUL_ENGINE) != 1 &&
+      kmm::supported(a, b, batches, m, n, k, ac, bc))
+    return kmm::launch(a, b, c, batches, m, n, k, dt, ac, bc, stream);
   DISPATCH_16(dt, (kn_matmul_float_kernel<__half><<<g, 256, 0, ST(stream)>>>((__half const *)a, (__half const *)b, (__half *)c, batches, m, n, k, ac, bc)),
               (kn_matmul_float_kernel<__nv_bfloat16><<<g, 256, 0, ST(stream)>>>((__nv_bfloat16 const *)a, (__nv_bfloat16 const *)b, (__nv_bfloat16 *)c, batches, m, n, k, ac, bc)))
   return check_launch("kn_matmul_float_kernel");

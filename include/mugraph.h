@@ -134,8 +134,9 @@ enum {
   MG_OPT_INTERP_THREADS = 4,    /* generic interpreters: threads per block, 256 / 512 / 1024 */
   MG_OPT_WAIT_LIMIT = 5,        /* split-KV attention: polls before a tile wait gives up; 1 = give up without polling
                                    (failure-path tests), n > 1 = n polls */
-  MG_OPT_ATTN_PERSISTENT = 6    /* split-KV attention with more blocks than fit at once: 1 = one block per work item,
+  MG_OPT_ATTN_PERSISTENT = 6,   /* split-KV attention with more blocks than fit at once: 1 = one block per work item,
                                    2 = resident blocks that walk the work items (the default where it fits) */
+  MG_OPT_KN_MATMUL_ENGINE = 7   /* kernel-level float matmul: 1 = CUDA cores, 2 = tcgen05 (the default where it applies) */
 };
 int mg_runtime_set_option(mg_runtime *rt, int32_t key, int32_t value);
 int mg_runtime_get_option(mg_runtime *rt, int32_t key, int32_t *value);

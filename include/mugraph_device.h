@@ -259,7 +259,9 @@ enum {
                                      polling (failure-path tests), n > 1 = n polls */
   MGD_OPT_ATTN_PERSISTENT = 6,    /* split-KV attention with more blocks than fit at once: 1 = one block per work item,
                                      2 = resident blocks that walk the work items (the default where it fits) */
-  MGD_OPT_COUNT = 7
+  MGD_OPT_KN_MATMUL_ENGINE = 7,   /* kernel-level float matmul: 1 = CUDA cores, 2 = tcgen05 (the default where the
+                                     operands are 16-byte aligned with rows of a multiple of 8 elements) */
+  MGD_OPT_COUNT = 8
 };
 int mgd_set_option(int32_t key, int32_t value);
 int mgd_get_option(int32_t key, int32_t *value);

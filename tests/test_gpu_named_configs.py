@@ -269,6 +269,37 @@ def test_kn_float_matmul_exp_reduction(runtime, dtype):
         assert np.array_equal(H.download_fingerprint(), mo.kn_reduction_fp(x[2], 1, 64))
 
 
+@pytest.mark.parametrize("dtype", [mg.float16, mg.bfloat16], ids=["fp16", "bf16"])
+@pytest.mark.parametrize("shape", [(2, 256, 4096, 64), (3, 200, 136, 328), (1, 32, 8, 16), (2, 128, 128, 1024), (1, 520, 72, 40)],
+                         ids=["spec_decode_s", "ragged", "smallest", "square_tiles", "many_row_tiles"])
+def test_kn_float_matmul_on_tensor_cores(runtime, shape, dtype):
+    """Kernel-level float matmul, every combination of operand layouts, on the tcgen05 kernel and on the CUDA-core
+    loop: both against the fp64 product of the stored 16-bit operands.  Shapes with ragged edges in every dimension
+    (rows, columns and contraction steps beyond the tensors are zeros of the TMA fill)."""
+    B, M, N, K = shape
+    rng = np.random.default_rng(sum(shape))
+    rnd = lambda a: from_bits(to_bits(a, dtype), dtype)
+    a = rnd(rng.standard_normal((B, M, K)) / np.sqrt(K))
+    b = rnd(rng.standard_normal((B, K, N)))
+    want = a.astype(np.float64) @ b.astype(np.float64)
+    for a_layout in (mg.DmemRowMajor, mg.DmemColumnMajor):
+        for b_layout in (mg.DmemRowMajor, mg.DmemColumnMajor):
+            for engine in (2, 1):
+                runtime.set_option(mg.OPT_KN_MATMUL_ENGINE, engine)
+                try:
+                    with mg.PyGraph(runtime) as g:
+                        A = g.new_input((B, M, K), dtype, a_layout)
+                        Bt = g.new_input((B, K, N), dtype, b_layout)
+                        C = g.matmul(A, Bt)
+                        A.upload_data(to_bits(a if a_layout == mg.DmemRowMajor else np.ascontiguousarray(a.transpose(0, 2, 1)), dtype))
+                        Bt.upload_data(to_bits(b if b_layout == mg.DmemRowMajor else np.ascontiguousarray(b.transpose(0, 2, 1)), dtype))
+                        g.run()
+                        got = from_bits(C.download_data(), dtype).reshape(C.shape)
+                        assert_close(got, want, dtype, "layouts %d/%d engine %d" % (a_layout, b_layout, engine))
+                finally:
+                    runtime.set_option(mg.OPT_KN_MATMUL_ENGINE, 0)
+
+
 # ---- launch policies ------------------------------------------------------------------------------------------------------
 def test_throughput_policy_parity_and_captured_overlap(runtime):
     """The launch sizing the benchmark's headline uses (small blocks, several calls in flight): every graph on its
