@@ -30,6 +30,99 @@ __global__ void kn_matmul_fp_kernel(uint16_t const *A, uint16_t const *B, uint16
   }
 }
 
+// The same product on the integer tensor cores, exact (the byte-plane scheme of the threadblock-level matmul,
+// fp_interp.cu): a uint16 is lo + 256 hi, a row-major uint16 tile is a byte matrix with the planes interleaved along
+// k, and the 16 rows of an m16n8k32 u8 MMA carry three byte-masked copies of 4 rows of A - [lo,0], [0,hi], [hi,lo] -
+// which give LL, HH and LH+HL in int32;  A B = LL + 256 (LH+HL) + 65536 HH, reduced modulo PQ once per output.
+// A block of 4 warps owns a 16 x 64 tile of C (a warp: 4 rows x 64 columns, eight independent MMAs per k-step) and
+// walks k in chunks of 64 staged in shared memory with 16-byte loads (rows padded by 16 bytes: conflict-free
+// ldmatrix).  Needs k and n multiples of 8, 16-byte aligned operands and k <= 16384 (int32 sums); rows, columns and
+// k-steps past the extents are zeros.
+constexpr int kFpTM = 16, kFpTN = 64, kFpTK = 64, kFpPitch = 72;
+__global__ void __launch_bounds__(128) kn_matmul_fp_tc_kernel(uint16_t const *A, uint16_t const *B, uint16_t *C, int batches, int m,
+                                                              int n, int k) {
+  __shared__ __align__(16) uint16_t As[kFpTM * kFpPitch];
+  __shared__ __align__(16) uint16_t Bs[kFpTK * kFpPitch];
+  int const tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  int const g = lane >> 2, t = lane & 3, mi = lane >> 3, rr = lane & 7;
+  int const tiles_m = (m + kFpTM - 1) / kFpTM, tiles_n = (n + kFpTN - 1) / kFpTN;
+  int64_t const tiles = (int64_t)batches * tiles_m * tiles_n;
+  uint32_t const bs_base = (uint32_t)__cvta_generic_to_shared(Bs);
+  for (int64_t tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+    int const nt_ = (int)(tile % tiles_n), mt = (int)((tile / tiles_n) % tiles_m);
+    int64_t const b = tile / ((int64_t)tiles_n * tiles_m);
+    int const m0 = mt * kFpTM, n0 = nt_ * kFpTN;
+    uint16_t const *Ab = A + b * m * k, *Bb = B + b * k * n;
+    int const row = warp * 4 + (g & 3); // row of the tile this lane's A fragments come from
+    int32_t acc[4][2][4];
+#pragma unroll
+    for (int c = 0; c < 4; c++)
+#pragma unroll
+      for (int h = 0; h < 2; h++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) acc[c][h][j] = 0;
+    for (int k0 = 0; k0 < k; k0 += kFpTK) {
+      __syncthreads(); // the previous chunk (or tile) has been read
+      {
+        int const r = tid >> 3, c8 = (tid & 7) * 8;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (m0 + r < m && k0 + c8 < k) v = __ldg(reinterpret_cast<uint4 const *>(Ab + (int64_t)(m0 + r) * k + k0 + c8));
+        *reinterpret_cast<uint4 *>(As + r * kFpPitch + c8) = v;
+      }
+#pragma unroll
+      for (int i = 0; i < 4; i++) {
+        int const idx = tid + i * 128, r = idx >> 3, c8 = (idx & 7) * 8;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (k0 + r < k && n0 + c8 < n) v = __ldg(reinterpret_cast<uint4 const *>(Bb + (int64_t)(k0 + r) * n + n0 + c8));
+        *reinterpret_cast<uint4 *>(Bs + r * kFpPitch + c8) = v;
+      }
+      __syncthreads();
+      uint16_t const *arow = As + row * kFpPitch + 2 * t;
+#pragma unroll
+      for (int ks = 0; ks < kFpTK / 16; ks++) {
+        uint32_t const w0 = *reinterpret_cast<uint32_t const *>(arow + ks * 16);
+        uint32_t const w1 = *reinterpret_cast<uint32_t const *>(arow + ks * 16 + 8);
+        uint32_t a[4];
+        if (g < 4) { // MMA rows 0-3: [lo,0] bytes; MMA rows 8-11: [hi,lo] bytes
+          a[0] = w0 & 0x00FF00FFu; a[2] = w1 & 0x00FF00FFu;
+          a[1] = __byte_perm(w0, 0, 0x2301); a[3] = __byte_perm(w1, 0, 0x2301);
+        } else {     // MMA rows 4-7: [0,hi] bytes; MMA rows 12-15 unused
+          a[0] = w0 & 0xFF00FF00u; a[2] = w1 & 0xFF00FF00u;
+          a[1] = 0u; a[3] = 0u;
+        }
+        uint32_t bf[4][4];
+#pragma unroll
+        for (int c = 0; c < 4; c++) {
+          // ldmatrix (transposed): this lane addresses k-row (mi % 2) * 8 + rr of the 8 columns starting at (mi / 2) * 8
+          uint32_t const addr = bs_base + (uint32_t)(((ks * 16 + (mi & 1) * 8 + rr) * kFpPitch + c * 16 + (mi >> 1) * 8) * 2);
+          asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                       : "=r"(bf[c][0]), "=r"(bf[c][1]), "=r"(bf[c][2]), "=r"(bf[c][3]) : "r"(addr));
+        }
+#pragma unroll
+        for (int c = 0; c < 4; c++)
+#pragma unroll
+          for (int h = 0; h < 2; h++)
+            asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                         : "+r"(acc[c][h][0]), "+r"(acc[c][h][1]), "+r"(acc[c][h][2]), "+r"(acc[c][h][3])
+                         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(bf[c][2 * h]), "r"(bf[c][2 * h + 1]));
+      }
+    }
+#pragma unroll
+    for (int c = 0; c < 4; c++)
+#pragma unroll
+      for (int h = 0; h < 2; h++) {
+        // lanes 16-31 hold the HH sums of the rows lanes 0-15 work on
+        int32_t const hh0 = __shfl_down_sync(0xffffffffu, acc[c][h][0], 16), hh1 = __shfl_down_sync(0xffffffffu, acc[c][h][1], 16);
+        int const col = n0 + c * 16 + h * 8 + 2 * t;
+        if (g < 4 && m0 + row < m && col < n) {
+          uint32_t v0 = ((uint32_t)acc[c][h][0] % PQ + 256u * ((uint32_t)acc[c][h][2] % PQ) + (65536u % PQ) * ((uint32_t)hh0 % PQ)) % PQ;
+          uint32_t v1 = ((uint32_t)acc[c][h][1] % PQ + 256u * ((uint32_t)acc[c][h][3] % PQ) + (65536u % PQ) * ((uint32_t)hh1 % PQ)) % PQ;
+          *reinterpret_cast<uint32_t *>(C + (b * m + m0 + row) * (int64_t)n + col) = v0 | (v1 << 16);
+        }
+      }
+  }
+}
+
 __global__ void kn_exp_fp_kernel(uint16_t const *x, uint16_t *y, int64_t n) {
   int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) y[i] = (uint16_t)field_exp(x[i]);
@@ -130,6 +223,15 @@ extern "C" {
 int mgd_kn_matmul_fingerprint(const uint16_t *a, const uint16_t *b, uint16_t *c, int32_t batches, int32_t m, int32_t n,
                               int32_t k, void *stream) {
   if (!a || !b || !c || batches <= 0 || m <= 0 || n <= 0 || k <= 0) return set_error(MG_ERR_INVALID_ARGUMENT, "kn matmul: bad argument");
+  // integer tensor cores where the operands allow 16-byte loads and the int32 plane sums cannot overflow
+  // (MGD_OPT_KN_MATMUL_ENGINE: 1 = CUDA cores)
+  if (option(MGD_OPT_KN_MATMUL_ENGINE) != 1 && (k & 7) == 0 && (n & 7) == 0 && k <= 16384 &&
+      ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(c)) & 15) == 0) {
+    int64_t const tiles = (int64_t)batches * ((m + kFpTM - 1) / kFpTM) * ((n + kFpTN - 1) / kFpTN);
+    int64_t const cap = 148 * 16;
+    kn_matmul_fp_tc_kernel<<<(unsigned)(tiles < cap ? tiles : cap), 128, 0, ST(stream)>>>(a, b, c, batches, m, n, k);
+    return check_launch("kn_matmul_fp_tc_kernel");
+  }
   kn_matmul_fp_kernel<<<blocks_for((int64_t)batches * m * n), 256, 0, ST(stream)>>>(a, b, c, batches, m, n, k);
   return check_launch("kn_matmul_fp_kernel");
 }

@@ -300,6 +300,35 @@ def test_kn_float_matmul_on_tensor_cores(runtime, shape, dtype):
                     runtime.set_option(mg.OPT_KN_MATMUL_ENGINE, 0)
 
 
+@pytest.mark.parametrize("shape", [(2, 256, 4096, 64), (3, 37, 136, 328), (1, 5, 8, 16), (2, 64, 64, 4096), (1, 130, 72, 24)],
+                         ids=["spec_decode_s", "ragged", "smallest", "long_k", "ragged_k"])
+@pytest.mark.parametrize("hi", [mo.FP_P, 65536], ids=["lt_P", "any_u16"])
+def test_kn_fingerprint_matmul_on_tensor_cores(runtime, shape, hi):
+    """Kernel-level fingerprint matmul on the integer tensor cores (byte planes) and on the CUDA-core loop: both equal
+    the oracle's exact product modulo PQ, for every storable operand value and for ragged shapes."""
+    B, M, N, K = shape
+    rng = np.random.default_rng(sum(shape) + hi)
+    a = rng.integers(0, hi, size=(B, M, K)).astype(np.uint16)
+    b = rng.integers(0, hi, size=(B, K, N)).astype(np.uint16)
+    if hi == 65536:
+        a[0, 0, :] = 65535
+        b[0, :, 0] = 65535
+    want = mo.kn_matmul_fp(a, b)
+    for engine in (2, 1):
+        runtime.set_option(mg.OPT_KN_MATMUL_ENGINE, engine)
+        try:
+            with mg.PyGraph(runtime) as g:
+                A = g.new_input((B, M, K))
+                Bt = g.new_input((B, K, N))
+                C = g.matmul(A, Bt)
+                A.upload_fingerprint(a)
+                Bt.upload_fingerprint(b)
+                g.fingerprint()
+                assert np.array_equal(C.download_fingerprint(), want), "engine %d" % engine
+        finally:
+            runtime.set_option(mg.OPT_KN_MATMUL_ENGINE, 0)
+
+
 # ---- launch policies ------------------------------------------------------------------------------------------------------
 def test_throughput_policy_parity_and_captured_overlap(runtime):
     """The launch sizing the benchmark's headline uses (small blocks, several calls in flight): every graph on its
