@@ -129,12 +129,26 @@ __device__ __forceinline__ void merge_head(uint16_t const *op, uint16_t const *r
   }
 }
 
+// Which slots hold sums when the split-KV kernel summed runs of tiles: the launch's tiles were dealt to blocks in
+// order, `per` tiles each and the first `extra` blocks one more; a head's tiles [unit * tiles_per_head, + tiles_per_head)
+// then lie in consecutive blocks, and block i of them wrote slot i.  per = 0: every slot holds a sum.
+struct MergeRuns {
+  uint32_t per, extra, tiles_per_head;
+};
+__device__ __forceinline__ uint64_t held_slots(MergeRuns const &runs, uint32_t unit) {
+  if (runs.per == 0) return ~0ull;
+  uint32_t const wide = runs.extra * (runs.per + 1);
+  auto block_of = [&](uint32_t g) { return g < wide ? g / (runs.per + 1) : runs.extra + (g - wide) / runs.per; };
+  uint32_t const count = block_of((unit + 1) * runs.tiles_per_head - 1) - block_of(unit * runs.tiles_per_head) + 1;
+  return count >= 64 ? ~0ull : ((1ull << count) - 1ull);
+}
+
 // Stand-alone merge launch (attn_split.cu): blocks of 128 threads take 8 query rows of one head each.  With
 // `after_previous_kernel` the launch uses programmatic stream serialisation: its blocks are scheduled while the
 // previous kernel of the stream drains and wait (griddepcontrol.wait) until that kernel's memory is visible.
 // kind: kMergeF16 / kMergeBF16 / kMergeFingerprint; d must be 64 or 128 (returns false otherwise, nothing launched).
 bool launch_merge_rows(int kind, int d, uint16_t const *o_part, uint16_t const *r_part, uint16_t *out, int heads, int m,
                        int splits, int num_sets, long long o_set_stride, long long r_set_stride, long long out_set_stride,
-                       bool after_previous_kernel, void *stream);
+                       bool after_previous_kernel, void *stream, MergeRuns runs = MergeRuns{0, 0, 0});
 
 } // namespace mgk

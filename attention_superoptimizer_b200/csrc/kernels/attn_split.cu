@@ -675,8 +675,11 @@ constexpr int kMergeRowsPerBlock = 8;
 template <int KIND, int D>
 __global__ void __launch_bounds__(128) attn_merge_rows_kernel(uint16_t const *o_part, uint16_t const *r_part, uint16_t *out,
                                                               int heads, int m, int splits, long long o_stride,
-                                                              long long r_stride, long long out_stride) {
+                                                              long long r_stride, long long out_stride, MergeRuns runs) {
   asm volatile("griddepcontrol.wait;" ::: "memory"); // no-op unless launched with programmatic serialisation
+  // The kernel before this one is complete now; the one behind it may be scheduled while this small grid runs (it
+  // holds back its own stores until this grid has completed).
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   int const chunks = (m + kMergeRowsPerBlock - 1) / kMergeRowsPerBlock;
   int const chunk = blockIdx.x % chunks, bh = blockIdx.x / chunks, head = bh % heads;
   long long const set = bh / heads;
@@ -684,12 +687,12 @@ __global__ void __launch_bounds__(128) attn_merge_rows_kernel(uint16_t const *o_
   uint16_t const *op = o_part + set * o_stride + ((long long)head * m + r0) * splits * D;
   uint16_t const *rp = r_part + set * r_stride + ((long long)head * m + r0) * splits;
   uint16_t *dst = out + set * out_stride + ((long long)head * m + r0) * D;
-  merge_head<KIND, D>(op, rp, dst, rows, splits, (int)threadIdx.x, 128);
+  merge_head<KIND, D>(op, rp, dst, rows, splits, (int)threadIdx.x, 128, held_slots(runs, (uint32_t)bh));
 }
 
 template <int KIND, int D>
 static void launch_merge_rows_t(uint16_t const *o_part, uint16_t const *r_part, uint16_t *out, int heads, int m, int splits,
-                                int num_sets, long long os, long long rs, long long outs, bool pdl, void *stream) {
+                                int num_sets, long long os, long long rs, long long outs, bool pdl, void *stream, MergeRuns runs) {
   cudaLaunchConfig_t cfg = {};
   int const chunks = (m + kMergeRowsPerBlock - 1) / kMergeRowsPerBlock;
   cfg.gridDim = dim3((unsigned)(heads * num_sets * chunks), 1, 1);
@@ -702,16 +705,16 @@ static void launch_merge_rows_t(uint16_t const *o_part, uint16_t const *r_part, 
     cfg.attrs = attr;
     cfg.numAttrs = 1;
   }
-  cudaLaunchKernelEx(&cfg, attn_merge_rows_kernel<KIND, D>, o_part, r_part, out, heads, m, splits, os, rs, outs);
+  cudaLaunchKernelEx(&cfg, attn_merge_rows_kernel<KIND, D>, o_part, r_part, out, heads, m, splits, os, rs, outs, runs);
 }
 
 bool launch_merge_rows(int kind, int d, uint16_t const *o_part, uint16_t const *r_part, uint16_t *out, int heads, int m,
-                       int splits, int num_sets, long long os, long long rs, long long outs, bool pdl, void *stream) {
+                       int splits, int num_sets, long long os, long long rs, long long outs, bool pdl, void *stream, MergeRuns runs) {
   if (d != 64 && d != 128) return false;
 #define MG_MERGE_CASE(K)                                                                                           \
   if (kind == K) {                                                                                                   \
-    if (d == 128) launch_merge_rows_t<K, 128>(o_part, r_part, out, heads, m, splits, num_sets, os, rs, outs, pdl, stream); \
-    else launch_merge_rows_t<K, 64>(o_part, r_part, out, heads, m, splits, num_sets, os, rs, outs, pdl, stream);         \
+    if (d == 128) launch_merge_rows_t<K, 128>(o_part, r_part, out, heads, m, splits, num_sets, os, rs, outs, pdl, stream, runs); \
+    else launch_merge_rows_t<K, 64>(o_part, r_part, out, heads, m, splits, num_sets, os, rs, outs, pdl, stream, runs);       \
     return true;                                                                                                     \
   }
   MG_MERGE_CASE(kMergeF16)

@@ -71,12 +71,24 @@ constexpr int kEBytes = kTileKv * kNQ * 2; // E^T: [128 kv][32 q]
 constexpr uint32_t kTmemCols = 128;        // S^T x2, O^T x2, 32 columns each
 constexpr int kThreads = 352;
 
-// Position in a block's flat tile sequence, advanced without divisions: item index li, tile j of the item, ring
-// stage s and the number of times the ring has wrapped (its low bit is the stage barriers' phase).
+// Position in a block's flat tile sequence, advanced without divisions.  The block's tiles are consecutive tiles of
+// the launch (item-major, so consecutive tiles of a head are consecutive KV positions).  A *run* is a stretch of
+// them that is summed into one accumulator: one item, or - when the partials are scratch - every tile of a head that
+// the block holds.  `period` = tiles per item, or per head in the second case; `pos` / `unit` = the tile's index in
+// its period and the period's number (item, or (set, head)).  n = tile number in the block, ri = run number in the
+// block, s / wraps = ring stage and how often the ring has wrapped (its low bit is the stage barriers' phase).
 struct TileCursor {
-  int li = 0, j = 0, s = 0, wraps = 0;
-  __device__ __forceinline__ void advance(int tiles_per_item) {
-    if (++j == tiles_per_item) { j = 0; li++; }
+  int n = 0, pos = 0, unit = 0, ri = 0, s = 0, wraps = 0;
+  __device__ __forceinline__ void start(uint32_t first_tile, int period) {
+    unit = (int)(first_tile / (uint32_t)period);
+    pos = (int)(first_tile - (uint32_t)unit * (uint32_t)period);
+  }
+  __device__ __forceinline__ bool first() const { return n == 0 || pos == 0; }
+  __device__ __forceinline__ bool last(int total, int period) const { return n == total - 1 || pos == period - 1; }
+  __device__ __forceinline__ void advance(int total, int period) {
+    if (last(total, period)) ri++;
+    n++;
+    if (++pos == period) { pos = 0; unit++; }
     if (++s == kStages) { s = 0; wraps++; }
   }
 };
@@ -92,13 +104,25 @@ struct Params {
   long long o_set_stride, r_set_stride;
   int heads, m, splits, tiles, kv_len, causal_window, num_items;
   int early_loads; // the inputs were not written by the previous kernel of the stream: load before waiting for it
+  // Work split: the launch's tiles are dealt in granules (an item's tiles, or single tiles when runs are summed) -
+  // block b takes `per` granules, the first `extra` blocks one more.
+  int sum_runs;    // the partials are scratch: a block sums every tile of a head it holds and writes one partial per run,
+                   // into slot (block - block that holds the head's first tile)
+  uint32_t per, extra;
 };
+
+// the block that holds tile g of the launch (granule = tiles per granule)
+__device__ __forceinline__ uint32_t block_of_tile(uint32_t g, uint32_t granule, uint32_t per, uint32_t extra) {
+  uint32_t const q = g / granule, wide = extra * (per + 1);
+  return q < wide ? q / (per + 1) : extra + (q - wide) / per;
+}
 
 struct Shared {
   uint64_t k_full[kStages], v_full[kStages], kv_empty[kStages];
   uint64_t q_full[2], q_empty[2], s_full[2], e_full[2], e_free[2], o_full[2], o_free[2], r_full[2], r_free[2];
   uint32_t tmem_base;
   int abort_flag;
+
   float rsum[2][4][kNQ]; // [item parity][exp warp][query column]
 };
 
@@ -157,28 +181,28 @@ attn_split_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_con
   // a kernel launched behind this one with programmatic serialisation (the merge) may be scheduled from now on;
   // it still waits for this grid to complete before it reads anything
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  // this block's items are blockIdx.x, blockIdx.x + gridDim.x, ...; its tiles form one sequence n = li * T + j
-  int const my_items = (p.num_items - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
-  int const total = my_items * T;
-  auto item_of = [&](int li) { return (int)blockIdx.x + li * (int)gridDim.x; };
-  // item -> (input set, head, split); (set, head) is one coordinate of the tensor maps
-  auto batch_of = [&](int item) { return item / p.splits; };
-  auto split_of = [&](int item) { return item % p.splits; };
+  // this block's tiles: granules [b * per + min(b, extra), + per (+ 1)) of the launch
+  uint32_t const granule = p.sum_runs ? 1u : (uint32_t)T;
+  uint32_t const first_tile = (blockIdx.x * p.per + (blockIdx.x < p.extra ? blockIdx.x : p.extra)) * granule;
+  int const total = (int)((p.per + (blockIdx.x < p.extra ? 1u : 0u)) * granule);
+  int const period = p.sum_runs ? p.splits * T : T;  // tiles of a run's period: a head, or an item
+  int const parts = p.sum_runs ? 1 : p.splits;       // periods per (set, head)
+  // period number -> (set, head), one coordinate of the tensor maps; tile -> first KV position
+  auto batch_of = [&](int unit) { return unit / parts; };
+  auto kv_of = [&](int unit, int pos) { return ((unit % parts) * period + pos) * kTileKv; };
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     bool ok = true;
     TDECL(w_e = 0, t0 = clock64());
     TileCursor c;
-    int batch = 0, kv_base = 0;
+    c.start(first_tile, period);
     if (!p.early_loads) asm volatile("griddepcontrol.wait;" ::: "memory");
-    for (int n = 0; n < total && ok; n++, c.advance(T)) {
-      int const li = c.li, j = c.j;
-      if (j == 0) { // a new item: its coordinates, and its Q
-        int const qb = li & 1, item = item_of(li);
-        batch = batch_of(item);
-        kv_base = split_of(item) * T * kTileKv;
-        if (li >= 2) ok = mbar_wait(smem_u32(&sh->q_empty[qb]), (uint32_t)(((li >> 1) - 1) & 1), abort_flag);
+    for (int n = 0; n < total && ok; n++, c.advance(total, period)) {
+      int const batch = batch_of(c.unit);
+      if (c.first()) { // a new run: its Q
+        int const ri = c.ri, qb = ri & 1;
+        if (ri >= 2) ok = mbar_wait(smem_u32(&sh->q_empty[qb]), (uint32_t)(((ri >> 1) - 1) & 1), abort_flag);
         if (!ok) break;
         if (lane == 0) {
           uint32_t full = smem_u32(&sh->q_full[qb]), dst = q_smem + (uint32_t)(qb * kQBytes);
@@ -187,7 +211,7 @@ attn_split_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_con
           tma_load_3d(dst + kQBytes / 2, &q_map, full, 64, 0, batch);
         }
       }
-      int const s = c.s, kv0 = kv_base + j * kTileKv;
+      int const s = c.s, kv0 = kv_of(c.unit, c.pos);
       TICK(a0);
       if (n >= kStages) ok = mbar_wait(smem_u32(&sh->kv_empty[s]), (uint32_t)((c.wraps - 1) & 1), abort_flag);
       TOCK(w_e, a0);
@@ -225,10 +249,11 @@ attn_split_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_con
     bool ok = true;
     TDECL(w_q = 0, w_k = 0, w_ef = 0, c_s = 0, c_lat = 0, t0 = clock64());
     TileCursor c;
-    for (int n = 0; n < total && ok; n++, c.advance(T)) {
-      int const li = c.li, j = c.j, qb = li & 1, s = c.s, b = n & 1;
+    c.start(first_tile, period);
+    for (int n = 0; n < total && ok; n++, c.advance(total, period)) {
+      int const ri = c.ri, qb = ri & 1, s = c.s, b = n & 1;
       TICK(a0);
-      if (j == 0) ok = mbar_wait(smem_u32(&sh->q_full[qb]), (uint32_t)((li >> 1) & 1), abort_flag);
+      if (c.first()) ok = mbar_wait(smem_u32(&sh->q_full[qb]), (uint32_t)((ri >> 1) & 1), abort_flag);
       TOCK(w_q, a0);
       TICK(a1);
       if (ok) ok = mbar_wait(smem_u32(&sh->k_full[s]), (uint32_t)(c.wraps & 1), abort_flag);
@@ -250,7 +275,7 @@ attn_split_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_con
           umma_f16(tmem_s, a, bq, idesc_s, ks > 0);
         }
         umma_commit(smem_u32(&sh->s_full[b]));
-        if (j == T - 1) umma_commit(smem_u32(&sh->q_empty[qb])); // the item's last use of its Q
+        if (c.last(total, period)) umma_commit(smem_u32(&sh->q_empty[qb])); // the run's last use of its Q
         TOCK(c_s, i0);
 #ifdef MG_STC_TIMING
         for (int i = 0; i < 100000 && !mbar_try_wait(smem_u32(&sh->s_full[b]), (uint32_t)((n >> 1) & 1)); i++) {
@@ -269,10 +294,12 @@ attn_split_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_con
     bool ok = true;
     TDECL(w_of = 0, w_ef = 0, w_v = 0, c_o = 0, t0 = clock64());
     TileCursor c;
-    for (int t = 0; t < total && ok; t++, c.advance(T)) {
-      int const li = c.li, j = c.j, ob = li & 1, s = c.s, eb = t & 1;
+    c.start(first_tile, period);
+    for (int t = 0; t < total && ok; t++, c.advance(total, period)) {
+      int const ri = c.ri, ob = ri & 1, s = c.s, eb = t & 1;
+      bool const run_begins = c.first();
       TICK(a2);
-      if (j == 0 && li >= 2) ok = mbar_wait(smem_u32(&sh->o_free[ob]), (uint32_t)(((li >> 1) - 1) & 1), abort_flag);
+      if (run_begins && ri >= 2) ok = mbar_wait(smem_u32(&sh->o_free[ob]), (uint32_t)(((ri >> 1) - 1) & 1), abort_flag);
       TOCK(w_of, a2);
       TICK(a3);
       if (ok) ok = mbar_wait(smem_u32(&sh->e_full[eb]), (uint32_t)((t >> 1) & 1), abort_flag);
@@ -290,12 +317,12 @@ attn_split_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_con
         for (int ks = 0; ks < kTileKv / 16; ks++) {
           uint64_t const a = vd + (V_KV ? mn_major_step(ks) : k_major_step(ks));
           uint64_t const be = ed + (uint64_t)((ks * 16 * 64) >> 4);
-          umma_f16(tmem_o, a, be, idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
+          umma_f16(tmem_o, a, be, idesc_o, (!run_begins || ks > 0) ? 1u : 0u);
         }
         // S^T of this tile completed before its E^T existed, so K_t and V_t are both consumed now
         umma_commit(smem_u32(&sh->kv_empty[s]));
         umma_commit(smem_u32(&sh->e_free[eb]));
-        if (j == T - 1) umma_commit(smem_u32(&sh->o_full[ob]));
+        if (c.last(total, period)) umma_commit(smem_u32(&sh->o_full[ob]));
         TOCK(c_o, i2);
       }
       __syncwarp();
@@ -313,11 +340,10 @@ attn_split_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_con
     bool ok = true;
     TDECL(w_s = 0, w_rf = 0, c_exp = 0, t0 = clock64());
     TileCursor c;
-    int kv_base = 0;
-    for (int n = 0; n < total && ok; n++, c.advance(T)) {
-      int const li = c.li, j = c.j, b = n & 1;
-      if (j == 0) kv_base = split_of(item_of(li)) * T * kTileKv;
-      int const kv_tile = kv_base + j * kTileKv; // first KV position of this tile
+    c.start(first_tile, period);
+    for (int n = 0; n < total && ok; n++, c.advance(total, period)) {
+      int const ri = c.ri, b = n & 1;
+      int const kv_tile = kv_of(c.unit, c.pos); // first KV position of this tile
       TICK(a0);
       ok = mbar_wait(smem_u32(&sh->s_full[b]), (uint32_t)((n >> 1) & 1), abort_flag);
       TOCK(w_s, a0);
@@ -356,7 +382,7 @@ attn_split_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_con
       tc_fence_before();
       mbar_arrive(smem_u32(&sh->e_full[b]));
       TOCK(c_exp, a1);
-      if (j == T - 1) {
+      if (c.last(total, period)) {
         // row sums over this warp's 32 KV lanes: transpose-reduce, lane q ends with column q
 #pragma unroll
         for (int s = 16; s >= 1; s >>= 1) {
@@ -368,9 +394,9 @@ attn_split_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_con
             rs[i] = keep + __shfl_xor_sync(0xffffffffu, send, s);
           }
         }
-        int const ob = li & 1;
+        int const ob = ri & 1;
         TICK(a2);
-        if (li >= 2) ok = mbar_wait(smem_u32(&sh->r_free[ob]), (uint32_t)(((li >> 1) - 1) & 1), abort_flag);
+        if (ri >= 2) ok = mbar_wait(smem_u32(&sh->r_free[ob]), (uint32_t)(((ri >> 1) - 1) & 1), abort_flag);
         TOCK(w_rf, a2);
         if (!ok) break;
         sh->rsum[ob][warp - 2][lane] = rs[0];
@@ -392,18 +418,26 @@ attn_split_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_con
     // has completed.
     asm volatile("griddepcontrol.wait;" ::: "memory");
     TDECL(w_r = 0, w_o = 0, c_out = 0, t0 = clock64());
-    for (int li = 0; li < my_items; li++) {
-      int const ob = li & 1, item = item_of(li), batch = batch_of(item), split = split_of(item);
+    // one pass per run: [g, run_end) of the launch's tiles
+    uint32_t const end_tile = first_tile + (uint32_t)total;
+    int ri = 0;
+    for (uint32_t g = first_tile; g < end_tile; ri++) {
+      int const ob = ri & 1, unit = (int)(g / (uint32_t)period), batch = batch_of(unit);
+      uint32_t const period_end = (uint32_t)(unit + 1) * (uint32_t)period;
+      // where the run's sums go: the item's split, or the number of this block among the blocks that hold the head
+      int const split = p.sum_runs ? (int)(blockIdx.x - block_of_tile((uint32_t)unit * (uint32_t)period, granule, p.per, p.extra))
+                                   : unit % p.splits;
+      g = period_end < end_tile ? period_end : end_tile;
       int const set = batch / p.heads, head = batch % p.heads;
       float r = 0.f;
       TICK(a0);
-      if (ok) ok = mbar_wait(smem_u32(&sh->r_full[ob]), (uint32_t)((li >> 1) & 1), abort_flag);
+      if (ok) ok = mbar_wait(smem_u32(&sh->r_full[ob]), (uint32_t)((ri >> 1) & 1), abort_flag);
       TOCK(w_r, a0);
       TICK(a1);
       if (ok) {
         if (et < kNQ) r = sh->rsum[ob][0][et] + sh->rsum[ob][1][et] + sh->rsum[ob][2][et] + sh->rsum[ob][3][et];
         mbar_arrive(smem_u32(&sh->r_free[ob]));
-        ok = mbar_wait(smem_u32(&sh->o_full[ob]), (uint32_t)((li >> 1) & 1), abort_flag);
+        ok = mbar_wait(smem_u32(&sh->o_full[ob]), (uint32_t)((ri >> 1) & 1), abort_flag);
       }
       TOCK(w_o, a1);
       TICK(a2);
@@ -432,10 +466,10 @@ attn_split_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_con
       asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt_now));
       if (gt_now - gt_entry > 36000)
         printf("slow [%d] epilogue done +%llu ns: wait r_full %lld o_full %lld out %lld items %d\n", (int)blockIdx.x,
-               gt_now - gt_entry, w_r, w_o, c_out, my_items);
+               gt_now - gt_entry, w_r, w_o, c_out, ri);
     }
 #endif
-    if (et == 0) TPRINT("[%d] epilogue: total %lld wait r_full %lld o_full %lld out %lld items %d\n", (int)blockIdx.x, clock64() - t0, w_r, w_o, c_out, my_items);
+    if (et == 0) TPRINT("[%d] epilogue: total %lld wait r_full %lld o_full %lld out %lld tiles %d\n", (int)blockIdx.x, clock64() - t0, w_r, w_o, c_out, total);
   }
 
   // ---- teardown: every role arrives here, failed or not --------------------------------------------------
@@ -519,9 +553,26 @@ int launch(mgd_attn_split const *p, void const *q, void const *k, void const *v,
   a.heads = p->heads; a.m = p->m; a.splits = p->splits; a.tiles = p->forloop_range * 64 / kTileKv;
   a.kv_len = p->kv_len; a.causal_window = p->causal_window;
   a.num_items = (int)((int64_t)p->heads * p->splits * p->num_sets);
+  // Work split.  When the merge rides along and the partials are scratch (overlap bit 3), the tiles are dealt singly
+  // - every block within one tile of the average - and a block sums what it holds of a head; a head then has one
+  // partial per block that touched it, which must fit the slots there are.
+  int64_t const total_tiles = (int64_t)a.num_items * a.tiles, tiles_per_head = (int64_t)p->splits * a.tiles;
+  if (total_tiles > 0x7fffffffLL) return set_error(MG_ERR_UNSUPPORTED, "tensor-core split-KV attention: too many tiles for one launch");
+  bool sum_runs = opts && opts->merged_out && (opts->overlap & 8);
+  unsigned blocks = 0;
+  for (;;) {
+    int64_t const granules = sum_runs ? total_tiles : (int64_t)a.num_items;
+    blocks = (unsigned)(granules < sm_count() ? granules : sm_count());
+    a.per = (uint32_t)(granules / blocks);
+    a.extra = (uint32_t)(granules % blocks);
+    if (!sum_runs) break;
+    int64_t const runs_per_head = (tiles_per_head + a.per - 1) / a.per + 1;
+    if (runs_per_head <= p->splits && runs_per_head <= 63) break;
+    sum_runs = false;
+  }
+  a.sum_runs = sum_runs ? 1 : 0;
   size_t const smem = 1024 + (size_t)kStages * 2 * kOperand + 2 * kQBytes + 2 * kEBytes + sizeof(Shared) + 64;
   if (smem > (size_t)kSmemLimit) return set_error(MG_ERR_UNSUPPORTED, "tensor-core split-KV attention: shared memory plan too large");
-  unsigned const blocks = (unsigned)(a.num_items < sm_count() ? a.num_items : sm_count());
   bool const bf16 = p->data_type == MG_DT_BFLOAT16;
   using Kernel = void (*)(CUtensorMap, CUtensorMap, CUtensorMap, Params);
   static Kernel const kernels[8] = {
@@ -555,7 +606,8 @@ int launch(mgd_attn_split const *p, void const *q, void const *k, void const *v,
     if (st != MG_OK) return st;
     launch_merge_rows(bf16 ? kMergeBF16 : kMergeF16, kD, static_cast<uint16_t const *>(o), static_cast<uint16_t const *>(r),
                       static_cast<uint16_t *>(opts->merged_out), p->heads, p->m, p->splits, p->num_sets, p->o_set_stride,
-                      p->r_set_stride, opts->merged_set_stride, true, stream);
+                      p->r_set_stride, opts->merged_set_stride, true, stream,
+                      sum_runs ? MergeRuns{a.per, a.extra, (uint32_t)tiles_per_head} : MergeRuns{0, 0, 0});
     return check_launch("attn_merge_rows_kernel");
   }
   return check_launch("attn_split_tc_kernel");

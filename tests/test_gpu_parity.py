@@ -456,6 +456,25 @@ def test_float_spec_decode_c3_full_size(runtime):
                 runtime.set_option(mg.OPT_ATTN_ENGINE, mg.ENGINE_AUTO)
             final = from_bits(f[0].download_data(), mg.float16).reshape(f[0].shape)
             assert_close(final, want, mg.float16, "masked output, engine %d" % engine)
+        # The batched entry point on the same graph (two sets, the second one a permutation of the heads): its
+        # partials are scratch, so the tcgen05 kernel deals single tiles to its blocks and sums what a block holds
+        # of a head (13 or 14 tiles of 64; five or six partial sums per head), and the merge reads those slots only.
+        import torch
+        perm = rng.permutation(B)
+        sets = [mem, [a[perm] for a in mem]]
+        dev = [torch.from_numpy(np.stack([to_bits(sets[s][i], mg.float16) for s in range(2)]).astype(np.int16)).cuda() for i in range(3)]
+        res = torch.zeros((2,) + tuple(f[0].shape), dtype=torch.int16, device="cuda")
+        wbytes = g.run_batched_workspace(2)
+        work = torch.empty(max(wbytes, 256), dtype=torch.uint8, device="cuda")
+        torch.cuda.synchronize()
+        for _ in range(2):
+            res.zero_()
+            torch.cuda.synchronize()
+            g.run_batched(2, [d.data_ptr() for d in dev], res.data_ptr(), work.data_ptr(), wbytes)
+            mg.synchronize()
+            got = from_bits(res.cpu().numpy().view(np.uint16), mg.float16)
+            assert_close(got[0], want, mg.float16, "batched, set 0")
+            assert_close(got[1], want[perm], mg.float16, "batched, set 1")
 
 
 def build_prefill(g, H, SQ, D, L, dtype, kl=mg.DmemColumnMajor, vl=mg.DmemColumnMajor):
