@@ -34,7 +34,7 @@ FP_P, FP_Q, FP_PQ = 227, 113, 25651
 
 POLICY_LATENCY, POLICY_THROUGHPUT = 0, 1
 (OPT_ATTN_STAGES, OPT_ATTN_TILE_GROUPS, OPT_ATTN_ENGINE, OPT_ROWS_ENGINE, OPT_INTERP_THREADS, OPT_WAIT_LIMIT,
- OPT_ATTN_PERSISTENT, OPT_KN_MATMUL_ENGINE) = range(8)
+ OPT_ATTN_PERSISTENT, OPT_KN_MATMUL_ENGINE, OPT_ATTN_DEPENDENT_LAUNCH) = range(9)
 ENGINE_AUTO, ENGINE_MMA_SYNC, ENGINE_TCGEN05 = 0, 1, 2
 ROWS_AUTO, ROWS_ONE_TILE, ROWS_TWO_TILES = 0, 1, 2
 KERNEL_INTERPRETER, KERNEL_ATTN_SPLIT, KERNEL_ATTN_MERGE, KERNEL_ATTN_ROWS = 0, 1, 2, 3

@@ -198,7 +198,8 @@ int mg_runtime_set_launch_policy(mg_runtime *rt, int policy) {
 static_assert(MG_OPT_ATTN_STAGES == MGD_OPT_ATTN_STAGES && MG_OPT_ATTN_TILE_GROUPS == MGD_OPT_ATTN_TILE_GROUPS &&
                   MG_OPT_ATTN_ENGINE == MGD_OPT_ATTN_ENGINE && MG_OPT_ROWS_ENGINE == MGD_OPT_ROWS_ENGINE &&
                   MG_OPT_INTERP_THREADS == MGD_OPT_INTERP_THREADS && MG_OPT_WAIT_LIMIT == MGD_OPT_WAIT_LIMIT &&
-                  MG_OPT_ATTN_PERSISTENT == MGD_OPT_ATTN_PERSISTENT && MG_OPT_KN_MATMUL_ENGINE == MGD_OPT_KN_MATMUL_ENGINE,
+                  MG_OPT_ATTN_PERSISTENT == MGD_OPT_ATTN_PERSISTENT && MG_OPT_KN_MATMUL_ENGINE == MGD_OPT_KN_MATMUL_ENGINE &&
+                  MG_OPT_ATTN_DEPENDENT_LAUNCH == MGD_OPT_ATTN_DEPENDENT_LAUNCH,
               "the option keys of the two headers are the same numbers");
 
 int mg_runtime_set_option(mg_runtime *rt, int32_t key, int32_t value) {

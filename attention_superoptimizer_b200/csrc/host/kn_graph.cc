@@ -823,7 +823,9 @@ int KNCustomizedOp::launch_split(bool fp, int num_sets, void const *const *in, l
     opts.merged_set_stride = merge->set_stride;
     outs.push_back(range_of(merge->out, merge->bytes));
   }
-  opts.overlap = 1 | (inputs_untouched(stream, ins) ? 2 : 0) | (DeviceMemoryManager::get_instance()->launch_policy == 1 ? 4 : 0) |
+  int32_t serial = 0;
+  mgd_get_option(MGD_OPT_ATTN_DEPENDENT_LAUNCH, &serial); // 1 = plain stream order (no programmatic dependent launch)
+  opts.overlap = (serial == 1 ? 0 : 1) | (inputs_untouched(stream, ins) && serial != 1 ? 2 : 0) | (DeviceMemoryManager::get_instance()->launch_policy == 1 ? 4 : 0) |
                  (merge != nullptr && merge->partials_are_scratch ? 8 : 0);
   int st = fp ? mgd_launch_attn_split_fingerprint_ex(&sp, (uint16_t const *)in[0], (uint16_t const *)in[1],
                                                      (uint16_t const *)in[2], (uint16_t *)out[0], (uint16_t *)out[1],

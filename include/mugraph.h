@@ -136,7 +136,8 @@ enum {
                                    (failure-path tests), n > 1 = n polls */
   MG_OPT_ATTN_PERSISTENT = 6,   /* split-KV attention with more blocks than fit at once: 1 = one block per work item,
                                    2 = resident blocks that walk the work items (the default where it fits) */
-  MG_OPT_KN_MATMUL_ENGINE = 7   /* kernel-level float matmul: 1 = CUDA cores, 2 = tcgen05 (the default where it applies) */
+  MG_OPT_KN_MATMUL_ENGINE = 7,  /* kernel-level float matmul: 1 = CUDA cores, 2 = tcgen05 (the default where it applies) */
+  MG_OPT_ATTN_DEPENDENT_LAUNCH = 8 /* split-KV attention: 1 = plain stream order, 2 = programmatic dependent launch (default) */
 };
 int mg_runtime_set_option(mg_runtime *rt, int32_t key, int32_t value);
 int mg_runtime_get_option(mg_runtime *rt, int32_t key, int32_t *value);
