@@ -33,8 +33,10 @@ struct mg_graph {
   // so that no clearing copy sits between two launches of a stream and one launch can start under the other's tail.
   int *batch_tickets = nullptr;
   size_t batch_ticket_ints = 0;
+  std::vector<int *> outgrown_tickets; // kept until the graph goes: a captured launch may still point at them
   ~mg_graph() {
     if (batch_tickets) cudaFree(batch_tickets);
+    for (int *p : outgrown_tickets) cudaFree(p);
   }
 };
 
@@ -506,13 +508,14 @@ static int run_batched(mg_graph *g, bool fp, int32_t num_sets, const void *const
   if (!in_ptrs || !out_ptr) return fail(MG_ERR_INVALID_ARGUMENT, "null tensor pointers");
   if (ticket_ints > g->batch_ticket_ints) {
     // grown on the first call and when a call brings more sets (allocation synchronises the device: not for a stream
-    // that is being captured - make the first call of a size outside the capture)
-    if (g->batch_tickets) MG_CUDA_TRY(cudaFree(g->batch_tickets));
-    g->batch_tickets = nullptr;
-    g->batch_ticket_ints = 0;
-    MG_CUDA_TRY(cudaMalloc(&g->batch_tickets, ticket_ints * sizeof(int)));
-    MG_CUDA_TRY(cudaMemset(g->batch_tickets, 0, ticket_ints * sizeof(int)));
-    g->batch_ticket_ints = ticket_ints;
+    // that is being captured - make the first call of a size outside the capture); the outgrown array stays alive
+    size_t const want = ticket_ints > 2 * g->batch_ticket_ints ? ticket_ints : 2 * g->batch_ticket_ints;
+    int *fresh = nullptr;
+    MG_CUDA_TRY(cudaMalloc(&fresh, want * sizeof(int)));
+    MG_CUDA_TRY(cudaMemset(fresh, 0, want * sizeof(int)));
+    if (g->batch_tickets) g->outgrown_tickets.push_back(g->batch_tickets);
+    g->batch_tickets = fresh;
+    g->batch_ticket_ints = want;
   }
   auto locate = [&](DTensor const &t, void const **ptr, long long *stride) -> bool {
     for (size_t i = 0; i < inputs.size(); i++)

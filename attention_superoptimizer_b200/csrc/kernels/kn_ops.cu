@@ -167,6 +167,21 @@ __global__ void kn_reduction_fp_kernel(uint16_t const *x, uint16_t *y, int64_t n
   }
 }
 
+// The same with a warp per output (lanes stride over the terms): for few outputs of many terms each, e.g. row sums
+// of a wide matrix, where a thread per output leaves most of the GPU idle.  A sum of 65535 terms fits 32 bits.
+__global__ void kn_reduction_fp_warp_kernel(uint16_t const *x, uint16_t *y, int64_t n_out, int factor, int64_t is, int64_t os) {
+  int const lane = threadIdx.x & 31;
+  int64_t const warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  for (int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; i < n_out; i += warps) {
+    int64_t const base = (i / os) * is + i % os;
+    uint32_t acc = 0;
+    for (int k = lane; k < factor; k += 32) acc += x[base + (int64_t)k * os];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (lane == 0) y[i] = (uint16_t)(acc % PQ);
+  }
+}
+
 // ---- float mode ------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void kn_matmul_float_kernel(T const *A, T const *B, T *C, int batches, int m, int n, int k, int a_col_major,
@@ -211,6 +226,23 @@ __global__ void kn_reduction_float_kernel(T const *x, T *y, int64_t n_out, int f
   }
 }
 
+template <typename T>
+__global__ void kn_reduction_float_warp_kernel(T const *x, T *y, int64_t n_out, int factor, int64_t is, int64_t os) {
+  int const lane = threadIdx.x & 31;
+  int64_t const warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  for (int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; i < n_out; i += warps) {
+    int64_t const base = (i / os) * is + i % os;
+    float acc = 0.f;
+    for (int k = lane; k < factor; k += 32) acc += to_float<T>(x[base + (int64_t)k * os]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (lane == 0) y[i] = from_float<T>(acc);
+  }
+}
+
+// a warp per output pays when there are too few outputs to fill the GPU with a thread each
+static bool reduce_by_warps(int64_t n_out, int factor) { return factor >= 32 && factor < 65536 && n_out < 148 * 256; }
+
 static bool dims_ok(int32_t const *d) { return d && d[0] > 0 && d[1] > 0 && d[2] > 0 && d[3] > 0; }
 static Dims4 pack(int32_t const *d) { return Dims4{{d[0], d[1], d[2], d[3]}}; }
 } // namespace mgk
@@ -251,6 +283,10 @@ int mgd_kn_binary_fingerprint(int32_t op, const uint16_t *x, const int32_t *xd, 
 int mgd_kn_reduction_fingerprint(const uint16_t *x, uint16_t *y, int64_t n_out, int32_t factor, int64_t is, int64_t os,
                                  void *stream) {
   if (!x || !y || n_out <= 0 || factor <= 0) return set_error(MG_ERR_INVALID_ARGUMENT, "kn reduction: bad argument");
+  if (reduce_by_warps(n_out, factor)) {
+    kn_reduction_fp_warp_kernel<<<blocks_for(n_out * 32), 256, 0, ST(stream)>>>(x, y, n_out, factor, is, os);
+    return check_launch("kn_reduction_fp_warp_kernel");
+  }
   kn_reduction_fp_kernel<<<blocks_for(n_out), 256, 0, ST(stream)>>>(x, y, n_out, factor, is, os);
   return check_launch("kn_reduction_fp_kernel");
 }
@@ -291,6 +327,12 @@ int mgd_kn_binary_float(int32_t op, const void *x, const int32_t *xd, const void
 int mgd_kn_reduction_float(const void *x, void *y, int64_t n_out, int32_t factor, int64_t is, int64_t os, int32_t dt,
                            void *stream) {
   if (!x || !y || n_out <= 0 || factor <= 0) return set_error(MG_ERR_INVALID_ARGUMENT, "kn reduction: bad argument");
+  if (reduce_by_warps(n_out, factor)) {
+    int const gw = blocks_for(n_out * 32);
+    DISPATCH_16(dt, (kn_reduction_float_warp_kernel<__half><<<gw, 256, 0, ST(stream)>>>((__half const *)x, (__half *)y, n_out, factor, is, os)),
+                (kn_reduction_float_warp_kernel<__nv_bfloat16><<<gw, 256, 0, ST(stream)>>>((__nv_bfloat16 const *)x, (__nv_bfloat16 *)y, n_out, factor, is, os)))
+    return check_launch("kn_reduction_float_warp_kernel");
+  }
   int g = blocks_for(n_out);
   DISPATCH_16(dt, (kn_reduction_float_kernel<__half><<<g, 256, 0, ST(stream)>>>((__half const *)x, (__half *)y, n_out, factor, is, os)),
               (kn_reduction_float_kernel<__nv_bfloat16><<<g, 256, 0, ST(stream)>>>((__nv_bfloat16 const *)x, (__nv_bfloat16 *)y, n_out, factor, is, os)))
