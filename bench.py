@@ -437,9 +437,8 @@ def fnv1a64_rows(np, rows):
 
 def run_fingerprint_sweep(args, mg, mo, rt, torch, dist, np, rank, world, stream, timed, barrier):
     """The verification sweep: the decode muGraph in fingerprint mode over independent seeded input sets (uniform in
-    [0, 227)), sets sharded over ranks.  Timed region: evaluation of this rank's sets in chunks, all-gather of each
-    chunk's fingerprints on a second stream while the next chunk evaluates, row-wise comparison of all gathered
-    fingerprints with reference fingerprints on the device.  The reference fingerprints are those of an untimed
+    [0, 227)), sets sharded over ranks.  Timed region: evaluation of this rank's sets in chunks, one all-gather of the
+    fingerprints, row-wise comparison of all gathered fingerprints with reference fingerprints on the device.  The reference fingerprints are those of an untimed
     first pass, every row of which is checked on the host against the digests produced by the reference's own host
     code (tests/golden/sweep_digests_gqa_decode.json)."""
     sh = stream.cuda_stream
@@ -462,15 +461,14 @@ def run_fingerprint_sweep(args, mg, mo, rt, torch, dist, np, rank, world, stream
         resident = my_sets * 2 * sum(elems) < 0.7 * free_bytes
         held = my_sets if resident else chunk
         bufs = [torch.empty(held * n, dtype=torch.int16, device="cuda") for n in elems]
-        # fingerprints are kept chunk-major: [chunk index][rank][set in chunk][row], so that the all-gather of one
-        # chunk is one contiguous block; set (r, c, s) is global set r * my_sets + c * chunk + s
+        # this rank's fingerprints [chunk index][set in chunk][row]; gathered [rank][chunk index][set in chunk][row], i.e.
+        # in global set order: set (r, c, s) is global set r * my_sets + c * chunk + s
         local = torch.zeros((nchunks, chunk, row), dtype=torch.int16, device="cuda")
-        gathered = torch.zeros((nchunks, world, chunk, row), dtype=torch.int16, device="cuda") if world > 1 else local.view(nchunks, 1, chunk, row)
+        gathered = torch.zeros((world, nchunks, chunk, row), dtype=torch.int16, device="cuda") if world > 1 else local.view(1, nchunks, chunk, row)
         wbytes = g.fingerprint_batched_workspace(chunk)
         work = torch.empty(max(wbytes, 256), dtype=torch.uint8, device="cuda")
         flags = torch.zeros(nchunks * world * chunk, dtype=torch.int32, device="cuda")
         mismatches = torch.zeros(1, dtype=torch.int32, device="cuda")
-        side = torch.cuda.Stream()
 
         def fill_chunk(c):
             slot0 = c * chunk if resident else 0
@@ -484,43 +482,33 @@ def run_fingerprint_sweep(args, mg, mo, rt, torch, dist, np, rank, world, stream
             g.fingerprint_batched(chunk, [b.data_ptr() + 2 * slot0 * n for b, n in zip(bufs, elems)],
                                   local[c].data_ptr(), work.data_ptr(), wbytes, stream=sh)
 
-        def gather_chunk(c):
-            """all-gather of chunk c on the side stream, after the evaluation that produced it"""
-            if world == 1:
-                return
-            ev = torch.cuda.Event()
-            ev.record(stream)
-            side.wait_event(ev)
-            with torch.cuda.stream(side):
-                dist.all_gather_into_tensor(gathered[c].view(torch.uint8).view(-1), local[c].view(torch.uint8).view(-1))
-
-        def join_side():
+        def gather_all():
+            """One all-gather of this rank's fingerprints behind the last evaluation.  (A gather per chunk on a second
+            stream, under the next chunk's evaluation, was slower: the evaluation kernel fills every SM with resident
+            blocks, so each small collective waited for a gap between two launches and lengthened the chain.)"""
             if world > 1:
-                ev = torch.cuda.Event()
-                ev.record(side)
-                stream.wait_event(ev)
+                with torch.cuda.stream(stream):
+                    dist.all_gather_into_tensor(gathered.view(torch.uint8).view(-1), local.view(torch.uint8).view(-1))
 
         # ---- untimed first pass: produces the reference fingerprints, checked on the host against the digests
         for c in range(nchunks):
             fill_chunk(c)
             eval_chunk(c)
-            gather_chunk(c)
             if not resident:
                 torch.cuda.synchronize()   # the next fill reuses the chunk's input buffers
-        join_side()
+        gather_all()
         barrier()
         reference = gathered.clone()
         checked, ok = 0, True
         if rank == 0 and os.path.exists(SWEEP_DIGESTS) and total_sets <= SWEEP_SETS:
             with open(SWEEP_DIGESTS) as f:
                 want = np.array([int(x) for x in json.load(f)["digests"]], dtype=np.uint64)
-            host = reference.cpu().numpy().view(np.uint16)                       # [nchunks, world, chunk, row]
-            got = fnv1a64_rows(np, host.reshape(-1, row)).reshape(nchunks, world, chunk)
-            for c in range(nchunks):
-                for r in range(world):
-                    first = r * my_sets + c * chunk
-                    ok = ok and bool(np.array_equal(got[c, r], want[first:first + chunk]))
-                    checked += chunk
+            host = reference.cpu().numpy().view(np.uint16)                       # [world, nchunks, chunk, row]
+            got = fnv1a64_rows(np, host.reshape(-1, row)).reshape(world, nchunks * chunk)
+            for r in range(world):
+                first = r * my_sets
+                ok = ok and bool(np.array_equal(got[r], want[first:first + nchunks * chunk]))
+                checked += nchunks * chunk
         # ---- timed pass
         gathered.zero_() if world > 1 else local.zero_()
         barrier()
@@ -528,8 +516,7 @@ def run_fingerprint_sweep(args, mg, mo, rt, torch, dist, np, rank, world, stream
         def sweep():
             for c in range(nchunks):
                 eval_chunk(c)
-                gather_chunk(c)
-            join_side()
+            gather_all()
             mg.compare_fingerprint_rows(rt, gathered.data_ptr(), reference.data_ptr(), nchunks * world * chunk, row,
                                         flags.data_ptr(), mismatches.data_ptr(), stream=sh)
 
@@ -544,8 +531,7 @@ def run_fingerprint_sweep(args, mg, mo, rt, torch, dist, np, rank, world, stream
                 t = timed(lambda: eval_chunk(c), 1, 0)
                 t_eval += t
                 t_total += t
-                gather_chunk(c)
-            join_side()
+            t_total += timed(gather_all, 1, 0)
             t_total += timed(lambda: mg.compare_fingerprint_rows(rt, gathered.data_ptr(), reference.data_ptr(), nchunks * world * chunk,
                                                                  row, flags.data_ptr(), mismatches.data_ptr(), stream=sh), 1, 0)
         mg.synchronize()
@@ -556,7 +542,7 @@ def run_fingerprint_sweep(args, mg, mo, rt, torch, dist, np, rank, world, stream
             "sets": nchunks * chunk * world, "sets_per_gpu": nchunks * chunk, "chunk_sets": chunk,
             "inputs_resident": bool(resident),
             "sweep_ms": round(t_total, 3), "eval_only_ms": round(t_eval, 3),
-            "timed_region": "evaluation of all chunks + all-gather of each chunk on a second stream + row-wise device "
+            "timed_region": "evaluation of all chunks + one all-gather of the fingerprints + row-wise device "
                             "comparison of all gathered fingerprints with the reference fingerprints",
             "rows_equal_to_reference": rows_equal, "rows_compared": nchunks * chunk * world,
             "mismatches": int(mismatches.item()),
