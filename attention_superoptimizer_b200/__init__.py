@@ -37,7 +37,7 @@ POLICY_LATENCY, POLICY_THROUGHPUT = 0, 1
  OPT_ATTN_PERSISTENT, OPT_KN_MATMUL_ENGINE, OPT_ATTN_DEPENDENT_LAUNCH) = range(9)
 ENGINE_AUTO, ENGINE_MMA_SYNC, ENGINE_TCGEN05 = 0, 1, 2
 ROWS_AUTO, ROWS_ONE_TILE, ROWS_TWO_TILES = 0, 1, 2
-KERNEL_INTERPRETER, KERNEL_ATTN_SPLIT, KERNEL_ATTN_MERGE, KERNEL_ATTN_ROWS = 0, 1, 2, 3
+KERNEL_INTERPRETER, KERNEL_ATTN_SPLIT, KERNEL_ATTN_MERGE, KERNEL_ATTN_ROWS, KERNEL_MATMUL_CHAIN, KERNEL_TILE_REDUCE = range(6)
 
 
 class InputNotFoundError(Exception):

@@ -255,4 +255,49 @@ bool match_attn_merge(mgd_program const &p, mgd_attn_merge *out, int *o_part_inp
   if (o_part_input) *o_part_input = o_in;
   return true;
 }
+bool match_matmul_chain(mgd_program const &p, mgd_matmul_chain *out) {
+  // ops: three inputs, matmul(in_a, in_b) -> t, matmul(t, in_c) -> u, output(u)
+  if (p.num_ops != 6 || p.num_inputs != 3 || p.num_outputs != 1) return false;
+  InputView in[3] = {InputView{p.ops[0]}, InputView{p.ops[1]}, InputView{p.ops[2]}};
+  MatmulView first{p.ops[3]}, second{p.ops[4]};
+  OutputView so{p.ops[5]};
+  if (!in[0].valid() || !in[1].valid() || !in[2].valid() || !first.valid() || !second.valid() || !so.valid()) return false;
+  auto input_at = [&](int offset) {
+    for (int i = 0; i < 3; i++)
+      if (in[i].tile_offset() == offset) return i;
+    return -1;
+  };
+  int const ix = input_at(first.a_offset()), iw1 = input_at(first.b_offset()), iw2 = input_at(second.b_offset());
+  if (ix < 0 || iw1 < 0 || iw2 < 0 || ix == iw1 || ix == iw2 || iw1 == iw2) return false;
+  if (second.a_offset() != first.c_offset() || so.source_offset() != second.c_offset()) return false;
+  int const m = first.m(), n1 = first.n(), kt = first.k(), n2 = second.n();
+  if (second.m() != m || second.k() != n1) return false;
+  if (in[ix].tile_rows() != m || in[ix].tile_cols() != kt || in[iw1].tile_rows() != kt || in[iw1].tile_cols() != n1 ||
+      in[iw2].tile_rows() != n1 || in[iw2].tile_cols() != n2)
+    return false;
+  mgd_op const &w2 = p.ops[iw2];
+  if (w2.a[MGD_IN_ROW_LOOP_STRIDE] != 0 || w2.a[MGD_IN_COL_LOOP_STRIDE] != 0 || w2.a[MGD_IN_LEAD_LOOP_STRIDE] != 0) return false;
+  if (p.ops[5].a[MGD_OUT_TILE_ROWS] != m || p.ops[5].a[MGD_OUT_TILE_COLS] != n2) return false;
+  std::memset(out, 0, sizeof(*out));
+  for (int i = 0; i < 3; i++) out->grid[i] = p.grid[i];
+  out->forloop_range = p.forloop_range;
+  out->m = m; out->kt = kt; out->n1 = n1; out->n2 = n2;
+  out->x = p.ops[ix]; out->w1 = p.ops[iw1]; out->w2 = w2; out->out = p.ops[5];
+  return true;
+}
+bool match_tile_reduce(mgd_program const &p, mgd_tile_reduce *out) {
+  if (p.num_ops != 3 || p.num_inputs != 1 || p.num_outputs != 1 || p.forloop_range != 1) return false;
+  InputView in{p.ops[0]};
+  ReductionView red{p.ops[1]};
+  OutputView so{p.ops[2]};
+  if (!in.valid() || !(red.plain() || red.to_dimx()) || !so.valid()) return false;
+  if (red.in_offset() != in.tile_offset() || so.source_offset() != red.out_offset()) return false;
+  if (red.out_elements() != so.tile_rows() * so.tile_cols()) return false;
+  if ((long long)red.out_elements() * red.degree() != (long long)in.tile_rows() * in.tile_cols()) return false;
+  std::memset(out, 0, sizeof(*out));
+  for (int i = 0; i < 3; i++) out->grid[i] = p.grid[i];
+  out->out_elements = red.out_elements(); out->degree = red.degree(); out->inner = red.inner();
+  out->in = p.ops[0]; out->out = p.ops[2];
+  return true;
+}
 } // namespace mg

@@ -696,6 +696,14 @@ bool KNCustomizedOp::ensure_lowered() {
     } else if (mgd_attn_rows rp; mg::match_attn_rows(program_, &rp, &o_output_)) {
       rp.data_type = (int)input_tensors[0].data_type;
       if (causal_window == 0 && mgd_attn_rows_supported(&rp)) kernel_float_ = mg::KERNEL_ATTN_ROWS;
+    } else if (mgd_matmul_chain mc; mg::match_matmul_chain(program_, &mc)) {
+      mc.data_type = (int)input_tensors[0].data_type;
+      if (mgd_matmul_chain_supported(&mc, 1)) kernel_fp_ = mg::KERNEL_MATMUL_CHAIN;
+      if (mgd_matmul_chain_supported(&mc, 0)) kernel_float_ = mg::KERNEL_MATMUL_CHAIN;
+    } else if (mgd_tile_reduce tr; mg::match_tile_reduce(program_, &tr)) {
+      tr.data_type = (int)input_tensors[0].data_type;
+      if (mgd_tile_reduce_supported(&tr, 1)) kernel_fp_ = mg::KERNEL_TILE_REDUCE;
+      if (mgd_tile_reduce_supported(&tr, 0)) kernel_float_ = mg::KERNEL_TILE_REDUCE;
     } else if (mg::match_attn_merge(program_, &mp, &o_input_)) {
       mp.data_type = (int)input_tensors[0].data_type;
       if (mgd_attn_merge_supported(&mp, 1)) kernel_fp_ = mg::KERNEL_ATTN_MERGE;
@@ -773,6 +781,18 @@ int KNCustomizedOp::launch_sets(bool fp, int num_sets, void const *const *in, lo
   for (int i = 0; i < program_.num_inputs; i++) { b.in[i] = in[i]; b.in_set_stride[i] = in_stride[i]; }
   for (int i = 0; i < program_.num_outputs; i++) { b.out[i] = out[i]; b.out_set_stride[i] = out_stride[i]; }
   b.num_sets = num_sets;
+  if (kernel == mg::KERNEL_TILE_REDUCE) {
+    mgd_tile_reduce tr;
+    mg::match_tile_reduce(program_, &tr);
+    tr.data_type = dt;
+    return finish(mgd_launch_tile_reduce(&tr, &b, fp ? 1 : 0, stream));
+  }
+  if (kernel == mg::KERNEL_MATMUL_CHAIN) {
+    mgd_matmul_chain mc;
+    mg::match_matmul_chain(program_, &mc);
+    mc.data_type = dt;
+    return finish(fp ? mgd_launch_matmul_chain_fingerprint(&mc, &b, stream) : mgd_launch_matmul_chain_float(&mc, &b, stream));
+  }
   return finish(fp ? mgd_launch_fingerprint_interp(&program_, &b, stream) : mgd_launch_float_interp(&program_, &b, dt, stream));
 }
 

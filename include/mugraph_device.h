@@ -207,6 +207,36 @@ int mgd_launch_attn_merge_float(const mgd_attn_merge *p, const void *o_part, con
 int mgd_launch_attn_merge_fingerprint(const mgd_attn_merge *p, const uint16_t *o_part, const uint16_t *r_part,
                                       uint16_t *out, void *stream);
 
+/* ---- two chained threadblock matmuls with for-loop accumulation ---------------------------------
+ * out = sum over the for-loop of (X_i W1_i) W2 with a loop-invariant W2: the customized operator made of two
+ * tb_matmul_op and an accumulating tb_output_op (the pattern of cpp_examples/mlp.cc).  x / w1 / w2 / out are the
+ * program's records of the three inputs and of the output (coordinates per block and iteration as in mgd_op). */
+typedef struct mgd_matmul_chain {
+  int32_t grid[3];
+  int32_t forloop_range;
+  int32_t m, kt, n1, n2; /* X_i [m x kt], W1_i [kt x n1], W2 [n1 x n2], out [m x n2] */
+  int32_t data_type;
+  int32_t reserved;
+  mgd_op x, w1, w2, out;
+} mgd_matmul_chain;
+int mgd_matmul_chain_supported(const mgd_matmul_chain *c, int32_t fingerprint_mode);
+int mgd_launch_matmul_chain_float(const mgd_matmul_chain *c, const mgd_bindings *bind, void *stream);
+int mgd_launch_matmul_chain_fingerprint(const mgd_matmul_chain *c, const mgd_bindings *bind, void *stream);
+
+/* ---- a customized operator that is one threadblock reduction ----------------------------------------
+ * input tile -> tb_reduction_*_op (plain or "to dimx") -> output tile, for-loop of one: the cross-block reduction
+ * behind a split operator.  in / out are the program's records of the input and the output; out element i of a tile
+ * = sum over k < degree of in_tile[(i / inner) * inner * degree + i % inner + k * inner] (dense row-major tile). */
+typedef struct mgd_tile_reduce {
+  int32_t grid[3];
+  int32_t out_elements, degree, inner;
+  int32_t data_type;
+  int32_t chunks; /* set by the launch */
+  mgd_op in, out;
+} mgd_tile_reduce;
+int mgd_tile_reduce_supported(const mgd_tile_reduce *c, int32_t fingerprint_mode);
+int mgd_launch_tile_reduce(const mgd_tile_reduce *c, const mgd_bindings *bind, int32_t fingerprint_mode, void *stream);
+
 /* ---- un-fused kernel-level operators, fingerprint mode ----------------------
  * replace compute_matmul_fingerprint (src/kernel/cuda/matmul_kernel.cu:145-173),
  * compute_elementunary_fingerprint (element_unary_kernel.cu:77-94),
