@@ -13,7 +13,6 @@
 // of fp_interp.cu on mma.sync m16n8k32 u8.  m <= 16 rows (an MMA's height); rows beyond m are zero and never stored.
 #include "common.cuh"
 #include <cstring>
-#include <cstdio>
 
 namespace mgk {
 namespace chain {
@@ -115,9 +114,9 @@ __host__ __device__ inline Plan make_plan(int kt, int n1, int n2, int stages) {
   return q;
 }
 
-// ---- float mode -----------------------------------------------------------------------------------------------
+// MODE: 0 fp16, 1 bf16, 2 fingerprints
 template <int MODE>
-__global__ void __launch_bounds__(kThreads) chain_float_kernel(const __grid_constant__ Params p) {
+__global__ void __launch_bounds__(kThreads) chain_kernel(const __grid_constant__ Params p) {
   extern __shared__ __align__(16) uint16_t smem[];
   mgd_matmul_chain const &c = p.c;
   int const tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
@@ -183,9 +182,14 @@ __global__ void __launch_bounds__(kThreads) chain_float_kernel(const __grid_cons
     cp_commit();
   }
 
-#ifdef MG_CH_TIMING
-  long long t0 = clock64(), t_wait = 0;
-#endif
+  uint16_t const *w2s = smem + q.w2_at;
+  int32_t const *oa = c.out.a;
+  long long const orow = (long long)bx * oa[0] + (long long)by * oa[1] + (long long)bz * oa[2];
+  long long const ocol = (long long)bx * oa[3] + (long long)by * oa[4] + (long long)bz * oa[5];
+  long long const olead = (long long)bx * oa[6] + (long long)by * oa[7] + (long long)bz * oa[8];
+  int const old = oa[MGD_OUT_COLS];
+  uint16_t *O = static_cast<uint16_t *>(p.out) + set * p.out_set + olead + orow * old + ocol;
+  if constexpr (MODE != 2) {
   // ---- phase 1: running sum of X_i W1_i.  The contraction is split over the warps: warp w takes the k-steps
   // w % 4, w % 4 + 4, ... of every tile and the 8-column slices w / 4, w / 4 + 2, ...: the MMAs of an iteration go
   // to different accumulators (a dependent MMA chain runs at about 100 cycles per step, the pipe takes one every 8),
@@ -198,14 +202,8 @@ __global__ void __launch_bounds__(kThreads) chain_float_kernel(const __grid_cons
     for (int j = 0; j < 4; j++) acc[i][j] = 0.f;
   int const slices = n1 >> 3, kq = warp & 3, sh = warp >> 2;
   for (int it = 0; it < loop; it++) {
-#ifdef MG_CH_TIMING
-    long long tw = clock64();
-#endif
     cp_wait_pending(S - 2); // stage `it` has landed (for this thread's copies; the barrier makes it everybody's)
     __syncthreads();        // also: every warp is done with stage it - 1, which the refill below overwrites
-#ifdef MG_CH_TIMING
-    t_wait += clock64() - tw;
-#endif
     if (it + S - 1 < loop) request_stage(it + S - 1);
     cp_commit();
     uint16_t const *xs = smem + (size_t)(it % S) * q.stage_elems, *ws = xs + 16 * q.x_pitch;
@@ -252,14 +250,8 @@ __global__ void __launch_bounds__(kThreads) chain_float_kernel(const __grid_cons
     *reinterpret_cast<uint32_t *>(a2_hi + r * q.a2_pitch + cc) = h;
     *reinterpret_cast<uint32_t *>(a2_lo + r * q.a2_pitch + cc) = Mma<MODE>::pack(v.x - f.x, v.y - f.y);
   }
-#ifdef MG_CH_TIMING
-  long long t1 = clock64();
-#endif
   cp_wait<0>();
   __syncthreads();
-#ifdef MG_CH_TIMING
-  long long t2 = clock64();
-#endif
 
   // ---- phase 2: out = running sum x W2; a warp takes 16 columns at a time --------------------------------------
   constexpr int kMaxK2 = 8; // n1 <= 128
@@ -271,13 +263,6 @@ __global__ void __launch_bounds__(kThreads) chain_float_kernel(const __grid_cons
       ldmatrix_x4(ah[ks], a2_hi + (lane & 15) * q.a2_pitch + ks * 16 + ((lane >> 4) << 3));
       if (MODE == 1) ldmatrix_x4(al[ks], a2_lo + (lane & 15) * q.a2_pitch + ks * 16 + ((lane >> 4) << 3));
     }
-  uint16_t const *w2s = smem + q.w2_at;
-  int32_t const *oa = c.out.a;
-  long long const orow = (long long)bx * oa[0] + (long long)by * oa[1] + (long long)bz * oa[2];
-  long long const ocol = (long long)bx * oa[3] + (long long)by * oa[4] + (long long)bz * oa[5];
-  long long const olead = (long long)bx * oa[6] + (long long)by * oa[7] + (long long)bz * oa[8];
-  int const old = oa[MGD_OUT_COLS];
-  uint16_t *O = static_cast<uint16_t *>(p.out) + set * p.out_set + olead + orow * old + ocol;
   // four 16-column blocks at a time: eight independent accumulate chains per warp
   constexpr int kCB = 4;
   for (int cb0 = warp * kCB; cb0 < (n2 >> 4); cb0 += kWarps * kCB) {
@@ -318,10 +303,121 @@ __global__ void __launch_bounds__(kThreads) chain_float_kernel(const __grid_cons
         }
       }
   }
-#ifdef MG_CH_TIMING
-  if (blockIdx.x == 0 && tid == 0)
-    printf("chain: stages %d | loop %lld cycles (waits %lld) | W2 wait %lld | phase 2 %lld\n", S, t1 - t0, t_wait, t2 - t1, clock64() - t2);
-#endif
+  } else {
+
+  // ---- fingerprint mode: the byte-plane scheme of fp_interp.cu.  A uint16 is lo + 256 hi; the 16 rows of an
+  // m16n8k32 u8 MMA carry three byte-masked copies of 4 rows of A - [lo,0], [0,hi], [hi,lo] - which give LL, HH and
+  // LH+HL in int32, and A B = LL + 256 (LH+HL) + 65536 HH modulo PQ.  Warp w takes row group w % 4 (4 rows) and the
+  // 16-column pairs w / 4, w / 4 + 2, ...; the plane sums stay in registers over the whole for-loop (exact while the
+  // contraction has at most 16384 terms) and are reduced once.
+  int const mi = lane >> 3, rr = lane & 7, rg = warp & 3, ch = warp >> 2;
+  int const row = rg * 4 + (g & 3);
+  auto planes = [&](uint32_t w0, uint32_t w1, uint32_t (&a)[4]) {
+    if (g < 4) { // MMA rows 0-3: [lo,0] bytes; MMA rows 8-11: [hi,lo] bytes
+      a[0] = w0 & 0x00FF00FFu; a[2] = w1 & 0x00FF00FFu;
+      a[1] = __byte_perm(w0, 0, 0x2301); a[3] = __byte_perm(w1, 0, 0x2301);
+    } else {     // MMA rows 4-7: [0,hi] bytes; MMA rows 12-15 unused
+      a[0] = w0 & 0xFF00FF00u; a[2] = w1 & 0xFF00FF00u;
+      a[1] = 0u; a[3] = 0u;
+    }
+  };
+  auto imma = [&](int32_t (&d)[4], uint32_t const (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  };
+  // the two values this lane owns of a 4 x 8 result (rows g % 4, columns 2t, 2t + 1), reduced modulo PQ
+  auto reduce_planes = [&](int32_t const (&d)[4]) {
+    int32_t const hh0 = __shfl_down_sync(0xffffffffu, d[0], 16), hh1 = __shfl_down_sync(0xffffffffu, d[1], 16);
+    uint32_t const v0 = ((uint32_t)d[0] % PQ + 256u * ((uint32_t)d[2] % PQ) + (65536u % PQ) * ((uint32_t)hh0 % PQ)) % PQ;
+    uint32_t const v1 = ((uint32_t)d[1] % PQ + 256u * ((uint32_t)d[3] % PQ) + (65536u % PQ) * ((uint32_t)hh1 % PQ)) % PQ;
+    return v0 | (v1 << 16);
+  };
+  constexpr int kMaxUnits = 4; // n1 <= 128: 8 column pairs, two interleaved halves
+  int32_t acc[kMaxUnits][2][4];
+#pragma unroll
+  for (int u = 0; u < kMaxUnits; u++)
+#pragma unroll
+    for (int h = 0; h < 2; h++)
+#pragma unroll
+      for (int j = 0; j < 4; j++) acc[u][h][j] = 0;
+  int const cpairs = n1 >> 4;
+  for (int it = 0; it < loop; it++) {
+    cp_wait_pending(S - 2);
+    __syncthreads();
+    if (it + S - 1 < loop) request_stage(it + S - 1);
+    cp_commit();
+    uint16_t const *xs = smem + (size_t)(it % S) * q.stage_elems, *ws = xs + 16 * q.x_pitch;
+    uint16_t const *arow = xs + row * q.x_pitch + 2 * t;
+    for (int ks = 0; ks < kt; ks += 16) {
+      uint32_t a[4];
+      planes(*reinterpret_cast<uint32_t const *>(arow + ks), *reinterpret_cast<uint32_t const *>(arow + ks + 8), a);
+#pragma unroll
+      for (int u = 0; u < kMaxUnits; u++) {
+        int const cp = ch + 2 * u;
+        if (cp < cpairs) {
+          uint32_t bf[4]; // ldmatrix (transposed): this lane addresses k-row (mi % 2) * 8 + rr of the columns (mi / 2) * 8 ..
+          ldmatrix_x4_trans(bf, ws + (ks + (mi & 1) * 8 + rr) * q.w1_pitch + cp * 16 + (mi >> 1) * 8);
+          imma(acc[u][0], a, bf[0], bf[1]);
+          imma(acc[u][1], a, bf[2], bf[3]);
+        }
+      }
+    }
+  }
+  uint16_t *a2 = smem + q.a2_at;
+#pragma unroll
+  for (int u = 0; u < kMaxUnits; u++) {
+    int const cp = ch + 2 * u;
+    if (cp < cpairs) {
+#pragma unroll
+      for (int h = 0; h < 2; h++) {
+        uint32_t const v = reduce_planes(acc[u][h]); // (every lane takes part in the shuffles)
+        if (g < 4) *reinterpret_cast<uint32_t *>(a2 + row * q.a2_pitch + cp * 16 + h * 8 + 2 * t) = v;
+      }
+    }
+  }
+  cp_wait<0>();
+  __syncthreads();
+  // second product: the A fragments of every k-step once, then four column pairs at a time
+  constexpr int kMaxK2 = 8;
+  uint32_t a2f[kMaxK2][4];
+  int const k2 = n1 >> 4, cpairs2 = n2 >> 4;
+  {
+    uint16_t const *arow2 = a2 + row * q.a2_pitch + 2 * t;
+#pragma unroll
+    for (int ks = 0; ks < kMaxK2; ks++)
+      if (ks < k2) planes(*reinterpret_cast<uint32_t const *>(arow2 + ks * 16), *reinterpret_cast<uint32_t const *>(arow2 + ks * 16 + 8), a2f[ks]);
+  }
+  for (int cb0 = ch * kMaxUnits; cb0 < cpairs2; cb0 += 2 * kMaxUnits) {
+    int32_t d[kMaxUnits][2][4];
+#pragma unroll
+    for (int u = 0; u < kMaxUnits; u++)
+#pragma unroll
+      for (int h = 0; h < 2; h++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) d[u][h][j] = 0;
+#pragma unroll
+    for (int ks = 0; ks < kMaxK2; ks++)
+      if (ks < k2) {
+#pragma unroll
+        for (int u = 0; u < kMaxUnits; u++)
+          if (cb0 + u < cpairs2) {
+            uint32_t bf[4];
+            ldmatrix_x4_trans(bf, w2s + (ks * 16 + (mi & 1) * 8 + rr) * q.w2_pitch + (cb0 + u) * 16 + (mi >> 1) * 8);
+            imma(d[u][0], a2f[ks], bf[0], bf[1]);
+            imma(d[u][1], a2f[ks], bf[2], bf[3]);
+          }
+      }
+#pragma unroll
+    for (int u = 0; u < kMaxUnits; u++)
+      if (cb0 + u < cpairs2) {
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+          uint32_t const v = reduce_planes(d[u][h]);
+          if (g < 4 && row < m) *reinterpret_cast<uint32_t *>(O + (long long)row * old + (cb0 + u) * 16 + h * 8 + 2 * t) = v;
+        }
+      }
+  }
+  }
 }
 
 } // namespace chain
@@ -355,13 +451,19 @@ int pick_stages(mgd_matmul_chain const *c) {
 extern "C" {
 
 int mgd_matmul_chain_supported(const mgd_matmul_chain *c, int32_t fingerprint_mode) {
-  if (!c || fingerprint_mode) return 0;
+  if (!c) return 0;
   if (c->m <= 0 || c->m > 16 || c->kt <= 0 || (c->kt & 15) || c->kt > 128 || c->n1 <= 0 || (c->n1 & 15) || c->n1 > 128 || c->n2 <= 0 || (c->n2 & 15)) return 0;
   if (c->forloop_range <= 0 || c->grid[0] <= 0 || c->grid[1] <= 0 || c->grid[2] <= 0) return 0;
-  if (c->data_type != MG_DT_FLOAT16 && c->data_type != MG_DT_BFLOAT16) return 0;
   if (!input_ok(c->x) || !input_ok(c->w1) || !input_ok(c->w2)) return 0;
-  for (mgd_op const *op : {&c->x, &c->w1, &c->w2})
-    if ((op->a[MGD_IN_LAYOUT] & 0xff) != MG_DMEM_ROW_MAJOR) return 0;
+  if (fingerprint_mode) {
+    // fingerprint buffers are row-major whatever the layout tag says; the int32 plane sums of the first product run
+    // over the whole contraction
+    if ((long long)c->forloop_range * c->kt > 16384) return 0;
+  } else {
+    if (c->data_type != MG_DT_FLOAT16 && c->data_type != MG_DT_BFLOAT16) return 0;
+    for (mgd_op const *op : {&c->x, &c->w1, &c->w2})
+      if ((op->a[MGD_IN_LAYOUT] & 0xff) != MG_DMEM_ROW_MAJOR) return 0;
+  }
   int32_t const *o = c->out.a;
   for (int i : {3, 4, 5, 6, 7, 8})
     if (o[i] & 1) return 0; // 32-bit stores of column pairs
@@ -369,8 +471,8 @@ int mgd_matmul_chain_supported(const mgd_matmul_chain *c, int32_t fingerprint_mo
   return pick_stages(c) >= 2;
 }
 
-int mgd_launch_matmul_chain_float(const mgd_matmul_chain *c, const mgd_bindings *bind, void *stream) {
-  if (!c || !bind || !mgd_matmul_chain_supported(c, 0)) return set_error(MG_ERR_UNSUPPORTED, "matmul chain: shape not supported");
+static int launch_chain(const mgd_matmul_chain *c, const mgd_bindings *bind, int mode, void *stream) {
+  if (!c || !bind || !mgd_matmul_chain_supported(c, mode == 2)) return set_error(MG_ERR_UNSUPPORTED, "matmul chain: shape not supported");
   chain::Params p;
   std::memset(&p, 0, sizeof(p));
   p.c = *c;
@@ -386,23 +488,25 @@ int mgd_launch_matmul_chain_float(const mgd_matmul_chain *c, const mgd_bindings 
   size_t const smem = chain::make_plan(c->kt, c->n1, c->n2, p.stages).total_bytes;
   long long const blocks = (long long)c->grid[0] * c->grid[1] * c->grid[2] * bind->num_sets;
   if (blocks > 0x7fffffffLL) return set_error(MG_ERR_UNSUPPORTED, "too many blocks for one launch");
-  static bool configured[64][2] = {};
+  using Kernel = void (*)(chain::Params);
+  static Kernel const kernels[3] = {chain::chain_kernel<0>, chain::chain_kernel<1>, chain::chain_kernel<2>};
+  static bool configured[64][3] = {};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
-  int const mode = c->data_type == MG_DT_BFLOAT16 ? 1 : 0;
   if (!configured[dev][mode]) {
-    cudaError_t e = mode ? cudaFuncSetAttribute(chain::chain_float_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit - 1024)
-                         : cudaFuncSetAttribute(chain::chain_float_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit - 1024);
-    if (e != cudaSuccess) return check_launch("cudaFuncSetAttribute(chain_float_kernel)");
+    if (cudaFuncSetAttribute(kernels[mode], cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit - 1024) != cudaSuccess)
+      return check_launch("cudaFuncSetAttribute(chain_kernel)");
     configured[dev][mode] = true;
   }
-  if (mode) chain::chain_float_kernel<1><<<(unsigned)blocks, chain::kThreads, smem, (cudaStream_t)stream>>>(p);
-  else chain::chain_float_kernel<0><<<(unsigned)blocks, chain::kThreads, smem, (cudaStream_t)stream>>>(p);
-  return check_launch("chain_float_kernel");
+  kernels[mode]<<<(unsigned)blocks, chain::kThreads, smem, (cudaStream_t)stream>>>(p);
+  return check_launch("chain_kernel");
 }
 
+int mgd_launch_matmul_chain_float(const mgd_matmul_chain *c, const mgd_bindings *bind, void *stream) {
+  if (!c || (c->data_type != MG_DT_FLOAT16 && c->data_type != MG_DT_BFLOAT16)) return set_error(MG_ERR_UNSUPPORTED, "matmul chain: fp16 or bf16");
+  return launch_chain(c, bind, c->data_type == MG_DT_BFLOAT16 ? 1 : 0, stream);
+}
 int mgd_launch_matmul_chain_fingerprint(const mgd_matmul_chain *c, const mgd_bindings *bind, void *stream) {
-  (void)c; (void)bind; (void)stream;
-  return set_error(MG_ERR_UNSUPPORTED, "matmul chain: no fingerprint kernel");
+  return launch_chain(c, bind, 2, stream);
 }
 }

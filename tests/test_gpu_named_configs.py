@@ -329,6 +329,69 @@ def test_kn_fingerprint_matmul_on_tensor_cores(runtime, shape, hi):
             runtime.set_option(mg.OPT_KN_MATMUL_ENGINE, 0)
 
 
+@pytest.mark.parametrize("shape", [(16, 1024, 1024, 1024, 16, 16), (16, 256, 128, 64, 4, 4), (5, 512, 256, 512, 2, 8),
+                                   (12, 128, 256, 256, 2, 1), (16, 768, 384, 256, 3, 6)],
+                         ids=["config_1", "small", "five_rows_n1_128", "loop_of_one", "three_blocks"])
+def test_matmul_chain_and_cross_block_sum_kernels(runtime, shape):
+    """The matmul-chain customized operator and the cross-block sum behind it on their specialised kernels: selected
+    when specialisation is on, equal (fingerprints: bit for bit) to the generic interpreters and to the oracle, in
+    float mode (fp16 and bf16) and in fingerprint mode over the full uint16 range."""
+    M, K, N1, N2, G, LOOP = shape  # X[M,K] W1[K,N1] W2[N1,N2]; G blocks over W1's columns / W2's rows
+    kt = K // LOOP
+    chain = mg.ExecutionPlan(ops=[(mg.TB_MATMUL_OP, [(0, 0), (1, 0)]), (mg.TB_MATMUL_OP, [(3, 0), (2, 0)])],
+                             input_map=[(-1, -1, -1), (1, -1, -1), (0, -1, -1)], forloop_dim=[1, 0, -1],
+                             input_smem_layouts=[mg.SmemRowMajor] * 3, output_map=(1, -1, -1), forloop_range=LOOP,
+                             grid_dim=(G, 1, 1), reduction_dimx=N2)
+    reduce_plan = mg.ExecutionPlan(ops=[(mg.TB_REDUCTION_1_TO_DIMX_OP, [(0, 0)])], input_map=[(0, -1, -1)],
+                                   forloop_dim=[-1], input_smem_layouts=[mg.SmemRowMajor], output_map=(0, -1, -1),
+                                   forloop_range=1, grid_dim=(M, 1, 1), reduction_dimx=N2)
+    assert kt % 16 == 0 and (N1 // G) % 16 == 0
+    rng = np.random.default_rng(sum(shape))
+    results = {}
+    try:
+        for level in (2, 0):
+            runtime.set_specialisation(level)
+            with mg.PyGraph(runtime) as g:
+                X = g.new_input((M, K)); W1 = g.new_input((K, N1)); W2 = g.new_input((N1, N2))
+                part = g.customized([X, W1, W2], chain)
+                final = g.customized(part, reduce_plan)
+                i1, i2 = g.customized_info(3), g.customized_info(4)
+                if level == 2:
+                    assert i1["kernel_float"] == mg.KERNEL_MATMUL_CHAIN and i1["kernel_fingerprint"] == mg.KERNEL_MATMUL_CHAIN
+                    assert i2["kernel_float"] == mg.KERNEL_TILE_REDUCE and i2["kernel_fingerprint"] == mg.KERNEL_TILE_REDUCE
+                else:
+                    assert i1["kernel_float"] == mg.KERNEL_INTERPRETER and i2["kernel_fingerprint"] == mg.KERNEL_INTERPRETER
+                fx = [rng.integers(0, 65536, size=t.shape).astype(np.uint16) for t in (X, W1, W2)] if level == 2 else results["fx"]
+                results["fx"] = fx
+                for t, a in zip((X, W1, W2), fx):
+                    t.upload_fingerprint(a)
+                for _ in range(2):
+                    g.fingerprint()
+                results[("fp", level)] = (part[0].download_fingerprint(), final[0].download_fingerprint())
+        a, b, c = (results["fx"][i].astype(object) for i in range(3))
+        want = np.array(((a @ b) % mo.FP_PQ @ c) % mo.FP_PQ, dtype=np.uint64).astype(np.uint16)
+        assert np.array_equal(results[("fp", 2)][1], want), "fingerprint result vs the exact product modulo PQ"
+        assert np.array_equal(results[("fp", 2)][0], results[("fp", 0)][0]), "partials: chain kernel vs interpreter"
+        assert np.array_equal(results[("fp", 2)][1], results[("fp", 0)][1]), "sums: reduction kernel vs interpreter"
+        for dtype in (mg.float16, mg.bfloat16):
+            rnd = lambda v: from_bits(to_bits(v, dtype), dtype)
+            x = rnd(rng.standard_normal((M, K)) * 0.05); w1 = rnd(rng.standard_normal((K, N1)) * 0.05)
+            w2 = rnd(rng.standard_normal((N1, N2)) * 0.05)
+            exact = (x.astype(np.float64) @ w1.astype(np.float64)) @ w2.astype(np.float64)
+            runtime.set_specialisation(2)
+            with mg.PyGraph(runtime) as g:
+                X = g.new_input((M, K), dtype); W1 = g.new_input((K, N1), dtype); W2 = g.new_input((N1, N2), dtype)
+                final = g.customized(g.customized([X, W1, W2], chain), reduce_plan)
+                for t, v in zip((X, W1, W2), (x, w1, w2)):
+                    t.upload_data(to_bits(v, dtype))
+                g.run()
+                g.run()
+                got = from_bits(final[0].download_data(), dtype).reshape(final[0].shape)
+            assert_close(got, exact, dtype, "chain result vs the fp64 product")
+    finally:
+        runtime.set_specialisation(2)
+
+
 # ---- launch policies ------------------------------------------------------------------------------------------------------
 def test_throughput_policy_parity_and_captured_overlap(runtime):
     """The launch sizing the benchmark's headline uses (small blocks, several calls in flight): every graph on its
