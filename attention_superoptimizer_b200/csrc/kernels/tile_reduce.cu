@@ -44,6 +44,7 @@ __global__ void __launch_bounds__(256) tile_reduce_kernel(const __grid_constant_
     int pos = (i / inner) * (inner * degree) + i % inner;
     float facc = 0.f;
     unsigned long long iacc = 0;
+#pragma unroll 4
     for (int k = 0; k < degree; k++, pos += inner) {
       int const r = pos / itc, cc = pos - r * itc;
       uint16_t const v = __ldg(src + (long long)r * ild + cc);

@@ -638,7 +638,7 @@ def run_one_config(args):
 def measure_other_configs(mg, rt, stream, timed, peaks, only=None, quick=False, world=1, rank=0):
     """Device-timed numbers for the remaining configurations (N = 1 only), each replayed from a CUDA graph:
     speculative decode with the causal draft window (fp16), dense prefill (bf16, tcgen05) and the matmul chain (both
-    modes on the generic interpreters).  `only` = "c1" | "c3" | "c4" runs one; `quick` = few replays (profiling)."""
+    modes).  `only` = "c1" | "c3" | "c4" runs one; `quick` = few replays (profiling)."""
     sh = stream.cuda_stream
     out = {}
 
@@ -751,16 +751,18 @@ def measure_other_configs(mg, rt, stream, timed, peaks, only=None, quick=False, 
         X.fill_data_seeded(943, 0.02); W1.fill_data_seeded(944, 0.02); W2.fill_data_seeded(945, 0.02)
         float_us = replay_us(graphs_runner([g]), 10)
         nbytes = 4259840
+        info = g.customized_info(3)
+        names = {0: "generic interpreter", 4: "chain_kernel + tile_reduce_kernel"}
         out["matmul_chain_c1"] = {"float_us_per_call": round(float_us, 1), "fingerprint_us_per_call": round(fp_us, 1),
-                                  "kernel": g.customized_info(3)["kernel_fingerprint"], "dtype": "fp16",
+                                  "kernel": info["kernel_fingerprint"], "kernel_float": info["kernel_float"], "dtype": "fp16",
                                   "bytes": nbytes, "flops": 67108864,
-                                  "roofline_float": hbm_roofline(nbytes, float_us, "float_interp_kernel<fp16>"),
-                                  "roofline_fingerprint": hbm_roofline(nbytes, fp_us, "fp_interp_kernel"),
+                                  "roofline_float": hbm_roofline(nbytes, float_us, names.get(info["kernel_float"], "?") + " (fp16)"),
+                                  "roofline_fingerprint": hbm_roofline(nbytes, fp_us, names.get(info["kernel_fingerprint"], "?") + " (fingerprints)"),
                                   "note": "two customized ops (16 blocks over the intermediate columns, for-loop 16 over K "
-                                          "tiles of 64; then the cross-block reduction), generic interpreters; inputs N(0, 0.02) / "
-                                          "uniform [0,227); both modes replayed from a CUDA graph; the HBM floor of 0.65 us is "
-                                          "not the binding limit of 16 blocks (launch latency and the plan's redundant "
-                                          "arithmetic are)"}
+                                          "tiles of 64; then the cross-block reduction); inputs N(0, 0.02) / uniform [0,227); both "
+                                          "modes replayed from a CUDA graph; the HBM floor of 0.65 us is not the binding limit of a "
+                                          "16-block plan (two dependent launches and the latency of one block's 290 KB of tiles are); "
+                                          "--interpreter-only times the generic interpreters on the same plan"}
         g.close()
 
     for name, fn in (("c3", config3), ("c4", config4), ("c1", config1)):
