@@ -144,6 +144,34 @@ def test_kernel_selection_and_launch_refusal(planning_runtime):
         assert e.value.status == 7
 
 
+def test_matmul_chain_and_reduction_patterns_are_recognised(planning_runtime):
+    """The lowered programs of the matmul-chain operator and of a single-reduction operator select their kernels;
+    a chain whose second right operand moves with the for-loop does not (it stays on the interpreters)."""
+    chain = mg.ExecutionPlan(ops=[(mg.TB_MATMUL_OP, [(0, 0), (1, 0)]), (mg.TB_MATMUL_OP, [(3, 0), (2, 0)])],
+                             input_map=[(-1, -1, -1), (1, -1, -1), (0, -1, -1)], forloop_dim=[1, 0, -1],
+                             input_smem_layouts=[mg.SmemRowMajor] * 3, output_map=(1, -1, -1), forloop_range=16,
+                             grid_dim=(16, 1, 1), reduction_dimx=1024)
+    reduce_plan = mg.ExecutionPlan(ops=[(mg.TB_REDUCTION_1_TO_DIMX_OP, [(0, 0)])], input_map=[(0, -1, -1)],
+                                   forloop_dim=[-1], input_smem_layouts=[mg.SmemRowMajor], output_map=(0, -1, -1),
+                                   forloop_range=1, grid_dim=(16, 1, 1), reduction_dimx=1024)
+    planning_runtime.set_max_smem(227 * 1024)
+    with mg.PyGraph(planning_runtime) as g:
+        X = g.new_input((16, 1024)); W1 = g.new_input((1024, 1024)); W2 = g.new_input((1024, 1024))
+        part = g.customized([X, W1, W2], chain)
+        g.customized(part, reduce_plan)
+        i1, i2 = g.customized_info(3), g.customized_info(4)
+        assert i1["kernel_float"] == mg.KERNEL_MATMUL_CHAIN and i1["kernel_fingerprint"] == mg.KERNEL_MATMUL_CHAIN
+        assert i2["kernel_float"] == mg.KERNEL_TILE_REDUCE and i2["kernel_fingerprint"] == mg.KERNEL_TILE_REDUCE
+    moving = mg.ExecutionPlan(ops=[(mg.TB_MATMUL_OP, [(0, 0), (1, 0)]), (mg.TB_MATMUL_OP, [(3, 0), (2, 0)])],
+                              input_map=[(-1, -1, -1), (1, -1, -1), (-1, -1, -1)], forloop_dim=[1, 0, 1],
+                              input_smem_layouts=[mg.SmemRowMajor] * 3, output_map=(1, -1, -1), forloop_range=4,
+                              grid_dim=(2, 1, 1), reduction_dimx=64)
+    with mg.PyGraph(planning_runtime) as g:
+        X = g.new_input((16, 256)); W1 = g.new_input((256, 128)); W2 = g.new_input((64, 256))
+        g.customized([X, W1, W2], moving)
+        assert g.customized_info(3)["kernel_float"] == mg.KERNEL_INTERPRETER
+
+
 def test_unfused_graph_shapes(planning_runtime):
     with mg.PyGraph(planning_runtime) as g:
         Q = g.new_input((2, 8, 64))
