@@ -246,6 +246,40 @@ def run_ours(args):
                 "bytes_per_launch": launch_bytes, "us_per_launch": round(us_per_launch, 3),
                 "launches_timed": int(gpu_launches)}
 
+    # ---- the same with the work per GPU and launch held constant (N > 1): 64 x N calls per launch, so that a GPU's
+    # launch carries the 8 x 64 (KV head, call) units it carries at N = 1.  Reported beside the headline, which
+    # keeps 64 calls per launch at every N (a GPU's launch shrinks with N there).
+    fixed_work = None
+    if world > 1:
+        wb = batch * world
+        wdense = [torch.empty(2 * wb * n, dtype=torch.int16, device="cuda") for n in elems]
+        wout = torch.zeros(2 * wb * (ob // 2), dtype=torch.int16, device="cuda")
+        for i, (buf, n) in enumerate(zip(wdense, elems)):
+            for s in range(2 * wb):
+                mg.fill_data_seeded_raw(rt, buf.data_ptr() + 2 * s * n, n, 3 * (90000 + 4000 * rank + s) + i,
+                                        HEAD_DIM ** -0.5 if i == 0 else 1.0)
+        ww = bg.run_batched_workspace(wb)
+        wwork = torch.empty(max(ww, 256), dtype=torch.uint8, device="cuda")
+
+        def launch_wide(b):
+            bg.run_batched(wb, [d.data_ptr() + 2 * b * wb * n for d, n in zip(wdense, elems)],
+                           wout.data_ptr() + b * wb * ob, wwork.data_ptr(), ww, stream=sh)
+
+        for b in range(2):
+            launch_wide(b)
+        mg.synchronize()
+        wide_graph = mg.CapturedSequence(sh, lambda: [launch_wide(b) for b in range(2)])
+        wreps = max(1, round(10e3 / (2 * wb * 2.9 * heads / KV_HEADS + 20)))
+        wide_ms = timed(lambda: [wide_graph.launch() for _ in range(wreps)], 5, 3) / 5
+        wide_graph.close()
+        mg.synchronize()
+        w_launch_us = wide_ms * 1000.0 / (wreps * 2)
+        fixed_work = {"calls_per_launch": wb, "us_per_call": round(wide_ms * 1000.0 / (wreps * 2 * wb), 3),
+                      "us_per_launch": round(w_launch_us, 2),
+                      "frac_of_hbm_peak_per_gpu": round(wb * (qb + kb + vb + ob) / (w_launch_us * 1e-6) / 1e9 / peaks["hbm_gbs"], 4),
+                      "note": "64 x N calls per launch: every GPU's launch keeps the size it has at N = 1"}
+        del wdense, wout, wwork
+
     # output check of the timed protocol: a few calls of the last replay against the fp32 evaluation
     checked_calls, worst = 0, 0.0
     if rank == 0:
@@ -408,7 +442,7 @@ def run_ours(args):
             "per_call_launch": per_call_launch,
             "stream_ordered_us_per_call": None if ordered_us is None else round(ordered_us, 3),
             "single_call_us_median": None if single_us is None else round(single_us, 3),
-            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(gpu_launches),
+            "roofline": roofline, "fixed_work_per_gpu": fixed_work, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(gpu_launches),
             "clocks": clocks, "fingerprint": fingerprint, "candidates": candidates, "other_configs": others,
         }
         print(json.dumps(line))
