@@ -37,17 +37,12 @@ namespace mgk {
 namespace pp {
 using namespace t5;
 
-// Optional role timing of block 0 (compile with -DMG_PP_TIMING; prints cycle totals from the device).
+// Optional timeline of block 0 (compile with -DMG_PP_TIMING): the MMA lane and one exp lane per query tile stamp the
+// cycle counter into shared memory for a few KV tiles, thread 0 prints the stamps when the block winds down.
 #ifdef MG_PP_TIMING
-#define TICK(var) long long var = clock64()
-#define TOCK(acc, var) acc += clock64() - var
-#define TDECL(...) long long __VA_ARGS__
-#define TPRINT(...) if (blockIdx.x == 0) printf(__VA_ARGS__)
+#define STAMP(slot) (slot) = clock64()
 #else
-#define TICK(var)
-#define TOCK(acc, var)
-#define TDECL(...)
-#define TPRINT(...)
+#define STAMP(slot)
 #endif
 
 constexpr int kD = 128, kTile = 128;
@@ -64,10 +59,13 @@ struct Params {
 };
 
 struct Shared {
-  uint64_t q_full, kv_full[kStages], kv_empty[kStages], s_full[2], e_full[2], o_full[2];
+  uint64_t q_full, k_full[kStages], k_empty[kStages], v_full[kStages], v_empty[kStages], s_full[2], e_full[2], o_full[2];
   uint32_t tmem_base;
   int abort_flag;
   float row_sums[2][2][kTile]; // [query tile][column half][row]
+#ifdef MG_PP_TIMING
+  long long t_block[10], t_lane[16][8], t_exp[2][16][4], t_arrive[2][8][2], t_ewait[16][2], t_spin[4][4];
+#endif
 };
 
 __device__ __forceinline__ uint64_t k_major_step(int ks) { return (uint64_t)(((ks >> 2) * kBox + (ks & 3) * 32) >> 4); }
@@ -93,14 +91,17 @@ attn_rows_pp_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
   int const F = p.forloop;
 
   if (tid == 0) {
+    STAMP(sh->t_block[0]);
     sh->abort_flag = 0;
     asm volatile("prefetch.tensormap [%0];" ::"l"(&q_map) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&k_map) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&v_map) : "memory");
     mbar_init(smem_u32(&sh->q_full), 1);
     for (int s = 0; s < kStages; s++) {
-      mbar_init(smem_u32(&sh->kv_full[s]), 1);
-      mbar_init(smem_u32(&sh->kv_empty[s]), 1);
+      mbar_init(smem_u32(&sh->k_full[s]), 1);
+      mbar_init(smem_u32(&sh->k_empty[s]), 1);
+      mbar_init(smem_u32(&sh->v_full[s]), 1);
+      mbar_init(smem_u32(&sh->v_empty[s]), 1);
     }
     for (int i = 0; i < 2; i++) {
       mbar_init(smem_u32(&sh->s_full[i]), 1);
@@ -115,43 +116,56 @@ attn_rows_pp_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
   __syncthreads();
   tc_fence_after();
   uint32_t const tmem = sh->tmem_base;
+  if (tid == 0) STAMP(sh->t_block[1]);
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
+    // K and V tiles have rings of their own: the slot of K_j is free once S1(j) has run, the slot of V_j once O'1(j)
+    // has, and both are next needed a whole round of MMAs later (K_{j+2} by S0(j+2), V_{j+2} by O'0(j+2)).
     if (lane == 0) {
-      uint32_t full = smem_u32(&sh->q_full);
+      uint32_t const full = smem_u32(&sh->q_full);
       mbar_expect_tx(full, 2 * kOperand);
       for (int i = 0; i < 2; i++) { // Q memory [heads][seq_q][d]: rows = query rows, two boxes over d
         tma_load_3d(q_smem + (uint32_t)(i * kOperand), &q_map, full, 0, q0 + i * kTile, head);
         tma_load_3d(q_smem + (uint32_t)(i * kOperand + kBox), &q_map, full, 64, q0 + i * kTile, head);
       }
-    }
-    __syncwarp();
-    for (int j = 0; j < F; j++) {
-      int const s = j % kStages;
-      if (j >= kStages && !mbar_wait(smem_u32(&sh->kv_empty[s]), (uint32_t)(((j / kStages) - 1) & 1), abort_flag)) break;
-      if (lane == 0) {
-        uint32_t full = smem_u32(&sh->kv_full[s]);
-        uint32_t kdst = ring + (uint32_t)(s * 2 * kOperand), vdst = kdst + kOperand;
+      auto load_k = [&](int j) {
+        uint32_t const bar = smem_u32(&sh->k_full[j % kStages]), dst = ring + (uint32_t)((j % kStages) * 2 * kOperand);
         int const kv0 = j * kTile;
-        mbar_expect_tx(full, 2 * kOperand);
+        mbar_expect_tx(bar, kOperand);
         if (K_KV) { // rows = KV positions, boxes over d
-          tma_load_3d(kdst, &k_map, full, 0, kv0, head);
-          tma_load_3d(kdst + kBox, &k_map, full, 64, kv0, head);
+          tma_load_3d(dst, &k_map, bar, 0, kv0, head);
+          tma_load_3d(dst + kBox, &k_map, bar, 64, kv0, head);
         } else {    // rows = d, boxes over this tile's KV positions
-          tma_load_3d(kdst, &k_map, full, kv0, 0, head);
-          tma_load_3d(kdst + kBox, &k_map, full, kv0 + 64, 0, head);
+          tma_load_3d(dst, &k_map, bar, kv0, 0, head);
+          tma_load_3d(dst + kBox, &k_map, bar, kv0 + 64, 0, head);
         }
+      };
+      auto load_v = [&](int j) {
+        uint32_t const bar = smem_u32(&sh->v_full[j % kStages]), dst = ring + (uint32_t)((j % kStages) * 2 * kOperand + kOperand);
+        int const kv0 = j * kTile;
+        mbar_expect_tx(bar, kOperand);
         if (V_KV) {
-          tma_load_3d(vdst, &v_map, full, 0, kv0, head);
-          tma_load_3d(vdst + kBox, &v_map, full, 64, kv0, head);
+          tma_load_3d(dst, &v_map, bar, 0, kv0, head);
+          tma_load_3d(dst + kBox, &v_map, bar, 64, kv0, head);
         } else {
-          tma_load_3d(vdst, &v_map, full, kv0, 0, head);
-          tma_load_3d(vdst + kBox, &v_map, full, kv0 + 64, 0, head);
+          tma_load_3d(dst, &v_map, bar, kv0, 0, head);
+          tma_load_3d(dst + kBox, &v_map, bar, kv0 + 64, 0, head);
+        }
+      };
+      load_k(0);
+      load_v(0);
+      if (F > 1) load_k(1);
+      for (int t = 1; t < F; t++) { // V_t, then K_{t+1}: the order in which their slots come free
+        if (t >= kStages && !mbar_wait(smem_u32(&sh->v_empty[t % kStages]), (uint32_t)(((t / kStages) - 1) & 1), abort_flag)) break;
+        load_v(t);
+        if (t + 1 < F) {
+          if (t + 1 >= kStages && !mbar_wait(smem_u32(&sh->k_empty[(t + 1) % kStages]), (uint32_t)((((t + 1) / kStages) - 1) & 1), abort_flag)) break;
+          load_k(t + 1);
         }
       }
-      __syncwarp();
     }
+    __syncwarp();
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     // Descriptors of stage 0 / tile 0; a stage, a tile or a K step only moves the start-address field, so the issuing
@@ -162,14 +176,15 @@ attn_rows_pp_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
     uint64_t const q_desc0 = smem_desc(q_smem, 16, 1024, 2);
     uint64_t const k_desc0 = K_KV ? smem_desc(ring, 16, 1024, 2) : smem_desc(ring, kBox, 1024, 2);
     uint64_t const v_desc0 = V_KV ? smem_desc(ring + kOperand, kBox, 1024, 2) : smem_desc(ring + kOperand, 16, 1024, 2);
-    auto issue_s = [&](int i, int j) { // S_i(j) = Q_i K_j
+    // S_i(j) = Q_i K_j, contraction steps [ks0, ks1); the last part commits to s_full
+    auto issue_s = [&](int i, int j, int ks0, int ks1) {
       uint64_t const qd = q_desc0 + (uint64_t)((i * kOperand) >> 4);
       uint64_t const kd = k_desc0 + (uint64_t)(((j % kStages) * 2 * kOperand) >> 4);
       uint32_t const d_tmem = tmem + (uint32_t)(i * kTile);
 #pragma unroll
-      for (int ks = 0; ks < kD / 16; ks++)
+      for (int ks = ks0; ks < ks1; ks++)
         umma_f16(d_tmem, qd + k_major_step(ks), kd + (K_KV ? k_major_step(ks) : mn_major_step(ks)), idesc_s, ks > 0);
-      umma_commit(smem_u32(&sh->s_full[i]));
+      if (ks1 == kD / 16) umma_commit(smem_u32(&sh->s_full[i]));
     };
     auto issue_o = [&](int i, int j) { // O'_i += E_i(j) V_j; E in the S buffer: half h at columns [64h, 64h+32), 8 per step
       uint64_t const vd = v_desc0 + (uint64_t)(((j % kStages) * 2 * kOperand) >> 4);
@@ -179,46 +194,83 @@ attn_rows_pp_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
         umma_f16_ts(d_tmem, e_tmem + (uint32_t)((ks >> 2) * 64 + (ks & 3) * 8), vd + (V_KV ? mn_major_step(ks) : k_major_step(ks)),
                     idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
     };
-    bool ok = mbar_wait(smem_u32(&sh->q_full), 0, abort_flag);
-    if (ok) ok = mbar_wait(smem_u32(&sh->kv_full[0]), 0, abort_flag);
-    if (ok) {
-      tc_fence_after();
-      if (lane == 0) {
-        issue_s(0, 0);
-        issue_s(1, 0);
-      }
-      __syncwarp();
-    }
-    TDECL(w_e0 = 0, w_e1 = 0, w_kv = 0, c_issue = 0, c_o = 0, c_c = 0, c_s = 0, t0 = clock64());
-    for (int j = 0; j < F && ok; j++) {
-      for (int i = 0; i < 2 && ok; i++) {
-        TICK(a0);
-        ok = mbar_wait(smem_u32(&sh->e_full[i]), (uint32_t)(j & 1), abort_flag);
-        if (i == 0) { TOCK(w_e0, a0); } else { TOCK(w_e1, a0); }
-        TICK(a1);
-        // K_{j+1}, V_{j+1} for the S MMA issued right behind this tile's O' MMA
-        if (ok && i == 0 && j + 1 < F) ok = mbar_wait(smem_u32(&sh->kv_full[(j + 1) % kStages]), (uint32_t)(((j + 1) / kStages) & 1), abort_flag);
-        TOCK(w_kv, a1);
-        if (!ok) break;
+    // One lane runs the whole loop.  An instruction of that lane that needs an answer from shared memory (a barrier
+    // test) gets it only after the MMAs issued before it have been handed to the tensor pipe, and the pipe queues
+    // little by itself: a test between two batches of MMAs leaves the pipe idle.  So what the next batch will wait
+    // for is tested `kProbeAt` MMAs into the S batch before it, and the wait in front of a batch is only taken when
+    // that test failed.  Tests and waits are `mbarrier.test_wait` polls: `try_wait` parks a thread whose phase is not
+    // complete, and a parked lane came back about 500 cycles after the phase had completed.
+    constexpr int kProbeAt = 5;
+    if (lane == 0) {
+      bool ok = mbar_spin_or_abort(smem_u32(&sh->q_full), 0, abort_flag);
+      STAMP(sh->t_block[2]);
+      if (ok) ok = mbar_spin_or_abort(smem_u32(&sh->k_full[0]), 0, abort_flag);
+      STAMP(sh->t_block[3]);
+      if (ok) {
         tc_fence_after();
-        TICK(a2);
-        if (lane == 0) {
-          TICK(b0);
-          issue_o(i, j);
-          TOCK(c_o, b0);
-          TICK(b1);
-          if (i == 1) umma_commit(smem_u32(&sh->kv_empty[j % kStages])); // K_j, V_j consumed by both tiles
-          if (j == F - 1) umma_commit(smem_u32(&sh->o_full[i]));
-          TOCK(c_c, b1);
-          TICK(b2);
-          if (j + 1 < F) issue_s(i, j + 1);
-          TOCK(c_s, b2);
-        }
-        __syncwarp();
-        TOCK(c_issue, a2);
+        issue_s(0, 0, 0, kD / 16);
+        issue_s(1, 0, 0, kD / 16);
+        umma_commit(smem_u32(&sh->k_empty[0]));
       }
+      STAMP(sh->t_block[4]);
+      bool e_known = false, v_known = false, k_known = false; // barriers of the coming batches already seen complete
+      for (int j = 0; j < F && ok; j++) {
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+#ifdef MG_PP_TIMING
+          if (!e_known && j >= 4 && j < 8 && i == 0) {
+            long long ta = clock64();
+            bool first = mbar_test_wait(smem_u32(&sh->e_full[i]), (uint32_t)(j & 1));
+            long long tb2 = clock64();
+            int n = 0;
+            while (!first && n < 100000 && !mbar_test_wait(smem_u32(&sh->e_full[i]), (uint32_t)(j & 1))) n++;
+            long long tc = clock64();
+            sh->t_spin[j - 4][0] = ta; sh->t_spin[j - 4][1] = tb2; sh->t_spin[j - 4][2] = tc; sh->t_spin[j - 4][3] = n + (first ? 1000000 : 0);
+            e_known = true;
+          }
+#endif
+          if (!e_known) ok = mbar_spin_or_abort(smem_u32(&sh->e_full[i]), (uint32_t)(j & 1), abort_flag);
+#ifdef MG_PP_TIMING
+          if (j < 16) STAMP(sh->t_ewait[j][i]);
+#endif
+          if (ok && i == 0 && !v_known) ok = mbar_spin_or_abort(smem_u32(&sh->v_full[j % kStages]), (uint32_t)((j / kStages) & 1), abort_flag);
+          if (!ok) break;
+#ifdef MG_PP_TIMING
+          if (j < 16) STAMP(sh->t_lane[j][i * 4 + 0]);
+#endif
+          tc_fence_after();
+          issue_o(i, j);
+          if (i == 1) umma_commit(smem_u32(&sh->v_empty[j % kStages])); // V_j consumed by both query tiles
+          if (j == F - 1) umma_commit(smem_u32(&sh->o_full[i]));
+#ifdef MG_PP_TIMING
+          if (j < 16) STAMP(sh->t_lane[j][i * 4 + 1]);
+#endif
+          e_known = false;
+          if (j + 1 < F) {
+            if (i == 0 && !k_known) ok = mbar_spin_or_abort(smem_u32(&sh->k_full[(j + 1) % kStages]), (uint32_t)(((j + 1) / kStages) & 1), abort_flag);
+            if (!ok) break;
+#ifdef MG_PP_TIMING
+            if (j < 16) STAMP(sh->t_lane[j][i * 4 + 2]);
+#endif
+            issue_s(i, j + 1, 0, kProbeAt);
+            if (i == 0) { // next batch: O'1(j), S1(j+1)
+              e_known = mbar_test_wait(smem_u32(&sh->e_full[1]), (uint32_t)(j & 1));
+            } else {      // next batch: O'0(j+1), S0(j+2)
+              e_known = mbar_test_wait(smem_u32(&sh->e_full[0]), (uint32_t)((j + 1) & 1));
+              v_known = mbar_test_wait(smem_u32(&sh->v_full[(j + 1) % kStages]), (uint32_t)(((j + 1) / kStages) & 1));
+              k_known = j + 2 < F && mbar_test_wait(smem_u32(&sh->k_full[(j + 2) % kStages]), (uint32_t)(((j + 2) / kStages) & 1));
+            }
+            issue_s(i, j + 1, kProbeAt, kD / 16);
+            if (i == 1) umma_commit(smem_u32(&sh->k_empty[(j + 1) % kStages])); // K_{j+1} consumed by both query tiles
+          }
+#ifdef MG_PP_TIMING
+          if (j < 16) STAMP(sh->t_lane[j][i * 4 + 3]);
+#endif
+        }
+      }
+      STAMP(sh->t_block[5]);
     }
-    if (lane == 0) TPRINT("mma: total %lld wait e_full0 %lld e_full1 %lld kv_full %lld issue %lld = O %lld + commits %lld + S(incl. its commit) %lld (%d kv tiles)\n", clock64() - t0, w_e0, w_e1, w_kv, c_issue, c_o, c_c, c_s, F);
+    __syncwarp();
   } else {
     // ------------------------------------------------------------------ exp / row sums / epilogue of one query tile
     int const i = (warp - 2) >> 3;                // query tile of this warp
@@ -230,20 +282,22 @@ attn_rows_pp_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
     uint32_t const s_tmem = tmem + (uint32_t)(i * kTile) + lane_base + (uint32_t)(half * 64);
     float rsum = 0.f;
     bool ok = true;
-    TDECL(w_s = 0, c_ld = 0, c_exp = 0, c_st = 0, t0 = clock64());
     for (int j = 0; j < F && ok; j++) {
-      TICK(a0);
       ok = mbar_wait(smem_u32(&sh->s_full[i]), (uint32_t)(j & 1), abort_flag);
-      TOCK(w_s, a0);
       if (!ok) break;
+#ifdef MG_PP_TIMING
+      bool const stamps = lane == 0 && wi == 0 && j < 16;
+      if (stamps) STAMP(sh->t_exp[i][j][0]);
+      if (lane == 0 && j == 5) STAMP(sh->t_arrive[i][wi][0]);
+#endif
       tc_fence_after();
-      TICK(a1);
       uint32_t flat[32]; // this thread's 64 values as 16-bit pairs
       {
         uint32_t v[64];
         tmem_ld64(s_tmem, v); // one load, one wait: the tensor-memory latency is paid once per tile
-        TOCK(c_ld, a1);
-        TICK(a2);
+#ifdef MG_PP_TIMING
+        if (stamps) STAMP(sh->t_exp[i][j][1]);
+#endif
         uint64_t sum2 = 0; // packed arithmetic: the exp warps share their schedulers with the MMA-issuing lane
 #pragma unroll
         for (int x = 0; x < 64; x += 2) {
@@ -255,22 +309,27 @@ attn_rows_pp_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
         float s0, s1;
         unpair(sum2, s0, s1);
         rsum += s0 + s1;
-        TOCK(c_exp, a2);
+#ifdef MG_PP_TIMING
+        if (stamps) STAMP(sh->t_exp[i][j][2]);
+#endif
       }
-      TICK(a3);
       // E replaces the S values this thread has just consumed: 32 packed columns at the start of its own half
       tmem_st32(s_tmem, flat);
       tc_fence_before();
       mbar_arrive(smem_u32(&sh->e_full[i]));
-      TOCK(c_st, a3);
+#ifdef MG_PP_TIMING
+      if (stamps) STAMP(sh->t_exp[i][j][3]);
+      if (lane == 0 && j == 5) STAMP(sh->t_arrive[i][wi][1]);
+#endif
     }
-    if (lane == 0 && (warp == 2 || warp == 10)) TPRINT("exp warp %d: total %lld wait s_full %lld ld %lld exp %lld st+arrive %lld\n", warp, clock64() - t0, w_s, c_ld, c_exp, c_st);
     // the two halves of a row add up their sums (named barrier per query tile, reached whether or not a wait gave up)
     sh->row_sums[i][half][row] = rsum;
     if (i == 0) asm volatile("bar.sync 1, 256;" ::: "memory");
     else asm volatile("bar.sync 2, 256;" ::: "memory");
     float const total = sh->row_sums[i][0][row] + sh->row_sums[i][1][row];
+    if (tid == 64) STAMP(sh->t_block[6]);
     if (ok) ok = mbar_wait(smem_u32(&sh->o_full[i]), 0, abort_flag);
+    if (tid == 64) STAMP(sh->t_block[7]);
     if (ok) {
       tc_fence_after();
       size_t const row_off = ((size_t)head * p.seq_q + q0 + i * kTile + row) * kD + half * 64;
@@ -304,13 +363,36 @@ attn_rows_pp_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
   }
 
   // ---- teardown: every role arrives here, failed or not --------------------------------------------------
+  if (tid == 64) STAMP(sh->t_block[8]);
   tc_fence_before();
   __syncthreads();
+#ifdef MG_PP_TIMING
+  if (blockIdx.x == 0 && tid == 0) {
+    long long const tb = sh->t_block[0];
+    printf("block 0: tensor memory %lld q_full %lld k_full0 %lld S(0) issued %lld lane loop end %lld | exp: loop end %lld o_full %lld stores done %lld\n",
+           sh->t_block[1] - tb, sh->t_block[2] - tb, sh->t_block[3] - tb, sh->t_block[4] - tb, sh->t_block[5] - tb,
+           sh->t_block[6] - tb, sh->t_block[7] - tb, sh->t_block[8] - tb);
+    for (int j = 4; j < 8 && j < F - 1; j++) {
+      long long const *l = sh->t_lane[j];
+      printf("  j=%d spin: first poll issued %lld returned %lld, then %lld polls until %lld\n", j, sh->t_spin[j - 4][0] - tb, sh->t_spin[j - 4][1] - tb, sh->t_spin[j - 4][3], sh->t_spin[j - 4][2] - tb);
+      printf("  j=%d e-wait done %lld / %lld\n", j, sh->t_ewait[j][0] - tb, sh->t_ewait[j][1] - tb);
+      if (j == 5) for (int i = 0; i < 2; i++) for (int w = 0; w < 8; w++) printf("      tile %d warp %d: s_full seen %lld arrive %lld\n", i, w, sh->t_arrive[i][w][0] - tb, sh->t_arrive[i][w][1] - tb);
+      printf("  j=%d lane: waits0 %lld O0 %lld k %lld S0 %lld | waits1 %lld O1 %lld - %lld S1 %lld\n", j, l[0] - tb, l[1] - tb, l[2] - tb,
+             l[3] - tb, l[4] - tb, l[5] - tb, l[6] - tb, l[7] - tb);
+      for (int i = 0; i < 2; i++)
+        printf("      exp%d: s_full %lld ld %lld exp %lld arrive %lld\n", i, sh->t_exp[i][j][0] - tb, sh->t_exp[i][j][1] - tb,
+               sh->t_exp[i][j][2] - tb, sh->t_exp[i][j][3] - tb);
+    }
+  }
+#endif
   if (*abort_flag && tid == 0) {
     // copies this block issued may still be in flight: give them a bounded time to land before the block exits
-    for (int s = 0; s < kStages; s++)
-      for (int n = 0; n < 20000 && !mbar_try_wait(smem_u32(&sh->kv_full[s]), 0) && !mbar_try_wait(smem_u32(&sh->kv_full[s]), 1); n++) {
+    for (int s = 0; s < kStages; s++) {
+      for (int n = 0; n < 20000 && !mbar_try_wait(smem_u32(&sh->k_full[s]), 0) && !mbar_try_wait(smem_u32(&sh->k_full[s]), 1); n++) {
       }
+      for (int n = 0; n < 20000 && !mbar_try_wait(smem_u32(&sh->v_full[s]), 0) && !mbar_try_wait(smem_u32(&sh->v_full[s]), 1); n++) {
+      }
+    }
     atomicExch(p.status, 4);
   }
   __syncthreads();

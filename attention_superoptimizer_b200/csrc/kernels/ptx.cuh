@@ -35,6 +35,15 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
                : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
   return ok != 0;
 }
+// Non-blocking test of a phase.  `try_wait` may park the thread for a while when the phase is not complete, and a
+// parked thread wakes hundreds of cycles after the phase completes; a thread on a kernel's critical path polls with
+// this instead.
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+               : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
 // Bounded wait: false after `limit` polls.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int limit = kWaitLimit) {
   for (int i = 0; i < limit; i++)
@@ -48,6 +57,17 @@ __device__ __forceinline__ bool mbar_wait_or_abort(uint32_t bar, uint32_t parity
   for (int i = 0; i < limit; i++) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((i & 1023) == 1023 && *abort_flag) return false;
+  }
+  *abort_flag = 1;
+  return false;
+}
+
+// The same as a spin on `mbar_test_wait` (for one thread that must see the phase as soon as it completes).
+__device__ __forceinline__ bool mbar_spin_or_abort(uint32_t bar, uint32_t parity, volatile int *abort_flag,
+                                                   int limit = 16 * kWaitLimit) {
+  for (int i = 0; i < limit; i++) {
+    if (mbar_test_wait(bar, parity)) return true;
+    if ((i & 4095) == 4095 && *abort_flag) return false;
   }
   *abort_flag = 1;
   return false;

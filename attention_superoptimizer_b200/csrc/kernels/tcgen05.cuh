@@ -13,6 +13,8 @@ using ptx::mbar_init;
 using ptx::mbar_expect_tx;
 using ptx::mbar_arrive;
 using ptx::mbar_try_wait;
+using ptx::mbar_test_wait;
+using ptx::mbar_spin_or_abort;
 using ptx::tma_load_3d;
 using ptx::fence_proxy_async_smem;
 constexpr int kWaitLimit = ptx::kWaitLimit;
