@@ -32,6 +32,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <mutex>
+#include <type_traits>
 
 namespace mgk {
 namespace pp {
@@ -64,12 +65,12 @@ struct Shared {
   int abort_flag;
   float row_sums[2][2][kTile]; // [query tile][column half][row]
 #ifdef MG_PP_TIMING
-  long long t_block[10], t_lane[16][8], t_exp[2][16][4], t_arrive[2][8][2], t_ewait[16][2], t_spin[4][4];
+  long long t_block[10], t_lane[16][8], t_exp[2][16][4];
 #endif
 };
 
-__device__ __forceinline__ uint64_t k_major_step(int ks) { return (uint64_t)(((ks >> 2) * kBox + (ks & 3) * 32) >> 4); }
-__device__ __forceinline__ uint64_t mn_major_step(int ks) { return (uint64_t)((ks * 16 * 128) >> 4); }
+__device__ __forceinline__ uint32_t k_major_step(int ks) { return (uint32_t)(((ks >> 2) * kBox + (ks & 3) * 32) >> 4); }
+__device__ __forceinline__ uint32_t mn_major_step(int ks) { return (uint32_t)((ks * 16 * 128) >> 4); }
 
 // K_KV: K memory is [kv][d] (K-major B of S) else [d][kv] (MN-major); V_KV: V memory is [kv][d] (MN-major B of O')
 // else [d][kv] (K-major).
@@ -168,32 +169,29 @@ attn_rows_pp_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
     __syncwarp();
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    // Descriptors of stage 0 / tile 0; a stage, a tile or a K step only moves the start-address field, so the issuing
-    // lane pays one 64-bit add per operand and MMA.
+    // The issuing lane's instruction stream is what feeds the tensor pipe (an MMA of 128 x 128 x 16 takes the pipe
+    // about 68 cycles, and the lane shares its scheduler with four exp warps), so everything an MMA needs is laid
+    // out before the loop: the low descriptor words of every (tile, contraction step) of Q, of every (stage, step) of
+    // K and V - a stage, a tile or a step only moves the start-address field of the low word - and the tensor-memory
+    // addresses of E.  The loop body is unrolled over query tiles and ring stages, so these are plain registers.
     uint32_t const fmt = BF16 ? 1u : 0u;
     uint32_t const idesc_s = instr_desc_f16(fmt, false, !K_KV, kTile, kTile);
     uint32_t const idesc_o = instr_desc_f16(fmt, false, V_KV, kTile, kD);
     uint64_t const q_desc0 = smem_desc(q_smem, 16, 1024, 2);
     uint64_t const k_desc0 = K_KV ? smem_desc(ring, 16, 1024, 2) : smem_desc(ring, kBox, 1024, 2);
     uint64_t const v_desc0 = V_KV ? smem_desc(ring + kOperand, kBox, 1024, 2) : smem_desc(ring + kOperand, 16, 1024, 2);
-    // S_i(j) = Q_i K_j, contraction steps [ks0, ks1); the last part commits to s_full
-    auto issue_s = [&](int i, int j, int ks0, int ks1) {
-      uint64_t const qd = q_desc0 + (uint64_t)((i * kOperand) >> 4);
-      uint64_t const kd = k_desc0 + (uint64_t)(((j % kStages) * 2 * kOperand) >> 4);
-      uint32_t const d_tmem = tmem + (uint32_t)(i * kTile);
+    uint32_t const q_hi = (uint32_t)(q_desc0 >> 32), k_hi = (uint32_t)(k_desc0 >> 32), v_hi = (uint32_t)(v_desc0 >> 32);
+    constexpr int kSteps = kD / 16; // contraction steps of either product (kD = kTile)
+    uint32_t q_lo[2][kSteps], k_lo[kStages][kSteps], v_lo[kStages][kSteps], e_at[2][kSteps];
 #pragma unroll
-      for (int ks = ks0; ks < ks1; ks++)
-        umma_f16(d_tmem, qd + k_major_step(ks), kd + (K_KV ? k_major_step(ks) : mn_major_step(ks)), idesc_s, ks > 0);
-      if (ks1 == kD / 16) umma_commit(smem_u32(&sh->s_full[i]));
-    };
-    auto issue_o = [&](int i, int j) { // O'_i += E_i(j) V_j; E in the S buffer: half h at columns [64h, 64h+32), 8 per step
-      uint64_t const vd = v_desc0 + (uint64_t)(((j % kStages) * 2 * kOperand) >> 4);
-      uint32_t const d_tmem = tmem + 256 + (uint32_t)(i * kTile), e_tmem = tmem + (uint32_t)(i * kTile);
+    for (int x = 0; x < 2; x++)
 #pragma unroll
-      for (int ks = 0; ks < kTile / 16; ks++)
-        umma_f16_ts(d_tmem, e_tmem + (uint32_t)((ks >> 2) * 64 + (ks & 3) * 8), vd + (V_KV ? mn_major_step(ks) : k_major_step(ks)),
-                    idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
-    };
+      for (int ks = 0; ks < kSteps; ks++) {
+        q_lo[x][ks] = (uint32_t)q_desc0 + (uint32_t)((x * kOperand) >> 4) + k_major_step(ks);
+        k_lo[x][ks] = (uint32_t)k_desc0 + (uint32_t)((x * 2 * kOperand) >> 4) + (K_KV ? k_major_step(ks) : mn_major_step(ks));
+        v_lo[x][ks] = (uint32_t)v_desc0 + (uint32_t)((x * 2 * kOperand) >> 4) + (V_KV ? mn_major_step(ks) : k_major_step(ks));
+        e_at[x][ks] = tmem + (uint32_t)(x * kTile) + (uint32_t)((ks >> 2) * 64 + (ks & 3) * 8); // half h at [64h, 64h+32), 8 per step
+      }
     // One lane runs the whole loop.  An instruction of that lane that needs an answer from shared memory (a barrier
     // test) gets it only after the MMAs issued before it have been handed to the tensor pipe, and the pipe queues
     // little by itself: a test between two batches of MMAs leaves the pipe idle.  So what the next batch will wait
@@ -202,71 +200,73 @@ attn_rows_pp_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
     // complete, and a parked lane came back about 500 cycles after the phase had completed.
     constexpr int kProbeAt = 5;
     if (lane == 0) {
+      bool e_known = false, v_known = false, k_known = false; // barriers of the coming batches already seen complete
+      // S_I(j) = Q_I K_j with K_j in stage ST, contraction steps [ks0, ks1); the last part commits to s_full
+      auto issue_s = [&](auto I, auto ST, int ks0, int ks1) {
+        constexpr int i = decltype(I)::value, st = decltype(ST)::value;
+#pragma unroll
+        for (int ks = ks0; ks < ks1; ks++)
+          umma_f16_halves(tmem + (uint32_t)(i * kTile), q_lo[i][ks], q_hi, k_lo[st][ks], k_hi, idesc_s, ks > 0);
+        if (ks1 == kSteps) umma_commit(smem_u32(&sh->s_full[i]));
+      };
+      // One batch: O'_I += E_I(j) V_j (V_j in stage ST), then S_I(j+1) (K_{j+1} in the other stage)
+      auto batch = [&](auto I, auto ST, int j) -> bool {
+        constexpr int i = decltype(I)::value, st = decltype(ST)::value;
+        if (!e_known && !mbar_spin_or_abort(smem_u32(&sh->e_full[i]), (uint32_t)(j & 1), abort_flag)) return false;
+        if (i == 0 && !v_known && !mbar_spin_or_abort(smem_u32(&sh->v_full[st]), (uint32_t)((j / kStages) & 1), abort_flag)) return false;
+#ifdef MG_PP_TIMING
+        if (j < 16) STAMP(sh->t_lane[j][i * 4 + 0]);
+#endif
+        tc_fence_after();
+        uint32_t const first = j > 0 ? 1u : 0u;
+#pragma unroll
+        for (int ks = 0; ks < kSteps; ks++)
+          umma_f16_ts_halves(tmem + 256 + (uint32_t)(i * kTile), e_at[i][ks], v_lo[st][ks], v_hi, idesc_o, ks > 0 ? 1u : first);
+        if (i == 1) umma_commit(smem_u32(&sh->v_empty[st])); // V_j consumed by both query tiles
+        if (j == F - 1) umma_commit(smem_u32(&sh->o_full[i]));
+#ifdef MG_PP_TIMING
+        if (j < 16) STAMP(sh->t_lane[j][i * 4 + 1]);
+#endif
+        e_known = false;
+        if (j + 1 < F) {
+          if (i == 0 && !k_known && !mbar_spin_or_abort(smem_u32(&sh->k_full[st ^ 1]), (uint32_t)(((j + 1) / kStages) & 1), abort_flag)) return false;
+#ifdef MG_PP_TIMING
+          if (j < 16) STAMP(sh->t_lane[j][i * 4 + 2]);
+#endif
+          issue_s(I, std::integral_constant<int, (st ^ 1)>{}, 0, kProbeAt);
+          if (i == 0) { // next batch: O'1(j), S1(j+1)
+            e_known = mbar_test_wait(smem_u32(&sh->e_full[1]), (uint32_t)(j & 1));
+          } else {      // next batch: O'0(j+1), S0(j+2); K_{j+2} comes into stage ST (K_{j+1} stands in when there is none)
+            bool const more = j + 2 < F;
+            uint32_t const seen = mbar_test_wait3(smem_u32(&sh->e_full[0]), (uint32_t)((j + 1) & 1),
+                                                  smem_u32(&sh->v_full[st ^ 1]), (uint32_t)(((j + 1) / kStages) & 1),
+                                                  smem_u32(&sh->k_full[more ? st : (st ^ 1)]), (uint32_t)((((more ? j + 2 : j + 1)) / kStages) & 1));
+            e_known = seen & 1; v_known = seen & 2; k_known = seen & 4;
+          }
+          issue_s(I, std::integral_constant<int, (st ^ 1)>{}, kProbeAt, kSteps);
+          if (i == 1) umma_commit(smem_u32(&sh->k_empty[st ^ 1])); // K_{j+1} consumed by both query tiles
+        }
+#ifdef MG_PP_TIMING
+        if (j < 16) STAMP(sh->t_lane[j][i * 4 + 3]);
+#endif
+        return true;
+      };
+      std::integral_constant<int, 0> const c0{};
+      std::integral_constant<int, 1> const c1{};
       bool ok = mbar_spin_or_abort(smem_u32(&sh->q_full), 0, abort_flag);
       STAMP(sh->t_block[2]);
       if (ok) ok = mbar_spin_or_abort(smem_u32(&sh->k_full[0]), 0, abort_flag);
       STAMP(sh->t_block[3]);
       if (ok) {
         tc_fence_after();
-        issue_s(0, 0, 0, kD / 16);
-        issue_s(1, 0, 0, kD / 16);
+        issue_s(c0, c0, 0, kSteps);
+        issue_s(c1, c0, 0, kSteps);
         umma_commit(smem_u32(&sh->k_empty[0]));
       }
       STAMP(sh->t_block[4]);
-      bool e_known = false, v_known = false, k_known = false; // barriers of the coming batches already seen complete
-      for (int j = 0; j < F && ok; j++) {
-#pragma unroll
-        for (int i = 0; i < 2; i++) {
-#ifdef MG_PP_TIMING
-          if (!e_known && j >= 4 && j < 8 && i == 0) {
-            long long ta = clock64();
-            bool first = mbar_test_wait(smem_u32(&sh->e_full[i]), (uint32_t)(j & 1));
-            long long tb2 = clock64();
-            int n = 0;
-            while (!first && n < 100000 && !mbar_test_wait(smem_u32(&sh->e_full[i]), (uint32_t)(j & 1))) n++;
-            long long tc = clock64();
-            sh->t_spin[j - 4][0] = ta; sh->t_spin[j - 4][1] = tb2; sh->t_spin[j - 4][2] = tc; sh->t_spin[j - 4][3] = n + (first ? 1000000 : 0);
-            e_known = true;
-          }
-#endif
-          if (!e_known) ok = mbar_spin_or_abort(smem_u32(&sh->e_full[i]), (uint32_t)(j & 1), abort_flag);
-#ifdef MG_PP_TIMING
-          if (j < 16) STAMP(sh->t_ewait[j][i]);
-#endif
-          if (ok && i == 0 && !v_known) ok = mbar_spin_or_abort(smem_u32(&sh->v_full[j % kStages]), (uint32_t)((j / kStages) & 1), abort_flag);
-          if (!ok) break;
-#ifdef MG_PP_TIMING
-          if (j < 16) STAMP(sh->t_lane[j][i * 4 + 0]);
-#endif
-          tc_fence_after();
-          issue_o(i, j);
-          if (i == 1) umma_commit(smem_u32(&sh->v_empty[j % kStages])); // V_j consumed by both query tiles
-          if (j == F - 1) umma_commit(smem_u32(&sh->o_full[i]));
-#ifdef MG_PP_TIMING
-          if (j < 16) STAMP(sh->t_lane[j][i * 4 + 1]);
-#endif
-          e_known = false;
-          if (j + 1 < F) {
-            if (i == 0 && !k_known) ok = mbar_spin_or_abort(smem_u32(&sh->k_full[(j + 1) % kStages]), (uint32_t)(((j + 1) / kStages) & 1), abort_flag);
-            if (!ok) break;
-#ifdef MG_PP_TIMING
-            if (j < 16) STAMP(sh->t_lane[j][i * 4 + 2]);
-#endif
-            issue_s(i, j + 1, 0, kProbeAt);
-            if (i == 0) { // next batch: O'1(j), S1(j+1)
-              e_known = mbar_test_wait(smem_u32(&sh->e_full[1]), (uint32_t)(j & 1));
-            } else {      // next batch: O'0(j+1), S0(j+2)
-              e_known = mbar_test_wait(smem_u32(&sh->e_full[0]), (uint32_t)((j + 1) & 1));
-              v_known = mbar_test_wait(smem_u32(&sh->v_full[(j + 1) % kStages]), (uint32_t)(((j + 1) / kStages) & 1));
-              k_known = j + 2 < F && mbar_test_wait(smem_u32(&sh->k_full[(j + 2) % kStages]), (uint32_t)(((j + 2) / kStages) & 1));
-            }
-            issue_s(i, j + 1, kProbeAt, kD / 16);
-            if (i == 1) umma_commit(smem_u32(&sh->k_empty[(j + 1) % kStages])); // K_{j+1} consumed by both query tiles
-          }
-#ifdef MG_PP_TIMING
-          if (j < 16) STAMP(sh->t_lane[j][i * 4 + 3]);
-#endif
-        }
+      for (int j = 0; j < F && ok; j += 2) {
+        ok = batch(c0, c0, j) && batch(c1, c0, j);
+        if (ok && j + 1 < F) ok = batch(c0, c1, j + 1) && batch(c1, c1, j + 1);
       }
       STAMP(sh->t_block[5]);
     }
@@ -288,7 +288,6 @@ attn_rows_pp_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
 #ifdef MG_PP_TIMING
       bool const stamps = lane == 0 && wi == 0 && j < 16;
       if (stamps) STAMP(sh->t_exp[i][j][0]);
-      if (lane == 0 && j == 5) STAMP(sh->t_arrive[i][wi][0]);
 #endif
       tc_fence_after();
       uint32_t flat[32]; // this thread's 64 values as 16-bit pairs
@@ -319,7 +318,6 @@ attn_rows_pp_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
       mbar_arrive(smem_u32(&sh->e_full[i]));
 #ifdef MG_PP_TIMING
       if (stamps) STAMP(sh->t_exp[i][j][3]);
-      if (lane == 0 && j == 5) STAMP(sh->t_arrive[i][wi][1]);
 #endif
     }
     // the two halves of a row add up their sums (named barrier per query tile, reached whether or not a wait gave up)
@@ -374,9 +372,6 @@ attn_rows_pp_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
            sh->t_block[6] - tb, sh->t_block[7] - tb, sh->t_block[8] - tb);
     for (int j = 4; j < 8 && j < F - 1; j++) {
       long long const *l = sh->t_lane[j];
-      printf("  j=%d spin: first poll issued %lld returned %lld, then %lld polls until %lld\n", j, sh->t_spin[j - 4][0] - tb, sh->t_spin[j - 4][1] - tb, sh->t_spin[j - 4][3], sh->t_spin[j - 4][2] - tb);
-      printf("  j=%d e-wait done %lld / %lld\n", j, sh->t_ewait[j][0] - tb, sh->t_ewait[j][1] - tb);
-      if (j == 5) for (int i = 0; i < 2; i++) for (int w = 0; w < 8; w++) printf("      tile %d warp %d: s_full seen %lld arrive %lld\n", i, w, sh->t_arrive[i][w][0] - tb, sh->t_arrive[i][w][1] - tb);
       printf("  j=%d lane: waits0 %lld O0 %lld k %lld S0 %lld | waits1 %lld O1 %lld - %lld S1 %lld\n", j, l[0] - tb, l[1] - tb, l[2] - tb,
              l[3] - tb, l[4] - tb, l[5] - tb, l[6] - tb, l[7] - tb);
       for (int i = 0; i < 2; i++)

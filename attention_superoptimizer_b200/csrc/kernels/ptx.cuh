@@ -44,6 +44,20 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
                : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
   return ok != 0;
 }
+// Three phases tested at once: bit n of the result says that phase n is complete.  The tests overlap, so the thread
+// pays one round trip to shared memory instead of three.
+__device__ __forceinline__ uint32_t mbar_test_wait3(uint32_t bar0, uint32_t parity0, uint32_t bar1, uint32_t parity1,
+                                                    uint32_t bar2, uint32_t parity2) {
+  uint32_t a, b, c;
+  asm volatile("{\n\t.reg .pred p, q, r;\n\t"
+               "mbarrier.test_wait.parity.shared::cta.b64 p, [%3], %4;\n\t"
+               "mbarrier.test_wait.parity.shared::cta.b64 q, [%5], %6;\n\t"
+               "mbarrier.test_wait.parity.shared::cta.b64 r, [%7], %8;\n\t"
+               "selp.u32 %0, 1, 0, p;\n\tselp.u32 %1, 2, 0, q;\n\tselp.u32 %2, 4, 0, r;\n\t}"
+               : "=r"(a), "=r"(b), "=r"(c)
+               : "r"(bar0), "r"(parity0), "r"(bar1), "r"(parity1), "r"(bar2), "r"(parity2) : "memory");
+  return a | b | c;
+}
 // Bounded wait: false after `limit` polls.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int limit = kWaitLimit) {
   for (int i = 0; i < limit; i++)

@@ -14,6 +14,7 @@ using ptx::mbar_expect_tx;
 using ptx::mbar_arrive;
 using ptx::mbar_try_wait;
 using ptx::mbar_test_wait;
+using ptx::mbar_test_wait3;
 using ptx::mbar_spin_or_abort;
 using ptx::tma_load_3d;
 using ptx::fence_proxy_async_smem;
@@ -55,6 +56,23 @@ __device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, ui
   asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
                "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
                ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// The same two with the descriptors given as 32-bit halves: a stage, a tile or a contraction step only moves the
+// start-address field in the low word (shared-memory addresses stay below 2^18, so there is no carry out of the
+// field), and the issuing lane, whose instruction stream is what feeds the tensor pipe, pays a 32-bit add per operand.
+__device__ __forceinline__ void umma_f16_halves(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
+                                                uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %6, 0;\n\t"
+               "mov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"
+               "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}"
+               ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_f16_ts_halves(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
+                                                   uint32_t accumulate) {
+  asm volatile("{\n\t.reg .pred p;\n\t.reg .b64 db;\n\tsetp.ne.b32 p, %5, 0;\n\t"
+               "mov.b64 db, {%2, %3};\n\t"
+               "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}"
+               ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate) : "memory");
 }
 // the mbarrier gets one arrival when every MMA issued so far by this thread has completed
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
