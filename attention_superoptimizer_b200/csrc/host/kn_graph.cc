@@ -755,8 +755,7 @@ int KNCustomizedOp::launch_sets(bool fp, int num_sets, void const *const *in, lo
     mgd_attn_rows rp;
     mg::match_attn_rows(program_, &rp, nullptr);
     rp.data_type = dt;
-    record_anything(stream);
-    return finish(mgd_launch_attn_rows_float(&rp, in[0], in[1], in[2], out[o_output_], out[1 - o_output_], stream));
+    return launch_rows(&rp, in, out[o_output_], out[1 - o_output_], nullptr, stream);
   }
   if (kernel == mg::KERNEL_ATTN_MERGE) {
     mgd_attn_merge mp;
@@ -856,6 +855,24 @@ int KNCustomizedOp::launch_split(bool fp, int num_sets, void const *const *in, l
   return finish(st);
 }
 
+// Dense attention launch (with the division that follows fused in when `o_div` is given).  Like the split-KV launch
+// it lets the next kernel of the stream start while it drains, and reads its inputs early when the library knows that
+// the kernel in front of it did not write them.
+int KNCustomizedOp::launch_rows(mgd_attn_rows const *rp, void const *const *in, void *o_acc, void *r_acc, void *o_div,
+                                void *stream) {
+  size_t const q_bytes = (size_t)rp->heads * rp->seq_q * rp->d * 2, kv_bytes = (size_t)rp->heads * rp->kv_len * rp->d * 2;
+  std::vector<Range> ins = {range_of(in[0], q_bytes), range_of(in[1], kv_bytes), range_of(in[2], kv_bytes)};
+  std::vector<Range> outs = {range_of(o_acc, q_bytes), range_of(r_acc, (size_t)rp->heads * rp->seq_q * 2)};
+  if (o_div) outs.push_back(range_of(o_div, q_bytes));
+  int32_t serial = 0;
+  mgd_get_option(MGD_OPT_ATTN_DEPENDENT_LAUNCH, &serial); // 1 = plain stream order (no programmatic dependent launch)
+  int32_t const overlap = serial == 1 ? 0 : (1 | (inputs_untouched(stream, ins) ? 2 : 0));
+  int const st = mgd_launch_attn_rows_float_overlapped(rp, in[0], in[1], in[2], o_acc, r_acc, o_div, overlap, stream);
+  if (st == MG_OK) record_outputs(stream, outs);
+  else record_anything(stream);
+  return finish(st);
+}
+
 bool KNCustomizedOp::can_fuse_with(KNOperator *next, bool fp) {
   if (DeviceMemoryManager::get_instance()->specialise < 2 || !next) return false;
   if (next->op_type != KN_CUSTOMIZED_OP || !ensure_lowered()) return false;
@@ -904,8 +921,7 @@ int KNCustomizedOp::launch_fused_sets(KNCustomizedOp *merge, bool fp, int num_se
     mgd_attn_rows rp;
     mg::match_attn_rows(program_, &rp, nullptr);
     rp.data_type = (int)input_tensors[0].data_type;
-    record_anything(stream);
-    return finish(mgd_launch_attn_rows_float_ex(&rp, in[0], in[1], in[2], out[o_output_], out[1 - o_output_], merged_out, stream));
+    return launch_rows(&rp, in, out[o_output_], out[1 - o_output_], merged_out, stream);
   }
   void *o[2] = {out[o_output_], out[1 - o_output_]};
   long long os[2] = {out_stride[o_output_], out_stride[1 - o_output_]};

@@ -57,6 +57,7 @@ struct Params {
   void *o_acc, *r_acc, *o_div;
   int32_t *status;
   int heads, seq_q, forloop;
+  int overlap; // bit 0: launched with programmatic stream serialisation; bit 1: Q, K, V were not written by the kernel before
 };
 
 struct Shared {
@@ -90,6 +91,14 @@ attn_rows_pp_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
   int const pairs = p.seq_q / (2 * kTile);
   int const head = blockIdx.x / pairs, q0 = (blockIdx.x % pairs) * 2 * kTile;
   int const F = p.forloop;
+
+  // Programmatic dependent launch (both are no-ops in a plain launch).  The kernel that follows may be scheduled as
+  // soon as every block of this one is running - with 1.73 blocks per SM in the prefill configuration its first
+  // blocks fill the SMs this kernel's second round leaves idle.  This kernel in turn reads Q, K and V before the
+  // kernel in front of it has finished only when that kernel did not write them, and writes nothing to global
+  // memory before it has finished (the exp warps wait in front of their stores).
+  if (!(p.overlap & 2)) ptx::grid_dependency_wait();
+  ptx::grid_launch_dependents();
 
   if (tid == 0) {
     STAMP(sh->t_block[0]);
@@ -328,6 +337,7 @@ attn_rows_pp_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
     if (tid == 64) STAMP(sh->t_block[6]);
     if (ok) ok = mbar_wait(smem_u32(&sh->o_full[i]), 0, abort_flag);
     if (tid == 64) STAMP(sh->t_block[7]);
+    ptx::grid_dependency_wait(); // the kernel in front may still be writing these outputs (a replay of the same graph)
     if (ok) {
       tc_fence_after();
       size_t const row_off = ((size_t)head * p.seq_q + q0 + i * kTile + row) * kD + half * 64;
@@ -388,6 +398,7 @@ attn_rows_pp_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
       for (int n = 0; n < 20000 && !mbar_try_wait(smem_u32(&sh->v_full[s]), 0) && !mbar_try_wait(smem_u32(&sh->v_full[s]), 1); n++) {
       }
     }
+    ptx::grid_dependency_wait();
     atomicExch(p.status, 4);
   }
   __syncthreads();
@@ -423,7 +434,7 @@ bool supported(mgd_attn_rows const *p) {
 }
 
 int launch(mgd_attn_rows const *p, void const *q, void const *k, void const *v, void *o_acc, void *r_acc, void *o_div,
-           void *stream) {
+           int overlap, void *stream) {
   if (!supported(p)) return set_error(MG_ERR_UNSUPPORTED, "dense attention (two query tiles per block): shape not supported");
   bool const k_kv = p->k_layout == MG_DMEM_COLUMN_MAJOR, v_kv = p->v_layout == MG_DMEM_ROW_MAJOR;
   CUtensorMap qm, km, vm;
@@ -436,6 +447,7 @@ int launch(mgd_attn_rows const *p, void const *q, void const *k, void const *v, 
   a.status = device_error_word();
   if (!a.status) return set_error(MG_ERR_CUDA, "cannot allocate the device status word");
   a.heads = p->heads; a.seq_q = p->seq_q; a.forloop = p->forloop_range;
+  a.overlap = (overlap & 1) ? (overlap & 3) : 0;
   size_t const smem = 1024 + (size_t)(2 + 2 * kStages) * kOperand + sizeof(Shared) + 64;
   unsigned const blocks = (unsigned)(p->heads * (p->seq_q / (2 * kTile)));
   bool const bf16 = p->data_type == MG_DT_BFLOAT16;
@@ -452,7 +464,19 @@ int launch(mgd_attn_rows const *p, void const *q, void const *k, void const *v, 
       return check_launch("cudaFuncSetAttribute(attn_rows_pp_kernel)");
     configured[which] = true;
   }
-  kernels[which]<<<blocks, kThreads, smem, (cudaStream_t)stream>>>(qm, km, vm, a);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(blocks, 1, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = (cudaStream_t)stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  if (a.overlap & 1) {
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+  }
+  cudaLaunchKernelEx(&cfg, kernels[which], qm, km, vm, a);
   return check_launch("attn_rows_pp_kernel");
 }
 

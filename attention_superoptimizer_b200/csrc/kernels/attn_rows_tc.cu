@@ -456,7 +456,7 @@ namespace mgk {
 namespace pp { // attn_rows_pp.cu: two query tiles per block, all K / V layouts
 bool supported(mgd_attn_rows const *p);
 int launch(mgd_attn_rows const *p, void const *q, void const *k, void const *v, void *o_acc, void *r_acc, void *o_div,
-           void *stream);
+           int overlap, void *stream);
 } // namespace pp
 } // namespace mgk
 
@@ -482,8 +482,13 @@ int mgd_launch_attn_rows_float(const mgd_attn_rows *p, const void *q, const void
 
 int mgd_launch_attn_rows_float_ex(const mgd_attn_rows *p, const void *q, const void *k, const void *v, void *o_acc,
                                   void *r_acc, void *o_div, void *stream) {
+  return mgd_launch_attn_rows_float_overlapped(p, q, k, v, o_acc, r_acc, o_div, 0, stream);
+}
+
+int mgd_launch_attn_rows_float_overlapped(const mgd_attn_rows *p, const void *q, const void *k, const void *v, void *o_acc,
+                                          void *r_acc, void *o_div, int32_t overlap, void *stream) {
   if (!q || !k || !v || !o_acc || !r_acc) return set_error(MG_ERR_INVALID_ARGUMENT, "dense attention: null tensor");
-  if (use_two_tile_kernel(p)) return pp::launch(p, q, k, v, o_acc, r_acc, o_div, stream);
+  if (use_two_tile_kernel(p)) return pp::launch(p, q, k, v, o_acc, r_acc, o_div, overlap, stream);
   if (!tc::rows_supported(p)) return set_error(MG_ERR_UNSUPPORTED, "dense attention: shape or layout not supported");
   CUtensorMap km, vm;
   bool ok = tc::make_map(&km, k, p->heads, p->kv_len, tc::kD) && tc::make_map(&vm, v, p->heads, tc::kD, p->kv_len);

@@ -79,6 +79,7 @@ private:
   };
   int launch_split(bool fingerprint_mode, int num_sets, void const *const *in, long long const *in_stride,
                    void *const *out, long long const *out_stride, FusedMerge const *merge, void *stream);
+  int launch_rows(struct mgd_attn_rows const *rows, void const *const *in, void *o_acc, void *r_acc, void *o_div, void *stream);
   int launch_sets(bool fingerprint_mode, int num_sets, void const *const *in, long long const *in_stride,
                   void *const *out, long long const *out_stride, void *stream);
   int *tickets_ = nullptr; // per-head "last block done" counters of the fused launch (arena scratch)

@@ -164,6 +164,13 @@ int mgd_launch_attn_rows_float(const mgd_attn_rows *p, const void *q, const void
  * o_div[heads, seq_q, d] = O_acc / R, from the fp32 accumulators; NULL = none */
 int mgd_launch_attn_rows_float_ex(const mgd_attn_rows *p, const void *q, const void *k, const void *v, void *o_acc,
                                   void *r_acc, void *o_div, void *stream);
+/* the same with the `overlap` bits of mgd_attn_launch_opts (bits 0 and 1; the others are ignored): bit 0 launches with
+ * programmatic stream serialisation, so that the NEXT kernel of the stream may start on the SMs this one leaves idle in
+ * its last round of blocks; bit 1 says that the kernel in front of this one did not write Q, K or V, so this one may
+ * read them before that kernel has finished.  Global memory is only written after it has.  The one-tile-per-block
+ * kernel (query lengths that are not a multiple of 256) ignores the bits. */
+int mgd_launch_attn_rows_float_overlapped(const mgd_attn_rows *p, const void *q, const void *k, const void *v, void *o_acc,
+                                          void *r_acc, void *o_div, int32_t overlap, void *stream);
 
 /* Allocation-free variant of the fused decode launch (split-KV partials + cross-split merge in one kernel).
  * It has no counterpart in the reference.
