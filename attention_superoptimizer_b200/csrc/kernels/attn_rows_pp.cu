@@ -78,7 +78,8 @@ __device__ __forceinline__ uint32_t mn_major_step(int ks) { return (uint32_t)((k
 template <bool BF16, bool K_KV, bool V_KV>
 __global__ void __launch_bounds__(kThreads)
 attn_rows_pp_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
-                    const __grid_constant__ CUtensorMap v_map, const __grid_constant__ Params p) {
+                    const __grid_constant__ CUtensorMap v_map, const __grid_constant__ CUtensorMap o_map,
+                    const __grid_constant__ CUtensorMap d_map, const __grid_constant__ Params p) {
   extern __shared__ unsigned char smem_dyn[];
   unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
   // [Q0 32 KB][Q1 32 KB][stage 0: K 32 KB, V 32 KB][stage 1][barriers]
@@ -106,6 +107,8 @@ attn_rows_pp_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
     asm volatile("prefetch.tensormap [%0];" ::"l"(&q_map) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&k_map) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&v_map) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&o_map) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&d_map) : "memory");
     mbar_init(smem_u32(&sh->q_full), 1);
     for (int s = 0; s < kStages; s++) {
       mbar_init(smem_u32(&sh->k_full[s]), 1);
@@ -338,35 +341,53 @@ attn_rows_pp_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
     if (ok) ok = mbar_wait(smem_u32(&sh->o_full[i]), 0, abort_flag);
     if (tid == 64) STAMP(sh->t_block[7]);
     ptx::grid_dependency_wait(); // the kernel in front may still be writing these outputs (a replay of the same graph)
+    // O' (and O'/R') leave through shared memory: a thread owns half a row, so direct stores would put 16 bytes into
+    // each of 32 rows per instruction; staged as [128 rows][64 columns] boxes (128-byte swizzle, one 128-byte row of a
+    // box per thread) they go out as four TMA stores per tile.  Tile 0 stages into the Q buffers - both last read by
+    // S1(F-1), which the pipe finished before O'0(F-1) - and tile 1 into ring stage 0, free once every MMA is done.
+    unsigned char *const stage = smem + (i == 0 ? 0 : 2 * kOperand); // [O' | O'/R'] x [column half] boxes of 16 KB
     if (ok) {
       tc_fence_after();
-      size_t const row_off = ((size_t)head * p.seq_q + q0 + i * kTile + row) * kD + half * 64;
-      uint16_t *o_row = static_cast<uint16_t *>(p.o_acc) + row_off;
-      uint16_t *d_row = p.o_div ? static_cast<uint16_t *>(p.o_div) + row_off : nullptr;
       float const inv = 1.0f / total;
+      uint32_t const row_at = (uint32_t)(half * kBox + row * 128);
 #pragma unroll
       for (int c = 0; c < 2; c++) {
         uint32_t v[32];
         tmem_ld32(tmem + 256 + (uint32_t)(i * kTile) + lane_base + (uint32_t)(half * 64 + c * 32), v);
 #pragma unroll
         for (int q = 0; q < 4; q++) {
+          uint32_t const at = row_at + (uint32_t)((((c * 4 + q) ^ (row & 7)) << 4));
           uint4 out;
           out.x = pack2<BF16>(__uint_as_float(v[8 * q]), __uint_as_float(v[8 * q + 1]));
           out.y = pack2<BF16>(__uint_as_float(v[8 * q + 2]), __uint_as_float(v[8 * q + 3]));
           out.z = pack2<BF16>(__uint_as_float(v[8 * q + 4]), __uint_as_float(v[8 * q + 5]));
           out.w = pack2<BF16>(__uint_as_float(v[8 * q + 6]), __uint_as_float(v[8 * q + 7]));
-          *reinterpret_cast<uint4 *>(o_row + c * 32 + q * 8) = out;
-          if (d_row) {
+          *reinterpret_cast<uint4 *>(stage + at) = out;
+          if (p.o_div) {
             out.x = pack2<BF16>(__uint_as_float(v[8 * q]) * inv, __uint_as_float(v[8 * q + 1]) * inv);
             out.y = pack2<BF16>(__uint_as_float(v[8 * q + 2]) * inv, __uint_as_float(v[8 * q + 3]) * inv);
             out.z = pack2<BF16>(__uint_as_float(v[8 * q + 4]) * inv, __uint_as_float(v[8 * q + 5]) * inv);
             out.w = pack2<BF16>(__uint_as_float(v[8 * q + 6]) * inv, __uint_as_float(v[8 * q + 7]) * inv);
-            *reinterpret_cast<uint4 *>(d_row + c * 32 + q * 8) = out;
+            *reinterpret_cast<uint4 *>(stage + kOperand + at) = out;
           }
         }
       }
+      fence_proxy_async_smem(); // the staged boxes are read by the TMA engine
       if (half == 0)
         static_cast<uint16_t *>(p.r_acc)[(size_t)head * p.seq_q + q0 + i * kTile + row] = (uint16_t)(pack2<BF16>(total, 0.f) & 0xFFFFu);
+    }
+    if (i == 0) asm volatile("bar.sync 1, 256;" ::: "memory");
+    else asm volatile("bar.sync 2, 256;" ::: "memory");
+    if (wi == 0 && lane == 0 && ok && !*abort_flag) {
+      uint32_t const src = smem_u32(stage);
+      int const r0 = q0 + i * kTile;
+      ptx::tma_store_3d(&o_map, src, 0, r0, head);
+      ptx::tma_store_3d(&o_map, src + kBox, 64, r0, head);
+      if (p.o_div) {
+        ptx::tma_store_3d(&d_map, src + kOperand, 0, r0, head);
+        ptx::tma_store_3d(&d_map, src + kOperand + kBox, 64, r0, head);
+      }
+      ptx::tma_store_commit_and_wait_read(); // the boxes must stay until the engine has read them
     }
   }
 
@@ -437,8 +458,9 @@ int launch(mgd_attn_rows const *p, void const *q, void const *k, void const *v, 
            int overlap, void *stream) {
   if (!supported(p)) return set_error(MG_ERR_UNSUPPORTED, "dense attention (two query tiles per block): shape not supported");
   bool const k_kv = p->k_layout == MG_DMEM_COLUMN_MAJOR, v_kv = p->v_layout == MG_DMEM_ROW_MAJOR;
-  CUtensorMap qm, km, vm;
-  bool ok = make_map(&qm, q, p->heads, p->seq_q, kD);
+  CUtensorMap qm, km, vm, om, dm;
+  bool ok = make_map(&qm, q, p->heads, p->seq_q, kD) && make_map(&om, o_acc, p->heads, p->seq_q, kD) &&
+            make_map(&dm, o_div ? o_div : o_acc, p->heads, p->seq_q, kD);
   ok = ok && (k_kv ? make_map(&km, k, p->heads, p->kv_len, kD) : make_map(&km, k, p->heads, kD, p->kv_len));
   ok = ok && (v_kv ? make_map(&vm, v, p->heads, p->kv_len, kD) : make_map(&vm, v, p->heads, kD, p->kv_len));
   if (!ok) return set_error(MG_ERR_CUDA, "dense attention: cuTensorMapEncodeTiled failed");
@@ -451,7 +473,7 @@ int launch(mgd_attn_rows const *p, void const *q, void const *k, void const *v, 
   size_t const smem = 1024 + (size_t)(2 + 2 * kStages) * kOperand + sizeof(Shared) + 64;
   unsigned const blocks = (unsigned)(p->heads * (p->seq_q / (2 * kTile)));
   bool const bf16 = p->data_type == MG_DT_BFLOAT16;
-  using Kernel = void (*)(CUtensorMap, CUtensorMap, CUtensorMap, Params);
+  using Kernel = void (*)(CUtensorMap, CUtensorMap, CUtensorMap, CUtensorMap, CUtensorMap, Params);
   static Kernel const kernels[8] = {
       attn_rows_pp_kernel<false, false, false>, attn_rows_pp_kernel<false, false, true>,
       attn_rows_pp_kernel<false, true, false>,  attn_rows_pp_kernel<false, true, true>,
@@ -476,7 +498,7 @@ int launch(mgd_attn_rows const *p, void const *q, void const *k, void const *v, 
     cfg.attrs = attr;
     cfg.numAttrs = 1;
   }
-  cudaLaunchKernelEx(&cfg, kernels[which], qm, km, vm, a);
+  cudaLaunchKernelEx(&cfg, kernels[which], qm, km, vm, om, dm, a);
   return check_launch("attn_rows_pp_kernel");
 }
 

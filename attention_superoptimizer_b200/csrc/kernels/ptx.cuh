@@ -97,6 +97,16 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, CUtensorMap const *map
   asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
                ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
 }
+// TMA tile store from shared memory (same alignment rule; never at a negative coordinate), and the wait that lets the
+// issuing thread reuse or give up the shared-memory source.
+__device__ __forceinline__ void tma_store_3d(CUtensorMap const *map, uint32_t src, int c0, int c1, int c2) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+               ::"l"(map), "r"(src), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+__device__ __forceinline__ void tma_store_commit_and_wait_read() {
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+  asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
 __device__ __forceinline__ void prefetch_tensormap(CUtensorMap const *map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }

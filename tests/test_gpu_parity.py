@@ -523,6 +523,55 @@ def test_float_prefill_tensor_core_kernel(runtime, shape, layouts, dtype):
         assert np.array_equal(final, again)
 
 
+def test_prefill_calls_back_to_back_on_one_stream(runtime):
+    """Dense attention launches let the next kernel of the stream start while they drain, and read their inputs before
+    the kernel in front has finished when the library knows that kernel did not write them.  A stream of calls - two
+    graphs taking turns, each several times, nothing synchronised in between - leaves in every graph what one call
+    alone leaves; and a call whose input is the output of the call in front waits for it."""
+    import torch
+    H, SQ, L, D = 4, 512, 1024, 128
+    runtime.set_max_smem(BIG)
+    runtime.set_specialisation(2)
+    rng = np.random.default_rng(77)
+    stream = torch.cuda.Stream()
+    sh = stream.cuda_stream
+    with mg.PyGraph(runtime) as ga, mg.PyGraph(runtime) as gb:
+        built = []
+        for g in (ga, gb):
+            ins, acc, out, plans = build_prefill(g, H, SQ, D, L, mg.bfloat16)
+            (q, k, v), mem = float_inputs(rng, H, SQ, D, L, mg.DmemColumnMajor, mg.DmemColumnMajor, mg.bfloat16)
+            for t, a in zip(ins, mem):
+                t.upload_data(to_bits(a, mg.bfloat16))
+            g.run()
+            built.append((ins, out, from_bits(out[0].download_data(), mg.bfloat16).copy(), mem))
+        for _ in range(6):
+            ga.run(stream=sh, sync=False)
+            gb.run(stream=sh, sync=False)
+        stream.synchronize()
+        mg.synchronize()
+        for ins, out, alone, _ in built:
+            assert np.array_equal(from_bits(out[0].download_data(), mg.bfloat16), alone)
+        # graph B takes its Q from graph A's output: B's loads must wait for A although B is launched to overlap it
+        (qa, _, _), out_a, _, mem_a = built[0]
+        _, out_b, _, _ = built[1]
+        gb.rebind_input(0, data_ptr=out_a[0].pod.data_ptr)
+        ga.run()
+        gb.run()
+        stale = from_bits(out_b[0].download_data(), mg.bfloat16).copy()
+        q2 = float_inputs(rng, H, SQ, D, L, mg.DmemColumnMajor, mg.DmemColumnMajor, mg.bfloat16)[1][0]
+        qa.upload_data(to_bits(q2, mg.bfloat16))
+        for _ in range(3):
+            ga.run(stream=sh, sync=False)
+            gb.run(stream=sh, sync=False)
+        stream.synchronize()
+        mg.synchronize()
+        chained = from_bits(out_b[0].download_data(), mg.bfloat16).copy()
+        ga.run()
+        gb.run()
+        assert np.array_equal(chained, from_bits(out_b[0].download_data(), mg.bfloat16))
+        assert not np.array_equal(chained, stale)
+
+
 def test_prefill_fingerprint_uses_interpreter(runtime):
     """The same dense graph in fingerprint mode (128 x 128 x 128 mod-PQ contractions) stays bit-exact."""
     H, SQ, D, L = 1, 128, 128, 256
