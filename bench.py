@@ -757,12 +757,17 @@ def measure_other_configs(mg, rt, stream, timed, peaks, only=None, quick=False, 
         us_single = replay_us(graphs_runner([g]), 1)
         flops = 4.0 * H * SQ * L * d
         tf = flops / us / 1e6
+        sustained = peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"])
         out["prefill_c4"] = {"us_per_call": round(us, 2), "us_single_call": round(us_single, 2),
                              "tflops_single_call": round(flops / us_single / 1e6, 1), "tflops": round(tf, 1),
-                             "frac_of_bf16_peak": round(tf / peaks["bf16_tflops"], 4), "flops": flops,
+                             "frac_of_bf16_peak": round(tf / peaks["bf16_tflops"], 4),
+                             "frac_of_sustained_bf16_peak": round(tf / sustained, 4), "flops": flops,
+                             # timed inside a long loop (0.3 s of replays, then 800 calls) at the end of a long run: the
+                             # GPU sits at its power cap, which is what the sustained cuBLAS figure was measured under
                              "roofline": {"bound": "tensor", "kernel": "attn_rows_pp_kernel<bf16>", "achieved": round(tf, 1),
-                                          "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": round(tf / peaks["bf16_tflops"], 4),
-                                          "frac_of_sustained_peak": round(tf / peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"]), 4),
+                                          "peak": sustained, "peak_kind": "sustained (kernel timed inside a long loop)",
+                                          "unit": "TFLOP/s", "frac": round(tf / sustained, 4),
+                                          "frac_of_burst_peak": round(tf / peaks["bf16_tflops"], 4),
                                           "flops_per_call": flops},
                              "kernel": g.customized_info(3)["kernel_float"], "dtype": "bf16",
                              "note": "both customized ops in one launch (division fused into the tcgen05 kernel's epilogue); us_per_call: calls back "
