@@ -61,7 +61,7 @@ struct Params {
 };
 
 struct Shared {
-  uint64_t q_full, k_full[kStages], k_empty[kStages], v_full[kStages], v_empty[kStages], s_full[2], e_full[2], o_full[2];
+  uint64_t q_full[2], k_full[kStages], k_empty[kStages], v_full[kStages], v_empty[kStages], s_full[2], e_full[2], o_full[2];
   uint32_t tmem_base;
   int abort_flag;
   float row_sums[2][2][kTile]; // [query tile][column half][row]
@@ -109,7 +109,8 @@ attn_rows_pp_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
     asm volatile("prefetch.tensormap [%0];" ::"l"(&v_map) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&o_map) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&d_map) : "memory");
-    mbar_init(smem_u32(&sh->q_full), 1);
+    mbar_init(smem_u32(&sh->q_full[0]), 1);
+    mbar_init(smem_u32(&sh->q_full[1]), 1);
     for (int s = 0; s < kStages; s++) {
       mbar_init(smem_u32(&sh->k_full[s]), 1);
       mbar_init(smem_u32(&sh->k_empty[s]), 1);
@@ -136,12 +137,14 @@ attn_rows_pp_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
     // K and V tiles have rings of their own: the slot of K_j is free once S1(j) has run, the slot of V_j once O'1(j)
     // has, and both are next needed a whole round of MMAs later (K_{j+2} by S0(j+2), V_{j+2} by O'0(j+2)).
     if (lane == 0) {
-      uint32_t const full = smem_u32(&sh->q_full);
-      mbar_expect_tx(full, 2 * kOperand);
-      for (int i = 0; i < 2; i++) { // Q memory [heads][seq_q][d]: rows = query rows, two boxes over d
+      // Q memory [heads][seq_q][d]: rows = query rows, two boxes over d.  The first S needs Q0 and K_0 only, so these
+      // two are asked for first: a round of blocks starts with 148 blocks fetching at once
+      auto load_q = [&](int i) {
+        uint32_t const full = smem_u32(&sh->q_full[i]);
+        mbar_expect_tx(full, kOperand);
         tma_load_3d(q_smem + (uint32_t)(i * kOperand), &q_map, full, 0, q0 + i * kTile, head);
         tma_load_3d(q_smem + (uint32_t)(i * kOperand + kBox), &q_map, full, 64, q0 + i * kTile, head);
-      }
+      };
       auto load_k = [&](int j) {
         uint32_t const bar = smem_u32(&sh->k_full[j % kStages]), dst = ring + (uint32_t)((j % kStages) * 2 * kOperand);
         int const kv0 = j * kTile;
@@ -166,7 +169,9 @@ attn_rows_pp_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
           tma_load_3d(dst + kBox, &v_map, bar, kv0 + 64, 0, head);
         }
       };
+      load_q(0);
       load_k(0);
+      load_q(1);
       load_v(0);
       if (F > 1) load_k(1);
       for (int t = 1; t < F; t++) { // V_t, then K_{t+1}: the order in which their slots come free
@@ -265,13 +270,17 @@ attn_rows_pp_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
       };
       std::integral_constant<int, 0> const c0{};
       std::integral_constant<int, 1> const c1{};
-      bool ok = mbar_spin_or_abort(smem_u32(&sh->q_full), 0, abort_flag);
+      bool ok = mbar_spin_or_abort(smem_u32(&sh->q_full[0]), 0, abort_flag);
       STAMP(sh->t_block[2]);
       if (ok) ok = mbar_spin_or_abort(smem_u32(&sh->k_full[0]), 0, abort_flag);
       STAMP(sh->t_block[3]);
       if (ok) {
         tc_fence_after();
         issue_s(c0, c0, 0, kSteps);
+        ok = mbar_spin_or_abort(smem_u32(&sh->q_full[1]), 0, abort_flag);
+      }
+      if (ok) {
+        tc_fence_after();
         issue_s(c1, c0, 0, kSteps);
         umma_commit(smem_u32(&sh->k_empty[0]));
       }

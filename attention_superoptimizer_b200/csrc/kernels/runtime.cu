@@ -29,17 +29,72 @@ int check_launch(char const *name) {
 static std::atomic<int32_t> g_options[MGD_OPT_COUNT];
 int option(int key) { return key >= 0 && key < MGD_OPT_COUNT ? g_options[key].load(std::memory_order_relaxed) : 0; }
 
+// cuTensorMapEncodeTiled is a pure function of its arguments and costs about a microsecond of host time; a launch
+// encodes two to five maps.  Callers get a wrapper that remembers the last few results per thread, so that a host
+// which calls again and again on the same buffers (a serving loop on a resident KV cache) pays for the encoding once.
+namespace {
+TensorMapEncodeFn g_driver_encode = nullptr;
+struct MapKey {
+  int32_t data_type, interleave, swizzle, l2_promotion, oob_fill;
+  uint32_t rank;
+  void *base;
+  uint64_t dims[5], strides[4];
+  uint32_t box[5], element_strides[5];
+};
+struct MapEntry {
+  MapKey key;
+  CUtensorMap map;
+  bool used;
+};
+constexpr int kCachedMaps = 16;
+
+CUresult encode_tiled_remembered(CUtensorMap *map, CUtensorMapDataType data_type, cuuint32_t rank, void *base,
+                                 cuuint64_t const *dims, cuuint64_t const *strides, cuuint32_t const *box,
+                                 cuuint32_t const *element_strides, CUtensorMapInterleave interleave,
+                                 CUtensorMapSwizzle swizzle, CUtensorMapL2promotion l2_promotion,
+                                 CUtensorMapFloatOOBfill oob_fill) {
+  if (rank < 1 || rank > 5)
+    return g_driver_encode(map, data_type, rank, base, dims, strides, box, element_strides, interleave, swizzle, l2_promotion, oob_fill);
+  MapKey key;
+  std::memset(&key, 0, sizeof(key));
+  key.data_type = (int32_t)data_type; key.interleave = (int32_t)interleave; key.swizzle = (int32_t)swizzle;
+  key.l2_promotion = (int32_t)l2_promotion; key.oob_fill = (int32_t)oob_fill;
+  key.rank = rank;
+  key.base = base;
+  for (uint32_t i = 0; i < rank; i++) {
+    key.dims[i] = dims[i];
+    key.box[i] = box[i];
+    key.element_strides[i] = element_strides[i];
+    if (i + 1 < rank) key.strides[i] = strides[i];
+  }
+  thread_local MapEntry table[kCachedMaps];
+  thread_local unsigned next = 0;
+  for (MapEntry const &e : table)
+    if (e.used && std::memcmp(&e.key, &key, sizeof(key)) == 0) {
+      *map = e.map;
+      return CUDA_SUCCESS;
+    }
+  CUresult const r = g_driver_encode(map, data_type, rank, base, dims, strides, box, element_strides, interleave, swizzle, l2_promotion, oob_fill);
+  if (r == CUDA_SUCCESS) {
+    MapEntry &e = table[next++ % kCachedMaps];
+    e.key = key;
+    e.map = *map;
+    e.used = true;
+  }
+  return r;
+}
+} // namespace
+
 TensorMapEncodeFn tensor_map_encoder() {
-  static TensorMapEncodeFn fn = nullptr;
   static std::once_flag once;
   std::call_once(once, [] {
     void *sym = nullptr;
     cudaDriverEntryPointQueryResult q;
     if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
         q == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<TensorMapEncodeFn>(sym);
+      g_driver_encode = reinterpret_cast<TensorMapEncodeFn>(sym);
   });
-  return fn;
+  return g_driver_encode ? &encode_tiled_remembered : nullptr;
 }
 
 int32_t *device_error_word() {
