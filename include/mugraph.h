@@ -137,11 +137,12 @@ enum {
   MG_OPT_ATTN_PERSISTENT = 6,   /* split-KV attention with more blocks than fit at once: 1 = one block per work item,
                                    2 = resident blocks that walk the work items (the default where it fits) */
   MG_OPT_KN_MATMUL_ENGINE = 7,  /* kernel-level float matmul: 1 = CUDA cores, 2 = tcgen05 (the default where it applies) */
-  MG_OPT_ATTN_DEPENDENT_LAUNCH = 8 /* split-KV attention: 1 = plain stream order, 2 = programmatic dependent launch (default) */
+  MG_OPT_ATTN_DEPENDENT_LAUNCH = 8 /* split-KV and dense attention: 1 = plain stream order, 2 = programmatic dependent launch (default) */
 };
 int mg_runtime_set_option(mg_runtime *rt, int32_t key, int32_t value);
 int mg_runtime_get_option(mg_runtime *rt, int32_t key, int32_t *value);
-/* The split-KV attention kernel starts fetching K and V while the previous kernel of its stream is still draining,
+/* The split-KV and the dense attention kernels start fetching Q, K and V while the previous kernel of their stream is
+ * still draining (the dense kernel's first blocks then run on the SMs that kernel's last round of blocks leaves idle),
  * when the library knows that kernel and knows it did not write them.  Launches, copies and fills that go through
  * this ABI are tracked.  A caller that writes a graph's input tensors with work of its own (a kernel given
  * data_ptr / fp_ptr) enqueued on `stream` says so with this call, after enqueueing that work and before the next

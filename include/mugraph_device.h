@@ -298,7 +298,7 @@ enum {
                                      2 = resident blocks that walk the work items (the default where it fits) */
   MGD_OPT_KN_MATMUL_ENGINE = 7,   /* kernel-level float matmul: 1 = CUDA cores, 2 = tcgen05 (the default where the
                                      operands are 16-byte aligned with rows of a multiple of 8 elements) */
-  MGD_OPT_ATTN_DEPENDENT_LAUNCH = 8, /* split-KV attention: 1 = plain stream order, 2 = programmatic dependent launch (default) */
+  MGD_OPT_ATTN_DEPENDENT_LAUNCH = 8, /* split-KV and dense attention: 1 = plain stream order, 2 = programmatic dependent launch (default) */
   MGD_OPT_COUNT = 9
 };
 int mgd_set_option(int32_t key, int32_t value);
