@@ -4,7 +4,7 @@
 // cpp_examples/multi_head_attn_prefill.cc:43-98; the division that follows it can be fused in): per 128 query rows
 //     S = Q K,  E = exp(S),  O' += E V,  R' += rowsum(E)        over KV tiles of 128
 // One query tile alone leaves the tensor pipe idle while its exp runs and the MUFU pipe idle while its MMAs run: per
-// KV tile both need about 1000 cycles (16 MMAs of 64 cycles; 16384 exps at 16 per cycle) and they depend on each
+// KV tile both need about 1100 cycles (16 MMAs of 68 cycles; 16384 exps at 16 per cycle) and they depend on each
 // other.  Here a block owns TWO query tiles of a head, each with its own exp warps, and one lane issues the MMAs of
 // both in the order
 //     S0(0) S1(0) | O0(0) S0(1) | O1(0) S1(1) | O0(1) S0(2) | ...
@@ -15,16 +15,22 @@
 // tile overwrites its own S values (packed 16-bit pairs: the thread that read S columns [64h, 64h+64) writes E to
 // [64h, 64h+32)) and is the A operand of the O' MMAs; S of the next KV tile is issued after them by the same lane, and
 // MMAs of one lane execute in order.  Q stays in shared memory (A operand of the S MMAs).
-// Shared memory: Q0, Q1 (32 KB each), a two-stage ring of K and V tiles (64 KB per stage), barriers.
+// Shared memory: Q0, Q1 (32 KB each), two-slot rings of K tiles and of V tiles (32 KB per slot, a barrier pair per
+// slot: a K slot is free after S1 of its tile, a V slot after O'1, each a whole round of MMAs before its next use),
+// barriers.  At the end the outputs are staged in the Q buffers (tile 0) and in ring stage 0 (tile 1) as swizzled
+// boxes and leave by TMA stores.
 // Operand layouts: all four combinations of K and V memory order; an operand whose N index is contiguous in memory is
 // described as MN-major.
 //
 // Warp roles (576 threads):
-//   warp 0, one lane   TMA producer: Q0, Q1 once; K and V tiles.
-//   warp 1             allocates / frees tensor memory; one lane issues every MMA and commits to mbarriers.
+//   warp 0, one lane   TMA producer: Q0, K_0, Q1, V_0, K_1, then V_t and K_{t+1} as their slots come free.
+//   warp 1             allocates / frees tensor memory; one lane runs the whole MMA loop and commits to mbarriers (its
+//                      instruction stream sets the pace of the tensor pipe: see the comments at the loop).
 //   warps 2-9          exp warps of tile 0: thread = (query row, 64-column half); tcgen05.ld its S half-row, exp, row
-//   warps 10-17        sum, pack, tcgen05.st E.  Same for tile 1.  At the end: O', R' (and O'/R' when the division
-//                      is fused) to global memory.
+//   warps 10-17        sum, pack, tcgen05.st E.  Same for tile 1.  At the end: O' (and O'/R' when the division is
+//                      fused) from tensor memory into the staging boxes, one thread per tile issues the TMA stores;
+//                      R' by plain stores.
+// Launch: with programmatic stream serialisation when the host asks for it (see the top of the kernel).
 // Every wait on an mbarrier is bounded; a role that gives up raises a block-wide flag, the others stop at their next
 // wait, the block frees its tensor memory, records the failure in the device status word and returns.
 #include "common.cuh"
