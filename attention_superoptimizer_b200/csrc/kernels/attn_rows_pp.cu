@@ -100,12 +100,19 @@ attn_rows_pp_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
   int const F = p.forloop;
 
   // Programmatic dependent launch (both are no-ops in a plain launch).  The kernel that follows may be scheduled as
-  // soon as every block of this one is running - with 1.73 blocks per SM in the prefill configuration its first
-  // blocks fill the SMs this kernel's second round leaves idle.  This kernel in turn reads Q, K and V before the
+  // soon as every block of this one has released it - with 1.73 blocks per SM in the prefill configuration at once,
+  // and its first blocks fill the SMs this kernel's second round leaves idle.  This kernel in turn reads Q, K and V before the
   // kernel in front of it has finished only when that kernel did not write them, and writes nothing to global
   // memory before it has finished (the exp warps wait in front of their stores).
+  // The early release is only given by a grid with more blocks than SMs.  Then a kernel two launches on cannot start
+  // before this one has completed: it needs every block of the kernel in between to have started, more than an SM
+  // each, so some of those have exited, and a block only exits after its wait on this kernel.  The host's check of
+  // the inputs (bit 1) looks at the launch directly in front and no further, which is all that can still be running.
+  uint32_t sm_total;
+  asm volatile("mov.u32 %0, %%nsmid;" : "=r"(sm_total));
+  bool const early_release = gridDim.x > sm_total;
   if (!(p.overlap & 2)) ptx::grid_dependency_wait();
-  ptx::grid_launch_dependents();
+  if (early_release) ptx::grid_launch_dependents();
 
   if (tid == 0) {
     STAMP(sh->t_block[0]);
@@ -356,6 +363,7 @@ attn_rows_pp_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
     if (ok) ok = mbar_wait(smem_u32(&sh->o_full[i]), 0, abort_flag);
     if (tid == 64) STAMP(sh->t_block[7]);
     ptx::grid_dependency_wait(); // the kernel in front may still be writing these outputs (a replay of the same graph)
+    if (!early_release) ptx::grid_launch_dependents();
     // O' (and O'/R') leave through shared memory: a thread owns half a row, so direct stores would put 16 bytes into
     // each of 32 rows per instruction; staged as [128 rows][64 columns] boxes (128-byte swizzle, one 128-byte row of a
     // box per thread) they go out as four TMA stores per tile.  Tile 0 stages into the Q buffers - both last read by
