@@ -451,25 +451,34 @@ bool KNReductionOp::profile(ProfileResult &r) { return profile_with_events(r, 16
 // "anything": the early loads are then left out for the next launch.
 namespace {
 struct Range { char const *lo, *hi; };
+struct Written { std::vector<Range> last, before; }; // by the launch in front, and by the one in front of that
 std::mutex g_track_mutex;
-std::unordered_map<void *, std::vector<Range>> g_last_outputs;
+std::unordered_map<void *, Written> g_last_outputs;
 constexpr size_t kMaxTrackedStreams = 4096; // the table is cleared beyond this: forgetting is the safe direction
+Range const kAnything{(char const *)nullptr, (char const *)UINTPTR_MAX};
 
+// Two launches deep: a kernel that is released as soon as its predecessor starts may run beside the launch in front of
+// that one (never beside an older one: see the release rules in attn_split.cu and attn_rows_pp.cu).
 void record_outputs(void *stream, std::vector<Range> const &r) {
   std::lock_guard<std::mutex> lock(g_track_mutex);
   if (g_last_outputs.size() > kMaxTrackedStreams) g_last_outputs.clear();
-  g_last_outputs[stream] = r;
+  auto it = g_last_outputs.find(stream);
+  if (it == g_last_outputs.end()) {
+    g_last_outputs[stream] = Written{r, {kAnything}}; // what ran before the first launch seen here is unknown
+    return;
+  }
+  it->second.before = std::move(it->second.last);
+  it->second.last = r;
 }
-void record_anything(void *stream) {
-  record_outputs(stream, {Range{(char const *)nullptr, (char const *)UINTPTR_MAX}});
-}
+void record_anything(void *stream) { record_outputs(stream, {kAnything}); }
 bool inputs_untouched(void *stream, std::vector<Range> const &inputs) {
   std::lock_guard<std::mutex> lock(g_track_mutex);
   auto it = g_last_outputs.find(stream);
   if (it == g_last_outputs.end()) return false; // unknown predecessor
-  for (Range const &a : it->second)
-    for (Range const &b : inputs)
-      if (a.lo < b.hi && b.lo < a.hi) return false;
+  for (std::vector<Range> const *written : {&it->second.last, &it->second.before})
+    for (Range const &a : *written)
+      for (Range const &b : inputs)
+        if (a.lo < b.hi && b.lo < a.hi) return false;
   return true;
 }
 Range range_of(void const *p, size_t bytes) { return Range{(char const *)p, (char const *)p + bytes}; }

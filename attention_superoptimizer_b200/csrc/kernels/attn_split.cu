@@ -116,6 +116,7 @@ struct AttnSplitParams {
   int32_t *tickets;     // one counter per (set, head)
   long long merged_set_stride;
   int early_loads;      // tile loads may be issued before the wait on the previous kernel of the stream
+  int early_release;    // the next kernel of the stream is released when this one starts, not after its wait
   int wait_limit;       // polls before a tile wait gives up
   int num_sets;
   int sum_runs;         // persistent with a fused merge whose partials are scratch: consecutive splits of a head
@@ -264,7 +265,11 @@ attn_split_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
   // With inputs that the previous kernel did not write, a block goes further: it also does its arithmetic before the
   // wait and only holds back its stores, so the previous kernel's write-out, tickets and merges run under it.
   // A walking block does the same up to the end of its first run.
+  // A launch that covers more than half of the GPU's block slots may release its successor at once: the kernel after
+  // that one cannot start before a block of the successor has exited, which happens after the successor's wait on
+  // this kernel - three launches are never in flight, and the host's check of the inputs looks two launches back.
   bool late_wait = p.early_loads != 0;
+  if (p.early_release) ptx::grid_launch_dependents();
   select_item(0);
   if (p.early_loads) {
     issue_first();
@@ -445,14 +450,22 @@ attn_split_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
   }
   if (!run_ends) continue; // (a run that goes on stays with its head: no new rows)
 
-  if (late_wait) { // from here on global memory is written
-    ptx::grid_dependency_wait();
-    ptx::grid_launch_dependents();
-    late_wait = false;
-  }
+  // A block that still owes the wait on the previous kernel of the stream takes it as late as it can: the sums over
+  // slices and tile groups below only touch shared memory, so each thread waits right in front of its first store
+  // to global memory, and the whole block once more behind the stores, where it also releases the next kernel
+  // unless it did so at its start.
+  bool const release_here = late_wait && !p.early_release;
+  auto wait_before_store = [&]() {
+    if (late_wait) {
+      ptx::grid_dependency_wait();
+      late_wait = false;
+    }
+  };
   if (failed) s_failed = 1;
   __syncthreads(); // also: every tile has been read, the stage memory may be reused as scratch
   if (s_failed) { // a bounded wait gave up: flag it and leave the outputs alone
+    wait_before_store();
+    if (release_here) ptx::grid_launch_dependents();
     if (tid == 0) {
       atomicExch(p.status, 1);
       // Tile loads still in flight must land before this block's shared memory is handed to another block:
@@ -543,6 +556,7 @@ attn_split_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
     if (MODE == kFingerprint) v = (uint16_t)((uint32_t)a % PQ);
     else if (MODE == kF16) { __half h = __float2half_rn((float)a); v = *reinterpret_cast<uint16_t *>(&h); }
     else { __nv_bfloat16 h = __float2bfloat16_rn((float)a); v = *reinterpret_cast<uint16_t *>(&h); }
+    wait_before_store();
     r_out[(size_t)row * p.splits] = v;
   }
   if (whole_head) __syncthreads();
@@ -575,15 +589,19 @@ attn_split_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_consta
           if (MODE == kFingerprint) packed = field_div((uint32_t)a0, (uint32_t)den % PQ) | (field_div((uint32_t)a1, (uint32_t)den % PQ) << 16);
           else if (MODE == kF16) packed = pack_f16((float)a0 / (float)den, (float)a1 / (float)den);
           else packed = pack_bf16((float)a0 / (float)den, (float)a1 / (float)den);
+          wait_before_store();
           *reinterpret_cast<uint32_t *>(final_out + (size_t)row * DH + c) = packed;
           continue;
         }
         if (MODE == kFingerprint) packed = (uint32_t)a0 | ((uint32_t)a1 << 16);
         else if (MODE == kF16) packed = pack_f16((float)a0, (float)a1);
         else packed = pack_bf16((float)a0, (float)a1);
+        wait_before_store();
         *reinterpret_cast<uint32_t *>(o_out + (size_t)row * out_ld + c) = packed;
       }
   }
+  wait_before_store(); // threads without a store; the tickets and the merge below are global memory traffic too
+  if (release_here) ptx::grid_launch_dependents();
 
   // ---- optional: the block that completes a head's splits merges the head's partials -----------------------
   if (p.merged_out != nullptr && !whole_head) {
@@ -801,7 +819,23 @@ static int launch_form_as(cudaLaunchConfig_t cfg, CUtensorMap const &kmap, CUten
     unsigned resident = (unsigned)per_sm * (unsigned)sm_count();
     if (resident < cfg.gridDim.x) cfg.gridDim.x = resident;
   }
-  cudaLaunchKernelEx(&cfg, attn_split_kernel<MODE, DH, FORM, PERSIST>, kmap, vmap, a);
+  AttnSplitParams launch = a;
+  if (!PERSIST && a.early_loads && cfg.numAttrs > 0) {
+    // the successor is released at once when this launch holds more than half of the block slots (see the kernel)
+    static std::atomic<int> slots_per_sm[kMaxDevices]; // occupancy of this instantiation at the last (threads, smem) seen
+    static std::atomic<uint64_t> slots_key[kMaxDevices];
+    uint64_t const key = ((uint64_t)cfg.blockDim.x << 32) | (uint64_t)cfg.dynamicSmemBytes;
+    int per_sm = slots_key[dev].load(std::memory_order_acquire) == key ? slots_per_sm[dev].load(std::memory_order_relaxed) : 0;
+    if (per_sm <= 0) {
+      if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attn_split_kernel<MODE, DH, FORM, PERSIST>, (int)cfg.blockDim.x,
+                                                        cfg.dynamicSmemBytes) != cudaSuccess || per_sm <= 0)
+        return check_launch("cudaOccupancyMaxActiveBlocksPerMultiprocessor(attn_split_kernel)");
+      slots_per_sm[dev].store(per_sm, std::memory_order_relaxed);
+      slots_key[dev].store(key, std::memory_order_release);
+    }
+    launch.early_release = 2ull * cfg.gridDim.x > (uint64_t)per_sm * (uint64_t)sm_count() ? 1 : 0;
+  }
+  cudaLaunchKernelEx(&cfg, attn_split_kernel<MODE, DH, FORM, PERSIST>, kmap, vmap, launch);
   return check_launch("attn_split_kernel");
 }
 
@@ -883,6 +917,7 @@ static int launch_split(mgd_attn_split const *p, void const *q, void const *k, v
   a.tickets = opts ? opts->tickets : nullptr;
   a.merged_set_stride = opts ? opts->merged_set_stride : 0;
   a.early_loads = opts && (opts->overlap & 2) ? 1 : 0;
+  a.early_release = 0; // decided per launch form, where the block slots are known
   // MGD_OPT_WAIT_LIMIT: 0 = default, 1 = give up without polling, n = n polls
   int const forced_limit = option(MGD_OPT_WAIT_LIMIT);
   a.wait_limit = forced_limit == 0 ? ptx::kWaitLimit : (forced_limit == 1 ? 0 : forced_limit);
