@@ -143,7 +143,8 @@ int mg_runtime_set_option(mg_runtime *rt, int32_t key, int32_t value);
 int mg_runtime_get_option(mg_runtime *rt, int32_t key, int32_t *value);
 /* The split-KV and the dense attention kernels start fetching Q, K and V while the previous kernel of their stream is
  * still draining (the dense kernel's first blocks then run on the SMs that kernel's last round of blocks leaves idle),
- * when the library knows that kernel and knows it did not write them.  Launches, copies and fills that go through
+ * when the library knows the two launches in front of it and knows they did not write them (a kernel may run beside
+ * both, never beside an older one).  Launches, copies and fills that go through
  * this ABI are tracked.  A caller that writes a graph's input tensors with work of its own (a kernel given
  * data_ptr / fp_ptr) enqueued on `stream` says so with this call, after enqueueing that work and before the next
  * launch of this library on that stream; that launch then reads its inputs only after the stream's previous kernel
