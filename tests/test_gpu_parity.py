@@ -572,6 +572,46 @@ def test_prefill_calls_back_to_back_on_one_stream(runtime):
         assert not np.array_equal(chained, stale)
 
 
+def test_decode_calls_released_early_wait_for_an_older_producer(runtime):
+    """A one-call decode launch (128 blocks) releases its successor as soon as it starts, so a call may run beside the
+    TWO calls in front of it.  Three graphs on one stream, nothing synchronised: A writes a tensor, X has nothing to do
+    with it, B takes its Q from A's output.  B must see what the A two launches in front of it wrote, every time."""
+    import torch
+    B_, M, D, L, S, F = 8, 4, 128, 4096, 16, 4
+    runtime.set_max_smem(BIG)
+    runtime.set_specialisation(2)
+    rng = np.random.default_rng(4242)
+    stream = torch.cuda.Stream()
+    sh = stream.cuda_stream
+    with mg.PyGraph(runtime) as ga, mg.PyGraph(runtime) as gx, mg.PyGraph(runtime) as gb:
+        built = []
+        for g in (ga, gx, gb):
+            ins, o, f, plans = build_gqa(g, B_, M, D, L, S, F)
+            (q, k, v), mem = float_inputs(rng, B_, M, D, L, mg.DmemColumnMajor, mg.DmemColumnMajor, mg.float16)
+            for t, a in zip(ins, mem):
+                t.upload_data(to_bits(a, mg.float16))
+            built.append((ins, f))
+        (qa, _, _), fa = built[0]
+        _, fb = built[2]
+        gb.rebind_input(0, data_ptr=fa[0].pod.data_ptr)
+        results = []
+        for trial in range(4):
+            q_new = float_inputs(rng, B_, M, D, L, mg.DmemColumnMajor, mg.DmemColumnMajor, mg.float16)[1][0]
+            qa.upload_data(to_bits(q_new, mg.float16))
+            for _ in range(3):  # A, X, B back to back; B's input is rewritten by every A
+                ga.run(stream=sh, sync=False)
+                gx.run(stream=sh, sync=False)
+                gb.run(stream=sh, sync=False)
+            stream.synchronize()
+            mg.synchronize()
+            chained = from_bits(fb[0].download_data(), mg.float16).copy()
+            ga.run()
+            gb.run()
+            assert np.array_equal(chained, from_bits(fb[0].download_data(), mg.float16)), "trial %d" % trial
+            results.append(chained)
+        assert not np.array_equal(results[0], results[1])
+
+
 def test_prefill_fingerprint_uses_interpreter(runtime):
     """The same dense graph in fingerprint mode (128 x 128 x 128 mod-PQ contractions) stays bit-exact."""
     H, SQ, D, L = 1, 128, 128, 256
