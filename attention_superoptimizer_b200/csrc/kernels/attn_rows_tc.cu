@@ -145,6 +145,7 @@ struct Barriers {
 template <bool BF16>
 __global__ void __launch_bounds__(320)
 attn_rows_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
+                    const __grid_constant__ CUtensorMap o_map, const __grid_constant__ CUtensorMap d_map,
                     const __grid_constant__ RowsParams p) {
   extern __shared__ unsigned char smem_dyn[];
   unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
@@ -375,37 +376,52 @@ attn_rows_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
     asm volatile("bar.sync 1, 256;" ::: "memory");
     float const total = bar->row_sums[0][row] + bar->row_sums[1][row];
     if (ok) ok = mbar_wait(smem_u32(&bar->o_full), 0, abort_flag);
+    // O' (and O'/R') leave through shared memory: a thread owns half a row, so direct stores would put 16 bytes into
+    // each of 32 rows per instruction; staged in ring stage 0 (free once every MMA is done) as [128 rows][64 columns]
+    // boxes with the 128-byte swizzle - one 128-byte row of a box per thread - they go out as TMA stores.
+    unsigned char *const stage = smem; // [O' | O'/R'] x [column half] boxes of 16 KB
     if (ok) {
       tc_fence_after();
-      size_t const row_off = ((size_t)head * p.seq_q + q0 + row) * kD + col_base;
-      uint16_t *o_row = static_cast<uint16_t *>(p.o_acc) + row_off;
-      uint16_t *d_row = p.o_div ? static_cast<uint16_t *>(p.o_div) + row_off : nullptr;
       float const inv = 1.0f / total;
+      uint32_t const row_at = (uint32_t)(half * kSubTile + row * 128);
 #pragma unroll
       for (int c = 0; c < 2; c++) {
         uint32_t v[32];
         tmem_ld32(tmem_o + lane_base + col_base + (uint32_t)(c * 32), v);
 #pragma unroll
         for (int q = 0; q < 4; q++) {
+          uint32_t const at = row_at + (uint32_t)((((c * 4 + q) ^ (row & 7)) << 4));
           uint4 out;
           out.x = pack2<BF16>(__uint_as_float(v[8 * q]), __uint_as_float(v[8 * q + 1]));
           out.y = pack2<BF16>(__uint_as_float(v[8 * q + 2]), __uint_as_float(v[8 * q + 3]));
           out.z = pack2<BF16>(__uint_as_float(v[8 * q + 4]), __uint_as_float(v[8 * q + 5]));
           out.w = pack2<BF16>(__uint_as_float(v[8 * q + 6]), __uint_as_float(v[8 * q + 7]));
-          *reinterpret_cast<uint4 *>(o_row + c * 32 + q * 8) = out;
-          if (d_row) {
+          *reinterpret_cast<uint4 *>(stage + at) = out;
+          if (p.o_div) {
             out.x = pack2<BF16>(__uint_as_float(v[8 * q]) * inv, __uint_as_float(v[8 * q + 1]) * inv);
             out.y = pack2<BF16>(__uint_as_float(v[8 * q + 2]) * inv, __uint_as_float(v[8 * q + 3]) * inv);
             out.z = pack2<BF16>(__uint_as_float(v[8 * q + 4]) * inv, __uint_as_float(v[8 * q + 5]) * inv);
             out.w = pack2<BF16>(__uint_as_float(v[8 * q + 6]) * inv, __uint_as_float(v[8 * q + 7]) * inv);
-            *reinterpret_cast<uint4 *>(d_row + c * 32 + q * 8) = out;
+            *reinterpret_cast<uint4 *>(stage + kOperand + at) = out;
           }
         }
       }
+      ptx::fence_proxy_async_smem(); // the staged boxes are read by the TMA engine
       if (half == 0) {
         uint32_t r2 = pack2<BF16>(total, 0.f);
         static_cast<uint16_t *>(p.r_acc)[(size_t)head * p.seq_q + q0 + row] = (uint16_t)(r2 & 0xFFFF);
       }
+    }
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    if (warp == 2 && lane == 0 && ok && !*abort_flag) {
+      uint32_t const src = smem_u32(stage);
+      ptx::tma_store_3d(&o_map, src, 0, q0, head);
+      ptx::tma_store_3d(&o_map, src + kSubTile, 64, q0, head);
+      if (p.o_div) {
+        ptx::tma_store_3d(&d_map, src + kOperand, 0, q0, head);
+        ptx::tma_store_3d(&d_map, src + kOperand + kSubTile, 64, q0, head);
+      }
+      ptx::tma_store_commit_and_wait_read(); // the boxes must stay until the engine has read them
     }
   }
 
@@ -491,7 +507,9 @@ int mgd_launch_attn_rows_float_overlapped(const mgd_attn_rows *p, const void *q,
   if (use_two_tile_kernel(p)) return pp::launch(p, q, k, v, o_acc, r_acc, o_div, overlap, stream);
   if (!tc::rows_supported(p)) return set_error(MG_ERR_UNSUPPORTED, "dense attention: shape or layout not supported");
   CUtensorMap km, vm;
-  bool ok = tc::make_map(&km, k, p->heads, p->kv_len, tc::kD) && tc::make_map(&vm, v, p->heads, tc::kD, p->kv_len);
+  CUtensorMap om, dm; // outputs: [heads][seq_q][d], the same box geometry
+  bool ok = tc::make_map(&km, k, p->heads, p->kv_len, tc::kD) && tc::make_map(&vm, v, p->heads, tc::kD, p->kv_len) &&
+            tc::make_map(&om, o_acc, p->heads, p->seq_q, tc::kD) && tc::make_map(&dm, o_div ? o_div : o_acc, p->heads, p->seq_q, tc::kD);
   if (!ok) return set_error(MG_ERR_CUDA, "dense attention: cuTensorMapEncodeTiled failed");
   tc::RowsParams a;
   a.q = q; a.o_acc = o_acc; a.r_acc = r_acc; a.o_div = o_div;
@@ -508,8 +526,8 @@ int mgd_launch_attn_rows_float_overlapped(const mgd_attn_rows *p, const void *q,
     if (e != cudaSuccess) return check_launch("cudaFuncSetAttribute(attn_rows_tc_kernel)");
     configured[bf16] = true;
   }
-  if (bf16) tc::attn_rows_tc_kernel<true><<<blocks, 320, smem, (cudaStream_t)stream>>>(km, vm, a);
-  else tc::attn_rows_tc_kernel<false><<<blocks, 320, smem, (cudaStream_t)stream>>>(km, vm, a);
+  if (bf16) tc::attn_rows_tc_kernel<true><<<blocks, 320, smem, (cudaStream_t)stream>>>(km, vm, om, dm, a);
+  else tc::attn_rows_tc_kernel<false><<<blocks, 320, smem, (cudaStream_t)stream>>>(km, vm, om, dm, a);
   return check_launch("attn_rows_tc_kernel");
 }
 }
